@@ -1,0 +1,277 @@
+/*
+ * poplibs_b200 -- C ABI of the B200 (sm_100a) implementation of the poplin
+ * dense-contraction path: poplin::matMul and poplin::convolution (forward,
+ * backward-data and weight-update passes).
+ *
+ * The reference exposes this path only as deferred C++ graph construction
+ * (include/poplin/MatMul.hpp, include/poplin/Convolution.hpp: calls take
+ * poplar::Graph / Tensor / program::Sequence and nothing runs until
+ * poplar::Engine::run).  This header is the layer underneath the C++ drop-in
+ * (include/poplin/ *.hpp of this repository): plain pointers and sizes, device
+ * buffers owned by the caller, every call enqueues its kernels on the
+ * context's CUDA stream.  It is also what a foreign-language binding (ctypes,
+ * cgo, JNI) would bind.
+ *
+ * Conventions
+ *  - Every function returns 0 on success and a non-zero plb_status otherwise;
+ *    plb_last_error() gives the message for the calling thread (the C++ layer
+ *    rethrows it as poputil::poplibs_error / poplar::invalid_option, the
+ *    exception types of include/poputil/exceptions.hpp:17-21 and
+ *    include/poputil/OptionParsing.hpp:204-221).
+ *  - Pointers named d_* are device pointers, h_* host pointers.
+ *  - Device layouts (they mirror poplin's internal channels-innermost shapes,
+ *    lib/poplin/ConvUtilInternal.cpp:147-175):
+ *      activations  [N][field...][G*C]           ("NHWC")
+ *      weights      [G][kernel...][Co][Ci]
+ *    plb_rearrange_* convert from / to the external shapes of
+ *    include/poplin/Convolution.hpp:81-82, 323-328 ([N][G*C][field...],
+ *    [G][Co][Ci][kernel...]).
+ *  - There is no CPU fallback: if no CUDA device / sm_100a kernel image is
+ *    available the calls fail with PLB_ERR_CUDA.
+ */
+#ifndef POPLIBS_B200_H
+#define POPLIBS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define PLB_API __attribute__((visibility("default")))
+#else
+#define PLB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PLB_MAX_FIELD_DIMS 3
+
+typedef enum plb_status {
+  PLB_OK = 0,
+  PLB_ERR_INVALID_PARAMS = 1, /* poputil::poplibs_error in the C++ layer      */
+  PLB_ERR_INVALID_OPTION = 2, /* poplar::invalid_option                       */
+  PLB_ERR_UNSUPPORTED = 3,    /* valid poplin request this build cannot run   */
+  PLB_ERR_CUDA = 4,           /* CUDA runtime / driver failure                */
+  PLB_ERR_KERNEL = 5,         /* a kernel reported a non-zero status word     */
+  PLB_ERR_OUT_OF_MEMORY = 6   /* poplar::graph_memory_allocation_error        */
+} plb_status;
+
+/* poplar::Type values used on this path (HALF, FLOAT, QUARTER). */
+typedef enum plb_dtype { PLB_HALF = 0, PLB_FLOAT = 1, PLB_QUARTER = 2 } plb_dtype;
+
+/* poplin::Pass (lib/poplin/ConvOptions.hpp:13-24). */
+typedef enum plb_pass {
+  PLB_PASS_NONE = 0,
+  PLB_PASS_NONE_MATMUL,
+  PLB_PASS_INFERENCE_FWD,
+  PLB_PASS_TRAINING_FWD,
+  PLB_PASS_TRAINING_BWD,
+  PLB_PASS_TRAINING_WU,
+  PLB_PASS_FC_INFERENCE_FWD,
+  PLB_PASS_FC_TRAINING_FWD,
+  PLB_PASS_FC_TRAINING_BWD,
+  PLB_PASS_FC_TRAINING_WU
+} plb_pass;
+
+PLB_API const char *plb_last_error(void);
+/* Library version and the GPU architecture the kernels were compiled for. */
+PLB_API const char *plb_version(void);
+
+/* ------------------------------------------------------------------------ */
+/* Context: one CUDA device + stream + kernel status word + scratch memory.  */
+/* Stands in for the poplar::Graph / Engine pair a poplin call is made on    */
+/* (tools/single_conv_layer.cpp:585-587, 1169, 1326-1340).                   */
+/* ------------------------------------------------------------------------ */
+typedef struct plb_context plb_context;
+
+PLB_API int plb_context_create(int device, plb_context **out);
+/* Same, on a CUDA stream the caller owns (cudaStream_t passed as void*). */
+PLB_API int plb_context_create_on_stream(int device, void *cuda_stream, plb_context **out);
+PLB_API void plb_context_destroy(plb_context *ctx);
+PLB_API void *plb_context_stream(plb_context *ctx);
+/* Blocks until all enqueued work is done, then checks the kernel status word:
+ * returns PLB_ERR_KERNEL if any kernel gave up on a bounded wait. */
+PLB_API int plb_synchronize(plb_context *ctx);
+/* Number of kernels this context has launched so far. */
+PLB_API uint64_t plb_launch_count(const plb_context *ctx);
+
+/* Device memory helpers for callers without an allocator of their own. */
+PLB_API int plb_malloc(plb_context *ctx, size_t bytes, void **d_ptr);
+PLB_API int plb_free(plb_context *ctx, void *d_ptr);
+PLB_API int plb_memcpy_h2d(plb_context *ctx, void *d_dst, const void *h_src, size_t bytes);
+PLB_API int plb_memcpy_d2h(plb_context *ctx, void *h_dst, const void *d_src, size_t bytes);
+PLB_API int plb_memset(plb_context *ctx, void *d_dst, int value, size_t bytes);
+
+/* ------------------------------------------------------------------------ */
+/* poplin::matMul / matMulGrouped / matMulAcc                                */
+/* (include/poplin/MatMul.hpp:110-420, lib/poplin/MatMul.cpp:368-404,        */
+/*  782-856; tools/general_matrix_multiply.cpp:355-370)                      */
+/* ------------------------------------------------------------------------ */
+typedef struct plb_matmul_desc {
+  uint32_t groups, m, k, n;
+  int32_t input_type;   /* plb_dtype: PLB_HALF or PLB_QUARTER              */
+  int32_t output_type;  /* plb_dtype: PLB_HALF or PLB_FLOAT                */
+  int32_t partials_type;/* plb_dtype: option "partialsType"; accumulation is
+                           always fp32 on this hardware, PLB_HALF is accepted
+                           and widened (lib/poplin/ConvValidation.cpp:28-51) */
+  int32_t transpose_a;  /* A is stored [g][k][m] ("--left-matrix-op transpose") */
+  int32_t transpose_b;  /* B is stored [g][n][k] ("--right-matrix-op transpose",
+                           also the layout preArrangeMatMulInputRHS produces) */
+  float alpha, beta;    /* D = beta*C + alpha*A*B (matMulAcc: beta=1, alpha=k) */
+  int32_t scale_a, scale_b; /* QUARTER metadata exponents: value = stored*2^scale
+                               (poplar::QuarterMetadata), range [-32, 31]  */
+  int64_t lda, ldb, ldc;/* row strides in elements; 0 = densely packed     */
+} plb_matmul_desc;
+
+/* d_c may be NULL when beta == 0; d_c may alias d_d.  A, B, C, D are
+ * [groups][rows][cols] row-major with the leading dimensions above. */
+PLB_API int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a,
+               const void *d_b, const void *d_c, void *d_d);
+/* Same through host buffers: uploads A, B (and C), runs, downloads D and
+ * synchronises.  This is the end-to-end call the benchmark times. */
+PLB_API int plb_matmul_host(plb_context *ctx, const plb_matmul_desc *desc, const void *h_a,
+                    const void *h_b, const void *h_c, void *h_d);
+
+/* ------------------------------------------------------------------------ */
+/* poplin::ConvParams (include/poplin/ConvParams.hpp:16-224), flattened.     */
+/* Channel counts are per group, as in the reference.                        */
+/* ------------------------------------------------------------------------ */
+typedef struct plb_conv_params {
+  int32_t input_type;  /* plb_dtype */
+  int32_t output_type; /* plb_dtype */
+  uint32_t num_field_dims; /* 1..3 */
+  uint32_t batch;
+  uint32_t groups;
+  uint32_t in_chans_per_group;
+  uint32_t out_chans_per_group;
+  uint32_t field[PLB_MAX_FIELD_DIMS];
+  uint32_t kernel[PLB_MAX_FIELD_DIMS];
+  /* InputTransform of the activations */
+  uint32_t in_trunc_lo[PLB_MAX_FIELD_DIMS], in_trunc_hi[PLB_MAX_FIELD_DIMS];
+  uint32_t in_dilation[PLB_MAX_FIELD_DIMS];
+  uint32_t in_pad_lo[PLB_MAX_FIELD_DIMS], in_pad_hi[PLB_MAX_FIELD_DIMS];
+  uint32_t in_flip[PLB_MAX_FIELD_DIMS];
+  /* InputTransform of the kernel */
+  uint32_t k_trunc_lo[PLB_MAX_FIELD_DIMS], k_trunc_hi[PLB_MAX_FIELD_DIMS];
+  uint32_t k_dilation[PLB_MAX_FIELD_DIMS];
+  uint32_t k_pad_lo[PLB_MAX_FIELD_DIMS], k_pad_hi[PLB_MAX_FIELD_DIMS];
+  uint32_t k_flip[PLB_MAX_FIELD_DIMS];
+  /* OutputTransform */
+  uint32_t out_trunc_lo[PLB_MAX_FIELD_DIMS], out_trunc_hi[PLB_MAX_FIELD_DIMS];
+  uint32_t stride[PLB_MAX_FIELD_DIMS];
+  uint32_t out_pad_lo[PLB_MAX_FIELD_DIMS], out_pad_hi[PLB_MAX_FIELD_DIMS];
+} plb_conv_params;
+
+/* ConvParams::validate (lib/poplin/ConvParams.cpp:172-266). */
+PLB_API int plb_conv_validate(const plb_conv_params *p);
+/* ConvParams::getOutputSize (lib/poplin/ConvParams.cpp:670-698). */
+PLB_API int plb_conv_output_field(const plb_conv_params *p, uint32_t out_field[PLB_MAX_FIELD_DIMS]);
+/* poplin::getInputIndex (lib/poplin/ConvUtil.cpp:234-292): index of the input
+ * element read by (output, kernel) in one dimension, or -1 for padding. */
+PLB_API int plb_conv_input_index(const plb_conv_params *p, uint32_t dim, uint32_t out_index,
+                         uint32_t kernel_index);
+/* getNumberOfMACs (lib/poplin/PerformanceEstimation.hpp:1641-1666): products
+ * with padding are not counted.  getFwdFlops = 2 * this
+ * (lib/poplin/Convolution.cpp:3217-3225). */
+PLB_API uint64_t plb_conv_macs(const plb_conv_params *p);
+
+/* Options that change what is computed or how it is planned
+ * (lib/poplin/ConvOptions.cpp:105-152).  Zero-initialise for the defaults. */
+typedef struct plb_conv_options {
+  int32_t pass;          /* plb_pass */
+  int32_t partials_type; /* plb_dtype; see plb_matmul_desc.partials_type */
+  /* plan constraints this implementation understands; 0 = planner's choice */
+  int32_t tile_n;        /* output channels per CTA tile: 64, 128 or 256     */
+  int32_t split_k;       /* CTAs that share one output tile (weight update)  */
+  int32_t reserved[6];
+} plb_conv_options;
+
+/* out = conv(in, weights) (+ bias), poplin::convolution
+ * (include/poplin/Convolution.hpp:345-384, lib/poplin/Convolution.cpp:3128-3215).
+ * d_bias may be NULL (poplin::addBias fused, include/poplin/Convolution.hpp:536-544). */
+PLB_API int plb_conv_fwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                 const void *d_in, const void *d_weights, const float *d_bias, void *d_out);
+/* Gradient w.r.t. the input from the FORWARD pass's params and weights:
+ * what convolution(zDeltas, weights, getGradientParams(p), true) computes
+ * (lib/poplin/ConvUtil.cpp:728-795, lib/poplin/Convolution.cpp:3077-3086). */
+PLB_API int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                 const void *d_out_grads, const void *d_weights, void *d_in_grads);
+/* Weight gradient of the FORWARD pass's params, poplin::calculateWeightDeltas
+ * (include/poplin/Convolution.hpp:460-466, lib/poplin/Convolution.cpp:3436-3507).
+ * d_weight_grads has the device weights layout and type p->input_type
+ * (lib/poplin/Convolution.cpp:3537); if d_weight_grads_f32 is not NULL the
+ * fp32 sums are also left there (what a multi-GPU caller all-reduces). */
+PLB_API int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                const void *d_acts, const void *d_out_grads, void *d_weight_grads,
+                float *d_weight_grads_f32);
+/* weights += scale * weight_grads_f32, cast to the weights' type
+ * (popops::scaledAddTo in convolutionWeightUpdate, lib/poplin/Convolution.cpp:3509-3522). */
+PLB_API int plb_scaled_add_to(plb_context *ctx, int32_t dtype, void *d_weights,
+                      const float *d_deltas_f32, float scale, size_t count);
+/* fp32 -> half/float cast of a buffer (popops::cast after a reduction). */
+PLB_API int plb_cast_from_f32(plb_context *ctx, int32_t dtype, void *d_dst, const float *d_src,
+                      size_t count);
+
+/* Host-buffer variants (device layouts, host memory): upload, run, download,
+ * synchronise. */
+PLB_API int plb_conv_fwd_host(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                      const void *h_in, const void *h_weights, const float *h_bias, void *h_out);
+
+/* ------------------------------------------------------------------------ */
+/* Layout changes between poplin's external shapes and the device layouts.   */
+/* ------------------------------------------------------------------------ */
+/* [N][C][field...] -> [N][field...][C] and back; elem_bytes is 1, 2 or 4. */
+PLB_API int plb_rearrange_acts_to_device(plb_context *ctx, uint32_t elem_bytes, uint32_t batch,
+                                 uint32_t chans, uint64_t field_elems, const void *d_src,
+                                 void *d_dst);
+PLB_API int plb_rearrange_acts_from_device(plb_context *ctx, uint32_t elem_bytes, uint32_t batch,
+                                   uint32_t chans, uint64_t field_elems, const void *d_src,
+                                   void *d_dst);
+/* [G][Co][Ci][kernel...] -> [G][kernel...][Co][Ci] and back. */
+PLB_API int plb_rearrange_weights_to_device(plb_context *ctx, uint32_t elem_bytes, uint32_t groups,
+                                    uint32_t out_chans, uint32_t in_chans, uint64_t kernel_elems,
+                                    const void *d_src, void *d_dst);
+PLB_API int plb_rearrange_weights_from_device(plb_context *ctx, uint32_t elem_bytes, uint32_t groups,
+                                      uint32_t out_chans, uint32_t in_chans,
+                                      uint64_t kernel_elems, const void *d_src, void *d_dst);
+/* poplin::weightsTransposeChansFlipXY on device-layout weights
+ * (include/poplin/Convolution.hpp:434-439): [G][k...][Co][Ci] ->
+ * [G][flipped k...][Ci][Co]. */
+PLB_API int plb_weights_transpose_chans_flip_xy(plb_context *ctx, uint32_t elem_bytes, uint32_t groups,
+                                        uint32_t out_chans, uint32_t in_chans,
+                                        uint64_t kernel_elems, const void *d_src, void *d_dst);
+/* Row-major matrix transpose [rows][cols] -> [cols][rows] per group
+ * (poplin::transposeGroupedMatrix, include/poplin/MatMul.hpp:600-606). */
+PLB_API int plb_transpose_matrix(plb_context *ctx, uint32_t elem_bytes, uint32_t groups, uint32_t rows,
+                         uint32_t cols, const void *d_src, void *d_dst);
+
+/* ------------------------------------------------------------------------ */
+/* Planner: the CTA-level plan chosen for a contraction (the role of         */
+/* poplin::getPlan, lib/poplin/ConvPlan.cpp:1877-1923, and what               */
+/* poplin::reportPlanInfo prints, include/poplin/Convolution.hpp:584-594).    */
+/* ------------------------------------------------------------------------ */
+typedef struct plb_plan {
+  int32_t kernel;      /* 0 = implicit GEMM (fwd/bwd/matmul), 1 = weight update, 2 = small-channel */
+  int32_t tile_m;      /* output pixels (rows) per CTA tile                  */
+  int32_t tile_n;      /* output channels (columns) per CTA tile             */
+  int32_t tile_k_bytes;/* bytes of K per pipeline stage                      */
+  int32_t box_w, box_h, box_n; /* pixel box of one activation TMA load       */
+  int32_t stages;      /* shared-memory pipeline depth                       */
+  int32_t split_k;     /* CTAs per output tile                               */
+  int32_t grid;        /* CTAs launched                                      */
+  int32_t tiles;       /* output tiles                                       */
+  int32_t b_mn_major;  /* right operand fed as an MN-major matrix            */
+  uint64_t flops;      /* 2 * MACs (padding excluded)                        */
+  uint64_t bytes;      /* operands read once + output written once           */
+  uint64_t workspace_bytes;
+} plb_plan;
+
+PLB_API int plb_matmul_plan(const plb_matmul_desc *desc, plb_plan *plan);
+PLB_API int plb_conv_plan(const plb_conv_params *p, const plb_conv_options *opt, int32_t pass,
+                  plb_plan *plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POPLIBS_B200_H */

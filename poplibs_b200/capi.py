@@ -1,0 +1,308 @@
+"""ctypes binding of include/poplibs_b200.h (one-to-one, no logic of its own)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libpoplibs_b200.so")
+
+HALF, FLOAT, QUARTER = 0, 1, 2
+PASS_NONE, PASS_NONE_MATMUL, PASS_INFERENCE_FWD, PASS_TRAINING_FWD, PASS_TRAINING_BWD, \
+    PASS_TRAINING_WU, PASS_FC_INFERENCE_FWD, PASS_FC_TRAINING_FWD, PASS_FC_TRAINING_BWD, \
+    PASS_FC_TRAINING_WU = range(10)
+MAX_DIMS = 3
+_U3 = C.c_uint32 * MAX_DIMS
+
+
+class PlbError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[plb status {code}] {message}")
+        self.code = code
+        self.message = message
+
+
+class MatmulDesc(C.Structure):
+    _fields_ = [("groups", C.c_uint32), ("m", C.c_uint32), ("k", C.c_uint32), ("n", C.c_uint32),
+                ("input_type", C.c_int32), ("output_type", C.c_int32), ("partials_type", C.c_int32),
+                ("transpose_a", C.c_int32), ("transpose_b", C.c_int32),
+                ("alpha", C.c_float), ("beta", C.c_float),
+                ("scale_a", C.c_int32), ("scale_b", C.c_int32),
+                ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64)]
+
+    @staticmethod
+    def make(m, k, n, groups=1, input_type=HALF, output_type=HALF, transpose_a=False,
+             transpose_b=False, alpha=1.0, beta=0.0, scale_a=0, scale_b=0, partials_type=FLOAT):
+        d = MatmulDesc()
+        d.groups, d.m, d.k, d.n = groups, m, k, n
+        d.input_type, d.output_type, d.partials_type = input_type, output_type, partials_type
+        d.transpose_a, d.transpose_b = int(transpose_a), int(transpose_b)
+        d.alpha, d.beta = alpha, beta
+        d.scale_a, d.scale_b = scale_a, scale_b
+        return d
+
+
+class ConvParams(C.Structure):
+    _fields_ = [("input_type", C.c_int32), ("output_type", C.c_int32),
+                ("num_field_dims", C.c_uint32), ("batch", C.c_uint32), ("groups", C.c_uint32),
+                ("in_chans_per_group", C.c_uint32), ("out_chans_per_group", C.c_uint32),
+                ("field", _U3), ("kernel", _U3),
+                ("in_trunc_lo", _U3), ("in_trunc_hi", _U3), ("in_dilation", _U3),
+                ("in_pad_lo", _U3), ("in_pad_hi", _U3), ("in_flip", _U3),
+                ("k_trunc_lo", _U3), ("k_trunc_hi", _U3), ("k_dilation", _U3),
+                ("k_pad_lo", _U3), ("k_pad_hi", _U3), ("k_flip", _U3),
+                ("out_trunc_lo", _U3), ("out_trunc_hi", _U3), ("stride", _U3),
+                ("out_pad_lo", _U3), ("out_pad_hi", _U3)]
+
+    _VECS = ("in_trunc_lo", "in_trunc_hi", "in_dilation", "in_pad_lo", "in_pad_hi", "in_flip",
+             "k_trunc_lo", "k_trunc_hi", "k_dilation", "k_pad_lo", "k_pad_hi", "k_flip",
+             "out_trunc_lo", "out_trunc_hi", "stride", "out_pad_lo", "out_pad_hi")
+
+    @staticmethod
+    def make(batch, field: Sequence[int], kernel: Sequence[int], in_chans, out_chans, groups=1,
+             input_type=HALF, output_type=HALF, **transforms):
+        """``transforms`` are per-dimension lists named like the struct fields
+        (in_pad_lo, stride, k_dilation, ...); scalars are broadcast."""
+        p = ConvParams()
+        nd = len(field)
+        p.input_type, p.output_type = input_type, output_type
+        p.num_field_dims, p.batch, p.groups = nd, batch, groups
+        p.in_chans_per_group, p.out_chans_per_group = in_chans, out_chans
+        for i in range(nd):
+            p.field[i], p.kernel[i] = field[i], kernel[i]
+            p.in_dilation[i] = p.k_dilation[i] = p.stride[i] = 1
+        for name, val in transforms.items():
+            if name == "padding":
+                names = ("in_pad_lo", "in_pad_hi")
+            elif name in ConvParams._VECS:
+                names = (name,)
+            else:
+                raise TypeError(f"unknown ConvParams field {name}")
+            if val is None:
+                continue
+            vals = [int(val)] * nd if isinstance(val, (int, bool)) else [int(v) for v in val]
+            for nm in names:
+                arr = getattr(p, nm)
+                for i in range(nd):
+                    arr[i] = vals[i]
+        return p
+
+    def output_field(self):
+        out = _U3()
+        _check(lib().plb_conv_output_field(C.byref(self), out))
+        return [int(out[i]) for i in range(self.num_field_dims)]
+
+    def macs(self) -> int:
+        return int(lib().plb_conv_macs(C.byref(self)))
+
+
+class ConvOptions(C.Structure):
+    _fields_ = [("pass_", C.c_int32), ("partials_type", C.c_int32), ("tile_n", C.c_int32),
+                ("split_k", C.c_int32), ("reserved", C.c_int32 * 6)]
+
+    @staticmethod
+    def make(pass_=PASS_NONE, partials_type=FLOAT, tile_n=0, split_k=0):
+        o = ConvOptions()
+        o.pass_, o.partials_type, o.tile_n, o.split_k = pass_, partials_type, tile_n, split_k
+        return o
+
+
+class Plan(C.Structure):
+    _fields_ = [("kernel", C.c_int32), ("tile_m", C.c_int32), ("tile_n", C.c_int32),
+                ("tile_k_bytes", C.c_int32), ("box_w", C.c_int32), ("box_h", C.c_int32),
+                ("box_n", C.c_int32), ("stages", C.c_int32), ("split_k", C.c_int32),
+                ("grid", C.c_int32), ("tiles", C.c_int32), ("b_mn_major", C.c_int32),
+                ("flops", C.c_uint64), ("bytes", C.c_uint64), ("workspace_bytes", C.c_uint64)]
+
+    def as_dict(self):
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
+_LIB = None
+
+# every symbol include/poplibs_b200.h declares
+SYMBOLS = (
+    "plb_last_error", "plb_version", "plb_context_create", "plb_context_create_on_stream",
+    "plb_context_destroy", "plb_context_stream", "plb_synchronize", "plb_launch_count",
+    "plb_malloc", "plb_free", "plb_memcpy_h2d", "plb_memcpy_d2h", "plb_memset",
+    "plb_matmul", "plb_matmul_host", "plb_conv_validate", "plb_conv_output_field",
+    "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_conv_bwd", "plb_conv_wu",
+    "plb_scaled_add_to", "plb_cast_from_f32", "plb_conv_fwd_host",
+    "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
+    "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
+    "plb_weights_transpose_chans_flip_xy", "plb_transpose_matrix", "plb_matmul_plan",
+    "plb_conv_plan",
+)
+
+
+def lib():
+    """Loads libpoplibs_b200.so; raises if it is missing (there is no fallback)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python -m poplibs_b200.build` "
+            "(needs nvcc); poplibs_b200 has no CPU fallback")
+    L = C.CDLL(_LIB_PATH)
+    vp, u32, u64, i32, sz, f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_size_t, C.c_float
+    CP, MP, OP, PP = C.POINTER(ConvParams), C.POINTER(MatmulDesc), C.POINTER(ConvOptions), C.POINTER(Plan)
+    L.plb_last_error.restype = C.c_char_p
+    L.plb_version.restype = C.c_char_p
+    L.plb_context_create.argtypes = [C.c_int, C.POINTER(vp)]
+    L.plb_context_create_on_stream.argtypes = [C.c_int, vp, C.POINTER(vp)]
+    L.plb_context_destroy.argtypes = [vp]
+    L.plb_context_destroy.restype = None
+    L.plb_context_stream.argtypes = [vp]
+    L.plb_context_stream.restype = vp
+    L.plb_synchronize.argtypes = [vp]
+    L.plb_launch_count.argtypes = [vp]
+    L.plb_launch_count.restype = u64
+    L.plb_malloc.argtypes = [vp, sz, C.POINTER(vp)]
+    L.plb_free.argtypes = [vp, vp]
+    L.plb_memcpy_h2d.argtypes = [vp, vp, vp, sz]
+    L.plb_memcpy_d2h.argtypes = [vp, vp, vp, sz]
+    L.plb_memset.argtypes = [vp, vp, C.c_int, sz]
+    L.plb_matmul.argtypes = [vp, MP, vp, vp, vp, vp]
+    L.plb_matmul_host.argtypes = [vp, MP, vp, vp, vp, vp]
+    L.plb_conv_validate.argtypes = [CP]
+    L.plb_conv_output_field.argtypes = [CP, _U3]
+    L.plb_conv_input_index.argtypes = [CP, u32, u32, u32]
+    L.plb_conv_macs.argtypes = [CP]
+    L.plb_conv_macs.restype = u64
+    L.plb_conv_fwd.argtypes = [vp, CP, OP, vp, vp, vp, vp]
+    L.plb_conv_bwd.argtypes = [vp, CP, OP, vp, vp, vp]
+    L.plb_conv_wu.argtypes = [vp, CP, OP, vp, vp, vp, vp]
+    L.plb_scaled_add_to.argtypes = [vp, i32, vp, vp, f32, sz]
+    L.plb_cast_from_f32.argtypes = [vp, i32, vp, vp, sz]
+    L.plb_conv_fwd_host.argtypes = [vp, CP, OP, vp, vp, vp, vp]
+    for name in ("plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device"):
+        getattr(L, name).argtypes = [vp, u32, u32, u32, u64, vp, vp]
+    for name in ("plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
+                 "plb_weights_transpose_chans_flip_xy"):
+        getattr(L, name).argtypes = [vp, u32, u32, u32, u32, u64, vp, vp]
+    L.plb_transpose_matrix.argtypes = [vp, u32, u32, u32, u32, vp, vp]
+    L.plb_matmul_plan.argtypes = [MP, PP]
+    L.plb_conv_plan.argtypes = [CP, OP, i32, PP]
+    _LIB = L
+    return L
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise PlbError(rc, lib().plb_last_error().decode("utf-8", "replace"))
+
+
+def _ptr(x) -> Optional[int]:
+    """Device/host address of a torch tensor, numpy array, int or None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    raise TypeError(f"cannot take the address of {type(x)}")
+
+
+class Context:
+    """plb_context: one device, one stream."""
+
+    def __init__(self, device: int = 0, stream: Optional[int] = None):
+        self._h = C.c_void_p()
+        if stream is None:
+            _check(lib().plb_context_create(device, C.byref(self._h)))
+        else:
+            _check(lib().plb_context_create_on_stream(device, C.c_void_p(stream), C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().plb_context_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    @property
+    def stream(self) -> int:
+        return int(lib().plb_context_stream(self._h) or 0)
+
+    def synchronize(self):
+        _check(lib().plb_synchronize(self._h))
+
+    def launch_count(self) -> int:
+        return int(lib().plb_launch_count(self._h))
+
+    # ---- hot path ---------------------------------------------------------
+    def matmul(self, desc: MatmulDesc, a, b, c, d):
+        _check(lib().plb_matmul(self._h, C.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(d)))
+
+    def matmul_host(self, desc: MatmulDesc, a, b, c, d):
+        _check(lib().plb_matmul_host(self._h, C.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(d)))
+
+    def conv_fwd(self, p: ConvParams, x, w, out, bias=None, opt: Optional[ConvOptions] = None):
+        _check(lib().plb_conv_fwd(self._h, C.byref(p), C.byref(opt) if opt else None,
+                                  _ptr(x), _ptr(w), _ptr(bias), _ptr(out)))
+
+    def conv_fwd_host(self, p: ConvParams, x, w, out, bias=None, opt: Optional[ConvOptions] = None):
+        _check(lib().plb_conv_fwd_host(self._h, C.byref(p), C.byref(opt) if opt else None,
+                                       _ptr(x), _ptr(w), _ptr(bias), _ptr(out)))
+
+    def conv_bwd(self, p: ConvParams, dy, w, dx, opt: Optional[ConvOptions] = None):
+        _check(lib().plb_conv_bwd(self._h, C.byref(p), C.byref(opt) if opt else None,
+                                  _ptr(dy), _ptr(w), _ptr(dx)))
+
+    def conv_wu(self, p: ConvParams, x, dy, dw, dw_f32=None, opt: Optional[ConvOptions] = None):
+        _check(lib().plb_conv_wu(self._h, C.byref(p), C.byref(opt) if opt else None,
+                                 _ptr(x), _ptr(dy), _ptr(dw), _ptr(dw_f32)))
+
+    def scaled_add_to(self, dtype, weights, deltas_f32, scale, count):
+        _check(lib().plb_scaled_add_to(self._h, dtype, _ptr(weights), _ptr(deltas_f32), scale, count))
+
+    def cast_from_f32(self, dtype, dst, src, count):
+        _check(lib().plb_cast_from_f32(self._h, dtype, _ptr(dst), _ptr(src), count))
+
+    # ---- layouts ----------------------------------------------------------
+    def acts_to_device(self, elem_bytes, batch, chans, field_elems, src, dst):
+        _check(lib().plb_rearrange_acts_to_device(self._h, elem_bytes, batch, chans, field_elems,
+                                                  _ptr(src), _ptr(dst)))
+
+    def acts_from_device(self, elem_bytes, batch, chans, field_elems, src, dst):
+        _check(lib().plb_rearrange_acts_from_device(self._h, elem_bytes, batch, chans, field_elems,
+                                                    _ptr(src), _ptr(dst)))
+
+    def weights_to_device(self, elem_bytes, groups, co, ci, kelems, src, dst):
+        _check(lib().plb_rearrange_weights_to_device(self._h, elem_bytes, groups, co, ci, kelems,
+                                                     _ptr(src), _ptr(dst)))
+
+    def weights_from_device(self, elem_bytes, groups, co, ci, kelems, src, dst):
+        _check(lib().plb_rearrange_weights_from_device(self._h, elem_bytes, groups, co, ci, kelems,
+                                                       _ptr(src), _ptr(dst)))
+
+    def weights_transpose_chans_flip_xy(self, elem_bytes, groups, co, ci, kelems, src, dst):
+        _check(lib().plb_weights_transpose_chans_flip_xy(self._h, elem_bytes, groups, co, ci,
+                                                         kelems, _ptr(src), _ptr(dst)))
+
+    def transpose_matrix(self, elem_bytes, groups, rows, cols, src, dst):
+        _check(lib().plb_transpose_matrix(self._h, elem_bytes, groups, rows, cols, _ptr(src), _ptr(dst)))
+
+
+def matmul_plan(desc: MatmulDesc) -> Plan:
+    plan = Plan()
+    _check(lib().plb_matmul_plan(C.byref(desc), C.byref(plan)))
+    return plan
+
+
+def conv_plan(p: ConvParams, pass_: int = PASS_TRAINING_FWD, opt: Optional[ConvOptions] = None) -> Plan:
+    plan = Plan()
+    _check(lib().plb_conv_plan(C.byref(p), C.byref(opt) if opt else None, pass_, C.byref(plan)))
+    return plan

@@ -1,0 +1,526 @@
+// C ABI entry points of the contraction path: matMul, convolution forward and
+// backward-data.  Each maps its poplin-level description onto one or more
+// launches of the implicit-GEMM kernel (igemm_sm100.cuh).
+#include <cmath>
+
+#include "conv_geometry.h"
+#include "runtime.h"
+
+namespace plb {
+
+int launchScaleRows(plb_context *ctx, void *out, const void *c, float beta, bool out_f32,
+                    uint32_t rows, uint32_t cols, long long ldo, long long ldc);
+
+namespace {
+
+int checkMatmulDesc(const plb_matmul_desc &d) {
+  if (d.input_type != PLB_HALF && d.input_type != PLB_QUARTER)
+    return fail(PLB_ERR_INVALID_PARAMS, "matMul input type must be half or quarter");
+  if (d.output_type != PLB_HALF && d.output_type != PLB_FLOAT)
+    return fail(PLB_ERR_INVALID_PARAMS, "matMul output type must be half or float");
+  if (d.input_type == PLB_QUARTER && d.output_type != PLB_HALF)
+    // lib/poplin/ConvValidation.cpp:53-69: quarter input requires half output
+    return fail(PLB_ERR_INVALID_PARAMS, "Output type must be half when input type is quarter");
+  if (d.partials_type != PLB_HALF && d.partials_type != PLB_FLOAT)
+    return fail(PLB_ERR_INVALID_OPTION, "partialsType must be half or float");
+  if (d.scale_a < -32 || d.scale_a > 31 || d.scale_b < -32 || d.scale_b > 31)
+    return fail(PLB_ERR_INVALID_PARAMS, "quarter metadata scale must be in [-32, 31]");
+  return PLB_OK;
+}
+
+struct Ld {
+  long long a, b, c;
+};
+
+Ld leadingDims(const plb_matmul_desc &d) {
+  Ld l;
+  l.a = d.lda ? d.lda : (d.transpose_a ? d.m : d.k);
+  l.b = d.ldb ? d.ldb : (d.transpose_b ? d.k : d.n);
+  l.c = d.ldc ? d.ldc : d.n;
+  return l;
+}
+
+// Builds the igemm problem of one group of a matrix product.  `a` is [m][k]
+// (row stride lda), `b` either [n][k] (b_is_nk) or [k][n].
+IgemmProblem gemmProblem(const plb_matmul_desc &d, const void *a, long long lda, const void *b,
+                         long long ldb, bool b_is_nk, const void *c, void *out, long long ldc) {
+  IgemmProblem p;
+  const size_t es = dtypeBytes(d.input_type);
+  p.fp8 = d.input_type == PLB_QUARTER;
+  p.b_mn = !b_is_nk;
+  p.act = a;
+  p.act_dims[0] = d.k;
+  p.act_dims[1] = d.m;
+  p.act_strides[0] = uint64_t(lda) * es;
+  p.act_strides[1] = uint64_t(lda) * es * std::max<uint32_t>(d.m, 1);
+  p.act_strides[2] = p.act_strides[1];
+  p.wgt = b;
+  if (b_is_nk) {
+    p.wgt_dims[0] = d.k;
+    p.wgt_dims[1] = d.n;
+    p.wgt_strides[0] = uint64_t(ldb) * es;
+    p.wgt_strides[1] = uint64_t(ldb) * es * std::max<uint32_t>(d.n, 1);
+  } else {
+    p.wgt_dims[0] = d.n;
+    p.wgt_dims[1] = d.k;
+    p.wgt_strides[0] = uint64_t(ldb) * es;
+    p.wgt_strides[1] = uint64_t(ldb) * es * std::max<uint32_t>(d.k, 1);
+  }
+  p.out_w = int(d.m);
+  p.n_total = int(d.n);
+  p.k_per_tap = int(d.k);
+  p.out = out;
+  p.ldc = ldc;
+  p.addend = c;
+  p.ld_addend = ldc;
+  p.alpha = d.alpha;
+  if (p.fp8) p.alpha *= std::ldexp(1.0f, d.scale_a + d.scale_b);
+  p.beta = d.beta;
+  p.out_f32 = d.output_type == PLB_FLOAT;
+  return p;
+}
+
+uint64_t gemmBytes(const plb_matmul_desc &d) {
+  const uint64_t es = dtypeBytes(d.input_type), os = dtypeBytes(d.output_type);
+  return uint64_t(d.groups) * (uint64_t(d.m) * d.k * es + uint64_t(d.k) * d.n * es +
+                               uint64_t(d.m) * d.n * os * (d.beta != 0.f ? 2 : 1));
+}
+
+// ---- convolution --------------------------------------------------------------------
+
+struct ConvShape {
+  unsigned nd;
+  int H, W, OH, OW;      // input / output field (H = 1 for 1-D)
+  int KH, KW;
+  int padH, padW, dilH, dilW, strH, strW, flipH, flipW;
+};
+
+int igemmConvShape(const plb_conv_params &p, ConvShape *s) {
+  const std::string err = validate(p);
+  if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+  if (p.num_field_dims > 2)
+    return fail(PLB_ERR_UNSUPPORTED, "3-D convolutions are not implemented on this path yet");
+  if (p.input_type != PLB_HALF && p.input_type != PLB_QUARTER)
+    return fail(PLB_ERR_UNSUPPORTED, "convolution input type must be half or quarter");
+  if (p.output_type != PLB_HALF && p.output_type != PLB_FLOAT)
+    return fail(PLB_ERR_INVALID_PARAMS, "convolution output type must be half or float");
+  if (p.input_type == PLB_QUARTER && p.output_type != PLB_HALF)
+    return fail(PLB_ERR_INVALID_PARAMS, "Output type must be half when input type is quarter");
+  for (unsigned d = 0; d != p.num_field_dims; ++d) {
+    if (p.in_trunc_lo[d] || p.in_trunc_hi[d] || p.in_dilation[d] != 1 || p.in_flip[d] ||
+        p.k_trunc_lo[d] || p.k_trunc_hi[d] || p.k_pad_lo[d] || p.k_pad_hi[d] ||
+        p.out_trunc_lo[d] || p.out_trunc_hi[d] || p.out_pad_lo[d] || p.out_pad_hi[d])
+      return fail(PLB_ERR_UNSUPPORTED,
+                  "input truncation/dilation/flip, kernel truncation/padding and output "
+                  "truncation/padding are not implemented on this path yet");
+  }
+  s->nd = p.num_field_dims;
+  const unsigned hd = p.num_field_dims == 2 ? 0 : ~0u, wd = p.num_field_dims - 1;
+  auto get = [&](const uint32_t *v, unsigned d, int dflt) { return d == ~0u ? dflt : int(v[d]); };
+  s->H = get(p.field, hd, 1);
+  s->W = get(p.field, wd, 1);
+  s->KH = get(p.kernel, hd, 1);
+  s->KW = get(p.kernel, wd, 1);
+  s->padH = get(p.in_pad_lo, hd, 0);
+  s->padW = get(p.in_pad_lo, wd, 0);
+  s->dilH = get(p.k_dilation, hd, 1);
+  s->dilW = get(p.k_dilation, wd, 1);
+  s->strH = get(p.stride, hd, 1);
+  s->strW = get(p.stride, wd, 1);
+  s->flipH = get(p.k_flip, hd, 0);
+  s->flipW = get(p.k_flip, wd, 0);
+  s->OH = hd == ~0u ? 1 : int(outputSize(p, hd));
+  s->OW = int(outputSize(p, wd));
+  return PLB_OK;
+}
+
+uint64_t convBytes(const plb_conv_params &p, const ConvShape &s, int pass) {
+  const uint64_t es = dtypeBytes(p.input_type), os = dtypeBytes(p.output_type);
+  const uint64_t in = uint64_t(p.batch) * s.H * s.W * p.groups * p.in_chans_per_group;
+  const uint64_t out = uint64_t(p.batch) * s.OH * s.OW * p.groups * p.out_chans_per_group;
+  const uint64_t w = uint64_t(p.groups) * s.KH * s.KW * p.in_chans_per_group * p.out_chans_per_group;
+  // a 1x1 kernel with stride reads only every stride-th pixel
+  uint64_t in_read = in;
+  if (s.KH == 1 && s.KW == 1) in_read = uint64_t(p.batch) * s.OH * s.OW * p.groups * p.in_chans_per_group;
+  switch (pass) {
+    case PLB_PASS_TRAINING_BWD: return out * es + w * es + in * os;
+    case PLB_PASS_TRAINING_WU: return in * es + out * es + w * es;
+    default: return in_read * es + w * es + out * os;
+  }
+}
+
+// Forward problem of group g.
+int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const ConvShape &s,
+                   unsigned g, const void *in, const void *w, const float *bias, void *out,
+                   IgemmProblem *q) {
+  const size_t es = dtypeBytes(p.input_type), os = dtypeBytes(p.output_type);
+  const uint64_t ctot = uint64_t(p.groups) * p.in_chans_per_group;
+  const uint64_t cotot = uint64_t(p.groups) * p.out_chans_per_group;
+  const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
+  IgemmProblem r;
+  r.fp8 = p.input_type == PLB_QUARTER;
+  r.act = static_cast<const uint8_t *>(in) + size_t(g) * ci * es;
+  const bool pointwise = s.KH == 1 && s.KW == 1 && s.padH == 0 && s.padW == 0;
+  if (pointwise) {
+    // a strided 1x1 convolution reads a sub-lattice: describe only that
+    r.act_dims[0] = ci;
+    r.act_dims[1] = uint64_t(s.OW);
+    r.act_dims[2] = uint64_t(s.OH);
+    r.act_dims[3] = p.batch;
+    r.act_strides[0] = uint64_t(s.strW) * ctot * es;
+    r.act_strides[1] = uint64_t(s.strH) * s.W * ctot * es;
+    r.act_strides[2] = uint64_t(s.H) * s.W * ctot * es;
+  } else {
+    r.act_dims[0] = ci;
+    r.act_dims[1] = uint64_t(s.W);
+    r.act_dims[2] = uint64_t(s.H);
+    r.act_dims[3] = p.batch;
+    r.act_strides[0] = ctot * es;
+    r.act_strides[1] = uint64_t(s.W) * ctot * es;
+    r.act_strides[2] = uint64_t(s.H) * s.W * ctot * es;
+    r.stride_h = s.strH;
+    r.stride_w = s.strW;
+    r.act_elem_strides[1] = uint32_t(s.strW);
+    r.act_elem_strides[2] = uint32_t(s.strH);
+  }
+  r.wgt = static_cast<const uint8_t *>(w) + size_t(g) * s.KH * s.KW * co * ci * es;
+  r.wgt_dims[0] = ci;
+  r.wgt_dims[1] = co;
+  r.wgt_dims[2] = uint64_t(s.KH) * s.KW;
+  r.wgt_strides[0] = ci * es;
+  r.wgt_strides[1] = co * ci * es;
+  r.out_w = s.OW;
+  r.out_h = s.OH;
+  r.out_n = int(p.batch);
+  r.n_total = int(co);
+  r.k_per_tap = int(ci);
+  r.taps_h = s.KH;
+  r.taps_w = s.KW;
+  r.pad_h = s.padH;
+  r.pad_w = s.padW;
+  r.dil_h = s.dilH;
+  r.dil_w = s.dilW;
+  r.flip_h = s.flipH;
+  r.flip_w = s.flipW;
+  r.out = static_cast<uint8_t *>(out) + size_t(g) * co * os;
+  r.ldc = (long long)cotot;
+  r.bias = bias ? bias + size_t(g) * co : nullptr;
+  r.out_f32 = p.output_type == PLB_FLOAT;
+  r.force_tile_n = opt ? opt->tile_n : 0;
+  *q = r;
+  return PLB_OK;
+}
+
+// Backward-data problem of group g (stride 1): the output gradients take the
+// activations' role, the taps are traversed in the opposite order, the padding
+// becomes (k-1)*dilation - padding, and the stored [tap][Co][Ci] weights are
+// read as a K-by-N (MN-major) operand with K = Co, N = Ci.
+int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const ConvShape &s,
+                   unsigned g, const void *dy, const void *w, void *dx, bool weights_transposed,
+                   IgemmProblem *q) {
+  const size_t es = dtypeBytes(p.input_type), os = dtypeBytes(p.output_type);
+  const uint64_t ctot = uint64_t(p.groups) * p.in_chans_per_group;
+  const uint64_t cotot = uint64_t(p.groups) * p.out_chans_per_group;
+  const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
+  IgemmProblem r;
+  r.fp8 = p.input_type == PLB_QUARTER;
+  r.act = static_cast<const uint8_t *>(dy) + size_t(g) * co * es;
+  r.act_dims[0] = co;
+  r.act_dims[1] = uint64_t(s.OW);
+  r.act_dims[2] = uint64_t(s.OH);
+  r.act_dims[3] = p.batch;
+  r.act_strides[0] = cotot * es;
+  r.act_strides[1] = uint64_t(s.OW) * cotot * es;
+  r.act_strides[2] = uint64_t(s.OH) * s.OW * cotot * es;
+  r.wgt = static_cast<const uint8_t *>(w) + size_t(g) * s.KH * s.KW * co * ci * es;
+  if (weights_transposed) {
+    // [tap flipped][Ci][Co]: a K-major operand, taps already reversed
+    r.wgt_dims[0] = co;
+    r.wgt_dims[1] = ci;
+    r.wgt_strides[0] = co * es;
+    r.flip_h = s.flipH;
+    r.flip_w = s.flipW;
+  } else {
+    r.b_mn = true;
+    r.wgt_dims[0] = ci;
+    r.wgt_dims[1] = co;
+    r.wgt_strides[0] = ci * es;
+    r.flip_h = !s.flipH;
+    r.flip_w = !s.flipW;
+  }
+  r.wgt_dims[2] = uint64_t(s.KH) * s.KW;
+  r.wgt_strides[1] = co * ci * es;
+  r.out_w = s.W;
+  r.out_h = s.H;
+  r.out_n = int(p.batch);
+  r.n_total = int(ci);
+  r.k_per_tap = int(co);
+  r.taps_h = s.KH;
+  r.taps_w = s.KW;
+  r.pad_h = (s.KH - 1) * s.dilH - s.padH;
+  r.pad_w = (s.KW - 1) * s.dilW - s.padW;
+  r.dil_h = s.dilH;
+  r.dil_w = s.dilW;
+  r.out = static_cast<uint8_t *>(dx) + size_t(g) * ci * os;
+  r.ldc = (long long)ctot;
+  r.out_f32 = p.output_type == PLB_FLOAT;
+  r.force_tile_n = opt ? opt->tile_n : 0;
+  *q = r;
+  return PLB_OK;
+}
+
+}  // namespace
+}  // namespace plb
+
+using namespace plb;
+
+extern "C" {
+
+int plb_matmul_plan(const plb_matmul_desc *desc, plb_plan *plan) {
+  if (!desc || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  if (int rc = checkMatmulDesc(*desc)) return rc;
+  *plan = plb_plan{};
+  plan->flops = 2ull * desc->groups * desc->m * desc->k * desc->n;
+  plan->bytes = gemmBytes(*desc);
+  if (desc->groups == 0 || desc->m == 0 || desc->n == 0 || desc->k == 0) return PLB_OK;
+  const Ld ld = leadingDims(*desc);
+  const bool b_is_nk = desc->transpose_b || desc->input_type == PLB_QUARTER;
+  IgemmProblem p = gemmProblem(*desc, nullptr, ld.a, nullptr, ld.b, b_is_nk, nullptr, nullptr, ld.c);
+  if (int rc = planIgemm(p, 148, plan)) return rc;
+  const size_t es = dtypeBytes(desc->input_type);
+  if (desc->transpose_a) plan->workspace_bytes += size_t(desc->groups) * desc->m * desc->k * es;
+  if (!desc->transpose_b && desc->input_type == PLB_QUARTER)
+    plan->workspace_bytes += size_t(desc->groups) * desc->n * desc->k * es;
+  return PLB_OK;
+}
+
+int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a, const void *d_b,
+               const void *d_c, void *d_d) {
+  if (int rc = activate(ctx)) return rc;
+  if (!desc) return fail(PLB_ERR_INVALID_PARAMS, "null descriptor");
+  const plb_matmul_desc &d = *desc;
+  if (int rc = checkMatmulDesc(d)) return rc;
+  if (d.groups == 0 || d.m == 0 || d.n == 0) return PLB_OK;
+  if (d.beta != 0.f && d_c == nullptr)
+    return fail(PLB_ERR_INVALID_PARAMS, "beta != 0 needs a C matrix");
+  const Ld ld = leadingDims(d);
+  const size_t es = dtypeBytes(d.input_type), os = dtypeBytes(d.output_type);
+  if (d.k == 0) {
+    // empty reduction: D = beta * C
+    for (uint32_t g = 0; g < d.groups; ++g) {
+      const size_t off = size_t(g) * d.m * ld.c * os;
+      if (int rc = launchScaleRows(ctx, static_cast<uint8_t *>(d_d) + off,
+                                   d_c ? static_cast<const uint8_t *>(d_c) + off : nullptr,
+                                   d.beta, d.output_type == PLB_FLOAT, d.m, d.n, ld.c, ld.c))
+        return rc;
+    }
+    return PLB_OK;
+  }
+  // operand layouts the kernel takes directly: A as [m][k]; B as [n][k], or
+  // (half only) [k][n].  Anything else goes through a transpose into scratch.
+  const uint8_t *a = static_cast<const uint8_t *>(d_a);
+  const uint8_t *b = static_cast<const uint8_t *>(d_b);
+  long long lda = ld.a, ldb = ld.b;
+  bool b_is_nk = d.transpose_b != 0;
+  size_t scratch_bytes = 0;
+  const size_t a_bytes = size_t(d.groups) * d.m * d.k * es, b_bytes = size_t(d.groups) * d.n * d.k * es;
+  const bool transpose_b_now = !d.transpose_b && d.input_type == PLB_QUARTER;
+  if (d.transpose_a) scratch_bytes += (a_bytes + 255) & ~size_t(255);
+  if (transpose_b_now) scratch_bytes += b_bytes;
+  if (scratch_bytes) {
+    void *ws = nullptr;
+    if (int rc = scratch(ctx, 0, scratch_bytes, &ws)) return rc;
+    uint8_t *cursor = static_cast<uint8_t *>(ws);
+    if (d.transpose_a) {
+      if (ld.a != (long long)d.m)
+        return fail(PLB_ERR_UNSUPPORTED, "transposed A must be densely packed");
+      if (int rc = plb_transpose_matrix(ctx, uint32_t(es), d.groups, d.k, d.m, d_a, cursor)) return rc;
+      a = cursor;
+      lda = d.k;
+      cursor += (a_bytes + 255) & ~size_t(255);
+    }
+    if (transpose_b_now) {
+      if (ld.b != (long long)d.n)
+        return fail(PLB_ERR_UNSUPPORTED, "quarter B in [k][n] layout must be densely packed");
+      if (int rc = plb_transpose_matrix(ctx, uint32_t(es), d.groups, d.k, d.n, d_b, cursor)) return rc;
+      b = cursor;
+      ldb = d.k;
+      b_is_nk = true;
+    }
+  }
+  for (uint32_t g = 0; g < d.groups; ++g) {
+    const uint8_t *ag = a + size_t(g) * d.m * lda * es;
+    const uint8_t *bg = b + size_t(g) * (b_is_nk ? d.n : d.k) * ldb * es;
+    const size_t coff = size_t(g) * d.m * ld.c * os;
+    IgemmProblem p = gemmProblem(d, ag, lda, bg, ldb, b_is_nk,
+                                 d_c ? static_cast<const uint8_t *>(d_c) + coff : nullptr,
+                                 static_cast<uint8_t *>(d_d) + coff, ld.c);
+    plb_plan plan{};
+    if (int rc = planIgemm(p, ctx->sm_count, &plan)) return rc;
+    if (int rc = launchIgemm(ctx, p, plan)) return rc;
+  }
+  return PLB_OK;
+}
+
+int plb_matmul_host(plb_context *ctx, const plb_matmul_desc *desc, const void *h_a,
+                    const void *h_b, const void *h_c, void *h_d) {
+  if (int rc = activate(ctx)) return rc;
+  if (!desc) return fail(PLB_ERR_INVALID_PARAMS, "null descriptor");
+  const plb_matmul_desc &d = *desc;
+  if (int rc = checkMatmulDesc(d)) return rc;
+  const Ld ld = leadingDims(d);
+  const size_t es = dtypeBytes(d.input_type), os = dtypeBytes(d.output_type);
+  const size_t a_bytes = size_t(d.groups) * (d.transpose_a ? d.k : d.m) * ld.a * es;
+  const size_t b_bytes = size_t(d.groups) * (d.transpose_b ? d.n : d.k) * ld.b * es;
+  const size_t c_bytes = size_t(d.groups) * d.m * ld.c * os;
+  void *da = nullptr, *db = nullptr, *dc = nullptr, *dd = nullptr;
+  if (int rc = scratch(ctx, 1, a_bytes + 16, &da)) return rc;
+  if (int rc = scratch(ctx, 2, b_bytes + 16, &db)) return rc;
+  if (int rc = scratch(ctx, 3, c_bytes + 16, &dd)) return rc;
+  if (d.beta != 0.f) {
+    if (!h_c) return fail(PLB_ERR_INVALID_PARAMS, "beta != 0 needs a C matrix");
+    if (int rc = scratch(ctx, 4, c_bytes + 16, &dc)) return rc;
+    if (int rc = plb_memcpy_h2d(ctx, dc, h_c, c_bytes)) return rc;
+  }
+  if (int rc = plb_memcpy_h2d(ctx, da, h_a, a_bytes)) return rc;
+  if (int rc = plb_memcpy_h2d(ctx, db, h_b, b_bytes)) return rc;
+  if (int rc = plb_matmul(ctx, desc, da, db, dc, dd)) return rc;
+  if (int rc = plb_memcpy_d2h(ctx, h_d, dd, c_bytes)) return rc;
+  return plb_synchronize(ctx);
+}
+
+// ---------------------------------------------------------------------------
+
+int plb_conv_validate(const plb_conv_params *p) {
+  if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  const std::string err = validate(*p);
+  return err.empty() ? PLB_OK : fail(PLB_ERR_INVALID_PARAMS, err);
+}
+
+int plb_conv_output_field(const plb_conv_params *p, uint32_t out_field[PLB_MAX_FIELD_DIMS]) {
+  if (int rc = plb_conv_validate(p)) return rc;
+  for (unsigned d = 0; d != p->num_field_dims; ++d) out_field[d] = uint32_t(outputSize(*p, d));
+  return PLB_OK;
+}
+
+int plb_conv_input_index(const plb_conv_params *p, uint32_t dim, uint32_t out_index,
+                         uint32_t kernel_index) {
+  if (!p || dim >= p->num_field_dims) return -1;
+  return inputIndex(*p, dim, out_index, kernel_index);
+}
+
+uint64_t plb_conv_macs(const plb_conv_params *p) { return p ? numberOfMacs(*p) : 0; }
+
+int plb_conv_plan(const plb_conv_params *p, const plb_conv_options *opt, int32_t pass,
+                  plb_plan *plan) {
+  if (!p || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  ConvShape s;
+  if (int rc = igemmConvShape(*p, &s)) return rc;
+  *plan = plb_plan{};
+  IgemmProblem q;
+  if (pass == PLB_PASS_TRAINING_BWD) {
+    if (int rc = convBwdProblem(*p, opt, s, 0, nullptr, nullptr, nullptr,
+                                p->input_type == PLB_QUARTER, &q))
+      return rc;
+  } else {
+    if (int rc = convFwdProblem(*p, opt, s, 0, nullptr, nullptr, nullptr, nullptr, &q)) return rc;
+  }
+  if (q.n_total > 0 && q.out_w > 0 && q.out_h > 0 && q.out_n > 0 && q.k_per_tap > 0)
+    if (int rc = planIgemm(q, 148, plan)) return rc;
+  plan->flops = 2 * numberOfMacs(*p);
+  plan->bytes = convBytes(*p, s, pass);
+  return PLB_OK;
+}
+
+int plb_conv_fwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                 const void *d_in, const void *d_weights, const float *d_bias, void *d_out) {
+  if (int rc = activate(ctx)) return rc;
+  if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  ConvShape s;
+  if (int rc = igemmConvShape(*p, &s)) return rc;
+  if (p->batch == 0 || p->groups == 0 || p->out_chans_per_group == 0 || s.OH == 0 || s.OW == 0)
+    return PLB_OK;
+  if (p->in_chans_per_group == 0) {
+    // nothing to accumulate: the output is the bias (or zero)
+    return fail(PLB_ERR_UNSUPPORTED, "zero input channels are not implemented on this path yet");
+  }
+  if (s.strH > 1 || s.strW > 1) {
+    const bool pointwise = s.KH == 1 && s.KW == 1 && s.padH == 0 && s.padW == 0;
+    if (!pointwise && (s.strH > 8 || s.strW > 8))
+      return fail(PLB_ERR_UNSUPPORTED, "strides above 8 are not implemented for k > 1");
+  }
+  for (unsigned g = 0; g < p->groups; ++g) {
+    IgemmProblem q;
+    if (int rc = convFwdProblem(*p, opt, s, g, d_in, d_weights, d_bias, d_out, &q)) return rc;
+    plb_plan plan{};
+    if (int rc = planIgemm(q, ctx->sm_count, &plan)) return rc;
+    if (int rc = launchIgemm(ctx, q, plan)) return rc;
+  }
+  return PLB_OK;
+}
+
+int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                 const void *d_out_grads, const void *d_weights, void *d_in_grads) {
+  if (int rc = activate(ctx)) return rc;
+  if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  ConvShape s;
+  if (int rc = igemmConvShape(*p, &s)) return rc;
+  if (s.strH != 1 || s.strW != 1)
+    return fail(PLB_ERR_UNSUPPORTED,
+                "backward pass of a strided convolution is not implemented on this path yet");
+  if (p->batch == 0 || p->groups == 0 || p->in_chans_per_group == 0 || s.H == 0 || s.W == 0)
+    return PLB_OK;
+  const size_t es = dtypeBytes(p->input_type);
+  const void *w = d_weights;
+  bool transposed = false;
+  if (p->input_type == PLB_QUARTER) {
+    // no MN-major path for 8-bit operands: transpose + flip the (small) weights
+    const size_t bytes = size_t(p->groups) * s.KH * s.KW * p->in_chans_per_group *
+                         p->out_chans_per_group * es;
+    void *ws = nullptr;
+    if (int rc = scratch(ctx, 0, bytes, &ws)) return rc;
+    if (int rc = plb_weights_transpose_chans_flip_xy(ctx, uint32_t(es), p->groups,
+                                                     p->out_chans_per_group, p->in_chans_per_group,
+                                                     uint64_t(s.KH) * s.KW, d_weights, ws))
+      return rc;
+    w = ws;
+    transposed = true;
+  }
+  for (unsigned g = 0; g < p->groups; ++g) {
+    IgemmProblem q;
+    if (int rc = convBwdProblem(*p, opt, s, g, d_out_grads, w, d_in_grads, transposed, &q)) return rc;
+    plb_plan plan{};
+    if (int rc = planIgemm(q, ctx->sm_count, &plan)) return rc;
+    if (int rc = launchIgemm(ctx, q, plan)) return rc;
+  }
+  return PLB_OK;
+}
+
+int plb_conv_fwd_host(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                      const void *h_in, const void *h_weights, const float *h_bias, void *h_out) {
+  if (int rc = activate(ctx)) return rc;
+  if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  ConvShape s;
+  if (int rc = igemmConvShape(*p, &s)) return rc;
+  const size_t es = dtypeBytes(p->input_type), os = dtypeBytes(p->output_type);
+  const size_t in_bytes = size_t(p->batch) * s.H * s.W * p->groups * p->in_chans_per_group * es;
+  const size_t w_bytes =
+      size_t(p->groups) * s.KH * s.KW * p->in_chans_per_group * p->out_chans_per_group * es;
+  const size_t out_bytes = size_t(p->batch) * s.OH * s.OW * p->groups * p->out_chans_per_group * os;
+  const size_t bias_bytes = size_t(p->groups) * p->out_chans_per_group * sizeof(float);
+  void *di = nullptr, *dw = nullptr, *dout = nullptr, *dbias = nullptr;
+  if (int rc = scratch(ctx, 1, in_bytes + 16, &di)) return rc;
+  if (int rc = scratch(ctx, 2, w_bytes + 16, &dw)) return rc;
+  if (int rc = scratch(ctx, 3, out_bytes + 16, &dout)) return rc;
+  if (h_bias) {
+    if (int rc = scratch(ctx, 4, bias_bytes + 16, &dbias)) return rc;
+    if (int rc = plb_memcpy_h2d(ctx, dbias, h_bias, bias_bytes)) return rc;
+  }
+  if (int rc = plb_memcpy_h2d(ctx, di, h_in, in_bytes)) return rc;
+  if (int rc = plb_memcpy_h2d(ctx, dw, h_weights, w_bytes)) return rc;
+  if (int rc = plb_conv_fwd(ctx, p, opt, di, dw, static_cast<const float *>(dbias), dout)) return rc;
+  if (int rc = plb_memcpy_d2h(ctx, h_out, dout, out_bytes)) return rc;
+  return plb_synchronize(ctx);
+}
+
+}  // extern "C"

@@ -1,0 +1,471 @@
+// Context, memory and error plumbing of the C ABI, TMA tensor-map encoding and
+// the small data-movement kernels (layout changes, casts, scaled add).
+#include "runtime.h"
+
+#include <cuda_fp16.h>
+#include <cudaTypedefs.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace plb {
+
+static thread_local std::string g_last_error;
+
+int fail(int code, const std::string &message) {
+  g_last_error = message;
+  return code;
+}
+
+int cudaFail(cudaError_t err, const char *what) {
+  g_last_error = std::string("CUDA error: ") + cudaGetErrorString(err) + " in " + what;
+  return err == cudaErrorMemoryAllocation ? PLB_ERR_OUT_OF_MEMORY : PLB_ERR_CUDA;
+}
+
+int activate(plb_context *ctx) {
+  if (ctx == nullptr) return fail(PLB_ERR_INVALID_PARAMS, "null context");
+  PLB_CUDA(cudaSetDevice(ctx->device));
+  return PLB_OK;
+}
+
+int scratch(plb_context *ctx, int slot, size_t bytes, void **ptr) {
+  if (slot < 0 || slot >= plb_context::kScratchSlots)
+    return fail(PLB_ERR_INVALID_PARAMS, "bad scratch slot");
+  if (ctx->scratch_bytes[slot] < bytes) {
+    // work already enqueued may still read the old buffer
+    PLB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch[slot]) PLB_CUDA(cudaFree(ctx->scratch[slot]));
+    ctx->scratch[slot] = nullptr;
+    ctx->scratch_bytes[slot] = 0;
+    const size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    PLB_CUDA(cudaMalloc(&ctx->scratch[slot], rounded));
+    ctx->scratch_bytes[slot] = rounded;
+  }
+  *ptr = ctx->scratch[slot];
+  return PLB_OK;
+}
+
+int encodeTensorMap(CUtensorMap *tm, CUtensorMapDataType type, int rank, const void *base,
+                    const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box,
+                    const uint32_t *elem_strides) {
+  static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  static std::once_flag once;
+  static cudaError_t lookup_err = cudaSuccess;
+  std::call_once(once, [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    lookup_err = cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000,
+                                                  cudaEnableDefault, &qres);
+    if (lookup_err == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  });
+  if (encode == nullptr)
+    return fail(PLB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
+    return fail(PLB_ERR_UNSUPPORTED, "tensor base address must be 16-byte aligned for TMA");
+  for (int i = 0; i + 1 < rank; ++i)
+    if (strides_bytes[i] % 16 != 0)
+      return fail(PLB_ERR_UNSUPPORTED,
+                  "tensor stride of " + std::to_string(strides_bytes[i]) +
+                      " bytes is not a multiple of 16 (TMA requirement)");
+  cuuint64_t gdims[5], gstrides[4];
+  cuuint32_t gbox[5], gestr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    gestr[i] = elem_strides[i];
+    if (i + 1 < rank) gstrides[i] = strides_bytes[i];
+  }
+  const CUresult res = encode(tm, type, cuuint32_t(rank), const_cast<void *>(base), gdims,
+                              gstrides, gbox, gestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) {
+    std::string msg = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(res)) +
+                      " (rank " + std::to_string(rank) + ", dims";
+    for (int i = 0; i < rank; ++i) msg += " " + std::to_string(dims[i]);
+    msg += ", box";
+    for (int i = 0; i < rank; ++i) msg += " " + std::to_string(box[i]);
+    msg += ")";
+    return fail(PLB_ERR_CUDA, msg);
+  }
+  return PLB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Data-movement kernels
+// ---------------------------------------------------------------------------
+
+// Batched transpose src[b][rows][cols] -> dst[b][cols][rows] through a padded
+// shared-memory tile so that both sides are coalesced.
+template <typename T>
+__global__ void transposeKernel(const T *__restrict__ src, T *__restrict__ dst, uint32_t rows,
+                                uint32_t cols) {
+  __shared__ T tile[32][33];
+  const size_t batch_off = size_t(blockIdx.z) * rows * cols;
+  const uint32_t c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+    const uint32_t r = r0 + i, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[i][threadIdx.x] = src[batch_off + size_t(r) * cols + c];
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.y; i < 32; i += blockDim.y) {
+    const uint32_t c = c0 + i, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) dst[batch_off + size_t(c) * rows + r] = tile[threadIdx.x][i];
+  }
+}
+
+static int launchTranspose(plb_context *ctx, uint32_t elem_bytes, uint64_t batch, uint64_t rows,
+                           uint64_t cols, const void *src, void *dst) {
+  if (batch == 0 || rows == 0 || cols == 0) return PLB_OK;
+  if (rows > 0xffffffffull || cols > 0xffffffffull)
+    return fail(PLB_ERR_UNSUPPORTED, "matrix too large to transpose");
+  const dim3 block(32, 8);
+  const uint64_t gy = (rows + 31) / 32, gx = (cols + 31) / 32;
+  if (gy > 65535 || batch > 65535) {
+    // fold: process batches one launch at a time / split rows
+    if (gy > 65535) return fail(PLB_ERR_UNSUPPORTED, "matrix too tall to transpose");
+  }
+  for (uint64_t b0 = 0; b0 < batch; b0 += 65535) {
+    const uint32_t nb = uint32_t(std::min<uint64_t>(65535, batch - b0));
+    const dim3 grid(uint32_t(gx), uint32_t(gy), nb);
+    const size_t off = size_t(b0) * rows * cols;
+    switch (elem_bytes) {
+      case 1:
+        transposeKernel<uint8_t><<<grid, block, 0, ctx->stream>>>(
+            static_cast<const uint8_t *>(src) + off, static_cast<uint8_t *>(dst) + off,
+            uint32_t(rows), uint32_t(cols));
+        break;
+      case 2:
+        transposeKernel<uint16_t><<<grid, block, 0, ctx->stream>>>(
+            static_cast<const uint16_t *>(src) + off, static_cast<uint16_t *>(dst) + off,
+            uint32_t(rows), uint32_t(cols));
+        break;
+      case 4:
+        transposeKernel<uint32_t><<<grid, block, 0, ctx->stream>>>(
+            static_cast<const uint32_t *>(src) + off, static_cast<uint32_t *>(dst) + off,
+            uint32_t(rows), uint32_t(cols));
+        break;
+      default:
+        return fail(PLB_ERR_INVALID_PARAMS, "element size must be 1, 2 or 4 bytes");
+    }
+    PLB_CUDA(cudaGetLastError());
+    ctx->launches++;
+  }
+  return PLB_OK;
+}
+
+// [G][K][Co][Ci] -> [G][K flipped][Ci][Co]; weights are small, one element per thread.
+template <typename T>
+__global__ void transposeFlipKernel(const T *__restrict__ src, T *__restrict__ dst,
+                                    uint32_t groups, uint32_t kelems, uint32_t co, uint32_t ci) {
+  const size_t total = size_t(groups) * kelems * co * ci;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const uint32_t o = uint32_t(i % co);
+    size_t r = i / co;
+    const uint32_t c = uint32_t(r % ci);
+    r /= ci;
+    const uint32_t k = uint32_t(r % kelems);
+    const uint32_t g = uint32_t(r / kelems);
+    dst[i] = src[((size_t(g) * kelems + (kelems - 1 - k)) * co + o) * ci + c];
+  }
+}
+
+template <typename T>
+__global__ void castFromF32Kernel(T *__restrict__ dst, const float *__restrict__ src, size_t n);
+template <>
+__global__ void castFromF32Kernel<__half>(__half *__restrict__ dst, const float *__restrict__ src,
+                                          size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x)
+    dst[i] = __float2half_rn(src[i]);
+}
+template <>
+__global__ void castFromF32Kernel<float>(float *__restrict__ dst, const float *__restrict__ src,
+                                         size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
+
+template <typename T>
+__global__ void scaledAddKernel(T *__restrict__ w, const float *__restrict__ d, float scale,
+                                size_t n);
+template <>
+__global__ void scaledAddKernel<__half>(__half *__restrict__ w, const float *__restrict__ d,
+                                        float scale, size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x)
+    w[i] = __float2half_rn(__half2float(w[i]) + scale * d[i]);
+}
+template <>
+__global__ void scaledAddKernel<float>(float *__restrict__ w, const float *__restrict__ d,
+                                       float scale, size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x)
+    w[i] = w[i] + scale * d[i];
+}
+
+// out = beta * c (matrix product with an empty reduction dimension)
+__global__ void scaleRowsKernel(void *out, const void *c, float beta, int out_f32, uint32_t rows,
+                                uint32_t cols, long long ldo, long long ldc) {
+  const size_t total = size_t(rows) * cols;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = i / cols, col = i % cols;
+    if (out_f32) {
+      const float v = c ? beta * static_cast<const float *>(c)[r * ldc + col] : 0.f;
+      static_cast<float *>(out)[r * ldo + col] = v;
+    } else {
+      const float v = c ? beta * __half2float(static_cast<const __half *>(c)[r * ldc + col]) : 0.f;
+      static_cast<__half *>(out)[r * ldo + col] = __float2half_rn(v);
+    }
+  }
+}
+
+int launchScaleRows(plb_context *ctx, void *out, const void *c, float beta, bool out_f32,
+                    uint32_t rows, uint32_t cols, long long ldo, long long ldc) {
+  if (rows == 0 || cols == 0) return PLB_OK;
+  const size_t total = size_t(rows) * cols;
+  const int grid = int(std::min<size_t>((total + 255) / 256, 148 * 8));
+  scaleRowsKernel<<<grid, 256, 0, ctx->stream>>>(out, c, beta, out_f32 ? 1 : 0, rows, cols, ldo,
+                                                 ldc);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+}  // namespace plb
+
+using namespace plb;
+
+// ---------------------------------------------------------------------------
+// C ABI: context and memory
+// ---------------------------------------------------------------------------
+extern "C" {
+
+const char *plb_last_error(void) { return g_last_error.c_str(); }
+
+const char *plb_version(void) { return "poplibs_b200 0.1 (sm_100a)"; }
+
+int plb_context_create_on_stream(int device, void *cuda_stream, plb_context **out) {
+  if (out == nullptr) return fail(PLB_ERR_INVALID_PARAMS, "null output pointer");
+  *out = nullptr;
+  int count = 0;
+  PLB_CUDA(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count)
+    return fail(PLB_ERR_CUDA, "CUDA device " + std::to_string(device) + " not present (" +
+                                  std::to_string(count) + " visible)");
+  PLB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  PLB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(PLB_ERR_CUDA, std::string("device '") + prop.name + "' is compute capability " +
+                                  std::to_string(prop.major) + "." + std::to_string(prop.minor) +
+                                  "; this library only carries sm_100a kernels");
+  plb_context *ctx = new plb_context();
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  if (cuda_stream != nullptr) {
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    ctx->owns_stream = false;
+  } else {
+    cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+      delete ctx;
+      return cudaFail(e, "cudaStreamCreateWithFlags");
+    }
+    ctx->owns_stream = true;
+  }
+  cudaError_t e = cudaMalloc(&ctx->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) {
+    plb_context_destroy(ctx);
+    return cudaFail(e, "status word allocation");
+  }
+  *out = ctx;
+  return PLB_OK;
+}
+
+int plb_context_create(int device, plb_context **out) {
+  return plb_context_create_on_stream(device, nullptr, out);
+}
+
+void plb_context_destroy(plb_context *ctx) {
+  if (ctx == nullptr) return;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  for (int i = 0; i < plb_context::kScratchSlots; ++i)
+    if (ctx->scratch[i]) cudaFree(ctx->scratch[i]);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+}
+
+void *plb_context_stream(plb_context *ctx) { return ctx ? ctx->stream : nullptr; }
+
+uint64_t plb_launch_count(const plb_context *ctx) { return ctx ? ctx->launches : 0; }
+
+int plb_synchronize(plb_context *ctx) {
+  if (int rc = activate(ctx)) return rc;
+  PLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  int status = 0;
+  PLB_CUDA(cudaMemcpy(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (status != 0) {
+    cudaMemset(ctx->d_status, 0, sizeof(int));
+    static const char *names[] = {"ok", "TMA producer wait ran out", "MMA issuer wait ran out",
+                                  "epilogue wait ran out", "teardown could not see copies complete"};
+    return fail(PLB_ERR_KERNEL, std::string("kernel status ") + std::to_string(status) + ": " +
+                                    (status > 0 && status < 5 ? names[status] : "unknown"));
+  }
+  return PLB_OK;
+}
+
+int plb_malloc(plb_context *ctx, size_t bytes, void **d_ptr) {
+  if (int rc = activate(ctx)) return rc;
+  if (d_ptr == nullptr) return fail(PLB_ERR_INVALID_PARAMS, "null output pointer");
+  *d_ptr = nullptr;
+  if (bytes == 0) bytes = 16;
+  PLB_CUDA(cudaMalloc(d_ptr, bytes));
+  return PLB_OK;
+}
+
+int plb_free(plb_context *ctx, void *d_ptr) {
+  if (int rc = activate(ctx)) return rc;
+  if (d_ptr) {
+    PLB_CUDA(cudaStreamSynchronize(ctx->stream));
+    PLB_CUDA(cudaFree(d_ptr));
+  }
+  return PLB_OK;
+}
+
+int plb_memcpy_h2d(plb_context *ctx, void *d_dst, const void *h_src, size_t bytes) {
+  if (int rc = activate(ctx)) return rc;
+  if (bytes) PLB_CUDA(cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return PLB_OK;
+}
+
+int plb_memcpy_d2h(plb_context *ctx, void *h_dst, const void *d_src, size_t bytes) {
+  if (int rc = activate(ctx)) return rc;
+  if (bytes) PLB_CUDA(cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  PLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return PLB_OK;
+}
+
+int plb_memset(plb_context *ctx, void *d_dst, int value, size_t bytes) {
+  if (int rc = activate(ctx)) return rc;
+  if (bytes) PLB_CUDA(cudaMemsetAsync(d_dst, value, bytes, ctx->stream));
+  return PLB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// C ABI: layout changes, casts
+// ---------------------------------------------------------------------------
+
+int plb_rearrange_acts_to_device(plb_context *ctx, uint32_t elem_bytes, uint32_t batch,
+                                 uint32_t chans, uint64_t field_elems, const void *d_src,
+                                 void *d_dst) {
+  if (int rc = activate(ctx)) return rc;
+  return launchTranspose(ctx, elem_bytes, batch, chans, field_elems, d_src, d_dst);
+}
+
+int plb_rearrange_acts_from_device(plb_context *ctx, uint32_t elem_bytes, uint32_t batch,
+                                   uint32_t chans, uint64_t field_elems, const void *d_src,
+                                   void *d_dst) {
+  if (int rc = activate(ctx)) return rc;
+  return launchTranspose(ctx, elem_bytes, batch, field_elems, chans, d_src, d_dst);
+}
+
+int plb_rearrange_weights_to_device(plb_context *ctx, uint32_t elem_bytes, uint32_t groups,
+                                    uint32_t out_chans, uint32_t in_chans, uint64_t kernel_elems,
+                                    const void *d_src, void *d_dst) {
+  if (int rc = activate(ctx)) return rc;
+  return launchTranspose(ctx, elem_bytes, groups, uint64_t(out_chans) * in_chans, kernel_elems,
+                         d_src, d_dst);
+}
+
+int plb_rearrange_weights_from_device(plb_context *ctx, uint32_t elem_bytes, uint32_t groups,
+                                      uint32_t out_chans, uint32_t in_chans,
+                                      uint64_t kernel_elems, const void *d_src, void *d_dst) {
+  if (int rc = activate(ctx)) return rc;
+  return launchTranspose(ctx, elem_bytes, groups, kernel_elems, uint64_t(out_chans) * in_chans,
+                         d_src, d_dst);
+}
+
+int plb_weights_transpose_chans_flip_xy(plb_context *ctx, uint32_t elem_bytes, uint32_t groups,
+                                        uint32_t out_chans, uint32_t in_chans,
+                                        uint64_t kernel_elems, const void *d_src, void *d_dst) {
+  if (int rc = activate(ctx)) return rc;
+  const size_t total = size_t(groups) * kernel_elems * out_chans * in_chans;
+  if (total == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((total + 255) / 256, 148 * 16));
+  switch (elem_bytes) {
+    case 1:
+      transposeFlipKernel<uint8_t><<<grid, 256, 0, ctx->stream>>>(
+          static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), groups,
+          uint32_t(kernel_elems), out_chans, in_chans);
+      break;
+    case 2:
+      transposeFlipKernel<uint16_t><<<grid, 256, 0, ctx->stream>>>(
+          static_cast<const uint16_t *>(d_src), static_cast<uint16_t *>(d_dst), groups,
+          uint32_t(kernel_elems), out_chans, in_chans);
+      break;
+    case 4:
+      transposeFlipKernel<uint32_t><<<grid, 256, 0, ctx->stream>>>(
+          static_cast<const uint32_t *>(d_src), static_cast<uint32_t *>(d_dst), groups,
+          uint32_t(kernel_elems), out_chans, in_chans);
+      break;
+    default:
+      return fail(PLB_ERR_INVALID_PARAMS, "element size must be 1, 2 or 4 bytes");
+  }
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int plb_transpose_matrix(plb_context *ctx, uint32_t elem_bytes, uint32_t groups, uint32_t rows,
+                         uint32_t cols, const void *d_src, void *d_dst) {
+  if (int rc = activate(ctx)) return rc;
+  return launchTranspose(ctx, elem_bytes, groups, rows, cols, d_src, d_dst);
+}
+
+int plb_cast_from_f32(plb_context *ctx, int32_t dtype, void *d_dst, const float *d_src,
+                      size_t count) {
+  if (int rc = activate(ctx)) return rc;
+  if (count == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((count + 255) / 256, 148 * 16));
+  if (dtype == PLB_HALF)
+    castFromF32Kernel<__half><<<grid, 256, 0, ctx->stream>>>(static_cast<__half *>(d_dst), d_src,
+                                                             count);
+  else if (dtype == PLB_FLOAT)
+    castFromF32Kernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<float *>(d_dst), d_src,
+                                                            count);
+  else
+    return fail(PLB_ERR_INVALID_PARAMS, "cast target must be half or float");
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int plb_scaled_add_to(plb_context *ctx, int32_t dtype, void *d_weights, const float *d_deltas_f32,
+                      float scale, size_t count) {
+  if (int rc = activate(ctx)) return rc;
+  if (count == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((count + 255) / 256, 148 * 16));
+  if (dtype == PLB_HALF)
+    scaledAddKernel<__half><<<grid, 256, 0, ctx->stream>>>(static_cast<__half *>(d_weights),
+                                                           d_deltas_f32, scale, count);
+  else if (dtype == PLB_FLOAT)
+    scaledAddKernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<float *>(d_weights),
+                                                          d_deltas_f32, scale, count);
+  else
+    return fail(PLB_ERR_INVALID_PARAMS, "weights must be half or float");
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+}  // extern "C"

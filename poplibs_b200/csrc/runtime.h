@@ -1,0 +1,94 @@
+// Internal host-side runtime shared by the C ABI entry points: the context
+// (device, stream, kernel status word, scratch memory), error reporting and
+// TMA tensor-map construction.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "poplibs_b200.h"
+
+struct plb_context {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  bool owns_stream = false;
+  int *d_status = nullptr;        // kernel status word (0 = OK)
+  uint64_t launches = 0;          // kernels launched through this context
+  // grow-only scratch buffers: [0] operand rearrangement / partial sums,
+  // [1..] staging for the host-buffer entry points
+  static constexpr int kScratchSlots = 8;
+  void *scratch[kScratchSlots] = {};
+  size_t scratch_bytes[kScratchSlots] = {};
+};
+
+namespace plb {
+
+// Records the message for plb_last_error() and returns `code`.
+int fail(int code, const std::string &message);
+int cudaFail(cudaError_t err, const char *what);
+
+#define PLB_CUDA(expr)                                         \
+  do {                                                         \
+    cudaError_t plb_err__ = (expr);                            \
+    if (plb_err__ != cudaSuccess) return ::plb::cudaFail(plb_err__, #expr); \
+  } while (0)
+
+// Makes the context's device current.
+int activate(plb_context *ctx);
+// Returns a scratch buffer of at least `bytes` (grows, synchronising first, if needed).
+int scratch(plb_context *ctx, int slot, size_t bytes, void **ptr);
+
+// cuTensorMapEncodeTiled with 128-byte swizzle and zero fill outside the
+// tensor.  dims[0] is the contiguous dimension; strides_bytes[i] is the byte
+// stride of dims[i + 1].
+int encodeTensorMap(CUtensorMap *tm, CUtensorMapDataType type, int rank, const void *base,
+                    const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box,
+                    const uint32_t *elem_strides);
+
+inline size_t dtypeBytes(int dtype) {
+  return dtype == PLB_FLOAT ? 4 : dtype == PLB_HALF ? 2 : 1;
+}
+
+// ---- contraction launch (igemm_launch.cu) -----------------------------------
+
+// A fully resolved implicit-GEMM problem: one launch of the igemm kernel.
+struct IgemmProblem {
+  bool fp8 = false;      // E4M3 operands (else fp16)
+  bool b_mn = false;     // right operand stored [tap][K][N], N contiguous
+  // activations: 4-D tensor (C, W, H, N) with byte strides of W, H, N
+  const void *act = nullptr;
+  uint64_t act_dims[4] = {1, 1, 1, 1};
+  uint64_t act_strides[3] = {16, 16, 16};
+  uint32_t act_elem_strides[4] = {1, 1, 1, 1};  // traversal strides (conv stride on W, H)
+  // weights: (K, N, taps) K-major or (N, K, taps) MN-major, byte strides of dims 1, 2
+  const void *wgt = nullptr;
+  uint64_t wgt_dims[3] = {1, 1, 1};
+  uint64_t wgt_strides[2] = {16, 16};
+  // output
+  int out_w = 1, out_h = 1, out_n = 1;  // pixels
+  int n_total = 0;                      // output channels
+  int k_per_tap = 0;                    // reduction length per tap (elements)
+  int taps_h = 1, taps_w = 1, pad_h = 0, pad_w = 0, dil_h = 1, dil_w = 1;
+  int flip_h = 0, flip_w = 0;
+  int stride_h = 1, stride_w = 1;
+  void *out = nullptr;
+  long long ldc = 0;
+  const void *addend = nullptr;
+  long long ld_addend = 0;
+  const float *bias = nullptr;
+  float alpha = 1.f, beta = 0.f;
+  bool out_f32 = false;
+  int force_tile_n = 0;  // 0 = planner's choice
+};
+
+// Fills the tiling part of `plan` for a problem; returns non-zero if the
+// problem cannot be run by the igemm kernel (message recorded).
+int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan);
+int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan);
+
+}  // namespace plb

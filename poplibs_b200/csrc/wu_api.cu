@@ -1,0 +1,215 @@
+// Weight-update pass: planning and launch of the weight-gradient kernel.
+#include <algorithm>
+
+#include "conv_geometry.h"
+#include "runtime.h"
+#include "wu_sm100.cuh"
+
+namespace plb {
+namespace {
+
+struct WuShape {
+  int H, W, OH, OW, KH, KW, padH, padW, dilH, dilW, strH, strW;
+};
+
+int wuShape(const plb_conv_params &p, WuShape *s) {
+  const std::string err = validate(p);
+  if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+  if (p.num_field_dims > 2)
+    return fail(PLB_ERR_UNSUPPORTED, "3-D convolutions are not implemented on this path yet");
+  if (p.input_type != PLB_HALF)
+    // the reference never runs the weight update in quarter either
+    // (tools/single_conv_layer.cpp:725-733)
+    return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half input only");
+  for (unsigned d = 0; d != p.num_field_dims; ++d) {
+    if (p.in_trunc_lo[d] || p.in_trunc_hi[d] || p.in_dilation[d] != 1 || p.in_flip[d] ||
+        p.k_trunc_lo[d] || p.k_trunc_hi[d] || p.k_pad_lo[d] || p.k_pad_hi[d] || p.k_flip[d] ||
+        p.out_trunc_lo[d] || p.out_trunc_hi[d] || p.out_pad_lo[d] || p.out_pad_hi[d])
+      return fail(PLB_ERR_UNSUPPORTED,
+                  "input truncation/dilation/flip, kernel truncation/padding/flip and output "
+                  "truncation/padding are not implemented on this path yet");
+    if (p.stride[d] > 8) return fail(PLB_ERR_UNSUPPORTED, "strides above 8 are not implemented");
+  }
+  const unsigned hd = p.num_field_dims == 2 ? 0 : ~0u, wd = p.num_field_dims - 1;
+  auto get = [&](const uint32_t *v, unsigned d, int dflt) { return d == ~0u ? dflt : int(v[d]); };
+  s->H = get(p.field, hd, 1);
+  s->W = get(p.field, wd, 1);
+  s->KH = get(p.kernel, hd, 1);
+  s->KW = get(p.kernel, wd, 1);
+  s->padH = get(p.in_pad_lo, hd, 0);
+  s->padW = get(p.in_pad_lo, wd, 0);
+  s->dilH = get(p.k_dilation, hd, 1);
+  s->dilW = get(p.k_dilation, wd, 1);
+  s->strH = get(p.stride, hd, 1);
+  s->strW = get(p.stride, wd, 1);
+  s->OH = hd == ~0u ? 1 : int(outputSize(p, hd));
+  s->OW = int(outputSize(p, wd));
+  return PLB_OK;
+}
+
+// Tiling of one group's weight update.
+void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_split,
+            WuArgs *a, plb_plan *plan) {
+  const int co = int(p.out_chans_per_group), ci = int(p.in_chans_per_group);
+  const int taps = s.KH * s.KW;
+  a->taps_h = s.KH;
+  a->taps_w = s.KW;
+  a->pad_h = s.padH;
+  a->pad_w = s.padW;
+  a->dil_h = s.dilH;
+  a->dil_w = s.dilW;
+  a->stride_h = s.strH;
+  a->stride_w = s.strW;
+  a->co_total = co;
+  a->ci_total = ci;
+  a->co_blocks = (co + 127) / 128;
+  a->ci_blk = std::min(256, (ci + 31) / 32 * 32);
+  a->ci_blk64 = (a->ci_blk + 63) / 64;
+  a->ci_blocks = (ci + a->ci_blk - 1) / a->ci_blk;
+  a->taps_per_group = std::max(1, std::min(taps, 512 / a->ci_blk));
+  a->tap_groups = (taps + a->taps_per_group - 1) / a->taps_per_group;
+  // even out the groups (9 taps, 4 per group -> 3 groups of 3)
+  a->taps_per_group = (taps + a->tap_groups - 1) / a->tap_groups;
+  int cols = a->taps_per_group * a->ci_blk, pow2 = 32;
+  while (pow2 < cols) pow2 <<= 1;
+  a->tmem_cols = pow2;
+  // pixel box: 64 pixels, fewest tiles, then widest rows
+  long best = -1;
+  for (int w = 64; w >= 1; w >>= 1)
+    for (int h = 64 / w; h >= 1; h >>= 1) {
+      const int n = 64 / (w * h);
+      if ((w - 1) * s.strW + 1 > 256 || (h - 1) * s.strH + 1 > 256) continue;
+      const long tiles =
+          long((s.OW + w - 1) / w) * ((s.OH + h - 1) / h) * ((long(p.batch) + n - 1) / n);
+      if (best < 0 || tiles < best) {
+        best = tiles;
+        a->box_w = w;
+        a->box_h = h;
+        a->box_n = n;
+      }
+    }
+  a->tiles_w = (s.OW + a->box_w - 1) / a->box_w;
+  a->tiles_h = (s.OH + a->box_h - 1) / a->box_h;
+  a->tiles_n = (int(p.batch) + a->box_n - 1) / a->box_n;
+  const int stage_bytes = (2 + a->taps_per_group * a->ci_blk64) * kWuBlockBytes;
+  a->stages = std::max(2, std::min(kWuMaxStages, (200 * 1024) / stage_bytes));
+  const int units = a->co_blocks * a->ci_blocks * a->tap_groups;
+  int ksplit = force_split > 0 ? force_split : std::max(1, (sm_count > 0 ? sm_count : 148) / units);
+  ksplit = int(std::min<long>(ksplit, std::max<long>(best, 1)));
+  a->ksplit = ksplit;
+  if (plan) {
+    plan->kernel = 1;
+    plan->tile_m = 128;
+    plan->tile_n = a->taps_per_group * a->ci_blk;
+    plan->tile_k_bytes = kWuPixelsPerStage * 2;
+    plan->box_w = a->box_w;
+    plan->box_h = a->box_h;
+    plan->box_n = a->box_n;
+    plan->stages = a->stages;
+    plan->split_k = ksplit;
+    plan->tiles = units;
+    plan->grid = units * ksplit;
+    plan->b_mn_major = 1;
+    plan->workspace_bytes = size_t(ksplit) * taps * co * ci * sizeof(float);
+  }
+}
+
+}  // namespace
+}  // namespace plb
+
+using namespace plb;
+
+extern "C" {
+
+int plb_conv_wu_plan(const plb_conv_params *p, const plb_conv_options *opt, plb_plan *plan) {
+  if (!p || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  WuShape s;
+  if (int rc = wuShape(*p, &s)) return rc;
+  *plan = plb_plan{};
+  WuArgs a{};
+  planWu(*p, s, 148, opt ? opt->split_k : 0, &a, plan);
+  plan->flops = 2 * numberOfMacs(*p);
+  const uint64_t es = dtypeBytes(p->input_type);
+  plan->bytes = es * (uint64_t(p->batch) * s.H * s.W * p->groups * p->in_chans_per_group +
+                      uint64_t(p->batch) * s.OH * s.OW * p->groups * p->out_chans_per_group +
+                      uint64_t(p->groups) * s.KH * s.KW * p->in_chans_per_group *
+                          p->out_chans_per_group);
+  return PLB_OK;
+}
+
+int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                const void *d_acts, const void *d_out_grads, void *d_weight_grads,
+                float *d_weight_grads_f32) {
+  if (int rc = activate(ctx)) return rc;
+  if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  WuShape s;
+  if (int rc = wuShape(*p, &s)) return rc;
+  const int co = int(p->out_chans_per_group), ci = int(p->in_chans_per_group);
+  const int taps = s.KH * s.KW;
+  const size_t w_elems = size_t(taps) * co * ci;
+  if (p->groups == 0 || w_elems == 0) return PLB_OK;
+  if (p->batch == 0 || s.OH == 0 || s.OW == 0) {
+    // empty reduction: the gradient is zero
+    const size_t n = size_t(p->groups) * w_elems;
+    if (d_weight_grads) PLB_CUDA(cudaMemsetAsync(d_weight_grads, 0, n * dtypeBytes(p->input_type), ctx->stream));
+    if (d_weight_grads_f32) PLB_CUDA(cudaMemsetAsync(d_weight_grads_f32, 0, n * sizeof(float), ctx->stream));
+    return PLB_OK;
+  }
+  WuArgs a{};
+  planWu(*p, s, ctx->sm_count, opt ? opt->split_k : 0, &a, nullptr);
+  a.status = ctx->d_status;
+  void *ws = nullptr;
+  if (int rc = scratch(ctx, 0, size_t(a.ksplit) * w_elems * sizeof(float), &ws)) return rc;
+  a.partial = static_cast<float *>(ws);
+
+  const size_t es = 2;
+  const uint64_t ctot = uint64_t(p->groups) * ci, cotot = uint64_t(p->groups) * co;
+  const int stage_bytes = (2 + a.taps_per_group * a.ci_blk64) * kWuBlockBytes;
+  const int smem = a.stages * stage_bytes + 256 + 1024;
+  static bool configured[64] = {};
+  if (!configured[ctx->device & 63]) {
+    PLB_CUDA(cudaFuncSetAttribute(wu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured[ctx->device & 63] = true;
+  }
+  for (unsigned g = 0; g < p->groups; ++g) {
+    CUtensorMap tdy, tx;
+    {
+      const uint64_t dims[4] = {uint64_t(co), uint64_t(s.OW), uint64_t(s.OH), p->batch};
+      const uint64_t strides[3] = {cotot * es, uint64_t(s.OW) * cotot * es,
+                                   uint64_t(s.OH) * s.OW * cotot * es};
+      const uint32_t box[4] = {64, uint32_t(a.box_w), uint32_t(a.box_h), uint32_t(a.box_n)};
+      const uint32_t estr[4] = {1, 1, 1, 1};
+      if (int rc = encodeTensorMap(&tdy, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                                   static_cast<const uint8_t *>(d_out_grads) + size_t(g) * co * es,
+                                   dims, strides, box, estr))
+        return rc;
+    }
+    {
+      const uint64_t dims[4] = {uint64_t(ci), uint64_t(s.W), uint64_t(s.H), p->batch};
+      const uint64_t strides[3] = {ctot * es, uint64_t(s.W) * ctot * es,
+                                   uint64_t(s.H) * s.W * ctot * es};
+      const uint32_t box[4] = {64, uint32_t((a.box_w - 1) * s.strW + 1),
+                               uint32_t((a.box_h - 1) * s.strH + 1), uint32_t(a.box_n)};
+      const uint32_t estr[4] = {1, uint32_t(s.strW), uint32_t(s.strH), 1};
+      if (int rc = encodeTensorMap(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                                   static_cast<const uint8_t *>(d_acts) + size_t(g) * ci * es,
+                                   dims, strides, box, estr))
+        return rc;
+    }
+    const int grid = a.co_blocks * a.ci_blocks * a.tap_groups * a.ksplit;
+    wu_kernel<<<grid, kWuThreads, smem, ctx->stream>>>(tdy, tx, a);
+    PLB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
+    wu_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>(
+        a.partial, a.ksplit, w_elems,
+        d_weight_grads_f32 ? d_weight_grads_f32 + size_t(g) * w_elems : nullptr,
+        d_weight_grads ? static_cast<uint8_t *>(d_weight_grads) + size_t(g) * w_elems * es : nullptr,
+        0);
+    PLB_CUDA(cudaGetLastError());
+    ctx->launches++;
+  }
+  return PLB_OK;
+}
+
+}  // extern "C"
