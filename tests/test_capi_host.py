@@ -1,0 +1,150 @@
+"""Host-side checks that need no GPU: the C ABI library loads and exports every
+symbol the header declares, and its host logic (ConvParams algebra, planner,
+error reporting) agrees with the oracle and with the reference's messages."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import oracle
+from oracle import ConvSpec
+from poplibs_b200 import capi
+from test_oracle import OUTPUT_DIM_TABLE, RANGE_TABLE, random_spec
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "poplibs_b200.h")).read()
+    return sorted(set(re.findall(r"PLB_API[^;(]*?\b(plb_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = capi.lib()
+    names = declared_symbols()
+    assert len(names) >= 30
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/poplibs_b200.h but not exported"
+    assert sorted(capi.SYMBOLS) == names
+    assert b"sm_100a" in lib.plb_version()
+
+
+def params_from_spec(spec: ConvSpec) -> capi.ConvParams:
+    return capi.ConvParams.make(spec.batch, spec.field, spec.kernel, spec.in_chans, spec.out_chans,
+                                spec.groups, **spec.normalised_transforms()) \
+        if hasattr(spec, "normalised_transforms") else _params_from_spec(spec)
+
+
+def _params_from_spec(spec):
+    n = spec.normalised()
+    n.pop("field"), n.pop("kernel")
+    return capi.ConvParams.make(spec.batch, spec.field, spec.kernel, spec.in_chans, spec.out_chans,
+                                spec.groups, **n)
+
+
+def test_input_index_and_output_size_known_answers():
+    # the tables of tests/poplin/RangeTest.cpp:33-168
+    lib = capi.lib()
+    for (stride, lo, hi), rows in RANGE_TABLE.items():
+        p = capi.ConvParams.make(1, [10, 10], [3, 3], 1, 1, in_pad_lo=lo, in_pad_hi=hi, stride=stride)
+        for out, k, expected in rows:
+            assert lib.plb_conv_input_index(C.byref(p), 0, out, k) == expected
+    for field, kernel, stride, lo, hi, expected in OUTPUT_DIM_TABLE:
+        p = capi.ConvParams.make(1, list(field), list(kernel), 1, 1, in_pad_lo=list(lo),
+                                 in_pad_hi=list(hi), stride=list(stride))
+        assert tuple(p.output_field()) == expected
+
+
+def test_geometry_matches_oracle_on_random_params():
+    r = np.random.default_rng(3)
+    lib, olib = capi.lib(), oracle._lib()
+    for _ in range(200):
+        spec = random_spec(r)
+        p = _params_from_spec(spec)
+        assert p.output_field() == spec.out_field()
+        assert p.macs() == spec.macs()
+        op = spec.to_c()
+        for d, (o, k) in enumerate(zip(spec.out_field(), spec.kernel)):
+            for oi in range(o):
+                for ki in range(k):
+                    assert lib.plb_conv_input_index(C.byref(p), d, oi, ki) == \
+                        olib.oracle_conv_input_index(C.byref(op), d, oi, ki)
+
+
+def test_flop_counts_of_the_benchmark_layers():
+    mk = capi.ConvParams.make
+    assert 2 * mk(32, [56, 56], [3, 3], 64, 64, padding=1).macs() == 7223640064
+    assert 2 * mk(256, [28, 28], [3, 3], 128, 128, padding=1).macs() == 56405000192
+    assert 2 * mk(256, [56, 56], [1, 1], 256, 512, stride=2).macs() == 52613349376
+    assert 2 * mk(256, [224, 224], [7, 7], 3, 64, padding=3, stride=2).macs() == 59501838336  # 2*256*3*64*778^2
+
+
+def test_validate_messages():
+    # lib/poplin/ConvParams.cpp:172-266
+    lib = capi.lib()
+
+    def err(**kw):
+        p = capi.ConvParams.make(1, [4, 4], [3, 3], 1, 1, **kw)
+        rc = lib.plb_conv_validate(C.byref(p))
+        return rc, lib.plb_last_error().decode()
+
+    assert err()[0] == 0
+    rc, msg = err(stride=[0, 1])
+    assert rc == 1 and msg == "Stride must be non zero"
+    rc, msg = err(in_dilation=[1, 0])
+    assert rc == 1 and msg.startswith("Input dilation must be non zero")
+    rc, msg = err(k_dilation=[0, 1])
+    assert rc == 1 and msg.startswith("Kernel dilation must be non zero")
+    rc, msg = err(in_trunc_lo=[3, 0], in_trunc_hi=[2, 0])
+    assert rc == 1 and "truncates by more than the size of the field (4)" in msg
+    rc, msg = err(k_trunc_lo=[2, 0], k_trunc_hi=[2, 0])
+    assert rc == 1 and "truncates by more than the size of the kernel (3)" in msg
+    rc, msg = err(k_trunc_lo=[3, 0])
+    assert rc == 1 and msg == "Transformed kernel for dimension 0 has zero size"
+    rc, msg = err(k_dilation=[2, 1])
+    assert rc == 1 and msg == ("Transformed input size for dimension 0 (4) is less than the "
+                               "transformed kernel size (5)")
+    rc, msg = err(out_trunc_lo=[2, 0], out_trunc_hi=[1, 0])
+    assert rc == 1 and "truncates by more than the size of the convolution output (2)" in msg
+
+
+def test_planner_choices():
+    plan = capi.conv_plan(capi.ConvParams.make(32, [56, 56], [3, 3], 64, 64, padding=1))
+    assert (plan.tile_m, plan.tile_n) == (128, 64)
+    assert plan.box_w * plan.box_h * plan.box_n == 128
+    assert plan.tiles == 784 and plan.grid == 148          # no padded pixels
+    assert plan.flops == 7223640064 and plan.bytes == 25763840
+    plan = capi.conv_plan(capi.ConvParams.make(256, [28, 28], [3, 3], 128, 128, padding=1))
+    assert plan.tile_n == 128 and plan.tiles == 1568
+    plan = capi.conv_plan(capi.ConvParams.make(256, [56, 56], [1, 1], 256, 512, stride=2))
+    assert plan.tile_n == 256 and plan.bytes == 308543488
+    plan = capi.matmul_plan(capi.MatmulDesc.make(8192, 8192, 8192))
+    assert plan.tile_n == 256 and plan.tiles == 2048 and plan.b_mn_major == 1
+    assert plan.flops == 2 * 8192 ** 3 and plan.bytes == 3 * 8192 * 8192 * 2
+    plan = capi.matmul_plan(capi.MatmulDesc.make(8192, 8192, 8192, input_type=capi.QUARTER))
+    assert plan.bytes == 2 * 8192 * 8192 + 8192 * 8192 * 2
+    plan = capi.matmul_plan(capi.MatmulDesc.make(5, 0, 4))
+    assert plan.tiles == 0 and plan.flops == 0
+
+
+def test_option_and_type_errors():
+    with pytest.raises(capi.PlbError) as e:
+        capi.matmul_plan(capi.MatmulDesc.make(4, 4, 4, input_type=capi.QUARTER, output_type=capi.FLOAT))
+    assert e.value.code == 1 and "Output type must be half when input type is quarter" in e.value.message
+    with pytest.raises(capi.PlbError) as e:
+        capi.matmul_plan(capi.MatmulDesc.make(4, 4, 4, partials_type=capi.QUARTER))
+    assert e.value.code == 2
+    with pytest.raises(capi.PlbError) as e:
+        capi.conv_plan(capi.ConvParams.make(1, [4, 4], [3, 3], 8, 8), opt=capi.ConvOptions.make(tile_n=96))
+    assert e.value.code == 2
+
+
+def test_no_silent_fallback_without_a_gpu():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(capi.PlbError) as e:
+        capi.Context(0)
+    assert e.value.code == 4  # PLB_ERR_CUDA: fails loudly, nothing is computed on the host

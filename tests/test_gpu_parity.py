@@ -1,0 +1,361 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.
+
+Tolerances.  Data whose sums are exactly representable (+-1 and small
+integers, the reference tool's own exact mode, tools/single_conv_layer.cpp:
+979-1005) must match the oracle BIT FOR BIT.  Uniform / normal data use
+poplibs_test::checkIsClose with relative tolerance 1e-3 for half inputs with
+float partials and 5e-2 for quarter inputs; the absolute tolerance is
+max(1e-5, 2.5e-4 * rms(expected)): an output that is near zero because large
+terms cancel cannot be reproduced to 1e-3 of ITSELF by any fp32 accumulation,
+so such elements are held to a quarter of the relative tolerance measured
+against the typical output magnitude instead.
+"""
+import zlib
+
+import numpy as np
+import pytest
+
+import common as T
+import oracle
+from poplibs_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+REL_HALF, REL_QUARTER = T.REL_TOL_HALF, T.REL_TOL_QUARTER
+
+
+def assert_close(got, exp, rel, what):
+    got = np.asarray(got, dtype=np.float64)
+    exp = np.asarray(exp, dtype=np.float64).reshape(got.shape)
+    rms = float(np.sqrt(np.mean(exp * exp))) if exp.size else 0.0
+    abs_tol = max(T.ABS_TOL, 2.5e-4 * rms)
+    bad, first, worst = oracle.check_is_close(got, exp, rel, abs_tol)
+    assert bad == 0, (f"{what}: {bad}/{got.size} elements outside rel={rel} abs={abs_tol:.2e}; first at "
+                      f"{np.unravel_index(first, got.shape)} got {got.ravel()[first]} expected {exp.ravel()[first]}")
+
+
+def assert_exact(got, exp, what):
+    got = np.asarray(got, dtype=np.float64)
+    exp = np.asarray(exp, dtype=np.float64).reshape(got.shape)
+    diff = got != exp
+    assert not diff.any(), f"{what}: {int(diff.sum())}/{got.size} elements differ; first at {np.argwhere(diff)[0]}"
+
+
+# --------------------------------------------------------------------------- matMul
+
+GEMM_SHAPES = [(128, 64, 64), (1, 8, 1), (1, 1000, 1), (5, 8, 4), (300, 200, 72), (129, 72, 257),
+               (256, 128, 128), (128, 64, 256), (640, 320, 520)]
+
+
+@pytest.mark.parametrize("m,k,n", GEMM_SHAPES)
+@pytest.mark.parametrize("tb", [False, True])
+def test_matmul_exact(gpu_ctx, m, k, n, tb):
+    if not tb and n % 8:
+        pytest.skip("row-major right operand needs n % 8 == 0 for TMA (padding path not built)")
+    r = T.rng(m * 7 + k * 3 + n)
+    a = T.small_int_half(r, (m, k))
+    b = T.small_int_half(r, (n, k) if tb else (k, n), -3, 3)
+    got = T.gpu_matmul(a, b, transpose_b=tb, out_dtype=np.float32)
+    assert_exact(got, oracle.gemm(a, b, transpose_b=tb), f"matMul {m}x{k}x{n} tb={tb}")
+
+
+def test_matmul_config1_uniform(gpu_ctx):
+    # poplin::matMul fp16 A[512x1024].B[1024x1024], fp32 partials, fp16 out
+    r = T.rng(1234 + 1)
+    a, b = T.uniform_half(r, (512, 1024)), T.uniform_half(r, (1024, 1024))
+    got = T.gpu_matmul(a, b)
+    assert_close(got, oracle.gemm(a, b), REL_HALF, "config 1")
+    # the gemm tool's own data ranges and D = beta*C + alpha*A*B
+    a, b = T.uniform_half(r, (512, 1024), -4, 4), T.uniform_half(r, (1024, 1024), -3, 3)
+    c = T.uniform_half(r, (512, 1024), -2, 2)
+    got = T.gpu_matmul(a, b, c, alpha=1.0, beta=1.0)
+    assert_close(got, oracle.gemm(a, b, c, 1.0, 1.0), REL_HALF, "config 1, alpha=beta=1")
+
+
+def test_matmul_transposes_groups_alpha_beta(gpu_ctx):
+    r = T.rng(11)
+    g, m, k, n = 3, 72, 136, 88
+    for ta in (False, True):
+        for tb in (False, True):
+            a = T.small_int_half(r, (g, k, m) if ta else (g, m, k))
+            b = T.small_int_half(r, (g, n, k) if tb else (g, k, n), -3, 3)
+            c = T.small_int_half(r, (g, m, n), -2, 2)
+            got = T.gpu_matmul(a, b, c, transpose_a=ta, transpose_b=tb, alpha=2.0, beta=-1.0,
+                               out_dtype=np.float32)
+            assert_exact(got, oracle.gemm(a, b, c, 2.0, -1.0, ta, tb), f"grouped ta={ta} tb={tb}")
+
+
+def test_matmul_empty_dimensions(gpu_ctx):
+    r = T.rng(12)
+    # gemm_5x0x4: an empty reduction leaves beta*C
+    a = np.zeros((5, 0), np.float16)
+    b = np.zeros((4, 0), np.float16)
+    c = T.small_int_half(r, (5, 4))
+    got = T.gpu_matmul(a, b, c, transpose_b=True, beta=1.0, out_dtype=np.float32)
+    assert_exact(got, c, "5x0x4")
+    got = T.gpu_matmul(np.zeros((0, 8), np.float16), np.zeros((4, 8), np.float16), transpose_b=True)
+    assert got.shape == (0, 4)
+
+
+def test_matmul_quarter_exact_and_scaled(gpu_ctx):
+    r = T.rng(13)
+    for (m, k, n) in [(128, 128, 64), (300, 256, 72), (256, 512, 256)]:
+        av = r.integers(-4, 5, size=(m, k)).astype(np.float64)
+        bv = r.integers(-3, 4, size=(k, n)).astype(np.float64)
+        a8, b8 = oracle.e4m3_encode(av), oracle.e4m3_encode(bv)
+        got = T.gpu_matmul(a8, np.ascontiguousarray(b8.T), transpose_b=True, scale_a=-3, scale_b=-2)
+        assert_exact(got, oracle.gemm(av, bv) * 2.0 ** -5, f"quarter {m}x{k}x{n} scaled")
+        got = T.gpu_matmul(a8, b8)   # [k][n] right operand goes through the transpose kernel
+        assert_exact(got, oracle.gemm(av, bv), f"quarter {m}x{k}x{n} row-major B")
+
+
+def quantised_normal(r, shape, exponent):
+    """N(0,1) data stored as E4M3 with value = stored * 2^exponent: returns the
+    bytes and the dequantised doubles the oracle is given."""
+    x = r.normal(size=shape)
+    bits = oracle.e4m3_encode(x * 2.0 ** (-exponent))
+    return bits, oracle.e4m3_decode(bits) * 2.0 ** exponent
+
+
+def test_matmul_config5_quarter_sampled_rows(gpu_ctx):
+    # 8192^3 E4M3, scales 2^-3 and 2^-2, fp16 out: full-size run, oracle on sampled rows
+    import torch
+    r = T.rng(1234 + 5)
+    n = 8192
+    a8, av = quantised_normal(r, (n, n), -3)
+    b8, bv = quantised_normal(r, (n, n), -2)
+    got = T.gpu_matmul(a8, np.ascontiguousarray(b8.T), transpose_b=True, scale_a=-3, scale_b=-2)
+    rows = np.sort(r.choice(n, 48, replace=False))
+    assert_close(got[rows], oracle.gemm(av[rows], bv), REL_QUARTER, "config 5 fp8 rows")
+    torch.cuda.empty_cache()
+
+
+def test_matmul_config5_half_sampled_rows(gpu_ctx):
+    import torch
+    r = T.rng(1234 + 6)
+    n = 8192
+    a = r.normal(size=(n, n)).astype(np.float16)
+    b = r.normal(size=(n, n)).astype(np.float16)
+    got = T.gpu_matmul(a, b)
+    rows = np.sort(r.choice(n, 48, replace=False))
+    assert_close(got[rows], oracle.gemm(a[rows], b), REL_HALF, "config 5 fp16 rows")
+    # size-independent property: (2A)B == 2(AB) exactly in binary floating point
+    got2 = T.gpu_matmul((2 * a).astype(np.float16), b)
+    assert (got2[rows].astype(np.float64) == 2 * got[rows].astype(np.float64)).all()
+    torch.cuda.empty_cache()
+
+
+# --------------------------------------------------------------------------- convolution
+
+def conv_case(batch, field, kernel, ci, co, **kw):
+    return dict(batch=batch, field=field, kernel=kernel, in_chans=ci, out_chans=co, **kw)
+
+
+SMALL_CONVS = {
+    "3x3_pad1": conv_case(2, [8, 8], [3, 3], 64, 64, padding=1),
+    "1x1": conv_case(2, [8, 8], [1, 1], 128, 64),
+    "ragged_chans": conv_case(3, [7, 9], [3, 3], 72, 40, padding=1),
+    "wide_chans": conv_case(2, [6, 6], [3, 3], 320, 192, padding=1),
+    "kernel_dilation": conv_case(2, [12, 12], [3, 3], 64, 64, padding=2, k_dilation=2),
+    "asym_padding": conv_case(2, [9, 6], [3, 2], 64, 72, in_pad_lo=[2, 0], in_pad_hi=[0, 1]),
+    "flipped_kernel": conv_case(2, [7, 7], [3, 3], 64, 64, padding=1, k_flip=[1, 0]),
+    "one_dim": conv_case(4, [33], [5], 64, 96, padding=2),
+    "groups2": conv_case(2, [6, 6], [3, 3], 64, 64, padding=1, groups=2),
+    "batch1_big_field": conv_case(1, [40, 23], [3, 3], 64, 64, padding=1),
+}
+STRIDED_CONVS = {
+    "1x1_s2": conv_case(2, [8, 8], [1, 1], 64, 128, stride=2),
+    "3x3_s2": conv_case(2, [9, 9], [3, 3], 64, 64, padding=1, stride=2),
+    "3x3_s2x3": conv_case(2, [11, 13], [3, 3], 64, 64, padding=1, stride=[2, 3]),
+}
+
+
+def conv_data(p, kw, r, exact):
+    gen = T.binary_half if exact else T.uniform_half
+    g = p.groups
+    x = gen(r, (p.batch, g * p.in_chans_per_group, *kw["field"]))
+    fan_in = p.in_chans_per_group * int(np.prod(kw["kernel"]))
+    if exact:
+        w = gen(r, (g, p.out_chans_per_group, p.in_chans_per_group, *kw["kernel"]))
+    else:
+        bound = 1.0 / np.sqrt(fan_in)
+        w = T.uniform_half(r, (g, p.out_chans_per_group, p.in_chans_per_group, *kw["kernel"]), -bound, bound)
+    dy = gen(r, (p.batch, g * p.out_chans_per_group, *p.output_field()))
+    return x, w, dy
+
+
+@pytest.mark.parametrize("name", sorted({**SMALL_CONVS, **STRIDED_CONVS}))
+def test_conv_fwd_small(gpu_ctx, name):
+    kw = {**SMALL_CONVS, **STRIDED_CONVS}[name]
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(zlib.crc32(name.encode()) % 1000)
+    x, w, _ = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), f"fwd {name} exact")
+    x, w, _ = conv_data(p, kw, r, exact=False)
+    bias = r.uniform(-2, 6, p.groups * p.out_chans_per_group).astype(np.float32)
+    assert_close(T.gpu_conv_fwd(p, x, w, bias=bias), oracle.conv_fwd(spec, x, w, bias), REL_HALF,
+                 f"fwd {name} uniform + bias")
+
+
+@pytest.mark.parametrize("name", sorted(SMALL_CONVS))
+def test_conv_bwd_small(gpu_ctx, name):
+    kw = SMALL_CONVS[name]
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(zlib.crc32(name.encode()) % 1000 + 1)
+    _, w, dy = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), f"bwd {name} exact")
+    _, w, dy = conv_data(p, kw, r, exact=False)
+    assert_close(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), REL_HALF, f"bwd {name} uniform")
+
+
+@pytest.mark.parametrize("name", sorted(n for n in {**SMALL_CONVS, **STRIDED_CONVS} if n != "flipped_kernel"))
+def test_conv_wu_small(gpu_ctx, name):
+    kw = {**SMALL_CONVS, **STRIDED_CONVS}[name]
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(zlib.crc32(name.encode()) % 1000 + 2)
+    x, _, dy = conv_data(p, kw, r, exact=True)
+    dw16, dw32 = T.gpu_conv_wu(p, x, dy)
+    exp, _ = oracle.conv_wu(spec, x, dy)
+    assert_exact(dw32, exp, f"wu {name} exact (fp32 sums)")
+    x, _, dy = conv_data(p, kw, r, exact=False)
+    dw16, dw32 = T.gpu_conv_wu(p, x, dy)
+    exp, _ = oracle.conv_wu(spec, x, dy)
+    assert_close(dw16, exp, REL_HALF, f"wu {name} uniform")
+    # the two outputs of one call agree: half result is the rounded fp32 sum
+    assert (dw32.astype(np.float16) == dw16).all()
+
+
+def test_conv_float_output(gpu_ctx):
+    kw = conv_case(2, [8, 8], [3, 3], 64, 64, padding=1)
+    p = capi.ConvParams.make(output_type=capi.FLOAT, **kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(21)
+    x, w, _ = conv_data(p, kw, r, exact=False)
+    got = T.gpu_conv_fwd(p, x, w)
+    assert got.dtype == np.float32
+    assert_close(got, oracle.conv_fwd(spec, x, w), 1e-4, "fwd fp32 out")
+
+
+def test_conv_quarter_fwd_bwd(gpu_ctx):
+    kw = conv_case(2, [8, 8], [3, 3], 128, 64, padding=1)
+    p = capi.ConvParams.make(input_type=capi.QUARTER, **kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(22)
+    xv = r.integers(-2, 3, (2, 128, 8, 8)).astype(np.float64)
+    wv = r.integers(-2, 3, (1, 64, 128, 3, 3)).astype(np.float64)
+    got = T.gpu_conv_fwd(p, oracle.e4m3_encode(xv), oracle.e4m3_encode(wv))
+    assert_exact(got, oracle.conv_fwd(spec, xv, wv), "quarter fwd")
+    dyv = r.integers(-2, 3, (2, 64, 8, 8)).astype(np.float64)
+    got = T.gpu_conv_bwd(p, oracle.e4m3_encode(dyv), oracle.e4m3_encode(wv))
+    assert_exact(got, oracle.conv_bwd(spec, dyv, wv), "quarter bwd")
+
+
+# BASELINE configurations at full size -------------------------------------------------
+
+def test_config2_conv3x3_fwd(gpu_ctx):
+    kw = conv_case(32, [56, 56], [3, 3], 64, 64, padding=1)
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(1234 + 2)
+    x, w, _ = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), "config 2 exact")
+    x, w, _ = conv_data(p, kw, r, exact=False)     # x ~ U[-1,1], w ~ U[-1/24, 1/24]
+    assert_close(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), REL_HALF, "config 2 uniform")
+
+
+def test_config3b_pointwise_stride2_fwd(gpu_ctx):
+    kw = conv_case(256, [56, 56], [1, 1], 256, 512, stride=2)
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(1234 + 3)
+    x, w, _ = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), "config 3b exact")
+
+
+def test_config4_fwd_bwd_wu(gpu_ctx):
+    kw = conv_case(256, [28, 28], [3, 3], 128, 128, padding=1)
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(1234 + 4)
+    x, w, dy = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), "config 4 fwd exact")
+    assert_exact(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), "config 4 bwd exact")
+    _, dw32 = T.gpu_conv_wu(p, x, dy)
+    assert_exact(dw32, oracle.conv_wu(spec, x, dy)[0], "config 4 wu exact (fp32 sums < 2^24)")
+    x, w, dy = conv_data(p, kw, r, exact=False)
+    assert_close(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), REL_HALF, "config 4 fwd uniform")
+    dw16, _ = T.gpu_conv_wu(p, x, dy)
+    assert_close(dw16, oracle.conv_wu(spec, x, dy)[0], REL_HALF, "config 4 wu uniform")
+
+
+# --------------------------------------------------------------------------- plumbing
+
+def test_layout_kernels(gpu_ctx):
+    import torch
+    r = T.rng(31)
+    x = r.integers(0, 60000, (3, 10, 7, 5)).astype(np.uint16)             # [N][C][H][W]
+    dx, out = T.to_dev(x.view(np.float16)), T.empty_dev((3, 7, 5, 10), np.float16)
+    torch.cuda.synchronize()
+    gpu_ctx.acts_to_device(2, 3, 10, 35, dx, out)
+    gpu_ctx.synchronize()
+    assert (out.cpu().numpy().view(np.uint16) == T.acts_to_device_layout(x)).all()
+    back = T.empty_dev((3, 10, 7, 5), np.float16)
+    torch.cuda.synchronize()
+    gpu_ctx.acts_from_device(2, 3, 10, 35, out, back)
+    gpu_ctx.synchronize()
+    assert (back.cpu().numpy().view(np.uint16) == x).all()
+    w = r.integers(0, 250, (2, 6, 5, 3, 3)).astype(np.uint8)              # [G][Co][Ci][kh][kw]
+    dw, wd = T.to_dev(w), T.empty_dev((2, 3, 3, 6, 5), np.uint8)
+    torch.cuda.synchronize()
+    gpu_ctx.weights_to_device(1, 2, 6, 5, 9, dw, wd)
+    gpu_ctx.synchronize()
+    assert (wd.cpu().numpy() == T.weights_to_device_layout(w)).all()
+    # weightsTransposeChansFlipXY: [G][k][Co][Ci] -> [G][flipped k][Ci][Co]
+    wt = T.empty_dev((2, 3, 3, 5, 6), np.uint8)
+    torch.cuda.synchronize()
+    gpu_ctx.weights_transpose_chans_flip_xy(1, 2, 6, 5, 9, wd, wt)
+    gpu_ctx.synchronize()
+    expect = np.transpose(T.weights_to_device_layout(w)[:, ::-1, ::-1], (0, 1, 2, 4, 3))
+    assert (wt.cpu().numpy() == expect).all()
+
+
+def test_host_buffer_entry_points(gpu_ctx):
+    r = T.rng(32)
+    a, b = T.small_int_half(r, (192, 128)), T.small_int_half(r, (128, 136), -3, 3)
+    d = np.empty((192, 136), np.float16)
+    gpu_ctx.matmul_host(capi.MatmulDesc.make(192, 128, 136), a, b, None, d)
+    assert_exact(d, oracle.gemm(a, b), "matmul_host")
+    kw = conv_case(2, [8, 8], [3, 3], 64, 64, padding=1)
+    p = capi.ConvParams.make(**kw)
+    x, w, _ = conv_data(p, kw, r, exact=True)
+    y = np.empty((2, 8, 8, 64), np.float16)
+    gpu_ctx.conv_fwd_host(p, T.acts_to_device_layout(x), T.weights_to_device_layout(w), y)
+    assert_exact(T.acts_from_device_layout(y), oracle.conv_fwd(T.spec_from_params(p), x, w), "conv_fwd_host")
+
+
+def test_scaled_add_and_cast(gpu_ctx):
+    import torch
+    r = T.rng(33)
+    w = T.uniform_half(r, (1000,))
+    d = r.uniform(-1, 1, 1000).astype(np.float32)
+    dw, dd = T.to_dev(w), T.to_dev(d)
+    torch.cuda.synchronize()
+    gpu_ctx.scaled_add_to(capi.HALF, dw, dd, -0.05, 1000)
+    gpu_ctx.synchronize()
+    expect = (w.astype(np.float32) + np.float32(-0.05) * d).astype(np.float16)
+    assert (dw.cpu().numpy() == expect).all()
+
+
+def test_unsupported_requests_fail_loudly(gpu_ctx):
+    p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, in_dilation=2)
+    with pytest.raises(capi.PlbError) as e:
+        gpu_ctx.conv_fwd(p, 0, 0, 0)
+    assert e.value.code == 3
+    p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, stride=0)
+    with pytest.raises(capi.PlbError) as e:
+        gpu_ctx.conv_fwd(p, 0, 0, 0)
+    assert e.value.code == 1 and e.value.message == "Stride must be non zero"
+    assert gpu_ctx.launch_count() > 0
