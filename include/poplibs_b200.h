@@ -184,8 +184,14 @@ typedef struct plb_conv_options {
   /* plan constraints this implementation understands; 0 = planner's choice */
   int32_t tile_n;        /* output channels per CTA tile: 64, 128 or 256     */
   int32_t split_k;       /* CTAs that share one output tile (weight update)  */
-  int32_t reserved[6];
+  int32_t plan_flags;    /* PLB_PLAN_* bits                                   */
+  int32_t reserved[5];
 } plb_conv_options;
+
+/* plb_conv_options.plan_flags */
+#define PLB_PLAN_FORCE_RESIDENT_WEIGHTS 1 /* keep weights in shared memory even for few tiles */
+#define PLB_PLAN_NO_RESIDENT_WEIGHTS 2    /* always stream the weights                        */
+#define PLB_PLAN_NO_HALO 4                /* one activation load per filter tap               */
 
 /* out = conv(in, weights) (+ bias), poplin::convolution
  * (include/poplin/Convolution.hpp:345-384, lib/poplin/Convolution.cpp:3128-3215).
@@ -246,6 +252,20 @@ PLB_API int plb_weights_transpose_chans_flip_xy(plb_context *ctx, uint32_t elem_
 PLB_API int plb_transpose_matrix(plb_context *ctx, uint32_t elem_bytes, uint32_t groups, uint32_t rows,
                          uint32_t cols, const void *d_src, void *d_dst);
 
+/* General strided element copy dst[i0..] = src[i0..] over a common logical
+ * shape (rank <= 8); strides are in elements and may be zero (broadcast source)
+ * or negative.  This is what a poplar::program::Copy between two tensor views
+ * lowers to, and how host data in logical order reaches a device layout. */
+#define PLB_MAX_VIEW_RANK 8
+PLB_API int plb_copy_strided(plb_context *ctx, uint32_t elem_bytes, uint32_t rank, const uint64_t *shape,
+                     const int64_t *src_strides, const int64_t *dst_strides, const void *d_src,
+                     void *d_dst);
+/* Fills `count` elements of type `dtype` (PLB_HALF / PLB_FLOAT) with `value`. */
+PLB_API int plb_fill(plb_context *ctx, int32_t dtype, void *d_dst, float value, size_t count);
+/* Device-side stopwatch on the context's stream (CUDA events). */
+PLB_API int plb_timer_start(plb_context *ctx);
+PLB_API int plb_timer_stop(plb_context *ctx, float *milliseconds);
+
 /* ------------------------------------------------------------------------ */
 /* Planner: the CTA-level plan chosen for a contraction (the role of         */
 /* poplin::getPlan, lib/poplin/ConvPlan.cpp:1877-1923, and what               */
@@ -262,6 +282,9 @@ typedef struct plb_plan {
   int32_t grid;        /* CTAs launched                                      */
   int32_t tiles;       /* output tiles                                       */
   int32_t b_mn_major;  /* right operand fed as an MN-major matrix            */
+  int32_t resident_weights; /* weights loaded once per CTA and kept in shared memory */
+  int32_t halo_rows;   /* extra input rows per activation load that let one load
+                          serve every vertical filter tap (0 = one load per tap) */
   uint64_t flops;      /* 2 * MACs (padding excluded)                        */
   uint64_t bytes;      /* operands read once + output written once           */
   uint64_t workspace_bytes;

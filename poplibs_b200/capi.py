@@ -13,6 +13,7 @@ PASS_NONE, PASS_NONE_MATMUL, PASS_INFERENCE_FWD, PASS_TRAINING_FWD, PASS_TRAININ
     PASS_TRAINING_WU, PASS_FC_INFERENCE_FWD, PASS_FC_TRAINING_FWD, PASS_FC_TRAINING_BWD, \
     PASS_FC_TRAINING_WU = range(10)
 MAX_DIMS = 3
+PLAN_FORCE_RESIDENT_WEIGHTS, PLAN_NO_RESIDENT_WEIGHTS, PLAN_NO_HALO = 1, 2, 4
 _U3 = C.c_uint32 * MAX_DIMS
 
 
@@ -99,12 +100,13 @@ class ConvParams(C.Structure):
 
 class ConvOptions(C.Structure):
     _fields_ = [("pass_", C.c_int32), ("partials_type", C.c_int32), ("tile_n", C.c_int32),
-                ("split_k", C.c_int32), ("reserved", C.c_int32 * 6)]
+                ("split_k", C.c_int32), ("plan_flags", C.c_int32), ("reserved", C.c_int32 * 5)]
 
     @staticmethod
-    def make(pass_=PASS_NONE, partials_type=FLOAT, tile_n=0, split_k=0):
+    def make(pass_=PASS_NONE, partials_type=FLOAT, tile_n=0, split_k=0, plan_flags=0):
         o = ConvOptions()
         o.pass_, o.partials_type, o.tile_n, o.split_k = pass_, partials_type, tile_n, split_k
+        o.plan_flags = plan_flags
         return o
 
 
@@ -113,7 +115,7 @@ class Plan(C.Structure):
                 ("tile_k_bytes", C.c_int32), ("box_w", C.c_int32), ("box_h", C.c_int32),
                 ("box_n", C.c_int32), ("stages", C.c_int32), ("split_k", C.c_int32),
                 ("grid", C.c_int32), ("tiles", C.c_int32), ("b_mn_major", C.c_int32),
-                ("flops", C.c_uint64), ("bytes", C.c_uint64), ("workspace_bytes", C.c_uint64)]
+                ("resident_weights", C.c_int32), ("halo_rows", C.c_int32), ("flops", C.c_uint64), ("bytes", C.c_uint64), ("workspace_bytes", C.c_uint64)]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
@@ -132,7 +134,7 @@ SYMBOLS = (
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
     "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
     "plb_weights_transpose_chans_flip_xy", "plb_transpose_matrix", "plb_matmul_plan",
-    "plb_conv_plan",
+    "plb_conv_plan", "plb_copy_strided", "plb_fill", "plb_timer_start", "plb_timer_stop",
 )
 
 
@@ -183,6 +185,11 @@ def lib():
                  "plb_weights_transpose_chans_flip_xy"):
         getattr(L, name).argtypes = [vp, u32, u32, u32, u32, u64, vp, vp]
     L.plb_transpose_matrix.argtypes = [vp, u32, u32, u32, u32, vp, vp]
+    L.plb_copy_strided.argtypes = [vp, u32, u32, C.POINTER(u64), C.POINTER(C.c_int64),
+                                   C.POINTER(C.c_int64), vp, vp]
+    L.plb_fill.argtypes = [vp, i32, vp, f32, sz]
+    L.plb_timer_start.argtypes = [vp]
+    L.plb_timer_stop.argtypes = [vp, C.POINTER(f32)]
     L.plb_matmul_plan.argtypes = [MP, PP]
     L.plb_conv_plan.argtypes = [CP, OP, i32, PP]
     _LIB = L
@@ -291,6 +298,15 @@ class Context:
     def weights_transpose_chans_flip_xy(self, elem_bytes, groups, co, ci, kelems, src, dst):
         _check(lib().plb_weights_transpose_chans_flip_xy(self._h, elem_bytes, groups, co, ci,
                                                          kelems, _ptr(src), _ptr(dst)))
+
+    def copy_strided(self, elem_bytes, shape, src_strides, dst_strides, src, dst):
+        n = len(shape)
+        _check(lib().plb_copy_strided(self._h, elem_bytes, n, (C.c_uint64 * n)(*shape),
+                                      (C.c_int64 * n)(*src_strides), (C.c_int64 * n)(*dst_strides),
+                                      _ptr(src), _ptr(dst)))
+
+    def fill(self, dtype, dst, value, count):
+        _check(lib().plb_fill(self._h, dtype, _ptr(dst), value, count))
 
     def transpose_matrix(self, elem_bytes, groups, rows, cols, src, dst):
         _check(lib().plb_transpose_matrix(self._h, elem_bytes, groups, rows, cols, _ptr(src), _ptr(dst)))

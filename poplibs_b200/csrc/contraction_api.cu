@@ -10,6 +10,14 @@ namespace plb {
 
 int launchScaleRows(plb_context *ctx, void *out, const void *c, float beta, bool out_f32,
                     uint32_t rows, uint32_t cols, long long ldo, long long ldc);
+int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+                         const void *d_in, const void *d_weights, const float *d_bias,
+                         void *d_out, plb_plan *plan_only);
+
+// TMA needs 16-byte pixel strides: 8 half / 16 quarter channels.
+static bool channelsFitTma(const plb_conv_params &p, uint32_t chans) {
+  return (size_t(chans) * dtypeBytes(p.input_type)) % 16 == 0;
+}
 
 namespace {
 
@@ -207,6 +215,7 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.bias = bias ? bias + size_t(g) * co : nullptr;
   r.out_f32 = p.output_type == PLB_FLOAT;
   r.force_tile_n = opt ? opt->tile_n : 0;
+  r.plan_flags = opt ? opt->plan_flags : 0;
   *q = r;
   return PLB_OK;
 }
@@ -265,6 +274,7 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.ldc = (long long)ctot;
   r.out_f32 = p.output_type == PLB_FLOAT;
   r.force_tile_n = opt ? opt->tile_n : 0;
+  r.plan_flags = opt ? opt->plan_flags : 0;
   *q = r;
   return PLB_OK;
 }
@@ -417,6 +427,13 @@ int plb_conv_plan(const plb_conv_params *p, const plb_conv_options *opt, int32_t
   ConvShape s;
   if (int rc = igemmConvShape(*p, &s)) return rc;
   *plan = plb_plan{};
+  if (pass != PLB_PASS_TRAINING_BWD && !channelsFitTma(*p, p->in_chans_per_group)) {
+    if (int rc = convFwdSmallChannels(nullptr, *p, opt, nullptr, nullptr, nullptr, nullptr, plan))
+      return rc;
+    plan->flops = 2 * numberOfMacs(*p);
+    plan->bytes = convBytes(*p, s, pass);
+    return PLB_OK;
+  }
   IgemmProblem q;
   if (pass == PLB_PASS_TRAINING_BWD) {
     if (int rc = convBwdProblem(*p, opt, s, 0, nullptr, nullptr, nullptr,
@@ -444,6 +461,8 @@ int plb_conv_fwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
     // nothing to accumulate: the output is the bias (or zero)
     return fail(PLB_ERR_UNSUPPORTED, "zero input channels are not implemented on this path yet");
   }
+  if (!channelsFitTma(*p, p->in_chans_per_group))
+    return convFwdSmallChannels(ctx, *p, opt, d_in, d_weights, d_bias, d_out, nullptr);
   if (s.strH > 1 || s.strW > 1) {
     const bool pointwise = s.KH == 1 && s.KW == 1 && s.padH == 0 && s.padW == 0;
     if (!pointwise && (s.strH > 8 || s.strW > 8))

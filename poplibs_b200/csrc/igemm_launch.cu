@@ -8,31 +8,61 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 namespace plb {
 
 namespace {
 
-template <int BN, bool kFp8, bool kBMn>
+// PLB_DISABLE_TMA_STORE=1 forces the plain vector-store epilogue (for A/B timing).
+const bool g_disable_tma_store = [] {
+  const char *e = std::getenv("PLB_DISABLE_TMA_STORE");
+  return e != nullptr && e[0] == '1';
+}();
+// PLB_DISABLE_HALO=1 loads one activation box per filter tap even where a strip
+// with a halo could serve a whole filter column.
+const bool g_disable_halo = [] {
+  const char *e = std::getenv("PLB_DISABLE_HALO");
+  return e != nullptr && e[0] == '1';
+}();
+// PLB_DISABLE_RESIDENT_WEIGHTS=1 keeps the weights in the streamed pipeline.
+const bool g_disable_resident = [] {
+  const char *e = std::getenv("PLB_DISABLE_RESIDENT_WEIGHTS");
+  return e != nullptr && e[0] == '1';
+}();
+
+template <int BN, bool kFp8, bool kBMn, bool kResB, bool kHalo>
 int launchInstance(plb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb,
-                   const IgemmArgs &args, int grid) {
-  using S = IgemmSmem<BN>;
+                   const CUtensorMap &tout, const IgemmArgs &args, int grid, int resident_bytes) {
+  using S = IgemmSmem<BN, kResB>;
   static bool configured[64] = {};
-  auto kernel = igemm_kernel<BN, kFp8, kBMn>;
+  auto kernel = igemm_kernel<BN, kFp8, kBMn, kResB, kHalo>;
   if (!configured[ctx->device & 63]) {
-    PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+    PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kIgemmSmemLimit));
     configured[ctx->device & 63] = true;
   }
-  kernel<<<grid, kIgemmThreads, S::kTotal, ctx->stream>>>(ta, tb, args);
+  const int smem = S::totalBytes(args.a_stage_bytes, args.num_stages, resident_bytes);
+  kernel<<<grid, kIgemmThreads, smem, ctx->stream>>>(ta, tb, tout, args);
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
 }
 
-template <int BN>
-int stagesFor() {
-  return IgemmSmem<BN>::kStages;
+int stagesFor(int bn, int a_stage_bytes, bool resident, int resident_bytes) {
+  const int a = a_stage_bytes;
+  switch (bn) {
+    case 64: return resident ? IgemmSmem<64, true>::stagesFor(a, resident_bytes) : IgemmSmem<64, false>::stagesFor(a, 0);
+    case 128: return resident ? IgemmSmem<128, true>::stagesFor(a, resident_bytes) : IgemmSmem<128, false>::stagesFor(a, 0);
+    default: return resident ? IgemmSmem<256, true>::stagesFor(a, resident_bytes) : IgemmSmem<256, false>::stagesFor(a, 0);
+  }
 }
+
+// Weights stay in shared memory when one N tile covers all output channels,
+// every CTA gets several pixel tiles to amortise the load over, and the
+// weights leave room for a pipeline of at least six activation stages.
+constexpr int kMaxResidentBytes = 96 * 1024;
 
 }  // namespace
 
@@ -84,13 +114,63 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
   plan->box_w = bw;
   plan->box_h = bh;
   plan->box_n = bb;
-  plan->stages = bn == 64 ? stagesFor<64>() : bn == 128 ? stagesFor<128>() : stagesFor<256>();
   plan->split_k = 1;
   plan->tiles = int(best_tiles * n_tiles);
   plan->grid = std::min(plan->tiles, sm_count > 0 ? sm_count : 148);
+  const int k_elems = kStageKBytes / elem;
+  const long k_iters = long(p.taps_h) * p.taps_w * ((p.k_per_tap + k_elems - 1) / k_elems);
+  const long resident_bytes = k_iters * bn * kStageKBytes;
+  const bool want_resident = (p.plan_flags & PLB_PLAN_FORCE_RESIDENT_WEIGHTS) != 0 ||
+                             plan->tiles >= 2 * plan->grid;
+  plan->resident_weights =
+      (!g_disable_resident && (p.plan_flags & PLB_PLAN_NO_RESIDENT_WEIGHTS) == 0 && n_tiles == 1 &&
+       resident_bytes <= kMaxResidentBytes && want_resident)
+          ? 1
+          : 0;
+  plan->halo_rows = 0;
+  plan->stages = stagesFor(bn, kTileM * kStageKBytes, plan->resident_weights != 0,
+                           plan->resident_weights ? int(resident_bytes) : 0);
+  // Halo mode: with resident weights and a filter taller than one row (unit
+  // vertical stride), load (box_h + halo) input rows once per horizontal tap
+  // instead of box_h rows per tap.  The tile rows are ordered (w, n, h) so that
+  // a vertical shift is a whole number of 8-row groups: box_w * box_n % 8 == 0.
+  const int halo = (p.taps_h - 1) * p.dil_h;
+  if (plan->resident_weights && !g_disable_halo && (p.plan_flags & PLB_PLAN_NO_HALO) == 0 &&
+      p.taps_h > 1 && p.stride_h == 1) {
+    long best_rows = -1, best_t = -1;
+    int hw = 0, hh = 0, hn = 0;
+    for (int w = 128; w >= 1; w >>= 1)
+      for (int n = 128 / w; n >= 1; n >>= 1) {
+        const int h = 128 / (w * n);
+        if ((w * n) % 8 != 0 || h + halo > 256 || (w - 1) * p.stride_w + 1 > 256) continue;
+        const long tiles = long((p.out_w + w - 1) / w) * ((p.out_h + h - 1) / h) *
+                           ((p.out_n + n - 1) / n);
+        const long rows = tiles * w * n * (h + halo);
+        if (best_rows < 0 || rows < best_rows || (rows == best_rows && tiles < best_t)) {
+          best_rows = rows;
+          best_t = tiles;
+          hw = w;
+          hh = h;
+          hn = n;
+        }
+      }
+    if (best_rows > 0) {
+      const int a_stage = hw * hn * (hh + halo) * kStageKBytes;
+      const int st = stagesFor(bn, a_stage, true, int(resident_bytes));
+      // worthwhile only if it really loads fewer rows than one box per tap
+      if (st >= 3 && best_rows * p.taps_w < best_tiles * kTileM * long(p.taps_h) * p.taps_w) {
+        plan->halo_rows = halo;
+        plan->box_w = hw;
+        plan->box_h = hh;
+        plan->box_n = hn;
+        plan->stages = st;
+        plan->tiles = int(best_t * n_tiles);
+        plan->grid = std::min(plan->tiles, sm_count > 0 ? sm_count : 148);
+      }
+    }
+  }
   plan->b_mn_major = p.b_mn ? 1 : 0;
   plan->workspace_bytes = 0;
-  (void)elem;
   return PLB_OK;
 }
 
@@ -100,13 +180,29 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   const CUtensorMapDataType dt =
       p.fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 
+  const bool halo = plan.halo_rows > 0;
+  // In halo mode the pixel dimensions are ordered (w, n, h) in every tensor map.
+  auto order = [&](uint64_t w, uint64_t h, uint64_t n, uint64_t *out3) {
+    out3[0] = w;
+    out3[1] = halo ? n : h;
+    out3[2] = halo ? h : n;
+  };
   CUtensorMap ta, tb;
   {
-    const uint32_t box[4] = {uint32_t(k_elems_per_stage),
-                             uint32_t((plan.box_w - 1) * p.stride_w + 1),
-                             uint32_t((plan.box_h - 1) * p.stride_h + 1), uint32_t(plan.box_n)};
-    const uint32_t es[4] = {1, uint32_t(p.stride_w), uint32_t(p.stride_h), 1};
-    if (int rc = encodeTensorMap(&ta, dt, 4, p.act, p.act_dims, p.act_strides, box, es)) return rc;
+    uint64_t dims[4] = {p.act_dims[0], 0, 0, 0}, strides[3];
+    order(p.act_dims[1], p.act_dims[2], p.act_dims[3], dims + 1);
+    strides[0] = p.act_strides[0];
+    strides[1] = halo ? p.act_strides[2] : p.act_strides[1];
+    strides[2] = halo ? p.act_strides[1] : p.act_strides[2];
+    uint64_t b3[3];
+    order(uint64_t((plan.box_w - 1) * p.stride_w + 1),
+          uint64_t((plan.box_h + plan.halo_rows - 1) * p.stride_h + 1), uint64_t(plan.box_n), b3);
+    const uint32_t box[4] = {uint32_t(k_elems_per_stage), uint32_t(b3[0]), uint32_t(b3[1]),
+                             uint32_t(b3[2])};
+    uint64_t e3[3];
+    order(uint64_t(p.stride_w), uint64_t(p.stride_h), 1, e3);
+    const uint32_t es[4] = {1, uint32_t(e3[0]), uint32_t(e3[1]), uint32_t(e3[2])};
+    if (int rc = encodeTensorMap(&ta, dt, 4, p.act, dims, strides, box, es)) return rc;
   }
   {
     uint32_t box[3];
@@ -124,6 +220,37 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   }
 
   IgemmArgs a{};
+  // Output through TMA when the tensor can be described to it: 16-byte aligned
+  // base and pixel stride.  Each epilogue warp stores a (columns, w, h, n) box
+  // holding its 32 pixels; 128 bytes of columns per box.
+  CUtensorMap tout;
+  std::memset(&tout, 0, sizeof tout);
+  const size_t out_es = p.out_f32 ? 4 : 2;
+  // the 32 rows of one epilogue warp as a box over the tile's row order
+  const int d2 = halo ? plan.box_n : plan.box_h;
+  a.sub_w = std::min(plan.box_w, 32);
+  a.sub_h = std::min(d2, 32 / a.sub_w);  // extent along the second row dimension
+  const int sub_3 = 32 / (a.sub_w * a.sub_h);
+  a.use_tma_store = 0;
+  if (!g_disable_tma_store && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
+      (size_t(p.ldc) * out_es) % 16 == 0) {
+    uint64_t dims[4] = {uint64_t(p.n_total), 0, 0, 0}, strides[3];
+    order(uint64_t(p.out_w), uint64_t(p.out_h), uint64_t(p.out_n), dims + 1);
+    const uint64_t sw = uint64_t(p.ldc) * out_es, sh = uint64_t(p.out_w) * p.ldc * out_es,
+                   sn = uint64_t(p.out_h) * p.out_w * p.ldc * out_es;
+    strides[0] = sw;
+    strides[1] = halo ? sn : sh;
+    strides[2] = halo ? sh : sn;
+    const uint32_t box[4] = {uint32_t(128 / out_es), uint32_t(a.sub_w), uint32_t(a.sub_h),
+                             uint32_t(sub_3)};
+    const uint32_t es[4] = {1, 1, 1, 1};
+    if (int rc = encodeTensorMap(&tout,
+                                 p.out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                 4, p.out, dims, strides, box, es))
+      return rc;
+    a.use_tma_store = 1;
+  }
   a.box_w = plan.box_w;
   a.box_h = plan.box_h;
   a.box_n = plan.box_n;
@@ -147,6 +274,12 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.flip_h = p.flip_h;
   a.flip_w = p.flip_w;
   a.group_m = 16;
+  a.h_outer = halo ? 1 : 0;
+  a.a_stage_bytes = plan.box_w * plan.box_n * (plan.box_h + plan.halo_rows) * kStageKBytes;
+  a.halo_step_bytes = p.dil_h * plan.box_w * plan.box_n * kStageKBytes;
+  a.num_stages = plan.stages;
+  const int resident_bytes =
+      plan.resident_weights ? a.taps_h * a.taps_w * a.k_chunks * plan.tile_n * kStageKBytes : 0;
   a.out = p.out;
   a.ldc = p.ldc;
   a.addend = p.beta != 0.f ? p.addend : nullptr;
@@ -156,12 +289,21 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.beta = p.beta;
   a.out_is_f32 = p.out_f32 ? 1 : 0;
   a.status = ctx->d_status;
+  a.trace = ctx->trace;
 
   const int grid = plan.grid;
-#define PLB_DISPATCH(BN)                                                      \
-  if (p.fp8) return launchInstance<BN, true, false>(ctx, ta, tb, a, grid);    \
-  if (p.b_mn) return launchInstance<BN, false, true>(ctx, ta, tb, a, grid);   \
-  return launchInstance<BN, false, false>(ctx, ta, tb, a, grid);
+#define PLB_DISPATCH2(BN, RES, HALO)                                                                   \
+  if (p.fp8) return launchInstance<BN, true, false, RES, HALO>(ctx, ta, tb, tout, a, grid, resident_bytes);  \
+  if (p.b_mn) return launchInstance<BN, false, true, RES, HALO>(ctx, ta, tb, tout, a, grid, resident_bytes); \
+  return launchInstance<BN, false, false, RES, HALO>(ctx, ta, tb, tout, a, grid, resident_bytes);
+#define PLB_DISPATCH(BN)                       \
+  if (halo) {                                  \
+    PLB_DISPATCH2(BN, true, true)              \
+  } else if (plan.resident_weights) {          \
+    PLB_DISPATCH2(BN, true, false)             \
+  } else {                                     \
+    PLB_DISPATCH2(BN, false, false)            \
+  }
   switch (plan.tile_n) {
     case 64: PLB_DISPATCH(64)
     case 128: PLB_DISPATCH(128)
@@ -169,6 +311,7 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
     default: break;
   }
 #undef PLB_DISPATCH
+#undef PLB_DISPATCH2
   return fail(PLB_ERR_INVALID_OPTION, "unsupported tile_n in plan");
 }
 

@@ -225,6 +225,37 @@ __global__ void scaleRowsKernel(void *out, const void *c, float beta, int out_f3
   }
 }
 
+struct StridedCopyArgs {
+  uint32_t rank;
+  uint64_t shape[PLB_MAX_VIEW_RANK];
+  long long src_strides[PLB_MAX_VIEW_RANK];
+  long long dst_strides[PLB_MAX_VIEW_RANK];
+};
+
+template <typename T>
+__global__ void stridedCopyKernel(const T *__restrict__ src, T *__restrict__ dst,
+                                  StridedCopyArgs a, size_t total) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    size_t r = i;
+    long long so = 0, dof = 0;
+    for (int d = int(a.rank) - 1; d >= 0; --d) {
+      const size_t idx = r % a.shape[d];
+      r /= a.shape[d];
+      so += (long long)idx * a.src_strides[d];
+      dof += (long long)idx * a.dst_strides[d];
+    }
+    dst[dof] = src[so];
+  }
+}
+
+template <typename T>
+__global__ void fillKernel(T *dst, T value, size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n;
+       i += size_t(gridDim.x) * blockDim.x)
+    dst[i] = value;
+}
+
 int launchScaleRows(plb_context *ctx, void *out, const void *c, float beta, bool out_f32,
                     uint32_t rows, uint32_t cols, long long ldo, long long ldc) {
   if (rows == 0 || cols == 0) return PLB_OK;
@@ -301,6 +332,8 @@ void plb_context_destroy(plb_context *ctx) {
   for (int i = 0; i < plb_context::kScratchSlots; ++i)
     if (ctx->scratch[i]) cudaFree(ctx->scratch[i]);
   if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
+  if (ctx->timer_stop) cudaEventDestroy(ctx->timer_stop);
   if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
 }
@@ -432,6 +465,81 @@ int plb_transpose_matrix(plb_context *ctx, uint32_t elem_bytes, uint32_t groups,
   return launchTranspose(ctx, elem_bytes, groups, rows, cols, d_src, d_dst);
 }
 
+int plb_copy_strided(plb_context *ctx, uint32_t elem_bytes, uint32_t rank, const uint64_t *shape,
+                     const int64_t *src_strides, const int64_t *dst_strides, const void *d_src,
+                     void *d_dst) {
+  if (int rc = activate(ctx)) return rc;
+  if (rank > PLB_MAX_VIEW_RANK) return fail(PLB_ERR_UNSUPPORTED, "tensor rank above 8");
+  StridedCopyArgs a{};
+  a.rank = rank ? rank : 1;
+  size_t total = 1;
+  a.shape[0] = 1;
+  for (uint32_t d = 0; d < rank; ++d) {
+    a.shape[d] = shape[d];
+    a.src_strides[d] = src_strides[d];
+    a.dst_strides[d] = dst_strides[d];
+    total *= shape[d];
+  }
+  if (total == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(148) * 32));
+  switch (elem_bytes) {
+    case 1:
+      stridedCopyKernel<uint8_t><<<grid, 256, 0, ctx->stream>>>(
+          static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), a, total);
+      break;
+    case 2:
+      stridedCopyKernel<uint16_t><<<grid, 256, 0, ctx->stream>>>(
+          static_cast<const uint16_t *>(d_src), static_cast<uint16_t *>(d_dst), a, total);
+      break;
+    case 4:
+      stridedCopyKernel<uint32_t><<<grid, 256, 0, ctx->stream>>>(
+          static_cast<const uint32_t *>(d_src), static_cast<uint32_t *>(d_dst), a, total);
+      break;
+    default:
+      return fail(PLB_ERR_INVALID_PARAMS, "element size must be 1, 2 or 4 bytes");
+  }
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int plb_fill(plb_context *ctx, int32_t dtype, void *d_dst, float value, size_t count) {
+  if (int rc = activate(ctx)) return rc;
+  if (count == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((count + 255) / 256, size_t(148) * 16));
+  if (dtype == PLB_HALF)
+    fillKernel<__half><<<grid, 256, 0, ctx->stream>>>(static_cast<__half *>(d_dst),
+                                                      __float2half_rn(value), count);
+  else if (dtype == PLB_FLOAT)
+    fillKernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<float *>(d_dst), value, count);
+  else
+    return fail(PLB_ERR_INVALID_PARAMS, "fill type must be half or float");
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int plb_timer_start(plb_context *ctx) {
+  if (int rc = activate(ctx)) return rc;
+  if (!ctx->timer_start) {
+    PLB_CUDA(cudaEventCreate(&ctx->timer_start));
+    PLB_CUDA(cudaEventCreate(&ctx->timer_stop));
+  }
+  PLB_CUDA(cudaEventRecord(ctx->timer_start, ctx->stream));
+  return PLB_OK;
+}
+
+int plb_timer_stop(plb_context *ctx, float *milliseconds) {
+  if (int rc = activate(ctx)) return rc;
+  if (!ctx->timer_start) return fail(PLB_ERR_INVALID_PARAMS, "timer was not started");
+  PLB_CUDA(cudaEventRecord(ctx->timer_stop, ctx->stream));
+  PLB_CUDA(cudaEventSynchronize(ctx->timer_stop));
+  float ms = 0.f;
+  PLB_CUDA(cudaEventElapsedTime(&ms, ctx->timer_start, ctx->timer_stop));
+  if (milliseconds) *milliseconds = ms;
+  return PLB_OK;
+}
+
 int plb_cast_from_f32(plb_context *ctx, int32_t dtype, void *d_dst, const float *d_src,
                       size_t count) {
   if (int rc = activate(ctx)) return rc;
@@ -469,3 +577,11 @@ int plb_scaled_add_to(plb_context *ctx, int32_t dtype, void *d_weights, const fl
 }
 
 }  // extern "C"
+
+#ifdef PLB_TRACE
+// Development builds only: attach a device buffer of 3*4096 clock stamps.
+extern "C" __attribute__((visibility("default"))) void plb_debug_set_trace(plb_context *ctx,
+                                                                            long long *d_trace) {
+  ctx->trace = d_trace;
+}
+#endif

@@ -19,6 +19,8 @@ struct plb_context {
   bool owns_stream = false;
   int *d_status = nullptr;        // kernel status word (0 = OK)
   uint64_t launches = 0;          // kernels launched through this context
+  long long *trace = nullptr;     // device timeline buffer for builds with -DPLB_TRACE
+  cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
   // grow-only scratch buffers: [0] operand rearrangement / partial sums,
   // [1..] staging for the host-buffer entry points
   static constexpr int kScratchSlots = 8;
@@ -84,6 +86,7 @@ struct IgemmProblem {
   float alpha = 1.f, beta = 0.f;
   bool out_f32 = false;
   int force_tile_n = 0;  // 0 = planner's choice
+  int plan_flags = 0;    // PLB_PLAN_* bits
 };
 
 // Fills the tiling part of `plan` for a problem; returns non-zero if the

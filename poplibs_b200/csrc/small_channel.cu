@@ -1,0 +1,197 @@
+// Forward convolution for layers whose input has too few channels for a TMA
+// row (the ResNet stem: 3 channels, 7x7, stride 2).  NHWC pixels of 6 bytes
+// cannot be addressed by TMA (16-byte granularity), and a 3-channel reduction
+// would waste the tensor core's K dimension.  The layer is rewritten as an
+// equivalent stride-1 convolution with the horizontal taps folded into K:
+//
+//  1. space-to-depth: stride s and the padding are absorbed into a rearranged
+//     input X2[n][h2][w2][(ph, pw, c)] with C2 = s*s*Cp channels (Cp = channels
+//     padded so that a pixel is a multiple of 16 bytes), zero where the
+//     original is padding.  The s-strided KHxKW filter becomes a stride-1
+//     K2h x K2w filter over X2 (K2 = ceil(K / s)).
+//  2. the K2w horizontal taps of one output pixel are K2w consecutive pixels
+//     of X2, i.e. one contiguous run of K2w*C2 elements (<= 64): the activation
+//     tensor map describes overlapping windows (pixel stride C2 elements,
+//     window 64 elements), so each K step is one ordinary 128-byte row per
+//     output pixel and the implicit-GEMM kernel runs unchanged with K2h taps.
+//
+// This is the role the reference gives to its expandDims / outChanFlattenDims
+// input transforms for small channel counts (lib/poplin/ConvPlan.cpp:1100-1224,
+// lib/poplin/Convolution.cpp:665-978).
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "conv_geometry.h"
+#include "runtime.h"
+
+namespace plb {
+
+struct S2dShape {
+  int N, H, W, C;       // input
+  int s, padH, padW;    // stride (both dims), padding
+  int KH, KW;
+  int OH, OW;
+  int Cp, C2;           // padded channels per original pixel, channels of X2
+  int K2h, K2w;         // taps after folding the stride
+  int H2, W2;           // extent of X2
+};
+
+// X2[n][h2][w2][(ph*s + pw)*Cp + c] = X[n][h2*s + ph - padH][w2*s + pw - padW][c]
+__global__ void s2dInputKernel(const __half *__restrict__ x, __half *__restrict__ x2, S2dShape g) {
+  // one thread per 8 output halves (16 bytes)
+  const size_t vecs_per_pixel = size_t(g.C2) / 8;
+  const size_t total = size_t(g.N) * g.H2 * g.W2 * vecs_per_pixel;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const int v = int(i % vecs_per_pixel);
+    size_t r = i / vecs_per_pixel;
+    const int w2 = int(r % g.W2);
+    r /= g.W2;
+    const int h2 = int(r % g.H2);
+    const int n = int(r / g.H2);
+    __align__(16) __half vals[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c2 = v * 8 + j;
+      const int sub = c2 / g.Cp, c = c2 - sub * g.Cp;
+      const int ph = sub / g.s, pw = sub - ph * g.s;
+      const int ih = h2 * g.s + ph - g.padH, iw = w2 * g.s + pw - g.padW;
+      __half val = __float2half(0.f);
+      if (c < g.C && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W)
+        val = x[((size_t(n) * g.H + ih) * g.W + iw) * g.C + c];
+      vals[j] = val;
+    }
+    *reinterpret_cast<uint4 *>(x2 + i * 8) = *reinterpret_cast<const uint4 *>(vals);
+  }
+}
+
+// W2[a][co][(b*s*s + ph*s + pw)*Cp + c] = W[a*s + ph][b*s + pw][co][c], rows padded to 64.
+__global__ void s2dWeightsKernel(const __half *__restrict__ w, __half *__restrict__ w2, S2dShape g,
+                                 int co_total) {
+  const size_t total = size_t(g.K2h) * co_total * 64;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const int k = int(i % 64);
+    size_t r = i / 64;
+    const int co = int(r % co_total);
+    const int a = int(r / co_total);
+    __half val = __float2half(0.f);
+    const int b = k / g.C2;
+    if (b < g.K2w) {
+      const int c2 = k - b * g.C2;
+      const int sub = c2 / g.Cp, c = c2 - sub * g.Cp;
+      const int ph = sub / g.s, pw = sub - ph * g.s;
+      const int kh = a * g.s + ph, kw = b * g.s + pw;
+      if (c < g.C && kh < g.KH && kw < g.KW)
+        val = w[((size_t(kh) * g.KW + kw) * co_total + co) * g.C + c];
+    }
+    w2[i] = val;
+  }
+}
+
+// Returns PLB_ERR_UNSUPPORTED (with a message) when the layer does not fit this path.
+int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+                         const void *d_in, const void *d_weights, const float *d_bias,
+                         void *d_out, plb_plan *plan_only) {
+  if (p.num_field_dims != 2 || p.groups != 1 || p.input_type != PLB_HALF)
+    return fail(PLB_ERR_UNSUPPORTED,
+                "input channel count must be a multiple of 8 (half) / 16 (quarter) unless the "
+                "layer is a 2-D, ungrouped half convolution");
+  for (unsigned d = 0; d != 2; ++d)
+    if (p.in_trunc_lo[d] || p.in_trunc_hi[d] || p.in_dilation[d] != 1 || p.in_flip[d] ||
+        p.k_trunc_lo[d] || p.k_trunc_hi[d] || p.k_pad_lo[d] || p.k_pad_hi[d] || p.k_flip[d] ||
+        p.k_dilation[d] != 1 || p.out_trunc_lo[d] || p.out_trunc_hi[d] || p.out_pad_lo[d] ||
+        p.out_pad_hi[d])
+      return fail(PLB_ERR_UNSUPPORTED,
+                  "small-channel convolutions support padding and stride only");
+  if (p.stride[0] != p.stride[1] || p.stride[0] > 2)
+    return fail(PLB_ERR_UNSUPPORTED, "small-channel convolutions need equal strides of 1 or 2");
+  S2dShape g{};
+  g.N = int(p.batch);
+  g.H = int(p.field[0]);
+  g.W = int(p.field[1]);
+  g.C = int(p.in_chans_per_group);
+  g.s = int(p.stride[0]);
+  g.padH = int(p.in_pad_lo[0]);
+  g.padW = int(p.in_pad_lo[1]);
+  g.KH = int(p.kernel[0]);
+  g.KW = int(p.kernel[1]);
+  g.OH = int(outputSize(p, 0));
+  g.OW = int(outputSize(p, 1));
+  // pixel of X2 must be a multiple of 16 bytes = 8 halves
+  g.Cp = g.C;
+  while ((g.s * g.s * g.Cp) % 8 != 0) ++g.Cp;
+  g.C2 = g.s * g.s * g.Cp;
+  g.K2h = (g.KH + g.s - 1) / g.s;
+  g.K2w = (g.KW + g.s - 1) / g.s;
+  if (g.K2w * g.C2 > 64)
+    return fail(PLB_ERR_UNSUPPORTED,
+                "small-channel convolution: folded filter row of " +
+                    std::to_string(g.K2w * g.C2) + " elements exceeds one 128-byte K step");
+  g.H2 = g.OH + g.K2h - 1;
+  g.W2 = g.OW + g.K2w - 1;
+  const int co = int(p.out_chans_per_group);
+  // tail of the last row: the 64-element window of the last pixel may run past
+  // the K2w*C2 elements that carry weights; pad the allocation so it stays inside
+  const size_t x2_elems = size_t(g.N) * g.H2 * g.W2 * g.C2 + 64;
+  const size_t w2_elems = size_t(g.K2h) * co * 64;
+
+  IgemmProblem q;
+  q.act_dims[0] = 64;
+  q.act_dims[1] = uint64_t(g.OW);
+  q.act_dims[2] = uint64_t(g.H2);
+  q.act_dims[3] = uint64_t(g.N);
+  q.act_strides[0] = uint64_t(g.C2) * 2;
+  q.act_strides[1] = uint64_t(g.W2) * g.C2 * 2;
+  q.act_strides[2] = uint64_t(g.H2) * g.W2 * g.C2 * 2;
+  q.wgt_dims[0] = 64;
+  q.wgt_dims[1] = uint64_t(co);
+  q.wgt_dims[2] = uint64_t(g.K2h);
+  q.wgt_strides[0] = 128;
+  q.wgt_strides[1] = uint64_t(co) * 128;
+  q.out_w = g.OW;
+  q.out_h = g.OH;
+  q.out_n = g.N;
+  q.n_total = co;
+  q.k_per_tap = 64;
+  q.taps_h = g.K2h;
+  q.taps_w = 1;
+  q.ldc = co;
+  q.bias = d_bias;
+  q.out_f32 = p.output_type == PLB_FLOAT;
+  q.force_tile_n = opt ? opt->tile_n : 0;
+  q.plan_flags = opt ? opt->plan_flags : 0;
+  plb_plan plan{};
+  if (int rc = planIgemm(q, ctx ? ctx->sm_count : 148, &plan)) return rc;
+  plan.kernel = 2;
+  plan.workspace_bytes = (x2_elems + w2_elems) * 2;
+  if (plan_only) {
+    *plan_only = plan;
+    return PLB_OK;
+  }
+  void *ws = nullptr;
+  if (int rc = scratch(ctx, 0, plan.workspace_bytes + 256, &ws)) return rc;
+  __half *x2 = static_cast<__half *>(ws);
+  __half *w2 = x2 + ((x2_elems + 127) & ~size_t(127));
+  {
+    const size_t vecs = size_t(g.N) * g.H2 * g.W2 * (g.C2 / 8);
+    const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 16));
+    s2dInputKernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const __half *>(d_in), x2, g);
+    PLB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    // the 64 trailing elements only ever meet zero weights, but must be finite
+    PLB_CUDA(cudaMemsetAsync(x2 + size_t(g.N) * g.H2 * g.W2 * g.C2, 0, 128, ctx->stream));
+    const int wgrid = int((w2_elems + 255) / 256);
+    s2dWeightsKernel<<<wgrid, 256, 0, ctx->stream>>>(static_cast<const __half *>(d_weights), w2, g,
+                                                     co);
+    PLB_CUDA(cudaGetLastError());
+    ctx->launches++;
+  }
+  q.act = x2;
+  q.wgt = w2;
+  q.out = d_out;
+  return launchIgemm(ctx, q, plan);
+}
+
+}  // namespace plb

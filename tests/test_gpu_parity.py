@@ -228,6 +228,65 @@ def test_conv_wu_small(gpu_ctx, name):
     assert (dw32.astype(np.float16) == dw16).all()
 
 
+PLAN_VARIANTS = {
+    "streamed": capi.PLAN_NO_RESIDENT_WEIGHTS,
+    "resident": capi.PLAN_FORCE_RESIDENT_WEIGHTS | capi.PLAN_NO_HALO,
+    "resident_halo": capi.PLAN_FORCE_RESIDENT_WEIGHTS,
+}
+
+
+@pytest.mark.parametrize("variant", sorted(PLAN_VARIANTS))
+@pytest.mark.parametrize("name", ["3x3_pad1", "ragged_chans", "kernel_dilation", "asym_padding",
+                                  "flipped_kernel", "batch1_big_field", "3x3_s2x3", "one_dim"])
+def test_conv_plan_variants_agree_with_oracle(gpu_ctx, name, variant):
+    """Every way the planner may run a layer (weights streamed, weights
+    resident, resident with halo strips) must give the oracle's result."""
+    kw = {**SMALL_CONVS, **STRIDED_CONVS}[name]
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    opt = capi.ConvOptions.make(plan_flags=PLAN_VARIANTS[variant])
+    r = T.rng(zlib.crc32((name + variant).encode()) % 1000)
+    x, w, dy = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w, opt=opt), oracle.conv_fwd(spec, x, w), f"fwd {name} {variant}")
+    if name not in STRIDED_CONVS:
+        assert_exact(T.gpu_conv_bwd(p, dy, w, opt=opt), oracle.conv_bwd(spec, dy, w), f"bwd {name} {variant}")
+
+
+def test_small_channel_stem_layers(gpu_ctx):
+    # 3-channel inputs go through the space-to-depth path
+    for kw in (conv_case(2, [18, 22], [7, 7], 3, 64, padding=3, stride=2),
+               conv_case(3, [9, 11], [3, 3], 3, 32, padding=1),
+               conv_case(2, [12, 12], [5, 5], 4, 64, padding=2, stride=2),
+               conv_case(1, [224, 224], [7, 7], 3, 64, padding=3, stride=2)):
+        p = capi.ConvParams.make(**kw)
+        spec = T.spec_from_params(p)
+        r = T.rng(77)
+        x, w, _ = conv_data(p, kw, r, exact=True)
+        assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), f"stem {kw} exact")
+        x, w, _ = conv_data(p, kw, r, exact=False)
+        assert_close(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), REL_HALF, f"stem {kw} uniform")
+
+
+def test_config3a_stem_sampled_images(gpu_ctx):
+    # 7x7 stride 2 pad 3, N=256 224x224x3 -> 64: full-size run, oracle on sampled images
+    import torch
+    kw = conv_case(256, [224, 224], [7, 7], 3, 64, padding=3, stride=2)
+    p = capi.ConvParams.make(**kw)
+    r = T.rng(1234 + 3)
+    x, w, _ = conv_data(p, kw, r, exact=True)
+    got = T.gpu_conv_fwd(p, x, w)
+    pick = [0, 100, 255]
+    p1 = capi.ConvParams.make(**{**kw, "batch": len(pick)})
+    assert_exact(got[pick], oracle.conv_fwd(T.spec_from_params(p1), x[pick], w), "config 3a sampled images")
+    # every image is an independent problem: a second image set equal to the
+    # first must give identical outputs (no cross-image leakage through tiles)
+    x[128:] = x[:128]
+    got = T.gpu_conv_fwd(p, x, w)
+    assert (got[128:] == got[:128]).all()
+    del got
+    torch.cuda.empty_cache()
+
+
 def test_conv_float_output(gpu_ctx):
     kw = conv_case(2, [8, 8], [3, 3], 64, 64, padding=1)
     p = capi.ConvParams.make(output_type=capi.FLOAT, **kw)
