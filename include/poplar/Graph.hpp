@@ -76,6 +76,8 @@ public:
   const std::map<std::string, Tensor> &hostReads() const;
   /// Scratch variable that lives as long as the graph (plan-private buffers).
   Tensor addScratch(const Type &type, const std::vector<std::size_t> &shape);
+  /// Gives every variable created so far its device memory (done by the Engine).
+  void allocateDeviceMemory();
 
 private:
   Tensor addConstantImpl(const Type &type, const std::vector<std::size_t> &shape, double value,

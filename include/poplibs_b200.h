@@ -185,7 +185,9 @@ typedef struct plb_conv_options {
   int32_t tile_n;        /* output channels per CTA tile: 64, 128 or 256     */
   int32_t split_k;       /* CTAs that share one output tile (weight update)  */
   int32_t plan_flags;    /* PLB_PLAN_* bits                                   */
-  int32_t reserved[5];
+  int32_t scale_in;      /* QUARTER metadata exponents of the activations and  */
+  int32_t scale_weights; /* the weights: value = stored * 2^scale              */
+  int32_t reserved[3];
 } plb_conv_options;
 
 /* plb_conv_options.plan_flags */
@@ -198,6 +200,15 @@ typedef struct plb_conv_options {
  * d_bias may be NULL (poplin::addBias fused, include/poplin/Convolution.hpp:536-544). */
 PLB_API int plb_conv_fwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
                  const void *d_in, const void *d_weights, const float *d_bias, void *d_out);
+/* The general form behind poplin::convolution(..., transposeAndFlipWeights, ...)
+ * (lib/poplin/Convolution.cpp:3067-3126): with transpose_and_flip_weights != 0
+ * d_weights holds [G][kernel...][Ci][Co] -- the device layout of the weights of
+ * the layer this convolution is the backward pass of -- and is used with its
+ * channel axes swapped and its spatial axes flipped, without being rearranged
+ * in memory (half; quarter weights are transposed into scratch first). */
+PLB_API int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                    const void *d_in, const void *d_weights, const float *d_bias, void *d_out,
+                    int transpose_and_flip_weights);
 /* Gradient w.r.t. the input from the FORWARD pass's params and weights:
  * what convolution(zDeltas, weights, getGradientParams(p), true) computes
  * (lib/poplin/ConvUtil.cpp:728-795, lib/poplin/Convolution.cpp:3077-3086). */
@@ -215,6 +226,10 @@ PLB_API int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_co
  * (popops::scaledAddTo in convolutionWeightUpdate, lib/poplin/Convolution.cpp:3509-3522). */
 PLB_API int plb_scaled_add_to(plb_context *ctx, int32_t dtype, void *d_weights,
                       const float *d_deltas_f32, float scale, size_t count);
+/* acts[pixel][c] += biases[c] on device-layout activations (poplin::addBias,
+ * include/poplin/Convolution.hpp:570-572); biases have the activations' type. */
+PLB_API int plb_add_bias(plb_context *ctx, int32_t dtype, void *d_acts, const void *d_biases,
+                 uint64_t pixels, uint32_t chans);
 /* fp32 -> half/float cast of a buffer (popops::cast after a reduction). */
 PLB_API int plb_cast_from_f32(plb_context *ctx, int32_t dtype, void *d_dst, const float *d_src,
                       size_t count);
@@ -293,6 +308,9 @@ typedef struct plb_plan {
 PLB_API int plb_matmul_plan(const plb_matmul_desc *desc, plb_plan *plan);
 PLB_API int plb_conv_plan(const plb_conv_params *p, const plb_conv_options *opt, int32_t pass,
                   plb_plan *plan);
+/* Plan of the weight-update pass of the FORWARD parameters `p`
+ * (poplin::reportWeightUpdatePlanInfo, include/poplin/Convolution.hpp:690-694). */
+PLB_API int plb_conv_wu_plan(const plb_conv_params *p, const plb_conv_options *opt, plb_plan *plan);
 
 #ifdef __cplusplus
 }

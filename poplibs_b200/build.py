@@ -71,3 +71,35 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+
+
+POPLIN_OUT = os.path.join(HERE, "libpoplin_b200.so")
+POPLIN_DIRS = [os.path.join(CSRC, "poplar"), os.path.join(CSRC, "poplin")]
+CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
+
+
+def build_poplin(force: bool = False) -> str:
+    """The C++ poplar / poplin layer over the C ABI -> libpoplin_b200.so."""
+    build()
+    cxx = shutil.which("g++") or "g++"
+    objs, procs = [], []
+    headers = _headers()
+    for d in POPLIN_DIRS:
+        headers += [os.path.join(d, f) for f in os.listdir(d) if f.endswith((".hpp", ".h"))]
+    for d in POPLIN_DIRS:
+        for src in sorted(f for f in os.listdir(d) if f.endswith(".cpp")):
+            path = os.path.join(d, src)
+            obj = os.path.join(OBJ_DIR, "poplin_" + os.path.splitext(src)[0] + ".o")
+            objs.append(obj)
+            if not force and _newer(obj, [path] + headers):
+                continue
+            procs.append((src, subprocess.Popen([cxx] + CXX_FLAGS + ["-c", path, "-o", obj],
+                                                stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for src, proc in procs:
+        out, _ = proc.communicate()
+        if proc.returncode != 0:
+            raise RuntimeError(f"g++ failed on {src}:\n{out}")
+    if force or procs or not _newer(POPLIN_OUT, objs + [OUT]):
+        subprocess.run([cxx, "-shared", "-o", POPLIN_OUT] + objs +
+                       ["-L" + HERE, "-lpoplibs_b200", "-Wl,-rpath,$ORIGIN"], check=True)
+    return POPLIN_OUT

@@ -100,13 +100,15 @@ class ConvParams(C.Structure):
 
 class ConvOptions(C.Structure):
     _fields_ = [("pass_", C.c_int32), ("partials_type", C.c_int32), ("tile_n", C.c_int32),
-                ("split_k", C.c_int32), ("plan_flags", C.c_int32), ("reserved", C.c_int32 * 5)]
+                ("split_k", C.c_int32), ("plan_flags", C.c_int32), ("scale_in", C.c_int32), ("scale_weights", C.c_int32),
+                ("reserved", C.c_int32 * 3)]
 
     @staticmethod
-    def make(pass_=PASS_NONE, partials_type=FLOAT, tile_n=0, split_k=0, plan_flags=0):
+    def make(pass_=PASS_NONE, partials_type=FLOAT, tile_n=0, split_k=0, plan_flags=0, scale_in=0,
+             scale_weights=0):
         o = ConvOptions()
         o.pass_, o.partials_type, o.tile_n, o.split_k = pass_, partials_type, tile_n, split_k
-        o.plan_flags = plan_flags
+        o.plan_flags, o.scale_in, o.scale_weights = plan_flags, scale_in, scale_weights
         return o
 
 
@@ -129,12 +131,12 @@ SYMBOLS = (
     "plb_context_destroy", "plb_context_stream", "plb_synchronize", "plb_launch_count",
     "plb_malloc", "plb_free", "plb_memcpy_h2d", "plb_memcpy_d2h", "plb_memset",
     "plb_matmul", "plb_matmul_host", "plb_conv_validate", "plb_conv_output_field",
-    "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_conv_bwd", "plb_conv_wu",
-    "plb_scaled_add_to", "plb_cast_from_f32", "plb_conv_fwd_host",
+    "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution", "plb_conv_bwd", "plb_conv_wu",
+    "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_fwd_host",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
     "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
     "plb_weights_transpose_chans_flip_xy", "plb_transpose_matrix", "plb_matmul_plan",
-    "plb_conv_plan", "plb_copy_strided", "plb_fill", "plb_timer_start", "plb_timer_stop",
+    "plb_conv_plan", "plb_conv_wu_plan", "plb_copy_strided", "plb_fill", "plb_timer_start", "plb_timer_stop",
 )
 
 
@@ -174,10 +176,12 @@ def lib():
     L.plb_conv_macs.argtypes = [CP]
     L.plb_conv_macs.restype = u64
     L.plb_conv_fwd.argtypes = [vp, CP, OP, vp, vp, vp, vp]
+    L.plb_convolution.argtypes = [vp, CP, OP, vp, vp, vp, vp, C.c_int]
     L.plb_conv_bwd.argtypes = [vp, CP, OP, vp, vp, vp]
     L.plb_conv_wu.argtypes = [vp, CP, OP, vp, vp, vp, vp]
     L.plb_scaled_add_to.argtypes = [vp, i32, vp, vp, f32, sz]
     L.plb_cast_from_f32.argtypes = [vp, i32, vp, vp, sz]
+    L.plb_add_bias.argtypes = [vp, i32, vp, vp, u64, u32]
     L.plb_conv_fwd_host.argtypes = [vp, CP, OP, vp, vp, vp, vp]
     for name in ("plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device"):
         getattr(L, name).argtypes = [vp, u32, u32, u32, u64, vp, vp]
@@ -192,6 +196,7 @@ def lib():
     L.plb_timer_stop.argtypes = [vp, C.POINTER(f32)]
     L.plb_matmul_plan.argtypes = [MP, PP]
     L.plb_conv_plan.argtypes = [CP, OP, i32, PP]
+    L.plb_conv_wu_plan.argtypes = [CP, OP, PP]
     _LIB = L
     return L
 
@@ -264,6 +269,11 @@ class Context:
         _check(lib().plb_conv_fwd_host(self._h, C.byref(p), C.byref(opt) if opt else None,
                                        _ptr(x), _ptr(w), _ptr(bias), _ptr(out)))
 
+    def convolution(self, p: ConvParams, x, w, out, bias=None, opt: Optional[ConvOptions] = None,
+                    transpose_and_flip_weights=False):
+        _check(lib().plb_convolution(self._h, C.byref(p), C.byref(opt) if opt else None, _ptr(x),
+                                     _ptr(w), _ptr(bias), _ptr(out), int(transpose_and_flip_weights)))
+
     def conv_bwd(self, p: ConvParams, dy, w, dx, opt: Optional[ConvOptions] = None):
         _check(lib().plb_conv_bwd(self._h, C.byref(p), C.byref(opt) if opt else None,
                                   _ptr(dy), _ptr(w), _ptr(dx)))
@@ -320,5 +330,8 @@ def matmul_plan(desc: MatmulDesc) -> Plan:
 
 def conv_plan(p: ConvParams, pass_: int = PASS_TRAINING_FWD, opt: Optional[ConvOptions] = None) -> Plan:
     plan = Plan()
-    _check(lib().plb_conv_plan(C.byref(p), C.byref(opt) if opt else None, pass_, C.byref(plan)))
+    if pass_ == PASS_TRAINING_WU:
+        _check(lib().plb_conv_wu_plan(C.byref(p), C.byref(opt) if opt else None, C.byref(plan)))
+    else:
+        _check(lib().plb_conv_plan(C.byref(p), C.byref(opt) if opt else None, pass_, C.byref(plan)))
     return plan

@@ -158,9 +158,12 @@ uint64_t convBytes(const plb_conv_params &p, const ConvShape &s, int pass) {
 }
 
 // Forward problem of group g.
+// With `swapped_weights` the weights are stored [G][tap][Ci][Co] (the forward
+// layout of the layer this convolution is the backward pass of) and are used
+// with their spatial axes flipped: they are read as a K-by-N (MN-major) operand.
 int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const ConvShape &s,
                    unsigned g, const void *in, const void *w, const float *bias, void *out,
-                   IgemmProblem *q) {
+                   IgemmProblem *q, bool swapped_weights = false) {
   const size_t es = dtypeBytes(p.input_type), os = dtypeBytes(p.output_type);
   const uint64_t ctot = uint64_t(p.groups) * p.in_chans_per_group;
   const uint64_t cotot = uint64_t(p.groups) * p.out_chans_per_group;
@@ -192,10 +195,11 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
     r.act_elem_strides[2] = uint32_t(s.strH);
   }
   r.wgt = static_cast<const uint8_t *>(w) + size_t(g) * s.KH * s.KW * co * ci * es;
-  r.wgt_dims[0] = ci;
-  r.wgt_dims[1] = co;
+  r.b_mn = swapped_weights;
+  r.wgt_dims[0] = swapped_weights ? co : ci;
+  r.wgt_dims[1] = swapped_weights ? ci : co;
   r.wgt_dims[2] = uint64_t(s.KH) * s.KW;
-  r.wgt_strides[0] = ci * es;
+  r.wgt_strides[0] = (swapped_weights ? co : ci) * es;
   r.wgt_strides[1] = co * ci * es;
   r.out_w = s.OW;
   r.out_h = s.OH;
@@ -208,14 +212,15 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.pad_w = s.padW;
   r.dil_h = s.dilH;
   r.dil_w = s.dilW;
-  r.flip_h = s.flipH;
-  r.flip_w = s.flipW;
+  r.flip_h = swapped_weights ? !s.flipH : s.flipH;
+  r.flip_w = swapped_weights ? !s.flipW : s.flipW;
   r.out = static_cast<uint8_t *>(out) + size_t(g) * co * os;
   r.ldc = (long long)cotot;
   r.bias = bias ? bias + size_t(g) * co : nullptr;
   r.out_f32 = p.output_type == PLB_FLOAT;
   r.force_tile_n = opt ? opt->tile_n : 0;
   r.plan_flags = opt ? opt->plan_flags : 0;
+  if (r.fp8 && opt) r.alpha = std::ldexp(1.0f, opt->scale_in + opt->scale_weights);
   *q = r;
   return PLB_OK;
 }
@@ -275,6 +280,7 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.out_f32 = p.output_type == PLB_FLOAT;
   r.force_tile_n = opt ? opt->tile_n : 0;
   r.plan_flags = opt ? opt->plan_flags : 0;
+  if (r.fp8 && opt) r.alpha = std::ldexp(1.0f, opt->scale_in + opt->scale_weights);
   *q = r;
   return PLB_OK;
 }
@@ -449,33 +455,59 @@ int plb_conv_plan(const plb_conv_params *p, const plb_conv_options *opt, int32_t
   return PLB_OK;
 }
 
-int plb_conv_fwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
-                 const void *d_in, const void *d_weights, const float *d_bias, void *d_out) {
+int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                    const void *d_in, const void *d_weights, const float *d_bias, void *d_out,
+                    int transpose_and_flip_weights) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
   ConvShape s;
   if (int rc = igemmConvShape(*p, &s)) return rc;
   if (p->batch == 0 || p->groups == 0 || p->out_chans_per_group == 0 || s.OH == 0 || s.OW == 0)
     return PLB_OK;
-  if (p->in_chans_per_group == 0) {
-    // nothing to accumulate: the output is the bias (or zero)
+  if (p->in_chans_per_group == 0)
     return fail(PLB_ERR_UNSUPPORTED, "zero input channels are not implemented on this path yet");
-  }
-  if (!channelsFitTma(*p, p->in_chans_per_group))
+  if (!channelsFitTma(*p, p->in_chans_per_group)) {
+    if (transpose_and_flip_weights)
+      return fail(PLB_ERR_UNSUPPORTED,
+                  "small-channel convolutions cannot take transposed weights");
     return convFwdSmallChannels(ctx, *p, opt, d_in, d_weights, d_bias, d_out, nullptr);
+  }
   if (s.strH > 1 || s.strW > 1) {
     const bool pointwise = s.KH == 1 && s.KW == 1 && s.padH == 0 && s.padW == 0;
     if (!pointwise && (s.strH > 8 || s.strW > 8))
       return fail(PLB_ERR_UNSUPPORTED, "strides above 8 are not implemented for k > 1");
   }
+  const size_t es = dtypeBytes(p->input_type);
+  const void *w = d_weights;
+  bool swapped = transpose_and_flip_weights != 0;
+  if (swapped && (p->input_type == PLB_QUARTER || !channelsFitTma(*p, p->out_chans_per_group))) {
+    // no MN-major path for 8-bit operands (or for rows TMA cannot address):
+    // transpose + flip the (small) weights into scratch, then run as usual
+    const size_t bytes = size_t(p->groups) * s.KH * s.KW * p->in_chans_per_group *
+                         p->out_chans_per_group * es;
+    void *ws = nullptr;
+    if (int rc = scratch(ctx, 0, bytes, &ws)) return rc;
+    // stored [G][k][Ci][Co] -> [G][flipped k][Co][Ci]
+    if (int rc = plb_weights_transpose_chans_flip_xy(ctx, uint32_t(es), p->groups,
+                                                     p->in_chans_per_group, p->out_chans_per_group,
+                                                     uint64_t(s.KH) * s.KW, d_weights, ws))
+      return rc;
+    w = ws;
+    swapped = false;
+  }
   for (unsigned g = 0; g < p->groups; ++g) {
     IgemmProblem q;
-    if (int rc = convFwdProblem(*p, opt, s, g, d_in, d_weights, d_bias, d_out, &q)) return rc;
+    if (int rc = convFwdProblem(*p, opt, s, g, d_in, w, d_bias, d_out, &q, swapped)) return rc;
     plb_plan plan{};
     if (int rc = planIgemm(q, ctx->sm_count, &plan)) return rc;
     if (int rc = launchIgemm(ctx, q, plan)) return rc;
   }
   return PLB_OK;
+}
+
+int plb_conv_fwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                 const void *d_in, const void *d_weights, const float *d_bias, void *d_out) {
+  return plb_convolution(ctx, p, opt, d_in, d_weights, d_bias, d_out, 0);
 }
 
 int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,

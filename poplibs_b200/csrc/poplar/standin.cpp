@@ -512,9 +512,9 @@ const std::map<std::string, Tensor> &Graph::hostWrites() const { return impl_->h
 const std::map<std::string, Tensor> &Graph::hostReads() const { return impl_->hostReads; }
 
 // Attaches device memory to every variable that has none yet.
-static void materialise(Graph &graph, detail::GraphImpl &g) {
-  plb_context *ctx = graph.context();
-  for (auto &w : g.storages) {
+void Graph::allocateDeviceMemory() {
+  plb_context *ctx = context();
+  for (auto &w : impl_->storages) {
     auto s = w.lock();
     if (!s || s->device) continue;
     const std::size_t bytes = std::max<std::size_t>(s->elements * s->type.bytes(), 16);
@@ -601,13 +601,13 @@ Repeat::Repeat(unsigned count, const Program &body, const DebugContext &) {
 Engine::Engine(Graph &graph, const program::Program &prog, const OptionFlags &)
     : graph_(&graph) {
   programs_.push_back(prog.steps());
-  materialise(graph, *reinterpret_cast<detail::GraphImpl *const &>(*reinterpret_cast<void *const *>(&graph)));
+  graph.allocateDeviceMemory();
 }
 
 Engine::Engine(Graph &graph, const std::vector<program::Sequence> &progs, const OptionFlags &)
     : graph_(&graph) {
   for (const auto &p : progs) programs_.push_back(p.steps());
-  materialise(graph, *reinterpret_cast<detail::GraphImpl *const &>(*reinterpret_cast<void *const *>(&graph)));
+  graph.allocateDeviceMemory();
 }
 
 void Engine::run(unsigned index) {

@@ -250,6 +250,23 @@ __global__ void stridedCopyKernel(const T *__restrict__ src, T *__restrict__ dst
 }
 
 template <typename T>
+__global__ void addBiasKernel(T *acts, const T *__restrict__ biases, size_t total, uint32_t chans);
+template <>
+__global__ void addBiasKernel<__half>(__half *acts, const __half *__restrict__ biases, size_t total,
+                                      uint32_t chans) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x)
+    acts[i] = __float2half_rn(__half2float(acts[i]) + __half2float(biases[i % chans]));
+}
+template <>
+__global__ void addBiasKernel<float>(float *acts, const float *__restrict__ biases, size_t total,
+                                     uint32_t chans) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x)
+    acts[i] += biases[i % chans];
+}
+
+template <typename T>
 __global__ void fillKernel(T *dst, T value, size_t n) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n;
        i += size_t(gridDim.x) * blockDim.x)
@@ -514,6 +531,25 @@ int plb_fill(plb_context *ctx, int32_t dtype, void *d_dst, float value, size_t c
     fillKernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<float *>(d_dst), value, count);
   else
     return fail(PLB_ERR_INVALID_PARAMS, "fill type must be half or float");
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int plb_add_bias(plb_context *ctx, int32_t dtype, void *d_acts, const void *d_biases,
+                 uint64_t pixels, uint32_t chans) {
+  if (int rc = activate(ctx)) return rc;
+  const size_t total = size_t(pixels) * chans;
+  if (total == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(148) * 16));
+  if (dtype == PLB_HALF)
+    addBiasKernel<__half><<<grid, 256, 0, ctx->stream>>>(
+        static_cast<__half *>(d_acts), static_cast<const __half *>(d_biases), total, chans);
+  else if (dtype == PLB_FLOAT)
+    addBiasKernel<float><<<grid, 256, 0, ctx->stream>>>(
+        static_cast<float *>(d_acts), static_cast<const float *>(d_biases), total, chans);
+  else
+    return fail(PLB_ERR_INVALID_PARAMS, "bias add needs half or float activations");
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
