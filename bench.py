@@ -57,6 +57,9 @@ WORKLOADS = {
     "conv1x1_s2_fwd_n256_56x56_c256_c512": dict(kind="conv", pass_="fwd", bound="hbm",
                                                 params=dict(batch=256, field=[56, 56], kernel=[1, 1],
                                                             in_chans=256, out_chans=512, stride=2)),
+    "conv7x7_s2_fwd_n256_224x224_c3_c64": dict(kind="conv", pass_="fwd", bound="hbm",
+                                               params=dict(batch=256, field=[224, 224], kernel=[7, 7],
+                                                           in_chans=3, out_chans=64, padding=3, stride=2)),
     "matmul_fp16_512x1024x1024": dict(kind="gemm", m=512, k=1024, n=1024, quarter=False, bound="tensor"),
     "matmul_fp16_8192": dict(kind="gemm", m=8192, k=8192, n=8192, quarter=False, bound="tensor"),
     "matmul_fp8_8192": dict(kind="gemm", m=8192, k=8192, n=8192, quarter=True, bound="tensor"),
@@ -142,10 +145,11 @@ class Workload:
     """Device-resident rotating buffer sets (so that consecutive steps do not
     find their inputs in L2) and pinned host copies for the end-to-end leg."""
 
-    def __init__(self, name, spec, ctx, device, sets_bytes_target=300 << 20):
+    def __init__(self, name, spec, ctx, device, rank=0, world=1, sets_bytes_target=300 << 20):
         import torch
         from poplibs_b200 import capi
         self.name, self.spec, self.ctx, self.capi = name, spec, ctx, capi
+        self.rank, self.world = rank, world
         g = torch.Generator(device="cpu").manual_seed(1234)
         self.kind = spec["kind"]
         if self.kind == "conv":
@@ -165,6 +169,11 @@ class Workload:
                 "dy": (torch.rand(y_shape, generator=g) * 2 - 1).half().pin_memory(),
             }
             self.pass_ = spec["pass_"]
+            if world > 1:
+                from poplibs_b200 import parallel
+                # weak scaling: every rank holds one full per-GPU batch of the layer
+                glob = dict(kw, batch=kw["batch"] * world)
+                self.sharded = parallel.ShardedConv(ctx, glob, rank, world)
             self.plan = (capi.conv_plan(p, capi.PASS_TRAINING_BWD) if self.pass_ == "bwd"
                          else capi.conv_plan(p)).as_dict()
             self.bytes = self.plan["bytes"]
@@ -215,8 +224,11 @@ class Workload:
             self.ctx.conv_fwd(self.p, d["x"], d["w"], d["out"])
         elif self.pass_ == "bwd":
             self.ctx.conv_bwd(self.p, d["dy"], d["w"], d["out"])
-        else:
+        elif self.world == 1:
             self.ctx.conv_wu(self.p, d["x"], d["dy"], d["out"], d["out32"])
+        else:
+            # per-rank batch reduced locally, then the one collective of the path
+            self.sharded.wu(d["x"], d["dy"], d["out"], d["out32"])
 
     def step_e2e(self, i):
         if self.kind == "gemm":
@@ -359,13 +371,16 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     from poplibs_b200 import capi
 
-    ctx = capi.Context(local_rank)
-    wl = Workload(args.workload, spec, ctx, device)
+    # the library enqueues on a torch stream so that NCCL collectives (weight
+    # update at N > 1) are ordered with the kernels without host synchronisation
+    torch_stream = torch.cuda.Stream(device=device)
+    ctx = capi.Context(local_rank, stream=torch_stream.cuda_stream)
+    wl = Workload(args.workload, spec, ctx, device, rank, world)
     config["plan"] = wl.plan
     if spec["kind"] == "conv":
         config["per_gpu_batch"] = spec["params"]["batch"]
         config["global_batch"] = spec["params"]["batch"] * world
-    stream = torch.cuda.ExternalStream(ctx.stream, device=device)
+    stream = torch_stream
 
     def barrier():
         torch.cuda.synchronize()
@@ -375,8 +390,9 @@ def main():
         torch.cuda.synchronize()
 
     def timed(step_fn, steps, warmup):
-        for i in range(warmup):
-            step_fn(i)
+        with torch.cuda.stream(stream):
+            for i in range(warmup):
+                step_fn(i)
         barrier()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = ctx.launch_count()

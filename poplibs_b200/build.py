@@ -103,3 +103,25 @@ def build_poplin(force: bool = False) -> str:
         subprocess.run([cxx, "-shared", "-o", POPLIN_OUT] + objs +
                        ["-L" + HERE, "-lpoplibs_b200", "-Wl,-rpath,$ORIGIN"], check=True)
     return POPLIN_OUT
+
+
+TOOLS_DIR = os.path.join(HERE, "tools")
+TOOLS_BIN = os.path.join(TOOLS_DIR, "bin")
+
+
+def build_tools(force: bool = False):
+    """The driver tools (ports of the reference's single_conv_layer and
+    general_matrix_multiply) -> poplibs_b200/tools/bin/."""
+    build_poplin()
+    cxx = shutil.which("g++") or "g++"
+    os.makedirs(TOOLS_BIN, exist_ok=True)
+    built = []
+    deps = _headers() + [os.path.join(TOOLS_DIR, "tool_util.hpp"), POPLIN_OUT]
+    for src in sorted(f for f in os.listdir(TOOLS_DIR) if f.endswith(".cpp")):
+        exe = os.path.join(TOOLS_BIN, os.path.splitext(src)[0])
+        path = os.path.join(TOOLS_DIR, src)
+        if force or not _newer(exe, [path] + deps):
+            subprocess.run([cxx] + CXX_FLAGS + ["-I" + TOOLS_DIR, path, "-o", exe, "-L" + HERE,
+                            "-lpoplin_b200", "-lpoplibs_b200", "-Wl,-rpath,$ORIGIN/../.."], check=True)
+        built.append(exe)
+    return built

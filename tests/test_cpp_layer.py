@@ -24,3 +24,127 @@ def test_poplin_host_layer(tmp_path):
     out = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "all host checks passed" in out.stdout
+
+
+def tool(name):
+    from poplibs_b200 import build
+    build.build_tools()
+    return os.path.join(LIBDIR, "tools", "bin", name)
+
+
+def test_tools_build_graphs_without_a_device():
+    out = subprocess.run([tool("single_conv_layer"), "--input-channels=64", "--output-channels=64",
+                          "--field={56,56}", "--kernel-size=3", "--padding=1", "--batch-size=32", "--bias=0",
+                          "--single-phase=all", "--report-plan", "--compile-only"],
+                         capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stderr
+    assert "CTA tile (pixels x chans)  128 x 64" in out.stdout
+    assert "weight update (split-K)" in out.stdout
+    out = subprocess.run([tool("general_matrix_multiply"), "--m", "8192", "--k", "8192", "--n", "8192",
+                          "--report-plan", "--compile-only"], capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stderr
+    assert "128 x 256" in out.stdout
+    # the reference tools' error conventions: unknown options and bad option values fail
+    bad = subprocess.run([tool("general_matrix_multiply"), "--m", "8", "--k", "8", "--n", "8",
+                          "--partials-type", "double", "--compile-only"], capture_output=True, text=True)
+    assert bad.returncode == 1 and "Invalid value 'double' for option 'partialsType'" in bad.stderr
+    bad = subprocess.run([tool("single_conv_layer"), "--input-channels=8", "--output-channels=8",
+                          "--field={4,4}", "--kernel-size=3", "--stride=0", "--compile-only"],
+                         capture_output=True, text=True)
+    assert bad.returncode == 1 and "Stride must be non zero" in bad.stderr
+
+
+def load_dump(directory):
+    import numpy as np
+    tensors = {}
+    with open(os.path.join(directory, "manifest.txt")) as f:
+        for line in f:
+            name, *shape = line.split()
+            tensors[name] = np.fromfile(os.path.join(directory, name + ".f64")).reshape([int(s) for s in shape])
+    return tensors
+
+
+@pytest.mark.gpu
+def test_general_matrix_multiply_tool_against_oracle(tmp_path):
+    import numpy as np
+    import oracle
+    cases = [
+        (["--m", "512", "--k", "1024", "--n", "1024", "--beta", "0"], 1e-3),
+        (["--m", "300", "--k", "200", "--n", "72", "--g", "2", "--alpha", "0.5", "--beta", "1"], 1e-3),
+        (["--m", "64", "--k", "136", "--n", "40", "--left-matrix-op", "transpose", "--beta", "1", "--integer-data",
+          "--output-type", "float"], 0.0),
+        (["--m", "64", "--k", "136", "--n", "40", "--right-matrix-op", "transpose", "--beta", "0", "--integer-data",
+          "--output-type", "float"], 0.0),
+        (["--m", "1", "--k", "1000", "--n", "1", "--beta", "1", "--integer-data", "--output-type", "float"], 0.0),
+        (["--m", "5", "--k", "0", "--n", "4", "--beta", "1", "--integer-data"], 0.0),
+        (["--m", "256", "--k", "512", "--n", "256", "--input-type", "quarter", "--fp8-scale-A=-3", "--fp8-scale-B=-2",
+          "--beta", "0"], 0.0),
+    ]
+    for i, (flags, tol) in enumerate(cases):
+        d = tmp_path / f"gemm{i}"
+        d.mkdir()
+        out = subprocess.run([tool("general_matrix_multiply"), "--dump-dir", str(d)] + flags,
+                             capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, f"{flags}: {out.stderr}"
+        t = load_dump(str(d))
+        alpha = float(flags[flags.index("--alpha") + 1]) if "--alpha" in flags else 1.0
+        beta = float(flags[flags.index("--beta") + 1]) if "--beta" in flags else 1.0
+        ta = "--left-matrix-op" in flags
+        tb = "--right-matrix-op" in flags
+        expect = oracle.gemm(t["A"], t["B"], t["C"], alpha, beta, ta, tb)
+        if tol == 0.0:
+            assert (t["D"] == expect).all(), flags
+        else:
+            rms = float(np.sqrt(np.mean(expect * expect)))
+            bad, first, worst = oracle.check_is_close(t["D"], expect, tol, max(1e-5, 2.5e-4 * rms))
+            assert bad == 0, (flags, bad, worst)
+
+
+@pytest.mark.gpu
+def test_single_conv_layer_tool_against_oracle(tmp_path):
+    import numpy as np
+    import oracle
+    from oracle import ConvSpec
+    cases = [
+        dict(flags=["--input-channels=64", "--output-channels=64", "--field={14,14}", "--kernel-size=3",
+                    "--padding=1", "--batch-size=4", "--integer-data", "--learning-rate=0.5"],
+             spec=ConvSpec.simple(4, [14, 14], [3, 3], 64, 64, padding=1), bias=True),
+        dict(flags=["--input-channels=72", "--output-channels=40", "--field={7,9}", "--kernel-size={3,2}",
+                    "--padding-lower={2,0}", "--padding-upper={0,1}", "--batch-size=3", "--bias=0",
+                    "--integer-data", "--learning-rate=0.25"],
+             spec=ConvSpec(3, [7, 9], [3, 2], 72, 40, in_pad_lo=[2, 0], in_pad_hi=[0, 1]), bias=False),
+        dict(flags=["--input-channels=64", "--output-channels=64", "--field={9,9}", "--kernel-size=3",
+                    "--padding=1", "--stride=2", "--batch-size=2", "--bias=0", "--integer-data",
+                    "--single-phase=fwd"],
+             spec=ConvSpec.simple(2, [9, 9], [3, 3], 64, 64, padding=1, stride=2), bias=False),
+        dict(flags=["--input-channels=32", "--output-channels=32", "--field={6,6}", "--kernel-size=3",
+                    "--padding=1", "--conv-groups=2", "--batch-size=2", "--bias=0", "--integer-data",
+                    "--learning-rate=0.5"],
+             spec=ConvSpec.simple(2, [6, 6], [3, 3], 32, 32, padding=1, groups=2), bias=False),
+        dict(flags=["--input-channels=128", "--output-channels=64", "--field={8,8}", "--kernel-size=3",
+                    "--padding=1", "--batch-size=2", "--bias=0", "--input-type=quarter",
+                    "--fp8-scale-fwd=1", "--fp8-scale-weights=0", "--fp8-scale-bwd=1"],
+             spec=ConvSpec.simple(2, [8, 8], [3, 3], 128, 64, padding=1), bias=False),
+    ]
+    for i, case in enumerate(cases):
+        d = tmp_path / f"conv{i}"
+        d.mkdir()
+        out = subprocess.run([tool("single_conv_layer"), "--dump-dir", str(d)] + case["flags"],
+                             capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, f"{case['flags']}: {out.stderr}"
+        t = load_dump(str(d))
+        spec = case["spec"]
+        flat = lambda a, lead: a.reshape(a.shape[0], a.shape[1], -1) if lead == 2 else a.reshape(*a.shape[:3], -1)  # noqa: E731
+        x, w0 = flat(t["prevAct"], 2), flat(t["weights"], 3)
+        if "nextAct" in t:
+            y = oracle.conv_fwd(spec, x, w0, t.get("biases") if case["bias"] else None)
+            assert (flat(t["nextAct"], 2) == y).all(), case["flags"]
+        if "prevDeltas" in t:
+            dx = oracle.conv_bwd(spec, flat(t["zDeltas"], 2), w0)
+            assert (flat(t["prevDeltas"], 2) == dx).all(), case["flags"]
+        if "weightDeltas" in t:
+            dw, _ = oracle.conv_wu(spec, x, flat(t["zDeltas"], 2))
+            assert (flat(t["weightDeltas"], 3) == dw).all(), case["flags"]
+            lr = float([f for f in case["flags"] if f.startswith("--learning-rate")][0].split("=")[1])  # exact in half
+            expect = (w0 - lr * dw).astype(np.float16).astype(np.float64)
+            assert (flat(t["weightsUpdated"], 3) == expect).all(), case["flags"]
