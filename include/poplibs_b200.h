@@ -222,6 +222,27 @@ PLB_API int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_c
 PLB_API int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
                 const void *d_acts, const void *d_out_grads, void *d_weight_grads,
                 float *d_weight_grads_f32);
+/* The same weight gradient for callers that cannot allocate device memory when
+ * they need it (code running under an allocator that owns all device memory or
+ * inside its hooks, loops that may not take the allocator's lock, processes with
+ * a memory budget fixed at start-up).  This entry point has no counterpart in the
+ * reference.  It calls no cudaMalloc / cudaFree: the split-K partial sums live in
+ * a 32 MiB array that is part of the library's device image (every GPU that loads
+ * the library holds it until the process exits), the caller passes the device
+ * ordinal, the CUDA stream (cudaStream_t as void*) and all input / output
+ * buffers.  Limits and rules:
+ *  - one group's fp32 gradient (kernel elements * Co * Ci * 4 bytes) must fit in
+ *    32 MiB, else PLB_ERR_UNSUPPORTED; fewer K splits are used than plb_conv_wu
+ *    would choose when only fewer fit;
+ *  - the first call on a device looks up the array's device address (and sets a
+ *    kernel attribute): make that first call before any stream capture;
+ *  - all calls share the one array: calls that overlap on the GPU (different
+ *    streams or threads) race.  The call synchronises the stream before it
+ *    returns and reports a kernel failure as PLB_ERR_KERNEL. */
+PLB_API int plb_conv_wu_static_scratch(int device, void *cuda_stream, const plb_conv_params *p,
+                               const plb_conv_options *opt, const void *d_acts,
+                               const void *d_out_grads, void *d_weight_grads,
+                               float *d_weight_grads_f32);
 /* weights += scale * weight_grads_f32, cast to the weights' type
  * (popops::scaledAddTo in convolutionWeightUpdate, lib/poplin/Convolution.cpp:3509-3522). */
 PLB_API int plb_scaled_add_to(plb_context *ctx, int32_t dtype, void *d_weights,

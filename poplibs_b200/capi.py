@@ -131,7 +131,8 @@ SYMBOLS = (
     "plb_context_destroy", "plb_context_stream", "plb_synchronize", "plb_launch_count",
     "plb_malloc", "plb_free", "plb_memcpy_h2d", "plb_memcpy_d2h", "plb_memset",
     "plb_matmul", "plb_matmul_host", "plb_conv_validate", "plb_conv_output_field",
-    "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution", "plb_conv_bwd", "plb_conv_wu",
+    "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution",
+    "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
     "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_fwd_host",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
     "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
@@ -179,6 +180,7 @@ def lib():
     L.plb_convolution.argtypes = [vp, CP, OP, vp, vp, vp, vp, C.c_int]
     L.plb_conv_bwd.argtypes = [vp, CP, OP, vp, vp, vp]
     L.plb_conv_wu.argtypes = [vp, CP, OP, vp, vp, vp, vp]
+    L.plb_conv_wu_static_scratch.argtypes = [C.c_int, vp, CP, OP, vp, vp, vp, vp]
     L.plb_scaled_add_to.argtypes = [vp, i32, vp, vp, f32, sz]
     L.plb_cast_from_f32.argtypes = [vp, i32, vp, vp, sz]
     L.plb_add_bias.argtypes = [vp, i32, vp, vp, u64, u32]
@@ -320,6 +322,15 @@ class Context:
 
     def transpose_matrix(self, elem_bytes, groups, rows, cols, src, dst):
         _check(lib().plb_transpose_matrix(self._h, elem_bytes, groups, rows, cols, _ptr(src), _ptr(dst)))
+
+
+def conv_wu_static_scratch(device: int, stream: int, p: ConvParams, x, dy, dw, dw_f32=None,
+                           opt: Optional[ConvOptions] = None):
+    """plb_conv_wu_static_scratch: the weight gradient without any device
+    allocation by the library (no Context is involved)."""
+    _check(lib().plb_conv_wu_static_scratch(device, C.c_void_p(stream), C.byref(p),
+                                            C.byref(opt) if opt else None, _ptr(x), _ptr(dy),
+                                            _ptr(dw), _ptr(dw_f32)))
 
 
 def matmul_plan(desc: MatmulDesc) -> Plan:

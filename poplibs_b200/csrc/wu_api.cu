@@ -1,5 +1,7 @@
 // Weight-update pass: planning and launch of the weight-gradient kernel.
 #include <algorithm>
+#include <mutex>
+#include <string>
 
 #include "conv_geometry.h"
 #include "runtime.h"
@@ -213,3 +215,142 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Weight update for callers that must not allocate device memory
+// ---------------------------------------------------------------------------
+// Some callers of this library cannot call cudaMalloc when they need a weight
+// gradient: code running inside a framework's allocator hooks or under a
+// caching allocator that owns all device memory, real-time loops that may not
+// take the allocator's global lock, and processes whose memory budget was fixed
+// at start-up.  plb_conv_wu grows a scratch buffer with cudaMalloc on demand;
+// this entry point instead keeps the split-K partial sums in a fixed array that
+// is part of the library's device image.  Every GPU that loads the library
+// holds these bytes until the process exits, so the size is kept modest.
+
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(32) << 20;  // 32 MiB
+static __device__ __align__(256) unsigned char g_wu_static_scratch[kStaticScratchBytes];
+static __device__ int g_wu_static_status;
+
+// Device addresses of the two symbols, looked up once per device.  In host code
+// the arrays' names are only host-side handles for the symbols, not device
+// addresses: kernels must be given what cudaGetSymbolAddress returns.
+struct StaticScratch {
+  bool ready = false;
+  float *partial = nullptr;
+  int *status = nullptr;
+};
+StaticScratch g_static_scratch[64];
+std::mutex g_static_scratch_mutex;
+
+int staticScratchFor(int device, StaticScratch *out) {
+  if (device < 0 || device >= 64) return fail(PLB_ERR_INVALID_PARAMS, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  StaticScratch &s = g_static_scratch[device];
+  if (!s.ready) {
+    // the caller has made `device` current
+    void *scratch_ptr = nullptr, *status_ptr = nullptr;
+    PLB_CUDA(cudaGetSymbolAddress(&scratch_ptr, g_wu_static_scratch));
+    PLB_CUDA(cudaGetSymbolAddress(&status_ptr, g_wu_static_status));
+    PLB_CUDA(cudaFuncSetAttribute(wu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    s.partial = static_cast<float *>(scratch_ptr);
+    s.status = static_cast<int *>(status_ptr);
+    s.ready = true;
+  }
+  *out = s;
+  return PLB_OK;
+}
+
+}  // namespace
+
+extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const plb_conv_params *p,
+                                          const plb_conv_options *opt, const void *d_acts,
+                                          const void *d_out_grads, void *d_weight_grads,
+                                          float *d_weight_grads_f32) {
+  if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  PLB_CUDA(cudaSetDevice(device));
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  WuShape s;
+  if (int rc = wuShape(*p, &s)) return rc;
+  const int co = int(p->out_chans_per_group), ci = int(p->in_chans_per_group);
+  const int taps = s.KH * s.KW;
+  const size_t w_elems = size_t(taps) * co * ci;
+  if (p->groups == 0 || w_elems == 0) return PLB_OK;
+  if (w_elems * sizeof(float) > kStaticScratchBytes)
+    return fail(PLB_ERR_UNSUPPORTED,
+                "weight gradient of " + std::to_string(w_elems * sizeof(float)) +
+                    " bytes per group exceeds the " + std::to_string(kStaticScratchBytes) +
+                    "-byte static scratch of plb_conv_wu_static_scratch; use plb_conv_wu");
+  StaticScratch scratch;
+  if (int rc = staticScratchFor(device, &scratch)) return rc;
+  const size_t es = 2;
+  if (p->batch == 0 || s.OH == 0 || s.OW == 0) {
+    const size_t n = size_t(p->groups) * w_elems;
+    if (d_weight_grads) PLB_CUDA(cudaMemsetAsync(d_weight_grads, 0, n * es, stream));
+    if (d_weight_grads_f32) PLB_CUDA(cudaMemsetAsync(d_weight_grads_f32, 0, n * sizeof(float), stream));
+    PLB_CUDA(cudaStreamSynchronize(stream));
+    return PLB_OK;
+  }
+  cudaDeviceProp prop;
+  PLB_CUDA(cudaGetDeviceProperties(&prop, device));
+  WuArgs a{};
+  planWu(*p, s, prop.multiProcessorCount, opt ? opt->split_k : 0, &a, nullptr);
+  // as many K splits as the fixed scratch can hold
+  const int max_split = int(kStaticScratchBytes / (w_elems * sizeof(float)));
+  a.ksplit = std::max(1, std::min(a.ksplit, max_split));
+  a.partial = scratch.partial;
+  a.status = scratch.status;
+  // the array keeps whatever the previous call left: the status word must start
+  // at zero; the partial sums need no clearing, every CTA overwrites its slice
+  PLB_CUDA(cudaMemsetAsync(scratch.status, 0, sizeof(int), stream));
+
+  const uint64_t ctot = uint64_t(p->groups) * ci, cotot = uint64_t(p->groups) * co;
+  const int stage_bytes = (2 + a.taps_per_group * a.ci_blk64) * kWuBlockBytes;
+  const int smem = a.stages * stage_bytes + 256 + 1024;
+  for (unsigned g = 0; g < p->groups; ++g) {
+    CUtensorMap tdy, tx;
+    {
+      const uint64_t dims[4] = {uint64_t(co), uint64_t(s.OW), uint64_t(s.OH), p->batch};
+      const uint64_t strides[3] = {cotot * es, uint64_t(s.OW) * cotot * es,
+                                   uint64_t(s.OH) * s.OW * cotot * es};
+      const uint32_t box[4] = {64, uint32_t(a.box_w), uint32_t(a.box_h), uint32_t(a.box_n)};
+      const uint32_t estr[4] = {1, 1, 1, 1};
+      if (int rc = encodeTensorMap(&tdy, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                                   static_cast<const uint8_t *>(d_out_grads) + size_t(g) * co * es,
+                                   dims, strides, box, estr))
+        return rc;
+    }
+    {
+      const uint64_t dims[4] = {uint64_t(ci), uint64_t(s.W), uint64_t(s.H), p->batch};
+      const uint64_t strides[3] = {ctot * es, uint64_t(s.W) * ctot * es,
+                                   uint64_t(s.H) * s.W * ctot * es};
+      const uint32_t box[4] = {64, uint32_t((a.box_w - 1) * s.strW + 1),
+                               uint32_t((a.box_h - 1) * s.strH + 1), uint32_t(a.box_n)};
+      const uint32_t estr[4] = {1, uint32_t(s.strW), uint32_t(s.strH), 1};
+      if (int rc = encodeTensorMap(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                                   static_cast<const uint8_t *>(d_acts) + size_t(g) * ci * es,
+                                   dims, strides, box, estr))
+        return rc;
+    }
+    const int grid = a.co_blocks * a.ci_blocks * a.tap_groups * a.ksplit;
+    wu_kernel<<<grid, kWuThreads, smem, stream>>>(tdy, tx, a);
+    PLB_CUDA(cudaGetLastError());
+    const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
+    wu_reduce_kernel<<<rgrid, 256, 0, stream>>>(
+        a.partial, a.ksplit, w_elems,
+        d_weight_grads_f32 ? d_weight_grads_f32 + size_t(g) * w_elems : nullptr,
+        d_weight_grads ? static_cast<uint8_t *>(d_weight_grads) + size_t(g) * w_elems * es : nullptr,
+        0);
+    PLB_CUDA(cudaGetLastError());
+  }
+  // report a kernel that gave up on a bounded wait; this also makes the call
+  // complete before it returns, so a second call cannot overlap the first
+  PLB_CUDA(cudaStreamSynchronize(stream));
+  int status = 0;
+  PLB_CUDA(cudaMemcpy(&status, scratch.status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (status != 0)
+    return fail(PLB_ERR_KERNEL, "weight update kernel reported status " + std::to_string(status));
+  return PLB_OK;
+}
