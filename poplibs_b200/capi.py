@@ -339,6 +339,11 @@ def matmul_plan(desc: MatmulDesc) -> Plan:
     return plan
 
 
+def conv_wu_plan(p: ConvParams, opt: Optional[ConvOptions] = None) -> Plan:
+    """plb_conv_wu_plan: tiling of the weight-update pass."""
+    return conv_plan(p, PASS_TRAINING_WU, opt)
+
+
 def conv_plan(p: ConvParams, pass_: int = PASS_TRAINING_FWD, opt: Optional[ConvOptions] = None) -> Plan:
     plan = Plan()
     if pass_ == PASS_TRAINING_WU:

@@ -51,7 +51,7 @@ int wuShape(const plb_conv_params &p, WuShape *s) {
 
 // Tiling of one group's weight update.
 void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_split,
-            WuArgs *a, plb_plan *plan) {
+            unsigned plan_flags, WuArgs *a, plb_plan *plan) {
   const int co = int(p.out_chans_per_group), ci = int(p.in_chans_per_group);
   const int taps = s.KH * s.KW;
   a->taps_h = s.KH;
@@ -90,10 +90,50 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
         a->box_n = n;
       }
     }
+  int stage_bytes = (2 + a->taps_per_group * a->ci_blk64) * kWuBlockBytes;
+  // Strip mode: one tap group per filter column, the activations of a K step
+  // loaded once for all filter rows.  Needs a unit vertical stride, all filter
+  // rows' accumulators in TMEM at once and box_w * box_n a multiple of 8; taken
+  // when it costs at most 1/8 more pixel tiles than the best box.
+  a->strip_mode = 0;
+  const int halo = (s.KH - 1) * s.dilH;
+  if (s.KH > 1 && s.strH == 1 && s.KH * a->ci_blk <= 512 && (plan_flags & PLB_PLAN_NO_HALO) == 0) {
+    long sbest = -1;
+    int sw = 0, sh = 0, sn = 0;
+    for (int h = 64; h >= 1; h >>= 1)  // tallest first: least halo per row
+      for (int w = 64 / h; w >= 1; w >>= 1) {
+        const int n = 64 / (w * h);
+        if ((w * n) % 8 != 0 || h + halo > 256 || (w - 1) * s.strW + 1 > 256) continue;
+        const long tiles =
+            long((s.OW + w - 1) / w) * ((s.OH + h - 1) / h) * ((long(p.batch) + n - 1) / n);
+        if (sbest < 0 || tiles < sbest) {
+          sbest = tiles;
+          sw = w;
+          sh = h;
+          sn = n;
+        }
+      }
+    const int strip_rows = sw * sn * (sh + halo);
+    const int sbytes = 2 * kWuBlockBytes + a->ci_blk64 * strip_rows * 128;
+    if (sbest > 0 && sbest * 8 <= best * 9 && 2 * sbytes <= 200 * 1024) {
+      a->strip_mode = 1;
+      a->box_w = sw;
+      a->box_h = sh;
+      a->box_n = sn;
+      a->strip_rows = strip_rows;
+      a->halo_step_bytes = s.dilH * sw * sn * 128;
+      a->taps_per_group = s.KH;
+      a->tap_groups = s.KW;
+      a->tmem_cols = 32;
+      while (a->tmem_cols < s.KH * a->ci_blk) a->tmem_cols <<= 1;
+      stage_bytes = sbytes;
+      best = sbest;
+    }
+  }
   a->tiles_w = (s.OW + a->box_w - 1) / a->box_w;
   a->tiles_h = (s.OH + a->box_h - 1) / a->box_h;
   a->tiles_n = (int(p.batch) + a->box_n - 1) / a->box_n;
-  const int stage_bytes = (2 + a->taps_per_group * a->ci_blk64) * kWuBlockBytes;
+  a->stage_bytes = stage_bytes;
   a->stages = std::max(2, std::min(kWuMaxStages, (200 * 1024) / stage_bytes));
   const int units = a->co_blocks * a->ci_blocks * a->tap_groups;
   int ksplit = force_split > 0 ? force_split : std::max(1, (sm_count > 0 ? sm_count : 148) / units);
@@ -112,8 +152,86 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
     plan->tiles = units;
     plan->grid = units * ksplit;
     plan->b_mn_major = 1;
+    plan->halo_rows = a->strip_mode ? halo : 0;
     plan->workspace_bytes = size_t(ksplit) * taps * co * ci * sizeof(float);
   }
+}
+
+// Launches the weight-gradient kernel and the reduction over K splits for every
+// group.  `a.partial` and `a.status` are set by the caller.
+int launchWu(cudaStream_t stream, const plb_conv_params &p, const WuShape &s, const WuArgs &a,
+             const void *d_acts, const void *d_out_grads, void *d_weight_grads,
+             float *d_weight_grads_f32, uint64_t *launches) {
+  const int co = int(p.out_chans_per_group), ci = int(p.in_chans_per_group);
+  const int taps = s.KH * s.KW;
+  const size_t w_elems = size_t(taps) * co * ci;
+  const size_t es = 2;
+  const uint64_t ctot = uint64_t(p.groups) * ci, cotot = uint64_t(p.groups) * co;
+  const int smem = a.stages * a.stage_bytes + 256 + 1024;
+  const uint32_t ones[4] = {1, 1, 1, 1};
+  CUtensorMap tout;
+  {
+    // partial sums [ksplit][taps][co][ci] fp32, stored in blocks of 32 x 32
+    const uint64_t dims[4] = {uint64_t(ci), uint64_t(co), uint64_t(taps), uint64_t(a.ksplit)};
+    const uint64_t strides[3] = {uint64_t(ci) * 4, uint64_t(co) * ci * 4, uint64_t(w_elems) * 4};
+    const uint32_t box[4] = {32, 32, 1, 1};
+    if (int rc = encodeTensorMap(&tout, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.partial, dims,
+                                 strides, box, ones))
+      return rc;
+  }
+  for (unsigned g = 0; g < p.groups; ++g) {
+    CUtensorMap tdy, tx;
+    // pixel dimensions (w, h, n); strip mode orders them (w, n, h)
+    const bool strip = a.strip_mode != 0;
+    const int halo = strip ? (s.KH - 1) * s.dilH : 0;
+    {
+      const uint64_t sh = uint64_t(s.OW) * cotot * es, sn = uint64_t(s.OH) * s.OW * cotot * es;
+      const uint64_t dims[4] = {uint64_t(co), uint64_t(s.OW), strip ? p.batch : uint64_t(s.OH),
+                                strip ? uint64_t(s.OH) : p.batch};
+      const uint64_t strides[3] = {cotot * es, strip ? sn : sh, strip ? sh : sn};
+      const uint32_t box[4] = {64, uint32_t(a.box_w), uint32_t(strip ? a.box_n : a.box_h),
+                               uint32_t(strip ? a.box_h : a.box_n)};
+      if (int rc = encodeTensorMap(&tdy, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                                   static_cast<const uint8_t *>(d_out_grads) + size_t(g) * co * es,
+                                   dims, strides, box, ones))
+        return rc;
+    }
+    {
+      const uint64_t sh = uint64_t(s.W) * ctot * es, sn = uint64_t(s.H) * s.W * ctot * es;
+      const uint64_t dims[4] = {uint64_t(ci), uint64_t(s.W), strip ? p.batch : uint64_t(s.H),
+                                strip ? uint64_t(s.H) : p.batch};
+      const uint64_t strides[3] = {ctot * es, strip ? sn : sh, strip ? sh : sn};
+      const uint32_t bw = uint32_t((a.box_w - 1) * s.strW + 1);
+      const uint32_t bh = strip ? uint32_t(a.box_h + halo) : uint32_t((a.box_h - 1) * s.strH + 1);
+      const uint32_t box[4] = {64, bw, strip ? uint32_t(a.box_n) : bh, strip ? bh : uint32_t(a.box_n)};
+      const uint32_t estr[4] = {1, uint32_t(s.strW), strip ? 1u : uint32_t(s.strH), 1};
+      if (int rc = encodeTensorMap(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                                   static_cast<const uint8_t *>(d_acts) + size_t(g) * ci * es,
+                                   dims, strides, box, estr))
+        return rc;
+    }
+    const int grid = a.co_blocks * a.ci_blocks * a.tap_groups * a.ksplit;
+    wu_kernel<<<grid, kWuThreads, smem, stream>>>(tdy, tx, tout, a);
+    PLB_CUDA(cudaGetLastError());
+    float *out32 = d_weight_grads_f32 ? d_weight_grads_f32 + size_t(g) * w_elems : nullptr;
+    uint8_t *out16 =
+        d_weight_grads ? static_cast<uint8_t *>(d_weight_grads) + size_t(g) * w_elems * es : nullptr;
+    if (w_elems % 4 == 0 && (reinterpret_cast<uintptr_t>(out32) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out16) & 7) == 0) {
+      const size_t count4 = w_elems / 4;
+      const int rgrid = int(std::min<size_t>((count4 + 127) / 128, size_t(148) * 16));
+      wu_reduce4_kernel<<<rgrid, 128, 0, stream>>>(reinterpret_cast<const float4 *>(a.partial),
+                                                   a.ksplit, count4,
+                                                   reinterpret_cast<float4 *>(out32),
+                                                   reinterpret_cast<uint2 *>(out16));
+    } else {
+      const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
+      wu_reduce_kernel<<<rgrid, 256, 0, stream>>>(a.partial, a.ksplit, w_elems, out32, out16, 0);
+    }
+    PLB_CUDA(cudaGetLastError());
+    if (launches) *launches += 2;
+  }
+  return PLB_OK;
 }
 
 }  // namespace
@@ -129,7 +247,7 @@ int plb_conv_wu_plan(const plb_conv_params *p, const plb_conv_options *opt, plb_
   if (int rc = wuShape(*p, &s)) return rc;
   *plan = plb_plan{};
   WuArgs a{};
-  planWu(*p, s, 148, opt ? opt->split_k : 0, &a, plan);
+  planWu(*p, s, 148, opt ? opt->split_k : 0, opt ? opt->plan_flags : 0, &a, plan);
   plan->flops = 2 * numberOfMacs(*p);
   const uint64_t es = dtypeBytes(p->input_type);
   plan->bytes = es * (uint64_t(p->batch) * s.H * s.W * p->groups * p->in_chans_per_group +
@@ -158,59 +276,23 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
     return PLB_OK;
   }
   WuArgs a{};
-  planWu(*p, s, ctx->sm_count, opt ? opt->split_k : 0, &a, nullptr);
+  planWu(*p, s, ctx->sm_count, opt ? opt->split_k : 0, opt ? opt->plan_flags : 0, &a, nullptr);
   a.status = ctx->d_status;
+  a.trace = ctx->trace;
   void *ws = nullptr;
   if (int rc = scratch(ctx, 0, size_t(a.ksplit) * w_elems * sizeof(float), &ws)) return rc;
   a.partial = static_cast<float *>(ws);
 
-  const size_t es = 2;
-  const uint64_t ctot = uint64_t(p->groups) * ci, cotot = uint64_t(p->groups) * co;
-  const int stage_bytes = (2 + a.taps_per_group * a.ci_blk64) * kWuBlockBytes;
-  const int smem = a.stages * stage_bytes + 256 + 1024;
   static bool configured[64] = {};
   if (!configured[ctx->device & 63]) {
     PLB_CUDA(cudaFuncSetAttribute(wu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     configured[ctx->device & 63] = true;
   }
-  for (unsigned g = 0; g < p->groups; ++g) {
-    CUtensorMap tdy, tx;
-    {
-      const uint64_t dims[4] = {uint64_t(co), uint64_t(s.OW), uint64_t(s.OH), p->batch};
-      const uint64_t strides[3] = {cotot * es, uint64_t(s.OW) * cotot * es,
-                                   uint64_t(s.OH) * s.OW * cotot * es};
-      const uint32_t box[4] = {64, uint32_t(a.box_w), uint32_t(a.box_h), uint32_t(a.box_n)};
-      const uint32_t estr[4] = {1, 1, 1, 1};
-      if (int rc = encodeTensorMap(&tdy, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                                   static_cast<const uint8_t *>(d_out_grads) + size_t(g) * co * es,
-                                   dims, strides, box, estr))
-        return rc;
-    }
-    {
-      const uint64_t dims[4] = {uint64_t(ci), uint64_t(s.W), uint64_t(s.H), p->batch};
-      const uint64_t strides[3] = {ctot * es, uint64_t(s.W) * ctot * es,
-                                   uint64_t(s.H) * s.W * ctot * es};
-      const uint32_t box[4] = {64, uint32_t((a.box_w - 1) * s.strW + 1),
-                               uint32_t((a.box_h - 1) * s.strH + 1), uint32_t(a.box_n)};
-      const uint32_t estr[4] = {1, uint32_t(s.strW), uint32_t(s.strH), 1};
-      if (int rc = encodeTensorMap(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                                   static_cast<const uint8_t *>(d_acts) + size_t(g) * ci * es,
-                                   dims, strides, box, estr))
-        return rc;
-    }
-    const int grid = a.co_blocks * a.ci_blocks * a.tap_groups * a.ksplit;
-    wu_kernel<<<grid, kWuThreads, smem, ctx->stream>>>(tdy, tx, a);
-    PLB_CUDA(cudaGetLastError());
-    ctx->launches++;
-    const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
-    wu_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>(
-        a.partial, a.ksplit, w_elems,
-        d_weight_grads_f32 ? d_weight_grads_f32 + size_t(g) * w_elems : nullptr,
-        d_weight_grads ? static_cast<uint8_t *>(d_weight_grads) + size_t(g) * w_elems * es : nullptr,
-        0);
-    PLB_CUDA(cudaGetLastError());
-    ctx->launches++;
-  }
+  uint64_t launches = 0;
+  if (int rc = launchWu(ctx->stream, *p, s, a, d_acts, d_out_grads, d_weight_grads,
+                        d_weight_grads_f32, &launches))
+    return rc;
+  ctx->launches += launches;
   return PLB_OK;
 }
 
@@ -296,7 +378,8 @@ extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const p
   cudaDeviceProp prop;
   PLB_CUDA(cudaGetDeviceProperties(&prop, device));
   WuArgs a{};
-  planWu(*p, s, prop.multiProcessorCount, opt ? opt->split_k : 0, &a, nullptr);
+  planWu(*p, s, prop.multiProcessorCount, opt ? opt->split_k : 0, opt ? opt->plan_flags : 0, &a,
+         nullptr);
   // as many K splits as the fixed scratch can hold
   const int max_split = int(kStaticScratchBytes / (w_elems * sizeof(float)));
   a.ksplit = std::max(1, std::min(a.ksplit, max_split));
@@ -306,45 +389,9 @@ extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const p
   // at zero; the partial sums need no clearing, every CTA overwrites its slice
   PLB_CUDA(cudaMemsetAsync(scratch.status, 0, sizeof(int), stream));
 
-  const uint64_t ctot = uint64_t(p->groups) * ci, cotot = uint64_t(p->groups) * co;
-  const int stage_bytes = (2 + a.taps_per_group * a.ci_blk64) * kWuBlockBytes;
-  const int smem = a.stages * stage_bytes + 256 + 1024;
-  for (unsigned g = 0; g < p->groups; ++g) {
-    CUtensorMap tdy, tx;
-    {
-      const uint64_t dims[4] = {uint64_t(co), uint64_t(s.OW), uint64_t(s.OH), p->batch};
-      const uint64_t strides[3] = {cotot * es, uint64_t(s.OW) * cotot * es,
-                                   uint64_t(s.OH) * s.OW * cotot * es};
-      const uint32_t box[4] = {64, uint32_t(a.box_w), uint32_t(a.box_h), uint32_t(a.box_n)};
-      const uint32_t estr[4] = {1, 1, 1, 1};
-      if (int rc = encodeTensorMap(&tdy, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                                   static_cast<const uint8_t *>(d_out_grads) + size_t(g) * co * es,
-                                   dims, strides, box, estr))
-        return rc;
-    }
-    {
-      const uint64_t dims[4] = {uint64_t(ci), uint64_t(s.W), uint64_t(s.H), p->batch};
-      const uint64_t strides[3] = {ctot * es, uint64_t(s.W) * ctot * es,
-                                   uint64_t(s.H) * s.W * ctot * es};
-      const uint32_t box[4] = {64, uint32_t((a.box_w - 1) * s.strW + 1),
-                               uint32_t((a.box_h - 1) * s.strH + 1), uint32_t(a.box_n)};
-      const uint32_t estr[4] = {1, uint32_t(s.strW), uint32_t(s.strH), 1};
-      if (int rc = encodeTensorMap(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                                   static_cast<const uint8_t *>(d_acts) + size_t(g) * ci * es,
-                                   dims, strides, box, estr))
-        return rc;
-    }
-    const int grid = a.co_blocks * a.ci_blocks * a.tap_groups * a.ksplit;
-    wu_kernel<<<grid, kWuThreads, smem, stream>>>(tdy, tx, a);
-    PLB_CUDA(cudaGetLastError());
-    const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
-    wu_reduce_kernel<<<rgrid, 256, 0, stream>>>(
-        a.partial, a.ksplit, w_elems,
-        d_weight_grads_f32 ? d_weight_grads_f32 + size_t(g) * w_elems : nullptr,
-        d_weight_grads ? static_cast<uint8_t *>(d_weight_grads) + size_t(g) * w_elems * es : nullptr,
-        0);
-    PLB_CUDA(cudaGetLastError());
-  }
+  if (int rc = launchWu(stream, *p, s, a, d_acts, d_out_grads, d_weight_grads, d_weight_grads_f32,
+                        nullptr))
+    return rc;
   // report a kernel that gave up on a bounded wait; this also makes the call
   // complete before it returns, so a second call cannot overlap the first
   PLB_CUDA(cudaStreamSynchronize(stream));

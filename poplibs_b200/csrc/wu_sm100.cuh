@@ -12,16 +12,30 @@
 //
 // Work split: the grid is (Co blocks of 128) x (Ci blocks) x (groups of filter
 // taps whose accumulators fit the 512 TMEM columns) x (K splits over pixel
-// tiles).  Every CTA leaves its partial sums in a global fp32 scratch buffer;
+// tiles).  With a unit vertical stride a group is one filter column: the
+// activations of a K step are loaded once, as a strip of box_h + halo input
+// rows, and serve all taps_h vertical taps.  The pixels of a tile are then
+// ordered (w, n, h), h slowest, and box_w * box_n is a multiple of 8, so that
+// moving down one filter row moves the operand's start by whole 1024-byte
+// swizzle atoms.  Every CTA leaves its partial sums in a global fp32 scratch buffer;
 // a second kernel adds the K splits in a fixed order (the role of the
 // reference's ReduceAdd codelet, lib/poplin/codelets/ReduceAdd.cpp) and casts.
+//
+// Roles inside a CTA: warps 0..2 issue the tensor copies of every K step
+// between them (a copy costs its issuing thread on the order of a hundred
+// cycles, a K step needs 2 + taps * ci_blk64 copies), warp 3 issues the MMAs
+// (neighbouring taps share one instruction when their accumulators and
+// operand blocks are contiguous, which halves the reads of the outGrad tile),
+// warps 4..7 move the accumulators TMEM -> registers -> swizzled shared memory
+// -> global with tensor stores.
 #pragma once
 
 #include "sm100_prims.cuh"
 
 namespace plb {
 
-constexpr int kWuThreads = 192;
+constexpr int kWuThreads = 256;
+constexpr int kWuProducers = 3;  // warps 0..2 issue TMA, warp 3 issues MMA, warps 4..7 drain
 constexpr int kWuPixelsPerStage = 64;   // K per pipeline stage
 constexpr int kWuBlockBytes = kWuPixelsPerStage * 128;  // one 64-channel block of one stage
 constexpr int kWuMaxStages = 8;
@@ -38,18 +52,38 @@ struct WuArgs {
   int co_total, ci_total;
   int ksplit;
   int stages;
+  int stage_bytes;  // host-side copy of the kernel's stage size
   int tmem_cols;
+  // Strip mode (halo_rows > 0, or a filter of height 1 handled the same way):
+  // tap group g = filter column g, local tap t = filter row t.
+  int strip_mode;
+  int strip_rows;       // pixels of one strip: box_w * box_n * (box_h + halo)
+  int halo_step_bytes;  // operand offset from one filter row to the next
   float *partial;  // [ksplit][taps][co_total][ci_total]
   int *status;
+  long long *trace;  // optional timeline of CTA 0 (builds with -DPLB_TRACE only)
 };
+
+#ifdef PLB_TRACE
+#define PLB_WU_STAMP(role, slot)                                               \
+  do {                                                                         \
+    if (args.trace != nullptr && blockIdx.x == 0 && (slot) < 4096)             \
+      args.trace[(role)*4096 + (slot)] = clock64();                            \
+  } while (0)
+#else
+#define PLB_WU_STAMP(role, slot) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(kWuThreads, 1)
 wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_x,
-          const WuArgs args) {
+          const __grid_constant__ CUtensorMap tm_out, const WuArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int a_bytes = 2 * kWuBlockBytes;  // 128 output channels
-  const int b_bytes = args.taps_per_group * args.ci_blk64 * kWuBlockBytes;
+  const bool strip = args.strip_mode != 0;
+  // one 64-channel block of the activations of a stage
+  const int b_block_bytes = strip ? args.strip_rows * 128 : kWuBlockBytes;
+  const int b_bytes = (strip ? 1 : args.taps_per_group) * args.ci_blk64 * b_block_bytes;
   const int stage_bytes = a_bytes + b_bytes;
   const int stages = args.stages;
   const uint32_t bar_base = smem_base + stages * stage_bytes;
@@ -68,7 +102,7 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), kWuProducers);
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(acc_bar, 1);
@@ -76,8 +110,9 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
     mbar_fence_init();
     tma_prefetch_desc(&tm_dy);
     tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_out);
   }
-  if (warp == 1) {
+  if (warp == 3) {
     tmem_alloc(tmem_slot, uint32_t(args.tmem_cols));
     tmem_relinquish();
   }
@@ -95,85 +130,144 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
   const int ci_block = unit % args.ci_blocks;
   const int co_block = unit / args.ci_blocks;
   const int taps = args.taps_h * args.taps_w;
-  const int tap0 = tap_group * args.taps_per_group;
-  const int ntaps = min(args.taps_per_group, taps - tap0);
+  // local tap t of this CTA is filter tap tap0 + t * tap_step
+  const int tap0 = strip ? tap_group : tap_group * args.taps_per_group;
+  const int tap_step = strip ? args.taps_w : 1;
+  const int ntaps = strip ? args.taps_h : min(args.taps_per_group, taps - tap0);
   const int pixel_tiles = args.tiles_w * args.tiles_h * args.tiles_n;
   const int t_begin = int((long long)pixel_tiles * split / args.ksplit);
   const int t_end = int((long long)pixel_tiles * (split + 1) / args.ksplit);
   const int k_iters = t_end - t_begin;
 
-  if (warp == 0) {
-    // ===================== TMA producer =====================
+  if (warp < kWuProducers) {
+    // ===================== TMA producers =====================
+    // Copy c of a K step (0, 1: the two 64-channel halves of the outGrad tile;
+    // then the 64-channel blocks of the activations, per tap or per strip) is
+    // issued by producer c mod kWuProducers; each producer arrives once per
+    // stage with the byte count of its own copies.
     if (elect_one()) {
+      const int me = warp;
+      const int copies = 2 + (strip ? 1 : ntaps) * args.ci_blk64;
+      uint32_t my_bytes = 0;
+      for (int c = me; c < copies; c += kWuProducers)
+        my_bytes += uint32_t(c < 2 ? kWuBlockBytes : b_block_bytes);
       int stage = 0;
       uint32_t phase = 0;
+      // pixel tile of the current K step, advanced without divisions
+      int tw = t_begin % args.tiles_w;
+      int th = (t_begin / args.tiles_w) % args.tiles_h;
+      int tn = t_begin / (args.tiles_w * args.tiles_h);
+      [[maybe_unused]] int trace_slot = 0;
       for (int it = 0; it < k_iters; ++it) {
-        const int tile = t_begin + it;
-        const int tw = tile % args.tiles_w;
-        const int th = (tile / args.tiles_w) % args.tiles_h;
-        const int tn = tile / (args.tiles_w * args.tiles_h);
         const int w0 = tw * args.box_w, h0 = th * args.box_h, n0 = tn * args.box_n;
+        if (me == 0) { PLB_WU_STAMP(0, trace_slot); ++trace_slot; }
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
           atomicCAS(args.status, kStatusOk, kStatusProducerTimeout);
           break;
         }
+        if (me == 0) { PLB_WU_STAMP(0, trace_slot); ++trace_slot; }
         const uint32_t a_dst = smem_base + stage * stage_bytes;
         const uint32_t b_dst = a_dst + a_bytes;
-        mbar_expect_tx(full_bar(stage), uint32_t(a_bytes + ntaps * args.ci_blk64 * kWuBlockBytes));
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-          tma_load_4d(a_dst + j * kWuBlockBytes, &tm_dy, full_bar(stage),
-                      co_block * 128 + j * 64, w0, h0, n0);
-        for (int t = 0; t < ntaps; ++t) {
-          const int tap = tap0 + t;
-          const int r = tap / args.taps_w, s = tap - r * args.taps_w;
-          const int iw = w0 * args.stride_w + s * args.dil_w - args.pad_w;
-          const int ih = h0 * args.stride_h + r * args.dil_h - args.pad_h;
-          for (int j = 0; j < args.ci_blk64; ++j)
-            tma_load_4d(b_dst + (t * args.ci_blk64 + j) * kWuBlockBytes, &tm_x, full_bar(stage),
+        mbar_expect_tx(full_bar(stage), my_bytes);
+        for (int c = me; c < copies; c += kWuProducers) {
+          if (c < 2) {
+            // tensor dimensions are (channel, w, h, n), in strip mode (channel, w, n, h)
+            tma_load_4d(a_dst + c * kWuBlockBytes, &tm_dy, full_bar(stage),
+                        co_block * 128 + c * 64, w0, strip ? n0 : h0, strip ? h0 : n0);
+          } else if (strip) {
+            const int j = c - 2;
+            const int iw = w0 * args.stride_w + tap0 * args.dil_w - args.pad_w;
+            const int ih = h0 - args.pad_h;
+            tma_load_4d(b_dst + j * b_block_bytes, &tm_x, full_bar(stage),
+                        ci_block * args.ci_blk + j * 64, iw, n0, ih);
+          } else {
+            const int t = (c - 2) / args.ci_blk64, j = (c - 2) - t * args.ci_blk64;
+            const int tap = tap0 + t;
+            const int r = tap / args.taps_w, sx = tap - r * args.taps_w;
+            const int iw = w0 * args.stride_w + sx * args.dil_w - args.pad_w;
+            const int ih = h0 * args.stride_h + r * args.dil_h - args.pad_h;
+            tma_load_4d(b_dst + (c - 2) * kWuBlockBytes, &tm_x, full_bar(stage),
                         ci_block * args.ci_blk + j * 64, iw, ih, n0);
+          }
         }
+        if (me == 0) { PLB_WU_STAMP(0, trace_slot); ++trace_slot; }
         if (++stage == stages) {
           stage = 0;
           phase ^= 1u;
         }
+        if (++tw == args.tiles_w) {
+          tw = 0;
+          if (++th == args.tiles_h) {
+            th = 0;
+            ++tn;
+          }
+        }
       }
-      // all copies issued by this thread must have landed before the CTA exits
-      for (int s = 0; s < stages; ++s) {
-        const uint32_t last = (s < stage) ? phase : (phase ^ 1u);
-        const long long start = clock64();
-        while (!mbar_try_wait(full_bar(s), last)) {
-          if (clock64() - start > kWaitCycleLimit) {
-            atomicCAS(args.status, kStatusOk, kStatusDrainTimeout);
-            break;
+      // producer 0: all copies must have landed before the CTA exits.  Stage st
+      // was last filled by K step g = the largest g < k_iters with g mod stages
+      // == st, in phase (g / stages) & 1.
+      if (me == 0) {
+        for (int st = 0; st < stages; ++st) {
+          if (k_iters <= st) continue;
+          const int g = st + ((k_iters - 1 - st) / stages) * stages;
+          const uint32_t last = uint32_t((g / stages) & 1);
+          const long long start = clock64();
+          while (!mbar_try_wait(full_bar(st), last)) {
+            if (*abort_flag != 0 || clock64() - start > kWaitCycleLimit) {
+              atomicCAS(args.status, kStatusOk, kStatusDrainTimeout);
+              break;
+            }
           }
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 3) {
     // ===================== MMA issuer =====================
     if (elect_one()) {
-      const uint32_t idesc = make_idesc(128, uint32_t(args.ci_blk), 0, 0, true, true);
+      // taps whose accumulator columns and operand blocks follow one another
+      // without a gap go into one instruction of up to 256 columns
+      const int merge =
+          !strip && args.ci_blk == args.ci_blk64 * 64 ? max(1, 256 / args.ci_blk) : 1;
+      const int tap_bytes = strip ? args.halo_step_bytes : args.ci_blk64 * kWuBlockBytes;
+      const uint32_t idesc_full =
+          make_idesc(128, uint32_t(merge * args.ci_blk), 0, 0, true, true);
+      const uint32_t idesc_rest =
+          make_idesc(128, uint32_t(max(1, ntaps % merge) * args.ci_blk), 0, 0, true, true);
+      const uint32_t d_step = uint32_t(merge * args.ci_blk);
+      const uint64_t b_step16 = uint64_t(merge * tap_bytes) >> 4;
+      const uint64_t a_desc0 = make_smem_desc(smem_base, kWuBlockBytes, 1024);
+      const uint64_t b_desc0 = make_smem_desc(smem_base + a_bytes, uint32_t(b_block_bytes), 1024);
       int stage = 0;
       uint32_t phase = 0;
+      [[maybe_unused]] int trace_slot = 0;
       for (int it = 0; it < k_iters; ++it) {
+        PLB_WU_STAMP(1, trace_slot); ++trace_slot;
         if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
           atomicCAS(args.status, kStatusOk, kStatusMmaTimeout);
           break;
         }
         tc_fence_after_sync();
-        const uint32_t a_addr = smem_base + stage * stage_bytes;
-        const uint32_t b_addr = a_addr + a_bytes;
+        PLB_WU_STAMP(1, trace_slot); ++trace_slot;
+        // The issuing thread's own instructions bound the MMA rate when an MMA
+        // is short, so descriptors are advanced with one addition each: the
+        // start-address field counts 16-byte units and never overflows.
+        const uint32_t stage_off16 = uint32_t(stage * stage_bytes) >> 4;
+        const uint64_t a_stage = a_desc0 + stage_off16;
+        const uint64_t b_stage = b_desc0 + stage_off16;
 #pragma unroll
         for (int k = 0; k < kWuPixelsPerStage / 16; ++k) {
           // 16 pixels = 16 rows of 128 bytes
-          const uint64_t a_desc = make_smem_desc(a_addr + k * 2048, kWuBlockBytes, 1024);
-          for (int t = 0; t < ntaps; ++t) {
-            const uint64_t b_desc = make_smem_desc(
-                b_addr + t * args.ci_blk64 * kWuBlockBytes + k * 2048, kWuBlockBytes, 1024);
-            umma_ss<false>(tmem_base + t * args.ci_blk, a_desc, b_desc, idesc,
-                           (it | k) != 0 ? 1u : 0u);
+          const uint64_t a_desc = a_stage + uint64_t(k * (2048 >> 4));
+          uint64_t b_desc = b_stage + uint64_t(k * (2048 >> 4));
+          uint32_t d_col = tmem_base;
+          const uint32_t accumulate = (it | k) != 0 ? 1u : 0u;
+          int t = 0;
+          for (; t + merge <= ntaps; t += merge) {
+            umma_ss<false>(d_col, a_desc, b_desc, idesc_full, accumulate);
+            d_col += d_step;
+            b_desc += b_step16;
           }
+          if (t < ntaps) umma_ss<false>(d_col, a_desc, b_desc, idesc_rest, accumulate);
         }
         umma_commit(empty_bar(stage));
         if (++stage == stages) {
@@ -191,46 +285,55 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
         }
       }
     }
-  } else {
-    // ===================== epilogue (warps 2..5) =====================
+  } else if (warp >= 4) {
+    // ===================== epilogue (warps 4..7) =====================
+    // Each warp owns 32 output channels (its TMEM lanes).  A 32 x 32 block of
+    // fp32 sums goes through a 4 KB staging buffer in the (now idle) pipeline
+    // memory, written with the 128-byte swizzle the tensor map expects, and
+    // leaves with one tensor store; two buffers per warp overlap the store of
+    // one block with the TMEM read of the next.  The store clips rows and
+    // columns beyond the tensor's extents.
     const int quarter = warp & 3;
-    const int co = co_block * 128 + quarter * 32 + lane;
+    const int co0 = co_block * 128 + quarter * 32;
     if (mbar_wait(acc_bar, 0, abort_flag)) {
       tc_fence_after_sync();
+      if (threadIdx.x == 128) PLB_WU_STAMP(2, 0);
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t stage_buf = smem_base + uint32_t(quarter) * 8192u;
+      int buf = 0;
       for (int t = 0; t < ntaps; ++t) {
-        const int tap = tap0 + t;
-        float *row = args.partial +
-                     ((size_t(split) * taps + tap) * args.co_total + co) * size_t(args.ci_total) +
-                     size_t(ci_block) * args.ci_blk;
         for (int c = 0; c < args.ci_blk; c += 32) {
+          const int ci0 = ci_block * args.ci_blk + c;
+          if (co0 >= args.co_total || ci0 >= args.ci_total) continue;  // warp-uniform
           uint32_t v[32];
-          __syncwarp();
           if (k_iters > 0) {
-            // ci_blk is a multiple of 16: the last chunk may be half valid
             tmem_ld_32x32(t_addr + t * args.ci_blk + c, v);
             tmem_ld_wait();
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0u;
           }
-          if (co < args.co_total) {
-            const int ci0 = ci_block * args.ci_blk + c;
-            const int valid = min(min(32, args.ci_blk - c), args.ci_total - ci0);
-            if (valid == 32 && (reinterpret_cast<uintptr_t>(row + c) & 15) == 0) {
+          // the store issued from this buffer two blocks ago must have read it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          const uint32_t row_addr = stage_buf + uint32_t(buf) * 4096u + uint32_t(lane) * 128u;
 #pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4 *>(row + c + j) =
-                    make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < valid) row[c + j] = __uint_as_float(v[j]);
-            }
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(row_addr + (uint32_t(j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1],
+                         v[4 * j + 2], v[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(&tm_out, stage_buf + uint32_t(buf) * 4096u, ci0, co0,
+                         tap0 + t * tap_step, split);
+            tma_store_commit();
           }
+          buf ^= 1;
         }
       }
+      if (lane == 0) tma_store_wait_all<0>();
+      __syncwarp();
+      if (threadIdx.x == 128) PLB_WU_STAMP(2, 1);
     } else {
       atomicCAS(args.status, kStatusOk, kStatusEpilogueTimeout);
     }
@@ -238,7 +341,7 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 3) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, uint32_t(args.tmem_cols));
   }
@@ -258,6 +361,30 @@ __global__ void wu_reduce_kernel(const float *__restrict__ partial, int ksplit, 
         static_cast<float *>(out_cast)[i] = s;
       else
         static_cast<__half *>(out_cast)[i] = __float2half_rn(s);
+    }
+  }
+}
+
+// The same over four consecutive sums per thread (count is a multiple of 4
+// and the pointers are 16-byte / 8-byte aligned).
+__global__ void wu_reduce4_kernel(const float4 *__restrict__ partial, int ksplit, size_t count4,
+                                  float4 *__restrict__ out_f32, uint2 *__restrict__ out_half) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < count4;
+       i += size_t(gridDim.x) * blockDim.x) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int k = 0; k < ksplit; ++k) {
+      const float4 v = partial[size_t(k) * count4 + i];
+      s.x += v.x;
+      s.y += v.y;
+      s.z += v.z;
+      s.w += v.w;
+    }
+    if (out_f32) out_f32[i] = s;
+    if (out_half) {
+      const __half2 lo = __floats2half2_rn(s.x, s.y), hi = __floats2half2_rn(s.z, s.w);
+      out_half[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                               *reinterpret_cast<const uint32_t *>(&hi));
     }
   }
 }

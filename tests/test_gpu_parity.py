@@ -162,11 +162,13 @@ SMALL_CONVS = {
     "one_dim": conv_case(4, [33], [5], 64, 96, padding=2),
     "groups2": conv_case(2, [6, 6], [3, 3], 64, 64, padding=1, groups=2),
     "batch1_big_field": conv_case(1, [40, 23], [3, 3], 64, 64, padding=1),
+    "5x5_pad2": conv_case(3, [10, 10], [5, 5], 64, 72, padding=2),
 }
 STRIDED_CONVS = {
     "1x1_s2": conv_case(2, [8, 8], [1, 1], 64, 128, stride=2),
     "3x3_s2": conv_case(2, [9, 9], [3, 3], 64, 64, padding=1, stride=2),
     "3x3_s2x3": conv_case(2, [11, 13], [3, 3], 64, 64, padding=1, stride=[2, 3]),
+    "3x3_s1x2": conv_case(5, [10, 13], [3, 3], 64, 64, padding=1, stride=[1, 2]),
 }
 
 
@@ -226,6 +228,25 @@ def test_conv_wu_small(gpu_ctx, name):
     assert_close(dw16, exp, REL_HALF, f"wu {name} uniform")
     # the two outputs of one call agree: half result is the rounded fp32 sum
     assert (dw32.astype(np.float16) == dw16).all()
+
+
+@pytest.mark.parametrize("name", ["3x3_pad1", "kernel_dilation", "5x5_pad2", "3x3_s1x2", "groups2"])
+def test_conv_wu_plan_variants(gpu_ctx, name):
+    """One activation strip per filter column (the default where the vertical
+    stride is 1) and one box per tap give the same sums; so does any K split."""
+    kw = {**SMALL_CONVS, **STRIDED_CONVS}[name]
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(zlib.crc32(name.encode()) % 1000 + 3)
+    x, _, dy = conv_data(p, kw, r, exact=True)
+    exp, _ = oracle.conv_wu(spec, x, dy)
+    assert capi.conv_wu_plan(p).halo_rows == (kw["kernel"][0] - 1) * kw.get("k_dilation", 1)
+    for flags, split in ((0, 0), (capi.PLAN_NO_HALO, 0), (0, 1), (0, 3), (capi.PLAN_NO_HALO, 2)):
+        opt = capi.ConvOptions.make(plan_flags=flags, split_k=split)
+        plan = capi.conv_wu_plan(p, opt)
+        assert (plan.halo_rows == 0) == bool(flags & capi.PLAN_NO_HALO)
+        _, dw32 = T.gpu_conv_wu(p, x, dy, opt=opt)
+        assert_exact(dw32, exp, f"wu {name} flags={flags} split={split}")
 
 
 PLAN_VARIANTS = {
