@@ -22,13 +22,16 @@
 //                 tensor copy costs a thread a few hundred cycles, so a single
 //                 producer cannot keep the tensor core fed on narrow tiles.
 //   warp 3        issues tcgen05.mma with fp32 accumulators in tensor memory.
-//   warps 4..7    epilogue: drain a finished accumulator (tcgen05.ld), scale /
-//                 add / cast, stage 32 rows x 128 bytes per warp in shared
-//                 memory and hand them to a TMA store (coalesced, clipped to
-//                 the tensor by the hardware); plain vector stores are the
-//                 fallback when the output cannot be described to TMA.
+//   warps 4..11   epilogue, two groups of four warps: drain a finished
+//                 accumulator (tcgen05.ld, the next 32 columns in flight while
+//                 the current ones are processed), scale / add / cast, stage
+//                 32 rows x 128 bytes per warp in shared memory and hand them
+//                 to a TMA store (coalesced, clipped to the tensor by the
+//                 hardware); plain vector stores are the fallback when the
+//                 output cannot be described to TMA.
 // Two accumulators alternate so the epilogue of one tile overlaps the main loop
-// of the next.
+// of the next; accumulator g is always drained by epilogue group g, so a group
+// has two tile periods for its tile.
 #pragma once
 
 #include "sm100_prims.cuh"
@@ -41,10 +44,10 @@ namespace plb {
 
 constexpr int kTileM = 128;        // pixels (rows) per tile = TMEM lanes
 constexpr int kStageKBytes = 128;  // bytes of K per pipeline stage row (one swizzle span)
-constexpr int kIgemmThreads = 256;
+constexpr int kIgemmThreads = 384;
 constexpr int kIgemmProducers = PLB_IGEMM_PRODUCERS;
 constexpr int kIgemmMmaWarp = 3;
-constexpr int kEpiStagingBytes = 4 * 2 * 4096;  // 4 warps x 2 buffers x (32 rows x 128 B)
+constexpr int kEpiStagingBytes = 8 * 4096;  // 8 epilogue warps x (32 rows x 128 B)
 static_assert(kIgemmProducers >= 1 && kIgemmProducers <= 3, "producer warps are warps 0..2");
 
 struct IgemmArgs {
@@ -362,6 +365,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     // ===================== MMA issuer =====================
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc(kTileM, BN, 0, 0, false, kBMn);
+      const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
+      // B tiles: resident ones start at resb_base, streamed ones follow the
+      // activations inside their stage
+      const uint64_t b_desc0 =
+          kBMn ? make_smem_desc(kResB ? resb_base : smem_base + uint32_t(args.a_stage_bytes),
+                                64 * kStageKBytes, 1024)
+               : make_smem_desc(kResB ? resb_base : smem_base + uint32_t(args.a_stage_bytes), 16,
+                                1024);
+      [[maybe_unused]] const uint64_t halo_step16 = uint64_t(uint32_t(args.halo_step_bytes) >> 4);
+      [[maybe_unused]] const uint64_t b_row_step16 =
+          uint64_t(uint32_t(args.taps_w * args.k_chunks) * (S::kBBytes >> 4));
       int stage = 0;
       uint32_t phase = 0;
       uint32_t acc_phase[2] = {0, 0};
@@ -396,17 +410,21 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           }
           tc_fence_after_sync();
           PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
-          const uint32_t a_addr = smem_base + stage * stage_bytes;
+          // Descriptors are advanced by adding to their start-address field
+          // (16-byte units, cannot overflow for shared-memory addresses): the
+          // issuing thread's own instruction count bounds the MMA rate on
+          // narrow tiles.
+          const uint32_t stage_off16 = uint32_t(stage * stage_bytes) >> 4;
+          uint64_t a_desc = a_desc0 + stage_off16;
+          uint64_t b_desc;
+          if constexpr (kHalo)
+            b_desc = b_desc0 + uint64_t((s_tap * args.k_chunks + kc) * (S::kBBytes >> 4));
+          else if constexpr (kResB)
+            b_desc = b_desc0 + uint64_t(it * (S::kBBytes >> 4));
+          else
+            b_desc = b_desc0 + stage_off16;
           const int row_taps = kHalo ? args.taps_h : 1;
           for (int r = 0; r < row_taps; ++r) {
-            // weight tile of this K step: resident tiles are indexed (r, s, kc)
-            const int b_index = kHalo ? ((r * args.taps_w + s_tap) * args.k_chunks + kc) : it;
-            const uint32_t b_addr =
-                kResB ? resb_base + b_index * S::kBBytes : a_addr + args.a_stage_bytes;
-            const uint64_t a_desc =
-                make_smem_desc(a_addr + (kHalo ? r * args.halo_step_bytes : 0), 16, 1024);
-            const uint64_t b_desc = kBMn ? make_smem_desc(b_addr, 64 * kStageKBytes, 1024)
-                                         : make_smem_desc(b_addr, 16, 1024);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               // one instruction consumes 32 bytes of K: advance the start address
@@ -415,6 +433,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
               const uint64_t b_k =
                   b_desc + uint64_t(kBMn ? k * ((16 * kStageKBytes) >> 4) : k * 2);
               umma_ss<kFp8>(d_tmem, a_k, b_k, idesc, (it | r | k) != 0 ? 1u : 0u);
+            }
+            if constexpr (kHalo) {
+              // next filter row: the strip shifted by whole 8-row groups; its
+              // resident weight tile is taps_w * k_chunks tiles further on
+              a_desc += halo_step16;
+              b_desc += b_row_step16;
             }
           }
           umma_commit(empty_bar(stage));  // frees the stage when these MMAs retire
@@ -441,21 +465,25 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       }
     }
   } else if (warp >= 4) {
-    // ===================== epilogue (warps 4..7) =====================
+    // ===================== epilogue (warps 4..11) =====================
+    const int group = (warp - 4) >> 2;       // drains accumulator `group`
     const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
     const int row = quarter * 32 + lane;     // tile row handled by this thread
-    uint32_t acc_phase[2] = {0, 0};
-    int local_tile = 0;
+    uint32_t acc_phase = 0;
     int rw, rh, rn;
     row_pixel(row, rw, rh, rn);
     // origin of this warp's 32 rows inside the tile's pixel box
     int qw, qh, qn;
     row_pixel(quarter * 32, qw, qh, qn);
-    const uint32_t my_staging = staging_base + uint32_t(quarter) * 8192u;
+    const uint32_t buf = staging_base + uint32_t(warp - 4) * 4096u;  // this warp's staged rows
+    const uint32_t row_addr = buf + uint32_t(lane) * 128u;
     const bool tma_store = args.use_tma_store != 0;
     const bool out_f32 = args.out_is_f32 != 0;
-    uint32_t store_count = 0;                // staging buffers used so far (selects the buffer)
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
+    const bool stamp = threadIdx.x == 128;
+    const int acc = group;
+    int local_tile = group;
+    for (int tile = int(blockIdx.x) + group * int(gridDim.x); tile < total_tiles;
+         tile += 2 * int(gridDim.x), local_tile += 2) {
       int m_idx, n_idx;
       tile_coords(tile, m_idx, n_idx);
       int w0, h0, n0;
@@ -463,29 +491,23 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       const int ow = w0 + rw, oh = h0 + rh, on = n0 + rn;
       const bool row_ok = ow < args.out_w && oh < args.out_h && on < args.out_n;
       const long long pixel = (static_cast<long long>(on) * args.out_h + oh) * args.out_w + ow;
-      const int acc = local_tile & 1;
-      if (threadIdx.x == 128) PLB_TRACE_STAMP(2, local_tile * 4 + 0);
-      if (!mbar_wait(tmem_full_bar(acc), acc_phase[acc], abort_flag)) {
+      if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 0);
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) {
         atomicCAS(args.status, kStatusOk, kStatusEpilogueTimeout);
         break;
       }
-      acc_phase[acc] ^= 1u;
+      acc_phase ^= 1u;
       tc_fence_after_sync();
-      if (threadIdx.x == 128) PLB_TRACE_STAMP(2, local_tile * 4 + 1);
+      if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 1);
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       const int col_base = n_idx * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        __syncwarp();
-        tmem_ld_32x32(t_addr + c, v);
-        tmem_ld_wait();
-        if (c + 32 >= BN) {
-          // the accumulator is fully read: hand it back before the stores
-          tc_fence_before_sync();
-          mbar_arrive(tmem_empty_bar(acc));
-          if (threadIdx.x == 128) PLB_TRACE_STAMP(2, local_tile * 4 + 2);
-        }
+      const bool box_ok = w0 + qw < args.out_w && h0 + qh < args.out_h && n0 + qn < args.out_n;
+
+      // 32 accumulator columns [c, c + 32) of this thread's row: scale / add /
+      // cast and store (or stage for the tensor store)
+      auto process = [&](const uint32_t (&v)[32], const int c) {
+        [[maybe_unused]] const bool fine = stamp && local_tile == 2;
+        if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 0);
         const int col0 = col_base + c;
         const int valid = min(32, args.n_total - col0);  // may be <= 0 on a padded N tile
         float f[32];
@@ -515,12 +537,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           // are XOR-swizzled with the row index, the pattern the tensor map uses.
           const int pass = out_f32 ? 0 : ((c >> 5) & 1);
           if (pass == 0) {
-            // the buffer about to be written must no longer be read by an older store
-            if (lane == 0) tma_store_wait_read<1>();
+            // the previous store from this buffer must have read it
+            if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 1);
+            if (lane == 0) tma_store_wait_read<0>();
             __syncwarp();
           }
-          const uint32_t buf = my_staging + (store_count & 1u) * 4096u;
-          const uint32_t row_addr = buf + uint32_t(lane) * 128u;
+          if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 2);
           if (out_f32) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -540,14 +562,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             }
           }
           const bool last_pass = out_f32 || pass == 1 || c + 32 >= BN;
+          if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 3);
           if (last_pass) {
             fence_proxy_async_smem();
             __syncwarp();
+            if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 4);
             if (lane == 0) {
               const int store_col = col_base + (out_f32 ? c : (c & ~63));
               // a box that starts outside the tensor has nothing to write
-              if (store_col < args.n_total && w0 + qw < args.out_w && h0 + qh < args.out_h &&
-                  n0 + qn < args.out_n) {
+              if (store_col < args.n_total && box_ok) {
                 if (args.h_outer)
                   tma_store_4d(&tm_out, buf, store_col, w0 + qw, n0 + qn, h0 + qh);
                 else
@@ -555,12 +578,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
               }
               tma_store_commit();
             }
-            ++store_count;
+            if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 5);
           }
         } else if (row_ok && valid > 0) {
           if (out_f32) {
             float *dst = static_cast<float *>(args.out) + pixel * args.ldc + col0;
-            if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+              // whole 32-byte sectors per lane
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                st_global_v8(dst + j, __float_as_uint(f[j]), __float_as_uint(f[j + 1]),
+                             __float_as_uint(f[j + 2]), __float_as_uint(f[j + 3]),
+                             __float_as_uint(f[j + 4]), __float_as_uint(f[j + 5]),
+                             __float_as_uint(f[j + 6]), __float_as_uint(f[j + 7]));
+            } else if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
                 *reinterpret_cast<float4 *>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
@@ -572,18 +603,21 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           } else {
             __half *dst = static_cast<__half *>(args.out) + pixel * args.ldc + col0;
             if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+              uint32_t pk[16];
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __half2 h0 = __floats2half2_rn(f[j], f[j + 1]);
-                __half2 h1 = __floats2half2_rn(f[j + 2], f[j + 3]);
-                __half2 h2 = __floats2half2_rn(f[j + 4], f[j + 5]);
-                __half2 h3 = __floats2half2_rn(f[j + 6], f[j + 7]);
-                pk.x = *reinterpret_cast<uint32_t *>(&h0);
-                pk.y = *reinterpret_cast<uint32_t *>(&h1);
-                pk.z = *reinterpret_cast<uint32_t *>(&h2);
-                pk.w = *reinterpret_cast<uint32_t *>(&h3);
-                *reinterpret_cast<uint4 *>(dst + j) = pk;
+              for (int j = 0; j < 16; ++j) {
+                __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+                pk[j] = *reinterpret_cast<uint32_t *>(&h);
+              }
+              if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+                // whole 32-byte sectors per lane
+                st_global_v8(dst, pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]);
+                st_global_v8(dst + 16, pk[8], pk[9], pk[10], pk[11], pk[12], pk[13], pk[14], pk[15]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  *reinterpret_cast<uint4 *>(dst + 8 * j) =
+                      make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
               }
             } else {
 #pragma unroll
@@ -592,8 +626,31 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             }
           }
         }
+      };
+
+      // Two register buffers: while one block of 32 columns is processed the
+      // load of the next is in flight (tcgen05.wait::ld covers all loads issued
+      // so far, so it is only executed between a load and the use of its data).
+      uint32_t va[32], vb[32];
+      __syncwarp();
+      tmem_ld_32x32(t_addr, va);
+#pragma unroll
+      for (int c = 0; c < BN; c += 64) {
+        tmem_ld_wait_for(va);
+        tmem_ld_32x32(t_addr + c + 32, vb);
+        process(va, c);
+        tmem_ld_wait_for(vb);
+        if (c + 64 < BN) {
+          tmem_ld_32x32(t_addr + c + 64, va);
+        } else {
+          // the accumulator is fully read: hand it back before the last stores
+          tc_fence_before_sync();
+          mbar_arrive(tmem_empty_bar(acc));
+          if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 2);
+        }
+        process(vb, c + 32);
       }
-      if (threadIdx.x == 128) PLB_TRACE_STAMP(2, local_tile * 4 + 3);
+      if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 3);
     }
     // all of this thread's stores must be complete before the CTA exits
     if (tma_store && lane == 0) tma_store_wait_all<0>();

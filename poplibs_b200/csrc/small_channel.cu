@@ -66,6 +66,62 @@ __global__ void s2dInputKernel(const __half *__restrict__ x, __half *__restrict_
   }
 }
 
+// The same rearrangement, one (n, h2) row of X2 per block iteration: the s
+// input rows that feed it are staged in shared memory with coalesced loads
+// (16-byte vectors when the rows are 16-byte aligned), then every thread
+// assembles 16-byte output vectors from them.  `lut` maps a channel of X2 to
+// (ph, pw, c) once per block instead of dividing per element.
+__global__ void __launch_bounds__(128)
+s2dInputRowsKernel(const __half *__restrict__ x, __half *__restrict__ x2, S2dShape g,
+                   int rows_aligned) {
+  extern __shared__ __align__(16) unsigned char s2d_smem[];
+  const int row_elems = g.W * g.C;
+  const int row_stride = (row_elems + 7) & ~7;  // halves; keeps every staged row 16-byte aligned
+  __half *rows = reinterpret_cast<__half *>(s2d_smem);
+  int *lut = reinterpret_cast<int *>(s2d_smem + size_t(g.s) * row_stride * 2);
+  for (int c2 = threadIdx.x; c2 < g.C2; c2 += blockDim.x) {
+    const int sub = c2 / g.Cp, c = c2 - sub * g.Cp;
+    const int ph = sub / g.s, pw = sub - ph * g.s;
+    lut[c2] = c < g.C ? (ph << 16) | (pw << 8) | c : -1;
+  }
+  const int vecs_per_pixel = g.C2 / 8;
+  const int out_vecs = g.W2 * vecs_per_pixel;
+  for (int blk = blockIdx.x; blk < g.N * g.H2; blk += gridDim.x) {
+    const int n = blk / g.H2, h2 = blk - n * g.H2;
+    __syncthreads();  // previous iteration's readers are done (and the table is written)
+    for (int ph = 0; ph < g.s; ++ph) {
+      const int ih = h2 * g.s + ph - g.padH;
+      if (ih < 0 || ih >= g.H) continue;  // block-uniform
+      const __half *src = x + (size_t(n) * g.H + ih) * row_elems;
+      __half *dst = rows + ph * row_stride;
+      if (rows_aligned) {
+        const uint4 *src4 = reinterpret_cast<const uint4 *>(src);
+        uint4 *dst4 = reinterpret_cast<uint4 *>(dst);
+        for (int v = threadIdx.x; v < row_elems / 8; v += blockDim.x) dst4[v] = src4[v];
+      } else {
+        for (int e = threadIdx.x; e < row_elems; e += blockDim.x) dst[e] = src[e];
+      }
+    }
+    __syncthreads();
+    __half *out_row = x2 + size_t(blk) * g.W2 * g.C2;
+    for (int o = threadIdx.x; o < out_vecs; o += blockDim.x) {
+      const int w2 = o / vecs_per_pixel, v = o - w2 * vecs_per_pixel;
+      __align__(16) __half vals[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int code = lut[v * 8 + j];
+        const int ph = code >> 16, pw = (code >> 8) & 0xff, c = code & 0xff;
+        const int ih = h2 * g.s + ph - g.padH, iw = w2 * g.s + pw - g.padW;
+        __half val = __float2half(0.f);
+        if (code >= 0 && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W)
+          val = rows[ph * row_stride + iw * g.C + c];
+        vals[j] = val;
+      }
+      *reinterpret_cast<uint4 *>(out_row + size_t(o) * 8) = *reinterpret_cast<const uint4 *>(vals);
+    }
+  }
+}
+
 // W2[a][co][(b*s*s + ph*s + pw)*Cp + c] = W[a*s + ph][b*s + pw][co][c], rows padded to 64.
 __global__ void s2dWeightsKernel(const __half *__restrict__ w, __half *__restrict__ w2, S2dShape g,
                                  int co_total) {
@@ -175,9 +231,19 @@ int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_c
   __half *x2 = static_cast<__half *>(ws);
   __half *w2 = x2 + ((x2_elems + 127) & ~size_t(127));
   {
-    const size_t vecs = size_t(g.N) * g.H2 * g.W2 * (g.C2 / 8);
-    const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 16));
-    s2dInputKernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const __half *>(d_in), x2, g);
+    const int row_elems = g.W * g.C;
+    const size_t smem = size_t(g.s) * ((row_elems + 7) & ~7) * 2 + size_t(g.C2) * sizeof(int);
+    if (smem <= 48 * 1024 && g.C < 256 && g.s < 256) {
+      const int rows_aligned =
+          (row_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) ? 1 : 0;
+      const int grid = int(std::min<size_t>(size_t(g.N) * g.H2, size_t(ctx->sm_count) * 16));
+      s2dInputRowsKernel<<<grid, 128, smem, ctx->stream>>>(static_cast<const __half *>(d_in), x2, g,
+                                                           rows_aligned);
+    } else {
+      const size_t vecs = size_t(g.N) * g.H2 * g.W2 * (g.C2 / 8);
+      const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 16));
+      s2dInputKernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const __half *>(d_in), x2, g);
+    }
     PLB_CUDA(cudaGetLastError());
     ctx->launches++;
     // the 64 trailing elements only ever meet zero weights, but must be finite

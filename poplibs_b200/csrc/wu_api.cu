@@ -219,11 +219,10 @@ int launchWu(cudaStream_t stream, const plb_conv_params &p, const WuShape &s, co
     if (w_elems % 4 == 0 && (reinterpret_cast<uintptr_t>(out32) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(out16) & 7) == 0) {
       const size_t count4 = w_elems / 4;
-      const int rgrid = int(std::min<size_t>((count4 + 127) / 128, size_t(148) * 16));
-      wu_reduce4_kernel<<<rgrid, 128, 0, stream>>>(reinterpret_cast<const float4 *>(a.partial),
-                                                   a.ksplit, count4,
-                                                   reinterpret_cast<float4 *>(out32),
-                                                   reinterpret_cast<uint2 *>(out16));
+      const unsigned rgrid = unsigned((count4 + 31) / 32);
+      wu_reduce4_kernel<<<rgrid, dim3(32, kWuReduceLanes), 0, stream>>>(
+          reinterpret_cast<const float4 *>(a.partial), a.ksplit, count4,
+          reinterpret_cast<float4 *>(out32), reinterpret_cast<uint2 *>(out16));
     } else {
       const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
       wu_reduce_kernel<<<rgrid, 256, 0, stream>>>(a.partial, a.ksplit, w_elems, out32, out16, 0);

@@ -366,15 +366,34 @@ __global__ void wu_reduce_kernel(const float *__restrict__ partial, int ksplit, 
 }
 
 // The same over four consecutive sums per thread (count is a multiple of 4
-// and the pointers are 16-byte / 8-byte aligned).
-__global__ void wu_reduce4_kernel(const float4 *__restrict__ partial, int ksplit, size_t count4,
-                                  float4 *__restrict__ out_f32, uint2 *__restrict__ out_half) {
-  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < count4;
-       i += size_t(gridDim.x) * blockDim.x) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int k = 0; k < ksplit; ++k) {
+// and the pointers are 16-byte / 8-byte aligned), with the K splits of one
+// output spread over kWuReduceLanes threads so that enough loads are in
+// flight: lane y adds splits y, y + lanes, ... in order, then the lanes'
+// sums are added in lane order.  The order of additions is fixed, so the
+// result does not depend on timing.
+constexpr int kWuReduceLanes = 8;
+__global__ void __launch_bounds__(32 * kWuReduceLanes)
+wu_reduce4_kernel(const float4 *__restrict__ partial, int ksplit, size_t count4,
+                  float4 *__restrict__ out_f32, uint2 *__restrict__ out_half) {
+  __shared__ float4 part[kWuReduceLanes][32];
+  const size_t i = blockIdx.x * size_t(32) + threadIdx.x;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (i < count4) {
+#pragma unroll 4
+    for (int k = threadIdx.y; k < ksplit; k += kWuReduceLanes) {
       const float4 v = partial[size_t(k) * count4 + i];
+      s.x += v.x;
+      s.y += v.y;
+      s.z += v.z;
+      s.w += v.w;
+    }
+  }
+  part[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && i < count4) {
+#pragma unroll
+    for (int y = 1; y < kWuReduceLanes; ++y) {
+      const float4 v = part[y][threadIdx.x];
       s.x += v.x;
       s.y += v.y;
       s.z += v.z;
