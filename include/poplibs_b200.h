@@ -194,6 +194,8 @@ typedef struct plb_conv_options {
 #define PLB_PLAN_FORCE_RESIDENT_WEIGHTS 1 /* keep weights in shared memory even for few tiles */
 #define PLB_PLAN_NO_RESIDENT_WEIGHTS 2    /* always stream the weights                        */
 #define PLB_PLAN_NO_HALO 4                /* one activation load per filter tap               */
+#define PLB_PLAN_NO_CTA_PAIR 8            /* every CTA issues its own 128-row MMAs            */
+#define PLB_PLAN_FORCE_CTA_PAIR 16        /* CTA pairs whenever the shape allows them         */
 
 /* out = conv(in, weights) (+ bias), poplin::convolution
  * (include/poplin/Convolution.hpp:345-384, lib/poplin/Convolution.cpp:3128-3215).
@@ -247,6 +249,13 @@ PLB_API int plb_conv_wu_static_scratch(int device, void *cuda_stream, const plb_
  * (popops::scaledAddTo in convolutionWeightUpdate, lib/poplin/Convolution.cpp:3509-3522). */
 PLB_API int plb_scaled_add_to(plb_context *ctx, int32_t dtype, void *d_weights,
                       const float *d_deltas_f32, float scale, size_t count);
+/* biases[c] += scale * sum over pixels of out_grads[pixel][c] on device-layout
+ * output gradients, sums in fp32 (poplin::convolutionBiasUpdate,
+ * include/poplin/Convolution.hpp:536-561; a reduce with update = true and the
+ * given scale, lib/poplin/Convolution.cpp:3601-3637). */
+PLB_API int plb_conv_bias_update(plb_context *ctx, int32_t acts_dtype, const void *d_out_grads,
+                         uint64_t pixels, uint32_t chans, int32_t bias_dtype, void *d_biases,
+                         float scale);
 /* acts[pixel][c] += biases[c] on device-layout activations (poplin::addBias,
  * include/poplin/Convolution.hpp:570-572); biases have the activations' type. */
 PLB_API int plb_add_bias(plb_context *ctx, int32_t dtype, void *d_acts, const void *d_biases,
@@ -321,6 +330,8 @@ typedef struct plb_plan {
   int32_t resident_weights; /* weights loaded once per CTA and kept in shared memory */
   int32_t halo_rows;   /* extra input rows per activation load that let one load
                           serve every vertical filter tap (0 = one load per tap) */
+  int32_t cta_pair;    /* 1 = clusters of two CTAs share 256-row tensor-core instructions */
+  int32_t reserved;
   uint64_t flops;      /* 2 * MACs (padding excluded)                        */
   uint64_t bytes;      /* operands read once + output written once           */
   uint64_t workspace_bytes;

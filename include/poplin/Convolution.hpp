@@ -108,6 +108,15 @@ void convolutionWeightUpdate(poplar::Graph &graph, const poplar::Tensor &zDeltas
                              const poplar::DebugContext &debugContext = {},
                              const poplar::OptionFlags &options = {},
                              PlanningCache *cache = nullptr);
+/// biases[c] += scale * sum over batch and field of zDeltas[n][c][...]; sums in fp32.
+void convolutionBiasUpdate(poplar::Graph &graph, const poplar::Tensor &zDeltas,
+                           const poplar::Tensor &biases, const poplar::Tensor &scale,
+                           const poplar::OptionFlags &options, poplar::program::Sequence &prog,
+                           const poplar::DebugContext &debugContext = {});
+void convolutionBiasUpdate(poplar::Graph &graph, const poplar::Tensor &zDeltas,
+                           const poplar::Tensor &biases, float scale,
+                           const poplar::OptionFlags &options, poplar::program::Sequence &prog,
+                           const poplar::DebugContext &debugContext = {});
 /// acts[n][c][...] += biases[c].
 void addBias(poplar::Graph &graph, const poplar::Tensor &in, const poplar::Tensor &biases,
              poplar::program::Sequence &prog, const poplar::DebugContext &debugContext = {});

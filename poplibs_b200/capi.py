@@ -13,7 +13,7 @@ PASS_NONE, PASS_NONE_MATMUL, PASS_INFERENCE_FWD, PASS_TRAINING_FWD, PASS_TRAININ
     PASS_TRAINING_WU, PASS_FC_INFERENCE_FWD, PASS_FC_TRAINING_FWD, PASS_FC_TRAINING_BWD, \
     PASS_FC_TRAINING_WU = range(10)
 MAX_DIMS = 3
-PLAN_FORCE_RESIDENT_WEIGHTS, PLAN_NO_RESIDENT_WEIGHTS, PLAN_NO_HALO = 1, 2, 4
+PLAN_FORCE_RESIDENT_WEIGHTS, PLAN_NO_RESIDENT_WEIGHTS, PLAN_NO_HALO, PLAN_NO_CTA_PAIR, PLAN_FORCE_CTA_PAIR = 1, 2, 4, 8, 16
 _U3 = C.c_uint32 * MAX_DIMS
 
 
@@ -117,7 +117,8 @@ class Plan(C.Structure):
                 ("tile_k_bytes", C.c_int32), ("box_w", C.c_int32), ("box_h", C.c_int32),
                 ("box_n", C.c_int32), ("stages", C.c_int32), ("split_k", C.c_int32),
                 ("grid", C.c_int32), ("tiles", C.c_int32), ("b_mn_major", C.c_int32),
-                ("resident_weights", C.c_int32), ("halo_rows", C.c_int32), ("flops", C.c_uint64), ("bytes", C.c_uint64), ("workspace_bytes", C.c_uint64)]
+                ("resident_weights", C.c_int32), ("halo_rows", C.c_int32), ("cta_pair", C.c_int32),
+                ("reserved", C.c_int32), ("flops", C.c_uint64), ("bytes", C.c_uint64), ("workspace_bytes", C.c_uint64)]
 
     def as_dict(self):
         return {n: int(getattr(self, n)) for n, _ in self._fields_}
@@ -133,7 +134,7 @@ SYMBOLS = (
     "plb_matmul", "plb_matmul_host", "plb_conv_validate", "plb_conv_output_field",
     "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution",
     "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
-    "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_fwd_host",
+    "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_bias_update", "plb_conv_fwd_host",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
     "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
     "plb_weights_transpose_chans_flip_xy", "plb_transpose_matrix", "plb_matmul_plan",
@@ -184,6 +185,7 @@ def lib():
     L.plb_scaled_add_to.argtypes = [vp, i32, vp, vp, f32, sz]
     L.plb_cast_from_f32.argtypes = [vp, i32, vp, vp, sz]
     L.plb_add_bias.argtypes = [vp, i32, vp, vp, u64, u32]
+    L.plb_conv_bias_update.argtypes = [vp, i32, vp, u64, u32, i32, vp, f32]
     L.plb_conv_fwd_host.argtypes = [vp, CP, OP, vp, vp, vp, vp]
     for name in ("plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device"):
         getattr(L, name).argtypes = [vp, u32, u32, u32, u64, vp, vp]
@@ -286,6 +288,10 @@ class Context:
 
     def scaled_add_to(self, dtype, weights, deltas_f32, scale, count):
         _check(lib().plb_scaled_add_to(self._h, dtype, _ptr(weights), _ptr(deltas_f32), scale, count))
+
+    def conv_bias_update(self, acts_dtype, out_grads, pixels, chans, bias_dtype, biases, scale):
+        _check(lib().plb_conv_bias_update(self._h, acts_dtype, _ptr(out_grads), pixels, chans,
+                                          bias_dtype, _ptr(biases), scale))
 
     def cast_from_f32(self, dtype, dst, src, count):
         _check(lib().plb_cast_from_f32(self._h, dtype, _ptr(dst), _ptr(src), count))

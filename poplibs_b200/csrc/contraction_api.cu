@@ -1,7 +1,9 @@
 // C ABI entry points of the contraction path: matMul, convolution forward and
 // backward-data.  Each maps its poplin-level description onto one or more
 // launches of the implicit-GEMM kernel (igemm_sm100.cuh).
+#include <algorithm>
 #include <cmath>
+#include <vector>
 
 #include "conv_geometry.h"
 #include "runtime.h"
@@ -98,9 +100,18 @@ uint64_t gemmBytes(const plb_matmul_desc &d) {
 
 struct ConvShape {
   unsigned nd;
-  int H, W, OH, OW;      // input / output field (H = 1 for 1-D)
+  int H, W, OH, OW;      // input / output field as stored (H = 1 for 1-D)
   int KH, KW;
+  // padH/padW: input padding minus output truncation at the low end, i.e.
+  // output position o, tap r reads truncated-input row o*stride + r*dil - pad
+  // (may be negative: the first rows are skipped)
   int padH, padW, dilH, dilW, strH, strW, flipH, flipW;
+  int tH, tW;            // input truncation at the low end (rows / columns not used)
+  int He, We;            // extent of the truncated input
+  int opH, opW;          // output padding at the low end (zero rows / columns)
+  int OHc, OWc;          // extent of the computed (not padded) output
+  bool zero_fill_out;    // the output has padded positions
+  bool zero_fill_in;     // the input has truncated positions (backward pass zeroes them)
 };
 
 int igemmConvShape(const plb_conv_params &p, ConvShape *s) {
@@ -114,13 +125,15 @@ int igemmConvShape(const plb_conv_params &p, ConvShape *s) {
     return fail(PLB_ERR_INVALID_PARAMS, "convolution output type must be half or float");
   if (p.input_type == PLB_QUARTER && p.output_type != PLB_HALF)
     return fail(PLB_ERR_INVALID_PARAMS, "Output type must be half when input type is quarter");
+  // Input truncation, output truncation and output padding are views and
+  // offsets (below).  Input dilation only arrives through the backward pass of
+  // a strided layer, which plb_conv_bwd takes in forward terms.
   for (unsigned d = 0; d != p.num_field_dims; ++d) {
-    if (p.in_trunc_lo[d] || p.in_trunc_hi[d] || p.in_dilation[d] != 1 || p.in_flip[d] ||
-        p.k_trunc_lo[d] || p.k_trunc_hi[d] || p.k_pad_lo[d] || p.k_pad_hi[d] ||
-        p.out_trunc_lo[d] || p.out_trunc_hi[d] || p.out_pad_lo[d] || p.out_pad_hi[d])
+    if (p.in_dilation[d] != 1 || p.in_flip[d] || p.k_trunc_lo[d] || p.k_trunc_hi[d] ||
+        p.k_pad_lo[d] || p.k_pad_hi[d])
       return fail(PLB_ERR_UNSUPPORTED,
-                  "input truncation/dilation/flip, kernel truncation/padding and output "
-                  "truncation/padding are not implemented on this path yet");
+                  "input dilation/flip and kernel truncation/padding are not implemented on "
+                  "this path yet");
   }
   s->nd = p.num_field_dims;
   const unsigned hd = p.num_field_dims == 2 ? 0 : ~0u, wd = p.num_field_dims - 1;
@@ -139,6 +152,18 @@ int igemmConvShape(const plb_conv_params &p, ConvShape *s) {
   s->flipW = get(p.k_flip, wd, 0);
   s->OH = hd == ~0u ? 1 : int(outputSize(p, hd));
   s->OW = int(outputSize(p, wd));
+  s->tH = get(p.in_trunc_lo, hd, 0);
+  s->tW = get(p.in_trunc_lo, wd, 0);
+  s->He = s->H - s->tH - get(p.in_trunc_hi, hd, 0);
+  s->We = s->W - s->tW - get(p.in_trunc_hi, wd, 0);
+  s->padH -= get(p.out_trunc_lo, hd, 0);
+  s->padW -= get(p.out_trunc_lo, wd, 0);
+  s->opH = get(p.out_pad_lo, hd, 0);
+  s->opW = get(p.out_pad_lo, wd, 0);
+  s->OHc = s->OH - s->opH - get(p.out_pad_hi, hd, 0);
+  s->OWc = s->OW - s->opW - get(p.out_pad_hi, wd, 0);
+  s->zero_fill_out = s->OHc != s->OH || s->OWc != s->OW;
+  s->zero_fill_in = s->He != s->H || s->We != s->W;
   return PLB_OK;
 }
 
@@ -170,21 +195,23 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
   IgemmProblem r;
   r.fp8 = p.input_type == PLB_QUARTER;
-  r.act = static_cast<const uint8_t *>(in) + size_t(g) * ci * es;
+  // the truncated input is a view: same strides, shifted base, smaller extents
+  r.act = static_cast<const uint8_t *>(in) +
+          ((size_t(s.tH) * s.W + s.tW) * ctot + size_t(g) * ci) * es;
   const bool pointwise = s.KH == 1 && s.KW == 1 && s.padH == 0 && s.padW == 0;
   if (pointwise) {
     // a strided 1x1 convolution reads a sub-lattice: describe only that
     r.act_dims[0] = ci;
-    r.act_dims[1] = uint64_t(s.OW);
-    r.act_dims[2] = uint64_t(s.OH);
+    r.act_dims[1] = uint64_t(s.OWc);
+    r.act_dims[2] = uint64_t(s.OHc);
     r.act_dims[3] = p.batch;
     r.act_strides[0] = uint64_t(s.strW) * ctot * es;
     r.act_strides[1] = uint64_t(s.strH) * s.W * ctot * es;
     r.act_strides[2] = uint64_t(s.H) * s.W * ctot * es;
   } else {
     r.act_dims[0] = ci;
-    r.act_dims[1] = uint64_t(s.W);
-    r.act_dims[2] = uint64_t(s.H);
+    r.act_dims[1] = uint64_t(s.We);
+    r.act_dims[2] = uint64_t(s.He);
     r.act_dims[3] = p.batch;
     r.act_strides[0] = ctot * es;
     r.act_strides[1] = uint64_t(s.W) * ctot * es;
@@ -201,8 +228,9 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.wgt_dims[2] = uint64_t(s.KH) * s.KW;
   r.wgt_strides[0] = (swapped_weights ? co : ci) * es;
   r.wgt_strides[1] = co * ci * es;
-  r.out_w = s.OW;
-  r.out_h = s.OH;
+  // the computed part of the output is a view of the stored (padded) one
+  r.out_w = s.OWc;
+  r.out_h = s.OHc;
   r.out_n = int(p.batch);
   r.n_total = int(co);
   r.k_per_tap = int(ci);
@@ -214,8 +242,11 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.dil_w = s.dilW;
   r.flip_h = swapped_weights ? !s.flipH : s.flipH;
   r.flip_w = swapped_weights ? !s.flipW : s.flipW;
-  r.out = static_cast<uint8_t *>(out) + size_t(g) * co * os;
+  r.out = static_cast<uint8_t *>(out) +
+          ((size_t(s.opH) * s.OW + s.opW) * cotot + size_t(g) * co) * os;
   r.ldc = (long long)cotot;
+  r.out_stride_h = (long long)(cotot * s.OW);
+  r.out_stride_n = (long long)(cotot * s.OW * s.OH);
   r.bias = bias ? bias + size_t(g) * co : nullptr;
   r.out_f32 = p.output_type == PLB_FLOAT;
   r.force_tile_n = opt ? opt->tile_n : 0;
@@ -238,10 +269,12 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
   IgemmProblem r;
   r.fp8 = p.input_type == PLB_QUARTER;
-  r.act = static_cast<const uint8_t *>(dy) + size_t(g) * co * es;
+  // computed part of the output gradients / used part of the input gradients
+  r.act = static_cast<const uint8_t *>(dy) +
+          ((size_t(s.opH) * s.OW + s.opW) * cotot + size_t(g) * co) * es;
   r.act_dims[0] = co;
-  r.act_dims[1] = uint64_t(s.OW);
-  r.act_dims[2] = uint64_t(s.OH);
+  r.act_dims[1] = uint64_t(s.OWc);
+  r.act_dims[2] = uint64_t(s.OHc);
   r.act_dims[3] = p.batch;
   r.act_strides[0] = cotot * es;
   r.act_strides[1] = uint64_t(s.OW) * cotot * es;
@@ -264,8 +297,8 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   }
   r.wgt_dims[2] = uint64_t(s.KH) * s.KW;
   r.wgt_strides[1] = co * ci * es;
-  r.out_w = s.W;
-  r.out_h = s.H;
+  r.out_w = s.We;
+  r.out_h = s.He;
   r.out_n = int(p.batch);
   r.n_total = int(ci);
   r.k_per_tap = int(co);
@@ -275,13 +308,179 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.pad_w = (s.KW - 1) * s.dilW - s.padW;
   r.dil_h = s.dilH;
   r.dil_w = s.dilW;
-  r.out = static_cast<uint8_t *>(dx) + size_t(g) * ci * os;
+  r.out = static_cast<uint8_t *>(dx) + ((size_t(s.tH) * s.W + s.tW) * ctot + size_t(g) * ci) * os;
   r.ldc = (long long)ctot;
+  r.out_stride_h = (long long)(ctot * s.W);
+  r.out_stride_n = (long long)(ctot * s.W * s.H);
   r.out_f32 = p.output_type == PLB_FLOAT;
   r.force_tile_n = opt ? opt->tile_n : 0;
   r.plan_flags = opt ? opt->plan_flags : 0;
   if (r.fp8 && opt) r.alpha = std::ldexp(1.0f, opt->scale_in + opt->scale_weights);
   *q = r;
+  return PLB_OK;
+}
+
+// Filter taps (r0h + jh*sh, r0w + jw*sw), jh < JH, jw < JW, of [G][KH*KW][inner]
+// weights gathered into [G][JH*JW][inner]; 16-byte vectors.
+__global__ void gatherTapsKernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, int groups,
+                                 int KH, int KW, int JH, int JW, int r0h, int r0w, int sh, int sw,
+                                 size_t inner_vecs) {
+  const size_t total = size_t(groups) * JH * JW * inner_vecs;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const size_t v = i % inner_vecs;
+    size_t t = i / inner_vecs;
+    const int jw = int(t % JW);
+    t /= JW;
+    const int jh = int(t % JH);
+    const int g = int(t / JH);
+    const size_t tap = size_t(r0h + jh * sh) * KW + size_t(r0w + jw * sw);
+    dst[i] = src[(size_t(g) * KH * KW + tap) * inner_vecs + v];
+  }
+}
+
+// One dimension of the backward pass of a strided convolution, for the input
+// positions i*stride + phase: which filter taps reach them and where.
+struct BwdPhase {
+  int first_tap;   // r0: smallest tap with (phase + pad - r*dil) divisible by stride
+  int taps;        // J: taps r0, r0 + stride, ...
+  int offset;      // (phase + pad - r0*dil) / stride: output index read by tap r0 at i = 0
+  int extent;      // input positions of this phase
+};
+// Returns false when dilation and stride share a factor (taps are then not
+// evenly spaced; not implemented).
+bool bwdPhase(int phase, int in_size, int kernel, int pad, int dil, int stride, BwdPhase *out) {
+  out->extent = phase < in_size ? (in_size - phase + stride - 1) / stride : 0;
+  out->first_tap = -1;
+  out->taps = 0;
+  out->offset = 0;
+  for (int r = 0; r < kernel; ++r) {
+    const int num = phase + pad - r * dil;
+    if (((num % stride) + stride) % stride != 0) continue;
+    if (out->first_tap < 0) {
+      out->first_tap = r;
+      // exact: num is a multiple of stride (possibly negative)
+      out->offset = num / stride;
+    } else if ((r - out->first_tap) % stride != 0) {
+      return false;
+    }
+    ++out->taps;
+  }
+  if (out->taps > 1) {
+    // evenly spaced taps need the second one exactly `stride` further on
+    int second = -1;
+    for (int r = out->first_tap + 1; r < kernel && second < 0; ++r)
+      if ((((phase + pad - r * dil) % stride) + stride) % stride == 0) second = r;
+    if (second != out->first_tap + stride) return false;
+  }
+  return true;
+}
+
+// Backward pass of a strided convolution (the reference's getGradientParams
+// gives the output gradients an input dilation equal to the forward stride,
+// lib/poplin/ConvUtil.cpp:728-795).  Multiplying the inserted zeros would
+// waste stride^2 of the work: instead the input gradient is computed per
+// phase (ih mod stride_h, iw mod stride_w).  The positions of one phase see a
+// fixed, evenly spaced subset of the filter taps, so each phase is a stride-1
+// convolution of the output gradients with the gathered sub-filter, written
+// to the strided sub-lattice of the input gradient.
+int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+                   const ConvShape &s, const void *dy, const void *w, void *dx) {
+  if (p.input_type != PLB_HALF)
+    return fail(PLB_ERR_UNSUPPORTED,
+                "backward pass of a strided quarter convolution is not implemented on this path yet");
+  const size_t es = 2, os = dtypeBytes(p.output_type);
+  const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
+  const uint64_t ctot = uint64_t(p.groups) * ci, cotot = uint64_t(p.groups) * co;
+  const size_t inner = size_t(co) * ci;  // elements per tap and group
+  if ((inner * es) % 16 != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0)
+    return fail(PLB_ERR_UNSUPPORTED, "weights must be 16-byte aligned per tap");
+  // phases and their taps
+  std::vector<BwdPhase> ph(size_t(s.strH)), pw(size_t(s.strW));
+  for (int a = 0; a < s.strH; ++a)
+    if (!bwdPhase(a, s.He, s.KH, s.padH, s.dilH, s.strH, &ph[size_t(a)]))
+      return fail(PLB_ERR_UNSUPPORTED,
+                  "backward pass: kernel dilation and stride with a common factor are not "
+                  "implemented on this path yet");
+  for (int b = 0; b < s.strW; ++b)
+    if (!bwdPhase(b, s.We, s.KW, s.padW, s.dilW, s.strW, &pw[size_t(b)]))
+      return fail(PLB_ERR_UNSUPPORTED,
+                  "backward pass: kernel dilation and stride with a common factor are not "
+                  "implemented on this path yet");
+  // positions no tap reaches get zero
+  bool any_empty = false;
+  size_t scratch_elems = 0;
+  for (const auto &a : ph)
+    for (const auto &b : pw) {
+      if (a.extent == 0 || b.extent == 0) continue;
+      if (a.taps == 0 || b.taps == 0) any_empty = true;
+      scratch_elems = std::max(scratch_elems, size_t(p.groups) * a.taps * b.taps * inner);
+    }
+  if (any_empty && !s.zero_fill_in)  // (otherwise the caller has cleared it)
+    PLB_CUDA(cudaMemsetAsync(dx, 0, size_t(p.batch) * s.H * s.W * ctot * os, ctx->stream));
+  void *ws = nullptr;
+  // one buffer per phase: the launches of different phases are in flight together
+  const size_t slot = (scratch_elems * es + 255) & ~size_t(255);
+  if (int rc = scratch(ctx, 0, slot * size_t(s.strH) * s.strW + 256, &ws)) return rc;
+  for (int a = 0; a < s.strH; ++a)
+    for (int b = 0; b < s.strW; ++b) {
+      const BwdPhase &A = ph[size_t(a)], &B = pw[size_t(b)];
+      if (A.extent == 0 || B.extent == 0 || A.taps == 0 || B.taps == 0) continue;
+      uint8_t *wsub = static_cast<uint8_t *>(ws) + slot * (size_t(a) * s.strW + b);
+      const size_t vecs = size_t(p.groups) * A.taps * B.taps * (inner * es / 16);
+      const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 8));
+      gatherTapsKernel<<<grid, 256, 0, ctx->stream>>>(
+          static_cast<const uint4 *>(w), reinterpret_cast<uint4 *>(wsub), int(p.groups), s.KH, s.KW,
+          A.taps, B.taps, A.first_tap, B.first_tap, s.strH, s.strW, inner * es / 16);
+      PLB_CUDA(cudaGetLastError());
+      ctx->launches++;
+      for (unsigned g = 0; g < p.groups; ++g) {
+        IgemmProblem r;
+        r.act = static_cast<const uint8_t *>(dy) +
+                ((size_t(s.opH) * s.OW + s.opW) * cotot + size_t(g) * co) * es;
+        r.act_dims[0] = co;
+        r.act_dims[1] = uint64_t(s.OWc);
+        r.act_dims[2] = uint64_t(s.OHc);
+        r.act_dims[3] = p.batch;
+        r.act_strides[0] = cotot * es;
+        r.act_strides[1] = uint64_t(s.OW) * cotot * es;
+        r.act_strides[2] = uint64_t(s.OH) * s.OW * cotot * es;
+        // gathered [tap][Co][Ci]: K = co rows of N = ci, an MN-major right operand
+        r.b_mn = true;
+        r.wgt = wsub + size_t(g) * A.taps * B.taps * inner * es;
+        r.wgt_dims[0] = ci;
+        r.wgt_dims[1] = co;
+        r.wgt_dims[2] = uint64_t(A.taps) * B.taps;
+        r.wgt_strides[0] = ci * es;
+        r.wgt_strides[1] = inner * es;
+        r.out_w = B.extent;
+        r.out_h = A.extent;
+        r.out_n = int(p.batch);
+        r.n_total = int(ci);
+        r.k_per_tap = int(co);
+        r.taps_h = A.taps;
+        r.taps_w = B.taps;
+        // position i of the phase reads output index i + offset - j*dil for the
+        // j-th gathered tap: a correlation with the taps reversed
+        r.dil_h = s.dilH;
+        r.dil_w = s.dilW;
+        r.pad_h = (A.taps - 1) * s.dilH - A.offset;
+        r.pad_w = (B.taps - 1) * s.dilW - B.offset;
+        r.flip_h = !s.flipH;
+        r.flip_w = !s.flipW;
+        r.out = static_cast<uint8_t *>(dx) +
+                ((size_t(s.tH + a) * s.W + (s.tW + b)) * ctot + size_t(g) * ci) * os;
+        r.ldc = (long long)(ctot * s.strW);
+        r.out_stride_h = (long long)(ctot * s.W * s.strH);
+        r.out_stride_n = (long long)(ctot * s.W * s.H);
+        r.out_f32 = p.output_type == PLB_FLOAT;
+        r.force_tile_n = opt ? opt->tile_n : 0;
+        r.plan_flags = opt ? opt->plan_flags : 0;
+        plb_plan plan{};
+        if (int rc = planIgemm(r, ctx->sm_count, &plan)) return rc;
+        if (int rc = launchIgemm(ctx, r, plan)) return rc;
+      }
+    }
   return PLB_OK;
 }
 
@@ -466,6 +665,17 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
     return PLB_OK;
   if (p->in_chans_per_group == 0)
     return fail(PLB_ERR_UNSUPPORTED, "zero input channels are not implemented on this path yet");
+  if (s.zero_fill_out || s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) {
+    // padded output positions (and everything, if nothing is computed) are zero
+    PLB_CUDA(cudaMemsetAsync(d_out, 0,
+                             size_t(p->batch) * s.OH * s.OW * p->groups * p->out_chans_per_group *
+                                 dtypeBytes(p->output_type),
+                             ctx->stream));
+    if (s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) return PLB_OK;
+    if (s.zero_fill_out && d_bias)
+      return fail(PLB_ERR_UNSUPPORTED,
+                  "a fused bias with output padding is not implemented: use plb_add_bias");
+  }
   if (!channelsFitTma(*p, p->in_chans_per_group)) {
     if (transpose_and_flip_weights)
       return fail(PLB_ERR_UNSUPPORTED,
@@ -516,12 +726,23 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
   ConvShape s;
   if (int rc = igemmConvShape(*p, &s)) return rc;
-  if (s.strH != 1 || s.strW != 1)
-    return fail(PLB_ERR_UNSUPPORTED,
-                "backward pass of a strided convolution is not implemented on this path yet");
   if (p->batch == 0 || p->groups == 0 || p->in_chans_per_group == 0 || s.H == 0 || s.W == 0)
     return PLB_OK;
   const size_t es = dtypeBytes(p->input_type);
+  if (s.zero_fill_in)  // truncated input positions receive no gradient
+    PLB_CUDA(cudaMemsetAsync(d_in_grads, 0,
+                             size_t(p->batch) * s.H * s.W * p->groups * p->in_chans_per_group *
+                                 dtypeBytes(p->output_type),
+                             ctx->stream));
+  if (s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) {
+    if (!s.zero_fill_in)
+      PLB_CUDA(cudaMemsetAsync(d_in_grads, 0,
+                               size_t(p->batch) * s.H * s.W * p->groups * p->in_chans_per_group *
+                                   dtypeBytes(p->output_type),
+                               ctx->stream));
+    return PLB_OK;
+  }
+  if (s.strH != 1 || s.strW != 1) return convBwdStrided(ctx, *p, opt, s, d_out_grads, d_weights, d_in_grads);
   const void *w = d_weights;
   bool transposed = false;
   if (p->input_type == PLB_QUARTER) {

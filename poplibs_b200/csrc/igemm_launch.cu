@@ -32,31 +32,87 @@ const bool g_disable_resident = [] {
   return e != nullptr && e[0] == '1';
 }();
 
-template <int BN, bool kFp8, bool kBMn, bool kResB, bool kHalo>
-int launchInstance(plb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb,
-                   const CUtensorMap &tout, const IgemmArgs &args, int grid, int resident_bytes) {
-  using S = IgemmSmem<BN, kResB>;
-  static bool configured[64] = {};
-  auto kernel = igemm_kernel<BN, kFp8, kBMn, kResB, kHalo>;
-  if (!configured[ctx->device & 63]) {
-    PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kIgemmSmemLimit));
-    configured[ctx->device & 63] = true;
-  }
-  const int smem = S::totalBytes(args.a_stage_bytes, args.num_stages, resident_bytes);
-  kernel<<<grid, kIgemmThreads, smem, ctx->stream>>>(ta, tb, tout, args);
-  PLB_CUDA(cudaGetLastError());
-  ctx->launches++;
-  return PLB_OK;
+// PLB_DISABLE_CTA_PAIR=1 keeps every CTA on its own 128-row MMAs.
+const bool g_disable_pair = [] {
+  const char *e = std::getenv("PLB_DISABLE_CTA_PAIR");
+  return e != nullptr && e[0] == '1';
+}();
+
+// PLB_FORCE_CTA_PAIR=1 (read at every plan, so a test can toggle it) pairs CTAs
+// whenever the shape allows, also for calls that carry no plan flags.
+bool forcePairFromEnv() {
+  const char *e = std::getenv("PLB_FORCE_CTA_PAIR");
+  return e != nullptr && e[0] == '1';
 }
 
-int stagesFor(int bn, int a_stage_bytes, bool resident, int resident_bytes) {
-  const int a = a_stage_bytes;
-  switch (bn) {
-    case 64: return resident ? IgemmSmem<64, true>::stagesFor(a, resident_bytes) : IgemmSmem<64, false>::stagesFor(a, 0);
-    case 128: return resident ? IgemmSmem<128, true>::stagesFor(a, resident_bytes) : IgemmSmem<128, false>::stagesFor(a, 0);
-    default: return resident ? IgemmSmem<256, true>::stagesFor(a, resident_bytes) : IgemmSmem<256, false>::stagesFor(a, 0);
+template <int BN, bool kFp8, bool kBMn, bool kResB, bool kHalo, bool k2Cta>
+int launchInstance(plb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb,
+                   const CUtensorMap &tout, const IgemmArgs &args, int grid, int resident_bytes) {
+  if constexpr (k2Cta && kBMn && BN < 128) {
+    return fail(PLB_ERR_INVALID_OPTION, "a CTA pair needs tile_n >= 128 for a row-major B");
+  } else {
+    using S = IgemmSmem<BN, kResB, k2Cta>;
+    static bool configured[64] = {};
+    static int max_clusters[64] = {};
+    auto kernel = igemm_kernel<BN, kFp8, kBMn, kResB, kHalo, k2Cta>;
+    const int dev = ctx->device & 63;
+    if (!configured[dev]) {
+      PLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kIgemmSmemLimit));
+      configured[dev] = true;
+    }
+    const int smem =
+        S::totalBytes(args.a_stage_bytes, args.b_tiles_per_stage, args.num_stages, resident_bytes);
+    if constexpr (!k2Cta) {
+      kernel<<<grid, kIgemmThreads, smem, ctx->stream>>>(ta, tb, tout, args);
+    } else {
+      // clusters of two CTAs; a persistent grid of as many clusters as can be
+      // resident at once (pairs of SMs in one GPC), each walking tile pairs
+      cudaLaunchConfig_t cfg{};
+      cfg.blockDim = dim3(kIgemmThreads);
+      cfg.dynamicSmemBytes = size_t(smem);
+      cfg.stream = ctx->stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      if (max_clusters[dev] == 0) {
+        // queried with the largest shared-memory size, a lower bound for smaller ones
+        cfg.gridDim = dim3(unsigned(2 * ctx->sm_count));
+        cfg.dynamicSmemBytes = size_t(kIgemmSmemLimit);
+        int n = 0;
+        PLB_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        if (n <= 0) return fail(PLB_ERR_CUDA, "no cluster of two CTAs can be resident on this device");
+        max_clusters[dev] = n;
+        cfg.dynamicSmemBytes = size_t(smem);
+      }
+      const int clusters = std::max(1, std::min(grid / 2, max_clusters[dev]));
+      cfg.gridDim = dim3(unsigned(2 * clusters));
+      PLB_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tout, args));
+    }
+    PLB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return PLB_OK;
   }
+}
+
+int stagesFor(int bn, int a_stage_bytes, int b_tiles, bool resident, int resident_bytes,
+              bool pair) {
+  const int a = a_stage_bytes;
+#define PLB_STAGES(BN)                                                                         \
+  return resident ? (pair ? IgemmSmem<BN, true, true>::stagesFor(a, b_tiles, resident_bytes)   \
+                          : IgemmSmem<BN, true, false>::stagesFor(a, b_tiles, resident_bytes)) \
+                  : (pair ? IgemmSmem<BN, false, true>::stagesFor(a, b_tiles, 0)               \
+                          : IgemmSmem<BN, false, false>::stagesFor(a, b_tiles, 0));
+  switch (bn) {
+    case 64: PLB_STAGES(64)
+    case 128: PLB_STAGES(128)
+    default: PLB_STAGES(256)
+  }
+#undef PLB_STAGES
 }
 
 // Weights stay in shared memory when one N tile covers all output channels,
@@ -116,10 +172,32 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
   plan->box_n = bb;
   plan->split_k = 1;
   plan->tiles = int(best_tiles * n_tiles);
-  plan->grid = std::min(plan->tiles, sm_count > 0 ? sm_count : 148);
+  // CTA pairs: two M tiles share one 256-row MMA, each CTA holding half of the
+  // weight tile.  Needs two M tiles and, for a row-major B, a whole 64-column
+  // block per CTA.
+  // Worth it when every CTA pair gets several tile pairs and a tile's K loop is
+  // long: the two SMs advance in lockstep per tile, which costs more than the
+  // halved weight traffic saves on short tiles and on grids of a few tiles.
+  const int k_elems_stage = kStageKBytes / elem;
+  const long k_steps_per_tile =
+      long(p.taps_h) * p.taps_w * ((p.k_per_tap + k_elems_stage - 1) / k_elems_stage);
+  const int sms_for_pair = sm_count > 0 ? sm_count : 148;
+  const bool pair = !g_disable_pair && (p.plan_flags & PLB_PLAN_NO_CTA_PAIR) == 0 &&
+                    (!p.b_mn || bn >= 128) &&
+                    ((p.plan_flags & PLB_PLAN_FORCE_CTA_PAIR) != 0 || forcePairFromEnv()
+                         ? best_tiles >= 2
+                         : (k_steps_per_tile >= 8 && best_tiles * n_tiles >= 2L * sms_for_pair));
+  plan->cta_pair = pair ? 1 : 0;
+  auto grid_for = [&](long m_tiles) {
+    const int sms = sm_count > 0 ? sm_count : 148;
+    if (!pair) return int(std::min<long>(m_tiles * n_tiles, sms));
+    return int(2 * std::min<long>(((m_tiles + 1) / 2) * n_tiles, sms / 2));
+  };
+  plan->grid = grid_for(best_tiles);
   const int k_elems = kStageKBytes / elem;
   const long k_iters = long(p.taps_h) * p.taps_w * ((p.k_per_tap + k_elems - 1) / k_elems);
-  const long resident_bytes = k_iters * bn * kStageKBytes;
+  // per CTA
+  const long resident_bytes = k_iters * (bn / (pair ? 2 : 1)) * kStageKBytes;
   const bool want_resident = (p.plan_flags & PLB_PLAN_FORCE_RESIDENT_WEIGHTS) != 0 ||
                              plan->tiles >= 2 * plan->grid;
   plan->resident_weights =
@@ -128,16 +206,23 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
           ? 1
           : 0;
   plan->halo_rows = 0;
-  plan->stages = stagesFor(bn, kTileM * kStageKBytes, plan->resident_weights != 0,
-                           plan->resident_weights ? int(resident_bytes) : 0);
+  plan->stages = stagesFor(bn, kTileM * kStageKBytes, 1, plan->resident_weights != 0,
+                           plan->resident_weights ? int(resident_bytes) : 0, pair);
   // Halo mode: with resident weights and a filter taller than one row (unit
   // vertical stride), load (box_h + halo) input rows once per horizontal tap
   // instead of box_h rows per tap.  The tile rows are ordered (w, n, h) so that
   // a vertical shift is a whole number of 8-row groups: box_w * box_n % 8 == 0.
   const int halo = (p.taps_h - 1) * p.dil_h;
-  if (plan->resident_weights && !g_disable_halo && (p.plan_flags & PLB_PLAN_NO_HALO) == 0 &&
-      p.taps_h > 1 && p.stride_h == 1) {
-    long best_rows = -1, best_t = -1;
+  if (!g_disable_halo && (p.plan_flags & PLB_PLAN_NO_HALO) == 0 && p.taps_h > 1 &&
+      p.stride_h == 1) {
+    // Shared-memory fill per pixel tile and channel chunk, the quantity that
+    // bounds a layer whose tensor-core work is short: activation rows plus,
+    // unless the weights are resident, one weight tile per filter tap.
+    const bool res = plan->resident_weights != 0;
+    const long b_tile = res ? 0 : long(bn / (pair ? 2 : 1)) * kStageKBytes;
+    const long base_cost =
+        best_tiles * p.taps_h * p.taps_w * (long(kTileM) * kStageKBytes + b_tile);
+    long best_cost = -1, best_t = -1;
     int hw = 0, hh = 0, hn = 0;
     for (int w = 128; w >= 1; w >>= 1)
       for (int n = 128 / w; n >= 1; n >>= 1) {
@@ -145,27 +230,30 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
         if ((w * n) % 8 != 0 || h + halo > 256 || (w - 1) * p.stride_w + 1 > 256) continue;
         const long tiles = long((p.out_w + w - 1) / w) * ((p.out_h + h - 1) / h) *
                            ((p.out_n + n - 1) / n);
-        const long rows = tiles * w * n * (h + halo);
-        if (best_rows < 0 || rows < best_rows || (rows == best_rows && tiles < best_t)) {
-          best_rows = rows;
+        const long cost =
+            tiles * p.taps_w * (long(w) * n * (h + halo) * kStageKBytes + p.taps_h * b_tile);
+        if (best_cost < 0 || cost < best_cost || (cost == best_cost && tiles < best_t)) {
+          best_cost = cost;
           best_t = tiles;
           hw = w;
           hh = h;
           hn = n;
         }
       }
-    if (best_rows > 0) {
+    if (best_cost > 0) {
       const int a_stage = hw * hn * (hh + halo) * kStageKBytes;
-      const int st = stagesFor(bn, a_stage, true, int(resident_bytes));
-      // worthwhile only if it really loads fewer rows than one box per tap
-      if (st >= 3 && best_rows * p.taps_w < best_tiles * kTileM * long(p.taps_h) * p.taps_w) {
+      const int st = stagesFor(bn, a_stage, res ? 1 : p.taps_h, res, res ? int(resident_bytes) : 0,
+                               pair);
+      // worthwhile only if it really fills less, without much more tensor-core
+      // work (padded tiles), and still leaves a pipeline
+      if (st >= 3 && best_cost < base_cost && best_t * 8 <= best_tiles * 9) {
         plan->halo_rows = halo;
         plan->box_w = hw;
         plan->box_h = hh;
         plan->box_n = hn;
         plan->stages = st;
         plan->tiles = int(best_t * n_tiles);
-        plan->grid = std::min(plan->tiles, sm_count > 0 ? sm_count : 148);
+        plan->grid = grid_for(best_t);
       }
     }
   }
@@ -212,7 +300,7 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
       box[2] = 1;
     } else {
       box[0] = uint32_t(k_elems_per_stage);
-      box[1] = uint32_t(plan.tile_n);
+      box[1] = uint32_t(plan.tile_n / (plan.cta_pair ? 2 : 1));
       box[2] = 1;
     }
     const uint32_t es[3] = {1, 1, 1};
@@ -226,6 +314,9 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   CUtensorMap tout;
   std::memset(&tout, 0, sizeof tout);
   const size_t out_es = p.out_f32 ? 4 : 2;
+  const long long out_stride_h = p.out_stride_h ? p.out_stride_h : (long long)p.out_w * p.ldc;
+  const long long out_stride_n =
+      p.out_stride_n ? p.out_stride_n : (long long)p.out_h * p.out_w * p.ldc;
   // the 32 rows of one epilogue warp as a box over the tile's row order
   const int d2 = halo ? plan.box_n : plan.box_h;
   a.sub_w = std::min(plan.box_w, 32);
@@ -233,11 +324,12 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   const int sub_3 = 32 / (a.sub_w * a.sub_h);
   a.use_tma_store = 0;
   if (!g_disable_tma_store && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
-      (size_t(p.ldc) * out_es) % 16 == 0) {
+      (size_t(p.ldc) * out_es) % 16 == 0 && (size_t(out_stride_h) * out_es) % 16 == 0 &&
+      (size_t(out_stride_n) * out_es) % 16 == 0) {
     uint64_t dims[4] = {uint64_t(p.n_total), 0, 0, 0}, strides[3];
     order(uint64_t(p.out_w), uint64_t(p.out_h), uint64_t(p.out_n), dims + 1);
-    const uint64_t sw = uint64_t(p.ldc) * out_es, sh = uint64_t(p.out_w) * p.ldc * out_es,
-                   sn = uint64_t(p.out_h) * p.out_w * p.ldc * out_es;
+    const uint64_t sw = uint64_t(p.ldc) * out_es, sh = uint64_t(out_stride_h) * out_es,
+                   sn = uint64_t(out_stride_n) * out_es;
     strides[0] = sw;
     strides[1] = halo ? sn : sh;
     strides[2] = halo ? sh : sn;
@@ -273,15 +365,20 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.stride_w = p.stride_w;
   a.flip_h = p.flip_h;
   a.flip_w = p.flip_w;
-  a.group_m = 16;
+  a.group_m = plan.cta_pair ? 8 : 16;  // M tiles (pairs of them) per band
   a.h_outer = halo ? 1 : 0;
   a.a_stage_bytes = plan.box_w * plan.box_n * (plan.box_h + plan.halo_rows) * kStageKBytes;
+  a.b_tiles_per_stage = (halo && !plan.resident_weights) ? p.taps_h : 1;
   a.halo_step_bytes = p.dil_h * plan.box_w * plan.box_n * kStageKBytes;
   a.num_stages = plan.stages;
   const int resident_bytes =
-      plan.resident_weights ? a.taps_h * a.taps_w * a.k_chunks * plan.tile_n * kStageKBytes : 0;
+      plan.resident_weights ? a.taps_h * a.taps_w * a.k_chunks *
+                                  (plan.tile_n / (plan.cta_pair ? 2 : 1)) * kStageKBytes
+                            : 0;
   a.out = p.out;
   a.ldc = p.ldc;
+  a.out_stride_h = out_stride_h;
+  a.out_stride_n = out_stride_n;
   a.addend = p.beta != 0.f ? p.addend : nullptr;
   a.ld_addend = p.ld_addend;
   a.bias = p.bias;
@@ -292,13 +389,25 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.trace = ctx->trace;
 
   const int grid = plan.grid;
-#define PLB_DISPATCH2(BN, RES, HALO)                                                                   \
-  if (p.fp8) return launchInstance<BN, true, false, RES, HALO>(ctx, ta, tb, tout, a, grid, resident_bytes);  \
-  if (p.b_mn) return launchInstance<BN, false, true, RES, HALO>(ctx, ta, tb, tout, a, grid, resident_bytes); \
-  return launchInstance<BN, false, false, RES, HALO>(ctx, ta, tb, tout, a, grid, resident_bytes);
+#define PLB_DISPATCH3(BN, RES, HALO, PAIR)                                                            \
+  if (p.fp8)                                                                                          \
+    return launchInstance<BN, true, false, RES, HALO, PAIR>(ctx, ta, tb, tout, a, grid,               \
+                                                            resident_bytes);                          \
+  if (p.b_mn)                                                                                         \
+    return launchInstance<BN, false, true, RES, HALO, PAIR>(ctx, ta, tb, tout, a, grid,               \
+                                                            resident_bytes);                          \
+  return launchInstance<BN, false, false, RES, HALO, PAIR>(ctx, ta, tb, tout, a, grid, resident_bytes);
+#define PLB_DISPATCH2(BN, RES, HALO)     \
+  if (plan.cta_pair) {                   \
+    PLB_DISPATCH3(BN, RES, HALO, true)   \
+  } else {                               \
+    PLB_DISPATCH3(BN, RES, HALO, false)  \
+  }
 #define PLB_DISPATCH(BN)                       \
-  if (halo) {                                  \
+  if (halo && plan.resident_weights) {         \
     PLB_DISPATCH2(BN, true, true)              \
+  } else if (halo) {                           \
+    PLB_DISPATCH2(BN, false, true)             \
   } else if (plan.resident_weights) {          \
     PLB_DISPATCH2(BN, true, false)             \
   } else {                                     \
@@ -312,6 +421,7 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   }
 #undef PLB_DISPATCH
 #undef PLB_DISPATCH2
+#undef PLB_DISPATCH3
   return fail(PLB_ERR_INVALID_OPTION, "unsupported tile_n in plan");
 }
 

@@ -22,13 +22,14 @@
 //                 tensor copy costs a thread a few hundred cycles, so a single
 //                 producer cannot keep the tensor core fed on narrow tiles.
 //   warp 3        issues tcgen05.mma with fp32 accumulators in tensor memory.
-//   warps 4..11   epilogue, two groups of four warps: drain a finished
-//                 accumulator (tcgen05.ld, the next 32 columns in flight while
-//                 the current ones are processed), scale / add / cast, stage
-//                 32 rows x 128 bytes per warp in shared memory and hand them
+//   warps 4..19   epilogue, two groups of eight warps: drain a finished
+//                 accumulator (tcgen05.ld), scale / add / cast, stage 32 rows
+//                 x 128 bytes per pair of warps in shared memory and hand them
 //                 to a TMA store (coalesced, clipped to the tensor by the
 //                 hardware); plain vector stores are the fallback when the
-//                 output cannot be described to TMA.
+//                 output cannot be described to TMA.  The per-warp chain
+//                 load -> convert -> stage -> store is latency bound, so the
+//                 epilogue's throughput comes from the number of warps.
 // Two accumulators alternate so the epilogue of one tile overlaps the main loop
 // of the next; accumulator g is always drained by epilogue group g, so a group
 // has two tile periods for its tile.
@@ -44,7 +45,7 @@ namespace plb {
 
 constexpr int kTileM = 128;        // pixels (rows) per tile = TMEM lanes
 constexpr int kStageKBytes = 128;  // bytes of K per pipeline stage row (one swizzle span)
-constexpr int kIgemmThreads = 384;
+constexpr int kIgemmThreads = 640;
 constexpr int kIgemmProducers = PLB_IGEMM_PRODUCERS;
 constexpr int kIgemmMmaWarp = 3;
 constexpr int kEpiStagingBytes = 8 * 4096;  // 8 epilogue warps x (32 rows x 128 B)
@@ -60,6 +61,7 @@ struct IgemmArgs {
   // serves all taps_h vertical taps (row r starts halo_step_bytes * r further on).
   int halo_step_bytes;
   int a_stage_bytes;        // bytes of activations per stage
+  int b_tiles_per_stage;    // streamed weight tiles per stage (taps_h with a halo strip, else 1)
   // ---- N side ---------------------------------------------------------------
   int n_tiles;  // tiles of BN output channels
   int n_total;  // valid output channels
@@ -74,7 +76,8 @@ struct IgemmArgs {
   int num_stages;  // pipeline depth (<= kIgemmMaxStages)
   // ---- epilogue ---------------------------------------------------------------
   void *out;
-  long long ldc;  // elements between consecutive output pixels
+  long long ldc;  // elements between consecutive output pixels (along w)
+  long long out_stride_h, out_stride_n;  // elements between output rows / images
   const void *addend;
   long long ld_addend;
   const float *bias;
@@ -99,28 +102,32 @@ struct IgemmArgs {
 #endif
 
 constexpr int kIgemmMaxStages = 8;
-constexpr int kIgemmBarrierBytes = 256;
+constexpr int kIgemmBarrierBytes = 384;
 constexpr int kIgemmSmemLimit = 227 * 1024;
 
 // Shared memory: [stages][resident weights][epilogue staging][barriers], after
 // up to 1023 bytes of alignment slack.  A stage holds the 128 x 128-byte
 // activation tile and, unless the weights are resident, the BN x 128-byte
 // weight tile of one K step.
-template <int BN, bool kResB>
+// With a CTA pair (k2Cta) each CTA holds half of the weight tile's rows.
+template <int BN, bool kResB, bool k2Cta = false>
 struct IgemmSmem {
   static constexpr int kABytes = kTileM * kStageKBytes;  // without a halo
-  static constexpr int kBBytes = BN * kStageKBytes;
+  static constexpr int kBBytes = (BN / (k2Cta ? 2 : 1)) * kStageKBytes;
   static constexpr int kFixedBytes = kEpiStagingBytes + kIgemmBarrierBytes + 1024;
-  __host__ __device__ static constexpr int stageBytes(int a_stage_bytes) {
-    return a_stage_bytes + (kResB ? 0 : kBBytes);
+  // b_tiles: streamed weight tiles per stage (1, or with a halo strip one per
+  // vertical filter tap)
+  __host__ __device__ static constexpr int stageBytes(int a_stage_bytes, int b_tiles) {
+    return a_stage_bytes + (kResB ? 0 : b_tiles * kBBytes);
   }
   // deepest pipeline that fits beside `resident` bytes of weights
-  static constexpr int stagesFor(int a_stage_bytes, int resident) {
-    const int n = (kIgemmSmemLimit - kFixedBytes - resident) / stageBytes(a_stage_bytes);
+  static constexpr int stagesFor(int a_stage_bytes, int b_tiles, int resident) {
+    const int n =
+        (kIgemmSmemLimit - kFixedBytes - resident) / stageBytes(a_stage_bytes, b_tiles);
     return n > kIgemmMaxStages ? kIgemmMaxStages : n;
   }
-  static constexpr int totalBytes(int a_stage_bytes, int stages, int resident) {
-    return stages * stageBytes(a_stage_bytes) + resident + kFixedBytes;
+  static constexpr int totalBytes(int a_stage_bytes, int b_tiles, int stages, int resident) {
+    return stages * stageBytes(a_stage_bytes, b_tiles) + resident + kFixedBytes;
   }
 };
 
@@ -134,29 +141,43 @@ struct IgemmSmem {
 //       Used when there is a single N tile and the weights fit (small filters
 //       with few channels), where re-fetching them per pixel tile would cost
 //       as much shared-memory fill bandwidth as the activations themselves.
-// kHalo: (with kResB) one activation strip per (horizontal tap, channel chunk)
-//       feeds all vertical taps: the strip of tap row r is the same shared
-//       memory shifted by whole 8-row groups, which the descriptor's start
-//       address can express.  Cuts the activation traffic of a KxK filter K-fold.
-template <int BN, bool kFp8, bool kBMn, bool kResB, bool kHalo>
+// kHalo: one activation strip per (horizontal tap, channel chunk) feeds all
+//       vertical taps: the strip of tap row r is the same shared memory shifted
+//       by whole 8-row groups, which the descriptor's start address can express.
+//       Cuts the activation traffic of a KxK filter K-fold.  Streamed weights
+//       (no kResB) then travel as taps_h tiles per stage.
+// k2Cta: the kernel is launched in clusters of two CTAs that share one
+//       tcgen05.mma of 256 rows (cta_group::2): the CTA of rank r works on M
+//       tile 2 * pair + r, loads its own activations and rows
+//       [r * BN/2, (r+1) * BN/2) of the weight tile, and drains its own
+//       accumulator.  Rank 0 issues the MMAs; its "full" barriers count the
+//       bytes of both CTAs' copies, its "accumulator free" barriers the
+//       epilogue threads of both, and its commits release the stages and
+//       publish the accumulators in both CTAs.  Halving the weight rows per
+//       CTA halves their shared-memory fill and operand fetch per FLOP, and
+//       the instruction is twice as large, which matters because a
+//       128-row instruction is bound by operand fetch, not by arithmetic.
+template <int BN, bool kFp8, bool kBMn, bool kResB, bool kHalo, bool k2Cta>
 __global__ void __launch_bounds__(kIgemmThreads, 1)
 igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
              const __grid_constant__ CUtensorMap tm_out, const IgemmArgs args) {
-  using S = IgemmSmem<BN, kResB>;
+  using S = IgemmSmem<BN, kResB, k2Cta>;
+  static_assert(!k2Cta || !kBMn || BN >= 128, "a CTA needs a whole 64-column block of MN-major B");
+  const uint32_t cta_rank = k2Cta ? cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;
   constexpr int kMaxStages = kIgemmMaxStages;
   const int kStages = args.num_stages;
   constexpr int P = kIgemmProducers;
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators
   static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "");
   static_assert(!(kFp8 && kBMn), "MN-major B is implemented for fp16 only");
-  static_assert(!kHalo || kResB, "halo mode keeps the weights resident");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // K steps: every (r, s, kc); pipeline steps: in halo mode one per (s, kc)
   const int k_iters = args.taps_h * args.taps_w * args.k_chunks;
   const int p_iters = kHalo ? args.taps_w * args.k_chunks : k_iters;
-  const int stage_bytes = S::stageBytes(args.a_stage_bytes);
+  const int stage_bytes = S::stageBytes(args.a_stage_bytes, args.b_tiles_per_stage);
   const uint32_t resb_base = smem_base + kStages * stage_bytes;
   const uint32_t staging_base = resb_base + (kResB ? k_iters * S::kBBytes : 0);
   const uint32_t bar_base = staging_base + kEpiStagingBytes;
@@ -172,6 +193,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   volatile uint32_t *tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t *>(bar_gen + 8 * (2 * kMaxStages + 6));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(bar_gen + 8 * (2 * kMaxStages + 7));
+  // epilogue warp pairs: "staging buffer free" and "staging buffer written", 8 pairs each
+  auto pair_free_bar = [&](int pr) { return bar_base + 8u * (2 * kMaxStages + 8 + pr); };
+  auto pair_staged_bar = [&](int pr) { return bar_base + 8u * (2 * kMaxStages + 16 + pr); };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -183,10 +207,14 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 128);
+      mbar_init(tmem_empty_bar(a), k2Cta ? 512 : 256);  // a group's epilogue threads (of both CTAs)
     }
     mbar_init(drain_bar, 1);
     mbar_init(resb_bar, 1);
+    for (int pr = 0; pr < 8; ++pr) {
+      mbar_init(pair_free_bar(pr), 2);    // one arrival per warp of the pair
+      mbar_init(pair_staged_bar(pr), 2);
+    }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tm_a);
@@ -194,16 +222,30 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     if (args.use_tma_store) tma_prefetch_desc(&tm_out);
   }
   if (warp == kIgemmMmaWarp) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if constexpr (k2Cta) {
+      tmem_alloc_pair(tmem_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  // the other CTA's copies and arrivals must find initialised barriers
+  if constexpr (k2Cta) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  // Work units: output tiles, or with a CTA pair, pairs of M tiles (the odd
+  // last one is padded: its copies read zeros and its stores are clipped).
   const int m_tiles = args.tiles_w * args.tiles_h * args.tiles_n;
-  const int total_tiles = m_tiles * args.n_tiles;
+  const int m_units = k2Cta ? (m_tiles + 1) / 2 : m_tiles;
+  const int total_tiles = m_units * args.n_tiles;
+  const int first_unit = k2Cta ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int unit_stride = k2Cta ? int(gridDim.x >> 1) : int(gridDim.x);
+  // barriers of the CTA that issues the MMAs, as cluster addresses
+  auto lead_bar = [&](uint32_t bar) { return k2Cta ? map_to_cta(bar, 0) : bar; };
   constexpr int kElemsPerStage = kFp8 ? 128 : 64;
 
   // tile index -> (m tile, n tile): bands of group_m M tiles, M fastest inside a band
@@ -212,9 +254,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     const int band = tile / band_tiles;
     const int within = tile - band * band_tiles;
     const int m0 = band * args.group_m;
-    const int gm = min(args.group_m, m_tiles - m0);
+    const int gm = min(args.group_m, m_units - m0);
     m_idx = m0 + within % gm;
     n_idx = within / gm;
+    if constexpr (k2Cta) m_idx = 2 * m_idx + int(cta_rank);
   };
 
   // M tile index -> first pixel of the tile; tile row -> pixel inside the tile
@@ -258,22 +301,37 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       auto load_b = [&](uint32_t dst, uint32_t bar, int r, int s, int kc, int n_col) {
         const int b_tap = (args.flip_h ? args.taps_h - 1 - r : r) * args.taps_w +
                           (args.flip_w ? args.taps_w - 1 - s : s);
+        // a CTA of a pair loads its half of the tile's N rows / columns
+        constexpr int kMyN = k2Cta ? BN / 2 : BN;
+        const int my_col = n_col + int(cta_rank) * kMyN;
         if constexpr (kBMn) {
           // K rows x 64 columns per block; blocks of 64 columns are 64 rows apart
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_3d(dst + j * (64 * kStageKBytes), &tm_b, bar, n_col + j * 64, kc * 64, b_tap);
+          for (int j = 0; j < kMyN / 64; ++j) {
+            if constexpr (k2Cta)
+              tma_load_3d_pair(dst + j * (64 * kStageKBytes), &tm_b, bar, my_col + j * 64, kc * 64,
+                               b_tap);
+            else
+              tma_load_3d(dst + j * (64 * kStageKBytes), &tm_b, bar, my_col + j * 64, kc * 64, b_tap);
+          }
         } else {
-          tma_load_3d(dst, &tm_b, bar, kc * kElemsPerStage, n_col, b_tap);
+          if constexpr (k2Cta)
+            tma_load_3d_pair(dst, &tm_b, bar, kc * kElemsPerStage, my_col, b_tap);
+          else
+            tma_load_3d(dst, &tm_b, bar, kc * kElemsPerStage, my_col, b_tap);
         }
       };
+      // the barriers that count copied bytes are those of the MMA-issuing CTA,
+      // which alone announces the byte count (both CTAs' shares)
+      constexpr uint32_t kPairFactor = k2Cta ? 2u : 1u;
       if constexpr (kResB) {
-        if (me == 0 && int(blockIdx.x) < total_tiles) {
+        if (me == 0 && first_unit < total_tiles) {
           // single N tile: every tile of this CTA uses the same weights
-          mbar_expect_tx(resb_bar, uint32_t(k_iters) * S::kBBytes);
+          if (leader) mbar_expect_tx(resb_bar, kPairFactor * uint32_t(k_iters) * S::kBBytes);
+          const uint32_t resb_bar_lead = lead_bar(resb_bar);
           int r = 0, s = 0, kc = 0;
           for (int it = 0; it < k_iters; ++it) {
-            load_b(resb_base + it * S::kBBytes, resb_bar, r, s, kc, 0);
+            load_b(resb_base + it * S::kBBytes, resb_bar_lead, r, s, kc, 0);
             if (++kc == args.k_chunks) {
               kc = 0;
               if (++s == args.taps_w) {
@@ -284,7 +342,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           }
         }
       }
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_unit; tile < total_tiles && ok; tile += unit_stride) {
         int m_idx, n_idx;
         tile_coords(tile, m_idx, n_idx);
         int w0, h0, n0;
@@ -302,14 +360,27 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             }
             if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
             const uint32_t a_dst = smem_base + stage * stage_bytes;
-            mbar_expect_tx(full_bar(stage), uint32_t(stage_bytes));
+            if (leader) mbar_expect_tx(full_bar(stage), kPairFactor * uint32_t(stage_bytes));
+            const uint32_t full = lead_bar(full_bar(stage));
             const int cw = w_base + s * args.dil_w, ch = h_base + r * args.dil_h;
-            if (args.h_outer)
-              tma_load_4d(a_dst, &tm_a, full_bar(stage), kc * kElemsPerStage, cw, n0, ch);
-            else
-              tma_load_4d(a_dst, &tm_a, full_bar(stage), kc * kElemsPerStage, cw, ch, n0);
-            if constexpr (!kResB)
-              load_b(a_dst + args.a_stage_bytes, full_bar(stage), r, s, kc, n_col);
+            if constexpr (k2Cta) {
+              if (args.h_outer)
+                tma_load_4d_pair(a_dst, &tm_a, full, kc * kElemsPerStage, cw, n0, ch);
+              else
+                tma_load_4d_pair(a_dst, &tm_a, full, kc * kElemsPerStage, cw, ch, n0);
+            } else {
+              if (args.h_outer)
+                tma_load_4d(a_dst, &tm_a, full, kc * kElemsPerStage, cw, n0, ch);
+              else
+                tma_load_4d(a_dst, &tm_a, full, kc * kElemsPerStage, cw, ch, n0);
+            }
+            if constexpr (!kResB) {
+              // with a halo strip the stage carries the weight tiles of every filter row
+              const int row_taps = kHalo ? args.taps_h : 1;
+              for (int rr = 0; rr < row_taps; ++rr)
+                load_b(a_dst + args.a_stage_bytes + rr * S::kBBytes, full, kHalo ? rr : r, s, kc,
+                       n_col);
+            }
             if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
             stage += P;
             if (stage >= kStages) {
@@ -333,9 +404,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       // them, so this costs one try_wait per stage.  Stage s was last filled
       // by K step g = the largest g < total with g mod kStages == s, in phase
       // (g / kStages) & 1; a stage that was never used is skipped.
-      if (me == 0) {
-        const int my_tiles = (total_tiles > int(blockIdx.x))
-                                 ? (total_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x)
+      // (With a CTA pair the barriers live in the MMA-issuing CTA, which waits
+      // for both CTAs' copies; the other CTA cannot leave before the cluster
+      // barrier at the end of the kernel.)
+      if (me == 0 && leader) {
+        const int my_tiles = (total_tiles > first_unit)
+                                 ? (total_tiles - first_unit + unit_stride - 1) / unit_stride
                                  : 0;
         const long long total_steps = (long long)my_tiles * p_iters;
         if (kResB && my_tiles > 0) {
@@ -363,8 +437,16 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     }
   } else if (warp == kIgemmMmaWarp) {
     // ===================== MMA issuer =====================
-    if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc(kTileM, BN, 0, 0, false, kBMn);
+    // (with a CTA pair only the CTA of rank 0 issues)
+    if (leader && elect_one()) {
+      constexpr uint32_t idesc = make_idesc(k2Cta ? 2 * kTileM : kTileM, BN, 0, 0, false, kBMn);
+      // completion of the MMAs issued so far -> barrier (in both CTAs of a pair)
+      auto commit = [&](uint32_t bar) {
+        if constexpr (k2Cta)
+          umma_commit_pair(bar, uint16_t(3));
+        else
+          umma_commit(bar);
+      };
       const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
       // B tiles: resident ones start at resb_base, streamed ones follow the
       // activations inside their stage
@@ -374,21 +456,23 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                : make_smem_desc(kResB ? resb_base : smem_base + uint32_t(args.a_stage_bytes), 16,
                                 1024);
       [[maybe_unused]] const uint64_t halo_step16 = uint64_t(uint32_t(args.halo_step_bytes) >> 4);
+      // weight tile of the next filter row: resident tiles are indexed (r, s, kc),
+      // streamed ones follow one another inside the stage
       [[maybe_unused]] const uint64_t b_row_step16 =
-          uint64_t(uint32_t(args.taps_w * args.k_chunks) * (S::kBBytes >> 4));
+          uint64_t(uint32_t(kResB ? args.taps_w * args.k_chunks : 1) * (S::kBBytes >> 4));
       int stage = 0;
       uint32_t phase = 0;
       uint32_t acc_phase[2] = {0, 0};
       int local_tile = 0;
       bool ok = true;
       [[maybe_unused]] int trace_slot = 0;
-      if (kResB && int(blockIdx.x) < total_tiles) {
+      if (kResB && first_unit < total_tiles) {
         if (!mbar_wait(resb_bar, 0, abort_flag)) {
           atomicCAS(args.status, kStatusOk, kStatusMmaTimeout);
           ok = false;
         }
       }
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+      for (int tile = first_unit; tile < total_tiles && ok; tile += unit_stride, ++local_tile) {
         const int acc = local_tile & 1;
         PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
         // wait for the epilogue to have drained this accumulator
@@ -417,7 +501,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           const uint32_t stage_off16 = uint32_t(stage * stage_bytes) >> 4;
           uint64_t a_desc = a_desc0 + stage_off16;
           uint64_t b_desc;
-          if constexpr (kHalo)
+          if constexpr (kHalo && kResB)
             b_desc = b_desc0 + uint64_t((s_tap * args.k_chunks + kc) * (S::kBBytes >> 4));
           else if constexpr (kResB)
             b_desc = b_desc0 + uint64_t(it * (S::kBBytes >> 4));
@@ -432,7 +516,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
               const uint64_t a_k = a_desc + uint64_t(k * 2);
               const uint64_t b_k =
                   b_desc + uint64_t(kBMn ? k * ((16 * kStageKBytes) >> 4) : k * 2);
-              umma_ss<kFp8>(d_tmem, a_k, b_k, idesc, (it | r | k) != 0 ? 1u : 0u);
+              if constexpr (k2Cta)
+                umma_ss_pair<kFp8>(d_tmem, a_k, b_k, idesc, (it | r | k) != 0 ? 1u : 0u);
+              else
+                umma_ss<kFp8>(d_tmem, a_k, b_k, idesc, (it | r | k) != 0 ? 1u : 0u);
             }
             if constexpr (kHalo) {
               // next filter row: the strip shifted by whole 8-row groups; its
@@ -441,7 +528,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
               b_desc += b_row_step16;
             }
           }
-          umma_commit(empty_bar(stage));  // frees the stage when these MMAs retire
+          commit(empty_bar(stage));  // frees the stage when these MMAs retire
           PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
           if (++stage == kStages) {
             stage = 0;
@@ -452,10 +539,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             ++s_tap;
           }
         }
-        if (ok) umma_commit(tmem_full_bar(acc));
+        if (ok) commit(tmem_full_bar(acc));
       }
       // make sure nothing is still executing before TMEM is released
-      umma_commit(drain_bar);
+      if constexpr (k2Cta)
+        umma_commit_pair(drain_bar, uint16_t(1));
+      else
+        umma_commit(drain_bar);
       const long long start = clock64();
       while (!mbar_try_wait(drain_bar, 0)) {
         if (clock64() - start > kWaitCycleLimit) {
@@ -465,8 +555,18 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       }
     }
   } else if (warp >= 4) {
-    // ===================== epilogue (warps 4..11) =====================
-    const int group = (warp - 4) >> 2;       // drains accumulator `group`
+    // ===================== epilogue (warps 4..19) =====================
+    // Accumulator g is drained by the eight warps of group g.  A warp can read
+    // the 32 TMEM lanes (tile rows) [32*(warp%4), +32); the two warps that share
+    // a lane quarter split every block of 64 columns between them (columns
+    // [0,32) and [32,64) of the block) and stage their halves of the same
+    // 32-row x 128-byte buffer, which one of them then hands to a tensor store.
+    // The two synchronise through two mbarriers (bounded waits, like every wait
+    // in this kernel): "buffer free" before writing, "buffer staged" before the
+    // store; the storing role alternates so that both wait for their own stores
+    // in turn.
+    const int group = (warp - 4) >> 3;       // drains accumulator `group`
+    const int half = ((warp - 4) >> 2) & 1;  // which 32 columns of each 64-column block
     const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
     const int row = quarter * 32 + lane;     // tile row handled by this thread
     uint32_t acc_phase = 0;
@@ -475,22 +575,43 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     // origin of this warp's 32 rows inside the tile's pixel box
     int qw, qh, qn;
     row_pixel(quarter * 32, qw, qh, qn);
-    const uint32_t buf = staging_base + uint32_t(warp - 4) * 4096u;  // this warp's staged rows
+    const int pair = group * 4 + quarter;    // staging buffer and named barrier of the two warps
+    const uint32_t buf = staging_base + uint32_t(pair) * 4096u;
     const uint32_t row_addr = buf + uint32_t(lane) * 128u;
     const bool tma_store = args.use_tma_store != 0;
     const bool out_f32 = args.out_is_f32 != 0;
+    // fp32 rows fill the 128-byte staged row with 32 columns: the `half == 1`
+    // warps then leave the work to their partners
+    const bool idle = tma_store && out_f32 && half == 1;
     const bool stamp = threadIdx.x == 128;
     const int acc = group;
     int local_tile = group;
-    for (int tile = int(blockIdx.x) + group * int(gridDim.x); tile < total_tiles;
-         tile += 2 * int(gridDim.x), local_tile += 2) {
+    uint32_t blocks_done = 0;                // 64-column blocks so far (selects the storing warp)
+    uint32_t pair_phase = 0;                 // both barriers complete once per block
+    bool pair_ok = true;
+    // arrive (one lane per warp, after the warp's own work is ordered) and wait
+    auto pair_sync = [&](uint32_t bar) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+      if (!mbar_wait(bar, pair_phase, abort_flag)) {
+        atomicCAS(args.status, kStatusOk, kStatusEpilogueTimeout);
+        pair_ok = false;
+      }
+    };
+    const uint32_t acc_free_bar = lead_bar(tmem_empty_bar(acc));
+    for (int tile = first_unit + group * unit_stride; tile < total_tiles;
+         tile += 2 * unit_stride, local_tile += 2) {
       int m_idx, n_idx;
       tile_coords(tile, m_idx, n_idx);
       int w0, h0, n0;
       tile_origin(m_idx, w0, h0, n0);
       const int ow = w0 + rw, oh = h0 + rh, on = n0 + rn;
       const bool row_ok = ow < args.out_w && oh < args.out_h && on < args.out_n;
+      // element offset of this row's output pixel; the addend is dense in pixels
       const long long pixel = (static_cast<long long>(on) * args.out_h + oh) * args.out_w + ow;
+      const long long out_off = static_cast<long long>(on) * args.out_stride_n +
+                                static_cast<long long>(oh) * args.out_stride_h +
+                                static_cast<long long>(ow) * args.ldc;
       if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 0);
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag)) {
         atomicCAS(args.status, kStatusOk, kStatusEpilogueTimeout);
@@ -502,15 +623,22 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       const uint32_t t_addr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       const int col_base = n_idx * BN;
       const bool box_ok = w0 + qw < args.out_w && h0 + qh < args.out_h && n0 + qn < args.out_n;
+      auto release_accumulator = [&]() {
+        tc_fence_before_sync();
+        if constexpr (k2Cta)
+          mbar_arrive_cluster(acc_free_bar);
+        else
+          mbar_arrive(acc_free_bar);
+      };
+      if (idle) {
+        release_accumulator();
+        continue;
+      }
 
-      // 32 accumulator columns [c, c + 32) of this thread's row: scale / add /
-      // cast and store (or stage for the tensor store)
-      auto process = [&](const uint32_t (&v)[32], const int c) {
-        [[maybe_unused]] const bool fine = stamp && local_tile == 2;
-        if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 0);
+      // 32 accumulator columns [c, c + 32) of this thread's row: scale / add / cast
+      auto finish = [&](const uint32_t (&v)[32], float (&f)[32], const int c) {
         const int col0 = col_base + c;
         const int valid = min(32, args.n_total - col0);  // may be <= 0 on a padded N tile
-        float f[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * args.alpha;
         if (args.bias != nullptr) {
@@ -531,125 +659,139 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
               if (j < valid) f[j] += args.beta * __half2float(src[j]);
           }
         }
-        if (tma_store) {
-          // 32 columns of this row go to its 128-byte staged row: fp32 fills the
-          // row, half fills half of it (two passes per store).  16-byte pieces
-          // are XOR-swizzled with the row index, the pattern the tensor map uses.
-          const int pass = out_f32 ? 0 : ((c >> 5) & 1);
-          if (pass == 0) {
-            // the previous store from this buffer must have read it
-            if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 1);
-            if (lane == 0) tma_store_wait_read<0>();
-            __syncwarp();
-          }
-          if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 2);
-          if (out_f32) {
+      };
+      // plain vector stores of 32 finished columns (output not describable to TMA)
+      auto store_direct = [&](const float (&f)[32], const int c) {
+        const int col0 = col_base + c;
+        const int valid = min(32, args.n_total - col0);
+        if (!row_ok || valid <= 0) return;
+        if (out_f32) {
+          float *dst = static_cast<float *>(args.out) + out_off + col0;
+          if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+            // whole 32-byte sectors per lane
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              st_shared_v4(row_addr + (uint32_t(j ^ (lane & 7)) << 4), __float_as_uint(f[4 * j]),
-                           __float_as_uint(f[4 * j + 1]), __float_as_uint(f[4 * j + 2]),
-                           __float_as_uint(f[4 * j + 3]));
+            for (int j = 0; j < 32; j += 8)
+              st_global_v8(dst + j, __float_as_uint(f[j]), __float_as_uint(f[j + 1]),
+                           __float_as_uint(f[j + 2]), __float_as_uint(f[j + 3]),
+                           __float_as_uint(f[j + 4]), __float_as_uint(f[j + 5]),
+                           __float_as_uint(f[j + 6]), __float_as_uint(f[j + 7]));
+          } else if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4 *>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              __half2 h0 = __floats2half2_rn(f[8 * j], f[8 * j + 1]);
-              __half2 h1 = __floats2half2_rn(f[8 * j + 2], f[8 * j + 3]);
-              __half2 h2 = __floats2half2_rn(f[8 * j + 4], f[8 * j + 5]);
-              __half2 h3 = __floats2half2_rn(f[8 * j + 6], f[8 * j + 7]);
-              st_shared_v4(row_addr + (uint32_t((pass * 4 + j) ^ (lane & 7)) << 4),
-                           *reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
-                           *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
-            }
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) dst[j] = f[j];
           }
-          const bool last_pass = out_f32 || pass == 1 || c + 32 >= BN;
-          if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 3);
-          if (last_pass) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 4);
-            if (lane == 0) {
-              const int store_col = col_base + (out_f32 ? c : (c & ~63));
-              // a box that starts outside the tensor has nothing to write
-              if (store_col < args.n_total && box_ok) {
-                if (args.h_outer)
-                  tma_store_4d(&tm_out, buf, store_col, w0 + qw, n0 + qn, h0 + qh);
-                else
-                  tma_store_4d(&tm_out, buf, store_col, w0 + qw, h0 + qh, n0 + qn);
-              }
-              tma_store_commit();
+        } else {
+          __half *dst = static_cast<__half *>(args.out) + out_off + col0;
+          if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+              pk[j] = *reinterpret_cast<uint32_t *>(&h);
             }
-            if (fine) PLB_TRACE_STAMP(2, 2048 + (c >> 5) * 8 + 5);
-          }
-        } else if (row_ok && valid > 0) {
-          if (out_f32) {
-            float *dst = static_cast<float *>(args.out) + pixel * args.ldc + col0;
-            if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
-              // whole 32-byte sectors per lane
-#pragma unroll
-              for (int j = 0; j < 32; j += 8)
-                st_global_v8(dst + j, __float_as_uint(f[j]), __float_as_uint(f[j + 1]),
-                             __float_as_uint(f[j + 2]), __float_as_uint(f[j + 3]),
-                             __float_as_uint(f[j + 4]), __float_as_uint(f[j + 5]),
-                             __float_as_uint(f[j + 6]), __float_as_uint(f[j + 7]));
-            } else if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4 *>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+              st_global_v8(dst, pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]);
+              st_global_v8(dst + 16, pk[8], pk[9], pk[10], pk[11], pk[12], pk[13], pk[14], pk[15]);
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < valid) dst[j] = f[j];
+              for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<uint4 *>(dst + 8 * j) =
+                    make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
             }
           } else {
-            __half *dst = static_cast<__half *>(args.out) + pixel * args.ldc + col0;
-            if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-              uint32_t pk[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
-                pk[j] = *reinterpret_cast<uint32_t *>(&h);
-              }
-              if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
-                // whole 32-byte sectors per lane
-                st_global_v8(dst, pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]);
-                st_global_v8(dst + 16, pk[8], pk[9], pk[10], pk[11], pk[12], pk[13], pk[14], pk[15]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  *reinterpret_cast<uint4 *>(dst + 8 * j) =
-                      make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < valid) dst[j] = __float2half_rn(f[j]);
-            }
+            for (int j = 0; j < 32; ++j)
+              if (j < valid) dst[j] = __float2half_rn(f[j]);
           }
         }
       };
-
-      // Two register buffers: while one block of 32 columns is processed the
-      // load of the next is in flight (tcgen05.wait::ld covers all loads issued
-      // so far, so it is only executed between a load and the use of its data).
-      uint32_t va[32], vb[32];
-      __syncwarp();
-      tmem_ld_32x32(t_addr, va);
-#pragma unroll
-      for (int c = 0; c < BN; c += 64) {
-        tmem_ld_wait_for(va);
-        tmem_ld_32x32(t_addr + c + 32, vb);
-        process(va, c);
-        tmem_ld_wait_for(vb);
-        if (c + 64 < BN) {
-          tmem_ld_32x32(t_addr + c + 64, va);
-        } else {
-          // the accumulator is fully read: hand it back before the last stores
-          tc_fence_before_sync();
-          mbar_arrive(tmem_empty_bar(acc));
-          if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 2);
+      // issue (lane 0) the tensor store of the staged buffer: columns [store_col, +128 bytes)
+      auto store_staged = [&](const int store_col) {
+        if (lane == 0) {
+          // a box that starts outside the tensor has nothing to write
+          if (store_col < args.n_total && box_ok) {
+            if (args.h_outer)
+              tma_store_4d(&tm_out, buf, store_col, w0 + qw, n0 + qn, h0 + qh);
+            else
+              tma_store_4d(&tm_out, buf, store_col, w0 + qw, h0 + qh, n0 + qn);
+          }
+          tma_store_commit();
         }
-        process(vb, c + 32);
+      };
+
+      uint32_t v[32];
+      float f[32];
+      if (!tma_store) {
+        // each warp stores its own 32 columns of every 64-column block
+#pragma unroll 1
+        for (int c = half * 32; c < BN; c += 64) {
+          __syncwarp();
+          tmem_ld_32x32(t_addr + c, v);
+          tmem_ld_wait_for(v);
+          if (c + 64 >= BN) release_accumulator();
+          finish(v, f, c);
+          store_direct(f, c);
+        }
+      } else if (out_f32) {
+        // (half == 0 warps only) one 32-column chunk per staged buffer and store
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          __syncwarp();
+          tmem_ld_32x32(t_addr + c, v);
+          tmem_ld_wait_for(v);
+          if (c + 32 >= BN) release_accumulator();
+          finish(v, f, c);
+          if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the buffer
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(row_addr + (uint32_t(j ^ (lane & 7)) << 4), __float_as_uint(f[4 * j]),
+                         __float_as_uint(f[4 * j + 1]), __float_as_uint(f[4 * j + 2]),
+                         __float_as_uint(f[4 * j + 3]));
+          fence_proxy_async_smem();
+          __syncwarp();
+          store_staged(col_base + c);
+        }
+      } else {
+        // half output: this warp's 32 columns are one 64-byte half of the staged
+        // rows; 16-byte pieces are XOR-swizzled with the row index, the pattern
+        // the tensor map uses
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 64, ++blocks_done) {
+          __syncwarp();
+          tmem_ld_32x32(t_addr + c + half * 32, v);
+          tmem_ld_wait_for(v);
+          if (c + 64 >= BN) release_accumulator();
+          finish(v, f, c + half * 32);
+          // the warp that stored the previous block waits until that store has
+          // read the buffer; then both may overwrite it
+          const bool stored_last = ((blocks_done + 1u) & 1u) == uint32_t(half);
+          const bool stores_now = (blocks_done & 1u) == uint32_t(half);
+          if (stored_last && lane == 0) tma_store_wait_read<0>();
+          pair_sync(pair_free_bar(pair));  // buffer free
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __half2 h0 = __floats2half2_rn(f[8 * j], f[8 * j + 1]);
+            __half2 h1 = __floats2half2_rn(f[8 * j + 2], f[8 * j + 3]);
+            __half2 h2 = __floats2half2_rn(f[8 * j + 4], f[8 * j + 5]);
+            __half2 h3 = __floats2half2_rn(f[8 * j + 6], f[8 * j + 7]);
+            st_shared_v4(row_addr + (uint32_t((half * 4 + j) ^ (lane & 7)) << 4),
+                         *reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                         *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+          }
+          fence_proxy_async_smem();
+          pair_sync(pair_staged_bar(pair));  // buffer staged by both warps
+          pair_phase ^= 1u;
+          if (!pair_ok) break;
+          if (stores_now) store_staged(col_base + c);
+        }
+        if (!pair_ok) break;
       }
+      if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 2);
       if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 3);
     }
     // all of this thread's stores must be complete before the CTA exits
@@ -658,9 +800,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
 
   tc_fence_before_sync();
   __syncthreads();
+  // Neither CTA of a pair may go away while the other can still touch its
+  // barriers, shared memory or tensor memory.
+  if constexpr (k2Cta) cluster_sync_all();
   if (warp == kIgemmMmaWarp) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (k2Cta)
+      tmem_dealloc_pair(tmem_base, kTmemCols);
+    else
+      tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 

@@ -56,7 +56,14 @@ plb_plan planFor(const ConvParams &params, const poplar::OptionFlags &options, i
     const auto it = cache->impl->plans.find(key);
     if (it != cache->impl->plans.end()) return it->second;
   }
-  const plb_conv_params flat = internal::toPlb(params);
+  // A convolution whose input is dilated is the backward pass of a strided
+  // layer: it is planned (and run) in that layer's forward terms.
+  const bool dilatedInput =
+      std::any_of(params.inputTransform.dilation.begin(), params.inputTransform.dilation.end(),
+                  [](unsigned d) { return d != 1; });
+  const plb_conv_params flat =
+      internal::toPlb(dilatedInput ? getGradientParams(params).canonicalize() : params);
+  if (dilatedInput && pass != PLB_PASS_TRAINING_WU) pass = PLB_PASS_TRAINING_BWD;
   const plb_conv_options opt = parsed.toPlb();
   plb_plan plan{};
   poplar::detail::check(plb_conv_plan(&flat, &opt, pass, &plan));
@@ -258,10 +265,31 @@ void convolutionWithOutput(Graph &graph, const Tensor &in, const Tensor &weights
   const bool outDirect = isDenseInOrder(out, actsOrder(out.rank()));
   const Tensor outA = outDirect ? out : arranged(graph, out, actsOrder(out.rank()), prog, false);
 
-  const plb_conv_params flat = internal::toPlb(params.canonicalize());
+  const ConvParams canonical = params.canonicalize();
   plb_conv_options opt = parsed.toPlb();
   const int transpose = transposeAndFlipWeights ? 1 : 0;
   const std::string name = dc.getPathName();
+  // The backward pass of a strided layer arrives as a convolution whose input
+  // (the output gradients) is dilated by the forward stride
+  // (getGradientParams, lib/poplin/ConvUtil.cpp:728-795).  The kernels take that
+  // pass in forward terms: getGradientParams is its own inverse up to
+  // canonicalisation, and the weights are the forward layer's.
+  const bool dilatedInput =
+      std::any_of(canonical.inputTransform.dilation.begin(), canonical.inputTransform.dilation.end(),
+                  [](unsigned d) { return d != 1; });
+  if (dilatedInput && transposeAndFlipWeights) {
+    const plb_conv_params fwd = internal::toPlb(getGradientParams(params).canonicalize());
+    prog.add([=](plb_context *ctx) mutable {
+      opt.scale_in = quarterExponent(inA);
+      opt.scale_weights = quarterExponent(wA);
+      logging::poplin::trace("convolution (backward of a strided layer) " + name);
+      poplar::detail::check(plb_conv_bwd(ctx, &fwd, &opt, inA.devicePointer(), wA.devicePointer(),
+                                         outA.devicePointer()));
+    });
+    if (!outDirect) prog.add(poplar::program::Copy(outA, out));
+    return;
+  }
+  const plb_conv_params flat = internal::toPlb(canonical);
   prog.add([=](plb_context *ctx) mutable {
     opt.scale_in = quarterExponent(inA);
     opt.scale_weights = quarterExponent(wA);
@@ -355,6 +383,22 @@ Tensor calculateWeightDeltas(Graph &graph, const Tensor &zDeltas, const Tensor &
   return weightDeltasImpl(graph, zDeltas, activations, params, prog, dc, options, cache).deltas;
 }
 
+// Reads a scalar float / half tensor from the device (synchronises the stream).
+static float fetchScalar(plb_context *ctx, const Tensor &t) {
+  float value = 0.f;
+  if (t.elementType() == poplar::FLOAT) {
+    poplar::detail::check(plb_memcpy_d2h(ctx, &value, t.devicePointer(), sizeof(float)));
+    return value;
+  }
+  uint16_t bits = 0;
+  poplar::detail::check(plb_memcpy_d2h(ctx, &bits, t.devicePointer(), sizeof bits));
+  // half -> float
+  const int sign = bits >> 15, e = (bits >> 10) & 31, m = bits & 1023;
+  const float mag = e == 0 ? std::ldexp(float(m), -24)
+                           : (e == 31 ? INFINITY : std::ldexp(float(m + 1024), e - 25));
+  return sign ? -mag : mag;
+}
+
 static void weightUpdateImpl(Graph &graph, const Tensor &zDeltas, const Tensor &weights_,
                              const Tensor &activations, const ConvParams &params,
                              const Tensor *scaleTensor, float scaleValue, Sequence &prog,
@@ -373,21 +417,7 @@ static void weightUpdateImpl(Graph &graph, const Tensor &zDeltas, const Tensor &
   Tensor scaleT;
   if (scaleTensor) scaleT = *scaleTensor;
   prog.add([=](plb_context *ctx) {
-    float scale = scaleValue;
-    if (scaleT.valid()) {
-      // a scalar on the device: fetch it (synchronises the stream)
-      if (scaleT.elementType() == poplar::FLOAT) {
-        poplar::detail::check(plb_memcpy_d2h(ctx, &scale, scaleT.devicePointer(), sizeof(float)));
-      } else {
-        uint16_t bits = 0;
-        poplar::detail::check(plb_memcpy_d2h(ctx, &bits, scaleT.devicePointer(), sizeof bits));
-        // half -> float
-        const int sign = bits >> 15, e = (bits >> 10) & 31, m = bits & 1023;
-        const float mag = e == 0 ? std::ldexp(float(m), -24)
-                                 : (e == 31 ? INFINITY : std::ldexp(float(m + 1024), e - 25));
-        scale = sign ? -mag : mag;
-      }
-    }
+    const float scale = scaleT.valid() ? fetchScalar(ctx, scaleT) : scaleValue;
     poplar::detail::check(plb_scaled_add_to(ctx, dtype, wA.devicePointer(),
                                             static_cast<const float *>(d32.devicePointer()), scale,
                                             wA.numElements()));
@@ -410,6 +440,47 @@ void convolutionWeightUpdate(Graph &graph, const Tensor &zDeltas, const Tensor &
                              const poplar::OptionFlags &options, PlanningCache *cache) {
   weightUpdateImpl(graph, zDeltas, weights, activations, params, nullptr, scale, prog, dc, options,
                    cache);
+}
+
+static void biasUpdateImpl(Graph &graph, const Tensor &zDeltas, const Tensor &biases,
+                           const Tensor *scaleTensor, float scaleValue,
+                           const poplar::OptionFlags &options, Sequence &prog) {
+  const internal::ConvOptions parsed(options);  // validates the keys; sums are always kept in fp32
+  (void)parsed;
+  if (zDeltas.rank() < 2)
+    throw poplibs_error("convolutionBiasUpdate with rank " + std::to_string(zDeltas.rank()) +
+                        "; must have at least channel and batch dimensions");
+  if (biases.rank() != 1 || biases.dim(0) != zDeltas.dim(1))
+    throw poplibs_error("convolutionBiasUpdate: biases must have one element per channel of zDeltas");
+  if (scaleTensor && scaleTensor->numElements() != 1)
+    throw poplibs_error("convolutionBiasUpdate: scale must be a scalar");
+  const Tensor z = arranged(graph, zDeltas, actsOrder(zDeltas.rank()), prog);
+  const bool direct = isDenseInOrder(biases, {0});
+  const Tensor b = direct ? biases : arranged(graph, biases, {0}, prog);
+  const int zType = poplar::detail::dtypeOf(zDeltas.elementType());
+  const int bType = poplar::detail::dtypeOf(biases.elementType());
+  const std::size_t chans = zDeltas.dim(1);
+  const std::size_t pixels = chans ? zDeltas.numElements() / chans : 0;
+  Tensor scaleT;
+  if (scaleTensor) scaleT = *scaleTensor;
+  prog.add([=](plb_context *ctx) {
+    const float scale = scaleT.valid() ? fetchScalar(ctx, scaleT) : scaleValue;
+    poplar::detail::check(plb_conv_bias_update(ctx, zType, z.devicePointer(), pixels,
+                                               uint32_t(chans), bType, b.devicePointer(), scale));
+  });
+  if (!direct) prog.add(poplar::program::Copy(b, biases));
+}
+
+void convolutionBiasUpdate(Graph &graph, const Tensor &zDeltas, const Tensor &biases,
+                           const Tensor &scale, const poplar::OptionFlags &options, Sequence &prog,
+                           const poplar::DebugContext &) {
+  biasUpdateImpl(graph, zDeltas, biases, &scale, 0.f, options, prog);
+}
+
+void convolutionBiasUpdate(Graph &graph, const Tensor &zDeltas, const Tensor &biases, float scale,
+                           const poplar::OptionFlags &options, Sequence &prog,
+                           const poplar::DebugContext &) {
+  biasUpdateImpl(graph, zDeltas, biases, nullptr, scale, options, prog);
 }
 
 void addBias(Graph &graph, const Tensor &acts, const Tensor &biases, Sequence &prog,
@@ -447,6 +518,7 @@ static void printPlan(std::ostream &out, const plb_plan &plan, const char *pass)
       << "        CTAs launched              " << plan.grid << "\n"
       << "        weights resident in SMEM   " << (plan.resident_weights ? "yes" : "no") << "\n"
       << "        halo rows per load         " << plan.halo_rows << "\n"
+      << "        CTA pair (256-row MMA)     " << plan.cta_pair << "\n"
       << "        right operand MN-major     " << (plan.b_mn_major ? "yes" : "no") << "\n"
       << "        workspace bytes            " << plan.workspace_bytes << "\n"
       << "        FLOPs (padding excluded)   " << plan.flops << "\n"

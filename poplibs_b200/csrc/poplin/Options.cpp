@@ -280,6 +280,8 @@ plb_conv_options ConvOptions::toPlb() const {
                                           : PLB_PLAN_NO_RESIDENT_WEIGHTS;
       if (const auto *v = level.second.find("halo"))
         if (v->text == "false") o.plan_flags |= PLB_PLAN_NO_HALO;
+      if (const auto *v = level.second.find("ctaPair"))
+        o.plan_flags |= v->text == "false" ? PLB_PLAN_NO_CTA_PAIR : PLB_PLAN_FORCE_CTA_PAIR;
       continue;
     }
     const json::Value *partition = level.second.find("partition");

@@ -273,6 +273,76 @@ __global__ void fillKernel(T *dst, T value, size_t n) {
     dst[i] = value;
 }
 
+// Column sums of a [rows][chans] matrix (device-layout activations: one row per
+// pixel), first stage: block (x, y) adds the rows y, y + gridDim.y, ... of the
+// 8-channel vectors it owns into fp32 and leaves one partial row per slab.
+// Threads are arranged as (vector of 8 channels, row lane).
+template <typename T>
+__global__ void __launch_bounds__(256)
+columnSumPartialKernel(const T *__restrict__ in, float *__restrict__ partial, uint64_t rows,
+                       uint32_t chans, uint32_t vec_lanes) {
+  constexpr int kVec = 16 / int(sizeof(T));  // elements per 16-byte load
+  __shared__ float red[256 * 8];
+  const uint32_t vx = threadIdx.x % vec_lanes, ry = threadIdx.x / vec_lanes;
+  const uint32_t row_lanes = blockDim.x / vec_lanes;
+  const uint32_t vec = blockIdx.x * vec_lanes + vx;
+  const uint32_t vecs = chans / kVec;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (vec < vecs) {
+    for (uint64_t r = uint64_t(blockIdx.y) * row_lanes + ry; r < rows;
+         r += uint64_t(gridDim.y) * row_lanes) {
+      const uint4 v = *reinterpret_cast<const uint4 *>(in + r * chans + size_t(vec) * kVec);
+      if constexpr (sizeof(T) == 2) {
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      } else {
+        const float *f = reinterpret_cast<const float *>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] += f[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) red[threadIdx.x * 8 + j] = acc[j];
+  __syncthreads();
+  // row lane 0 adds the lanes in order
+  if (ry == 0 && vec < vecs) {
+    for (uint32_t y = 1; y < row_lanes; ++y)
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) acc[j] += red[(y * vec_lanes + vx) * 8 + j];
+#pragma unroll
+    for (int j = 0; j < kVec; ++j)
+      partial[size_t(blockIdx.y) * chans + size_t(vec) * kVec + j] = acc[j];
+  }
+}
+// Generic first stage (any channel count / alignment): one thread per channel.
+template <typename T>
+__global__ void columnSumPartialScalarKernel(const T *__restrict__ in, float *__restrict__ partial,
+                                             uint64_t rows, uint32_t chans) {
+  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= chans) return;
+  float acc = 0.f;
+  for (uint64_t r = blockIdx.y; r < rows; r += gridDim.y) acc += float(in[r * chans + c]);
+  partial[size_t(blockIdx.y) * chans + c] = acc;
+}
+// Second stage: biases[c] += scale * (sum of the slabs' partial rows, in order).
+template <typename T>
+__global__ void biasUpdateKernel(const float *__restrict__ partial, uint32_t slabs, uint32_t chans,
+                                 T *__restrict__ biases, float scale) {
+  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= chans) return;
+  float s = 0.f;
+  for (uint32_t k = 0; k < slabs; ++k) s += partial[size_t(k) * chans + c];
+  biases[c] = T(float(biases[c]) + scale * s);
+}
+
 int launchScaleRows(plb_context *ctx, void *out, const void *c, float beta, bool out_f32,
                     uint32_t rows, uint32_t cols, long long ldo, long long ldc) {
   if (rows == 0 || cols == 0) return PLB_OK;
@@ -550,6 +620,63 @@ int plb_add_bias(plb_context *ctx, int32_t dtype, void *d_acts, const void *d_bi
         static_cast<float *>(d_acts), static_cast<const float *>(d_biases), total, chans);
   else
     return fail(PLB_ERR_INVALID_PARAMS, "bias add needs half or float activations");
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int plb_conv_bias_update(plb_context *ctx, int32_t acts_dtype, const void *d_out_grads,
+                         uint64_t pixels, uint32_t chans, int32_t bias_dtype, void *d_biases,
+                         float scale) {
+  if (int rc = activate(ctx)) return rc;
+  if ((acts_dtype != PLB_HALF && acts_dtype != PLB_FLOAT) ||
+      (bias_dtype != PLB_HALF && bias_dtype != PLB_FLOAT))
+    return fail(PLB_ERR_INVALID_PARAMS, "bias update needs half or float gradients and biases");
+  if (chans == 0) return PLB_OK;
+  // slabs of rows, enough blocks to fill the device; partial sums in fp32
+  const size_t es = dtypeBytes(acts_dtype);
+  const uint32_t vec = uint32_t(16 / es);
+  const bool vector_ok = chans % vec == 0 && (reinterpret_cast<uintptr_t>(d_out_grads) & 15) == 0;
+  uint32_t vec_lanes = 1, col_blocks = 1, slabs = 1;
+  if (vector_ok) {
+    const uint32_t vecs = chans / vec;
+    vec_lanes = 1;
+    while (vec_lanes < 32 && vec_lanes < vecs) vec_lanes <<= 1;
+    col_blocks = (vecs + vec_lanes - 1) / vec_lanes;
+    const uint32_t row_lanes = 256 / vec_lanes;
+    const uint64_t want = std::max<uint64_t>(1, uint64_t(ctx->sm_count) * 8 / col_blocks);
+    slabs = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>(want, (pixels + row_lanes - 1) / row_lanes)));
+  } else {
+    col_blocks = (chans + 127) / 128;
+    slabs = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>(pixels, uint64_t(ctx->sm_count) * 16 / col_blocks)));
+  }
+  void *ws = nullptr;
+  if (int rc = scratch(ctx, 5, size_t(slabs) * chans * sizeof(float), &ws)) return rc;
+  float *partial = static_cast<float *>(ws);
+  if (vector_ok) {
+    if (acts_dtype == PLB_HALF)
+      columnSumPartialKernel<__half><<<dim3(col_blocks, slabs), 256, 0, ctx->stream>>>(
+          static_cast<const __half *>(d_out_grads), partial, pixels, chans, vec_lanes);
+    else
+      columnSumPartialKernel<float><<<dim3(col_blocks, slabs), 256, 0, ctx->stream>>>(
+          static_cast<const float *>(d_out_grads), partial, pixels, chans, vec_lanes);
+  } else {
+    if (acts_dtype == PLB_HALF)
+      columnSumPartialScalarKernel<__half><<<dim3(col_blocks, slabs), 128, 0, ctx->stream>>>(
+          static_cast<const __half *>(d_out_grads), partial, pixels, chans);
+    else
+      columnSumPartialScalarKernel<float><<<dim3(col_blocks, slabs), 128, 0, ctx->stream>>>(
+          static_cast<const float *>(d_out_grads), partial, pixels, chans);
+  }
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  const uint32_t ugrid = (chans + 127) / 128;
+  if (bias_dtype == PLB_HALF)
+    biasUpdateKernel<__half><<<ugrid, 128, 0, ctx->stream>>>(partial, slabs, chans,
+                                                            static_cast<__half *>(d_biases), scale);
+  else
+    biasUpdateKernel<float><<<ugrid, 128, 0, ctx->stream>>>(partial, slabs, chans,
+                                                           static_cast<float *>(d_biases), scale);
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;

@@ -79,7 +79,9 @@ struct IgemmProblem {
   int flip_h = 0, flip_w = 0;
   int stride_h = 1, stride_w = 1;
   void *out = nullptr;
-  long long ldc = 0;
+  long long ldc = 0;  // elements between output pixels along w
+  // elements between output rows / images; 0 = dense (out_w * ldc, out_h * out_w * ldc)
+  long long out_stride_h = 0, out_stride_n = 0;
   const void *addend = nullptr;
   long long ld_addend = 0;
   const float *bias = nullptr;

@@ -12,6 +12,9 @@ namespace {
 
 struct WuShape {
   int H, W, OH, OW, KH, KW, padH, padW, dilH, dilW, strH, strW;
+  // views: input truncation (tH, tW; extent He x We), output padding (opH, opW;
+  // computed extent OHc x OWc); padH/padW already include the output truncation
+  int tH, tW, He, We, opH, opW, OHc, OWc;
 };
 
 int wuShape(const plb_conv_params &p, WuShape *s) {
@@ -24,12 +27,11 @@ int wuShape(const plb_conv_params &p, WuShape *s) {
     // (tools/single_conv_layer.cpp:725-733)
     return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half input only");
   for (unsigned d = 0; d != p.num_field_dims; ++d) {
-    if (p.in_trunc_lo[d] || p.in_trunc_hi[d] || p.in_dilation[d] != 1 || p.in_flip[d] ||
-        p.k_trunc_lo[d] || p.k_trunc_hi[d] || p.k_pad_lo[d] || p.k_pad_hi[d] || p.k_flip[d] ||
-        p.out_trunc_lo[d] || p.out_trunc_hi[d] || p.out_pad_lo[d] || p.out_pad_hi[d])
+    if (p.in_dilation[d] != 1 || p.in_flip[d] || p.k_trunc_lo[d] || p.k_trunc_hi[d] ||
+        p.k_pad_lo[d] || p.k_pad_hi[d] || p.k_flip[d])
       return fail(PLB_ERR_UNSUPPORTED,
-                  "input truncation/dilation/flip, kernel truncation/padding/flip and output "
-                  "truncation/padding are not implemented on this path yet");
+                  "input dilation/flip and kernel truncation/padding/flip are not implemented on "
+                  "this path yet");
     if (p.stride[d] > 8) return fail(PLB_ERR_UNSUPPORTED, "strides above 8 are not implemented");
   }
   const unsigned hd = p.num_field_dims == 2 ? 0 : ~0u, wd = p.num_field_dims - 1;
@@ -46,6 +48,16 @@ int wuShape(const plb_conv_params &p, WuShape *s) {
   s->strW = get(p.stride, wd, 1);
   s->OH = hd == ~0u ? 1 : int(outputSize(p, hd));
   s->OW = int(outputSize(p, wd));
+  s->tH = get(p.in_trunc_lo, hd, 0);
+  s->tW = get(p.in_trunc_lo, wd, 0);
+  s->He = s->H - s->tH - get(p.in_trunc_hi, hd, 0);
+  s->We = s->W - s->tW - get(p.in_trunc_hi, wd, 0);
+  s->padH -= get(p.out_trunc_lo, hd, 0);
+  s->padW -= get(p.out_trunc_lo, wd, 0);
+  s->opH = get(p.out_pad_lo, hd, 0);
+  s->opW = get(p.out_pad_lo, wd, 0);
+  s->OHc = s->OH - s->opH - get(p.out_pad_hi, hd, 0);
+  s->OWc = s->OW - s->opW - get(p.out_pad_hi, wd, 0);
   return PLB_OK;
 }
 
@@ -82,7 +94,7 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
       const int n = 64 / (w * h);
       if ((w - 1) * s.strW + 1 > 256 || (h - 1) * s.strH + 1 > 256) continue;
       const long tiles =
-          long((s.OW + w - 1) / w) * ((s.OH + h - 1) / h) * ((long(p.batch) + n - 1) / n);
+          long((s.OWc + w - 1) / w) * ((s.OHc + h - 1) / h) * ((long(p.batch) + n - 1) / n);
       if (best < 0 || tiles < best) {
         best = tiles;
         a->box_w = w;
@@ -105,7 +117,7 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
         const int n = 64 / (w * h);
         if ((w * n) % 8 != 0 || h + halo > 256 || (w - 1) * s.strW + 1 > 256) continue;
         const long tiles =
-            long((s.OW + w - 1) / w) * ((s.OH + h - 1) / h) * ((long(p.batch) + n - 1) / n);
+            long((s.OWc + w - 1) / w) * ((s.OHc + h - 1) / h) * ((long(p.batch) + n - 1) / n);
         if (sbest < 0 || tiles < sbest) {
           sbest = tiles;
           sw = w;
@@ -130,8 +142,8 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
       best = sbest;
     }
   }
-  a->tiles_w = (s.OW + a->box_w - 1) / a->box_w;
-  a->tiles_h = (s.OH + a->box_h - 1) / a->box_h;
+  a->tiles_w = (s.OWc + a->box_w - 1) / a->box_w;
+  a->tiles_h = (s.OHc + a->box_h - 1) / a->box_h;
   a->tiles_n = (int(p.batch) + a->box_n - 1) / a->box_n;
   a->stage_bytes = stage_bytes;
   a->stages = std::max(2, std::min(kWuMaxStages, (200 * 1024) / stage_bytes));
@@ -186,27 +198,29 @@ int launchWu(cudaStream_t stream, const plb_conv_params &p, const WuShape &s, co
     const int halo = strip ? (s.KH - 1) * s.dilH : 0;
     {
       const uint64_t sh = uint64_t(s.OW) * cotot * es, sn = uint64_t(s.OH) * s.OW * cotot * es;
-      const uint64_t dims[4] = {uint64_t(co), uint64_t(s.OW), strip ? p.batch : uint64_t(s.OH),
-                                strip ? uint64_t(s.OH) : p.batch};
+      const uint64_t dims[4] = {uint64_t(co), uint64_t(s.OWc), strip ? p.batch : uint64_t(s.OHc),
+                                strip ? uint64_t(s.OHc) : p.batch};
       const uint64_t strides[3] = {cotot * es, strip ? sn : sh, strip ? sh : sn};
       const uint32_t box[4] = {64, uint32_t(a.box_w), uint32_t(strip ? a.box_n : a.box_h),
                                uint32_t(strip ? a.box_h : a.box_n)};
       if (int rc = encodeTensorMap(&tdy, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                                   static_cast<const uint8_t *>(d_out_grads) + size_t(g) * co * es,
+                                   static_cast<const uint8_t *>(d_out_grads) +
+                                       ((size_t(s.opH) * s.OW + s.opW) * cotot + size_t(g) * co) * es,
                                    dims, strides, box, ones))
         return rc;
     }
     {
       const uint64_t sh = uint64_t(s.W) * ctot * es, sn = uint64_t(s.H) * s.W * ctot * es;
-      const uint64_t dims[4] = {uint64_t(ci), uint64_t(s.W), strip ? p.batch : uint64_t(s.H),
-                                strip ? uint64_t(s.H) : p.batch};
+      const uint64_t dims[4] = {uint64_t(ci), uint64_t(s.We), strip ? p.batch : uint64_t(s.He),
+                                strip ? uint64_t(s.He) : p.batch};
       const uint64_t strides[3] = {ctot * es, strip ? sn : sh, strip ? sh : sn};
       const uint32_t bw = uint32_t((a.box_w - 1) * s.strW + 1);
       const uint32_t bh = strip ? uint32_t(a.box_h + halo) : uint32_t((a.box_h - 1) * s.strH + 1);
       const uint32_t box[4] = {64, bw, strip ? uint32_t(a.box_n) : bh, strip ? bh : uint32_t(a.box_n)};
       const uint32_t estr[4] = {1, uint32_t(s.strW), strip ? 1u : uint32_t(s.strH), 1};
       if (int rc = encodeTensorMap(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                                   static_cast<const uint8_t *>(d_acts) + size_t(g) * ci * es,
+                                   static_cast<const uint8_t *>(d_acts) +
+                                       ((size_t(s.tH) * s.W + s.tW) * ctot + size_t(g) * ci) * es,
                                    dims, strides, box, estr))
         return rc;
     }
@@ -267,7 +281,7 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
   const int taps = s.KH * s.KW;
   const size_t w_elems = size_t(taps) * co * ci;
   if (p->groups == 0 || w_elems == 0) return PLB_OK;
-  if (p->batch == 0 || s.OH == 0 || s.OW == 0) {
+  if (p->batch == 0 || s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) {
     // empty reduction: the gradient is zero
     const size_t n = size_t(p->groups) * w_elems;
     if (d_weight_grads) PLB_CUDA(cudaMemsetAsync(d_weight_grads, 0, n * dtypeBytes(p->input_type), ctx->stream));
@@ -367,7 +381,7 @@ extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const p
   StaticScratch scratch;
   if (int rc = staticScratchFor(device, &scratch)) return rc;
   const size_t es = 2;
-  if (p->batch == 0 || s.OH == 0 || s.OW == 0) {
+  if (p->batch == 0 || s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) {
     const size_t n = size_t(p->groups) * w_elems;
     if (d_weight_grads) PLB_CUDA(cudaMemsetAsync(d_weight_grads, 0, n * es, stream));
     if (d_weight_grads_f32) PLB_CUDA(cudaMemsetAsync(d_weight_grads_f32, 0, n * sizeof(float), stream));

@@ -140,6 +140,11 @@ int main(int argc, char **argv) try {
       poplin::addBias(graph, nextAct, biases, once, "bias");
     }
     fwdProg.add(Repeat(numExecutions, once));
+  } else if (bias && doWu) {
+    // the weight-update pass also updates the biases (the reference tool
+    // always builds the forward pass and takes the biases' layout from it)
+    biases = poplin::createBiases(
+        graph, poplin::createConvOutput(graph, params, "nextAct", fwdOptions, &cache), "biases");
   }
   Tensor zDeltas, prevDeltas;
   if (doBwd || doWu) {
@@ -161,12 +166,18 @@ int main(int argc, char **argv) try {
                                                  wuOptions, &cache);
     poplin::convolutionWeightUpdate(graph, zDeltas, weights, prevAct, params, float(-learningRate),
                                     wuProg, "wuApply", wuOptions, &cache);
+    if (bias)
+      poplin::convolutionBiasUpdate(graph, zDeltas, biases, float(-learningRate), wuOptions, wuProg,
+                                    "biasUpdate");
   }
 
   graph.createHostWrite("prevAct", prevAct);
   graph.createHostWrite("weights", weights);
   graph.createHostRead("weights", weights);
-  if (biases.valid()) graph.createHostWrite("biases", biases);
+  if (biases.valid()) {
+    graph.createHostWrite("biases", biases);
+    graph.createHostRead("biases", biases);
+  }
   if (nextAct.valid()) graph.createHostRead("nextAct", nextAct);
   if (zDeltas.valid()) graph.createHostWrite("zDeltas", zDeltas);
   if (prevDeltas.valid()) graph.createHostRead("prevDeltas", prevDeltas);
@@ -247,6 +258,8 @@ int main(int argc, char **argv) try {
     report("wu (gradient + update)", 1);
     readBack("weightDeltas", weightDeltas, wShape);
     readBack("weights", weights, wShape, "weightsUpdated");
+    if (biases.valid())
+      readBack("biases", biases, {std::size_t(groups) * co}, "biasesUpdated");
   }
   if (profile) engine.printProfileSummary(std::cout);
   return 0;

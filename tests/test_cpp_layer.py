@@ -117,6 +117,14 @@ def test_single_conv_layer_tool_against_oracle(tmp_path):
                     "--padding=1", "--stride=2", "--batch-size=2", "--bias=0", "--integer-data",
                     "--single-phase=fwd"],
              spec=ConvSpec.simple(2, [9, 9], [3, 3], 64, 64, padding=1, stride=2), bias=False),
+        # strided layers in all passes; on an even field a 1x1 stride-2 layer leaves the
+        # last row and column unused (input truncation in the canonical parameters)
+        dict(flags=["--input-channels=64", "--output-channels=128", "--field={12,12}", "--kernel-size=1",
+                    "--stride=2", "--batch-size=3", "--bias=0", "--integer-data", "--learning-rate=0.5"],
+             spec=ConvSpec.simple(3, [12, 12], [1, 1], 64, 128, stride=2), bias=False),
+        dict(flags=["--input-channels=64", "--output-channels=64", "--field={12,11}", "--kernel-size=3",
+                    "--padding=1", "--stride=2", "--batch-size=2", "--integer-data", "--learning-rate=0.25"],
+             spec=ConvSpec.simple(2, [12, 11], [3, 3], 64, 64, padding=1, stride=2), bias=True),
         dict(flags=["--input-channels=32", "--output-channels=32", "--field={6,6}", "--kernel-size=3",
                     "--padding=1", "--conv-groups=2", "--batch-size=2", "--bias=0", "--integer-data",
                     "--learning-rate=0.5"],
@@ -148,3 +156,8 @@ def test_single_conv_layer_tool_against_oracle(tmp_path):
             lr = float([f for f in case["flags"] if f.startswith("--learning-rate")][0].split("=")[1])  # exact in half
             expect = (w0 - lr * dw).astype(np.float16).astype(np.float64)
             assert (flat(t["weightsUpdated"], 3) == expect).all(), case["flags"]
+            if case["bias"]:
+                # biases += -lr * sum of the output gradients (fp32 sums, cast to the bias type)
+                _, db = oracle.conv_wu(spec, x, flat(t["zDeltas"], 2))
+                expect_b = (t["biases"].ravel() - lr * db).astype(np.float16).astype(np.float64)
+                assert (t["biasesUpdated"].ravel() == expect_b).all(), case["flags"]

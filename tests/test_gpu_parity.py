@@ -10,6 +10,7 @@ terms cancel cannot be reproduced to 1e-3 of ITSELF by any fp32 accumulation,
 so such elements are held to a quarter of the relative tolerance measured
 against the typical output magnitude instead.
 """
+import os
 import zlib
 
 import numpy as np
@@ -169,6 +170,22 @@ STRIDED_CONVS = {
     "3x3_s2": conv_case(2, [9, 9], [3, 3], 64, 64, padding=1, stride=2),
     "3x3_s2x3": conv_case(2, [11, 13], [3, 3], 64, 64, padding=1, stride=[2, 3]),
     "3x3_s1x2": conv_case(5, [10, 13], [3, 3], 64, 64, padding=1, stride=[1, 2]),
+    "1x1_s2_even_field": conv_case(3, [12, 10], [1, 1], 64, 128, stride=2),   # last row / column unused
+    "3x3_s2_nopad_leftover": conv_case(2, [12, 13], [3, 3], 64, 64, stride=2),
+    "5x5_s3_dil1": conv_case(2, [17, 16], [5, 5], 64, 72, padding=2, stride=3),
+    "3x3_s2_dil3": conv_case(2, [15, 15], [3, 3], 64, 64, padding=3, stride=2, k_dilation=3),
+    "one_dim_s2": conv_case(4, [33], [5], 64, 96, padding=2, stride=2),
+}
+# Transforms that the reference's canonical form of ordinary layers produces
+# (input truncation for unused trailing rows) and its gradient parameters use
+# (output truncation / padding); all of them are views and offsets here.
+TRANSFORMED_CONVS = {
+    "in_trunc": conv_case(2, [11, 12], [3, 3], 64, 64, padding=1, in_trunc_lo=[1, 2], in_trunc_hi=[2, 0]),
+    "in_trunc_s2": conv_case(3, [12, 12], [1, 1], 64, 64, stride=2, in_trunc_hi=[1, 1]),
+    "out_trunc": conv_case(2, [10, 9], [3, 3], 64, 64, padding=2, out_trunc_lo=[1, 0], out_trunc_hi=[1, 2]),
+    "out_pad": conv_case(2, [8, 8], [3, 3], 64, 72, padding=1, out_pad_lo=[1, 0], out_pad_hi=[0, 2]),
+    "all_views_s2": conv_case(2, [14, 13], [3, 3], 64, 64, padding=1, stride=2, in_trunc_lo=[1, 0],
+                              out_trunc_lo=[2, 0], out_pad_lo=[0, 1], out_pad_hi=[1, 0]),
 }
 
 
@@ -200,9 +217,23 @@ def test_conv_fwd_small(gpu_ctx, name):
                  f"fwd {name} uniform + bias")
 
 
-@pytest.mark.parametrize("name", sorted(SMALL_CONVS))
+@pytest.mark.parametrize("name", sorted(TRANSFORMED_CONVS))
+def test_conv_transform_views(gpu_ctx, name):
+    """Input truncation, output truncation and output padding in all three passes."""
+    kw = TRANSFORMED_CONVS[name]
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(zlib.crc32(name.encode()) % 1000 + 7)
+    x, w, dy = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), f"fwd {name}")
+    assert_exact(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), f"bwd {name}")
+    _, dw32 = T.gpu_conv_wu(p, x, dy)
+    assert_exact(dw32, oracle.conv_wu(spec, x, dy)[0], f"wu {name}")
+
+
+@pytest.mark.parametrize("name", sorted({**SMALL_CONVS, **STRIDED_CONVS}))
 def test_conv_bwd_small(gpu_ctx, name):
-    kw = SMALL_CONVS[name]
+    kw = {**SMALL_CONVS, **STRIDED_CONVS}[name]
     p = capi.ConvParams.make(**kw)
     spec = T.spec_from_params(p)
     r = T.rng(zlib.crc32(name.encode()) % 1000 + 1)
@@ -251,8 +282,13 @@ def test_conv_wu_plan_variants(gpu_ctx, name):
 
 PLAN_VARIANTS = {
     "streamed": capi.PLAN_NO_RESIDENT_WEIGHTS,
+    "streamed_no_halo": capi.PLAN_NO_RESIDENT_WEIGHTS | capi.PLAN_NO_HALO,
     "resident": capi.PLAN_FORCE_RESIDENT_WEIGHTS | capi.PLAN_NO_HALO,
     "resident_halo": capi.PLAN_FORCE_RESIDENT_WEIGHTS,
+    "streamed_pair": capi.PLAN_NO_RESIDENT_WEIGHTS | capi.PLAN_FORCE_CTA_PAIR,
+    "resident_pair": capi.PLAN_FORCE_RESIDENT_WEIGHTS | capi.PLAN_NO_HALO | capi.PLAN_FORCE_CTA_PAIR,
+    "resident_halo_pair": capi.PLAN_FORCE_RESIDENT_WEIGHTS | capi.PLAN_FORCE_CTA_PAIR,
+    "no_pair": capi.PLAN_NO_CTA_PAIR,
 }
 
 
@@ -266,11 +302,72 @@ def test_conv_plan_variants_agree_with_oracle(gpu_ctx, name, variant):
     p = capi.ConvParams.make(**kw)
     spec = T.spec_from_params(p)
     opt = capi.ConvOptions.make(plan_flags=PLAN_VARIANTS[variant])
+    if variant in ("streamed_pair", "resident_pair", "resident_halo_pair"):
+        # two CTAs share 256-row MMAs (every case here has at least two pixel tiles)
+        plan = capi.conv_plan(p, capi.PASS_TRAINING_FWD, opt)
+        pixel_tiles = plan.tiles // -(-p.out_chans_per_group // plan.tile_n)
+        assert plan.cta_pair == (1 if pixel_tiles >= 2 else 0)
     r = T.rng(zlib.crc32((name + variant).encode()) % 1000)
     x, w, dy = conv_data(p, kw, r, exact=True)
     assert_exact(T.gpu_conv_fwd(p, x, w, opt=opt), oracle.conv_fwd(spec, x, w), f"fwd {name} {variant}")
-    if name not in STRIDED_CONVS:
-        assert_exact(T.gpu_conv_bwd(p, dy, w, opt=opt), oracle.conv_bwd(spec, dy, w), f"bwd {name} {variant}")
+    assert_exact(T.gpu_conv_bwd(p, dy, w, opt=opt), oracle.conv_bwd(spec, dy, w), f"bwd {name} {variant}")
+
+
+@pytest.fixture
+def force_cta_pair():
+    os.environ["PLB_FORCE_CTA_PAIR"] = "1"
+    yield
+    os.environ.pop("PLB_FORCE_CTA_PAIR", None)
+
+
+@pytest.mark.parametrize("m,k,n,tb", [(384, 192, 200, False), (384, 192, 200, True), (1000, 72, 136, False),
+                                      (256, 1024, 512, True), (130, 64, 64, True)])
+def test_matmul_cta_pair_exact(gpu_ctx, force_cta_pair, m, k, n, tb):
+    """Matrix products on CTA pairs: odd tile counts, ragged N, both B layouts."""
+    r = T.rng(m + k + n)
+    a = T.binary_half(r, (m, k))
+    b = T.binary_half(r, (n, k) if tb else (k, n))
+    got = T.gpu_matmul(a, b, transpose_b=tb)
+    assert_exact(got, oracle.gemm(a, b, transpose_b=tb), f"pair matmul {m}x{k}x{n} tb={tb}")
+
+
+def test_matmul_cta_pair_quarter(gpu_ctx, force_cta_pair):
+    r = T.rng(5)
+    av = r.integers(-3, 4, (384, 256)).astype(np.float64)
+    bv = r.integers(-3, 4, (256, 320)).astype(np.float64)
+    got = T.gpu_matmul(oracle.e4m3_encode(av), oracle.e4m3_encode(bv))
+    assert_exact(got, oracle.gemm(av, bv), "pair quarter matmul")
+
+
+def test_conv_bias_update(gpu_ctx):
+    """biases += scale * sum over pixels of the output gradients (fp32 sums)."""
+    import torch
+    ctx = T.context()
+    for (n, c, field, dt) in ((4, 64, (9, 7), np.float16), (3, 40, (5, 5), np.float16),
+                              (2, 132, (6, 6), np.float32), (5, 3, (4, 4), np.float16)):
+        r = T.rng(c)
+        dy = T.binary_half(r, (n, c, *field)).astype(dt)
+        b0 = r.integers(-4, 5, c).astype(dt)
+        ddy = T.to_dev(T.acts_to_device_layout(dy))
+        db = T.to_dev(b0.copy())
+        torch.cuda.synchronize()
+        ctx.conv_bias_update(capi.FLOAT if dt == np.float32 else capi.HALF, ddy, n * field[0] * field[1], c,
+                             capi.FLOAT if dt == np.float32 else capi.HALF, db, -0.5)
+        ctx.synchronize()
+        want = b0.astype(np.float64) - 0.5 * dy.astype(np.float64).sum(axis=(0, 2, 3))
+        assert_exact(db.cpu().numpy(), want, f"bias update c={c}")
+    # against the model's bias gradient on a convolution
+    kw = conv_case(3, [8, 8], [3, 3], 64, 72, padding=1)
+    p = capi.ConvParams.make(**kw)
+    r = T.rng(9)
+    x, _, dy = conv_data(p, kw, r, exact=True)
+    _, dbias = oracle.conv_wu(T.spec_from_params(p), x, dy)
+    ddy = T.to_dev(T.acts_to_device_layout(dy))
+    db = T.to_dev(np.zeros(72, np.float32))
+    torch.cuda.synchronize()
+    ctx.conv_bias_update(capi.HALF, ddy, 3 * 64, 72, capi.FLOAT, db, 1.0)
+    ctx.synchronize()
+    assert_exact(db.cpu().numpy(), dbias, "bias gradient vs model")
 
 
 def test_small_channel_stem_layers(gpu_ctx):
