@@ -228,8 +228,9 @@ class Workload:
                 # weak scaling: every rank holds one full per-GPU batch of the layer
                 glob = dict(kw, batch=kw["batch"] * world)
                 self.sharded = parallel.ShardedConv(ctx, glob, rank, world)
-            self.plan = (capi.conv_plan(p, capi.PASS_TRAINING_BWD) if self.pass_ == "bwd"
-                         else capi.conv_plan(p)).as_dict()
+            pass_id = {"bwd": capi.PASS_TRAINING_BWD, "wu": capi.PASS_TRAINING_WU}.get(
+                self.pass_, capi.PASS_TRAINING_FWD)
+            self.plan = capi.conv_plan(p, pass_id).as_dict()
             self.bytes = self.plan["bytes"]
             per_set = 2 * (int(np.prod(x_shape)) + int(np.prod(y_shape)))
             out_shape = {"fwd": y_shape, "bwd": x_shape, "wu": w_shape}[self.pass_]
