@@ -227,7 +227,16 @@ class Workload:
                 from poplibs_b200 import parallel
                 # weak scaling: every rank holds one full per-GPU batch of the layer
                 glob = dict(kw, batch=kw["batch"] * world)
-                self.sharded = parallel.ShardedConv(ctx, glob, rank, world)
+                self.allreduce = "none (no collective on this pass)"
+                peer = self.pass_ == "wu" and os.environ.get("PLB_BENCH_ALLREDUCE", "p2p") == "p2p"
+                try:
+                    self.sharded = parallel.ShardedConv(ctx, glob, rank, world, peer_allreduce=peer)
+                    if self.pass_ == "wu":
+                        self.allreduce = ("library kernel over NVLink peer memory" if peer
+                                          else "nccl all_reduce + cast")
+                except Exception as e:  # symmetric memory unavailable: the process group's all-reduce
+                    self.sharded = parallel.ShardedConv(ctx, glob, rank, world)
+                    self.allreduce = f"nccl all_reduce + cast (peer memory unavailable: {type(e).__name__})"
             pass_id = {"bwd": capi.PASS_TRAINING_BWD, "wu": capi.PASS_TRAINING_WU}.get(
                 self.pass_, capi.PASS_TRAINING_FWD)
             self.plan = capi.conv_plan(p, pass_id).as_dict()
@@ -284,6 +293,23 @@ class Workload:
         else:
             # per-rank batch reduced locally, then the one collective of the path
             self.sharded.wu(d["x"], d["dy"], d["out"], d["out32"])
+
+    def check_allreduce(self):
+        """One untimed step of the multi-GPU weight update compared with the
+        process group's own all-reduce of the per-rank gradients."""
+        import torch
+        import torch.distributed as dist
+        d = self.dev[0]
+        local = torch.empty_like(d["out32"])
+        self.ctx.conv_wu(self.p, d["x"], d["dy"], None, local)
+        self.ctx.synchronize()
+        dist.all_reduce(local)
+        self.sharded.wu(d["x"], d["dy"], d["out"], d["out32"])
+        self.ctx.synchronize()
+        torch.cuda.synchronize()
+        diff = float((local - d["out32"]).abs().max().item())
+        scale = float(local.abs().max().item())
+        return {"max_abs_diff_vs_nccl": diff, "max_abs": scale}
 
     def step_e2e(self, i):
         if self.kind == "gemm":
@@ -383,6 +409,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time one library call per step instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -432,6 +460,10 @@ def main():
     ctx = capi.Context(local_rank, stream=torch_stream.cuda_stream)
     wl = Workload(args.workload, spec, ctx, device, rank, world)
     config["plan"] = wl.plan
+    if world > 1 and spec["kind"] == "conv":
+        config["allreduce"] = wl.allreduce
+        if spec["pass_"] == "wu":
+            config["allreduce_check"] = wl.check_allreduce()
     if spec["kind"] == "conv":
         config["per_gpu_batch"] = spec["params"]["batch"]
         config["global_batch"] = spec["params"]["batch"] * world
@@ -444,32 +476,72 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(step_fn, steps, warmup):
+    def timed(step_fn, steps, warmup, graph_sets=0):
+        """Times `steps` calls of step_fn on the device.  With graph_sets = n the
+        steps are replayed from a CUDA graph of n consecutive steps (one per
+        rotating buffer set), which takes the host's per-launch cost (argument
+        marshalling, tensor-map encoding) out of a loop of microsecond kernels."""
         with torch.cuda.stream(stream):
             for i in range(warmup):
                 step_fn(i)
         barrier()
+        graph = None
+        if graph_sets:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for i in range(graph_sets):
+                        step_fn(i)
+                with torch.cuda.stream(stream):
+                    graph.replay()  # untimed: uploads the graph
+                barrier()
+            except Exception as e:  # capture not possible: plain launches
+                print(f"bench: CUDA graph capture failed ({type(e).__name__}: {e}); "
+                      "timing plain launches", file=sys.stderr)
+                graph = None
+                torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = ctx.launch_count()
         with torch.cuda.stream(stream):
             start.record()
-            for i in range(steps):
-                step_fn(warmup + i)
+            if graph is not None:
+                replays, rest = divmod(steps, graph_sets)
+                for _ in range(replays):
+                    graph.replay()
+                for i in range(rest):
+                    step_fn(i)
+            else:
+                for i in range(steps):
+                    step_fn(warmup + i)
             end.record()
         end.synchronize()
         barrier()
         ms = start.elapsed_time(end)
         launches = ctx.launch_count() - launches0
+        if graph is not None:
+            # replayed kernels are not counted by the library: add them
+            launches += (steps // graph_sets) * graph_sets * wl.launches_per_step
         if world > 1:
             t = torch.tensor([ms], device=device, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        return ms, launches
+        return ms, launches, graph is not None
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms, launches = timed(wl.step, args.steps, args.warmup)
+    # kernels per step, counted on one untimed step
+    n0 = ctx.launch_count()
+    with torch.cuda.stream(stream):
+        wl.step(0)
+    barrier()
+    wl.launches_per_step = ctx.launch_count() - n0
+    # The multi-GPU weight update passes a step counter to its all-reduce kernel,
+    # so its steps cannot be replayed from a graph.
+    use_graph = not args.no_graph and not (world > 1 and spec.get("pass_") == "wu")
+    ms, launches, graphed = timed(wl.step, args.steps, args.warmup, wl.nsets if use_graph else 0)
+    config["launch"] = (f"CUDA graph of {wl.nsets} steps (one per buffer set), replayed" if graphed
+                        else "one library call per step")
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
     value = wl.flops * world / (ms_per_step * 1e-3) / 1e12
@@ -477,7 +549,7 @@ def main():
     e2e = None
     if wl.has_e2e():
         e2e_steps = max(3, min(args.steps, 20))
-        ms_e, _ = timed(wl.step_e2e, e2e_steps, 3)
+        ms_e, _, _ = timed(wl.step_e2e, e2e_steps, 3)
         e2e = {"value": wl.flops * world / (ms_e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
                "ms_per_step": ms_e / e2e_steps}

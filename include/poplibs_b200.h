@@ -245,6 +245,25 @@ PLB_API int plb_conv_wu_static_scratch(int device, void *cuda_stream, const plb_
                                const plb_conv_options *opt, const void *d_acts,
                                const void *d_out_grads, void *d_weight_grads,
                                float *d_weight_grads_f32);
+/* All-reduce (sum) of `count` fp32 values over NVLink peer memory, fused with
+ * the cast to half: the multi-GPU step of the weight update.  No counterpart in
+ * the reference (which spreads one convolution over IPU tiles in one graph);
+ * it replaces ncclAllReduce + cast for this small message.
+ *   d_buffers[r]     rank r's input, addressable from this GPU (symmetric /
+ *                    IPC-mapped memory, one process per GPU), 16-byte aligned;
+ *   d_signal_pads[r] rank r's signal pad: plb_allreduce_p2p_signal_bytes(world)
+ *                    bytes, zero before the first call, used only by this call;
+ *   epoch            1, 2, 3, ... the same on every rank for the same step.
+ * The caller must alternate between two input buffers on successive epochs (a
+ * peer may still be reading the previous one).  Every rank must make the call:
+ * the kernel waits, with a cycle budget, for all peers' flags and reports a
+ * missing peer through the context's status word (plb_synchronize).  Sums are
+ * formed in rank order, so all ranks get identical bits.  Either output may be
+ * null. */
+PLB_API int plb_allreduce_f32_p2p(plb_context *ctx, int32_t rank, int32_t world,
+                          const void *const *d_buffers, void *const *d_signal_pads,
+                          uint32_t epoch, size_t count, float *d_out_f32, void *d_out_half);
+PLB_API uint32_t plb_allreduce_p2p_signal_bytes(int32_t world);
 /* weights += scale * weight_grads_f32, cast to the weights' type
  * (popops::scaledAddTo in convolutionWeightUpdate, lib/poplin/Convolution.cpp:3509-3522). */
 PLB_API int plb_scaled_add_to(plb_context *ctx, int32_t dtype, void *d_weights,

@@ -135,6 +135,7 @@ SYMBOLS = (
     "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution",
     "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
     "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_bias_update", "plb_conv_fwd_host",
+    "plb_allreduce_f32_p2p", "plb_allreduce_p2p_signal_bytes",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
     "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
     "plb_weights_transpose_chans_flip_xy", "plb_transpose_matrix", "plb_matmul_plan",
@@ -186,6 +187,9 @@ def lib():
     L.plb_cast_from_f32.argtypes = [vp, i32, vp, vp, sz]
     L.plb_add_bias.argtypes = [vp, i32, vp, vp, u64, u32]
     L.plb_conv_bias_update.argtypes = [vp, i32, vp, u64, u32, i32, vp, f32]
+    L.plb_allreduce_f32_p2p.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u32, sz, vp, vp]
+    L.plb_allreduce_p2p_signal_bytes.argtypes = [i32]
+    L.plb_allreduce_p2p_signal_bytes.restype = u32
     L.plb_conv_fwd_host.argtypes = [vp, CP, OP, vp, vp, vp, vp]
     for name in ("plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device"):
         getattr(L, name).argtypes = [vp, u32, u32, u32, u64, vp, vp]
@@ -255,6 +259,10 @@ class Context:
     def synchronize(self):
         _check(lib().plb_synchronize(self._h))
 
+    def memset(self, dst, value: int, nbytes: int):
+        """Fills device memory on the context's stream."""
+        _check(lib().plb_memset(self._h, _ptr(dst), value, nbytes))
+
     def launch_count(self) -> int:
         return int(lib().plb_launch_count(self._h))
 
@@ -292,6 +300,13 @@ class Context:
     def conv_bias_update(self, acts_dtype, out_grads, pixels, chans, bias_dtype, biases, scale):
         _check(lib().plb_conv_bias_update(self._h, acts_dtype, _ptr(out_grads), pixels, chans,
                                           bias_dtype, _ptr(biases), scale))
+
+    def allreduce_f32_p2p(self, rank, world, buffer_ptrs, signal_pad_ptrs, epoch, count, out_f32, out_half):
+        """buffer_ptrs / signal_pad_ptrs: `world` device addresses (ints)."""
+        bufs = (C.c_void_p * world)(*[int(p) for p in buffer_ptrs])
+        pads = (C.c_void_p * world)(*[int(p) for p in signal_pad_ptrs])
+        _check(lib().plb_allreduce_f32_p2p(self._h, rank, world, bufs, pads, epoch, count,
+                                           _ptr(out_f32), _ptr(out_half)))
 
     def cast_from_f32(self, dtype, dst, src, count):
         _check(lib().plb_cast_from_f32(self._h, dtype, _ptr(dst), _ptr(src), count))

@@ -48,7 +48,7 @@ constexpr int kStageKBytes = 128;  // bytes of K per pipeline stage row (one swi
 constexpr int kIgemmThreads = 640;
 constexpr int kIgemmProducers = PLB_IGEMM_PRODUCERS;
 constexpr int kIgemmMmaWarp = 3;
-constexpr int kEpiStagingBytes = 8 * 4096;  // 8 epilogue warps x (32 rows x 128 B)
+constexpr int kEpiStagingBytes = 8 * 4096;  // 8 pairs of epilogue warps x (32 rows x 128 B)
 static_assert(kIgemmProducers >= 1 && kIgemmProducers <= 3, "producer warps are warps 0..2");
 
 struct IgemmArgs {
@@ -325,13 +325,16 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       // which alone announces the byte count (both CTAs' shares)
       constexpr uint32_t kPairFactor = k2Cta ? 2u : 1u;
       if constexpr (kResB) {
-        if (me == 0 && first_unit < total_tiles) {
-          // single N tile: every tile of this CTA uses the same weights
-          if (leader) mbar_expect_tx(resb_bar, kPairFactor * uint32_t(k_iters) * S::kBBytes);
+        if (first_unit < total_tiles) {
+          // single N tile: every tile of this CTA uses the same weights.  The
+          // producers share the copies (a copy costs its issuing thread on the
+          // order of a hundred cycles and the first MMA waits for all of them).
+          if (me == 0 && leader)
+            mbar_expect_tx(resb_bar, kPairFactor * uint32_t(k_iters) * S::kBBytes);
           const uint32_t resb_bar_lead = lead_bar(resb_bar);
           int r = 0, s = 0, kc = 0;
           for (int it = 0; it < k_iters; ++it) {
-            load_b(resb_base + it * S::kBBytes, resb_bar_lead, r, s, kc, 0);
+            if (it % P == me) load_b(resb_base + it * S::kBBytes, resb_bar_lead, r, s, kc, 0);
             if (++kc == args.k_chunks) {
               kc = 0;
               if (++s == args.taps_w) {
@@ -576,6 +579,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     int qw, qh, qn;
     row_pixel(quarter * 32, qw, qh, qn);
     const int pair = group * 4 + quarter;    // staging buffer and named barrier of the two warps
+    // one staging buffer per pair (a second one was measured: it costs a
+    // pipeline stage and hides nothing, the chain below is bound by its own
+    // instructions and synchronisation, not by the store reading the buffer)
     const uint32_t buf = staging_base + uint32_t(pair) * 4096u;
     const uint32_t row_addr = buf + uint32_t(lane) * 128u;
     const bool tma_store = args.use_tma_store != 0;
@@ -639,8 +645,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       auto finish = [&](const uint32_t (&v)[32], float (&f)[32], const int c) {
         const int col0 = col_base + c;
         const int valid = min(32, args.n_total - col0);  // may be <= 0 on a padded N tile
+        if (args.alpha != 1.f) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * args.alpha;
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * args.alpha;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        }
         if (args.bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -710,7 +721,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         }
       };
       // issue (lane 0) the tensor store of the staged buffer: columns [store_col, +128 bytes)
-      auto store_staged = [&](const int store_col) {
+      auto store_staged = [&](const uint32_t buf, const int store_col) {
         if (lane == 0) {
           // a box that starts outside the tensor has nothing to write
           if (store_col < args.n_total && box_ok) {
@@ -739,7 +750,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       } else if (out_f32) {
         // (half == 0 warps only) one 32-column chunk per staged buffer and store
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = 0; c < BN; c += 32, ++blocks_done) {
           __syncwarp();
           tmem_ld_32x32(t_addr + c, v);
           tmem_ld_wait_for(v);
@@ -754,25 +765,32 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                          __float_as_uint(f[4 * j + 3]));
           fence_proxy_async_smem();
           __syncwarp();
-          store_staged(col_base + c);
+          store_staged(buf, col_base + c);
         }
       } else {
         // half output: this warp's 32 columns are one 64-byte half of the staged
         // rows; 16-byte pieces are XOR-swizzled with the row index, the pattern
-        // the tensor map uses
+        // the tensor map uses.  Block k is stored by the warp with half == k mod 2;
+        // before block k + 1 is staged, that warp waits until its store has
+        // read the buffer.
 #pragma unroll 1
         for (int c = 0; c < BN; c += 64, ++blocks_done) {
+          [[maybe_unused]] const bool fine = stamp && local_tile == 2;
+          [[maybe_unused]] const int fslot = 2048 + (c >> 6) * 8;
+          if (fine) PLB_TRACE_STAMP(2, fslot + 0);
           __syncwarp();
           tmem_ld_32x32(t_addr + c + half * 32, v);
           tmem_ld_wait_for(v);
+          if (fine) PLB_TRACE_STAMP(2, fslot + 1);
           if (c + 64 >= BN) release_accumulator();
           finish(v, f, c + half * 32);
+          const bool stores_now = (blocks_done & 1u) == uint32_t(half);
           // the warp that stored the previous block waits until that store has
           // read the buffer; then both may overwrite it
-          const bool stored_last = ((blocks_done + 1u) & 1u) == uint32_t(half);
-          const bool stores_now = (blocks_done & 1u) == uint32_t(half);
-          if (stored_last && lane == 0) tma_store_wait_read<0>();
+          if (!stores_now && lane == 0) tma_store_wait_read<0>();
+          if (fine) PLB_TRACE_STAMP(2, fslot + 2);
           pair_sync(pair_free_bar(pair));  // buffer free
+          if (fine) PLB_TRACE_STAMP(2, fslot + 3);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             __half2 h0 = __floats2half2_rn(f[8 * j], f[8 * j + 1]);
@@ -784,10 +802,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
                          *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
           }
           fence_proxy_async_smem();
+          if (fine) PLB_TRACE_STAMP(2, fslot + 4);
           pair_sync(pair_staged_bar(pair));  // buffer staged by both warps
           pair_phase ^= 1u;
+          if (fine) PLB_TRACE_STAMP(2, fslot + 5);
           if (!pair_ok) break;
-          if (stores_now) store_staged(col_base + c);
+          if (stores_now) store_staged(buf, col_base + c);
+          if (fine) PLB_TRACE_STAMP(2, fslot + 6);
         }
         if (!pair_ok) break;
       }

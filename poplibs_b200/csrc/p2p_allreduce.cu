@@ -1,0 +1,160 @@
+// All-reduce of the fp32 weight gradient over NVLink peer memory, fused with
+// the cast to the weights' type.
+//
+// The weight-update pass of a batch-sharded convolution leaves one full-size
+// fp32 gradient per GPU (a few hundred KB); the gradient of the whole batch is
+// their sum.  For a message this small a library all-reduce is dominated by
+// its launch and protocol latency.  Here every rank keeps its gradient in a
+// buffer that all peers can address (symmetric memory, one process per GPU),
+// and ONE kernel per rank
+//   1. tells every peer that this rank's buffer is complete (a flag written
+//      into the peer's signal pad over NVLink),
+//   2. waits, with a cycle budget, for the same flag from every peer,
+//   3. reads all ranks' buffers with plain peer loads, adds them in rank
+//      order (so every rank computes bit-identical sums) and writes the fp32
+//      sum and/or its cast to local memory.
+// No multicast objects and no TMA are involved: plain loads and stores to peer
+// pointers.  The kernels of different ranks wait on one another, which is only
+// sound because each runs on its own GPU.
+//
+// Re-use of the buffers: the caller alternates between two halves of its
+// symmetric buffer by the parity of `epoch`.  A rank can start step e + 2
+// (which overwrites the half read in step e) only after every peer has sent
+// its flag of step e + 1, i.e. after that peer's kernel of step e has retired.
+//
+// The reference has no counterpart (it spreads one convolution over IPU tiles
+// inside a single graph); this replaces the ncclAllReduce + cast that the
+// multi-GPU weight update would otherwise use.
+#include <cuda_fp16.h>
+
+#include <string>
+
+#include "runtime.h"
+#include "sm100_prims.cuh"
+
+namespace plb {
+namespace {
+
+constexpr int kP2pMaxWorld = 16;
+constexpr int kP2pBlocks = 32;      // blocks per rank; slot (source rank, block) in a signal pad
+constexpr int kP2pThreads = 256;
+constexpr int kStatusPeerTimeout = 5;  // a peer's flag did not arrive within the cycle budget
+
+struct P2pArgs {
+  const float *buffers[kP2pMaxWorld];   // every rank's gradient (this step's half)
+  uint32_t *signal_pads[kP2pMaxWorld];  // every rank's signal pad
+  int rank, world;
+  uint32_t epoch;
+  size_t count4;  // float4 elements
+  float4 *out_f32;
+  uint2 *out_half;
+  int *status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// peer data must come from the peer, not from a stale line of this GPU's caches
+__device__ __forceinline__ float4 ld_peer_f4(const float4 *p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(kP2pThreads)
+p2pAllReduceKernel(const P2pArgs a) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  // 1 + 2: flags.  Thread r of the block handles peer r.
+  if (threadIdx.x < unsigned(a.world) && int(threadIdx.x) != a.rank) {
+    const int peer = int(threadIdx.x);
+    // my flag in the peer's pad: slot (my rank, block)
+    st_release_sys(a.signal_pads[peer] + a.rank * kP2pBlocks + blockIdx.x, a.epoch);
+    // the peer's flag in my pad: slot (peer, block); epochs only grow
+    const uint32_t *mine = a.signal_pads[a.rank] + peer * kP2pBlocks + blockIdx.x;
+    const long long start = clock64();
+    while (int32_t(ld_acquire_sys(mine) - a.epoch) < 0) {
+      if (clock64() - start > kWaitCycleLimit) {
+        atomicCAS(a.status, kStatusOk, kStatusPeerTimeout);
+        ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!ok) return;
+  // 3: sum in rank order
+  for (size_t i = blockIdx.x * size_t(kP2pThreads) + threadIdx.x; i < a.count4;
+       i += size_t(gridDim.x) * kP2pThreads) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < a.world; ++r) {
+      const float4 *src = reinterpret_cast<const float4 *>(a.buffers[r]) + i;
+      const float4 v = r == a.rank ? *src : ld_peer_f4(src);
+      s.x += v.x;
+      s.y += v.y;
+      s.z += v.z;
+      s.w += v.w;
+    }
+    if (a.out_f32) a.out_f32[i] = s;
+    if (a.out_half) {
+      const __half2 lo = __floats2half2_rn(s.x, s.y), hi = __floats2half2_rn(s.z, s.w);
+      a.out_half[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                                 *reinterpret_cast<const uint32_t *>(&hi));
+    }
+  }
+}
+
+}  // namespace
+}  // namespace plb
+
+using namespace plb;
+
+extern "C" int plb_allreduce_f32_p2p(plb_context *ctx, int32_t rank, int32_t world,
+                                     const void *const *d_buffers, void *const *d_signal_pads,
+                                     uint32_t epoch, size_t count, float *d_out_f32,
+                                     void *d_out_half) {
+  if (int rc = activate(ctx)) return rc;
+  if (world < 1 || world > kP2pMaxWorld || rank < 0 || rank >= world)
+    return fail(PLB_ERR_INVALID_PARAMS, "rank / world size out of range (at most " +
+                                            std::to_string(kP2pMaxWorld) + " ranks)");
+  if (!d_buffers || !d_signal_pads) return fail(PLB_ERR_INVALID_PARAMS, "null pointer table");
+  if (count % 4 != 0) return fail(PLB_ERR_INVALID_PARAMS, "element count must be a multiple of 4");
+  if (epoch == 0) return fail(PLB_ERR_INVALID_PARAMS, "epochs start at 1 (pads are zero-initialised)");
+  if (count == 0) return PLB_OK;
+  P2pArgs a{};
+  for (int r = 0; r < world; ++r) {
+    if (!d_buffers[r] || !d_signal_pads[r]) return fail(PLB_ERR_INVALID_PARAMS, "null peer pointer");
+    if ((reinterpret_cast<uintptr_t>(d_buffers[r]) & 15) != 0)
+      return fail(PLB_ERR_INVALID_PARAMS, "peer buffers must be 16-byte aligned");
+    a.buffers[r] = static_cast<const float *>(d_buffers[r]);
+    a.signal_pads[r] = static_cast<uint32_t *>(d_signal_pads[r]);
+  }
+  if ((reinterpret_cast<uintptr_t>(d_out_f32) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(d_out_half) & 7) != 0)
+    return fail(PLB_ERR_INVALID_PARAMS, "outputs must be 16-byte (fp32) / 8-byte (half) aligned");
+  a.rank = rank;
+  a.world = world;
+  a.epoch = epoch;
+  a.count4 = count / 4;
+  a.out_f32 = reinterpret_cast<float4 *>(d_out_f32);
+  a.out_half = static_cast<uint2 *>(d_out_half);
+  a.status = ctx->d_status;
+  // every rank launches the same number of blocks: flags are exchanged per block
+  p2pAllReduceKernel<<<kP2pBlocks, kP2pThreads, 0, ctx->stream>>>(a);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+extern "C" uint32_t plb_allreduce_p2p_signal_bytes(int32_t world) {
+  return uint32_t(world) * kP2pBlocks * uint32_t(sizeof(uint32_t));
+}

@@ -306,10 +306,13 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\t"
                "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on a barrier that may live in the other CTA of the cluster.
+// Arrive on a barrier that may live in the other CTA of the cluster.  Default
+// semantics (release at CTA scope): the arrival only publishes that this
+// thread's tensor-memory reads are done (ordered by tcgen05.fence), no data
+// written to memory travels with it, and a cluster-scope release was measured
+// at over a thousand cycles per arrival.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 // Tensor copies whose completion may be signalled to the pair's other CTA.
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *tm,

@@ -10,6 +10,9 @@ CPU tests).  The path shards without communication except in one place:
 * convolution weight update: each rank reduces its batch slice to a full-size
   fp32 weight gradient; ONE all-reduce (sum) makes it the gradient of the whole
   batch, which is then cast to the weights' type.  This is the only collective.
+  On GPUs it is a kernel of this library over NVLink peer memory
+  (PeerAllReduce: flags + peer loads + the cast in one launch per rank); the
+  process group's all_reduce (NCCL / gloo) is the fallback and the checker.
 
 The reference has no counterpart: it spreads one convolution over the tiles of
 several IPUs inside a single graph (lib/poplin/ConvPlan.hpp:28-77).
@@ -49,14 +52,63 @@ def allreduce_weight_grads(dw_f32, group=None):
     return dw_f32
 
 
+class PeerAllReduce:
+    """Sum of one fp32 vector per rank over NVLink peer memory
+    (plb_allreduce_f32_p2p): every rank writes its vector into its half of a
+    symmetric buffer, one kernel per rank exchanges flags with the peers, adds
+    all ranks' vectors in rank order and writes the fp32 sum and its half cast.
+
+    The symmetric buffer comes from torch.distributed's symmetric memory (one
+    process per GPU, peers mapped through CUDA IPC / fabric handles)."""
+
+    def __init__(self, ctx: capi.Context, count: int, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        if count % 4:
+            raise ValueError("element count must be a multiple of 4")
+        self.ctx, self.count = ctx, count
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        device = torch.device("cuda", torch.cuda.current_device())
+        # two halves, used on alternate steps: a peer may still read the last one
+        self.buf = symm_mem.empty((2, count), dtype=torch.float32, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        need = capi.lib().plb_allreduce_p2p_signal_bytes(self.world)
+        if self.handle.signal_pad_size < need:
+            raise RuntimeError(f"signal pad of {self.handle.signal_pad_size} bytes is smaller than {need}")
+        self.buffer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.signal_ptrs = [int(p) for p in self.handle.signal_pad_ptrs]
+        self.epoch = 0
+
+    def input(self):
+        """The buffer (a torch view, `count` floats) this rank must fill for the next call."""
+        return self.buf[(self.epoch + 1) & 1]
+
+    def run(self, out_f32=None, out_half=None):
+        """All ranks call this after filling input(); enqueued on the context's stream."""
+        self.epoch += 1
+        offset = (self.epoch & 1) * self.count * 4
+        self.ctx.allreduce_f32_p2p(self.rank, self.world, [p + offset for p in self.buffer_ptrs],
+                                   self.signal_ptrs, self.epoch, self.count, out_f32, out_half)
+
+
 class ShardedConv:
     """One rank's part of a batch-sharded convolution layer."""
 
     def __init__(self, ctx: capi.Context, make_kwargs: dict, rank: int = 0, world: int = 1,
-                 group=None, opt: Optional[capi.ConvOptions] = None):
+                 group=None, opt: Optional[capi.ConvOptions] = None, peer_allreduce: bool = False):
         self.ctx, self.rank, self.world, self.group, self.opt = ctx, rank, world, group, opt
         self.params, self.begin, self.end = local_conv_params(make_kwargs, rank, world)
         self.global_batch = int(make_kwargs["batch"])
+        # the all-reduce over peer memory needs GPUs that can address one another
+        self.peer = None
+        if peer_allreduce and world > 1:
+            p = self.params
+            count = int(p.groups) * int(p.out_chans_per_group) * int(p.in_chans_per_group)
+            for i in range(p.num_field_dims):
+                count *= int(p.kernel[i])
+            self.peer = PeerAllReduce(ctx, count, group)
 
     def fwd(self, x_local, w, y_local, bias=None):
         if self.params.batch:
@@ -70,6 +122,16 @@ class ShardedConv:
         """dw (weights' type) and dw_f32 receive the gradient of the WHOLE batch
         on every rank.  dw_f32 is a torch tensor on the context's device."""
         import torch
+        if self.peer is not None:
+            # local gradient straight into this step's half of the symmetric
+            # buffer; one kernel then sums all ranks' halves and casts
+            mine = self.peer.input()
+            if self.params.batch:
+                self.ctx.conv_wu(self.params, x_local, dy_local, None, mine, opt=self.opt)
+            else:
+                self.ctx.memset(mine, 0, mine.numel() * 4)
+            self.peer.run(dw_f32, dw)
+            return
         if self.params.batch:
             self.ctx.conv_wu(self.params, x_local, dy_local, None, dw_f32, opt=self.opt)
         else:

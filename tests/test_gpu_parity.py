@@ -370,6 +370,52 @@ def test_conv_bias_update(gpu_ctx):
     assert_exact(db.cpu().numpy(), dbias, "bias gradient vs model")
 
 
+def test_allreduce_over_peer_memory_on_one_gpu(gpu_ctx):
+    """plb_allreduce_f32_p2p with all "ranks'" buffers on this GPU and the
+    peers' flags already set: checks the flags this rank writes, the rank-order
+    sum and the cast.  Then a step whose peers never signal: the kernel's
+    bounded wait must run out and report it, leaving the context usable."""
+    import torch
+    ctx = T.context()
+    world, rank, count = 3, 1, 4 * 1031
+    blocks = capi.lib().plb_allreduce_p2p_signal_bytes(world) // (4 * world)
+    g = torch.Generator().manual_seed(3)
+    bufs = [torch.randn(count, generator=g).cuda() for _ in range(world)]
+    pads = [torch.zeros(world * blocks, dtype=torch.int32, device="cuda") for _ in range(world)]
+    for peer in range(world):
+        if peer != rank:
+            pads[rank][peer * blocks:(peer + 1) * blocks] = 1   # "the peers' flags of epoch 1 arrived"
+    out32 = torch.empty(count, device="cuda")
+    out16 = torch.empty(count, device="cuda", dtype=torch.float16)
+    torch.cuda.synchronize()
+    ctx.allreduce_f32_p2p(rank, world, [b.data_ptr() for b in bufs], [p.data_ptr() for p in pads], 1,
+                          count, out32, out16)
+    ctx.synchronize()
+    want = (bufs[0] + bufs[1]) + bufs[2]          # rank order, fp32
+    assert torch.equal(out32, want)
+    assert torch.equal(out16, want.half())
+    for peer in range(world):
+        if peer != rank:
+            assert bool((pads[peer][rank * blocks:(rank + 1) * blocks] == 1).all()), "flag not sent"
+    # only one output requested
+    out32.zero_()
+    ctx.allreduce_f32_p2p(rank, world, [b.data_ptr() for b in bufs], [p.data_ptr() for p in pads], 1,
+                          count, out32, None)
+    ctx.synchronize()
+    assert torch.equal(out32, want)
+    # epoch 2: nobody signals -> the wait runs out (about two seconds) and is reported
+    ctx.allreduce_f32_p2p(rank, world, [b.data_ptr() for b in bufs], [p.data_ptr() for p in pads], 2,
+                          count, out32, None)
+    with pytest.raises(capi.PlbError):
+        ctx.synchronize()
+    # the context still works
+    ctx.allreduce_f32_p2p(0, 1, [bufs[0].data_ptr()], [pads[0].data_ptr()], 1, count, out32, None)
+    ctx.synchronize()
+    assert torch.equal(out32, bufs[0])
+    with pytest.raises(capi.PlbError):
+        ctx.allreduce_f32_p2p(0, 1, [bufs[0].data_ptr()], [pads[0].data_ptr()], 0, count, out32, None)
+
+
 def test_small_channel_stem_layers(gpu_ctx):
     # 3-channel inputs go through the space-to-depth path
     for kw in (conv_case(2, [18, 22], [7, 7], 3, 64, padding=3, stride=2),
