@@ -32,6 +32,11 @@ const bool g_disable_resident = [] {
   return e != nullptr && e[0] == '1';
 }();
 
+// PLB_DISABLE_PDL=1 launches without programmatic stream serialization.
+const bool g_disable_pdl = [] {
+  const char *e = std::getenv("PLB_DISABLE_PDL");
+  return e != nullptr && e[0] == '1';
+}();
 // PLB_DISABLE_CTA_PAIR=1 keeps every CTA on its own 128-row MMAs.
 const bool g_disable_pair = [] {
   const char *e = std::getenv("PLB_DISABLE_CTA_PAIR");
@@ -63,36 +68,48 @@ int launchInstance(plb_context *ctx, const CUtensorMap &ta, const CUtensorMap &t
     }
     const int smem =
         S::totalBytes(args.a_stage_bytes, args.b_tiles_per_stage, args.num_stages, resident_bytes);
+    // Launch attributes: programmatic stream serialization (the kernel's set-up
+    // may overlap the previous kernel's tail; it waits before touching global
+    // memory) and, for CTA pairs, clusters of two.
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(kIgemmThreads);
+    cfg.dynamicSmemBytes = size_t(smem);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    if (!g_disable_pdl) {
+      attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+      ++n_attr;
+    }
     if constexpr (!k2Cta) {
-      kernel<<<grid, kIgemmThreads, smem, ctx->stream>>>(ta, tb, tout, args);
+      cfg.gridDim = dim3(unsigned(grid));
     } else {
-      // clusters of two CTAs; a persistent grid of as many clusters as can be
-      // resident at once (pairs of SMs in one GPC), each walking tile pairs
-      cudaLaunchConfig_t cfg{};
-      cfg.blockDim = dim3(kIgemmThreads);
-      cfg.dynamicSmemBytes = size_t(smem);
-      cfg.stream = ctx->stream;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = 2;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
+      // a persistent grid of as many clusters as can be resident at once
+      // (pairs of SMs in one GPC), each walking tile pairs
+      attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+      attr[n_attr].val.clusterDim.x = 2;
+      attr[n_attr].val.clusterDim.y = 1;
+      attr[n_attr].val.clusterDim.z = 1;
+      ++n_attr;
       if (max_clusters[dev] == 0) {
         // queried with the largest shared-memory size, a lower bound for smaller ones
-        cfg.gridDim = dim3(unsigned(2 * ctx->sm_count));
-        cfg.dynamicSmemBytes = size_t(kIgemmSmemLimit);
+        cudaLaunchConfig_t q = cfg;
+        q.gridDim = dim3(unsigned(2 * ctx->sm_count));
+        q.dynamicSmemBytes = size_t(kIgemmSmemLimit);
+        q.attrs = &attr[n_attr - 1];
+        q.numAttrs = 1;
         int n = 0;
-        PLB_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        PLB_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &q));
         if (n <= 0) return fail(PLB_ERR_CUDA, "no cluster of two CTAs can be resident on this device");
         max_clusters[dev] = n;
-        cfg.dynamicSmemBytes = size_t(smem);
       }
       const int clusters = std::max(1, std::min(grid / 2, max_clusters[dev]));
       cfg.gridDim = dim3(unsigned(2 * clusters));
-      PLB_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tout, args));
     }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    PLB_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tout, args));
     PLB_CUDA(cudaGetLastError());
     ctx->launches++;
     return PLB_OK;

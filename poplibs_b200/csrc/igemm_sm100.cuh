@@ -236,6 +236,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   if constexpr (k2Cta) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Everything above touched only this SM (barriers, tensor memory): with a
+  // programmatic launch it overlaps the tail of the previous kernel in the
+  // stream.  From here on global memory is read and written.
+  pdl_launch_dependents();
+  pdl_wait();
 
   // Work units: output tiles, or with a CTA pair, pairs of M tiles (the odd
   // last one is padded: its copies read zeros and its stores are clipped).

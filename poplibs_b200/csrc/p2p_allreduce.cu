@@ -7,10 +7,13 @@
 // its launch and protocol latency.  Here every rank keeps its gradient in a
 // buffer that all peers can address (symmetric memory, one process per GPU),
 // and ONE kernel per rank
-//   1. tells every peer that this rank's buffer is complete (a flag written
-//      into the peer's signal pad over NVLink),
-//   2. waits, with a cycle budget, for the same flag from every peer,
-//   3. reads all ranks' buffers with plain peer loads, adds them in rank
+//   1. tells every peer that this rank's buffer is complete (block 0: a flag
+//      written into each peer's signal pad over NVLink),
+//   2. waits, with a cycle budget, for the same flag from every peer, then
+//      releases the kernel's other blocks through a word in local memory,
+//   3. reads all ranks' buffers with plain peer loads (one 16-byte load per
+//      rank per thread, all in flight together: the message is small, so the
+//      time is a few NVLink round trips, not bandwidth), adds them in rank
 //      order (so every rank computes bit-identical sums) and writes the fp32
 //      sum and/or its cast to local memory.
 // No multicast objects and no TMA are involved: plain loads and stores to peer
@@ -27,6 +30,7 @@
 // multi-GPU weight update would otherwise use.
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <string>
 
 #include "runtime.h"
@@ -36,9 +40,12 @@ namespace plb {
 namespace {
 
 constexpr int kP2pMaxWorld = 16;
-constexpr int kP2pBlocks = 32;      // blocks per rank; slot (source rank, block) in a signal pad
 constexpr int kP2pThreads = 256;
 constexpr int kStatusPeerTimeout = 5;  // a peer's flag did not arrive within the cycle budget
+
+// Signal pad of a rank, 32-bit words: [r] = latest epoch announced by rank r,
+// [kP2pMaxWorld] = latest epoch this rank's own block 0 has seen from everyone.
+constexpr int kP2pGoSlot = kP2pMaxWorld;
 
 struct P2pArgs {
   const float *buffers[kP2pMaxWorld];   // every rank's gradient (this step's half)
@@ -68,41 +75,72 @@ __device__ __forceinline__ float4 ld_peer_f4(const float4 *p) {
                : "memory");
   return v;
 }
+// epochs only grow; compare modulo 2^32
+__device__ __forceinline__ bool reached(uint32_t seen, uint32_t epoch) {
+  return int32_t(seen - epoch) >= 0;
+}
 
 __global__ void __launch_bounds__(kP2pThreads)
 p2pAllReduceKernel(const P2pArgs a) {
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
-  // 1 + 2: flags.  Thread r of the block handles peer r.
-  if (threadIdx.x < unsigned(a.world) && int(threadIdx.x) != a.rank) {
-    const int peer = int(threadIdx.x);
-    // my flag in the peer's pad: slot (my rank, block)
-    st_release_sys(a.signal_pads[peer] + a.rank * kP2pBlocks + blockIdx.x, a.epoch);
-    // the peer's flag in my pad: slot (peer, block); epochs only grow
-    const uint32_t *mine = a.signal_pads[a.rank] + peer * kP2pBlocks + blockIdx.x;
-    const long long start = clock64();
-    while (int32_t(ld_acquire_sys(mine) - a.epoch) < 0) {
-      if (clock64() - start > kWaitCycleLimit) {
-        atomicCAS(a.status, kStatusOk, kStatusPeerTimeout);
-        ok = 0;
-        break;
+  uint32_t *my_pad = a.signal_pads[a.rank];
+  if (blockIdx.x == 0) {
+    // 1 + 2: flags.  Thread r handles peer r.
+    if (threadIdx.x < unsigned(a.world) && int(threadIdx.x) != a.rank) {
+      const int peer = int(threadIdx.x);
+      st_release_sys(a.signal_pads[peer] + a.rank, a.epoch);
+      const long long start = clock64();
+      while (!reached(ld_acquire_sys(my_pad + peer), a.epoch)) {
+        if (clock64() - start > kWaitCycleLimit) {
+          atomicCAS(a.status, kStatusOk, kStatusPeerTimeout);
+          ok = 0;
+          break;
+        }
       }
     }
+    __syncthreads();
+    // release the other blocks (also after a timeout, so that they return)
+    if (threadIdx.x == 0) st_release_sys(my_pad + kP2pGoSlot, ok ? a.epoch : a.epoch | 0x80000000u);
+  } else {
+    if (threadIdx.x == 0) {
+      const long long start = clock64();
+      uint32_t seen;
+      while (true) {
+        seen = ld_acquire_sys(my_pad + kP2pGoSlot);
+        if ((seen & 0x7fffffffu) == (a.epoch & 0x7fffffffu)) break;
+        if (clock64() - start > 2 * kWaitCycleLimit) {
+          atomicCAS(a.status, kStatusOk, kStatusPeerTimeout);
+          seen = 0x80000000u;
+          break;
+        }
+      }
+      if (seen & 0x80000000u) ok = 0;
+    }
+    __syncthreads();
   }
-  __syncthreads();
   if (!ok) return;
-  // 3: sum in rank order
+  // 3: sum in rank order; all of a thread's peer loads are issued before the adds
   for (size_t i = blockIdx.x * size_t(kP2pThreads) + threadIdx.x; i < a.count4;
        i += size_t(gridDim.x) * kP2pThreads) {
+    float4 v[kP2pMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kP2pMaxWorld; ++r) {
+      if (r < a.world) {
+        const float4 *src = reinterpret_cast<const float4 *>(a.buffers[r]) + i;
+        v[r] = r == a.rank ? *src : ld_peer_f4(src);
+      }
+    }
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < a.world; ++r) {
-      const float4 *src = reinterpret_cast<const float4 *>(a.buffers[r]) + i;
-      const float4 v = r == a.rank ? *src : ld_peer_f4(src);
-      s.x += v.x;
-      s.y += v.y;
-      s.z += v.z;
-      s.w += v.w;
+#pragma unroll
+    for (int r = 0; r < kP2pMaxWorld; ++r) {
+      if (r < a.world) {
+        s.x += v[r].x;
+        s.y += v[r].y;
+        s.z += v[r].z;
+        s.w += v[r].w;
+      }
     }
     if (a.out_f32) a.out_f32[i] = s;
     if (a.out_half) {
@@ -148,13 +186,18 @@ extern "C" int plb_allreduce_f32_p2p(plb_context *ctx, int32_t rank, int32_t wor
   a.out_f32 = reinterpret_cast<float4 *>(d_out_f32);
   a.out_half = static_cast<uint2 *>(d_out_half);
   a.status = ctx->d_status;
-  // every rank launches the same number of blocks: flags are exchanged per block
-  p2pAllReduceKernel<<<kP2pBlocks, kP2pThreads, 0, ctx->stream>>>(a);
+  if (epoch & 0x80000000u) return fail(PLB_ERR_INVALID_PARAMS, "epoch must be below 2^31");
+  // one thread per 16 bytes, at most two blocks' worth per SM: block 0 (always
+  // among the first scheduled) exchanges the flags, the others wait for it
+  const size_t want = (a.count4 + kP2pThreads - 1) / kP2pThreads;
+  const unsigned blocks = unsigned(std::max<size_t>(1, std::min<size_t>(want, size_t(ctx->sm_count) * 2)));
+  p2pAllReduceKernel<<<blocks, kP2pThreads, 0, ctx->stream>>>(a);
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;
 }
 
 extern "C" uint32_t plb_allreduce_p2p_signal_bytes(int32_t world) {
-  return uint32_t(world) * kP2pBlocks * uint32_t(sizeof(uint32_t));
+  (void)world;
+  return uint32_t(kP2pMaxWorld + 1) * uint32_t(sizeof(uint32_t));
 }

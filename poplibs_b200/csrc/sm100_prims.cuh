@@ -286,6 +286,20 @@ __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t adesc, uint64_
   }
 }
 
+// ---- programmatic dependent launch -------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may
+// start while its predecessor in the stream is still running.  It must not
+// touch global memory the predecessor reads or writes before pdl_wait(), which
+// returns once the predecessor grid has completed and its writes are visible;
+// pdl_launch_dependents() lets the NEXT kernel in the stream start early.
+// Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- CTA pairs (cta_group::2) ------------------------------------------------
 // Two CTAs of a cluster (ranks 0 and 1) run one tcgen05.mma of M = 256 between
 // them: each holds its own 128 rows of A, half of the B tile's N rows and the
