@@ -225,8 +225,19 @@ int launchWu(cudaStream_t stream, const plb_conv_params &p, const WuShape &s, co
         return rc;
     }
     const int grid = a.co_blocks * a.ci_blocks * a.tap_groups * a.ksplit;
-    wu_kernel<<<grid, kWuThreads, smem, stream>>>(tdy, tx, tout, a);
-    PLB_CUDA(cudaGetLastError());
+    // programmatic stream serialization: the kernels' set-up overlaps the tail
+    // of whatever runs before them; they wait before touching global memory
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(kWuThreads);
+    cfg.dynamicSmemBytes = size_t(smem);
+    cfg.stream = stream;
+    cfg.attrs = pdl;
+    cfg.numAttrs = 1;
+    PLB_CUDA(cudaLaunchKernelEx(&cfg, wu_kernel, tdy, tx, tout, a));
     float *out32 = d_weight_grads_f32 ? d_weight_grads_f32 + size_t(g) * w_elems : nullptr;
     uint8_t *out16 =
         d_weight_grads ? static_cast<uint8_t *>(d_weight_grads) + size_t(g) * w_elems * es : nullptr;
@@ -234,9 +245,15 @@ int launchWu(cudaStream_t stream, const plb_conv_params &p, const WuShape &s, co
         (reinterpret_cast<uintptr_t>(out16) & 7) == 0) {
       const size_t count4 = w_elems / 4;
       const unsigned rgrid = unsigned((count4 + 31) / 32);
-      wu_reduce4_kernel<<<rgrid, dim3(32, kWuReduceLanes), 0, stream>>>(
-          reinterpret_cast<const float4 *>(a.partial), a.ksplit, count4,
-          reinterpret_cast<float4 *>(out32), reinterpret_cast<uint2 *>(out16));
+      cudaLaunchConfig_t rcfg{};
+      rcfg.gridDim = dim3(rgrid);
+      rcfg.blockDim = dim3(32, kWuReduceLanes);
+      rcfg.stream = stream;
+      rcfg.attrs = pdl;
+      rcfg.numAttrs = 1;
+      PLB_CUDA(cudaLaunchKernelEx(&rcfg, wu_reduce4_kernel,
+                                  reinterpret_cast<const float4 *>(a.partial), a.ksplit, count4,
+                                  reinterpret_cast<float4 *>(out32), reinterpret_cast<uint2 *>(out16)));
     } else {
       const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
       wu_reduce_kernel<<<rgrid, 256, 0, stream>>>(a.partial, a.ksplit, w_elems, out32, out16, 0);

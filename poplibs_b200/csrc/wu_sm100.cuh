@@ -120,6 +120,10 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // set-up done: with a programmatic launch everything above overlapped the
+  // previous kernel's tail; global memory is touched only from here on
+  pdl_launch_dependents();
+  pdl_wait();
 
   // ---- which unit of work is this CTA's ------------------------------------
   int unit = blockIdx.x;
@@ -376,6 +380,8 @@ __global__ void __launch_bounds__(32 * kWuReduceLanes)
 wu_reduce4_kernel(const float4 *__restrict__ partial, int ksplit, size_t count4,
                   float4 *__restrict__ out_f32, uint2 *__restrict__ out_half) {
   __shared__ float4 part[kWuReduceLanes][32];
+  pdl_launch_dependents();
+  pdl_wait();  // the partial sums come from the previous kernel in the stream
   const size_t i = blockIdx.x * size_t(32) + threadIdx.x;
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
   if (i < count4) {
