@@ -145,18 +145,27 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
     return fail(PLB_ERR_INVALID_PARAMS, "empty contraction reached the kernel planner");
   if (p.fp8 && p.b_mn)
     return fail(PLB_ERR_UNSUPPORTED, "MN-major right operand is only implemented for half");
-  // ---- N tile: smallest padded width, ties to the wider tile ----------------
+  // ---- N tile ---------------------------------------------------------------
+  // Cost model: waves of tiles over the SMs times the measured duration of a
+  // 128 x BN x 16 tensor-core instruction (operand fetch bound: 75 / 95 / 155
+  // cycles for BN = 64 / 128 / 256).  Wide tiles win whenever the grid fills
+  // the device; a grid of a few tiles (small matrix products) finishes sooner
+  // with narrow ones, which also spread it over more SMs.
   int bn = 0;
   if (p.force_tile_n) {
     bn = p.force_tile_n;
     if (bn != 64 && bn != 128 && bn != 256)
       return fail(PLB_ERR_INVALID_OPTION, "tile_n must be 64, 128 or 256");
   } else {
+    const long sms = sm_count > 0 ? sm_count : 148;
+    const long pixel_tiles = (long(p.out_w) * p.out_h * p.out_n + kTileM - 1) / kTileM;  // lower bound
     long best = -1;
     for (int cand : {256, 128, 64}) {
-      const long padded = long((p.n_total + cand - 1) / cand) * cand;
-      if (best < 0 || padded < best) {
-        best = padded;
+      const long n_tiles_c = (p.n_total + cand - 1) / cand;
+      const long waves = (pixel_tiles * n_tiles_c + sms - 1) / sms;
+      const long cost = waves * (cand == 256 ? 155 : cand == 128 ? 95 : 75);
+      if (best < 0 || cost < best) {
+        best = cost;
         bn = cand;
       }
     }

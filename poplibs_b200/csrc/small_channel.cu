@@ -122,6 +122,59 @@ s2dInputRowsKernel(const __half *__restrict__ x, __half *__restrict__ x2, S2dSha
   }
 }
 
+// The same rearrangement for the common stem shape (3 channels, stride 2, so
+// Cp = 4 and one X2 pixel is two 16-byte vectors, one per vertical phase):
+// a vector is [X(ih, iw) c0..2, 0, X(ih, iw+1) c0..2, 0], i.e. six consecutive
+// halves of one input row.  One thread per vector; consecutive threads take
+// consecutive w2, so a warp reads one contiguous span of the row (four aligned
+// 32-bit loads per thread, overlapping its neighbours' in L1) and writes 512
+// contiguous bytes.  No shared memory, no divisions per element.
+__global__ void __launch_bounds__(256)
+s2dStem3Kernel(const uint32_t *__restrict__ x32, uint4 *__restrict__ x2, S2dShape g) {
+  const long long row_halves = (long long)g.W * 3;  // even: rows start on a 32-bit word
+  const size_t total = size_t(g.N) * g.H2 * 2 * g.W2;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const int w2 = int(i % g.W2);
+    size_t r = i / g.W2;
+    const int ph = int(r & 1);
+    r >>= 1;
+    const int h2 = int(r % g.H2);
+    const int n = int(r / g.H2);
+    const int ih = 2 * h2 + ph - g.padH, iw = 2 * w2 - g.padW;
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (ih >= 0 && ih < g.H && iw + 1 >= 0 && iw < g.W) {
+      const long long row0 = ((long long)n * g.H + ih) * row_halves;  // first half of the row
+      const long long h0 = row0 + (long long)iw * 3;                  // first half wanted
+      const int odd = int(h0 & 1);
+      const long long w0 = (h0 - odd) / 2;  // first 32-bit word (exact division)
+      const long long row_w0 = row0 / 2, row_w1 = (row0 + row_halves) / 2;
+      uint32_t w[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        w[k] = (w0 + k >= row_w0 && w0 + k < row_w1) ? x32[w0 + k] : 0u;
+      // halves h0 .. h0 + 5 of the 8 loaded
+      uint32_t a, b, c;  // (h0,h1) (h2,h3) (h4,h5)
+      if (odd) {
+        a = __funnelshift_r(w[0], w[1], 16);
+        b = __funnelshift_r(w[1], w[2], 16);
+        c = __funnelshift_r(w[2], w[3], 16);
+      } else {
+        a = w[0];
+        b = w[1];
+        c = w[2];
+      }
+      const bool left = iw >= 0, right = iw + 1 < g.W;
+      // pixel iw: h0 h1 h2; pixel iw + 1: h3 h4 h5
+      out.x = left ? a : 0u;
+      out.y = left ? (b & 0xffffu) : 0u;
+      out.z = right ? ((b >> 16) | (c << 16)) : 0u;
+      out.w = right ? (c >> 16) : 0u;
+    }
+    x2[(((size_t(n) * g.H2 + h2) * g.W2 + w2) << 1) + ph] = out;
+  }
+}
+
 // W2[a][co][(b*s*s + ph*s + pw)*Cp + c] = W[a*s + ph][b*s + pw][co][c], rows padded to 64.
 __global__ void s2dWeightsKernel(const __half *__restrict__ w, __half *__restrict__ w2, S2dShape g,
                                  int co_total) {
@@ -233,7 +286,13 @@ int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_c
   {
     const int row_elems = g.W * g.C;
     const size_t smem = size_t(g.s) * ((row_elems + 7) & ~7) * 2 + size_t(g.C2) * sizeof(int);
-    if (smem <= 48 * 1024 && g.C < 256 && g.s < 256) {
+    if (g.C == 3 && g.s == 2 && g.Cp == 4 && row_elems % 2 == 0 &&
+        (reinterpret_cast<uintptr_t>(d_in) & 3) == 0) {
+      const size_t vecs = size_t(g.N) * g.H2 * g.W2 * 2;
+      const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 32));
+      s2dStem3Kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint32_t *>(d_in),
+                                                    reinterpret_cast<uint4 *>(x2), g);
+    } else if (smem <= 48 * 1024 && g.C < 256 && g.s < 256) {
       const int rows_aligned =
           (row_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) ? 1 : 0;
       const int grid = int(std::min<size_t>(size_t(g.N) * g.H2, size_t(ctx->sm_count) * 16));
