@@ -10,9 +10,14 @@ can be selected with --workload.  One JSON line is printed by rank 0.
 
   value      TFLOP/s with inputs resident in HBM (2 x MACs, products with
              padding not counted, as the reference's getFwdFlops does), timed
-             with CUDA events on the launching stream, max over ranks.
-  e2e        the same metric through the host-buffer C ABI call: pinned host
-             inputs, H2D, kernel, D2H inside the timed region.
+             with CUDA events on the launching stream, max over ranks.  The
+             steps are replayed from a CUDA graph holding one library call per
+             rotating buffer set (--no-graph: one call per step), so that the
+             host's per-launch cost does not pace microsecond kernels.
+  e2e        the same metric through the host-buffer C ABI calls: every step
+             uploads its inputs from pinned host memory, runs and downloads its
+             result, all inside the timed region; steps alternate between two
+             contexts so one step's download overlaps the next one's upload.
   roofline   achieved vs the measured bf16 burst peak (tensor bound) or the
              measured copy bandwidth (HBM bound) of MEASURED_PEAKS.json.
   cpu_baseline  the reference's own CPU model (oracle/_ref when built, else the
@@ -20,7 +25,8 @@ can be selected with --workload.  One JSON line is printed by rank 0.
 
 With N > 1 (launched under torchrun) every rank runs the same per-GPU
 workload on its own shard of a batch N times larger (weak scaling; the path
-needs no collective in the forward pass).
+needs no collective in the forward pass; the weight update sums the per-rank
+gradients with the library's all-reduce kernel over NVLink peer memory).
 """
 from __future__ import annotations
 
@@ -269,10 +275,12 @@ class Workload:
             if self.kind == "conv" and self.pass_ == "wu":
                 d["out32"] = torch.empty(out_shape, dtype=torch.float32, device=device)
             self.dev.append(d)
-        self.host_out = torch.empty(out_shape, dtype=torch.float16).pin_memory()
+        # end-to-end leg: two contexts (streams) and two pinned output buffers
+        self.host_out = [torch.empty(out_shape, dtype=torch.float16).pin_memory() for _ in range(2)]
+        self.e2e_ctx = None
         self.h2d_bytes = sum(v.numel() * v.element_size() for k, v in self.host.items()
                              if self._is_input(k))
-        self.d2h_bytes = self.host_out.numel() * 2
+        self.d2h_bytes = self.host_out[0].numel() * 2
         torch.cuda.synchronize()
 
     def _is_input(self, key):
@@ -312,10 +320,18 @@ class Workload:
         return {"max_abs_diff_vs_nccl": diff, "max_abs": scale}
 
     def step_e2e(self, i):
+        """One end-to-end step: pinned host inputs -> device -> kernel -> pinned
+        host output, through the host-buffer entry points.  Steps alternate
+        between two library contexts (streams), so one step's download overlaps
+        the next one's upload; a context is synchronised before it is reused,
+        i.e. the result of step i - 2 is complete on the host by then."""
+        c = self.e2e_ctx[i & 1]
+        c.synchronize()
+        out = self.host_out[i & 1]
         if self.kind == "gemm":
-            self.ctx.matmul_host(self.desc, self.host["a"], self.host["b"], None, self.host_out)
+            c.matmul_host(self.desc, self.host["a"], self.host["b"], None, out, sync=False)
         elif self.pass_ == "fwd":
-            self.ctx.conv_fwd_host(self.p, self.host["x"], self.host["w"], self.host_out)
+            c.conv_fwd_host(self.p, self.host["x"], self.host["w"], out, sync=False)
         else:
             raise RuntimeError("end-to-end leg is defined for the forward pass and matMul")
 
@@ -527,6 +543,34 @@ def main():
             ms = float(t.item())
         return ms, launches, graph is not None
 
+    def timed_e2e(steps, warmup):
+        """Device time of `steps` end-to-end steps over the two e2e streams."""
+        wl.e2e_ctx = [capi.Context(local_rank), capi.Context(local_rank)]
+        for i in range(warmup):
+            wl.step_e2e(i)
+        for c in wl.e2e_ctx:
+            c.synchronize()
+        barrier()
+        s_a, s_b = (torch.cuda.ExternalStream(c.stream, device=device) for c in wl.e2e_ctx)
+        start, end_b, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        start.record(s_a)
+        s_b.wait_event(start)
+        for i in range(steps):
+            wl.step_e2e(i)
+        end_b.record(s_b)
+        s_a.wait_event(end_b)
+        end.record(s_a)
+        end.synchronize()
+        for c in wl.e2e_ctx:
+            c.synchronize()
+        barrier()
+        ms = start.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -548,8 +592,8 @@ def main():
 
     e2e = None
     if wl.has_e2e():
-        e2e_steps = max(3, min(args.steps, 20))
-        ms_e, _, _ = timed(wl.step_e2e, e2e_steps, 3)
+        e2e_steps = max(4, min(args.steps, 40))
+        ms_e = timed_e2e(e2e_steps, 3)
         e2e = {"value": wl.flops * world / (ms_e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
                "ms_per_step": ms_e / e2e_steps}

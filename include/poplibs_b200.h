@@ -132,6 +132,14 @@ PLB_API int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void
  * synchronises.  This is the end-to-end call the benchmark times. */
 PLB_API int plb_matmul_host(plb_context *ctx, const plb_matmul_desc *desc, const void *h_a,
                     const void *h_b, const void *h_c, void *h_d);
+/* plb_matmul_host without the final synchronisation: copies and kernel are
+ * enqueued on the context's stream and the call returns.  The host buffers
+ * must be page-locked for the copies to overlap anything, and must stay valid
+ * (and h_d unread) until plb_synchronize(ctx).  Successive calls on one
+ * context reuse its staging buffers in stream order; alternate between two
+ * contexts to overlap one call's download with the next one's upload. */
+PLB_API int plb_matmul_host_async(plb_context *ctx, const plb_matmul_desc *desc, const void *h_a,
+                          const void *h_b, const void *h_c, void *h_d);
 
 /* ------------------------------------------------------------------------ */
 /* poplin::ConvParams (include/poplin/ConvParams.hpp:16-224), flattened.     */
@@ -287,6 +295,10 @@ PLB_API int plb_cast_from_f32(plb_context *ctx, int32_t dtype, void *d_dst, cons
  * synchronise. */
 PLB_API int plb_conv_fwd_host(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
                       const void *h_in, const void *h_weights, const float *h_bias, void *h_out);
+/* Without the final synchronisation (see plb_matmul_host_async). */
+PLB_API int plb_conv_fwd_host_async(plb_context *ctx, const plb_conv_params *p,
+                            const plb_conv_options *opt, const void *h_in, const void *h_weights,
+                            const float *h_bias, void *h_out);
 
 /* ------------------------------------------------------------------------ */
 /* Layout changes between poplin's external shapes and the device layouts.   */

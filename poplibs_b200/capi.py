@@ -135,7 +135,8 @@ SYMBOLS = (
     "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution",
     "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
     "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_bias_update", "plb_conv_fwd_host",
-    "plb_allreduce_f32_p2p", "plb_allreduce_p2p_signal_bytes",
+    "plb_allreduce_f32_p2p", "plb_allreduce_p2p_signal_bytes", "plb_matmul_host_async",
+    "plb_conv_fwd_host_async",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
     "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
     "plb_weights_transpose_chans_flip_xy", "plb_transpose_matrix", "plb_matmul_plan",
@@ -173,6 +174,7 @@ def lib():
     L.plb_memset.argtypes = [vp, vp, C.c_int, sz]
     L.plb_matmul.argtypes = [vp, MP, vp, vp, vp, vp]
     L.plb_matmul_host.argtypes = [vp, MP, vp, vp, vp, vp]
+    L.plb_matmul_host_async.argtypes = [vp, MP, vp, vp, vp, vp]
     L.plb_conv_validate.argtypes = [CP]
     L.plb_conv_output_field.argtypes = [CP, _U3]
     L.plb_conv_input_index.argtypes = [CP, u32, u32, u32]
@@ -191,6 +193,7 @@ def lib():
     L.plb_allreduce_p2p_signal_bytes.argtypes = [i32]
     L.plb_allreduce_p2p_signal_bytes.restype = u32
     L.plb_conv_fwd_host.argtypes = [vp, CP, OP, vp, vp, vp, vp]
+    L.plb_conv_fwd_host_async.argtypes = [vp, CP, OP, vp, vp, vp, vp]
     for name in ("plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device"):
         getattr(L, name).argtypes = [vp, u32, u32, u32, u64, vp, vp]
     for name in ("plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
@@ -270,16 +273,23 @@ class Context:
     def matmul(self, desc: MatmulDesc, a, b, c, d):
         _check(lib().plb_matmul(self._h, C.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(d)))
 
-    def matmul_host(self, desc: MatmulDesc, a, b, c, d):
-        _check(lib().plb_matmul_host(self._h, C.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(d)))
+    def matmul_host(self, desc: MatmulDesc, a, b, c, d, sync: bool = True):
+        """Host buffers in, host buffer out.  sync=False returns after enqueueing
+        (page-locked buffers; call synchronize() before reading d)."""
+        fn = lib().plb_matmul_host if sync else lib().plb_matmul_host_async
+        _check(fn(self._h, C.byref(desc), _ptr(a), _ptr(b), _ptr(c), _ptr(d)))
 
     def conv_fwd(self, p: ConvParams, x, w, out, bias=None, opt: Optional[ConvOptions] = None):
         _check(lib().plb_conv_fwd(self._h, C.byref(p), C.byref(opt) if opt else None,
                                   _ptr(x), _ptr(w), _ptr(bias), _ptr(out)))
 
-    def conv_fwd_host(self, p: ConvParams, x, w, out, bias=None, opt: Optional[ConvOptions] = None):
-        _check(lib().plb_conv_fwd_host(self._h, C.byref(p), C.byref(opt) if opt else None,
-                                       _ptr(x), _ptr(w), _ptr(bias), _ptr(out)))
+    def conv_fwd_host(self, p: ConvParams, x, w, out, bias=None, opt: Optional[ConvOptions] = None,
+                      sync: bool = True):
+        """Host buffers in, host buffer out.  sync=False returns after enqueueing
+        (page-locked buffers; call synchronize() before reading out)."""
+        fn = lib().plb_conv_fwd_host if sync else lib().plb_conv_fwd_host_async
+        _check(fn(self._h, C.byref(p), C.byref(opt) if opt else None, _ptr(x), _ptr(w), _ptr(bias),
+                  _ptr(out)))
 
     def convolution(self, p: ConvParams, x, w, out, bias=None, opt: Optional[ConvOptions] = None,
                     transpose_and_flip_weights=False):

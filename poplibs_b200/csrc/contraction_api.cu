@@ -579,6 +579,12 @@ int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a, c
 
 int plb_matmul_host(plb_context *ctx, const plb_matmul_desc *desc, const void *h_a,
                     const void *h_b, const void *h_c, void *h_d) {
+  if (int rc = plb_matmul_host_async(ctx, desc, h_a, h_b, h_c, h_d)) return rc;
+  return plb_synchronize(ctx);
+}
+
+int plb_matmul_host_async(plb_context *ctx, const plb_matmul_desc *desc, const void *h_a,
+                          const void *h_b, const void *h_c, void *h_d) {
   if (int rc = activate(ctx)) return rc;
   if (!desc) return fail(PLB_ERR_INVALID_PARAMS, "null descriptor");
   const plb_matmul_desc &d = *desc;
@@ -600,8 +606,7 @@ int plb_matmul_host(plb_context *ctx, const plb_matmul_desc *desc, const void *h
   if (int rc = plb_memcpy_h2d(ctx, da, h_a, a_bytes)) return rc;
   if (int rc = plb_memcpy_h2d(ctx, db, h_b, b_bytes)) return rc;
   if (int rc = plb_matmul(ctx, desc, da, db, dc, dd)) return rc;
-  if (int rc = plb_memcpy_d2h(ctx, h_d, dd, c_bytes)) return rc;
-  return plb_synchronize(ctx);
+  return plb_memcpy_d2h(ctx, h_d, dd, c_bytes);
 }
 
 // ---------------------------------------------------------------------------
@@ -770,6 +775,13 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
 
 int plb_conv_fwd_host(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
                       const void *h_in, const void *h_weights, const float *h_bias, void *h_out) {
+  if (int rc = plb_conv_fwd_host_async(ctx, p, opt, h_in, h_weights, h_bias, h_out)) return rc;
+  return plb_synchronize(ctx);
+}
+
+int plb_conv_fwd_host_async(plb_context *ctx, const plb_conv_params *p,
+                            const plb_conv_options *opt, const void *h_in, const void *h_weights,
+                            const float *h_bias, void *h_out) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
   ConvShape s;
@@ -791,8 +803,7 @@ int plb_conv_fwd_host(plb_context *ctx, const plb_conv_params *p, const plb_conv
   if (int rc = plb_memcpy_h2d(ctx, di, h_in, in_bytes)) return rc;
   if (int rc = plb_memcpy_h2d(ctx, dw, h_weights, w_bytes)) return rc;
   if (int rc = plb_conv_fwd(ctx, p, opt, di, dw, static_cast<const float *>(dbias), dout)) return rc;
-  if (int rc = plb_memcpy_d2h(ctx, h_out, dout, out_bytes)) return rc;
-  return plb_synchronize(ctx);
+  return plb_memcpy_d2h(ctx, h_out, dout, out_bytes);
 }
 
 }  // extern "C"

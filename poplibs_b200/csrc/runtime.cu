@@ -397,9 +397,14 @@ int plb_context_create_on_stream(int device, void *cuda_stream, plb_context **ou
     }
     ctx->owns_stream = true;
   }
-  cudaError_t e = cudaMalloc(&ctx->d_status, sizeof(int));
-  if (e == cudaSuccess) e = cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  void *host_word = nullptr, *dev_word = nullptr;
+  cudaError_t e = cudaHostAlloc(&host_word, sizeof(int), cudaHostAllocMapped);
+  if (e == cudaSuccess) {
+    ctx->h_status = static_cast<volatile int *>(host_word);
+    *ctx->h_status = 0;
+    e = cudaHostGetDevicePointer(&dev_word, host_word, 0);
+    ctx->d_status = static_cast<int *>(dev_word);
+  }
   if (e != cudaSuccess) {
     plb_context_destroy(ctx);
     return cudaFail(e, "status word allocation");
@@ -418,7 +423,7 @@ void plb_context_destroy(plb_context *ctx) {
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
   for (int i = 0; i < plb_context::kScratchSlots; ++i)
     if (ctx->scratch[i]) cudaFree(ctx->scratch[i]);
-  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->h_status) cudaFreeHost(const_cast<int *>(ctx->h_status));
   if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
   if (ctx->timer_stop) cudaEventDestroy(ctx->timer_stop);
   if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -432,14 +437,14 @@ uint64_t plb_launch_count(const plb_context *ctx) { return ctx ? ctx->launches :
 int plb_synchronize(plb_context *ctx) {
   if (int rc = activate(ctx)) return rc;
   PLB_CUDA(cudaStreamSynchronize(ctx->stream));
-  int status = 0;
-  PLB_CUDA(cudaMemcpy(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  const int status = *ctx->h_status;
   if (status != 0) {
-    cudaMemset(ctx->d_status, 0, sizeof(int));
+    *ctx->h_status = 0;
     static const char *names[] = {"ok", "TMA producer wait ran out", "MMA issuer wait ran out",
-                                  "epilogue wait ran out", "teardown could not see copies complete"};
+                                  "epilogue wait ran out", "teardown could not see copies complete",
+                                  "a peer's flag did not arrive (all-reduce over peer memory)"};
     return fail(PLB_ERR_KERNEL, std::string("kernel status ") + std::to_string(status) + ": " +
-                                    (status > 0 && status < 5 ? names[status] : "unknown"));
+                                    (status > 0 && status < 6 ? names[status] : "unknown"));
   }
   return PLB_OK;
 }

@@ -17,7 +17,11 @@ struct plb_context {
   int sm_count = 0;
   cudaStream_t stream = nullptr;
   bool owns_stream = false;
-  int *d_status = nullptr;        // kernel status word (0 = OK)
+  // Kernel status word (0 = OK): page-locked host memory mapped into the device,
+  // written by kernels only when a bounded wait runs out, read by the host
+  // without a copy (a copy would queue behind other streams' transfers).
+  int *d_status = nullptr;        // device address
+  volatile int *h_status = nullptr;  // host address of the same word
   uint64_t launches = 0;          // kernels launched through this context
   long long *trace = nullptr;     // device timeline buffer for builds with -DPLB_TRACE
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;

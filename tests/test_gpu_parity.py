@@ -370,6 +370,41 @@ def test_conv_bias_update(gpu_ctx):
     assert_exact(db.cpu().numpy(), dbias, "bias gradient vs model")
 
 
+def test_host_buffer_calls_pipelined_over_two_contexts(gpu_ctx):
+    """The asynchronous host-buffer entry points on two alternating contexts
+    (upload of one step overlapping the download of the previous one) give the
+    same results as the synchronous ones."""
+    import torch
+    kw = conv_case(4, [20, 20], [3, 3], 64, 64, padding=1)
+    p = capi.ConvParams.make(**kw)
+    r = T.rng(11)
+    ctxs = [capi.Context(0), capi.Context(0)]
+    xs, outs, want = [], [], []
+    _, w, _ = conv_data(p, kw, r, exact=True)
+    wh = torch.from_numpy(T.weights_to_device_layout(w)).pin_memory()
+    for i in range(6):
+        x, _, _ = conv_data(p, kw, r, exact=True)
+        xs.append(torch.from_numpy(T.acts_to_device_layout(x)).pin_memory())
+        outs.append(torch.empty((4, 20, 20, 64), dtype=torch.float16).pin_memory())
+        want.append(oracle.conv_fwd(T.spec_from_params(p), x, w))
+    for i in range(6):
+        c = ctxs[i & 1]
+        c.synchronize()                      # step i - 2 on this context is complete
+        c.conv_fwd_host(p, xs[i], wh, outs[i], sync=False)
+    for c in ctxs:
+        c.synchronize()
+    for i in range(6):
+        got = T.acts_from_device_layout(outs[i].numpy())
+        assert_exact(got, want[i], f"pipelined host step {i}")
+    a = T.binary_half(r, (256, 192))
+    b = T.binary_half(r, (192, 128))
+    ah, bh = torch.from_numpy(a).pin_memory(), torch.from_numpy(b).pin_memory()
+    dh = torch.empty((256, 128), dtype=torch.float16).pin_memory()
+    ctxs[0].matmul_host(capi.MatmulDesc.make(256, 192, 128), ah, bh, None, dh, sync=False)
+    ctxs[0].synchronize()
+    assert_exact(dh.numpy(), oracle.gemm(a, b), "async host matmul")
+
+
 def test_allreduce_over_peer_memory_on_one_gpu(gpu_ctx):
     """plb_allreduce_f32_p2p with all "ranks'" buffers on this GPU and the
     peers' flags already set: checks the flags this rank writes, the rank-order
