@@ -101,10 +101,13 @@ uint64_t gemmBytes(const plb_matmul_desc &d) {
 struct ConvShape {
   unsigned nd;
   int H, W, OH, OW;      // input / output field as stored (H = 1 for 1-D)
-  int KH, KW;
-  // padH/padW: input padding minus output truncation at the low end, i.e.
-  // output position o, tap r reads truncated-input row o*stride + r*dil - pad
-  // (may be negative: the first rows are skipped)
+  int KH, KW;            // filter taps that are used (the kernel after truncation)
+  int KHs, KWs;          // filter extent as stored
+  int ktH, ktW;          // kernel truncation at the low end
+  // padH/padW: input padding minus output truncation minus kernel padding at
+  // the low end (the high end's kernel padding for a flipped kernel), i.e.
+  // output position o, used tap r reads truncated-input row
+  // o*stride + r*dil - pad (may be negative: the first rows are skipped)
   int padH, padW, dilH, dilW, strH, strW, flipH, flipW;
   int tH, tW;            // input truncation at the low end (rows / columns not used)
   int He, We;            // extent of the truncated input
@@ -128,20 +131,24 @@ int igemmConvShape(const plb_conv_params &p, ConvShape *s) {
   // Input truncation, output truncation and output padding are views and
   // offsets (below).  Input dilation only arrives through the backward pass of
   // a strided layer, which plb_conv_bwd takes in forward terms.
+  // Kernel truncation selects a sub-rectangle of the taps (gathered by the
+  // entry points), kernel padding only shifts where the taps land.
   for (unsigned d = 0; d != p.num_field_dims; ++d) {
-    if (p.in_dilation[d] != 1 || p.in_flip[d] || p.k_trunc_lo[d] || p.k_trunc_hi[d] ||
-        p.k_pad_lo[d] || p.k_pad_hi[d])
+    if (p.in_dilation[d] != 1 || p.in_flip[d])
       return fail(PLB_ERR_UNSUPPORTED,
-                  "input dilation/flip and kernel truncation/padding are not implemented on "
-                  "this path yet");
+                  "input dilation/flip are not implemented on this path yet");
   }
   s->nd = p.num_field_dims;
   const unsigned hd = p.num_field_dims == 2 ? 0 : ~0u, wd = p.num_field_dims - 1;
   auto get = [&](const uint32_t *v, unsigned d, int dflt) { return d == ~0u ? dflt : int(v[d]); };
   s->H = get(p.field, hd, 1);
   s->W = get(p.field, wd, 1);
-  s->KH = get(p.kernel, hd, 1);
-  s->KW = get(p.kernel, wd, 1);
+  s->KHs = get(p.kernel, hd, 1);
+  s->KWs = get(p.kernel, wd, 1);
+  s->ktH = get(p.k_trunc_lo, hd, 0);
+  s->ktW = get(p.k_trunc_lo, wd, 0);
+  s->KH = s->KHs - s->ktH - get(p.k_trunc_hi, hd, 0);
+  s->KW = s->KWs - s->ktW - get(p.k_trunc_hi, wd, 0);
   s->padH = get(p.in_pad_lo, hd, 0);
   s->padW = get(p.in_pad_lo, wd, 0);
   s->dilH = get(p.k_dilation, hd, 1);
@@ -156,8 +163,8 @@ int igemmConvShape(const plb_conv_params &p, ConvShape *s) {
   s->tW = get(p.in_trunc_lo, wd, 0);
   s->He = s->H - s->tH - get(p.in_trunc_hi, hd, 0);
   s->We = s->W - s->tW - get(p.in_trunc_hi, wd, 0);
-  s->padH -= get(p.out_trunc_lo, hd, 0);
-  s->padW -= get(p.out_trunc_lo, wd, 0);
+  s->padH -= get(p.out_trunc_lo, hd, 0) + get(s->flipH ? p.k_pad_hi : p.k_pad_lo, hd, 0);
+  s->padW -= get(p.out_trunc_lo, wd, 0) + get(s->flipW ? p.k_pad_hi : p.k_pad_lo, wd, 0);
   s->opH = get(p.out_pad_lo, hd, 0);
   s->opW = get(p.out_pad_lo, wd, 0);
   s->OHc = s->OH - s->opH - get(p.out_pad_hi, hd, 0);
@@ -200,10 +207,11 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
           ((size_t(s.tH) * s.W + s.tW) * ctot + size_t(g) * ci) * es;
   const bool pointwise = s.KH == 1 && s.KW == 1 && s.padH == 0 && s.padW == 0;
   if (pointwise) {
-    // a strided 1x1 convolution reads a sub-lattice: describe only that
+    // a strided 1x1 convolution reads a sub-lattice: describe only that (its
+    // extent is what the input holds; outputs beyond it read zero padding)
     r.act_dims[0] = ci;
-    r.act_dims[1] = uint64_t(s.OWc);
-    r.act_dims[2] = uint64_t(s.OHc);
+    r.act_dims[1] = uint64_t(std::min(s.OWc, (s.We + s.strW - 1) / s.strW));
+    r.act_dims[2] = uint64_t(std::min(s.OHc, (s.He + s.strH - 1) / s.strH));
     r.act_dims[3] = p.batch;
     r.act_strides[0] = uint64_t(s.strW) * ctot * es;
     r.act_strides[1] = uint64_t(s.strH) * s.W * ctot * es;
@@ -321,10 +329,12 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
 }
 
 // Filter taps (r0h + jh*sh, r0w + jw*sw), jh < JH, jw < JW, of [G][KH*KW][inner]
-// weights gathered into [G][JH*JW][inner]; 16-byte vectors.
+// weights gathered into [G][JH*JW][inner]; 16-byte vectors.  With flip_h /
+// flip_w the tap indices count from the far end of the stored filter (the
+// filter is used spatially flipped).
 __global__ void gatherTapsKernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, int groups,
                                  int KH, int KW, int JH, int JW, int r0h, int r0w, int sh, int sw,
-                                 size_t inner_vecs) {
+                                 size_t inner_vecs, int flip_h = 0, int flip_w = 0) {
   const size_t total = size_t(groups) * JH * JW * inner_vecs;
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
        i += size_t(gridDim.x) * blockDim.x) {
@@ -334,7 +344,8 @@ __global__ void gatherTapsKernel(const uint4 *__restrict__ src, uint4 *__restric
     t /= JW;
     const int jh = int(t % JH);
     const int g = int(t / JH);
-    const size_t tap = size_t(r0h + jh * sh) * KW + size_t(r0w + jw * sw);
+    const int th = r0h + jh * sh, tw = r0w + jw * sw;
+    const size_t tap = size_t(flip_h ? KH - 1 - th : th) * KW + size_t(flip_w ? KW - 1 - tw : tw);
     dst[i] = src[(size_t(g) * KH * KW + tap) * inner_vecs + v];
   }
 }
@@ -374,6 +385,32 @@ bool bwdPhase(int phase, int in_size, int kernel, int pad, int dil, int stride, 
     if (second != out->first_tap + stride) return false;
   }
   return true;
+}
+
+// Weights of a truncated kernel: the used sub-rectangle of taps gathered into
+// scratch as a dense [G][KH*KW][Co*Ci] filter.  Returns `w` itself when the
+// kernel is not truncated.
+int usedTaps(plb_context *ctx, const plb_conv_params &p, const ConvShape &s, const void *w,
+             const void **out) {
+  *out = w;
+  if (s.KH == s.KHs && s.KW == s.KWs) return PLB_OK;
+  const size_t es = dtypeBytes(p.input_type);
+  const size_t inner = size_t(p.out_chans_per_group) * p.in_chans_per_group * es;
+  if (inner % 16 != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0)
+    return fail(PLB_ERR_UNSUPPORTED, "weights must be 16-byte aligned per tap");
+  if (s.KH <= 0 || s.KW <= 0) return PLB_OK;  // nothing is used; callers zero the result
+  void *ws = nullptr;
+  const size_t bytes = size_t(p.groups) * s.KH * s.KW * inner;
+  if (int rc = scratch(ctx, 6, bytes + 256, &ws)) return rc;
+  const size_t vecs = bytes / 16;
+  const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 8));
+  gatherTapsKernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint4 *>(w),
+                                                  static_cast<uint4 *>(ws), int(p.groups), s.KHs,
+                                                  s.KWs, s.KH, s.KW, s.ktH, s.ktW, 1, 1, inner / 16);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  *out = ws;
+  return PLB_OK;
 }
 
 // Backward pass of a strided convolution (the reference's getGradientParams
@@ -431,7 +468,8 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
       const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 8));
       gatherTapsKernel<<<grid, 256, 0, ctx->stream>>>(
           static_cast<const uint4 *>(w), reinterpret_cast<uint4 *>(wsub), int(p.groups), s.KH, s.KW,
-          A.taps, B.taps, A.first_tap, B.first_tap, s.strH, s.strW, inner * es / 16);
+          A.taps, B.taps, A.first_tap, B.first_tap, s.strH, s.strW, inner * es / 16, s.flipH,
+          s.flipW);
       PLB_CUDA(cudaGetLastError());
       ctx->launches++;
       for (unsigned g = 0; g < p.groups; ++g) {
@@ -466,8 +504,9 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
         r.dil_w = s.dilW;
         r.pad_h = (A.taps - 1) * s.dilH - A.offset;
         r.pad_w = (B.taps - 1) * s.dilW - B.offset;
-        r.flip_h = !s.flipH;
-        r.flip_w = !s.flipW;
+        // (a flipped forward kernel was un-flipped by the gather)
+        r.flip_h = 1;
+        r.flip_w = 1;
         r.out = static_cast<uint8_t *>(dx) +
                 ((size_t(s.tH + a) * s.W + (s.tW + b)) * ctot + size_t(g) * ci) * os;
         r.ldc = (long long)(ctot * s.strW);
@@ -693,7 +732,17 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
       return fail(PLB_ERR_UNSUPPORTED, "strides above 8 are not implemented for k > 1");
   }
   const size_t es = dtypeBytes(p->input_type);
-  const void *w = d_weights;
+  if (s.KH <= 0 || s.KW <= 0) {
+    // every tap is truncated away: the result is zero
+    PLB_CUDA(cudaMemsetAsync(d_out, 0,
+                             size_t(p->batch) * s.OH * s.OW * p->groups * p->out_chans_per_group *
+                                 dtypeBytes(p->output_type),
+                             ctx->stream));
+    return PLB_OK;
+  }
+  const void *w = nullptr;
+  if (int rc = usedTaps(ctx, *p, s, d_weights, &w)) return rc;
+  const void *const w_used = w;
   bool swapped = transpose_and_flip_weights != 0;
   if (swapped && (p->input_type == PLB_QUARTER || !channelsFitTma(*p, p->out_chans_per_group))) {
     // no MN-major path for 8-bit operands (or for rows TMA cannot address):
@@ -705,7 +754,7 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
     // stored [G][k][Ci][Co] -> [G][flipped k][Co][Ci]
     if (int rc = plb_weights_transpose_chans_flip_xy(ctx, uint32_t(es), p->groups,
                                                      p->in_chans_per_group, p->out_chans_per_group,
-                                                     uint64_t(s.KH) * s.KW, d_weights, ws))
+                                                     uint64_t(s.KH) * s.KW, w_used, ws))
       return rc;
     w = ws;
     swapped = false;
@@ -747,8 +796,18 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
                                ctx->stream));
     return PLB_OK;
   }
-  if (s.strH != 1 || s.strW != 1) return convBwdStrided(ctx, *p, opt, s, d_out_grads, d_weights, d_in_grads);
-  const void *w = d_weights;
+  if (s.KH <= 0 || s.KW <= 0) {
+    if (!s.zero_fill_in)
+      PLB_CUDA(cudaMemsetAsync(d_in_grads, 0,
+                               size_t(p->batch) * s.H * s.W * p->groups * p->in_chans_per_group *
+                                   dtypeBytes(p->output_type),
+                               ctx->stream));
+    return PLB_OK;
+  }
+  const void *w = nullptr;
+  if (int rc = usedTaps(ctx, *p, s, d_weights, &w)) return rc;
+  if (s.strH != 1 || s.strW != 1) return convBwdStrided(ctx, *p, opt, s, d_out_grads, w, d_in_grads);
+  const void *const w_used = w;
   bool transposed = false;
   if (p->input_type == PLB_QUARTER) {
     // no MN-major path for 8-bit operands: transpose + flip the (small) weights
@@ -758,7 +817,7 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
     if (int rc = scratch(ctx, 0, bytes, &ws)) return rc;
     if (int rc = plb_weights_transpose_chans_flip_xy(ctx, uint32_t(es), p->groups,
                                                      p->out_chans_per_group, p->in_chans_per_group,
-                                                     uint64_t(s.KH) * s.KW, d_weights, ws))
+                                                     uint64_t(s.KH) * s.KW, w_used, ws))
       return rc;
     w = ws;
     transposed = true;

@@ -27,11 +27,10 @@ int wuShape(const plb_conv_params &p, WuShape *s) {
     // (tools/single_conv_layer.cpp:725-733)
     return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half input only");
   for (unsigned d = 0; d != p.num_field_dims; ++d) {
-    if (p.in_dilation[d] != 1 || p.in_flip[d] || p.k_trunc_lo[d] || p.k_trunc_hi[d] ||
-        p.k_pad_lo[d] || p.k_pad_hi[d] || p.k_flip[d])
+    if (p.in_dilation[d] != 1 || p.in_flip[d] || p.k_trunc_lo[d] || p.k_trunc_hi[d] || p.k_flip[d])
       return fail(PLB_ERR_UNSUPPORTED,
-                  "input dilation/flip and kernel truncation/padding/flip are not implemented on "
-                  "this path yet");
+                  "input dilation/flip and kernel truncation/flip are not implemented on this "
+                  "path yet");
     if (p.stride[d] > 8) return fail(PLB_ERR_UNSUPPORTED, "strides above 8 are not implemented");
   }
   const unsigned hd = p.num_field_dims == 2 ? 0 : ~0u, wd = p.num_field_dims - 1;
@@ -52,8 +51,9 @@ int wuShape(const plb_conv_params &p, WuShape *s) {
   s->tW = get(p.in_trunc_lo, wd, 0);
   s->He = s->H - s->tH - get(p.in_trunc_hi, hd, 0);
   s->We = s->W - s->tW - get(p.in_trunc_hi, wd, 0);
-  s->padH -= get(p.out_trunc_lo, hd, 0);
-  s->padW -= get(p.out_trunc_lo, wd, 0);
+  // kernel padding only shifts where the taps land
+  s->padH -= get(p.out_trunc_lo, hd, 0) + get(p.k_pad_lo, hd, 0);
+  s->padW -= get(p.out_trunc_lo, wd, 0) + get(p.k_pad_lo, wd, 0);
   s->opH = get(p.out_pad_lo, hd, 0);
   s->opW = get(p.out_pad_lo, wd, 0);
   s->OHc = s->OH - s->opH - get(p.out_pad_hi, hd, 0);

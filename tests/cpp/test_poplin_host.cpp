@@ -19,6 +19,7 @@
 #include "poplin/Convolution.hpp"
 #include "poplin/FullyConnected.hpp"
 #include "poplin/MatMul.hpp"
+#include "poplin/MultiConvolution.hpp"
 #include "poplin/codelets.hpp"
 #include "poputil/exceptions.hpp"
 
@@ -336,6 +337,52 @@ static void testMatMulSurface() {
   CHECK(fc::getMatMulPrePlanParameters({1, 4, 8, 8}, {}, HALF, true).size() == 1);
 }
 
+static void testMultiConvAndBiasSurface() {
+  poplar::Graph graph(poplar::Target::createGPUTarget(0));
+  PlanningCache cache;
+  ConvParams p1(HALF, 4, {14, 14}, {3, 3}, 64, 64, 1);
+  p1.inputTransform.paddingLower = p1.inputTransform.paddingUpper = {1, 1};
+  ConvParams p2(HALF, 4, {12, 12}, {1, 1}, 64, 128, 1);
+  p2.outputTransform.stride = {2, 2};
+  const std::vector<multiconv::CreateTensorArgs> create{{p1, {}, "a"}, {p2, {}, "b"}};
+  std::vector<multiconv::ConvolutionArgs> args;
+  for (unsigned i = 0; i != 2; ++i)
+    args.push_back({multiconv::createInput(graph, create, i, {}, &cache),
+                    multiconv::createWeights(graph, create, i, {}, &cache), create[i].params, {}});
+  poplar::program::Sequence prog;
+  auto outs = multiconv::convolution(graph, args, false, prog, "mc", {{"planType", "serial"}}, &cache);
+  CHECK(outs.size() == 2);
+  CHECK((outs[1].shape() == std::vector<std::size_t>{4, 128, 6, 6}));
+  CHECK((throwsAs<poplar::invalid_option>(
+      [&] { multiconv::convolution(graph, args, false, prog, "mc", {{"planType", "sideways"}}); })));
+  CHECK((throwsAs<poplar::invalid_option>(
+      [&] { multiconv::convolution(graph, args, false, prog, "mc", {{"noSuchOption", "1"}}); })));
+  CHECK((throwsAs<poputil::poplibs_error>([&] { multiconv::createInput(graph, create, 2); })));
+  // gradients of both layers; the strided one plans in forward terms
+  std::vector<multiconv::CalculateWeightDeltasArgs> wu;
+  for (unsigned i = 0; i != 2; ++i) wu.push_back({outs[i], args[i].inputs, args[i].params, {}});
+  auto deltas = multiconv::calculateWeightDeltas(graph, wu, prog, "wu", {}, &cache);
+  CHECK(deltas.size() == 2 && deltas[1].shape() == args[1].weights.shape());
+  std::vector<multiconv::ConvWeightUpdateArgsScalar> upd;
+  for (unsigned i = 0; i != 2; ++i)
+    upd.push_back({outs[i], args[i].weights, args[i].inputs, -0.5f, args[i].params, {}});
+  multiconv::convolutionWeightUpdate(graph, upd, prog, "upd", {}, &cache);
+  // backward pass of the strided layer: transposed weights, input dilation in the parameters
+  const ConvParams bwd = getGradientParams(p2);
+  CHECK(bwd.inputTransform.dilation[0] == 2);
+  auto dIn = convolution(graph, outs[1], args[1].weights, bwd, true, prog, "bwd", {}, &cache);
+  CHECK(dIn.shape() == args[1].inputs.shape());
+  // bias surface
+  auto biases = createBiases(graph, outs[0], "biases");
+  CHECK((biases.shape() == std::vector<std::size_t>{64}));
+  addBias(graph, outs[0], biases, prog, "addBias");
+  convolutionBiasUpdate(graph, outs[0], biases, -0.1f, {{"partialsType", "float"}}, prog, "biasUpdate");
+  CHECK((throwsAs<poputil::poplibs_error>(
+      [&] { convolutionBiasUpdate(graph, outs[1], biases, 1.f, {}, prog); })));
+  CHECK((throwsAs<poplar::invalid_option>(
+      [&] { convolutionBiasUpdate(graph, outs[0], biases, 1.f, {{"partialsType", "int"}}, prog); })));
+}
+
 int main() {
   testConvParamsJson();
   testValidation();
@@ -345,6 +392,7 @@ int main() {
   testTensorViews();
   testGraphConstructionWithoutDevice();
   testMatMulSurface();
+  testMultiConvAndBiasSurface();
   if (failures) {
     std::printf("%d check(s) failed\n", failures);
     return 1;

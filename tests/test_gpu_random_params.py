@@ -1,0 +1,87 @@
+"""Seeded random ConvParams against the oracle, all three passes.
+
+The role of the reference's random-parameter runs
+(tools/single_conv_layer_random.py:22-50, tests/poplin/CMakeLists.txt:1040-1065):
+every transform of ConvParams that the CUDA path implements is drawn at
+random -- input truncation and padding, kernel truncation, dilation, padding
+and flip, stride, output truncation and padding, groups, 1-D and 2-D fields --
+and the result must match the oracle bit for bit on +-1 data (all sums stay
+below 2048, exact in half).  Parameters the path does not implement (input
+dilation / flip) are not drawn; a drawn combination that is not a valid
+convolution (empty output) is redrawn.
+"""
+import math
+
+import numpy as np
+import pytest
+
+import common as T
+import oracle
+from poplibs_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+def draw(seed):
+    r = np.random.default_rng(1000 + seed)
+    for _ in range(200):
+        nd = int(r.integers(1, 3))
+        vec = lambda lo, hi: [int(v) for v in r.integers(lo, hi + 1, nd)]  # noqa: E731
+        kw = dict(
+            batch=int(r.integers(1, 5)), field=vec(5, 14), kernel=vec(1, 5),
+            in_chans=int(r.choice([8, 16, 24, 40, 64])), out_chans=int(r.choice([8, 16, 24, 40, 72])),
+            groups=int(r.choice([1, 1, 2])),
+            in_trunc_lo=vec(0, 2), in_trunc_hi=vec(0, 2), in_pad_lo=vec(0, 3), in_pad_hi=vec(0, 3),
+            k_trunc_lo=vec(0, 1), k_trunc_hi=vec(0, 1), k_dilation=vec(1, 3), k_pad_lo=vec(0, 2),
+            k_pad_hi=vec(0, 2), k_flip=vec(0, 1), stride=vec(1, 3), out_trunc_lo=vec(0, 2),
+            out_trunc_hi=vec(0, 2), out_pad_lo=vec(0, 2), out_pad_hi=vec(0, 2))
+        # keep the draw simple half of the time: most layers use few transforms
+        if r.random() < 0.5:
+            for name in ("in_trunc_lo", "in_trunc_hi", "k_trunc_lo", "k_trunc_hi", "k_pad_lo", "k_pad_hi",
+                         "out_trunc_lo", "out_trunc_hi", "out_pad_lo", "out_pad_hi"):
+                if r.random() < 0.7:
+                    kw[name] = [0] * nd
+        if any(kw["kernel"][d] - kw["k_trunc_lo"][d] - kw["k_trunc_hi"][d] < 1 for d in range(nd)):
+            continue
+        if any(kw["field"][d] - kw["in_trunc_lo"][d] - kw["in_trunc_hi"][d] < 1 for d in range(nd)):
+            continue
+        p = capi.ConvParams.make(**kw)
+        try:
+            of = p.output_field()
+        except capi.PlbError:
+            continue
+        # a computed (not padded) output must exist
+        if any(of[d] - kw["out_pad_lo"][d] - kw["out_pad_hi"][d] < 1 for d in range(nd)):
+            continue
+        taps = int(np.prod([kw["kernel"][d] for d in range(nd)]))
+        if taps * kw["in_chans"] > 2000 or taps * kw["out_chans"] > 2000:
+            continue  # sums must stay exactly representable in half
+        return kw, p
+    raise RuntimeError("no valid parameters drawn")
+
+
+def data(kw, p, r):
+    g = p.groups
+    x = T.binary_half(r, (p.batch, g * p.in_chans_per_group, *kw["field"]))
+    w = T.binary_half(r, (g, p.out_chans_per_group, p.in_chans_per_group, *kw["kernel"]))
+    dy = T.binary_half(r, (p.batch, g * p.out_chans_per_group, *p.output_field()))
+    return x, w, dy
+
+
+@pytest.mark.parametrize("seed", range(120))
+def test_random_conv_params(gpu_ctx, seed):
+    kw, p = draw(seed)
+    spec = T.spec_from_params(p)
+    nd = len(kw["field"])
+    r = T.rng(seed)
+    x, w, dy = data(kw, p, r)
+    what = f"seed {seed}: {kw}"
+    got = T.gpu_conv_fwd(p, x, w)
+    assert np.array_equal(got.astype(np.float64), oracle.conv_fwd(spec, x, w).reshape(got.shape)), "fwd " + what
+    if all(kw["stride"][d] == 1 or math.gcd(kw["k_dilation"][d], kw["stride"][d]) == 1 for d in range(nd)):
+        got = T.gpu_conv_bwd(p, dy, w)
+        assert np.array_equal(got.astype(np.float64), oracle.conv_bwd(spec, dy, w).reshape(got.shape)), "bwd " + what
+    if not any(kw["k_flip"]) and not any(kw["k_trunc_lo"]) and not any(kw["k_trunc_hi"]) and \
+            all(s <= 8 for s in kw["stride"]):
+        _, dw32 = T.gpu_conv_wu(p, x, dy)
+        assert np.array_equal(dw32.astype(np.float64), oracle.conv_wu(spec, x, dy)[0].reshape(dw32.shape)), "wu " + what
