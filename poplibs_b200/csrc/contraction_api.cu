@@ -387,6 +387,32 @@ bool bwdPhase(int phase, int in_size, int kernel, int pad, int dil, int stride, 
   return true;
 }
 
+// ---- channel counts TMA cannot address -------------------------------------------
+// A pixel must be a multiple of 16 bytes for the tensor maps (8 half / 16 quarter
+// channels per group).  Other counts run on zero-padded copies: activations
+// [pixels][G][C -> Cp], weights [G][taps][Co -> Cop][Ci -> Cip]; padded input
+// channels meet zero weights, padded output channels are dropped.  One arena
+// (scratch slot 7) holds the copies.
+struct PaddedChans {
+  uint32_t ci, co, cip, cop;
+  bool needed;
+};
+PaddedChans paddedChans(const plb_conv_params &p) {
+  const uint32_t q = uint32_t(16 / dtypeBytes(p.input_type));
+  PaddedChans c{p.in_chans_per_group, p.out_chans_per_group, 0, 0, false};
+  c.cip = (c.ci + q - 1) / q * q;
+  c.cop = (c.co + q - 1) / q * q;
+  c.needed = c.cip != c.ci || c.cop != c.co;
+  return c;
+}
+// [G][taps][rows][cols] -> [G][taps][rows_p][cols_p]
+int padWeights(plb_context *ctx, const void *src, void *tmp, void *dst, size_t g_taps, uint32_t rows,
+               uint32_t cols, uint32_t rows_p, uint32_t cols_p, size_t es) {
+  if (int rc = resizeRows(ctx, src, tmp, g_taps * rows, cols * es, cols_p * es)) return rc;
+  return resizeRows(ctx, tmp, dst, g_taps, size_t(rows) * cols_p * es, size_t(rows_p) * cols_p * es);
+}
+size_t align256(size_t n) { return (n + 255) & ~size_t(255); }
+
 // Weights of a truncated kernel: the used sub-rectangle of taps gathered into
 // scratch as a dense [G][KH*KW][Co*Ci] filter.  Returns `w` itself when the
 // kernel is not truncated.
@@ -677,19 +703,28 @@ int plb_conv_plan(const plb_conv_params *p, const plb_conv_options *opt, int32_t
   if (int rc = igemmConvShape(*p, &s)) return rc;
   *plan = plb_plan{};
   if (pass != PLB_PASS_TRAINING_BWD && !channelsFitTma(*p, p->in_chans_per_group)) {
-    if (int rc = convFwdSmallChannels(nullptr, *p, opt, nullptr, nullptr, nullptr, nullptr, plan))
-      return rc;
-    plan->flops = 2 * numberOfMacs(*p);
-    plan->bytes = convBytes(*p, s, pass);
-    return PLB_OK;
+    const int rc = convFwdSmallChannels(nullptr, *p, opt, nullptr, nullptr, nullptr, nullptr, plan);
+    if (rc == PLB_OK) {
+      plan->flops = 2 * numberOfMacs(*p);
+      plan->bytes = convBytes(*p, s, pass);
+      return PLB_OK;
+    }
+    if (rc != PLB_ERR_UNSUPPORTED) return rc;
+  }
+  // channel counts TMA cannot address run zero-padded: plan what will run
+  plb_conv_params padded = *p;
+  const PaddedChans pc = paddedChans(*p);
+  if (pc.needed && (pass == PLB_PASS_TRAINING_BWD || !channelsFitTma(*p, pc.ci))) {
+    padded.in_chans_per_group = pc.cip;
+    padded.out_chans_per_group = pc.cop;
   }
   IgemmProblem q;
   if (pass == PLB_PASS_TRAINING_BWD) {
-    if (int rc = convBwdProblem(*p, opt, s, 0, nullptr, nullptr, nullptr,
+    if (int rc = convBwdProblem(padded, opt, s, 0, nullptr, nullptr, nullptr,
                                 p->input_type == PLB_QUARTER, &q))
       return rc;
   } else {
-    if (int rc = convFwdProblem(*p, opt, s, 0, nullptr, nullptr, nullptr, nullptr, &q)) return rc;
+    if (int rc = convFwdProblem(padded, opt, s, 0, nullptr, nullptr, nullptr, nullptr, &q)) return rc;
   }
   if (q.n_total > 0 && q.out_w > 0 && q.out_h > 0 && q.out_n > 0 && q.k_per_tap > 0)
     if (int rc = planIgemm(q, 148, plan)) return rc;
@@ -720,11 +755,39 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
       return fail(PLB_ERR_UNSUPPORTED,
                   "a fused bias with output padding is not implemented: use plb_add_bias");
   }
-  if (!channelsFitTma(*p, p->in_chans_per_group)) {
-    if (transpose_and_flip_weights)
-      return fail(PLB_ERR_UNSUPPORTED,
-                  "small-channel convolutions cannot take transposed weights");
-    return convFwdSmallChannels(ctx, *p, opt, d_in, d_weights, d_bias, d_out, nullptr);
+  if (!channelsFitTma(*p, p->in_chans_per_group) && !transpose_and_flip_weights) {
+    // few input channels (a stem): space-to-depth path, where it applies
+    const int rc = convFwdSmallChannels(ctx, *p, opt, d_in, d_weights, d_bias, d_out, nullptr);
+    if (rc != PLB_ERR_UNSUPPORTED) return rc;
+  }
+  const PaddedChans pc = paddedChans(*p);
+  if (pc.needed && !channelsFitTma(*p, pc.ci)) {
+    // run on zero-padded channel counts
+    const size_t es = dtypeBytes(p->input_type), os = dtypeBytes(p->output_type);
+    const size_t G = p->groups, taps = size_t(s.KHs) * s.KWs;
+    const size_t in_px = size_t(p->batch) * s.H * s.W, out_px = size_t(p->batch) * s.OH * s.OW;
+    const size_t x_b = align256(in_px * G * pc.cip * es), w_b = align256(G * taps * pc.cop * pc.cip * es),
+                 o_b = align256(out_px * G * pc.cop * os), b_b = align256(G * pc.cop * sizeof(float));
+    void *arena = nullptr;
+    if (int rc = scratch(ctx, 7, x_b + 2 * w_b + o_b + b_b, &arena)) return rc;
+    uint8_t *xp = static_cast<uint8_t *>(arena), *wp = xp + x_b, *wtmp = wp + w_b, *op = wtmp + w_b,
+            *bp = op + o_b;
+    if (int rc = resizeRows(ctx, d_in, xp, in_px * G, pc.ci * es, pc.cip * es)) return rc;
+    // stored [G][taps][Co][Ci], or [G][taps][Ci][Co] for transposed weights
+    if (transpose_and_flip_weights) {
+      if (int rc = padWeights(ctx, d_weights, wtmp, wp, G * taps, pc.ci, pc.co, pc.cip, pc.cop, es)) return rc;
+    } else {
+      if (int rc = padWeights(ctx, d_weights, wtmp, wp, G * taps, pc.co, pc.ci, pc.cop, pc.cip, es)) return rc;
+    }
+    if (d_bias)
+      if (int rc = resizeRows(ctx, d_bias, bp, G, pc.co * sizeof(float), pc.cop * sizeof(float))) return rc;
+    plb_conv_params q = *p;
+    q.in_chans_per_group = pc.cip;
+    q.out_chans_per_group = pc.cop;
+    if (int rc = plb_convolution(ctx, &q, opt, xp, wp, d_bias ? reinterpret_cast<const float *>(bp) : nullptr,
+                                 op, transpose_and_flip_weights))
+      return rc;
+    return resizeRows(ctx, op, d_out, out_px * G, pc.cop * os, pc.co * os);
   }
   if (s.strH > 1 || s.strW > 1) {
     const bool pointwise = s.KH == 1 && s.KW == 1 && s.padH == 0 && s.padW == 0;
@@ -795,6 +858,25 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
                                    dtypeBytes(p->output_type),
                                ctx->stream));
     return PLB_OK;
+  }
+  const PaddedChans pc = paddedChans(*p);
+  if (pc.needed) {
+    // run on zero-padded channel counts (see plb_convolution)
+    const size_t os = dtypeBytes(p->output_type);
+    const size_t G = p->groups, taps = size_t(s.KHs) * s.KWs;
+    const size_t in_px = size_t(p->batch) * s.H * s.W, out_px = size_t(p->batch) * s.OH * s.OW;
+    const size_t dy_b = align256(out_px * G * pc.cop * es), w_b = align256(G * taps * pc.cop * pc.cip * es),
+                 dx_b = align256(in_px * G * pc.cip * os);
+    void *arena = nullptr;
+    if (int rc = scratch(ctx, 7, dy_b + 2 * w_b + dx_b, &arena)) return rc;
+    uint8_t *dyp = static_cast<uint8_t *>(arena), *wp = dyp + dy_b, *wtmp = wp + w_b, *dxp = wtmp + w_b;
+    if (int rc = resizeRows(ctx, d_out_grads, dyp, out_px * G, pc.co * es, pc.cop * es)) return rc;
+    if (int rc = padWeights(ctx, d_weights, wtmp, wp, G * taps, pc.co, pc.ci, pc.cop, pc.cip, es)) return rc;
+    plb_conv_params q = *p;
+    q.in_chans_per_group = pc.cip;
+    q.out_chans_per_group = pc.cop;
+    if (int rc = plb_conv_bwd(ctx, &q, opt, dyp, wp, dxp)) return rc;
+    return resizeRows(ctx, dxp, d_in_grads, in_px * G, pc.cip * os, pc.ci * os);
   }
   if (s.KH <= 0 || s.KW <= 0) {
     if (!s.zero_fill_in)

@@ -343,6 +343,34 @@ __global__ void biasUpdateKernel(const float *__restrict__ partial, uint32_t sla
   biases[c] = T(float(biases[c]) + scale * s);
 }
 
+// Copies rows of `c_src` elements into rows of `c_dst` elements (same row
+// count), zero-filling the tail when the destination rows are longer and
+// dropping it when they are shorter: channel padding / un-padding.
+__global__ void resizeRowsKernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                 size_t rows, uint32_t src_bytes, uint32_t dst_bytes) {
+  // 2-byte granularity covers half and quarter-pairs; odd byte counts use bytes
+  const size_t total = rows * dst_bytes;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = i / dst_bytes;
+    const uint32_t b = uint32_t(i - r * dst_bytes);
+    dst[i] = b < src_bytes ? src[r * src_bytes + b] : uint8_t(0);
+  }
+}
+
+int resizeRows(plb_context *ctx, const void *src, void *dst, size_t rows, size_t src_bytes,
+               size_t dst_bytes) {
+  if (rows == 0 || dst_bytes == 0) return PLB_OK;
+  const size_t total = rows * dst_bytes;
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(ctx->sm_count) * 16));
+  resizeRowsKernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint8_t *>(src),
+                                                  static_cast<uint8_t *>(dst), rows,
+                                                  uint32_t(src_bytes), uint32_t(dst_bytes));
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
 int launchScaleRows(plb_context *ctx, void *out, const void *c, float beta, bool out_f32,
                     uint32_t rows, uint32_t cols, long long ldo, long long ldc) {
   if (rows == 0 || cols == 0) return PLB_OK;

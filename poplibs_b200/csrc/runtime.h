@@ -60,6 +60,10 @@ inline size_t dtypeBytes(int dtype) {
   return dtype == PLB_FLOAT ? 4 : dtype == PLB_HALF ? 2 : 1;
 }
 
+// Row resize (runtime.cu): rows of src_bytes -> rows of dst_bytes, zero fill / drop of the tail.
+int resizeRows(plb_context *ctx, const void *src, void *dst, size_t rows, size_t src_bytes,
+               size_t dst_bytes);
+
 // ---- contraction launch (igemm_launch.cu) -----------------------------------
 
 // A fully resolved implicit-GEMM problem: one launch of the igemm kernel.

@@ -305,6 +305,41 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
     if (d_weight_grads_f32) PLB_CUDA(cudaMemsetAsync(d_weight_grads_f32, 0, n * sizeof(float), ctx->stream));
     return PLB_OK;
   }
+  if (ci % 8 != 0 || co % 8 != 0) {
+    // Channel counts TMA cannot address (a pixel must be a multiple of 16
+    // bytes): run on zero-padded copies and drop the padded rows / columns of
+    // the gradient.  Arena in scratch slot 7.
+    const size_t es2 = 2, G = p->groups;
+    const uint32_t cip = uint32_t((ci + 7) / 8 * 8), cop = uint32_t((co + 7) / 8 * 8);
+    const size_t in_px = size_t(p->batch) * s.H * s.W, out_px = size_t(p->batch) * s.OH * s.OW;
+    auto al = [](size_t n) { return (n + 255) & ~size_t(255); };
+    const size_t x_b = al(in_px * G * cip * es2), dy_b = al(out_px * G * cop * es2);
+    const size_t wp_elems = G * size_t(taps) * cop * cip;
+    const size_t w16_b = al(wp_elems * es2), w32_b = al(wp_elems * 4);
+    void *arena = nullptr;
+    if (int rc = scratch(ctx, 7, x_b + dy_b + 2 * w16_b + 2 * w32_b, &arena)) return rc;
+    uint8_t *xp = static_cast<uint8_t *>(arena), *dyp = xp + x_b, *w16 = dyp + dy_b, *t16 = w16 + w16_b,
+            *w32 = t16 + w16_b, *t32 = w32 + w32_b;
+    if (int rc = resizeRows(ctx, d_acts, xp, in_px * G, size_t(ci) * es2, cip * es2)) return rc;
+    if (int rc = resizeRows(ctx, d_out_grads, dyp, out_px * G, size_t(co) * es2, cop * es2)) return rc;
+    plb_conv_params q = *p;
+    q.in_chans_per_group = cip;
+    q.out_chans_per_group = cop;
+    if (int rc = plb_conv_wu(ctx, &q, opt, xp, dyp, d_weight_grads ? w16 : nullptr,
+                             d_weight_grads_f32 ? reinterpret_cast<float *>(w32) : nullptr))
+      return rc;
+    // [G][taps][cop][cip] -> drop rows, then columns
+    const size_t gt = G * size_t(taps);
+    if (d_weight_grads) {
+      if (int rc = resizeRows(ctx, w16, t16, gt, size_t(cop) * cip * es2, size_t(co) * cip * es2)) return rc;
+      if (int rc = resizeRows(ctx, t16, d_weight_grads, gt * co, cip * es2, size_t(ci) * es2)) return rc;
+    }
+    if (d_weight_grads_f32) {
+      if (int rc = resizeRows(ctx, w32, t32, gt, size_t(cop) * cip * 4, size_t(co) * cip * 4)) return rc;
+      if (int rc = resizeRows(ctx, t32, d_weight_grads_f32, gt * co, cip * 4, size_t(ci) * 4)) return rc;
+    }
+    return PLB_OK;
+  }
   WuArgs a{};
   planWu(*p, s, ctx->sm_count, opt ? opt->split_k : 0, opt ? opt->plan_flags : 0, &a, nullptr);
   a.status = ctx->d_status;

@@ -217,6 +217,24 @@ def test_conv_fwd_small(gpu_ctx, name):
                  f"fwd {name} uniform + bias")
 
 
+@pytest.mark.parametrize("ci,co,groups", [(20, 12, 1), (12, 64, 1), (64, 20, 1), (10, 6, 3), (5, 8, 1)])
+def test_conv_channel_counts_that_need_padding(gpu_ctx, ci, co, groups):
+    """Channel counts that are not a multiple of 8 run on zero-padded copies."""
+    kw = conv_case(3, [9, 10], [3, 3], ci, co, padding=1, groups=groups)   # channels per group
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(ci * 100 + co)
+    x, w, dy = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), f"fwd ci={ci} co={co}")
+    assert_exact(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), f"bwd ci={ci} co={co}")
+    dw16, dw32 = T.gpu_conv_wu(p, x, dy)
+    exp = oracle.conv_wu(spec, x, dy)[0]
+    assert_exact(dw32, exp, f"wu ci={ci} co={co}")
+    assert (dw32.astype(np.float16) == dw16).all()
+    bias = r.integers(-3, 4, p.groups * p.out_chans_per_group).astype(np.float32)
+    assert_exact(T.gpu_conv_fwd(p, x, w, bias=bias), oracle.conv_fwd(spec, x, w, bias), f"fwd+bias ci={ci} co={co}")
+
+
 @pytest.mark.parametrize("name", sorted(TRANSFORMED_CONVS))
 def test_conv_transform_views(gpu_ctx, name):
     """Input truncation, output truncation and output padding in all three passes."""
