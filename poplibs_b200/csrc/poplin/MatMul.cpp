@@ -116,6 +116,9 @@ void matMulImpl(Graph &graph, const Tensor &A_, const Tensor &B_, const Tensor &
 
   Tensor A = A_, B = B_;
   MatrixLayout la = layoutOf(A), lb = layoutOf(B);
+  // a transposed left operand is transposed into scratch by the library, which
+  // takes it densely packed only: a padded one is copied like any other layout
+  if (la.ok && la.transposed && la.ld != (long long)m) la.ok = false;
   if (!la.ok && k > 0 && m > 0) {
     A = denseCopy(graph, A_, prog);
     la = layoutOf(A);

@@ -27,10 +27,11 @@ int wuShape(const plb_conv_params &p, WuShape *s) {
     // (tools/single_conv_layer.cpp:725-733)
     return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half input only");
   for (unsigned d = 0; d != p.num_field_dims; ++d) {
+    // (kernel truncation and flip are resolved by plb_conv_wu before it gets here)
     if (p.in_dilation[d] != 1 || p.in_flip[d] || p.k_trunc_lo[d] || p.k_trunc_hi[d] || p.k_flip[d])
       return fail(PLB_ERR_UNSUPPORTED,
-                  "input dilation/flip and kernel truncation/flip are not implemented on this "
-                  "path yet");
+                  "input dilation/flip are not implemented on this path yet (kernel truncation "
+                  "and flip only through plb_conv_wu)");
     if (p.stride[d] > 8) return fail(PLB_ERR_UNSUPPORTED, "strides above 8 are not implemented");
   }
   const unsigned hd = p.num_field_dims == 2 ? 0 : ~0u, wd = p.num_field_dims - 1;
@@ -81,6 +82,10 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
   a->ci_blk64 = (a->ci_blk + 63) / 64;
   a->ci_blocks = (ci + a->ci_blk - 1) / a->ci_blk;
   a->taps_per_group = std::max(1, std::min(taps, 512 / a->ci_blk));
+  // two pipeline stages of (outGrad tile + one activation box per tap) must fit
+  while (a->taps_per_group > 1 &&
+         2 * (2 + a->taps_per_group * a->ci_blk64) * kWuBlockBytes > 200 * 1024)
+    --a->taps_per_group;
   a->tap_groups = (taps + a->taps_per_group - 1) / a->taps_per_group;
   // even out the groups (9 taps, 4 per group -> 3 groups of 3)
   a->taps_per_group = (taps + a->tap_groups - 1) / a->tap_groups;
@@ -166,6 +171,28 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
     plan->b_mn_major = 1;
     plan->halo_rows = a->strip_mode ? halo : 0;
     plan->workspace_bytes = size_t(ksplit) * taps * co * ci * sizeof(float);
+  }
+}
+
+// Gradient of the used taps -> gradient of the stored filter: tap (th, tw) of
+// the [G][JH*JW][inner] source goes to tap (r0h + th', r0w + tw') of the
+// zero-initialised [G][KH*KW][inner] destination, th' = JH-1-th when the
+// kernel is used flipped in that dimension.  `vec_bytes` is 4 or 2.
+template <typename T>
+__global__ void scatterTapsKernel(const T *__restrict__ src, T *__restrict__ dst, int groups, int KH,
+                                  int KW, int JH, int JW, int r0h, int r0w, int flip_h, int flip_w,
+                                  size_t inner) {
+  const size_t total = size_t(groups) * JH * JW * inner;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const size_t v = i % inner;
+    size_t t = i / inner;
+    const int tw = int(t % JW);
+    t /= JW;
+    const int th = int(t % JH);
+    const int g = int(t / JH);
+    const int oh = r0h + (flip_h ? JH - 1 - th : th), ow = r0w + (flip_w ? JW - 1 - tw : tw);
+    dst[(size_t(g) * KH * KW + size_t(oh) * KW + ow) * inner + v] = src[i];
   }
 }
 
@@ -292,6 +319,64 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
                 float *d_weight_grads_f32) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  {
+    // A truncated and / or flipped kernel: the gradient of the used taps is
+    // that of an ordinary kernel of the truncated extent (with the kernel
+    // padding of a flipped dimension swapped), scattered back into the stored
+    // filter, whose unused taps get zero.
+    bool special = false;
+    for (unsigned d = 0; d != p->num_field_dims && d < PLB_MAX_FIELD_DIMS; ++d)
+      special |= p->k_trunc_lo[d] || p->k_trunc_hi[d] || p->k_flip[d];
+    if (special) {
+      const std::string err = validate(*p);
+      if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+      if (p->num_field_dims > 2)
+        return fail(PLB_ERR_UNSUPPORTED, "3-D convolutions are not implemented on this path yet");
+      plb_conv_params q = *p;
+      int K[2] = {1, 1}, J[2] = {1, 1}, r0[2] = {0, 0}, fl[2] = {0, 0};
+      for (unsigned d = 0; d != p->num_field_dims; ++d) {
+        const unsigned slot = p->num_field_dims == 2 ? d : 1;  // 1-D: the width
+        K[slot] = int(p->kernel[d]);
+        J[slot] = int(p->kernel[d]) - int(p->k_trunc_lo[d]) - int(p->k_trunc_hi[d]);
+        r0[slot] = int(p->k_trunc_lo[d]);
+        fl[slot] = p->k_flip[d] ? 1 : 0;
+        q.kernel[d] = uint32_t(J[slot]);
+        q.k_trunc_lo[d] = q.k_trunc_hi[d] = 0;
+        q.k_flip[d] = 0;
+        if (p->k_flip[d]) std::swap(q.k_pad_lo[d], q.k_pad_hi[d]);
+      }
+      const size_t inner = size_t(p->out_chans_per_group) * p->in_chans_per_group;
+      const size_t full = size_t(p->groups) * K[0] * K[1] * inner, used = size_t(p->groups) * J[0] * J[1] * inner;
+      const size_t es = dtypeBytes(p->input_type);
+      if (d_weight_grads) PLB_CUDA(cudaMemsetAsync(d_weight_grads, 0, full * es, ctx->stream));
+      if (d_weight_grads_f32) PLB_CUDA(cudaMemsetAsync(d_weight_grads_f32, 0, full * sizeof(float), ctx->stream));
+      if (used == 0 || full == 0) return PLB_OK;
+      void *tmp = nullptr;
+      const size_t used16 = (used * es + 255) & ~size_t(255);
+      if (int rc = scratch(ctx, 6, used16 + used * sizeof(float) + 256, &tmp)) return rc;
+      void *t16 = tmp;
+      float *t32 = reinterpret_cast<float *>(static_cast<uint8_t *>(tmp) + used16);
+      if (int rc = plb_conv_wu(ctx, &q, opt, d_acts, d_out_grads, d_weight_grads ? t16 : nullptr,
+                               d_weight_grads_f32 ? t32 : nullptr))
+        return rc;
+      const int grid = int(std::min<size_t>((used + 255) / 256, size_t(ctx->sm_count) * 8));
+      if (d_weight_grads) {
+        scatterTapsKernel<uint16_t><<<grid, 256, 0, ctx->stream>>>(
+            static_cast<const uint16_t *>(t16), static_cast<uint16_t *>(d_weight_grads), int(p->groups),
+            K[0], K[1], J[0], J[1], r0[0], r0[1], fl[0], fl[1], inner);
+        PLB_CUDA(cudaGetLastError());
+        ctx->launches++;
+      }
+      if (d_weight_grads_f32) {
+        scatterTapsKernel<float><<<grid, 256, 0, ctx->stream>>>(
+            t32, d_weight_grads_f32, int(p->groups), K[0], K[1], J[0], J[1], r0[0], r0[1], fl[0], fl[1],
+            inner);
+        PLB_CUDA(cudaGetLastError());
+        ctx->launches++;
+      }
+      return PLB_OK;
+    }
+  }
   WuShape s;
   if (int rc = wuShape(*p, &s)) return rc;
   const int co = int(p->out_chans_per_group), ci = int(p->in_chans_per_group);

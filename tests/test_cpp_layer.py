@@ -101,6 +101,56 @@ def test_general_matrix_multiply_tool_against_oracle(tmp_path):
 
 
 @pytest.mark.gpu
+def test_fully_connected_layer_tool_against_oracle(tmp_path):
+    """Forward, backward and weight-update passes of a (grouped) fully connected
+    layer through matMulGrouped / transposeGroupedMatrix / matMul[Grouped]Acc,
+    on small-integer data: every sum is exact, so the dumps must equal the
+    model's products bit for bit (after the cast to the output type)."""
+    import numpy as np
+    import oracle
+    cases = [
+        ["--input-size", "256", "--output-size", "128", "--batch-size", "64", "--integer-data", "--learning-rate", "0.25"],
+        ["--input-size", "72", "--output-size", "40", "--batch-size", "24", "--num-groups", "3", "--integer-data",
+         "--learning-rate", "0.5", "--output-type", "float"],
+        ["--input-size", "128", "--output-size", "64", "--batch-size", "16", "--bias", "0", "--integer-data",
+         "--single-phase", "bwd"],
+        ["--input-size", "256", "--output-size", "128", "--batch-size", "32", "--input-type", "quarter",
+         "--fp8-scale-fwd=-1", "--fp8-scale-weights=0", "--fp8-scale-bwd=1"],
+        ["--input-size", "64", "--output-size", "64", "--batch-size", "8", "--inference-only", "--integer-data"],
+    ]
+    for i, flags in enumerate(cases):
+        d = tmp_path / f"fc{i}"
+        d.mkdir()
+        out = subprocess.run([tool("fully_connected_layer"), "--dump-dir", str(d)] + flags,
+                             capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, f"{flags}: {out.stderr}"
+        t = load_dump(str(d))
+        lr = float(flags[flags.index("--learning-rate") + 1]) if "--learning-rate" in flags else 0.5
+        out_f32 = "float" in flags
+        cast = (lambda a: a.astype(np.float32).astype(np.float64)) if out_f32 else \
+               (lambda a: a.astype(np.float16).astype(np.float64))
+        x, w = t["prevAct"], t["weights"]
+        if "nextAct" in t:
+            y = oracle.gemm(x, w)
+            if "biases" in t:
+                # the product is cast to the output type first, then the bias is added in that type
+                y = cast(cast(y) + t["biases"][:, None, :])
+            assert (t["nextAct"] == cast(y)).all(), flags
+        if "prevDeltas" in t:
+            dx = oracle.gemm(t["zDeltas"], w, transpose_b=True)
+            assert (t["prevDeltas"] == cast(dx)).all(), flags
+        if "weightsUpdated" in t:
+            dw = oracle.gemm(x, t["zDeltas"], transpose_a=True)
+            in_cast = lambda a: a.astype(np.float16).astype(np.float64)  # noqa: E731 weights have the input type
+            assert (t["weightsUpdated"] == in_cast(w - lr * dw)).all(), flags
+            if "biasesUpdated" in t:
+                db = t["zDeltas"].sum(axis=1)
+                assert (t["biasesUpdated"] == cast(t["biases"] - lr * db)).all(), flags
+        if "--inference-only" in flags:
+            assert "prevDeltas" not in t and "weightsUpdated" not in t
+
+
+@pytest.mark.gpu
 def test_single_conv_layer_tool_against_oracle(tmp_path):
     import numpy as np
     import oracle
