@@ -129,6 +129,47 @@ def test_planner_choices():
     assert plan.tiles == 0 and plan.flops == 0
 
 
+def test_planner_rules_for_pairs_halo_tiles_and_padding():
+    """What the closed-form planner picks, per layer shape (no GPU involved)."""
+    c2 = capi.conv_plan(capi.ConvParams.make(32, [56, 56], [3, 3], 64, 64, padding=1))
+    # small filter, one N tile: weights resident, one strip per filter column, CTA pairs
+    assert (c2.resident_weights, c2.halo_rows, c2.cta_pair) == (1, 2, 1)
+    c4 = capi.conv_plan(capi.ConvParams.make(256, [28, 28], [3, 3], 128, 128, padding=1))
+    # weights too large to keep resident: streamed, but still one activation strip per column
+    assert (c4.resident_weights, c4.halo_rows, c4.cta_pair) == (0, 2, 1)
+    assert c4.box_w * c4.box_n % 8 == 0 and c4.stages >= 3
+    bwd = capi.conv_plan(capi.ConvParams.make(256, [28, 28], [3, 3], 128, 128, padding=1), capi.PASS_TRAINING_BWD)
+    assert bwd.b_mn_major == 1 and bwd.cta_pair == 1
+    # short K loops (4 steps) do not pair: the lockstep costs more than it saves
+    c3b = capi.conv_plan(capi.ConvParams.make(256, [56, 56], [1, 1], 256, 512, stride=2))
+    assert (c3b.tile_n, c3b.cta_pair, c3b.halo_rows) == (256, 0, 0)
+    # a grid of a few tiles takes narrow tiles and no pairs
+    c1 = capi.matmul_plan(capi.MatmulDesc.make(512, 1024, 1024))
+    assert (c1.tile_n, c1.tiles, c1.grid, c1.cta_pair) == (64, 64, 64, 0)
+    big = capi.matmul_plan(capi.MatmulDesc.make(8192, 8192, 8192))
+    assert (big.tile_n, big.cta_pair, big.grid) == (256, 1, 148)
+    # plan flags
+    p = capi.ConvParams.make(256, [28, 28], [3, 3], 128, 128, padding=1)
+    off = capi.conv_plan(p, capi.PASS_TRAINING_FWD, capi.ConvOptions.make(plan_flags=capi.PLAN_NO_CTA_PAIR | capi.PLAN_NO_HALO))
+    assert (off.cta_pair, off.halo_rows) == (0, 0)
+    small = capi.ConvParams.make(2, [12, 12], [3, 3], 64, 64, padding=1)
+    assert capi.conv_plan(small).cta_pair == 0
+    forced = capi.conv_plan(small, capi.PASS_TRAINING_FWD, capi.ConvOptions.make(plan_flags=capi.PLAN_FORCE_CTA_PAIR))
+    assert forced.cta_pair == 1 and forced.grid % 2 == 0
+    # channel counts that TMA cannot address are planned on their padded sizes
+    odd = capi.conv_plan(capi.ConvParams.make(4, [9, 9], [3, 3], 20, 12, padding=1, groups=2))
+    assert odd.tile_n == 64 and odd.tiles > 0
+    assert capi.conv_plan(capi.ConvParams.make(4, [9, 9], [3, 3], 20, 12, padding=1), capi.PASS_TRAINING_BWD).tiles > 0
+    # the stem goes to the small-channel path
+    assert capi.conv_plan(capi.ConvParams.make(8, [224, 224], [7, 7], 3, 64, padding=3, stride=2)).kernel == 2
+    # weight update: one strip per filter column with a unit vertical stride, K split to fill the device
+    wu = capi.conv_wu_plan(capi.ConvParams.make(256, [28, 28], [3, 3], 128, 128, padding=1))
+    assert (wu.kernel, wu.halo_rows, wu.tile_n, wu.split_k, wu.grid) == (1, 2, 384, 49, 147)
+    # ... and tap groups sized so that two pipeline stages fit in shared memory
+    wide = capi.conv_wu_plan(capi.ConvParams.make(4, [9, 13], [4, 4], 8, 24, stride=3))
+    assert wide.halo_rows == 0 and wide.tile_n <= 10 * 32 and wide.stages >= 2
+
+
 def test_option_and_type_errors():
     with pytest.raises(capi.PlbError) as e:
         capi.matmul_plan(capi.MatmulDesc.make(4, 4, 4, input_type=capi.QUARTER, output_type=capi.FLOAT))
