@@ -696,9 +696,12 @@ int plb_conv_input_index(const plb_conv_params *p, uint32_t dim, uint32_t out_in
 
 uint64_t plb_conv_macs(const plb_conv_params *p) { return p ? numberOfMacs(*p) : 0; }
 
-int plb_conv_plan(const plb_conv_params *p, const plb_conv_options *opt, int32_t pass,
+int plb_conv_plan(const plb_conv_params *p_in, const plb_conv_options *opt, int32_t pass,
                   plb_plan *plan) {
-  if (!p || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  if (!p_in || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  // a flipped input runs as the ordinary convolution of the reversed tensor
+  plb_conv_params unflipped;
+  const plb_conv_params *p = unflippedInputParams(*p_in, &unflipped) ? &unflipped : p_in;
   ConvShape s;
   if (int rc = igemmConvShape(*p, &s)) return rc;
   *plan = plb_plan{};
@@ -738,6 +741,23 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
                     int transpose_and_flip_weights) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  {
+    // a flipped input: reverse it once (scratch slot 8), then an ordinary convolution
+    plb_conv_params q;
+    if (unflippedInputParams(*p, &q) && p->num_field_dims <= 2) {
+      const std::string err = validate(*p);
+      if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+      const bool two = p->num_field_dims == 2;
+      const uint32_t H = two ? p->field[0] : 1, W = p->field[two ? 1 : 0];
+      const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->input_type);
+      void *xf = nullptr;
+      if (int rc = scratch(ctx, 8, size_t(p->batch) * H * W * px + 256, &xf)) return rc;
+      if (int rc = flipField(ctx, d_in, xf, p->batch, H, W, px, two && p->in_flip[0],
+                             p->in_flip[two ? 1 : 0] != 0))
+        return rc;
+      return plb_convolution(ctx, &q, opt, xf, d_weights, d_bias, d_out, transpose_and_flip_weights);
+    }
+  }
   ConvShape s;
   if (int rc = igemmConvShape(*p, &s)) return rc;
   if (p->batch == 0 || p->groups == 0 || p->out_chans_per_group == 0 || s.OH == 0 || s.OW == 0)
@@ -841,6 +861,22 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
                  const void *d_out_grads, const void *d_weights, void *d_in_grads) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  {
+    // a flipped input: the gradient of the reversed input, reversed back
+    plb_conv_params q;
+    if (unflippedInputParams(*p, &q) && p->num_field_dims <= 2) {
+      const std::string err = validate(*p);
+      if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+      const bool two = p->num_field_dims == 2;
+      const uint32_t H = two ? p->field[0] : 1, W = p->field[two ? 1 : 0];
+      const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->output_type);
+      void *gf = nullptr;
+      if (int rc = scratch(ctx, 8, size_t(p->batch) * H * W * px + 256, &gf)) return rc;
+      if (int rc = plb_conv_bwd(ctx, &q, opt, d_out_grads, d_weights, gf)) return rc;
+      return flipField(ctx, gf, d_in_grads, p->batch, H, W, px, two && p->in_flip[0],
+                       p->in_flip[two ? 1 : 0] != 0);
+    }
+  }
   ConvShape s;
   if (int rc = igemmConvShape(*p, &s)) return rc;
   if (p->batch == 0 || p->groups == 0 || p->in_chans_per_group == 0 || s.H == 0 || s.W == 0)

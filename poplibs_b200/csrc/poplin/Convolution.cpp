@@ -277,13 +277,25 @@ void convolutionWithOutput(Graph &graph, const Tensor &in, const Tensor &weights
   const bool dilatedInput =
       std::any_of(canonical.inputTransform.dilation.begin(), canonical.inputTransform.dilation.end(),
                   [](unsigned d) { return d != 1; });
-  if (dilatedInput && transposeAndFlipWeights) {
+  if (dilatedInput) {
+    // A dilated input met without the transpose flag is the same computation
+    // with this convolution's own weights standing for the transposed, flipped
+    // ones: hand the library their channel-transposed, spatially flipped copy.
+    Tensor wFwd = wA;
+    if (!transposeAndFlipWeights) {
+      Tensor t = makeWeights(graph, weights.elementType(), G, ci, co, params.kernelShape,
+                             name + "/asForwardWeights");
+      if (weights.elementType() == poplar::QUARTER && weights.hasMetadata())
+        graph.setQuarterMetadata(t, weights.getMetadata());
+      weightsTransposeChansFlipXY(graph, weights, t, prog, name);
+      wFwd = t;
+    }
     const plb_conv_params fwd = internal::toPlb(getGradientParams(params).canonicalize());
     prog.add([=](plb_context *ctx) mutable {
       opt.scale_in = quarterExponent(inA);
-      opt.scale_weights = quarterExponent(wA);
+      opt.scale_weights = quarterExponent(wFwd);
       logging::poplin::trace("convolution (backward of a strided layer) " + name);
-      poplar::detail::check(plb_conv_bwd(ctx, &fwd, &opt, inA.devicePointer(), wA.devicePointer(),
+      poplar::detail::check(plb_conv_bwd(ctx, &fwd, &opt, inA.devicePointer(), wFwd.devicePointer(),
                                          outA.devicePointer()));
     });
     if (!outDirect) prog.add(poplar::program::Copy(outA, out));

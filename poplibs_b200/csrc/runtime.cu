@@ -371,6 +371,51 @@ int resizeRows(plb_context *ctx, const void *src, void *dst, size_t rows, size_t
   return PLB_OK;
 }
 
+// dst[n][h][w][:] = src[n][flip_h ? H-1-h : h][flip_w ? W-1-w : w][:], pixels of
+// `pixel_bytes` bytes: the spatial flip of the reference's input transform.
+__global__ void flipFieldKernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                size_t n_images, uint32_t H, uint32_t W, uint32_t pixel_bytes,
+                                int flip_h, int flip_w) {
+  const size_t total = n_images * H * W * pixel_bytes;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const uint32_t b = uint32_t(i % pixel_bytes);
+    size_t r = i / pixel_bytes;
+    const uint32_t w = uint32_t(r % W);
+    r /= W;
+    const uint32_t h = uint32_t(r % H);
+    const size_t n = r / H;
+    const uint32_t sh = flip_h ? H - 1 - h : h, sw = flip_w ? W - 1 - w : w;
+    dst[i] = src[((n * H + sh) * W + sw) * size_t(pixel_bytes) + b];
+  }
+}
+
+bool unflippedInputParams(const plb_conv_params &p, plb_conv_params *q) {
+  bool any = false;
+  *q = p;
+  for (unsigned d = 0; d != p.num_field_dims && d < PLB_MAX_FIELD_DIMS; ++d) {
+    if (!p.in_flip[d]) continue;
+    any = true;
+    q->in_flip[d] = 0;
+    std::swap(q->in_pad_lo[d], q->in_pad_hi[d]);
+    std::swap(q->in_trunc_lo[d], q->in_trunc_hi[d]);
+  }
+  return any;
+}
+
+int flipField(plb_context *ctx, const void *src, void *dst, size_t n_images, uint32_t H, uint32_t W,
+              size_t pixel_bytes, bool flip_h, bool flip_w) {
+  const size_t total = n_images * H * W * pixel_bytes;
+  if (total == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(ctx->sm_count) * 16));
+  flipFieldKernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint8_t *>(src),
+                                                 static_cast<uint8_t *>(dst), n_images, H, W,
+                                                 uint32_t(pixel_bytes), flip_h ? 1 : 0, flip_w ? 1 : 0);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
 int launchScaleRows(plb_context *ctx, void *out, const void *c, float beta, bool out_f32,
                     uint32_t rows, uint32_t cols, long long ldo, long long ldc) {
   if (rows == 0 || cols == 0) return PLB_OK;

@@ -27,7 +27,7 @@ struct plb_context {
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
   // grow-only scratch buffers: [0] operand rearrangement / partial sums,
   // [1..] staging for the host-buffer entry points
-  static constexpr int kScratchSlots = 8;
+  static constexpr int kScratchSlots = 10;
   void *scratch[kScratchSlots] = {};
   size_t scratch_bytes[kScratchSlots] = {};
 };
@@ -63,6 +63,15 @@ inline size_t dtypeBytes(int dtype) {
 // Row resize (runtime.cu): rows of src_bytes -> rows of dst_bytes, zero fill / drop of the tail.
 int resizeRows(plb_context *ctx, const void *src, void *dst, size_t rows, size_t src_bytes,
                size_t dst_bytes);
+
+// Input flip of the reference's input transform: the convolution of a flipped
+// input equals the convolution of the reversed tensor with the input padding and
+// truncation of the flipped dimensions swapped.  Returns true and fills `q` if
+// `p` flips its input in some dimension.
+bool unflippedInputParams(const plb_conv_params &p, plb_conv_params *q);
+// Spatial flip of an [n][H][W][pixel] tensor (runtime.cu).
+int flipField(plb_context *ctx, const void *src, void *dst, size_t n_images, uint32_t H, uint32_t W,
+              size_t pixel_bytes, bool flip_h, bool flip_w);
 
 // ---- contraction launch (igemm_launch.cu) -----------------------------------
 

@@ -298,8 +298,19 @@ using namespace plb;
 
 extern "C" {
 
-int plb_conv_wu_plan(const plb_conv_params *p, const plb_conv_options *opt, plb_plan *plan) {
-  if (!p || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+int plb_conv_wu_plan(const plb_conv_params *p_in, const plb_conv_options *opt, plb_plan *plan) {
+  if (!p_in || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  // plan what plb_conv_wu runs: flipped inputs are reversed first, truncated /
+  // flipped kernels are computed as ordinary kernels of the truncated extent
+  plb_conv_params q;
+  unflippedInputParams(*p_in, &q);
+  for (unsigned d = 0; d != q.num_field_dims && d < PLB_MAX_FIELD_DIMS; ++d) {
+    q.kernel[d] -= std::min(q.kernel[d], q.k_trunc_lo[d] + q.k_trunc_hi[d]);
+    q.k_trunc_lo[d] = q.k_trunc_hi[d] = 0;
+    if (q.k_flip[d]) std::swap(q.k_pad_lo[d], q.k_pad_hi[d]);
+    q.k_flip[d] = 0;
+  }
+  const plb_conv_params *p = &q;
   WuShape s;
   if (int rc = wuShape(*p, &s)) return rc;
   *plan = plb_plan{};
@@ -319,6 +330,23 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
                 float *d_weight_grads_f32) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  {
+    // a flipped input: reverse it once (scratch slot 8), then an ordinary weight update
+    plb_conv_params q;
+    if (unflippedInputParams(*p, &q) && p->num_field_dims <= 2) {
+      const std::string err = validate(*p);
+      if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+      const bool two = p->num_field_dims == 2;
+      const uint32_t H = two ? p->field[0] : 1, W = p->field[two ? 1 : 0];
+      const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->input_type);
+      void *xf = nullptr;
+      if (int rc = scratch(ctx, 8, size_t(p->batch) * H * W * px + 256, &xf)) return rc;
+      if (int rc = flipField(ctx, d_acts, xf, p->batch, H, W, px, two && p->in_flip[0],
+                             p->in_flip[two ? 1 : 0] != 0))
+        return rc;
+      return plb_conv_wu(ctx, &q, opt, xf, d_out_grads, d_weight_grads, d_weight_grads_f32);
+    }
+  }
   {
     // A truncated and / or flipped kernel: the gradient of the used taps is
     // that of an ordinary kernel of the truncated extent (with the kernel

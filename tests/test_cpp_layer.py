@@ -175,6 +175,18 @@ def test_single_conv_layer_tool_against_oracle(tmp_path):
         dict(flags=["--input-channels=64", "--output-channels=64", "--field={12,11}", "--kernel-size=3",
                     "--padding=1", "--stride=2", "--batch-size=2", "--integer-data", "--learning-rate=0.25"],
              spec=ConvSpec.simple(2, [12, 11], [3, 3], 64, 64, padding=1, stride=2), bias=True),
+        # a dilated input without the transpose flag (a transposed convolution written as a
+        # forward one) and a flipped input, forward pass
+        dict(flags=["--input-channels=64", "--output-channels=72", "--field={6,7}", "--kernel-size=3",
+                    "--padding=2", "--in-dilation=2", "--batch-size=2", "--bias=0", "--integer-data",
+                    "--single-phase=fwd"],
+             spec=ConvSpec(2, [6, 7], [3, 3], 64, 72, in_pad_lo=[2, 2], in_pad_hi=[2, 2], in_dilation=[2, 2]),
+             bias=False),
+        dict(flags=["--input-channels=64", "--output-channels=64", "--field={7,8}", "--kernel-size=3",
+                    "--padding-lower={2,0}", "--padding-upper={0,1}", "--flip-input={1,1}", "--batch-size=2",
+                    "--bias=0", "--integer-data", "--learning-rate=0.5"],
+             spec=ConvSpec(2, [7, 8], [3, 3], 64, 64, in_pad_lo=[2, 0], in_pad_hi=[0, 1], in_flip=[1, 1]),
+             bias=False),
         dict(flags=["--input-channels=32", "--output-channels=32", "--field={6,6}", "--kernel-size=3",
                     "--padding=1", "--conv-groups=2", "--batch-size=2", "--bias=0", "--integer-data",
                     "--learning-rate=0.5"],

@@ -3,11 +3,11 @@
 The role of the reference's random-parameter runs
 (tools/single_conv_layer_random.py:22-50, tests/poplin/CMakeLists.txt:1040-1065):
 every transform of ConvParams that the CUDA path implements is drawn at
-random -- input truncation and padding, kernel truncation, dilation, padding
-and flip, stride, output truncation and padding, groups, 1-D and 2-D fields --
+random -- input truncation padding and flip, kernel truncation, dilation,
+padding and flip, stride, output truncation and padding, groups, 1-D and 2-D fields --
 and the result must match the oracle bit for bit on +-1 data (all sums stay
-below 2048, exact in half).  Parameters the path does not implement (input
-dilation / flip) are not drawn; a drawn combination that is not a valid
+below 2048, exact in half).  Free-standing input dilation, which the path does
+not implement, is not drawn; a drawn combination that is not a valid
 convolution (empty output) is redrawn.
 """
 import math
@@ -33,11 +33,11 @@ def draw(seed):
             groups=int(r.choice([1, 1, 2])),
             in_trunc_lo=vec(0, 2), in_trunc_hi=vec(0, 2), in_pad_lo=vec(0, 3), in_pad_hi=vec(0, 3),
             k_trunc_lo=vec(0, 1), k_trunc_hi=vec(0, 1), k_dilation=vec(1, 3), k_pad_lo=vec(0, 2),
-            k_pad_hi=vec(0, 2), k_flip=vec(0, 1), stride=vec(1, 3), out_trunc_lo=vec(0, 2),
+            k_pad_hi=vec(0, 2), k_flip=vec(0, 1), in_flip=vec(0, 1), stride=vec(1, 3), out_trunc_lo=vec(0, 2),
             out_trunc_hi=vec(0, 2), out_pad_lo=vec(0, 2), out_pad_hi=vec(0, 2))
         # keep the draw simple half of the time: most layers use few transforms
         if r.random() < 0.5:
-            for name in ("in_trunc_lo", "in_trunc_hi", "k_trunc_lo", "k_trunc_hi", "k_pad_lo", "k_pad_hi",
+            for name in ("in_flip", "in_trunc_lo", "in_trunc_hi", "k_trunc_lo", "k_trunc_hi", "k_pad_lo", "k_pad_hi",
                          "out_trunc_lo", "out_trunc_hi", "out_pad_lo", "out_pad_hi"):
                 if r.random() < 0.7:
                     kw[name] = [0] * nd
