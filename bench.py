@@ -205,7 +205,7 @@ class Workload:
     """Device-resident rotating buffer sets (so that consecutive steps do not
     find their inputs in L2) and pinned host copies for the end-to-end leg."""
 
-    def __init__(self, name, spec, ctx, device, rank=0, world=1, sets_bytes_target=300 << 20):
+    def __init__(self, name, spec, ctx, device, rank=0, world=1, sets_bytes_target=300 << 20, force_sets=0):
         import torch
         from poplibs_b200 import capi
         self.name, self.spec, self.ctx, self.capi = name, spec, ctx, capi
@@ -268,6 +268,8 @@ class Workload:
             per_set = a.numel() * a.element_size() + b.numel() * b.element_size() + 2 * m * n
             out_shape = (m, n)
         self.nsets = int(max(2, min(16, -(-sets_bytes_target // max(per_set, 1)))))
+        if force_sets > 0:
+            self.nsets = force_sets
         self.dev = []
         for _ in range(self.nsets):
             d = {k: v.to(device, non_blocking=False) for k, v in self.host.items()}
@@ -427,6 +429,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="time one library call per step instead of replaying a CUDA graph")
+    ap.add_argument("--buffer-sets", type=int, default=0,
+                    help="number of rotating buffer sets (default: enough to exceed L2; 1 = every step "
+                         "re-reads the same, L2-resident, inputs: a diagnostic, not a bench value)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -474,8 +479,11 @@ def main():
     # update at N > 1) are ordered with the kernels without host synchronisation
     torch_stream = torch.cuda.Stream(device=device)
     ctx = capi.Context(local_rank, stream=torch_stream.cuda_stream)
-    wl = Workload(args.workload, spec, ctx, device, rank, world)
+    wl = Workload(args.workload, spec, ctx, device, rank, world, force_sets=args.buffer_sets)
     config["plan"] = wl.plan
+    config["buffer_sets"] = wl.nsets
+    if args.buffer_sets > 0:
+        config["l2"] = f"DIAGNOSTIC: {wl.nsets} buffer set(s) forced; inputs may stay in L2 between steps"
     if world > 1 and spec["kind"] == "conv":
         config["allreduce"] = wl.allreduce
         if spec["pass_"] == "wu":
