@@ -699,6 +699,7 @@ uint64_t plb_conv_macs(const plb_conv_params *p) { return p ? numberOfMacs(*p) :
 int plb_conv_plan(const plb_conv_params *p_in, const plb_conv_options *opt, int32_t pass,
                   plb_plan *plan) {
   if (!p_in || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  if (p_in->num_field_dims == 3) return conv3dPlan(*p_in, opt, pass, plan);
   // a flipped input runs as the ordinary convolution of the reversed tensor
   plb_conv_params unflipped;
   const plb_conv_params *p = unflippedInputParams(*p_in, &unflipped) ? &unflipped : p_in;
@@ -741,6 +742,8 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
                     int transpose_and_flip_weights) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  if (p->num_field_dims == 3)
+    return conv3dFwd(ctx, *p, opt, d_in, d_weights, d_bias, d_out, transpose_and_flip_weights);
   {
     // a flipped input: reverse it once (scratch slot 8), then an ordinary convolution
     plb_conv_params q;
@@ -861,6 +864,7 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
                  const void *d_out_grads, const void *d_weights, void *d_in_grads) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  if (p->num_field_dims == 3) return conv3dBwd(ctx, *p, opt, d_out_grads, d_weights, d_in_grads);
   {
     // a flipped input: the gradient of the reversed input, reversed back
     plb_conv_params q;
@@ -961,13 +965,18 @@ int plb_conv_fwd_host_async(plb_context *ctx, const plb_conv_params *p,
                             const float *h_bias, void *h_out) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
-  ConvShape s;
-  if (int rc = igemmConvShape(*p, &s)) return rc;
+  const std::string err = validate(*p);
+  if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
   const size_t es = dtypeBytes(p->input_type), os = dtypeBytes(p->output_type);
-  const size_t in_bytes = size_t(p->batch) * s.H * s.W * p->groups * p->in_chans_per_group * es;
-  const size_t w_bytes =
-      size_t(p->groups) * s.KH * s.KW * p->in_chans_per_group * p->out_chans_per_group * es;
-  const size_t out_bytes = size_t(p->batch) * s.OH * s.OW * p->groups * p->out_chans_per_group * os;
+  size_t in_px = 1, taps = 1, out_px = 1;
+  for (unsigned d = 0; d != p->num_field_dims; ++d) {
+    in_px *= p->field[d];
+    taps *= p->kernel[d];
+    out_px *= size_t(outputSize(*p, d));
+  }
+  const size_t in_bytes = size_t(p->batch) * in_px * p->groups * p->in_chans_per_group * es;
+  const size_t w_bytes = size_t(p->groups) * taps * p->in_chans_per_group * p->out_chans_per_group * es;
+  const size_t out_bytes = size_t(p->batch) * out_px * p->groups * p->out_chans_per_group * os;
   const size_t bias_bytes = size_t(p->groups) * p->out_chans_per_group * sizeof(float);
   void *di = nullptr, *dw = nullptr, *dout = nullptr, *dbias = nullptr;
   if (int rc = scratch(ctx, 1, in_bytes + 16, &di)) return rc;

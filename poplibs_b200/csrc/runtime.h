@@ -27,7 +27,7 @@ struct plb_context {
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
   // grow-only scratch buffers: [0] operand rearrangement / partial sums,
   // [1..] staging for the host-buffer entry points
-  static constexpr int kScratchSlots = 10;
+  static constexpr int kScratchSlots = 12;
   void *scratch[kScratchSlots] = {};
   size_t scratch_bytes[kScratchSlots] = {};
 };
@@ -72,6 +72,17 @@ bool unflippedInputParams(const plb_conv_params &p, plb_conv_params *q);
 // Spatial flip of an [n][H][W][pixel] tensor (runtime.cu).
 int flipField(plb_context *ctx, const void *src, void *dst, size_t n_images, uint32_t H, uint32_t W,
               size_t pixel_bytes, bool flip_h, bool flip_w);
+
+// ---- 3-D fields (conv3d.cu): depth folded into the channels of a 2-D problem ----
+int conv3dFwd(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+              const void *d_in, const void *d_weights, const float *d_bias, void *d_out,
+              int transpose_and_flip_weights);
+int conv3dBwd(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+              const void *d_out_grads, const void *d_weights, void *d_in_grads);
+int conv3dWu(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+             const void *d_acts, const void *d_out_grads, void *d_weight_grads,
+             float *d_weight_grads_f32);
+int conv3dPlan(const plb_conv_params &p, const plb_conv_options *opt, int32_t pass, plb_plan *plan);
 
 // ---- contraction launch (igemm_launch.cu) -----------------------------------
 

@@ -300,6 +300,7 @@ extern "C" {
 
 int plb_conv_wu_plan(const plb_conv_params *p_in, const plb_conv_options *opt, plb_plan *plan) {
   if (!p_in || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  if (p_in->num_field_dims == 3) return conv3dPlan(*p_in, opt, PLB_PASS_TRAINING_WU, plan);
   // plan what plb_conv_wu runs: flipped inputs are reversed first, truncated /
   // flipped kernels are computed as ordinary kernels of the truncated extent
   plb_conv_params q;
@@ -330,6 +331,8 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
                 float *d_weight_grads_f32) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  if (p->num_field_dims == 3)
+    return conv3dWu(ctx, *p, opt, d_acts, d_out_grads, d_weight_grads, d_weight_grads_f32);
   {
     // a flipped input: reverse it once (scratch slot 8), then an ordinary weight update
     plb_conv_params q;

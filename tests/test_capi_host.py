@@ -170,6 +170,34 @@ def test_planner_rules_for_pairs_halo_tiles_and_padding():
     assert wide.halo_rows == 0 and wide.tile_n <= 10 * 32 and wide.stages >= 2
 
 
+def test_3d_layers_plan_as_2d_layers_with_depth_folded_into_channels():
+    """A 3-D field runs as the 2-D problem over the inner dimensions with the
+    kernel depth folded into the channels: batch * out-depth images and KD * Ci
+    input channels (forward, weight update), batch * depth images and KD * Co
+    output channels (backward).  Planning also cross-checks the device-side depth
+    index arithmetic against getInputIndex for every (output, kernel) pair."""
+    p3 = capi.ConvParams.make(4, [6, 14, 14], [3, 3, 3], 64, 128, padding=1, stride=[2, 1, 1])
+    od = p3.output_field()[0]
+    assert od == 3
+    fwd2 = capi.ConvParams.make(4 * od, [14, 14], [3, 3], 3 * 64, 128, padding=1)
+    bwd2 = capi.ConvParams.make(4 * 6, [14, 14], [3, 3], 64, 3 * 128, padding=1)
+    same = ("kernel", "tile_m", "tile_n", "stages", "grid", "tiles", "halo_rows", "cta_pair", "split_k")
+    for pass_id, p2 in ((capi.PASS_TRAINING_FWD, fwd2), (capi.PASS_TRAINING_BWD, bwd2), (capi.PASS_TRAINING_WU, fwd2)):
+        a, b = capi.conv_plan(p3, pass_id).as_dict(), capi.conv_plan(p2, pass_id).as_dict()
+        assert {k: a[k] for k in same} == {k: b[k] for k in same}, pass_id
+        assert a["flops"] == 2 * p3.macs()
+    # every depth transform is accepted (it only changes the gather)
+    odd = capi.ConvParams.make(2, [7, 5, 6], [3, 1, 3], 8, 16, in_pad_lo=[2, 0, 1], in_pad_hi=[0, 0, 1],
+                               k_dilation=[2, 1, 1], in_dilation=[2, 1, 1], in_trunc_lo=[1, 0, 0],
+                               k_flip=[1, 0, 0], in_flip=[1, 0, 0], out_pad_lo=[1, 0, 0], out_trunc_hi=[1, 0, 0],
+                               stride=[2, 1, 1])
+    for pass_id in (capi.PASS_TRAINING_FWD, capi.PASS_TRAINING_BWD, capi.PASS_TRAINING_WU):
+        assert capi.conv_plan(odd, pass_id).flops == 2 * odd.macs()
+    # inner-dimension limits are those of the 2-D path
+    with pytest.raises(capi.PlbError):
+        capi.conv_plan(capi.ConvParams.make(1, [4, 6, 6], [1, 3, 3], 16, 16, in_dilation=[1, 2, 1]))
+
+
 def test_option_and_type_errors():
     with pytest.raises(capi.PlbError) as e:
         capi.matmul_plan(capi.MatmulDesc.make(4, 4, 4, input_type=capi.QUARTER, output_type=capi.FLOAT))

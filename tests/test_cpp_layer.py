@@ -191,6 +191,13 @@ def test_single_conv_layer_tool_against_oracle(tmp_path):
                     "--padding=1", "--conv-groups=2", "--batch-size=2", "--bias=0", "--integer-data",
                     "--learning-rate=0.5"],
              spec=ConvSpec.simple(2, [6, 6], [3, 3], 32, 32, padding=1, groups=2), bias=False),
+        # a 3-D field in all three passes
+        dict(flags=["--input-channels=16", "--output-channels=24", "--field={5,6,6}", "--kernel-size=3",
+                    "--padding=1", "--batch-size=2", "--bias=0", "--integer-data", "--learning-rate=0.5"],
+             spec=ConvSpec.simple(2, [5, 6, 6], [3, 3, 3], 16, 24, padding=1), bias=False),
+        dict(flags=["--input-channels=16", "--output-channels=16", "--field={6,7,7}", "--kernel-size=3",
+                    "--padding=1", "--stride={2,1,2}", "--batch-size=2", "--integer-data", "--learning-rate=0.5"],
+             spec=ConvSpec.simple(2, [6, 7, 7], [3, 3, 3], 16, 16, padding=1, stride=[2, 1, 2]), bias=True),
         dict(flags=["--input-channels=128", "--output-channels=64", "--field={8,8}", "--kernel-size=3",
                     "--padding=1", "--batch-size=2", "--bias=0", "--input-type=quarter",
                     "--fp8-scale-fwd=1", "--fp8-scale-weights=0", "--fp8-scale-bwd=1"],

@@ -249,6 +249,46 @@ def test_conv_transform_views(gpu_ctx, name):
     assert_exact(dw32, oracle.conv_wu(spec, x, dy)[0], f"wu {name}")
 
 
+# 3-D fields: the depth dimension is folded into the channels of a 2-D problem,
+# so every transform of that dimension is fair game.
+CONVS_3D = {
+    "3x3x3_pad1": conv_case(2, [5, 6, 7], [3, 3, 3], 16, 24, padding=1),
+    "depth_stride2": conv_case(2, [7, 6, 6], [3, 3, 3], 16, 16, padding=1, stride=[2, 1, 1]),
+    "all_s2": conv_case(1, [8, 9, 9], [3, 3, 3], 16, 32, padding=1, stride=2),
+    "1x1x1": conv_case(2, [3, 4, 4], [1, 1, 1], 32, 16),
+    "depth_only_kernel": conv_case(2, [6, 5, 5], [3, 1, 1], 64, 64, padding=[1, 0, 0]),
+    "groups_unaligned": conv_case(2, [4, 5, 5], [2, 3, 3], 6, 10, padding=[0, 1, 1], groups=2),
+    "depth_transforms": conv_case(2, [7, 5, 6], [3, 1, 3], 8, 16, in_pad_lo=[2, 0, 1], in_pad_hi=[0, 0, 1],
+                                  k_dilation=[2, 1, 1], in_dilation=[2, 1, 1], in_trunc_lo=[1, 0, 0],
+                                  k_flip=[1, 0, 0], in_flip=[1, 0, 0], out_pad_lo=[1, 0, 0],
+                                  out_trunc_hi=[1, 0, 0], stride=[2, 1, 1]),
+    "depth_kernel_trunc_pad": conv_case(1, [6, 4, 4], [4, 3, 3], 8, 8, padding=[2, 1, 1], k_trunc_lo=[1, 0, 0],
+                                        k_pad_hi=[1, 0, 0], out_pad_hi=[2, 0, 0]),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CONVS_3D))
+def test_conv_3d_all_passes(gpu_ctx, name):
+    kw = CONVS_3D[name]
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(zlib.crc32(name.encode()) % 1000 + 11)
+    x, w, dy = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), f"3-D fwd {name}")
+    assert_exact(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), f"3-D bwd {name}")
+    dw16, dw32 = T.gpu_conv_wu(p, x, dy)
+    assert_exact(dw32, oracle.conv_wu(spec, x, dy)[0], f"3-D wu {name}")
+    assert (dw32.astype(np.float16) == dw16).all()
+    x, w, dy = conv_data(p, kw, r, exact=False)
+    bias = r.uniform(-2, 6, p.groups * p.out_chans_per_group).astype(np.float32)
+    assert_close(T.gpu_conv_fwd(p, x, w, bias=bias), oracle.conv_fwd(spec, x, w, bias), REL_HALF,
+                 f"3-D fwd {name} uniform + bias")
+    assert_close(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), REL_HALF, f"3-D bwd {name} uniform")
+    assert_close(T.gpu_conv_wu(p, x, dy)[0], oracle.conv_wu(spec, x, dy)[0], REL_HALF, f"3-D wu {name} uniform")
+    for pass_id in (capi.PASS_TRAINING_FWD, capi.PASS_TRAINING_BWD, capi.PASS_TRAINING_WU):
+        assert capi.conv_plan(p, pass_id).flops == 2 * p.macs()
+
+
 @pytest.mark.parametrize("name", sorted({**SMALL_CONVS, **STRIDED_CONVS}))
 def test_conv_bwd_small(gpu_ctx, name):
     kw = {**SMALL_CONVS, **STRIDED_CONVS}[name]

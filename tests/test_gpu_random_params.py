@@ -22,19 +22,22 @@ from poplibs_b200 import capi
 pytestmark = pytest.mark.gpu
 
 
-def draw(seed):
-    r = np.random.default_rng(1000 + seed)
+def draw(seed, dims=None):
+    r = np.random.default_rng(1000 + seed + (50000 if dims else 0))
     for _ in range(200):
-        nd = int(r.integers(1, 3))
+        nd = dims or int(r.integers(1, 3))
         vec = lambda lo, hi: [int(v) for v in r.integers(lo, hi + 1, nd)]  # noqa: E731
         kw = dict(
-            batch=int(r.integers(1, 5)), field=vec(5, 14), kernel=vec(1, 5),
+            batch=int(r.integers(1, 5)), field=vec(3, 8) if nd == 3 else vec(5, 14),
+            kernel=vec(1, 3) if nd == 3 else vec(1, 5),
             in_chans=int(r.choice([8, 16, 24, 40, 64])), out_chans=int(r.choice([8, 16, 24, 40, 72])),
             groups=int(r.choice([1, 1, 2])),
             in_trunc_lo=vec(0, 2), in_trunc_hi=vec(0, 2), in_pad_lo=vec(0, 3), in_pad_hi=vec(0, 3),
             k_trunc_lo=vec(0, 1), k_trunc_hi=vec(0, 1), k_dilation=vec(1, 3), k_pad_lo=vec(0, 2),
             k_pad_hi=vec(0, 2), k_flip=vec(0, 1), in_flip=vec(0, 1), stride=vec(1, 3), out_trunc_lo=vec(0, 2),
             out_trunc_hi=vec(0, 2), out_pad_lo=vec(0, 2), out_pad_hi=vec(0, 2))
+        if nd == 3:
+            kw["in_dilation"] = [int(r.integers(1, 3)), 1, 1]
         # keep the draw simple half of the time: most layers use few transforms
         if r.random() < 0.5:
             for name in ("in_flip", "in_trunc_lo", "in_trunc_hi", "k_trunc_lo", "k_trunc_hi", "k_pad_lo", "k_pad_hi",
@@ -68,9 +71,7 @@ def data(kw, p, r):
     return x, w, dy
 
 
-@pytest.mark.parametrize("seed", range(120))
-def test_random_conv_params(gpu_ctx, seed):
-    kw, p = draw(seed)
+def check_all_passes(seed, kw, p):
     spec = T.spec_from_params(p)
     nd = len(kw["field"])
     r = T.rng(seed)
@@ -78,9 +79,23 @@ def test_random_conv_params(gpu_ctx, seed):
     what = f"seed {seed}: {kw}"
     got = T.gpu_conv_fwd(p, x, w)
     assert np.array_equal(got.astype(np.float64), oracle.conv_fwd(spec, x, w).reshape(got.shape)), "fwd " + what
-    if all(kw["stride"][d] == 1 or math.gcd(kw["k_dilation"][d], kw["stride"][d]) == 1 for d in range(nd)):
+    # the depth dimension of a 3-D field is gathered, whatever its transforms
+    inner = range(1, 3) if nd == 3 else range(nd)
+    if all(kw["stride"][d] == 1 or math.gcd(kw["k_dilation"][d], kw["stride"][d]) == 1 for d in inner):
         got = T.gpu_conv_bwd(p, dy, w)
         assert np.array_equal(got.astype(np.float64), oracle.conv_bwd(spec, dy, w).reshape(got.shape)), "bwd " + what
     if all(s <= 8 for s in kw["stride"]):
         _, dw32 = T.gpu_conv_wu(p, x, dy)
         assert np.array_equal(dw32.astype(np.float64), oracle.conv_wu(spec, x, dy)[0].reshape(dw32.shape)), "wu " + what
+
+
+@pytest.mark.parametrize("seed", range(120))
+def test_random_conv_params(gpu_ctx, seed):
+    kw, p = draw(seed)
+    check_all_passes(seed, kw, p)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_conv_params_3d(gpu_ctx, seed):
+    kw, p = draw(seed, dims=3)
+    check_all_passes(seed, kw, p)
