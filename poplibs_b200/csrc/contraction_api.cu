@@ -351,40 +351,40 @@ __global__ void gatherTapsKernel(const uint4 *__restrict__ src, uint4 *__restric
 }
 
 // One dimension of the backward pass of a strided convolution, for the input
-// positions i*stride + phase: which filter taps reach them and where.
+// positions i*stride + phase: which filter taps reach them and where.  Tap r
+// reaches the phase iff (phase + pad - r*dil) is a multiple of the stride; with
+// g = gcd(dil, stride) those taps are r0, r0 + stride/g, ... and, from one to the
+// next, the output index read at a fixed i moves by dil/g.
 struct BwdPhase {
   int first_tap;   // r0: smallest tap with (phase + pad - r*dil) divisible by stride
-  int taps;        // J: taps r0, r0 + stride, ...
+  int taps;        // J: taps r0, r0 + step, ...
+  int step;        // stride / gcd(dil, stride)
+  int dil;         // dil / gcd(dil, stride): dilation of the gathered sub-filter
   int offset;      // (phase + pad - r0*dil) / stride: output index read by tap r0 at i = 0
   int extent;      // input positions of this phase
 };
-// Returns false when dilation and stride share a factor (taps are then not
-// evenly spaced; not implemented).
-bool bwdPhase(int phase, int in_size, int kernel, int pad, int dil, int stride, BwdPhase *out) {
+void bwdPhase(int phase, int in_size, int kernel, int pad, int dil, int stride, BwdPhase *out) {
+  int g = dil, t = stride;
+  while (t) {
+    const int u = g % t;
+    g = t;
+    t = u;
+  }
   out->extent = phase < in_size ? (in_size - phase + stride - 1) / stride : 0;
   out->first_tap = -1;
   out->taps = 0;
   out->offset = 0;
+  out->step = stride / g;
+  out->dil = dil / g;
   for (int r = 0; r < kernel; ++r) {
     const int num = phase + pad - r * dil;
     if (((num % stride) + stride) % stride != 0) continue;
     if (out->first_tap < 0) {
       out->first_tap = r;
-      // exact: num is a multiple of stride (possibly negative)
-      out->offset = num / stride;
-    } else if ((r - out->first_tap) % stride != 0) {
-      return false;
+      out->offset = num / stride;  // exact: num is a multiple of stride (possibly negative)
     }
     ++out->taps;
   }
-  if (out->taps > 1) {
-    // evenly spaced taps need the second one exactly `stride` further on
-    int second = -1;
-    for (int r = out->first_tap + 1; r < kernel && second < 0; ++r)
-      if ((((phase + pad - r * dil) % stride) + stride) % stride == 0) second = r;
-    if (second != out->first_tap + stride) return false;
-  }
-  return true;
 }
 
 // ---- channel counts TMA cannot address -------------------------------------------
@@ -449,10 +449,10 @@ int usedTaps(plb_context *ctx, const plb_conv_params &p, const ConvShape &s, con
 // to the strided sub-lattice of the input gradient.
 int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
                    const ConvShape &s, const void *dy, const void *w, void *dx) {
-  if (p.input_type != PLB_HALF)
-    return fail(PLB_ERR_UNSUPPORTED,
-                "backward pass of a strided quarter convolution is not implemented on this path yet");
-  const size_t es = 2, os = dtypeBytes(p.output_type);
+  // 8-bit operands have no MN-major form: their gathered sub-filters are
+  // transposed per tap ([Co][Ci] -> [Ci][Co]) into a second buffer
+  const bool fp8 = p.input_type == PLB_QUARTER;
+  const size_t es = dtypeBytes(p.input_type), os = dtypeBytes(p.output_type);
   const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
   const uint64_t ctot = uint64_t(p.groups) * ci, cotot = uint64_t(p.groups) * co;
   const size_t inner = size_t(co) * ci;  // elements per tap and group
@@ -460,16 +460,8 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
     return fail(PLB_ERR_UNSUPPORTED, "weights must be 16-byte aligned per tap");
   // phases and their taps
   std::vector<BwdPhase> ph(size_t(s.strH)), pw(size_t(s.strW));
-  for (int a = 0; a < s.strH; ++a)
-    if (!bwdPhase(a, s.He, s.KH, s.padH, s.dilH, s.strH, &ph[size_t(a)]))
-      return fail(PLB_ERR_UNSUPPORTED,
-                  "backward pass: kernel dilation and stride with a common factor are not "
-                  "implemented on this path yet");
-  for (int b = 0; b < s.strW; ++b)
-    if (!bwdPhase(b, s.We, s.KW, s.padW, s.dilW, s.strW, &pw[size_t(b)]))
-      return fail(PLB_ERR_UNSUPPORTED,
-                  "backward pass: kernel dilation and stride with a common factor are not "
-                  "implemented on this path yet");
+  for (int a = 0; a < s.strH; ++a) bwdPhase(a, s.He, s.KH, s.padH, s.dilH, s.strH, &ph[size_t(a)]);
+  for (int b = 0; b < s.strW; ++b) bwdPhase(b, s.We, s.KW, s.padW, s.dilW, s.strW, &pw[size_t(b)]);
   // positions no tap reaches get zero
   bool any_empty = false;
   size_t scratch_elems = 0;
@@ -484,7 +476,8 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
   void *ws = nullptr;
   // one buffer per phase: the launches of different phases are in flight together
   const size_t slot = (scratch_elems * es + 255) & ~size_t(255);
-  if (int rc = scratch(ctx, 0, slot * size_t(s.strH) * s.strW + 256, &ws)) return rc;
+  const size_t phases = size_t(s.strH) * s.strW;
+  if (int rc = scratch(ctx, 0, slot * phases * (fp8 ? 2 : 1) + 256, &ws)) return rc;
   for (int a = 0; a < s.strH; ++a)
     for (int b = 0; b < s.strW; ++b) {
       const BwdPhase &A = ph[size_t(a)], &B = pw[size_t(b)];
@@ -494,12 +487,20 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
       const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 8));
       gatherTapsKernel<<<grid, 256, 0, ctx->stream>>>(
           static_cast<const uint4 *>(w), reinterpret_cast<uint4 *>(wsub), int(p.groups), s.KH, s.KW,
-          A.taps, B.taps, A.first_tap, B.first_tap, s.strH, s.strW, inner * es / 16, s.flipH,
+          A.taps, B.taps, A.first_tap, B.first_tap, A.step, B.step, inner * es / 16, s.flipH,
           s.flipW);
       PLB_CUDA(cudaGetLastError());
       ctx->launches++;
+      if (fp8) {
+        uint8_t *wt = static_cast<uint8_t *>(ws) + slot * (phases + size_t(a) * s.strW + b);
+        if (int rc = plb_transpose_matrix(ctx, 1, uint32_t(p.groups * A.taps * B.taps), uint32_t(co),
+                                          uint32_t(ci), wsub, wt))
+          return rc;
+        wsub = wt;
+      }
       for (unsigned g = 0; g < p.groups; ++g) {
         IgemmProblem r;
+        r.fp8 = fp8;
         r.act = static_cast<const uint8_t *>(dy) +
                 ((size_t(s.opH) * s.OW + s.opW) * cotot + size_t(g) * co) * es;
         r.act_dims[0] = co;
@@ -509,13 +510,21 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
         r.act_strides[0] = cotot * es;
         r.act_strides[1] = uint64_t(s.OW) * cotot * es;
         r.act_strides[2] = uint64_t(s.OH) * s.OW * cotot * es;
-        // gathered [tap][Co][Ci]: K = co rows of N = ci, an MN-major right operand
-        r.b_mn = true;
         r.wgt = wsub + size_t(g) * A.taps * B.taps * inner * es;
-        r.wgt_dims[0] = ci;
-        r.wgt_dims[1] = co;
+        if (fp8) {
+          // transposed [tap][Ci][Co]: a K-major right operand
+          r.wgt_dims[0] = co;
+          r.wgt_dims[1] = ci;
+          r.wgt_strides[0] = co * es;
+          if (opt) r.alpha = std::ldexp(1.0f, opt->scale_in + opt->scale_weights);
+        } else {
+          // gathered [tap][Co][Ci]: K = co rows of N = ci, an MN-major right operand
+          r.b_mn = true;
+          r.wgt_dims[0] = ci;
+          r.wgt_dims[1] = co;
+          r.wgt_strides[0] = ci * es;
+        }
         r.wgt_dims[2] = uint64_t(A.taps) * B.taps;
-        r.wgt_strides[0] = ci * es;
         r.wgt_strides[1] = inner * es;
         r.out_w = B.extent;
         r.out_h = A.extent;
@@ -526,10 +535,10 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
         r.taps_w = B.taps;
         // position i of the phase reads output index i + offset - j*dil for the
         // j-th gathered tap: a correlation with the taps reversed
-        r.dil_h = s.dilH;
-        r.dil_w = s.dilW;
-        r.pad_h = (A.taps - 1) * s.dilH - A.offset;
-        r.pad_w = (B.taps - 1) * s.dilW - B.offset;
+        r.dil_h = A.dil;
+        r.dil_w = B.dil;
+        r.pad_h = (A.taps - 1) * A.dil - A.offset;
+        r.pad_w = (B.taps - 1) * B.dil - B.offset;
         // (a flipped forward kernel was un-flipped by the gather)
         r.flip_h = 1;
         r.flip_w = 1;

@@ -569,6 +569,44 @@ def test_conv_quarter_fwd_bwd(gpu_ctx):
     assert_exact(got, oracle.conv_bwd(spec, dyv, wv), "quarter bwd")
 
 
+@pytest.mark.parametrize("name,kw", [
+    ("3x3_s2", conv_case(2, [9, 10], [3, 3], 64, 32, padding=1, stride=2)),
+    ("1x1_s2", conv_case(2, [8, 8], [1, 1], 32, 64, stride=2)),
+    ("5x5_s2x3_groups", conv_case(2, [13, 11], [5, 5], 16, 32, padding=2, stride=[2, 3], groups=2)),
+    ("3d_depth_s2", conv_case(2, [5, 6, 6], [3, 3, 3], 16, 16, padding=1, stride=[2, 1, 1])),
+])
+def test_conv_quarter_strided_and_3d(gpu_ctx, name, kw):
+    """8-bit operands in the strided backward pass (sub-filters transposed per
+    tap, there is no MN-major operand form for them) and in 3-D layers."""
+    p = capi.ConvParams.make(input_type=capi.QUARTER, **kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(zlib.crc32(name.encode()) % 1000 + 23)
+    g = p.groups
+    xv = r.integers(-2, 3, (p.batch, g * p.in_chans_per_group, *kw["field"])).astype(np.float64)
+    wv = r.integers(-2, 3, (g, p.out_chans_per_group, p.in_chans_per_group, *kw["kernel"])).astype(np.float64)
+    dyv = r.integers(-2, 3, (p.batch, g * p.out_chans_per_group, *p.output_field())).astype(np.float64)
+    got = T.gpu_conv_fwd(p, oracle.e4m3_encode(xv), oracle.e4m3_encode(wv))
+    assert_exact(got, oracle.conv_fwd(spec, xv, wv), f"quarter fwd {name}")
+    got = T.gpu_conv_bwd(p, oracle.e4m3_encode(dyv), oracle.e4m3_encode(wv))
+    assert_exact(got, oracle.conv_bwd(spec, dyv, wv), f"quarter bwd {name}")
+    opt = capi.ConvOptions.make(scale_in=-2, scale_weights=1)
+    got = T.gpu_conv_bwd(p, oracle.e4m3_encode(dyv), oracle.e4m3_encode(wv), opt=opt)
+    assert_exact(got, oracle.conv_bwd(spec, dyv, wv) * 0.5, f"quarter bwd {name} scaled")
+
+
+def test_conv_bwd_kernel_dilation_sharing_a_factor_with_the_stride(gpu_ctx):
+    """dilation 2 / stride 2, 4 / 2, 2 / 4, 6 / 4: the taps that reach one
+    phase are stride / gcd apart and some phases see no tap at all."""
+    for i, (dil, stride, k) in enumerate(((2, 2, 3), (4, 2, 3), (2, 4, 4), (6, 4, 3), ([2, 3], [4, 3], 3))):
+        dmax = max(dil) if isinstance(dil, list) else dil
+        kw = conv_case(2, [19, 17], [k, k], 16, 24, padding=dmax, stride=stride, k_dilation=dil)
+        p = capi.ConvParams.make(**kw)
+        spec = T.spec_from_params(p)
+        r = T.rng(700 + i)
+        _, w, dy = conv_data(p, kw, r, exact=True)
+        assert_exact(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), f"bwd dil {dil} stride {stride}")
+
+
 # BASELINE configurations at full size -------------------------------------------------
 
 def test_config2_conv3x3_fwd(gpu_ctx):

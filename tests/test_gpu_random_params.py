@@ -10,8 +10,6 @@ below 2048, exact in half).  Free-standing input dilation, which the path does
 not implement, is not drawn; a drawn combination that is not a valid
 convolution (empty output) is redrawn.
 """
-import math
-
 import numpy as np
 import pytest
 
@@ -73,17 +71,13 @@ def data(kw, p, r):
 
 def check_all_passes(seed, kw, p):
     spec = T.spec_from_params(p)
-    nd = len(kw["field"])
     r = T.rng(seed)
     x, w, dy = data(kw, p, r)
     what = f"seed {seed}: {kw}"
     got = T.gpu_conv_fwd(p, x, w)
     assert np.array_equal(got.astype(np.float64), oracle.conv_fwd(spec, x, w).reshape(got.shape)), "fwd " + what
-    # the depth dimension of a 3-D field is gathered, whatever its transforms
-    inner = range(1, 3) if nd == 3 else range(nd)
-    if all(kw["stride"][d] == 1 or math.gcd(kw["k_dilation"][d], kw["stride"][d]) == 1 for d in inner):
-        got = T.gpu_conv_bwd(p, dy, w)
-        assert np.array_equal(got.astype(np.float64), oracle.conv_bwd(spec, dy, w).reshape(got.shape)), "bwd " + what
+    got = T.gpu_conv_bwd(p, dy, w)
+    assert np.array_equal(got.astype(np.float64), oracle.conv_bwd(spec, dy, w).reshape(got.shape)), "bwd " + what
     if all(s <= 8 for s in kw["stride"]):
         _, dw32 = T.gpu_conv_wu(p, x, dy)
         assert np.array_equal(dw32.astype(np.float64), oracle.conv_wu(spec, x, dy)[0].reshape(dw32.shape)), "wu " + what
