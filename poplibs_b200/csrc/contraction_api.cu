@@ -1,6 +1,8 @@
 // C ABI entry points of the contraction path: matMul, convolution forward and
 // backward-data.  Each maps its poplin-level description onto one or more
 // launches of the implicit-GEMM kernel (igemm_sm100.cuh).
+#include <cuda_fp16.h>
+
 #include <algorithm>
 #include <cmath>
 #include <vector>
@@ -348,6 +350,15 @@ __global__ void gatherTapsKernel(const uint4 *__restrict__ src, uint4 *__restric
     const size_t tap = size_t(flip_h ? KH - 1 - th : th) * KW + size_t(flip_w ? KW - 1 - tw : tw);
     dst[i] = src[(size_t(g) * KH * KW + tap) * inner_vecs + v];
   }
+}
+
+// out[pixel][c] = bias[c]: what a convolution with a fused bias leaves where
+// nothing is accumulated (output padding).
+template <typename T>
+__global__ void fillBiasKernel(T *out, const float *__restrict__ bias, size_t total, size_t chans) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x)
+    out[i] = T(bias[i % chans]);
 }
 
 // One dimension of the backward pass of a strided convolution, for the input
@@ -777,15 +788,22 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
   if (p->in_chans_per_group == 0)
     return fail(PLB_ERR_UNSUPPORTED, "zero input channels are not implemented on this path yet");
   if (s.zero_fill_out || s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) {
-    // padded output positions (and everything, if nothing is computed) are zero
-    PLB_CUDA(cudaMemsetAsync(d_out, 0,
-                             size_t(p->batch) * s.OH * s.OW * p->groups * p->out_chans_per_group *
-                                 dtypeBytes(p->output_type),
-                             ctx->stream));
+    // padded output positions (and everything, if nothing is computed) hold
+    // zero, or the bias alone
+    const size_t chans = size_t(p->groups) * p->out_chans_per_group;
+    const size_t total = size_t(p->batch) * s.OH * s.OW * chans;
+    if (d_bias) {
+      const int grid = int(std::min<size_t>((total + 255) / 256, size_t(ctx->sm_count) * 16));
+      if (p->output_type == PLB_FLOAT)
+        fillBiasKernel<float><<<grid, 256, 0, ctx->stream>>>(static_cast<float *>(d_out), d_bias, total, chans);
+      else
+        fillBiasKernel<__half><<<grid, 256, 0, ctx->stream>>>(static_cast<__half *>(d_out), d_bias, total, chans);
+      PLB_CUDA(cudaGetLastError());
+      ctx->launches++;
+    } else {
+      PLB_CUDA(cudaMemsetAsync(d_out, 0, total * dtypeBytes(p->output_type), ctx->stream));
+    }
     if (s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) return PLB_OK;
-    if (s.zero_fill_out && d_bias)
-      return fail(PLB_ERR_UNSUPPORTED,
-                  "a fused bias with output padding is not implemented: use plb_add_bias");
   }
   if (!channelsFitTma(*p, p->in_chans_per_group) && !transpose_and_flip_weights) {
     // few input channels (a stem): space-to-depth path, where it applies

@@ -607,6 +607,32 @@ def test_conv_bwd_kernel_dilation_sharing_a_factor_with_the_stride(gpu_ctx):
         assert_exact(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), f"bwd dil {dil} stride {stride}")
 
 
+def test_matmul_operands_beyond_4_gib(gpu_ctx):
+    """Byte offsets past 2^32 in the left operand (69632 x 32768 half times
+    32768 x 64) and element offsets past 2^31 in the output (69632 x 64 times
+    64 x 32768, half out), checked on sampled rows including the last ones."""
+    import torch
+    free, _ = torch.cuda.mem_get_info()
+    if free < 12 << 30:
+        pytest.skip("needs 12 GiB of free device memory")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    pm1 = lambda *shape: (torch.randint(0, 2, shape, generator=g, device="cuda", dtype=torch.int8) * 2 - 1).half()  # noqa: E731
+    m = 69632
+    rows = torch.as_tensor([0, 1, 127, 128, 32767, 65535, 65536, 65537, m - 129, m - 128, m - 2, m - 1], device="cuda")
+    for k, n, out_type, dtype in ((32768, 64, capi.FLOAT, torch.float32), (64, 32768, capi.HALF, torch.float16)):
+        a, b = pm1(m, k), pm1(k, n)
+        out = torch.empty((m, n), device="cuda", dtype=dtype)
+        desc = capi.MatmulDesc.make(m, k, n, output_type=out_type)
+        torch.cuda.synchronize()
+        gpu_ctx.matmul(desc, a, b, None, out)
+        gpu_ctx.synchronize()
+        torch.cuda.synchronize()
+        expect = a[rows].cpu().numpy().astype(np.float64) @ b.cpu().numpy().astype(np.float64)
+        assert_exact(out[rows].cpu().numpy(), expect, f"matmul {m}x{k}x{n} sampled rows")
+        del a, b, out
+        torch.cuda.empty_cache()
+
+
 # BASELINE configurations at full size -------------------------------------------------
 
 def test_config2_conv3x3_fwd(gpu_ctx):
