@@ -721,8 +721,11 @@ int plb_conv_plan(const plb_conv_params *p_in, const plb_conv_options *opt, int3
   if (!p_in || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
   if (p_in->num_field_dims == 3) return conv3dPlan(*p_in, opt, pass, plan);
   // a flipped input runs as the ordinary convolution of the reversed tensor
-  plb_conv_params unflipped;
+  plb_conv_params unflipped, undilated;
   const plb_conv_params *p = unflippedInputParams(*p_in, &unflipped) ? &unflipped : p_in;
+  DilatedField df;
+  // a dilated input runs as the ordinary convolution of the zero-stuffed tensor
+  if (undilatedInputParams(*p, &undilated, &df)) p = &undilated;
   ConvShape s;
   if (int rc = igemmConvShape(*p, &s)) return rc;
   *plan = plb_plan{};
@@ -779,6 +782,20 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
                              p->in_flip[two ? 1 : 0] != 0))
         return rc;
       return plb_convolution(ctx, &q, opt, xf, d_weights, d_bias, d_out, transpose_and_flip_weights);
+    }
+  }
+  {
+    // a dilated input: write the zero-stuffed tensor once (scratch slot 12)
+    plb_conv_params q;
+    DilatedField df;
+    if (undilatedInputParams(*p, &q, &df)) {
+      const std::string err = validate(*p);
+      if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+      const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->input_type);
+      void *xd = nullptr;
+      if (int rc = scratch(ctx, 12, size_t(p->batch) * df.Hd * df.Wd * px + 256, &xd)) return rc;
+      if (int rc = dilateField(ctx, d_in, xd, p->batch, df, px, false)) return rc;
+      return plb_convolution(ctx, &q, opt, xd, d_weights, d_bias, d_out, transpose_and_flip_weights);
     }
   }
   ConvShape s;
@@ -906,6 +923,21 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
       if (int rc = plb_conv_bwd(ctx, &q, opt, d_out_grads, d_weights, gf)) return rc;
       return flipField(ctx, gf, d_in_grads, p->batch, H, W, px, two && p->in_flip[0],
                        p->in_flip[two ? 1 : 0] != 0);
+    }
+  }
+  {
+    // a dilated input: the gradient of the zero-stuffed tensor (scratch slot 12),
+    // of which the lattice elements are the gradient of the input
+    plb_conv_params q;
+    DilatedField df;
+    if (undilatedInputParams(*p, &q, &df)) {
+      const std::string err = validate(*p);
+      if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+      const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->output_type);
+      void *gd = nullptr;
+      if (int rc = scratch(ctx, 12, size_t(p->batch) * df.Hd * df.Wd * px + 256, &gd)) return rc;
+      if (int rc = plb_conv_bwd(ctx, &q, opt, d_out_grads, d_weights, gd)) return rc;
+      return dilateField(ctx, gd, d_in_grads, p->batch, df, px, true);
     }
   }
   ConvShape s;

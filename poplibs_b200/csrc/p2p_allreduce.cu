@@ -84,6 +84,9 @@ __global__ void __launch_bounds__(kP2pThreads)
 p2pAllReduceKernel(const P2pArgs a) {
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
+  // launched with programmatic stream serialization: the kernel that produced
+  // this rank's gradient must have completed before the flag says so
+  pdl_wait();
   __syncthreads();
   uint32_t *my_pad = a.signal_pads[a.rank];
   if (blockIdx.x == 0) {
@@ -191,7 +194,17 @@ extern "C" int plb_allreduce_f32_p2p(plb_context *ctx, int32_t rank, int32_t wor
   // among the first scheduled) exchanges the flags, the others wait for it
   const size_t want = (a.count4 + kP2pThreads - 1) / kP2pThreads;
   const unsigned blocks = unsigned(std::max<size_t>(1, std::min<size_t>(want, size_t(ctx->sm_count) * 2)));
-  p2pAllReduceKernel<<<blocks, kP2pThreads, 0, ctx->stream>>>(a);
+  // the launch overlaps the tail of the kernel that writes this rank's gradient
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kP2pThreads);
+  cfg.stream = ctx->stream;
+  cfg.attrs = pdl;
+  cfg.numAttrs = 1;
+  PLB_CUDA(cudaLaunchKernelEx(&cfg, p2pAllReduceKernel, a));
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
   return PLB_OK;

@@ -416,6 +416,97 @@ int flipField(plb_context *ctx, const void *src, void *dst, size_t n_images, uin
   return PLB_OK;
 }
 
+// ---- input dilation as data ---------------------------------------------------
+// dst = dilate(truncate(src)): [n][Hd][Wd] with the truncated field's elements
+// dH / dW apart and zeros between them; or (adjoint) the gradient of that
+// operation: dst[n][h][w] = src[n][(h - tH)*dH][(w - tW)*dW] inside the
+// truncated range, zero outside.
+template <typename V>
+__device__ inline V dilateZero() {
+  return V(0);
+}
+template <>
+__device__ inline uint4 dilateZero<uint4>() {
+  return make_uint4(0, 0, 0, 0);
+}
+
+template <typename V>
+__global__ void dilateFieldKernel(const V *__restrict__ src, V *__restrict__ dst, size_t n_images,
+                                  DilatedField s, uint32_t vecs, int adjoint) {
+  const uint32_t OH = adjoint ? s.H : s.Hd, OW = adjoint ? s.W : s.Wd;
+  const size_t total = n_images * OH * OW * vecs;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const uint32_t v = uint32_t(i % vecs);
+    size_t r = i / vecs;
+    const uint32_t w = uint32_t(r % OW);
+    r /= OW;
+    const uint32_t h = uint32_t(r % OH);
+    const size_t n = r / OH;
+    V val = dilateZero<V>();
+    if (adjoint) {
+      if (h >= s.tH && h < s.tH + s.TH && w >= s.tW && w < s.tW + s.TW)
+        val = src[((n * s.Hd + size_t(h - s.tH) * s.dH) * s.Wd + size_t(w - s.tW) * s.dW) * vecs + v];
+    } else if (h % s.dH == 0 && w % s.dW == 0) {
+      val = src[((n * s.H + s.tH + h / s.dH) * s.W + s.tW + w / s.dW) * vecs + v];
+    }
+    dst[i] = val;
+  }
+}
+
+bool undilatedInputParams(const plb_conv_params &p, plb_conv_params *q, DilatedField *f) {
+  *q = p;
+  if (p.num_field_dims < 1 || p.num_field_dims > 2) return false;
+  bool any = false;
+  uint32_t size[2] = {1, 1}, trunc_lo[2] = {0, 0}, kept[2] = {1, 1}, dil[2] = {1, 1}, dilated[2] = {1, 1};
+  for (unsigned d = 0; d != p.num_field_dims; ++d) {
+    const unsigned slot = p.num_field_dims == 2 ? d : 1;
+    const uint32_t cut = p.in_trunc_lo[d] + p.in_trunc_hi[d];
+    size[slot] = p.field[d];
+    if (p.in_dilation[d] == 0 || cut > p.field[d]) return false;  // invalid: reported by validate()
+    if (p.in_dilation[d] != 1) any = true;
+    trunc_lo[slot] = p.in_trunc_lo[d];
+    kept[slot] = p.field[d] - cut;
+    dil[slot] = p.in_dilation[d];
+    dilated[slot] = kept[slot] == 0 ? 0 : 1 + (kept[slot] - 1) * dil[slot];
+  }
+  if (!any) return false;
+  for (unsigned d = 0; d != p.num_field_dims; ++d) {
+    const unsigned slot = p.num_field_dims == 2 ? d : 1;
+    q->field[d] = dilated[slot];
+    q->in_trunc_lo[d] = q->in_trunc_hi[d] = 0;
+    q->in_dilation[d] = 1;
+  }
+  *f = DilatedField{size[0], size[1], trunc_lo[0], trunc_lo[1], kept[0], kept[1], dil[0], dil[1],
+                    dilated[0], dilated[1]};
+  return true;
+}
+
+int dilateField(plb_context *ctx, const void *src, void *dst, size_t n_images, const DilatedField &f,
+                size_t pixel_bytes, bool adjoint) {
+  size_t vb = 16;
+  while (pixel_bytes % vb) vb >>= 1;
+  const uint32_t vecs = uint32_t(pixel_bytes / vb);
+  const size_t total = n_images * (adjoint ? size_t(f.H) * f.W : size_t(f.Hd) * f.Wd) * vecs;
+  if (total == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(ctx->sm_count) * 16));
+#define PLB_DILATE(V)                                                                        \
+  dilateFieldKernel<V><<<grid, 256, 0, ctx->stream>>>(static_cast<const V *>(src),           \
+                                                      static_cast<V *>(dst), n_images, f, vecs, \
+                                                      adjoint ? 1 : 0)
+  switch (vb) {
+    case 16: PLB_DILATE(uint4); break;
+    case 8: PLB_DILATE(uint64_t); break;
+    case 4: PLB_DILATE(uint32_t); break;
+    case 2: PLB_DILATE(uint16_t); break;
+    default: PLB_DILATE(uint8_t); break;
+  }
+#undef PLB_DILATE
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
 int launchScaleRows(plb_context *ctx, void *out, const void *c, float beta, bool out_f32,
                     uint32_t rows, uint32_t cols, long long ldo, long long ldc) {
   if (rows == 0 || cols == 0) return PLB_OK;

@@ -27,7 +27,7 @@ struct plb_context {
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
   // grow-only scratch buffers: [0] operand rearrangement / partial sums,
   // [1..] staging for the host-buffer entry points
-  static constexpr int kScratchSlots = 12;
+  static constexpr int kScratchSlots = 13;
   void *scratch[kScratchSlots] = {};
   size_t scratch_bytes[kScratchSlots] = {};
 };
@@ -72,6 +72,23 @@ bool unflippedInputParams(const plb_conv_params &p, plb_conv_params *q);
 // Spatial flip of an [n][H][W][pixel] tensor (runtime.cu).
 int flipField(plb_context *ctx, const void *src, void *dst, size_t n_images, uint32_t H, uint32_t W,
               size_t pixel_bytes, bool flip_h, bool flip_w);
+
+// Input dilation of the reference's input transform, as data: the convolution of
+// a dilated input equals the ordinary convolution of the zero-stuffed tensor
+// dilate(truncate(x)).  A fallback (the inserted zeros are multiplied); the
+// backward pass of a strided layer does not come this way (plb_conv_bwd takes
+// it in forward terms).  [n][H][W] field (H = 1 for 1-D), tH/tW lower truncation,
+// TH/TW kept extent, dH/dW dilation, Hd/Wd dilated extent.
+struct DilatedField {
+  uint32_t H, W, tH, tW, TH, TW, dH, dW, Hd, Wd;
+};
+// Returns true and fills `q` (field = dilated extent, no truncation, dilation 1)
+// and `f` if `p` (1-D or 2-D) dilates its input.
+bool undilatedInputParams(const plb_conv_params &p, plb_conv_params *q, DilatedField *f);
+// dst = dilate(truncate(src)) ([n][Hd][Wd]); adjoint: dst ([n][H][W]) = the
+// elements of src ([n][Hd][Wd]) on the lattice, zero in the truncated margins.
+int dilateField(plb_context *ctx, const void *src, void *dst, size_t n_images, const DilatedField &f,
+                size_t pixel_bytes, bool adjoint);
 
 // ---- 3-D fields (conv3d.cu): depth folded into the channels of a 2-D problem ----
 int conv3dFwd(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,

@@ -305,6 +305,11 @@ int plb_conv_wu_plan(const plb_conv_params *p_in, const plb_conv_options *opt, p
   // flipped kernels are computed as ordinary kernels of the truncated extent
   plb_conv_params q;
   unflippedInputParams(*p_in, &q);
+  {
+    plb_conv_params undilated;
+    DilatedField df;
+    if (undilatedInputParams(q, &undilated, &df)) q = undilated;
+  }
   for (unsigned d = 0; d != q.num_field_dims && d < PLB_MAX_FIELD_DIMS; ++d) {
     q.kernel[d] -= std::min(q.kernel[d], q.k_trunc_lo[d] + q.k_trunc_hi[d]);
     q.k_trunc_lo[d] = q.k_trunc_hi[d] = 0;
@@ -348,6 +353,20 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
                              p->in_flip[two ? 1 : 0] != 0))
         return rc;
       return plb_conv_wu(ctx, &q, opt, xf, d_out_grads, d_weight_grads, d_weight_grads_f32);
+    }
+  }
+  {
+    // a dilated input: write the zero-stuffed tensor once (scratch slot 12)
+    plb_conv_params q;
+    DilatedField df;
+    if (undilatedInputParams(*p, &q, &df)) {
+      const std::string err = validate(*p);
+      if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+      const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->input_type);
+      void *xd = nullptr;
+      if (int rc = scratch(ctx, 12, size_t(p->batch) * df.Hd * df.Wd * px + 256, &xd)) return rc;
+      if (int rc = dilateField(ctx, d_acts, xd, p->batch, df, px, false)) return rc;
+      return plb_conv_wu(ctx, &q, opt, xd, d_out_grads, d_weight_grads, d_weight_grads_f32);
     }
   }
   {

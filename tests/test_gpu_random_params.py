@@ -2,13 +2,13 @@
 
 The role of the reference's random-parameter runs
 (tools/single_conv_layer_random.py:22-50, tests/poplin/CMakeLists.txt:1040-1065):
-every transform of ConvParams that the CUDA path implements is drawn at
-random -- input truncation padding and flip, kernel truncation, dilation,
-padding and flip, stride, output truncation and padding, groups, 1-D and 2-D fields --
-and the result must match the oracle bit for bit on +-1 data (all sums stay
-below 2048, exact in half).  Free-standing input dilation, which the path does
-not implement, is not drawn; a drawn combination that is not a valid
-convolution (empty output) is redrawn.
+every transform of ConvParams is drawn at random -- input truncation, padding
+and flip, kernel truncation, dilation, padding and flip, stride, output
+truncation and padding, groups, 1-D, 2-D and 3-D fields, and (in runs of its
+own: it costs a zero-stuffed copy of the input, or is part of the depth gather
+of a 3-D field) input dilation -- and the result must match the oracle bit for
+bit on +-1 data (all sums stay below 2048, exact in half).  A drawn combination
+that is not a valid convolution (empty output) is redrawn.
 """
 import numpy as np
 import pytest
@@ -20,8 +20,8 @@ from poplibs_b200 import capi
 pytestmark = pytest.mark.gpu
 
 
-def draw(seed, dims=None):
-    r = np.random.default_rng(1000 + seed + (50000 if dims else 0))
+def draw(seed, dims=None, dilate_input=False):
+    r = np.random.default_rng(1000 + seed + (50000 if dims else 0) + (90000 if dilate_input else 0))
     for _ in range(200):
         nd = dims or int(r.integers(1, 3))
         vec = lambda lo, hi: [int(v) for v in r.integers(lo, hi + 1, nd)]  # noqa: E731
@@ -36,6 +36,8 @@ def draw(seed, dims=None):
             out_trunc_hi=vec(0, 2), out_pad_lo=vec(0, 2), out_pad_hi=vec(0, 2))
         if nd == 3:
             kw["in_dilation"] = [int(r.integers(1, 3)), 1, 1]
+        elif dilate_input:
+            kw["in_dilation"] = vec(1, 3)
         # keep the draw simple half of the time: most layers use few transforms
         if r.random() < 0.5:
             for name in ("in_flip", "in_trunc_lo", "in_trunc_hi", "k_trunc_lo", "k_trunc_hi", "k_pad_lo", "k_pad_hi",
@@ -92,4 +94,10 @@ def test_random_conv_params(gpu_ctx, seed):
 @pytest.mark.parametrize("seed", range(40))
 def test_random_conv_params_3d(gpu_ctx, seed):
     kw, p = draw(seed, dims=3)
+    check_all_passes(seed, kw, p)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_conv_params_dilated_input(gpu_ctx, seed):
+    kw, p = draw(seed, dilate_input=True)
     check_all_passes(seed, kw, p)
