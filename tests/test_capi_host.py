@@ -193,9 +193,10 @@ def test_3d_layers_plan_as_2d_layers_with_depth_folded_into_channels():
                                stride=[2, 1, 1])
     for pass_id in (capi.PASS_TRAINING_FWD, capi.PASS_TRAINING_BWD, capi.PASS_TRAINING_WU):
         assert capi.conv_plan(odd, pass_id).flops == 2 * odd.macs()
-    # inner-dimension limits are those of the 2-D path
-    with pytest.raises(capi.PlbError):
-        capi.conv_plan(capi.ConvParams.make(1, [4, 6, 6], [1, 3, 3], 16, 16, in_dilation=[1, 2, 1]))
+    # input dilation in an inner dimension runs on the zero-stuffed input (2-D path's fallback)
+    inner = capi.ConvParams.make(1, [4, 6, 6], [1, 3, 3], 16, 16, in_dilation=[1, 2, 1])
+    stuffed = capi.ConvParams.make(4, [11, 6], [3, 3], 16, 16)
+    assert capi.conv_plan(inner).tiles == capi.conv_plan(stuffed).tiles
 
 
 def test_option_and_type_errors():
