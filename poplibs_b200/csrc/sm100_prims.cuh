@@ -287,6 +287,46 @@ __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t adesc, uint64_
 }
 
 // ---- programmatic dependent launch -------------------------------------------
+// The same fp16 instruction with a collector hint for the A operand.  Consecutive
+// instructions of one thread that read the same A tile (same descriptor, same
+// shape) can keep it in the tensor core's collector buffer instead of fetching
+// it from shared memory again: the first says fill, the following ones use,
+// the last one lastuse.  kHint: 1 = fill, 2 = use, 3 = lastuse.
+template <int kHint>
+__device__ __forceinline__ void umma_ss_f16_collect_a(uint32_t tmem_d, uint64_t adesc,
+                                                      uint64_t bdesc, uint32_t idesc,
+                                                      uint32_t accumulate) {
+  static_assert(kHint >= 1 && kHint <= 3, "collector hint");
+  if constexpr (kHint == 1) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16.collector::a::fill [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if constexpr (kHint == 2) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16.collector::a::use [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16.collector::a::lastuse [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
 // A kernel launched with the programmatic-stream-serialization attribute may
 // start while its predecessor in the stream is still running.  It must not
 // touch global memory the predecessor reads or writes before pdl_wait(), which

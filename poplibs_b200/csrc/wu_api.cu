@@ -1,5 +1,6 @@
 // Weight-update pass: planning and launch of the weight-gradient kernel.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -113,6 +114,11 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
   // rows' accumulators in TMEM at once and box_w * box_n a multiple of 8; taken
   // when it costs at most 1/8 more pixel tiles than the best box.
   a->strip_mode = 0;
+  {
+    // measurement switch: fetch the outGrad tile for every instruction
+    const char *e = std::getenv("PLB_DISABLE_COLLECTOR");
+    a->reuse_a = (e && e[0] == '1') ? 0 : 1;
+  }
   const int halo = (s.KH - 1) * s.dilH;
   if (s.KH > 1 && s.strH == 1 && s.KH * a->ci_blk <= 512 && (plan_flags & PLB_PLAN_NO_HALO) == 0) {
     long sbest = -1;

@@ -59,6 +59,9 @@ struct WuArgs {
   int strip_mode;
   int strip_rows;       // pixels of one strip: box_w * box_n * (box_h + halo)
   int halo_step_bytes;  // operand offset from one filter row to the next
+  // The instructions of one 16-pixel step all read the same outGrad tile: keep
+  // it in the tensor core's collector buffer between them (0 = fetch it each time).
+  int reuse_a;
   float *partial;  // [ksplit][taps][co_total][ci_total]
   int *status;
   long long *trace;  // optional timeline of CTA 0 (builds with -DPLB_TRACE only)
@@ -241,6 +244,8 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
       const uint64_t b_step16 = uint64_t(merge * tap_bytes) >> 4;
       const uint64_t a_desc0 = make_smem_desc(smem_base, kWuBlockBytes, 1024);
       const uint64_t b_desc0 = make_smem_desc(smem_base + a_bytes, uint32_t(b_block_bytes), 1024);
+      // at least two instructions per step, all of the same shape
+      const bool reuse_a = args.reuse_a != 0 && ntaps % merge == 0 && ntaps / merge >= 2;
       int stage = 0;
       uint32_t phase = 0;
       [[maybe_unused]] int trace_slot = 0;
@@ -266,6 +271,19 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
           uint32_t d_col = tmem_base;
           const uint32_t accumulate = (it | k) != 0 ? 1u : 0u;
           int t = 0;
+          if (reuse_a) {
+            // same A tile and shape for all of them: fill, use ..., lastuse
+            umma_ss_f16_collect_a<1>(d_col, a_desc, b_desc, idesc_full, accumulate);
+            for (t = merge; t + 2 * merge <= ntaps; t += merge) {
+              d_col += d_step;
+              b_desc += b_step16;
+              umma_ss_f16_collect_a<2>(d_col, a_desc, b_desc, idesc_full, accumulate);
+            }
+            d_col += d_step;
+            b_desc += b_step16;
+            umma_ss_f16_collect_a<3>(d_col, a_desc, b_desc, idesc_full, accumulate);
+            continue;
+          }
           for (; t + merge <= ntaps; t += merge) {
             umma_ss<false>(d_col, a_desc, b_desc, idesc_full, accumulate);
             d_col += d_step;
