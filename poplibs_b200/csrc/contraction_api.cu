@@ -603,6 +603,8 @@ int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a, c
   if (d.groups == 0 || d.m == 0 || d.n == 0) return PLB_OK;
   if (d.beta != 0.f && d_c == nullptr)
     return fail(PLB_ERR_INVALID_PARAMS, "beta != 0 needs a C matrix");
+  if (d_d == nullptr || (d.k != 0 && (d_a == nullptr || d_b == nullptr)))
+    return fail(PLB_ERR_INVALID_PARAMS, "null device pointer for a matrix that has elements");
   const Ld ld = leadingDims(d);
   const size_t es = dtypeBytes(d.input_type), os = dtypeBytes(d.output_type);
   if (d.k == 0) {
@@ -765,6 +767,13 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
                     int transpose_and_flip_weights) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  {
+    size_t n_in, n_w, n_out;
+    convElementCounts(*p, &n_in, &n_w, &n_out);
+    if (n_in == 0 || n_w == 0) n_in = n_w = 0;  // nothing is read: the output is zero (or the bias)
+    if (int rc = checkConvRequest(*p, false, d_in, n_out ? n_in : 0, d_weights, n_out ? n_w : 0, d_out, n_out))
+      return rc;
+  }
   if (p->num_field_dims == 3)
     return conv3dFwd(ctx, *p, opt, d_in, d_weights, d_bias, d_out, transpose_and_flip_weights);
   {
@@ -908,6 +917,14 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
                  const void *d_out_grads, const void *d_weights, void *d_in_grads) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  {
+    size_t n_in, n_w, n_out;
+    convElementCounts(*p, &n_in, &n_w, &n_out);
+    if (n_out == 0 || n_w == 0) n_out = n_w = 0;  // nothing is read: the gradient is zero
+    if (int rc = checkConvRequest(*p, false, d_out_grads, n_in ? n_out : 0, d_weights, n_in ? n_w : 0,
+                                  d_in_grads, n_in))
+      return rc;
+  }
   if (p->num_field_dims == 3) return conv3dBwd(ctx, *p, opt, d_out_grads, d_weights, d_in_grads);
   {
     // a flipped input: the gradient of the reversed input, reversed back

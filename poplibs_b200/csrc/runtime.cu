@@ -1,5 +1,6 @@
 // Context, memory and error plumbing of the C ABI, TMA tensor-map encoding and
 // the small data-movement kernels (layout changes, casts, scaled add).
+#include "conv_geometry.h"
 #include "runtime.h"
 
 #include <cuda_fp16.h>
@@ -413,6 +414,39 @@ int flipField(plb_context *ctx, const void *src, void *dst, size_t n_images, uin
                                                  uint32_t(pixel_bytes), flip_h ? 1 : 0, flip_w ? 1 : 0);
   PLB_CUDA(cudaGetLastError());
   ctx->launches++;
+  return PLB_OK;
+}
+
+void convElementCounts(const plb_conv_params &p, size_t *in, size_t *weights, size_t *out) {
+  size_t in_px = 1, taps = 1, out_px = 1;
+  for (unsigned d = 0; d != p.num_field_dims && d < PLB_MAX_FIELD_DIMS; ++d) {
+    in_px *= p.field[d];
+    taps *= p.kernel[d];
+    const long o = outputSize(p, d);
+    out_px *= o > 0 ? size_t(o) : 0;
+  }
+  *in = size_t(p.batch) * in_px * p.groups * p.in_chans_per_group;
+  *weights = size_t(p.groups) * taps * p.in_chans_per_group * p.out_chans_per_group;
+  *out = size_t(p.batch) * out_px * p.groups * p.out_chans_per_group;
+}
+
+int checkConvRequest(const plb_conv_params &p, bool wu, const void *first, size_t first_elems,
+                     const void *second, size_t second_elems, const void *result,
+                     size_t result_elems) {
+  const std::string err = validate(p);
+  if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+  if (wu && p.input_type != PLB_HALF)
+    // the reference never runs the weight update in quarter either
+    // (tools/single_conv_layer.cpp:725-733)
+    return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half input only");
+  if (p.input_type != PLB_HALF && p.input_type != PLB_QUARTER)
+    return fail(PLB_ERR_UNSUPPORTED, "convolution input type must be half or quarter");
+  if (p.output_type != PLB_HALF && p.output_type != PLB_FLOAT)
+    return fail(PLB_ERR_INVALID_PARAMS, "convolution output type must be half or float");
+  if (p.input_type == PLB_QUARTER && p.output_type != PLB_HALF)
+    return fail(PLB_ERR_INVALID_PARAMS, "Output type must be half when input type is quarter");
+  if ((first_elems && !first) || (second_elems && !second) || (result_elems && !result))
+    return fail(PLB_ERR_INVALID_PARAMS, "null device pointer for a tensor that has elements");
   return PLB_OK;
 }
 

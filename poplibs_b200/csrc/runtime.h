@@ -73,6 +73,19 @@ bool unflippedInputParams(const plb_conv_params &p, plb_conv_params *q);
 int flipField(plb_context *ctx, const void *src, void *dst, size_t n_images, uint32_t H, uint32_t W,
               size_t pixel_bytes, bool flip_h, bool flip_w);
 
+// First check of every convolution entry point, before any pre-pass is
+// launched: the reference's parameter validation, the element types this path
+// implements (wu: the weight update takes half only) and that no tensor with
+// elements is passed as a null pointer.  `in` / `weights` / `out` follow the
+// forward naming; pass the tensors of the pass in that order
+// (backward: out grads, weights, in grads; weight update: acts, out grads, any
+// of the two gradient outputs).
+int checkConvRequest(const plb_conv_params &p, bool wu, const void *in_like, size_t in_elems,
+                     const void *second, size_t second_elems, const void *result,
+                     size_t result_elems);
+// Element counts of the activations, weights and output of `p` (any rank).
+void convElementCounts(const plb_conv_params &p, size_t *in, size_t *weights, size_t *out);
+
 // Input dilation of the reference's input transform, as data: the convolution of
 // a dilated input equals the ordinary convolution of the zero-stuffed tensor
 // dilate(truncate(x)).  A fallback (the inserted zeros are multiplied); the

@@ -342,6 +342,14 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
                 float *d_weight_grads_f32) {
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  {
+    size_t n_in, n_w, n_out;
+    convElementCounts(*p, &n_in, &n_w, &n_out);
+    if (n_in == 0 || n_out == 0) n_in = n_out = 0;  // nothing is read: the gradient is zero
+    const void *result = d_weight_grads ? d_weight_grads : static_cast<const void *>(d_weight_grads_f32);
+    if (int rc = checkConvRequest(*p, true, d_acts, n_w ? n_in : 0, d_out_grads, n_w ? n_out : 0, result, n_w))
+      return rc;
+  }
   if (p->num_field_dims == 3)
     return conv3dWu(ctx, *p, opt, d_acts, d_out_grads, d_weight_grads, d_weight_grads_f32);
   {
@@ -558,6 +566,7 @@ extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const p
                                           const void *d_out_grads, void *d_weight_grads,
                                           float *d_weight_grads_f32) {
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  if (int rc = checkConvRequest(*p, true, nullptr, 0, nullptr, 0, nullptr, 0)) return rc;
   PLB_CUDA(cudaSetDevice(device));
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   WuShape s;
@@ -571,6 +580,13 @@ extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const p
                 "weight gradient of " + std::to_string(w_elems * sizeof(float)) +
                     " bytes per group exceeds the " + std::to_string(kStaticScratchBytes) +
                     "-byte static scratch of plb_conv_wu_static_scratch; use plb_conv_wu");
+  {
+    size_t n_in, n_w, n_out;
+    convElementCounts(*p, &n_in, &n_w, &n_out);
+    if (n_in == 0 || n_out == 0) n_in = n_out = 0;
+    const void *result = d_weight_grads ? d_weight_grads : static_cast<const void *>(d_weight_grads_f32);
+    if (int rc = checkConvRequest(*p, true, d_acts, n_in, d_out_grads, n_out, result, n_w)) return rc;
+  }
   StaticScratch scratch;
   if (int rc = staticScratchFor(device, &scratch)) return rc;
   const size_t es = 2;

@@ -730,10 +730,26 @@ def test_scaled_add_and_cast(gpu_ctx):
 
 
 def test_unsupported_requests_fail_loudly(gpu_ctx):
-    p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, in_dilation=2)
+    # an element type the path does not implement: refused before anything is launched
+    p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, input_type=capi.FLOAT, output_type=capi.FLOAT)
     with pytest.raises(capi.PlbError) as e:
         gpu_ctx.conv_fwd(p, 0, 0, 0)
     assert e.value.code == 3
+    # null pointers for tensors that have elements: refused, whatever pre-pass the parameters need
+    for kw in (dict(), dict(in_dilation=2), dict(in_flip=1)):
+        p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, **kw)
+        with pytest.raises(capi.PlbError) as e:
+            gpu_ctx.conv_fwd(p, 0, 0, 0)
+        assert e.value.code == 1 and "null device pointer" in e.value.message
+        with pytest.raises(capi.PlbError):
+            gpu_ctx.conv_bwd(p, 0, 0, 0)
+        with pytest.raises(capi.PlbError):
+            gpu_ctx.conv_wu(p, 0, 0, 0, 0)
+    p3 = capi.ConvParams.make(1, [4, 8, 8], [3, 3, 3], 64, 64)
+    with pytest.raises(capi.PlbError):
+        gpu_ctx.conv_fwd(p3, 0, 0, 0)
+    with pytest.raises(capi.PlbError):
+        gpu_ctx.matmul(capi.MatmulDesc.make(64, 64, 64), 0, 0, None, 0)
     p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, stride=0)
     with pytest.raises(capi.PlbError) as e:
         gpu_ctx.conv_fwd(p, 0, 0, 0)
