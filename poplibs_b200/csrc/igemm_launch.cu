@@ -204,6 +204,8 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
   // Worth it when every CTA pair gets several tile pairs and a tile's K loop is
   // long: the two SMs advance in lockstep per tile, which costs more than the
   // halved weight traffic saves on short tiles and on grids of a few tiles.
+  // With 256-column tiles the weight tile is two thirds of a stage's bytes and
+  // half the K length already pays (1x1 stride-2 layer 256 -> 512: 71 -> 67 us).
   const int k_elems_stage = kStageKBytes / elem;
   const long k_steps_per_tile =
       long(p.taps_h) * p.taps_w * ((p.k_per_tap + k_elems_stage - 1) / k_elems_stage);
@@ -212,7 +214,8 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
                     (!p.b_mn || bn >= 128) &&
                     ((p.plan_flags & PLB_PLAN_FORCE_CTA_PAIR) != 0 || forcePairFromEnv()
                          ? best_tiles >= 2
-                         : (k_steps_per_tile >= 8 && best_tiles * n_tiles >= 2L * sms_for_pair));
+                         : (k_steps_per_tile >= (bn >= 256 ? 4 : 8) &&
+                            best_tiles * n_tiles >= 2L * sms_for_pair));
   plan->cta_pair = pair ? 1 : 0;
   auto grid_for = [&](long m_tiles) {
     const int sms = sm_count > 0 ? sm_count : 148;

@@ -140,9 +140,12 @@ def test_planner_rules_for_pairs_halo_tiles_and_padding():
     assert c4.box_w * c4.box_n % 8 == 0 and c4.stages >= 3
     bwd = capi.conv_plan(capi.ConvParams.make(256, [28, 28], [3, 3], 128, 128, padding=1), capi.PASS_TRAINING_BWD)
     assert bwd.b_mn_major == 1 and bwd.cta_pair == 1
-    # short K loops (4 steps) do not pair: the lockstep costs more than it saves
+    # a short K loop (4 steps) pairs only under 256-column tiles, where the weight tile is
+    # most of a stage; with narrower tiles the lockstep costs more than it saves
     c3b = capi.conv_plan(capi.ConvParams.make(256, [56, 56], [1, 1], 256, 512, stride=2))
-    assert (c3b.tile_n, c3b.cta_pair, c3b.halo_rows) == (256, 0, 0)
+    assert (c3b.tile_n, c3b.cta_pair, c3b.halo_rows) == (256, 1, 0)
+    short128 = capi.conv_plan(capi.ConvParams.make(256, [28, 28], [1, 1], 256, 128))
+    assert (short128.tile_n, short128.cta_pair) == (128, 0)
     # a grid of a few tiles takes narrow tiles and no pairs
     c1 = capi.matmul_plan(capi.MatmulDesc.make(512, 1024, 1024))
     assert (c1.tile_n, c1.tiles, c1.grid, c1.cta_pair) == (64, 64, 64, 0)

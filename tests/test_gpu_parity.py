@@ -389,6 +389,18 @@ def test_matmul_cta_pair_exact(gpu_ctx, force_cta_pair, m, k, n, tb):
     assert_exact(got, oracle.gemm(a, b, transpose_b=tb), f"pair matmul {m}x{k}x{n} tb={tb}")
 
 
+def test_matmul_short_k_pairs_under_wide_tiles(gpu_ctx):
+    """4 K steps, 256-column tiles, many tiles: the planner pairs CTAs by itself."""
+    m, k, n = 4096, 256, 4096
+    assert capi.matmul_plan(capi.MatmulDesc.make(m, k, n)).cta_pair == 1
+    r = T.rng(77)
+    a, b = T.binary_half(r, (m, k)), T.binary_half(r, (k, n))
+    got = T.gpu_matmul(a, b)
+    rows = np.array([0, 1, 127, 128, 255, 256, 2047, 2048, m - 257, m - 256, m - 1])
+    assert_exact(got[rows], oracle.gemm(a[rows], b), "short-K pair matmul, sampled rows")
+    assert_exact(got[:, :8].astype(np.float64), a.astype(np.float64) @ b[:, :8].astype(np.float64), "first columns")
+
+
 def test_matmul_cta_pair_quarter(gpu_ctx, force_cta_pair):
     r = T.rng(5)
     av = r.integers(-3, 4, (384, 256)).astype(np.float64)
