@@ -108,6 +108,13 @@ PLB_API int plb_memset(plb_context *ctx, void *d_dst, int value, size_t bytes);
 /* (include/poplin/MatMul.hpp:110-420, lib/poplin/MatMul.cpp:368-404,        */
 /*  782-856; tools/general_matrix_multiply.cpp:355-370)                      */
 /* ------------------------------------------------------------------------ */
+/* Bit layout of a QUARTER element (poplar::QuarterMetadata::Format,
+ * lib/poplin/codelets/convCastSupport.hpp:8-31).  The tensor core decodes the
+ * OCP encodings: PLB_F143 = E4M3 (bias 7, largest finite 448), PLB_F152 = E5M2
+ * (bias 15, infinities and NaNs as in binary16).  Graphcore's F143 / F152 use
+ * a bias one higher: the C++ layer folds that factor 1/2 into the scale. */
+typedef enum plb_quarter_format { PLB_F143 = 0, PLB_F152 = 1 } plb_quarter_format;
+
 typedef struct plb_matmul_desc {
   uint32_t groups, m, k, n;
   int32_t input_type;   /* plb_dtype: PLB_HALF or PLB_QUARTER              */
@@ -122,6 +129,8 @@ typedef struct plb_matmul_desc {
   int32_t scale_a, scale_b; /* QUARTER metadata exponents: value = stored*2^scale
                                (poplar::QuarterMetadata), range [-32, 31]  */
   int64_t lda, ldb, ldc;/* row strides in elements; 0 = densely packed     */
+  int32_t format_a, format_b; /* plb_quarter_format of QUARTER operands
+                                 (poplar::QuarterMetadata::Format)          */
 } plb_matmul_desc;
 
 /* d_c may be NULL when beta == 0; d_c may alias d_d.  A, B, C, D are
@@ -195,7 +204,9 @@ typedef struct plb_conv_options {
   int32_t plan_flags;    /* PLB_PLAN_* bits                                   */
   int32_t scale_in;      /* QUARTER metadata exponents of the activations and  */
   int32_t scale_weights; /* the weights: value = stored * 2^scale              */
-  int32_t reserved[3];
+  int32_t format_in;      /* plb_quarter_format of the activations (or, in the   */
+  int32_t format_weights; /* backward pass, the output gradients) and the weights */
+  int32_t reserved;
 } plb_conv_options;
 
 /* plb_conv_options.plan_flags */

@@ -354,6 +354,26 @@ def _e4m3_encode_np(x: np.ndarray) -> np.ndarray:
     return (sign | code.astype(np.uint8)).astype(np.uint8)
 
 
+def e5m2_encode(x) -> np.ndarray:
+    """RNE quantisation of doubles to E5M2 bytes (bias 15; the upper byte of the
+    binary16 encoding): round to binary16 first, then drop eight mantissa bits
+    with ties to even; values beyond the largest finite code (57344) saturate."""
+    x = np.asarray(x, dtype=np.float64)
+    h = np.clip(x, -57344.0, 57344.0).astype(np.float16).view(np.uint16).astype(np.uint32)
+    lower, upper = h & 0xFF, h >> 8
+    round_up = (lower > 0x80) | ((lower == 0x80) & ((upper & 1) == 1))
+    code = upper + round_up.astype(np.uint32)
+    # rounding must not carry into the infinity code
+    code = np.where((code & 0x7F) >= 0x7C, (code & 0x80) | 0x7B, code)
+    code = np.where(np.isnan(x), 0x7E, code)
+    return code.astype(np.uint8)
+
+
+def e5m2_decode(bits) -> np.ndarray:
+    b = np.asarray(bits, dtype=np.uint8).astype(np.uint16) << 8
+    return b.view(np.float16).astype(np.float64)
+
+
 _E4M3_TABLE = None
 
 

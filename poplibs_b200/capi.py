@@ -9,6 +9,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libpoplibs_b200.so")
 
 HALF, FLOAT, QUARTER = 0, 1, 2
+F143, F152 = 0, 1   # plb_quarter_format
 PASS_NONE, PASS_NONE_MATMUL, PASS_INFERENCE_FWD, PASS_TRAINING_FWD, PASS_TRAINING_BWD, \
     PASS_TRAINING_WU, PASS_FC_INFERENCE_FWD, PASS_FC_TRAINING_FWD, PASS_FC_TRAINING_BWD, \
     PASS_FC_TRAINING_WU = range(10)
@@ -30,17 +31,20 @@ class MatmulDesc(C.Structure):
                 ("transpose_a", C.c_int32), ("transpose_b", C.c_int32),
                 ("alpha", C.c_float), ("beta", C.c_float),
                 ("scale_a", C.c_int32), ("scale_b", C.c_int32),
-                ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64)]
+                ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
+                ("format_a", C.c_int32), ("format_b", C.c_int32)]
 
     @staticmethod
     def make(m, k, n, groups=1, input_type=HALF, output_type=HALF, transpose_a=False,
-             transpose_b=False, alpha=1.0, beta=0.0, scale_a=0, scale_b=0, partials_type=FLOAT):
+             transpose_b=False, alpha=1.0, beta=0.0, scale_a=0, scale_b=0, partials_type=FLOAT,
+             format_a=0, format_b=0):
         d = MatmulDesc()
         d.groups, d.m, d.k, d.n = groups, m, k, n
         d.input_type, d.output_type, d.partials_type = input_type, output_type, partials_type
         d.transpose_a, d.transpose_b = int(transpose_a), int(transpose_b)
         d.alpha, d.beta = alpha, beta
         d.scale_a, d.scale_b = scale_a, scale_b
+        d.format_a, d.format_b = format_a, format_b
         return d
 
 
@@ -101,14 +105,15 @@ class ConvParams(C.Structure):
 class ConvOptions(C.Structure):
     _fields_ = [("pass_", C.c_int32), ("partials_type", C.c_int32), ("tile_n", C.c_int32),
                 ("split_k", C.c_int32), ("plan_flags", C.c_int32), ("scale_in", C.c_int32), ("scale_weights", C.c_int32),
-                ("reserved", C.c_int32 * 3)]
+                ("format_in", C.c_int32), ("format_weights", C.c_int32), ("reserved", C.c_int32)]
 
     @staticmethod
     def make(pass_=PASS_NONE, partials_type=FLOAT, tile_n=0, split_k=0, plan_flags=0, scale_in=0,
-             scale_weights=0):
+             scale_weights=0, format_in=0, format_weights=0):
         o = ConvOptions()
         o.pass_, o.partials_type, o.tile_n, o.split_k = pass_, partials_type, tile_n, split_k
         o.plan_flags, o.scale_in, o.scale_weights = plan_flags, scale_in, scale_weights
+        o.format_in, o.format_weights = format_in, format_weights
         return o
 
 

@@ -37,6 +37,8 @@ int checkMatmulDesc(const plb_matmul_desc &d) {
     return fail(PLB_ERR_INVALID_OPTION, "partialsType must be half or float");
   if (d.scale_a < -32 || d.scale_a > 31 || d.scale_b < -32 || d.scale_b > 31)
     return fail(PLB_ERR_INVALID_PARAMS, "quarter metadata scale must be in [-32, 31]");
+  if ((d.format_a != PLB_F143 && d.format_a != PLB_F152) || (d.format_b != PLB_F143 && d.format_b != PLB_F152))
+    return fail(PLB_ERR_INVALID_PARAMS, "quarter format must be PLB_F143 or PLB_F152");
   return PLB_OK;
 }
 
@@ -59,6 +61,8 @@ IgemmProblem gemmProblem(const plb_matmul_desc &d, const void *a, long long lda,
   IgemmProblem p;
   const size_t es = dtypeBytes(d.input_type);
   p.fp8 = d.input_type == PLB_QUARTER;
+  p.fmt_a = d.format_a;
+  p.fmt_b = d.format_b;
   p.b_mn = !b_is_nk;
   p.act = a;
   p.act_dims[0] = d.k;
@@ -204,6 +208,8 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
   IgemmProblem r;
   r.fp8 = p.input_type == PLB_QUARTER;
+  r.fmt_a = opt ? opt->format_in : 0;
+  r.fmt_b = opt ? opt->format_weights : 0;
   // the truncated input is a view: same strides, shifted base, smaller extents
   r.act = static_cast<const uint8_t *>(in) +
           ((size_t(s.tH) * s.W + s.tW) * ctot + size_t(g) * ci) * es;
@@ -279,6 +285,8 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
   IgemmProblem r;
   r.fp8 = p.input_type == PLB_QUARTER;
+  r.fmt_a = opt ? opt->format_in : 0;
+  r.fmt_b = opt ? opt->format_weights : 0;
   // computed part of the output gradients / used part of the input gradients
   r.act = static_cast<const uint8_t *>(dy) +
           ((size_t(s.opH) * s.OW + s.opW) * cotot + size_t(g) * co) * es;
@@ -512,6 +520,8 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
       for (unsigned g = 0; g < p.groups; ++g) {
         IgemmProblem r;
         r.fp8 = fp8;
+        r.fmt_a = opt ? opt->format_in : 0;
+        r.fmt_b = opt ? opt->format_weights : 0;
         r.act = static_cast<const uint8_t *>(dy) +
                 ((size_t(s.opH) * s.OW + s.opW) * cotot + size_t(g) * co) * es;
         r.act_dims[0] = co;

@@ -411,6 +411,8 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.addend = p.beta != 0.f ? p.addend : nullptr;
   a.ld_addend = p.ld_addend;
   a.bias = p.bias;
+  a.idesc_formats = p.fp8 ? make_idesc(0, 0, uint32_t(p.fmt_a & 1), uint32_t(p.fmt_b & 1), false, false) & ~(1u << 4)
+                          : 0u;
   a.alpha = p.alpha;
   a.beta = p.beta;
   a.out_is_f32 = p.out_f32 ? 1 : 0;

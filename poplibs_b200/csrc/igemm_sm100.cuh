@@ -74,6 +74,7 @@ struct IgemmArgs {
   int flip_h, flip_w;  // tap (r, s) uses the weights stored at (R-1-r, ...) / (..., S-1-s)
   int group_m;    // tile rasterisation: M tiles per band
   int num_stages;  // pipeline depth (<= kIgemmMaxStages)
+  uint32_t idesc_formats;  // operand format bits of the instruction descriptor (8-bit operands: 1 = E5M2)
   // ---- epilogue ---------------------------------------------------------------
   void *out;
   long long ldc;  // elements between consecutive output pixels (along w)
@@ -447,7 +448,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     // ===================== MMA issuer =====================
     // (with a CTA pair only the CTA of rank 0 issues)
     if (leader && elect_one()) {
-      constexpr uint32_t idesc = make_idesc(k2Cta ? 2 * kTileM : kTileM, BN, 0, 0, false, kBMn);
+      const uint32_t idesc =
+          make_idesc(k2Cta ? 2 * kTileM : kTileM, BN, 0, 0, false, kBMn) | args.idesc_formats;
       // completion of the MMAs issued so far -> barrier (in both CTAs of a pair)
       auto commit = [&](uint32_t bar) {
         if constexpr (k2Cta)

@@ -154,15 +154,19 @@ void checkActsShape(const Tensor &t, std::size_t batch, std::size_t chans,
   }
 }
 
-// Exponent to add for a QUARTER operand: its metadata scale, minus one for the
-// F143 format, whose values are half of what the same bits mean in the E4M3
-// encoding the tensor core decodes.
+// Exponent to add for a QUARTER operand: its metadata scale, minus one because
+// the F143 / F152 formats (exponent bias 8 / 16) hold half of what the same bits
+// mean in the E4M3 / E5M2 encodings (bias 7 / 15) the tensor core decodes.
 int quarterExponent(const Tensor &t) {
   if (t.elementType() != poplar::QUARTER) return 0;
   const poplar::QuarterMetadata md = t.hasMetadata() ? t.getMetadata() : poplar::QuarterMetadata();
-  if (md.getFormat() != poplar::QuarterMetadata::Format::F143)
-    throw poplibs_error("quarter tensors must use the F143 format on this target");
   return int(md.getScale()) - 1;
+}
+
+// plb_quarter_format of a QUARTER operand (PLB_F143 for anything else).
+int quarterFormat(const Tensor &t) {
+  if (t.elementType() != poplar::QUARTER || !t.hasMetadata()) return PLB_F143;
+  return t.getMetadata().getFormat() == poplar::QuarterMetadata::Format::F152 ? PLB_F152 : PLB_F143;
 }
 
 void validateTypes(const ConvParams &p) {
@@ -294,6 +298,8 @@ void convolutionWithOutput(Graph &graph, const Tensor &in, const Tensor &weights
     prog.add([=](plb_context *ctx) mutable {
       opt.scale_in = quarterExponent(inA);
       opt.scale_weights = quarterExponent(wFwd);
+      opt.format_in = quarterFormat(inA);
+      opt.format_weights = quarterFormat(wFwd);
       logging::poplin::trace("convolution (backward of a strided layer) " + name);
       poplar::detail::check(plb_conv_bwd(ctx, &fwd, &opt, inA.devicePointer(), wFwd.devicePointer(),
                                          outA.devicePointer()));
@@ -305,6 +311,8 @@ void convolutionWithOutput(Graph &graph, const Tensor &in, const Tensor &weights
   prog.add([=](plb_context *ctx) mutable {
     opt.scale_in = quarterExponent(inA);
     opt.scale_weights = quarterExponent(wA);
+    opt.format_in = quarterFormat(inA);
+    opt.format_weights = quarterFormat(wA);
     if (flat.in_chans_per_group == 0 || std::any_of(flat.field, flat.field + flat.num_field_dims,
                                                     [](uint32_t f) { return f == 0; })) {
       // nothing is accumulated: the result is zero

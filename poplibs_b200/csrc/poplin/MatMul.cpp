@@ -84,9 +84,8 @@ MatrixLayout layoutOf(const Tensor &t) {
 int quarterExponent(const Tensor &t) {
   if (t.elementType() != poplar::QUARTER) return 0;
   const poplar::QuarterMetadata md = t.hasMetadata() ? t.getMetadata() : poplar::QuarterMetadata();
-  if (md.getFormat() != poplar::QuarterMetadata::Format::F143)
-    throw poplibs_error("quarter tensors must use the F143 format on this target");
-  return int(md.getScale()) - 1;  // F143 values are half the E4M3 reading of the same bits
+  // F143 / F152 values are half the E4M3 / E5M2 reading of the same bits
+  return int(md.getScale()) - 1;
 }
 
 // Dense row-major copy of a grouped matrix whose row length is padded to a
@@ -158,6 +157,14 @@ void matMulImpl(Graph &graph, const Tensor &A_, const Tensor &B_, const Tensor &
   prog.add([=](plb_context *ctx) mutable {
     d.scale_a = quarterExponent(A);
     d.scale_b = quarterExponent(B);
+    auto format = [](const Tensor &t) {
+      return t.elementType() == poplar::QUARTER && t.hasMetadata() &&
+                     t.getMetadata().getFormat() == poplar::QuarterMetadata::Format::F152
+                 ? PLB_F152
+                 : PLB_F143;
+    };
+    d.format_a = format(A);
+    d.format_b = format(B);
     if (d.scale_a < -32) d.scale_a = -32;
     if (d.scale_b < -32) d.scale_b = -32;
     const void *c = d.beta != 0.f ? O.devicePointer() : nullptr;

@@ -118,7 +118,8 @@ int conv3dPlan(const plb_conv_params &p, const plb_conv_options *opt, int32_t pa
 
 // A fully resolved implicit-GEMM problem: one launch of the igemm kernel.
 struct IgemmProblem {
-  bool fp8 = false;      // E4M3 operands (else fp16)
+  bool fp8 = false;      // 8-bit operands (else fp16)
+  int fmt_a = 0, fmt_b = 0;  // plb_quarter_format of the activations / weights when fp8
   bool b_mn = false;     // right operand stored [tap][K][N], N contiguous
   // activations: 4-D tensor (C, W, H, N) with byte strides of W, H, N
   const void *act = nullptr;

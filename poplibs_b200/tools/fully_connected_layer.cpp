@@ -64,9 +64,9 @@ int main(int argc, char **argv) try {
   const bool reportPlan = args.get<unsigned>("report-plan", 0) != 0;
   const int scaleFwd = args.get<int>("fp8-scale-fwd", 0), scaleW = args.get<int>("fp8-scale-weights", 0),
             scaleBwd = args.get<int>("fp8-scale-bwd", 0);
-  for (const char *fmt : {"fp8-format-fwd", "fp8-format-weights", "fp8-format-bwd"})
-    if (args.str(fmt, "F143") != "F143")
-      throw poputil::poplibs_error("only the F143 quarter format is supported on this target");
+  const auto formatFwd = tool::quarterFormat(args.str("fp8-format-fwd", "F143"));
+  const auto formatW = tool::quarterFormat(args.str("fp8-format-weights", "F143"));
+  const auto formatBwd = tool::quarterFormat(args.str("fp8-format-bwd", "F143"));
   const unsigned seed = args.get<unsigned>("seed", 42);
   const bool integerData = args.has("integer-data") || inputType == QUARTER;
   const std::string dumpDir = args.str("dump-dir");
@@ -101,8 +101,8 @@ int main(int argc, char **argv) try {
   Tensor biases;
   if (bias) biases = graph.addVariable(outputType, {numGroups, outputSize}, "biases");
   if (inputType == QUARTER) {
-    graph.setQuarterMetadata(prevAct, QuarterMetadata(QuarterMetadata::Format::F143, (signed char)scaleFwd));
-    graph.setQuarterMetadata(weights, QuarterMetadata(QuarterMetadata::Format::F143, (signed char)scaleW));
+    graph.setQuarterMetadata(prevAct, QuarterMetadata(formatFwd, (signed char)scaleFwd));
+    graph.setQuarterMetadata(weights, QuarterMetadata(formatW, (signed char)scaleW));
   }
 
   Sequence fwdProg, bwdProg;
@@ -139,7 +139,7 @@ int main(int argc, char **argv) try {
                                                   {numGroups, outputSize, inputSize}, "zDeltas",
                                                   bwdOptions, &cache);
     if (inputType == QUARTER)
-      graph.setQuarterMetadata(zDeltas, QuarterMetadata(QuarterMetadata::Format::F143, (signed char)scaleBwd));
+      graph.setQuarterMetadata(zDeltas, QuarterMetadata(formatBwd, (signed char)scaleBwd));
   }
   if (doBwd) {
     const Tensor weightsTransposed = poplin::transposeGroupedMatrix(weights);
@@ -202,8 +202,8 @@ int main(int argc, char **argv) try {
     auto hW = tool::randomValues(numGroups * inputSize * outputSize, -3.0, 3.0, rng, integerData);
     auto hBias = tool::randomValues(numGroups * outputSize, -4.0, 4.0, rng, integerData);
     auto hDeltas = tool::randomValues(numGroups * batchSize * outputSize, -5.0, 5.0, rng, integerData);
-    const auto rAct = tool::toDevice(hAct, inputType, scaleFwd);
-    const auto rW = tool::toDevice(hW, inputType, scaleW);
+    const auto rAct = tool::toDevice(hAct, inputType, scaleFwd, formatFwd == QuarterMetadata::Format::F152);
+    const auto rW = tool::toDevice(hW, inputType, scaleW, formatW == QuarterMetadata::Format::F152);
     engine.writeTensor("prevAct", rAct.data(), rAct.data() + rAct.size());
     engine.writeTensor("weights", rW.data(), rW.data() + rW.size());
     tool::dump(dumpDir, "prevAct", hAct, actShape);
@@ -214,7 +214,7 @@ int main(int argc, char **argv) try {
       tool::dump(dumpDir, "biases", hBias, {numGroups, outputSize});
     }
     if (zDeltas.valid()) {
-      const auto rD = tool::toDevice(hDeltas, inputType, scaleBwd);
+      const auto rD = tool::toDevice(hDeltas, inputType, scaleBwd, formatBwd == QuarterMetadata::Format::F152);
       engine.writeTensor("zDeltas", rD.data(), rD.data() + rD.size());
       tool::dump(dumpDir, "zDeltas", hDeltas, outShape);
     }

@@ -43,9 +43,8 @@ int main(int argc, char **argv) try {
   const bool transposeA = args.str("left-matrix-op", "normal") == "transpose";
   const bool transposeB = args.str("right-matrix-op", "normal") == "transpose";
   const int scaleA = args.get<int>("fp8-scale-A", 0), scaleB = args.get<int>("fp8-scale-B", 0);
-  for (const char *fmt : {"fp8-format-A", "fp8-format-B"})
-    if (args.str(fmt, "F143") != "F143")
-      throw poputil::poplibs_error("only the F143 quarter format is supported on this target");
+  const auto formatA = tool::quarterFormat(args.str("fp8-format-A", "F143"));
+  const auto formatB = tool::quarterFormat(args.str("fp8-format-B", "F143"));
   std::string planConstraints = args.str("plan-constraints");
   const std::string planConstraintsFile = args.str("plan-constraints-file");
   if (!planConstraints.empty() && !planConstraintsFile.empty())
@@ -92,8 +91,8 @@ int main(int argc, char **argv) try {
                                                     {g, k, n}, "matB", mmOpt, &cache);
   if (transposeB) matB = matB.dimShufflePartial({1, 2}, {2, 1});
   if (inputType == QUARTER) {
-    graph.setQuarterMetadata(matA, QuarterMetadata(QuarterMetadata::Format::F143, (signed char)scaleA));
-    graph.setQuarterMetadata(matB, QuarterMetadata(QuarterMetadata::Format::F143, (signed char)scaleB));
+    graph.setQuarterMetadata(matA, QuarterMetadata(formatA, (signed char)scaleA));
+    graph.setQuarterMetadata(matB, QuarterMetadata(formatB, (signed char)scaleB));
   }
   const Tensor lhs = transposeA ? matA.dimShufflePartial({1, 2}, {2, 1}) : matA;
   const Tensor rhs = transposeB ? matB.dimShufflePartial({1, 2}, {2, 1}) : matB;
@@ -131,8 +130,8 @@ int main(int argc, char **argv) try {
     hostA = tool::randomValues(std::size_t(g) * rowsA * colsA, -4.0, 4.0, rng, integerData);
     hostB = tool::randomValues(std::size_t(g) * rowsB * colsB, -3.0, 3.0, rng, integerData);
     hostC = tool::randomValues(std::size_t(g) * m * n, -2.0, 2.0, rng, integerData);
-    const auto rawA = tool::toDevice(hostA, inputType, scaleA);
-    const auto rawB = tool::toDevice(hostB, inputType, scaleB);
+    const auto rawA = tool::toDevice(hostA, inputType, scaleA, formatA == QuarterMetadata::Format::F152);
+    const auto rawB = tool::toDevice(hostB, inputType, scaleB, formatB == QuarterMetadata::Format::F152);
     const auto rawC = tool::toDevice(hostC, outputType);
     engine.writeTensor("matA", rawA.data(), rawA.data() + rawA.size());
     engine.writeTensor("matB", rawB.data(), rawB.data() + rawB.size());

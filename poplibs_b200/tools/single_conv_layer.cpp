@@ -68,9 +68,9 @@ int main(int argc, char **argv) try {
   else if (inputType == QUARTER) outputType = HALF;
   const int scaleFwd = args.get<int>("fp8-scale-fwd", 1), scaleW = args.get<int>("fp8-scale-weights", 2),
             scaleBwd = args.get<int>("fp8-scale-bwd", 1);
-  for (const char *fmt : {"fp8-format-fwd", "fp8-format-weights", "fp8-format-bwd"})
-    if (args.str(fmt, "F143") != "F143")
-      throw poputil::poplibs_error("only the F143 quarter format is supported on this target");
+  const auto formatFwd = tool::quarterFormat(args.str("fp8-format-fwd", "F143"));
+  const auto formatW = tool::quarterFormat(args.str("fp8-format-weights", "F143"));
+  const auto formatBwd = tool::quarterFormat(args.str("fp8-format-bwd", "F143"));
   const std::string phase = args.str("single-phase", "all");
   if (phase != "fwd" && phase != "bwd" && phase != "wu" && phase != "all")
     throw std::runtime_error("--single-phase must be fwd, bwd, wu or all");
@@ -127,8 +127,8 @@ int main(int argc, char **argv) try {
   Tensor prevAct = poplin::createInput(graph, params, "prevAct", fwdOptions, &cache);
   Tensor weights = poplin::createWeights(graph, params, "weights", fwdOptions, &cache);
   if (inputType == QUARTER) {
-    graph.setQuarterMetadata(prevAct, QuarterMetadata(QuarterMetadata::Format::F143, (signed char)scaleFwd));
-    graph.setQuarterMetadata(weights, QuarterMetadata(QuarterMetadata::Format::F143, (signed char)scaleW));
+    graph.setQuarterMetadata(prevAct, QuarterMetadata(formatFwd, (signed char)scaleFwd));
+    graph.setQuarterMetadata(weights, QuarterMetadata(formatW, (signed char)scaleW));
   }
   Sequence fwdProg, bwdProg, wuProg;
   Tensor nextAct, biases;
@@ -151,7 +151,7 @@ int main(int argc, char **argv) try {
     // the output gradients are the backward convolution's input
     zDeltas = poplin::createInput(graph, bwdParams, "zDeltas", bwdOptions, &cache);
     if (inputType == QUARTER)
-      graph.setQuarterMetadata(zDeltas, QuarterMetadata(QuarterMetadata::Format::F143, (signed char)scaleBwd));
+      graph.setQuarterMetadata(zDeltas, QuarterMetadata(formatBwd, (signed char)scaleBwd));
   }
   if (doBwd) {
     Sequence once;
@@ -207,8 +207,8 @@ int main(int argc, char **argv) try {
     auto hW = tool::randomValues(product(wShape), -1.0, 1.0, rng, integerData);
     auto hBias = tool::randomValues(std::size_t(groups) * co, -2.0, 6.0, rng, integerData);
     auto hDeltas = tool::randomValues(product(outShape), -3.0, 3.0, rng, integerData);
-    const auto rAct = tool::toDevice(hAct, inputType, scaleFwd);
-    const auto rW = tool::toDevice(hW, inputType, scaleW);
+    const auto rAct = tool::toDevice(hAct, inputType, scaleFwd, formatFwd == QuarterMetadata::Format::F152);
+    const auto rW = tool::toDevice(hW, inputType, scaleW, formatW == QuarterMetadata::Format::F152);
     engine.writeTensor("prevAct", rAct.data(), rAct.data() + rAct.size());
     engine.writeTensor("weights", rW.data(), rW.data() + rW.size());
     tool::dump(dumpDir, "prevAct", hAct, inShape);
@@ -219,7 +219,7 @@ int main(int argc, char **argv) try {
       tool::dump(dumpDir, "biases", hBias, {std::size_t(groups) * co});
     }
     if (zDeltas.valid()) {
-      const auto rD = tool::toDevice(hDeltas, inputType, scaleBwd);
+      const auto rD = tool::toDevice(hDeltas, inputType, scaleBwd, formatBwd == QuarterMetadata::Format::F152);
       engine.writeTensor("zDeltas", rD.data(), rD.data() + rD.size());
       tool::dump(dumpDir, "zDeltas", hDeltas, outShape);
     }

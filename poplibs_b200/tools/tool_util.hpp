@@ -180,9 +180,26 @@ inline double f143Value(uint8_t b) {
   return sign ? -v : v;
 }
 
+// Graphcore F152 (1-5-2, bias 16): half of the E5M2 reading of the same bits,
+// and E5M2 is the upper byte of binary16.  Round to nearest even, saturating at
+// the largest finite code.
+inline uint8_t f152Bits(double x) {
+  const double y = x * 2.0;  // E5M2 reading of the stored bits
+  if (std::isnan(y)) return 0x7e;
+  const uint16_t h = halfBits(std::max(-57344.0, std::min(57344.0, y)));
+  const unsigned lower = h & 0xffu;
+  unsigned code = h >> 8;
+  if (lower > 0x80u || (lower == 0x80u && (code & 1u))) ++code;
+  if ((code & 0x7fu) >= 0x7cu) code = (code & 0x80u) | 0x7bu;
+  return uint8_t(code);
+}
+
+inline double f152Value(uint8_t b) { return 0.5 * halfValue(uint16_t(uint16_t(b) << 8)); }
+
 /// Converts `values` to the device type (for QUARTER: value = stored * 2^scale)
 /// and replaces them by exactly what the device will see.
-inline std::vector<uint8_t> toDevice(std::vector<double> &values, const poplar::Type &type, int scale = 0) {
+inline std::vector<uint8_t> toDevice(std::vector<double> &values, const poplar::Type &type, int scale = 0,
+                                     bool f152 = false) {
   std::vector<uint8_t> raw(values.size() * type.bytes());
   for (std::size_t i = 0; i < values.size(); ++i) {
     if (type == poplar::HALF) {
@@ -194,14 +211,22 @@ inline std::vector<uint8_t> toDevice(std::vector<double> &values, const poplar::
       std::memcpy(&raw[4 * i], &f, 4);
       values[i] = f;
     } else if (type == poplar::QUARTER) {
-      const uint8_t b = f143Bits(std::ldexp(values[i], -scale));
+      const double scaled = std::ldexp(values[i], -scale);
+      const uint8_t b = f152 ? f152Bits(scaled) : f143Bits(scaled);
       raw[i] = b;
-      values[i] = std::ldexp(f143Value(b), scale);
+      values[i] = std::ldexp(f152 ? f152Value(b) : f143Value(b), scale);
     } else {
       throw std::runtime_error("unsupported element type " + type.toString());
     }
   }
   return raw;
+}
+
+/// "F143" / "F152" (tools' --fp8-format options).
+inline poplar::QuarterMetadata::Format quarterFormat(const std::string &name) {
+  if (name == "F143") return poplar::QuarterMetadata::Format::F143;
+  if (name == "F152") return poplar::QuarterMetadata::Format::F152;
+  throw std::runtime_error("unknown quarter format " + name + " (F143 or F152)");
 }
 
 inline std::vector<double> fromDevice(const std::vector<uint8_t> &raw, const poplar::Type &type) {

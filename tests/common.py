@@ -89,7 +89,7 @@ def context() -> capi.Context:
 
 
 def gpu_matmul(a, b, c=None, *, transpose_a=False, transpose_b=False, alpha=1.0, beta=0.0,
-               out_dtype=np.float16, scale_a=0, scale_b=0, ctx=None):
+               out_dtype=np.float16, scale_a=0, scale_b=0, format_a=0, format_b=0, ctx=None):
     """a: [g][m][k] (or [g][k][m] if transpose_a); b: [g][k][n] (or [g][n][k])."""
     import torch
     ctx = ctx or context()
@@ -105,7 +105,8 @@ def gpu_matmul(a, b, c=None, *, transpose_a=False, transpose_b=False, alpha=1.0,
                                 input_type=capi.QUARTER if quarter else capi.HALF,
                                 output_type=capi.FLOAT if out_dtype == np.float32 else capi.HALF,
                                 transpose_a=transpose_a, transpose_b=transpose_b,
-                                alpha=alpha, beta=beta, scale_a=scale_a, scale_b=scale_b)
+                                alpha=alpha, beta=beta, scale_a=scale_a, scale_b=scale_b,
+                                format_a=format_a, format_b=format_b)
     da, db = to_dev(a), to_dev(b)
     dc = to_dev(c.astype(out_dtype)) if c is not None else None
     dd = empty_dev((g, m, n), out_dtype)

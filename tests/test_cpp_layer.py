@@ -79,6 +79,11 @@ def test_general_matrix_multiply_tool_against_oracle(tmp_path):
         (["--m", "5", "--k", "0", "--n", "4", "--beta", "1", "--integer-data"], 0.0),
         (["--m", "256", "--k", "512", "--n", "256", "--input-type", "quarter", "--fp8-scale-A=-3", "--fp8-scale-B=-2",
           "--beta", "0"], 0.0),
+        # the 1-5-2 format (the reference tool's default), alone and mixed with 1-4-3
+        (["--m", "256", "--k", "512", "--n", "256", "--input-type", "quarter", "--fp8-format-A=F152",
+          "--fp8-format-B=F152", "--fp8-scale-A=-3", "--fp8-scale-B=-2", "--beta", "0"], 0.0),
+        (["--m", "200", "--k", "256", "--n", "136", "--input-type", "quarter", "--fp8-format-A=F143",
+          "--fp8-format-B=F152", "--fp8-scale-A=1", "--fp8-scale-B=0", "--beta", "0"], 0.0),
     ]
     for i, (flags, tol) in enumerate(cases):
         d = tmp_path / f"gemm{i}"

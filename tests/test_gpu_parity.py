@@ -409,6 +409,48 @@ def test_matmul_cta_pair_quarter(gpu_ctx, force_cta_pair):
     assert_exact(got, oracle.gemm(av, bv), "pair quarter matmul")
 
 
+@pytest.mark.parametrize("fa,fb", [(capi.F152, capi.F152), (capi.F143, capi.F152), (capi.F152, capi.F143)])
+def test_matmul_quarter_f152(gpu_ctx, fa, fb):
+    """The 1-5-2 quarter format, alone and mixed with 1-4-3, with scales."""
+    r = T.rng(40 + fa * 2 + fb)
+    m, k, n = 384, 64, 320
+    # integers exactly representable in either format; sums stay exact in half
+    av = r.integers(-4, 5, (m, k)).astype(np.float64)
+    bv = r.integers(-4, 5, (k, n)).astype(np.float64)
+    enc = {capi.F143: oracle.e4m3_encode, capi.F152: oracle.e5m2_encode}
+    dec = {capi.F143: oracle.e4m3_decode, capi.F152: oracle.e5m2_decode}
+    a8, b8 = enc[fa](av), enc[fb](bv)
+    assert (dec[fa](a8) == av).all() and (dec[fb](b8) == bv).all()
+    got = T.gpu_matmul(a8, b8, format_a=fa, format_b=fb)
+    assert_exact(got, oracle.gemm(av, bv), f"quarter matmul formats {fa},{fb}")
+    got = T.gpu_matmul(a8, b8, format_a=fa, format_b=fb, scale_a=-2, scale_b=1)
+    assert_exact(got, oracle.gemm(av, bv) * 0.5, f"quarter matmul formats {fa},{fb} scaled")
+    # fractions the two formats share, and magnitudes only E5M2 reaches (E4M3 stops at 448)
+    if fa == capi.F152 and fb == capi.F152:
+        vals = r.choice(np.array([1024.0, -2048.0, 4096.0, 0.0, 57344.0, 0.3125, -1.75, 2.0 ** -14]), (128, 64))
+        eye = np.eye(64)
+        v8 = oracle.e5m2_encode(vals)
+        assert (oracle.e5m2_decode(v8) == vals).all()
+        got = T.gpu_matmul(v8, oracle.e5m2_encode(eye), format_a=fa, format_b=fb)
+        assert_exact(got, vals, "E5M2 range")
+
+
+def test_conv_quarter_f152_fwd_bwd(gpu_ctx):
+    kw = conv_case(2, [9, 8], [3, 3], 16, 32, padding=1, stride=[2, 1])
+    p = capi.ConvParams.make(input_type=capi.QUARTER, **kw)
+    spec = T.spec_from_params(p)
+    r = T.rng(52)
+    xv = r.integers(-3, 4, (2, 16, 9, 8)).astype(np.float64)
+    wv = r.integers(-2, 3, (1, 32, 16, 3, 3)).astype(np.float64)
+    dyv = r.integers(-3, 4, (2, 32, *p.output_field())).astype(np.float64)
+    opt = capi.ConvOptions.make(format_in=capi.F152, format_weights=capi.F143, scale_in=1)
+    got = T.gpu_conv_fwd(p, oracle.e5m2_encode(xv), oracle.e4m3_encode(wv), opt=opt)
+    assert_exact(got, 2 * oracle.conv_fwd(spec, xv, wv), "quarter fwd, F152 activations")
+    opt = capi.ConvOptions.make(format_in=capi.F152, format_weights=capi.F152)
+    got = T.gpu_conv_bwd(p, oracle.e5m2_encode(dyv), oracle.e5m2_encode(wv), opt=opt)
+    assert_exact(got, oracle.conv_bwd(spec, dyv, wv), "quarter bwd (strided), F152 gradients and weights")
+
+
 def test_conv_bias_update(gpu_ctx):
     """biases += scale * sum over pixels of the output gradients (fp32 sums)."""
     import torch
