@@ -446,7 +446,7 @@ int usedTaps(plb_context *ctx, const plb_conv_params &p, const ConvShape &s, con
   if (s.KH <= 0 || s.KW <= 0) return PLB_OK;  // nothing is used; callers zero the result
   void *ws = nullptr;
   const size_t bytes = size_t(p.groups) * s.KH * s.KW * inner;
-  if (int rc = scratch(ctx, 6, bytes + 256, &ws)) return rc;
+  if (int rc = scratch(ctx, kSlotUsedTaps, bytes + 256, &ws)) return rc;
   const size_t vecs = bytes / 16;
   const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 8));
   gatherTapsKernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint4 *>(w),
@@ -496,7 +496,7 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
   // one buffer per phase: the launches of different phases are in flight together
   const size_t slot = (scratch_elems * es + 255) & ~size_t(255);
   const size_t phases = size_t(s.strH) * s.strW;
-  if (int rc = scratch(ctx, 0, slot * phases * (fp8 ? 2 : 1) + 256, &ws)) return rc;
+  if (int rc = scratch(ctx, kSlotOperands, slot * phases * (fp8 ? 2 : 1) + 256, &ws)) return rc;
   for (int a = 0; a < s.strH; ++a)
     for (int b = 0; b < s.strW; ++b) {
       const BwdPhase &A = ph[size_t(a)], &B = pw[size_t(b)];
@@ -641,7 +641,7 @@ int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a, c
   if (transpose_b_now) scratch_bytes += b_bytes;
   if (scratch_bytes) {
     void *ws = nullptr;
-    if (int rc = scratch(ctx, 0, scratch_bytes, &ws)) return rc;
+    if (int rc = scratch(ctx, kSlotOperands, scratch_bytes, &ws)) return rc;
     uint8_t *cursor = static_cast<uint8_t *>(ws);
     if (d.transpose_a) {
       if (ld.a != (long long)d.m)
@@ -692,12 +692,12 @@ int plb_matmul_host_async(plb_context *ctx, const plb_matmul_desc *desc, const v
   const size_t b_bytes = size_t(d.groups) * (d.transpose_b ? d.n : d.k) * ld.b * es;
   const size_t c_bytes = size_t(d.groups) * d.m * ld.c * os;
   void *da = nullptr, *db = nullptr, *dc = nullptr, *dd = nullptr;
-  if (int rc = scratch(ctx, 1, a_bytes + 16, &da)) return rc;
-  if (int rc = scratch(ctx, 2, b_bytes + 16, &db)) return rc;
-  if (int rc = scratch(ctx, 3, c_bytes + 16, &dd)) return rc;
+  if (int rc = scratch(ctx, kSlotHostIn, a_bytes + 16, &da)) return rc;
+  if (int rc = scratch(ctx, kSlotHostWeights, b_bytes + 16, &db)) return rc;
+  if (int rc = scratch(ctx, kSlotHostOut, c_bytes + 16, &dd)) return rc;
   if (d.beta != 0.f) {
     if (!h_c) return fail(PLB_ERR_INVALID_PARAMS, "beta != 0 needs a C matrix");
-    if (int rc = scratch(ctx, 4, c_bytes + 16, &dc)) return rc;
+    if (int rc = scratch(ctx, kSlotHostBias, c_bytes + 16, &dc)) return rc;
     if (int rc = plb_memcpy_h2d(ctx, dc, h_c, c_bytes)) return rc;
   }
   if (int rc = plb_memcpy_h2d(ctx, da, h_a, a_bytes)) return rc;
@@ -796,7 +796,7 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
       const uint32_t H = two ? p->field[0] : 1, W = p->field[two ? 1 : 0];
       const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->input_type);
       void *xf = nullptr;
-      if (int rc = scratch(ctx, 8, size_t(p->batch) * H * W * px + 256, &xf)) return rc;
+      if (int rc = scratch(ctx, kSlotFlipped, size_t(p->batch) * H * W * px + 256, &xf)) return rc;
       if (int rc = flipField(ctx, d_in, xf, p->batch, H, W, px, two && p->in_flip[0],
                              p->in_flip[two ? 1 : 0] != 0))
         return rc;
@@ -812,7 +812,7 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
       if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
       const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->input_type);
       void *xd = nullptr;
-      if (int rc = scratch(ctx, 12, size_t(p->batch) * df.Hd * df.Wd * px + 256, &xd)) return rc;
+      if (int rc = scratch(ctx, kSlotDilated, size_t(p->batch) * df.Hd * df.Wd * px + 256, &xd)) return rc;
       if (int rc = dilateField(ctx, d_in, xd, p->batch, df, px, false)) return rc;
       return plb_convolution(ctx, &q, opt, xd, d_weights, d_bias, d_out, transpose_and_flip_weights);
     }
@@ -855,7 +855,7 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
     const size_t x_b = align256(in_px * G * pc.cip * es), w_b = align256(G * taps * pc.cop * pc.cip * es),
                  o_b = align256(out_px * G * pc.cop * os), b_b = align256(G * pc.cop * sizeof(float));
     void *arena = nullptr;
-    if (int rc = scratch(ctx, 7, x_b + 2 * w_b + o_b + b_b, &arena)) return rc;
+    if (int rc = scratch(ctx, kSlotPaddedChans, x_b + 2 * w_b + o_b + b_b, &arena)) return rc;
     uint8_t *xp = static_cast<uint8_t *>(arena), *wp = xp + x_b, *wtmp = wp + w_b, *op = wtmp + w_b,
             *bp = op + o_b;
     if (int rc = resizeRows(ctx, d_in, xp, in_px * G, pc.ci * es, pc.cip * es)) return rc;
@@ -899,7 +899,7 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
     const size_t bytes = size_t(p->groups) * s.KH * s.KW * p->in_chans_per_group *
                          p->out_chans_per_group * es;
     void *ws = nullptr;
-    if (int rc = scratch(ctx, 0, bytes, &ws)) return rc;
+    if (int rc = scratch(ctx, kSlotOperands, bytes, &ws)) return rc;
     // stored [G][k][Ci][Co] -> [G][flipped k][Co][Ci]
     if (int rc = plb_weights_transpose_chans_flip_xy(ctx, uint32_t(es), p->groups,
                                                      p->in_chans_per_group, p->out_chans_per_group,
@@ -946,7 +946,7 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
       const uint32_t H = two ? p->field[0] : 1, W = p->field[two ? 1 : 0];
       const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->output_type);
       void *gf = nullptr;
-      if (int rc = scratch(ctx, 8, size_t(p->batch) * H * W * px + 256, &gf)) return rc;
+      if (int rc = scratch(ctx, kSlotFlipped, size_t(p->batch) * H * W * px + 256, &gf)) return rc;
       if (int rc = plb_conv_bwd(ctx, &q, opt, d_out_grads, d_weights, gf)) return rc;
       return flipField(ctx, gf, d_in_grads, p->batch, H, W, px, two && p->in_flip[0],
                        p->in_flip[two ? 1 : 0] != 0);
@@ -962,7 +962,7 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
       if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
       const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->output_type);
       void *gd = nullptr;
-      if (int rc = scratch(ctx, 12, size_t(p->batch) * df.Hd * df.Wd * px + 256, &gd)) return rc;
+      if (int rc = scratch(ctx, kSlotDilated, size_t(p->batch) * df.Hd * df.Wd * px + 256, &gd)) return rc;
       if (int rc = plb_conv_bwd(ctx, &q, opt, d_out_grads, d_weights, gd)) return rc;
       return dilateField(ctx, gd, d_in_grads, p->batch, df, px, true);
     }
@@ -994,7 +994,7 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
     const size_t dy_b = align256(out_px * G * pc.cop * es), w_b = align256(G * taps * pc.cop * pc.cip * es),
                  dx_b = align256(in_px * G * pc.cip * os);
     void *arena = nullptr;
-    if (int rc = scratch(ctx, 7, dy_b + 2 * w_b + dx_b, &arena)) return rc;
+    if (int rc = scratch(ctx, kSlotPaddedChans, dy_b + 2 * w_b + dx_b, &arena)) return rc;
     uint8_t *dyp = static_cast<uint8_t *>(arena), *wp = dyp + dy_b, *wtmp = wp + w_b, *dxp = wtmp + w_b;
     if (int rc = resizeRows(ctx, d_out_grads, dyp, out_px * G, pc.co * es, pc.cop * es)) return rc;
     if (int rc = padWeights(ctx, d_weights, wtmp, wp, G * taps, pc.co, pc.ci, pc.cop, pc.cip, es)) return rc;
@@ -1022,7 +1022,7 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
     const size_t bytes = size_t(p->groups) * s.KH * s.KW * p->in_chans_per_group *
                          p->out_chans_per_group * es;
     void *ws = nullptr;
-    if (int rc = scratch(ctx, 0, bytes, &ws)) return rc;
+    if (int rc = scratch(ctx, kSlotOperands, bytes, &ws)) return rc;
     if (int rc = plb_weights_transpose_chans_flip_xy(ctx, uint32_t(es), p->groups,
                                                      p->out_chans_per_group, p->in_chans_per_group,
                                                      uint64_t(s.KH) * s.KW, w_used, ws))
@@ -1065,11 +1065,11 @@ int plb_conv_fwd_host_async(plb_context *ctx, const plb_conv_params *p,
   const size_t out_bytes = size_t(p->batch) * out_px * p->groups * p->out_chans_per_group * os;
   const size_t bias_bytes = size_t(p->groups) * p->out_chans_per_group * sizeof(float);
   void *di = nullptr, *dw = nullptr, *dout = nullptr, *dbias = nullptr;
-  if (int rc = scratch(ctx, 1, in_bytes + 16, &di)) return rc;
-  if (int rc = scratch(ctx, 2, w_bytes + 16, &dw)) return rc;
-  if (int rc = scratch(ctx, 3, out_bytes + 16, &dout)) return rc;
+  if (int rc = scratch(ctx, kSlotHostIn, in_bytes + 16, &di)) return rc;
+  if (int rc = scratch(ctx, kSlotHostWeights, w_bytes + 16, &dw)) return rc;
+  if (int rc = scratch(ctx, kSlotHostOut, out_bytes + 16, &dout)) return rc;
   if (h_bias) {
-    if (int rc = scratch(ctx, 4, bias_bytes + 16, &dbias)) return rc;
+    if (int rc = scratch(ctx, kSlotHostBias, bias_bytes + 16, &dbias)) return rc;
     if (int rc = plb_memcpy_h2d(ctx, dbias, h_bias, bias_bytes)) return rc;
   }
   if (int rc = plb_memcpy_h2d(ctx, di, h_in, in_bytes)) return rc;

@@ -242,8 +242,8 @@ int conv3dFwd(plb_context *ctx, const plb_conv_params &p, const plb_conv_options
   if (p.batch == 0 || G == 0 || Co == 0 || f.OD == 0 || f.out_pixels == 0) return PLB_OK;
   if (Ci == 0) return fail(PLB_ERR_UNSUPPORTED, "zero input channels are not implemented on this path yet");
   void *xf = nullptr, *wf = nullptr;
-  if (int rc = scratch(ctx, 9, size_t(p.batch) * f.OD * f.in_pixels * G * f.KD * Ci * es + 256, &xf)) return rc;
-  if (int rc = scratch(ctx, 10, size_t(G) * f.KD * f.taps2 * Co * Ci * es + 256, &wf)) return rc;
+  if (int rc = scratch(ctx, kSlotDepthFold, size_t(p.batch) * f.OD * f.in_pixels * G * f.KD * Ci * es + 256, &xf)) return rc;
+  if (int rc = scratch(ctx, kSlotFoldedWeights, size_t(G) * f.KD * f.taps2 * Co * Ci * es + 256, &wf)) return rc;
   if (int rc = foldDepth(ctx, f, false, d_in, xf, p.batch, f.D, f.OD, f.in_pixels, G, Ci * es)) return rc;
   if (transpose_and_flip_weights) {
     // stored [g][kd][taps][Ci][Co], flipped in every dimension: undo the depth flip here
@@ -271,8 +271,8 @@ int conv3dBwd(plb_context *ctx, const plb_conv_params &p, const plb_conv_options
     return PLB_OK;
   }
   void *gf = nullptr, *wf = nullptr;
-  if (int rc = scratch(ctx, 9, size_t(p.batch) * f.D * f.out_pixels * G * f.KD * Co * es + 256, &gf)) return rc;
-  if (int rc = scratch(ctx, 10, size_t(G) * f.KD * f.taps2 * Co * Ci * es + 256, &wf)) return rc;
+  if (int rc = scratch(ctx, kSlotDepthFold, size_t(p.batch) * f.D * f.out_pixels * G * f.KD * Co * es + 256, &gf)) return rc;
+  if (int rc = scratch(ctx, kSlotFoldedWeights, size_t(G) * f.KD * f.taps2 * Co * Ci * es + 256, &wf)) return rc;
   if (int rc = foldDepth(ctx, f, true, d_out_grads, gf, p.batch, f.OD, f.D, f.out_pixels, G, Co * es)) return rc;
   if (int rc = foldWeights(ctx, f, uint32_t(es), G, Co, Ci, false, false, d_weights, wf)) return rc;
   plb_conv_params q = f.p2;
@@ -297,8 +297,8 @@ int conv3dWu(plb_context *ctx, const plb_conv_params &p, const plb_conv_options 
     return PLB_OK;
   }
   void *xf = nullptr, *ws = nullptr;
-  if (int rc = scratch(ctx, 9, size_t(p.batch) * f.OD * f.in_pixels * G * f.KD * Ci * es + 256, &xf)) return rc;
-  if (int rc = scratch(ctx, 11, 2 * w_elems * sizeof(float) + 512, &ws)) return rc;
+  if (int rc = scratch(ctx, kSlotDepthFold, size_t(p.batch) * f.OD * f.in_pixels * G * f.KD * Ci * es + 256, &xf)) return rc;
+  if (int rc = scratch(ctx, kSlotFoldedGrads, 2 * w_elems * sizeof(float) + 512, &ws)) return rc;
   float *folded = static_cast<float *>(ws);
   float *unfolded = d_weight_grads_f32 ? d_weight_grads_f32
                                        : folded + ((w_elems + 63) / 64) * 64;

@@ -854,7 +854,7 @@ int plb_conv_bias_update(plb_context *ctx, int32_t acts_dtype, const void *d_out
     slabs = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>(pixels, uint64_t(ctx->sm_count) * 16 / col_blocks)));
   }
   void *ws = nullptr;
-  if (int rc = scratch(ctx, 5, size_t(slabs) * chans * sizeof(float), &ws)) return rc;
+  if (int rc = scratch(ctx, kSlotBiasUpdate, size_t(slabs) * chans * sizeof(float), &ws)) return rc;
   float *partial = static_cast<float *>(ws);
   if (vector_ok) {
     if (acts_dtype == PLB_HALF)

@@ -12,6 +12,26 @@
 
 #include "poplibs_b200.h"
 
+// Grow-only scratch buffers of a context, by use.  Entry points call one
+// another (3-D -> 2-D -> flipped -> dilated -> padded channels ...), so every
+// pre-pass has a slot of its own.
+enum plb_scratch_slot {
+  kSlotOperands = 0,    // rearranged operands, split-K partial sums, gathered sub-filters
+  kSlotHostIn,          // staging of the host-buffer entry points
+  kSlotHostWeights,
+  kSlotHostOut,
+  kSlotHostBias,
+  kSlotBiasUpdate,      // column sums of the bias update
+  kSlotUsedTaps,        // taps of a truncated / flipped kernel
+  kSlotPaddedChans,     // zero-padded channel counts
+  kSlotFlipped,         // reversed input (input flip)
+  kSlotDepthFold,       // depth taps of a 3-D field gathered into the channels
+  kSlotFoldedWeights,
+  kSlotFoldedGrads,
+  kSlotDilated,         // zero-stuffed input (input dilation)
+  kSlotCount
+};
+
 struct plb_context {
   int device = 0;
   int sm_count = 0;
@@ -25,9 +45,8 @@ struct plb_context {
   uint64_t launches = 0;          // kernels launched through this context
   long long *trace = nullptr;     // device timeline buffer for builds with -DPLB_TRACE
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
-  // grow-only scratch buffers: [0] operand rearrangement / partial sums,
-  // [1..] staging for the host-buffer entry points
-  static constexpr int kScratchSlots = 13;
+  // grow-only scratch buffers, one per use (plb_scratch_slot)
+  static constexpr int kScratchSlots = kSlotCount;
   void *scratch[kScratchSlots] = {};
   size_t scratch_bytes[kScratchSlots] = {};
 };

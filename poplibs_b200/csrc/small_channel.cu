@@ -280,7 +280,7 @@ int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_c
     return PLB_OK;
   }
   void *ws = nullptr;
-  if (int rc = scratch(ctx, 0, plan.workspace_bytes + 256, &ws)) return rc;
+  if (int rc = scratch(ctx, kSlotOperands, plan.workspace_bytes + 256, &ws)) return rc;
   __half *x2 = static_cast<__half *>(ws);
   __half *w2 = x2 + ((x2_elems + 127) & ~size_t(127));
   {

@@ -362,7 +362,7 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
       const uint32_t H = two ? p->field[0] : 1, W = p->field[two ? 1 : 0];
       const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->input_type);
       void *xf = nullptr;
-      if (int rc = scratch(ctx, 8, size_t(p->batch) * H * W * px + 256, &xf)) return rc;
+      if (int rc = scratch(ctx, kSlotFlipped, size_t(p->batch) * H * W * px + 256, &xf)) return rc;
       if (int rc = flipField(ctx, d_acts, xf, p->batch, H, W, px, two && p->in_flip[0],
                              p->in_flip[two ? 1 : 0] != 0))
         return rc;
@@ -378,7 +378,7 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
       if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
       const size_t px = size_t(p->groups) * p->in_chans_per_group * dtypeBytes(p->input_type);
       void *xd = nullptr;
-      if (int rc = scratch(ctx, 12, size_t(p->batch) * df.Hd * df.Wd * px + 256, &xd)) return rc;
+      if (int rc = scratch(ctx, kSlotDilated, size_t(p->batch) * df.Hd * df.Wd * px + 256, &xd)) return rc;
       if (int rc = dilateField(ctx, d_acts, xd, p->batch, df, px, false)) return rc;
       return plb_conv_wu(ctx, &q, opt, xd, d_out_grads, d_weight_grads, d_weight_grads_f32);
     }
@@ -417,7 +417,7 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
       if (used == 0 || full == 0) return PLB_OK;
       void *tmp = nullptr;
       const size_t used16 = (used * es + 255) & ~size_t(255);
-      if (int rc = scratch(ctx, 6, used16 + used * sizeof(float) + 256, &tmp)) return rc;
+      if (int rc = scratch(ctx, kSlotUsedTaps, used16 + used * sizeof(float) + 256, &tmp)) return rc;
       void *t16 = tmp;
       float *t32 = reinterpret_cast<float *>(static_cast<uint8_t *>(tmp) + used16);
       if (int rc = plb_conv_wu(ctx, &q, opt, d_acts, d_out_grads, d_weight_grads ? t16 : nullptr,
@@ -466,7 +466,7 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
     const size_t wp_elems = G * size_t(taps) * cop * cip;
     const size_t w16_b = al(wp_elems * es2), w32_b = al(wp_elems * 4);
     void *arena = nullptr;
-    if (int rc = scratch(ctx, 7, x_b + dy_b + 2 * w16_b + 2 * w32_b, &arena)) return rc;
+    if (int rc = scratch(ctx, kSlotPaddedChans, x_b + dy_b + 2 * w16_b + 2 * w32_b, &arena)) return rc;
     uint8_t *xp = static_cast<uint8_t *>(arena), *dyp = xp + x_b, *w16 = dyp + dy_b, *t16 = w16 + w16_b,
             *w32 = t16 + w16_b, *t32 = w32 + w32_b;
     if (int rc = resizeRows(ctx, d_acts, xp, in_px * G, size_t(ci) * es2, cip * es2)) return rc;
@@ -494,7 +494,7 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
   a.status = ctx->d_status;
   a.trace = ctx->trace;
   void *ws = nullptr;
-  if (int rc = scratch(ctx, 0, size_t(a.ksplit) * w_elems * sizeof(float), &ws)) return rc;
+  if (int rc = scratch(ctx, kSlotOperands, size_t(a.ksplit) * w_elems * sizeof(float), &ws)) return rc;
   a.partial = static_cast<float *>(ws);
 
   static bool configured[64] = {};
