@@ -241,11 +241,18 @@ class Workload:
                 glob = dict(kw, batch=kw["batch"] * world)
                 self.allreduce = "none (no collective on this pass)"
                 peer = self.pass_ == "wu" and os.environ.get("PLB_BENCH_ALLREDUCE", "p2p") == "p2p"
+                # PLB_BENCH_OVERLAP=1: the all-reduce of step i runs on a stream of its own, behind
+                # step i + 1's kernels.  Off by default: the event between the kernels costs the
+                # programmatic launch overlap, and the measured step is not shorter
+                # (2 GPUs 57.1 vs 59.8 us, 8 GPUs 72.4 vs 68.8 us).
+                overlap = peer and os.environ.get("PLB_BENCH_OVERLAP", "0") == "1"
                 try:
-                    self.sharded = parallel.ShardedConv(ctx, glob, rank, world, peer_allreduce=peer)
+                    self.sharded = parallel.ShardedConv(ctx, glob, rank, world, peer_allreduce=peer,
+                                                        overlap_allreduce=overlap)
                     if self.pass_ == "wu":
-                        self.allreduce = ("library kernel over NVLink peer memory" if peer
-                                          else "nccl all_reduce + cast")
+                        self.allreduce = (("library kernel over NVLink peer memory"
+                                           + (", overlapped with the next step on a second stream" if overlap else ""))
+                                          if peer else "nccl all_reduce + cast")
                 except Exception as e:  # symmetric memory unavailable: the process group's all-reduce
                     self.sharded = parallel.ShardedConv(ctx, glob, rank, world)
                     self.allreduce = f"nccl all_reduce + cast (peer memory unavailable: {type(e).__name__})"
@@ -322,10 +329,29 @@ class Workload:
         dist.all_reduce(local)
         self.sharded.wu(d["x"], d["dy"], d["out"], d["out32"])
         self.ctx.synchronize()
+        self.sync_comm()
         torch.cuda.synchronize()
         diff = float((local - d["out32"]).abs().max().item())
         scale = float(local.abs().max().item())
         return {"max_abs_diff_vs_nccl": diff, "max_abs": scale}
+
+    def sync_comm(self):
+        """Waits for the communication stream of an overlapped all-reduce (and checks its status)."""
+        sharded = getattr(self, "sharded", None)
+        if sharded is not None and sharded.peer is not None:
+            sharded.peer.synchronize()
+
+    def join_comm(self):
+        """Orders the main stream after the latest overlapped all-reduce."""
+        sharded = getattr(self, "sharded", None)
+        if sharded is not None and sharded.peer is not None:
+            sharded.peer.wait()
+
+    def comm_launches(self):
+        sharded = getattr(self, "sharded", None)
+        if sharded is not None and sharded.peer is not None and sharded.peer.overlap:
+            return sharded.peer.comm_ctx.launch_count()
+        return 0
 
     def step_e2e(self, i):
         """One end-to-end step: pinned host inputs -> device -> kernel -> pinned
@@ -502,6 +528,7 @@ def main():
     def barrier():
         torch.cuda.synchronize()
         ctx.synchronize()
+        wl.sync_comm()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -531,7 +558,7 @@ def main():
                 graph = None
                 torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches0 = ctx.launch_count()
+        launches0, comm0 = ctx.launch_count(), wl.comm_launches()
         with torch.cuda.stream(stream):
             start.record()
             if graph is not None:
@@ -543,11 +570,12 @@ def main():
             else:
                 for i in range(steps):
                     step_fn(warmup + i)
+            wl.join_comm()   # the last step's all-reduce belongs to the timed region
             end.record()
         end.synchronize()
         barrier()
         ms = start.elapsed_time(end)
-        launches = ctx.launch_count() - launches0
+        launches = ctx.launch_count() - launches0 + wl.comm_launches() - comm0
         if graph is not None:
             # replayed kernels are not counted by the library: add them
             launches += (steps // graph_sets) * graph_sets * wl.launches_per_step

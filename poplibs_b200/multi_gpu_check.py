@@ -89,6 +89,19 @@ def main() -> int:
     dist.broadcast(first, 0)
     report("all ranks hold identical bits", torch.equal(first, dw32))
 
+    # the same with the all-reduce on a stream of its own, several steps in flight
+    sho = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, overlap_allreduce=True)
+    outs = [(torch.empty_like(dw16), torch.empty_like(dw32)) for _ in range(5)]
+    with torch.cuda.stream(stream):
+        for o16, o32 in outs:
+            sho.wu(x[b:e].contiguous(), dy[b:e].contiguous(), o16, o32)
+        sho.peer.wait()
+    ctx.synchronize()
+    sho.peer.synchronize()
+    torch.cuda.synchronize()
+    report("overlapped all-reduce, five steps in flight",
+           all(torch.equal(o32, dw_ref) and torch.equal(o16, dw_ref.half()) for o16, o32 in outs))
+
     m, k, n = 64 * world + 32, 256, 192
     a, bm = pm1(m, k).to(device), pm1(k, n).to(device)
     mm = parallel.ShardedMatMul(ctx, m, k, n, rank, world)

@@ -61,7 +61,12 @@ class PeerAllReduce:
     The symmetric buffer comes from torch.distributed's symmetric memory (one
     process per GPU, peers mapped through CUDA IPC / fabric handles)."""
 
-    def __init__(self, ctx: capi.Context, count: int, group=None):
+    def __init__(self, ctx: capi.Context, count: int, group=None, overlap: bool = False):
+        """With overlap=True the all-reduce kernel runs on a stream (and library
+        context) of its own: it is ordered after the kernels that fill input()
+        by an event, and the next step's kernels on the main stream do not wait
+        for it -- the exchange over NVLink then hides behind the next layer's
+        (or step's) compute.  Consumers of the outputs call wait() first."""
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
@@ -80,24 +85,61 @@ class PeerAllReduce:
         self.buffer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.signal_ptrs = [int(p) for p in self.handle.signal_pad_ptrs]
         self.epoch = 0
+        self.overlap = overlap
+        # per half: the view to fill and every rank's address of that half
+        self.halves = [self.buf[0], self.buf[1]]
+        self.half_ptrs = [[p + h * count * 4 for p in self.buffer_ptrs] for h in (0, 1)]
+        if overlap:
+            self.main_stream = torch.cuda.ExternalStream(ctx.stream, device=device)
+            self.comm_stream = torch.cuda.Stream(device=device)
+            self.comm_ctx = capi.Context(device.index, stream=self.comm_stream.cuda_stream)
+            self.filled = [torch.cuda.Event(), torch.cuda.Event()]   # input half written (main stream)
+            self.done = [None, None]                                  # all-reduce that read a half (comm stream)
 
     def input(self):
         """The buffer (a torch view, `count` floats) this rank must fill for the next call."""
-        return self.buf[(self.epoch + 1) & 1]
+        half = (self.epoch + 1) & 1
+        if self.overlap and self.done[half] is not None:
+            # the all-reduce of two steps ago read this half: it must have finished
+            self.main_stream.wait_event(self.done[half])
+        return self.halves[half]
 
     def run(self, out_f32=None, out_half=None):
-        """All ranks call this after filling input(); enqueued on the context's stream."""
+        """All ranks call this after filling input(); enqueued on the context's
+        stream, or with overlap on the communication stream behind an event."""
+        import torch
         self.epoch += 1
-        offset = (self.epoch & 1) * self.count * 4
-        self.ctx.allreduce_f32_p2p(self.rank, self.world, [p + offset for p in self.buffer_ptrs],
-                                   self.signal_ptrs, self.epoch, self.count, out_f32, out_half)
+        half = self.epoch & 1
+        ptrs = self.half_ptrs[half]
+        if not self.overlap:
+            self.ctx.allreduce_f32_p2p(self.rank, self.world, ptrs, self.signal_ptrs, self.epoch, self.count,
+                                       out_f32, out_half)
+            return
+        self.filled[half].record(self.main_stream)
+        self.comm_stream.wait_event(self.filled[half])
+        self.comm_ctx.allreduce_f32_p2p(self.rank, self.world, ptrs, self.signal_ptrs, self.epoch, self.count,
+                                        out_f32, out_half)
+        if self.done[half] is None:
+            self.done[half] = torch.cuda.Event()
+        self.done[half].record(self.comm_stream)
+
+    def wait(self):
+        """Orders the main stream after the latest all-reduce (overlap mode)."""
+        if self.overlap and self.epoch and self.done[self.epoch & 1] is not None:
+            self.main_stream.wait_event(self.done[self.epoch & 1])
+
+    def synchronize(self):
+        """Host-side wait for the communication stream; raises if a peer's flag timed out."""
+        if self.overlap:
+            self.comm_ctx.synchronize()
 
 
 class ShardedConv:
     """One rank's part of a batch-sharded convolution layer."""
 
     def __init__(self, ctx: capi.Context, make_kwargs: dict, rank: int = 0, world: int = 1,
-                 group=None, opt: Optional[capi.ConvOptions] = None, peer_allreduce: bool = False):
+                 group=None, opt: Optional[capi.ConvOptions] = None, peer_allreduce: bool = False,
+                 overlap_allreduce: bool = False):
         self.ctx, self.rank, self.world, self.group, self.opt = ctx, rank, world, group, opt
         self.params, self.begin, self.end = local_conv_params(make_kwargs, rank, world)
         self.global_batch = int(make_kwargs["batch"])
@@ -108,7 +150,7 @@ class ShardedConv:
             count = int(p.groups) * int(p.out_chans_per_group) * int(p.in_chans_per_group)
             for i in range(p.num_field_dims):
                 count *= int(p.kernel[i])
-            self.peer = PeerAllReduce(ctx, count, group)
+            self.peer = PeerAllReduce(ctx, count, group, overlap=overlap_allreduce)
 
     def fwd(self, x_local, w, y_local, bias=None):
         if self.params.batch:
