@@ -271,8 +271,16 @@ int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_c
   q.out_f32 = p.output_type == PLB_FLOAT;
   q.force_tile_n = opt ? opt->tile_n : 0;
   q.plan_flags = opt ? opt->plan_flags : 0;
+  // The K loop here is short (K2h steps), below the planner's general threshold
+  // for CTA pairs, but with 64 output channels the instruction is bound by its
+  // activation operand, which a pair splits between two SMs: measured 197 ->
+  // 191 us on the 7x7 stride-2 stem of 256 images.  Taken when there are many tiles.
+  const int sms = ctx ? ctx->sm_count : 148;
+  if ((q.plan_flags & PLB_PLAN_NO_CTA_PAIR) == 0 &&
+      uint64_t(g.OW) * g.OH * g.N >= uint64_t(128) * 8 * sms)
+    q.plan_flags |= PLB_PLAN_FORCE_CTA_PAIR;
   plb_plan plan{};
-  if (int rc = planIgemm(q, ctx ? ctx->sm_count : 148, &plan)) return rc;
+  if (int rc = planIgemm(q, sms, &plan)) return rc;
   plan.kernel = 2;
   plan.workspace_bytes = (x2_elems + w2_elems) * 2;
   if (plan_only) {
