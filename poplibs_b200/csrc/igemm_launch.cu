@@ -396,6 +396,10 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.flip_w = p.flip_w;
   a.group_m = plan.cta_pair ? 8 : 16;  // M tiles (pairs of them) per band
   a.h_outer = halo ? 1 : 0;
+  a.fd_band = make_fastdiv(uint32_t(std::max(1, a.group_m * a.n_tiles)));
+  a.fd_gm = make_fastdiv(uint32_t(std::max(1, a.group_m)));
+  a.fd_tw = make_fastdiv(uint32_t(std::max(1, a.tiles_w)));
+  a.fd_inner = make_fastdiv(uint32_t(std::max(1, a.h_outer ? a.tiles_n : a.tiles_h)));
   a.a_stage_bytes = plan.box_w * plan.box_n * (plan.box_h + plan.halo_rows) * kStageKBytes;
   a.b_tiles_per_stage = (halo && !plan.resident_weights) ? p.taps_h : 1;
   a.halo_step_bytes = p.dil_h * plan.box_w * plan.box_n * kStageKBytes;

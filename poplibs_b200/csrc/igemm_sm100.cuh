@@ -73,6 +73,8 @@ struct IgemmArgs {
   int stride_h, stride_w;  // output pixel oh starts at input row oh*stride_h (TMA traversal stride)
   int flip_h, flip_w;  // tap (r, s) uses the weights stored at (R-1-r, ...) / (..., S-1-s)
   int group_m;    // tile rasterisation: M tiles per band
+  // division by group_m * n_tiles, group_m, tiles_w and (h_outer ? tiles_n : tiles_h)
+  FastDiv fd_band, fd_gm, fd_tw, fd_inner;
   int num_stages;  // pipeline depth (<= kIgemmMaxStages)
   uint32_t idesc_formats;  // operand format bits of the instruction descriptor (8-bit operands: 1 = E5M2)
   // ---- epilogue ---------------------------------------------------------------
@@ -254,29 +256,41 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   auto lead_bar = [&](uint32_t bar) { return k2Cta ? map_to_cta(bar, 0) : bar; };
   constexpr int kElemsPerStage = kFp8 ? 128 : 64;
 
+  // Tile coordinates are needed once per tile by every producer and epilogue
+  // thread; a chain of hardware integer divisions there costs more than a
+  // thousand cycles per tile (measured: it paced the producers of short tiles).
+  // The divisors are fixed for the launch: divide by multiplication instead.
+  // (the multipliers come with the launch arguments: computing them here would
+  // put four 64-bit divisions into every thread's prologue)
+  const FastDiv fd_band = args.fd_band, fd_gm = args.fd_gm, fd_tw = args.fd_tw, fd_inner = args.fd_inner;
+
   // tile index -> (m tile, n tile): bands of group_m M tiles, M fastest inside a band
   auto tile_coords = [&](int tile, int &m_idx, int &n_idx) {
     const int band_tiles = args.group_m * args.n_tiles;
-    const int band = tile / band_tiles;
+    const int band = int(fast_div(uint32_t(tile), fd_band));
     const int within = tile - band * band_tiles;
     const int m0 = band * args.group_m;
     const int gm = min(args.group_m, m_units - m0);
-    m_idx = m0 + within % gm;
-    n_idx = within / gm;
+    // (only the last band can be narrower)
+    const int q = gm == args.group_m ? int(fast_div(uint32_t(within), fd_gm)) : within / gm;
+    m_idx = m0 + within - q * gm;
+    n_idx = q;
     if constexpr (k2Cta) m_idx = 2 * m_idx + int(cta_rank);
   };
 
   // M tile index -> first pixel of the tile; tile row -> pixel inside the tile
   auto tile_origin = [&](int m_idx, int &w0, int &h0, int &n0) {
-    const int tw = m_idx % args.tiles_w;
-    const int rest = m_idx / args.tiles_w;
+    const int rest = int(fast_div(uint32_t(m_idx), fd_tw));
+    const int tw = m_idx - rest * args.tiles_w;
+    const int outer = int(fast_div(uint32_t(rest), fd_inner));
+    const int inner = rest - outer * (args.h_outer ? args.tiles_n : args.tiles_h);
     int th, tn;
     if (args.h_outer) {
-      tn = rest % args.tiles_n;
-      th = rest / args.tiles_n;
+      tn = inner;
+      th = outer;
     } else {
-      th = rest % args.tiles_h;
-      tn = rest / args.tiles_h;
+      th = inner;
+      tn = outer;
     }
     w0 = tw * args.box_w;
     h0 = th * args.box_h;
@@ -352,16 +366,19 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         }
       }
       for (int tile = first_unit; tile < total_tiles && ok; tile += unit_stride) {
+        if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
         int m_idx, n_idx;
         tile_coords(tile, m_idx, n_idx);
         int w0, h0, n0;
         tile_origin(m_idx, w0, h0, n0);
+        if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
         const int w_base = w0 * args.stride_w - args.pad_w;
         const int h_base = h0 * args.stride_h - args.pad_h;
         const int n_col = n_idx * BN;
         int r = 0, s = 0, kc = 0;
         for (int it = 0; it < p_iters; ++it) {
           if (turn == me) {
+            if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
               atomicCAS(args.status, kStatusOk, kStatusProducerTimeout);
               ok = false;

@@ -92,6 +92,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   return true;
 }
 
+// ---- division by a divisor that is fixed for the launch ---------------------
+// q = floor(n / d) for 0 <= n < 2^31, d >= 1, as (umulhi(n, mul) + n) >> shift
+// with shift = ceil(log2 d), mul = floor(2^32 (2^shift - d) / d) + 1.
+struct FastDiv {
+  uint32_t mul, shift;
+};
+__host__ __device__ inline FastDiv make_fastdiv(uint32_t d) {
+  FastDiv f;
+  uint32_t s = 0;
+  while (s < 31 && (1u << s) < d) ++s;
+  f.shift = s;
+  f.mul = uint32_t((((uint64_t(1) << s) - d) << 32) / d + 1);
+  return f;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, FastDiv f) {
+  return (__umulhi(n, f.mul) + n) >> f.shift;
+}
+
 // ---- TMA -------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm))
