@@ -176,6 +176,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   static_assert(!(kFp8 && kBMn), "MN-major B is implemented for fp16 only");
 
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0) PLB_TRACE_STAMP(2, 4000);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // K steps: every (r, s, kc); pipeline steps: in halo mode one per (s, kc)
   const int k_iters = args.taps_h * args.taps_w * args.k_chunks;
@@ -203,23 +204,25 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+  // Set-up is spread over the warps: the lanes of warp 0 initialise the barrier
+  // words (one each), a thread of warp 1 asks for the tensor maps, warp 3
+  // allocates tensor memory.
+  if (warp == 0) {
+    // barrier slots: full[8], empty[8], tmem_full[2], tmem_empty[2], drain,
+    // resident-B, (tensor-memory address, abort flag), pair_free[8], pair_staged[8]
+    for (int i = lane; i < 2 * kMaxStages + 24; i += 32) {
+      if (i == 2 * kMaxStages + 6 || i == 2 * kMaxStages + 7) continue;
+      uint32_t count = 1;
+      if (i == 2 * kMaxStages + 2 || i == 2 * kMaxStages + 3)
+        count = k2Cta ? 512 : 256;  // a group's epilogue threads (of both CTAs)
+      else if (i >= 2 * kMaxStages + 8)
+        count = 2;                  // one arrival per warp of the pair
+      mbar_init(bar_base + 8u * i, count);
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), k2Cta ? 512 : 256);  // a group's epilogue threads (of both CTAs)
-    }
-    mbar_init(drain_bar, 1);
-    mbar_init(resb_bar, 1);
-    for (int pr = 0; pr < 8; ++pr) {
-      mbar_init(pair_free_bar(pr), 2);    // one arrival per warp of the pair
-      mbar_init(pair_staged_bar(pr), 2);
-    }
-    *abort_flag = 0;
+    if (lane == 0) *abort_flag = 0;
     mbar_fence_init();
+    if (lane == 0) PLB_TRACE_STAMP(2, 4010);
+  } else if (threadIdx.x == 32) {
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
     if (args.use_tma_store) tma_prefetch_desc(&tm_out);
@@ -235,15 +238,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) PLB_TRACE_STAMP(2, 4011);
   // the other CTA's copies and arrivals must find initialised barriers
-  if constexpr (k2Cta) cluster_sync_all();
+  // (published by fence.mbarrier_init above)
+  if constexpr (k2Cta) cluster_sync_relaxed();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
   // Everything above touched only this SM (barriers, tensor memory): with a
   // programmatic launch it overlaps the tail of the previous kernel in the
-  // stream.  From here on global memory is read and written.
+  // stream.  Each role goes on preparing what it can without reading or writing
+  // global memory (tile coordinates, descriptors, L2 prefetches of the first
+  // operands, which have no architectural effect) and calls pdl_wait() itself
+  // right before its first access.
+  if (threadIdx.x == 0) PLB_TRACE_STAMP(2, 4001);
   pdl_launch_dependents();
-  pdl_wait();
 
   // Work units: output tiles, or with a CTA pair, pairs of M tiles (the odd
   // last one is padded: its copies read zeros and its stores are clipped).
@@ -308,6 +316,46 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     }
   };
 
+  // B tile of K step (r, s, kc) -> shared memory at `dst`; with kPrefetch the
+  // same box is only pulled towards L2
+  auto load_b = [&](uint32_t dst, uint32_t bar, int r, int s, int kc, int n_col, bool prefetch) {
+    const int b_tap = (args.flip_h ? args.taps_h - 1 - r : r) * args.taps_w +
+                      (args.flip_w ? args.taps_w - 1 - s : s);
+    // a CTA of a pair loads its half of the tile's N rows / columns
+    constexpr int kMyN = k2Cta ? BN / 2 : BN;
+    const int my_col = n_col + int(cta_rank) * kMyN;
+    if constexpr (kBMn) {
+      // K rows x 64 columns per block; blocks of 64 columns are 64 rows apart
+#pragma unroll
+      for (int j = 0; j < kMyN / 64; ++j) {
+        if (prefetch)
+          tma_prefetch_l2_3d(&tm_b, my_col + j * 64, kc * 64, b_tap);
+        else if constexpr (k2Cta)
+          tma_load_3d_pair(dst + j * (64 * kStageKBytes), &tm_b, bar, my_col + j * 64, kc * 64,
+                           b_tap);
+        else
+          tma_load_3d(dst + j * (64 * kStageKBytes), &tm_b, bar, my_col + j * 64, kc * 64, b_tap);
+      }
+    } else {
+      if (prefetch)
+        tma_prefetch_l2_3d(&tm_b, kc * kElemsPerStage, my_col, b_tap);
+      else if constexpr (k2Cta)
+        tma_load_3d_pair(dst, &tm_b, bar, kc * kElemsPerStage, my_col, b_tap);
+      else
+        tma_load_3d(dst, &tm_b, bar, kc * kElemsPerStage, my_col, b_tap);
+    }
+  };
+  // pipeline step index inside a tile -> (filter row, filter column, channel chunk)
+  auto step_coords = [&](int it, int &r, int &s, int &kc) {
+    kc = it % args.k_chunks;
+    const int t = it / args.k_chunks;
+    s = t % args.taps_w;
+    r = t / args.taps_w;
+  };
+  // the barriers that count copied bytes are those of the MMA-issuing CTA,
+  // which alone announces the byte count (both CTAs' shares)
+  constexpr uint32_t kPairFactor = k2Cta ? 2u : 1u;
+
   if (warp < P) {
     // ===================== TMA producers =====================
     if (elect_one()) {
@@ -317,54 +365,45 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       int turn = 0;            // (global K step) mod P
       bool ok = true;
       [[maybe_unused]] int trace_slot = 0;
-      // B tile of K step (r, s, kc) -> shared memory at `dst`
-      auto load_b = [&](uint32_t dst, uint32_t bar, int r, int s, int kc, int n_col) {
-        const int b_tap = (args.flip_h ? args.taps_h - 1 - r : r) * args.taps_w +
-                          (args.flip_w ? args.taps_w - 1 - s : s);
-        // a CTA of a pair loads its half of the tile's N rows / columns
-        constexpr int kMyN = k2Cta ? BN / 2 : BN;
-        const int my_col = n_col + int(cta_rank) * kMyN;
-        if constexpr (kBMn) {
-          // K rows x 64 columns per block; blocks of 64 columns are 64 rows apart
-#pragma unroll
-          for (int j = 0; j < kMyN / 64; ++j) {
-            if constexpr (k2Cta)
-              tma_load_3d_pair(dst + j * (64 * kStageKBytes), &tm_b, bar, my_col + j * 64, kc * 64,
-                               b_tap);
-            else
-              tma_load_3d(dst + j * (64 * kStageKBytes), &tm_b, bar, my_col + j * 64, kc * 64, b_tap);
-          }
-        } else {
-          if constexpr (k2Cta)
-            tma_load_3d_pair(dst, &tm_b, bar, kc * kElemsPerStage, my_col, b_tap);
-          else
-            tma_load_3d(dst, &tm_b, bar, kc * kElemsPerStage, my_col, b_tap);
+      // One pipeline step: the activation box and, unless the weights are
+      // resident, the weight tile(s) of step (r, s, kc) -> stage memory at a_dst
+      // (or, before the predecessor kernel is known to have finished, only
+      // towards L2).
+      auto issue_step = [&](bool prefetch, uint32_t a_dst, uint32_t full, int r, int s, int kc,
+                            int w_base, int h_base, int n0, int n_col) {
+        const int cw = w_base + s * args.dil_w, ch = h_base + r * args.dil_h;
+        const int c2 = args.h_outer ? n0 : ch, c3 = args.h_outer ? ch : n0;
+        if (prefetch)
+          tma_prefetch_l2_4d(&tm_a, kc * kElemsPerStage, cw, c2, c3);
+        else if constexpr (k2Cta)
+          tma_load_4d_pair(a_dst, &tm_a, full, kc * kElemsPerStage, cw, c2, c3);
+        else
+          tma_load_4d(a_dst, &tm_a, full, kc * kElemsPerStage, cw, c2, c3);
+        if constexpr (!kResB) {
+          // with a halo strip the stage carries the weight tiles of every filter row
+          const int row_taps = kHalo ? args.taps_h : 1;
+          for (int rr = 0; rr < row_taps; ++rr)
+            load_b(a_dst + args.a_stage_bytes + rr * S::kBBytes, full, kHalo ? rr : r, s, kc, n_col,
+                   prefetch);
         }
       };
-      // the barriers that count copied bytes are those of the MMA-issuing CTA,
-      // which alone announces the byte count (both CTAs' shares)
-      constexpr uint32_t kPairFactor = k2Cta ? 2u : 1u;
-      if constexpr (kResB) {
-        if (first_unit < total_tiles) {
-          // single N tile: every tile of this CTA uses the same weights.  The
-          // producers share the copies (a copy costs its issuing thread on the
-          // order of a hundred cycles and the first MMA waits for all of them).
-          if (me == 0 && leader)
-            mbar_expect_tx(resb_bar, kPairFactor * uint32_t(k_iters) * S::kBBytes);
-          const uint32_t resb_bar_lead = lead_bar(resb_bar);
-          int r = 0, s = 0, kc = 0;
-          for (int it = 0; it < k_iters; ++it) {
-            if (it % P == me) load_b(resb_base + it * S::kBBytes, resb_bar_lead, r, s, kc, 0);
-            if (++kc == args.k_chunks) {
-              kc = 0;
-              if (++s == args.taps_w) {
-                s = 0;
-                ++r;
-              }
-            }
-          }
+      // While the predecessor kernel may still be running: pull the boxes of
+      // this producer's first steps towards L2.
+      if (first_unit < total_tiles) {
+        int m_idx, n_idx;
+        tile_coords(first_unit, m_idx, n_idx);
+        int w0, h0, n0;
+        tile_origin(m_idx, w0, h0, n0);
+        const int steps = min(p_iters, kStages);
+        for (int it = me; it < steps; it += P) {
+          int r, s, kc;
+          step_coords(it, r, s, kc);
+          issue_step(true, 0u, 0u, r, s, kc, w0 * args.stride_w - args.pad_w,
+                     h0 * args.stride_h - args.pad_h, n0, n_idx * BN);
         }
       }
+      pdl_wait();
+      if (me == 0) PLB_TRACE_STAMP(2, 4002);
       for (int tile = first_unit; tile < total_tiles && ok; tile += unit_stride) {
         if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
         int m_idx, n_idx;
@@ -388,25 +427,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             const uint32_t a_dst = smem_base + stage * stage_bytes;
             if (leader) mbar_expect_tx(full_bar(stage), kPairFactor * uint32_t(stage_bytes));
             const uint32_t full = lead_bar(full_bar(stage));
-            const int cw = w_base + s * args.dil_w, ch = h_base + r * args.dil_h;
-            if constexpr (k2Cta) {
-              if (args.h_outer)
-                tma_load_4d_pair(a_dst, &tm_a, full, kc * kElemsPerStage, cw, n0, ch);
-              else
-                tma_load_4d_pair(a_dst, &tm_a, full, kc * kElemsPerStage, cw, ch, n0);
-            } else {
-              if (args.h_outer)
-                tma_load_4d(a_dst, &tm_a, full, kc * kElemsPerStage, cw, n0, ch);
-              else
-                tma_load_4d(a_dst, &tm_a, full, kc * kElemsPerStage, cw, ch, n0);
-            }
-            if constexpr (!kResB) {
-              // with a halo strip the stage carries the weight tiles of every filter row
-              const int row_taps = kHalo ? args.taps_h : 1;
-              for (int rr = 0; rr < row_taps; ++rr)
-                load_b(a_dst + args.a_stage_bytes + rr * S::kBBytes, full, kHalo ? rr : r, s, kc,
-                       n_col);
-            }
+            issue_step(false, a_dst, full, r, s, kc, w_base, h_base, n0, n_col);
             if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
             stage += P;
             if (stage >= kStages) {
@@ -629,6 +650,33 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       }
     };
     const uint32_t acc_free_bar = lead_bar(tmem_empty_bar(acc));
+    if constexpr (kResB) {
+      // Resident weights: a single N tile, so every tile of this CTA uses the
+      // same weights.  The epilogue warps have nothing to do until the first
+      // accumulator is complete, so one lane of each issues a share of the
+      // copies (a copy costs its issuing thread some hundred cycles, and the
+      // first MMA waits for all of them), leaving the producers free to start
+      // on the activations at once.
+      if (lane == 0 && first_unit < total_tiles) {
+        for (int it = warp - 4; it < k_iters; it += 16) {
+          int r, s, kc;
+          step_coords(it, r, s, kc);
+          load_b(0u, 0u, r, s, kc, 0, true);
+        }
+        pdl_wait();
+        if (warp == 4 && leader)
+          mbar_expect_tx(resb_bar, kPairFactor * uint32_t(k_iters) * S::kBBytes);
+        const uint32_t resb_bar_lead = lead_bar(resb_bar);
+        for (int it = warp - 4; it < k_iters; it += 16) {
+          int r, s, kc;
+          step_coords(it, r, s, kc);
+          load_b(resb_base + it * S::kBBytes, resb_bar_lead, r, s, kc, 0, false);
+        }
+        if (warp == 4) PLB_TRACE_STAMP(2, 4012);
+      }
+      __syncwarp();
+    }
+    pdl_wait();
     for (int tile = first_unit + group * unit_stride; tile < total_tiles;
          tile += 2 * unit_stride, local_tile += 2) {
       int m_idx, n_idx;
@@ -839,15 +887,21 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 2);
       if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 3);
     }
-    // all of this thread's stores must be complete before the CTA exits
-    if (tma_store && lane == 0) tma_store_wait_all<0>();
+    // this thread's stores must have read their staging buffers before the CTA
+    // gives up its shared memory (the writes themselves complete with the grid)
+    if (tma_store && lane == 0) tma_store_wait_read<0>();
   }
 
+  if (threadIdx.x == 0) PLB_TRACE_STAMP(2, 4003);
   tc_fence_before_sync();
-  __syncthreads();
   // Neither CTA of a pair may go away while the other can still touch its
-  // barriers, shared memory or tensor memory.
-  if constexpr (k2Cta) cluster_sync_all();
+  // barriers, shared memory or tensor memory: the rendezvous of all threads of
+  // the cluster (which is also this CTA's own barrier) orders that.
+  if constexpr (k2Cta)
+    cluster_sync_relaxed();
+  else
+    __syncthreads();
+  if (threadIdx.x == 0) PLB_TRACE_STAMP(2, 4004);
   if (warp == kIgemmMmaWarp) {
     tc_fence_after_sync();
     if constexpr (k2Cta)
@@ -855,6 +909,14 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     else
       tmem_dealloc(tmem_base, kTmemCols);
   }
+#ifdef PLB_TRACE
+  if (threadIdx.x == 0) {
+    PLB_TRACE_STAMP(2, 4005);
+    uint32_t smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    if (args.trace != nullptr && blockIdx.x == 0) args.trace[2 * 4096 + 4006] = smid;
+  }
+#endif
 }
 
 }  // namespace plb

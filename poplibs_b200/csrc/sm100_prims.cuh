@@ -142,6 +142,25 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *tm,
       : "memory");
 }
 
+// Prefetch of a tensor box into L2.  It has no architectural effect (no data
+// reaches the SM, nothing is ordered by it), so it may be issued for memory
+// that an earlier kernel is still writing: a kernel launched programmatically
+// uses it to pull the operands of its first tiles towards L2 while it waits
+// for its predecessor to finish.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap *tm, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                   reinterpret_cast<uint64_t>(tm)),
+               "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap *tm, int c0, int c1, int c2,
+                                                   int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                   reinterpret_cast<uint64_t>(tm)),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
 // Tensor store shared -> global (bulk async group); the hardware clips the box
 // to the tensor's extents, so partial tiles need no masking.
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *tm, uint32_t src, int c0, int c1,
@@ -376,6 +395,16 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 }
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\t"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The same rendezvous without the release: it orders execution (no thread of
+// the cluster passes before all have arrived) but publishes no memory.  That is
+// all a lifetime barrier needs (barrier words made visible by
+// fence.mbarrier_init beforehand; shared / tensor memory that must not be
+// released while the other CTA can still reach it), and the release form costs
+// every thread a cluster-scope fence, measured at 650-1000 cycles per barrier.
+__device__ __forceinline__ void cluster_sync_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\t"
                "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 // Arrive on a barrier that may live in the other CTA of the cluster.  Default
