@@ -339,7 +339,8 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   IgemmArgs a{};
   // Output through TMA when the tensor can be described to it: 16-byte aligned
   // base and pixel stride.  Each epilogue warp stores a (columns, w, h, n) box
-  // holding its 32 pixels; 128 bytes of columns per box.
+  // holding its 32 pixels and 32 columns: 128-byte rows of fp32, 64-byte rows
+  // (64-byte swizzle) of half.
   CUtensorMap tout;
   std::memset(&tout, 0, sizeof tout);
   const size_t out_es = p.out_f32 ? 4 : 2;
@@ -362,13 +363,12 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
     strides[0] = sw;
     strides[1] = halo ? sn : sh;
     strides[2] = halo ? sh : sn;
-    const uint32_t box[4] = {uint32_t(128 / out_es), uint32_t(a.sub_w), uint32_t(a.sub_h),
-                             uint32_t(sub_3)};
+    const uint32_t box[4] = {32u, uint32_t(a.sub_w), uint32_t(a.sub_h), uint32_t(sub_3)};
     const uint32_t es[4] = {1, 1, 1, 1};
     if (int rc = encodeTensorMap(&tout,
                                  p.out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                                 4, p.out, dims, strides, box, es))
+                                 4, p.out, dims, strides, box, es, p.out_f32 ? 128 : 64))
       return rc;
     a.use_tma_store = 1;
   }

@@ -197,9 +197,6 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   volatile uint32_t *tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t *>(bar_gen + 8 * (2 * kMaxStages + 6));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(bar_gen + 8 * (2 * kMaxStages + 7));
-  // epilogue warp pairs: "staging buffer free" and "staging buffer written", 8 pairs each
-  auto pair_free_bar = [&](int pr) { return bar_base + 8u * (2 * kMaxStages + 8 + pr); };
-  auto pair_staged_bar = [&](int pr) { return bar_base + 8u * (2 * kMaxStages + 16 + pr); };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -208,16 +205,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   // words (one each), a thread of warp 1 asks for the tensor maps, warp 3
   // allocates tensor memory.
   if (warp == 0) {
-    // barrier slots: full[8], empty[8], tmem_full[2], tmem_empty[2], drain,
-    // resident-B, (tensor-memory address, abort flag), pair_free[8], pair_staged[8]
-    for (int i = lane; i < 2 * kMaxStages + 24; i += 32) {
-      if (i == 2 * kMaxStages + 6 || i == 2 * kMaxStages + 7) continue;
-      uint32_t count = 1;
-      if (i == 2 * kMaxStages + 2 || i == 2 * kMaxStages + 3)
-        count = k2Cta ? 512 : 256;  // a group's epilogue threads (of both CTAs)
-      else if (i >= 2 * kMaxStages + 8)
-        count = 2;                  // one arrival per warp of the pair
-      mbar_init(bar_base + 8u * i, count);
+    // barrier slots: full[8], empty[8], tmem_full[2], tmem_empty[2], drain, resident-B
+    if (lane < 2 * kMaxStages + 6) {
+      // tmem_empty counts a group's epilogue threads (of both CTAs of a pair)
+      const bool acc_free = lane == 2 * kMaxStages + 2 || lane == 2 * kMaxStages + 3;
+      mbar_init(bar_base + 8u * lane, acc_free ? (k2Cta ? 512u : 256u) : 1u);
     }
     if (lane == 0) *abort_flag = 0;
     mbar_fence_init();
@@ -446,41 +438,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           }
         }
       }
-      // Teardown (producer 0): every copy must have landed before the CTA may
-      // exit.  In a run without errors the consumer has already waited for
-      // them, so this costs one try_wait per stage.  Stage s was last filled
-      // by K step g = the largest g < total with g mod kStages == s, in phase
-      // (g / kStages) & 1; a stage that was never used is skipped.
-      // (With a CTA pair the barriers live in the MMA-issuing CTA, which waits
-      // for both CTAs' copies; the other CTA cannot leave before the cluster
-      // barrier at the end of the kernel.)
-      if (me == 0 && leader) {
-        const int my_tiles = (total_tiles > first_unit)
-                                 ? (total_tiles - first_unit + unit_stride - 1) / unit_stride
-                                 : 0;
-        const long long total_steps = (long long)my_tiles * p_iters;
-        if (kResB && my_tiles > 0) {
-          const long long start = clock64();
-          while (!mbar_try_wait(resb_bar, 0)) {
-            if (*abort_flag != 0 || clock64() - start > kWaitCycleLimit) {
-              atomicCAS(args.status, kStatusOk, kStatusDrainTimeout);
-              break;
-            }
-          }
-        }
-        for (int st = 0; st < kStages; ++st) {
-          if (total_steps <= st) continue;
-          const long long g = st + ((total_steps - 1 - st) / kStages) * kStages;
-          const uint32_t last = uint32_t((g / kStages) & 1);
-          const long long start = clock64();
-          while (!mbar_try_wait(full_bar(st), last)) {
-            if (*abort_flag != 0 || clock64() - start > kWaitCycleLimit) {
-              atomicCAS(args.status, kStatusOk, kStatusDrainTimeout);
-              break;
-            }
-          }
-        }
-      }
+      if (me == 0) PLB_TRACE_STAMP(2, 4014);
     }
   } else if (warp == kIgemmMmaWarp) {
     // ===================== MMA issuer =====================
@@ -601,6 +559,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           break;
         }
       }
+      PLB_TRACE_STAMP(2, 4015);
     }
   } else if (warp >= 4) {
     // ===================== epilogue (warps 4..19) =====================
@@ -623,11 +582,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     // origin of this warp's 32 rows inside the tile's pixel box
     int qw, qh, qn;
     row_pixel(quarter * 32, qw, qh, qn);
-    const int pair = group * 4 + quarter;    // staging buffer and named barrier of the two warps
-    // one staging buffer per pair (a second one was measured: it costs a
-    // pipeline stage and hides nothing, the chain below is bound by its own
-    // instructions and synchronisation, not by the store reading the buffer)
-    const uint32_t buf = staging_base + uint32_t(pair) * 4096u;
+    // fp32 output: one 32-row x 128-byte staging buffer per lane quarter of a
+    // group (a second one was measured: it costs a pipeline stage and hides
+    // nothing, the chain below is bound by its own instructions, not by the
+    // store reading the buffer)
+    const uint32_t buf = staging_base + uint32_t(group * 4 + quarter) * 4096u;
     const uint32_t row_addr = buf + uint32_t(lane) * 128u;
     const bool tma_store = args.use_tma_store != 0;
     const bool out_f32 = args.out_is_f32 != 0;
@@ -637,18 +596,6 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     const bool stamp = threadIdx.x == 128;
     const int acc = group;
     int local_tile = group;
-    uint32_t blocks_done = 0;                // 64-column blocks so far (selects the storing warp)
-    uint32_t pair_phase = 0;                 // both barriers complete once per block
-    bool pair_ok = true;
-    // arrive (one lane per warp, after the warp's own work is ordered) and wait
-    auto pair_sync = [&](uint32_t bar) {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar);
-      if (!mbar_wait(bar, pair_phase, abort_flag)) {
-        atomicCAS(args.status, kStatusOk, kStatusEpilogueTimeout);
-        pair_ok = false;
-      }
-    };
     const uint32_t acc_free_bar = lead_bar(tmem_empty_bar(acc));
     if constexpr (kResB) {
       // Resident weights: a single N tile, so every tile of this CTA uses the
@@ -822,7 +769,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       } else if (out_f32) {
         // (half == 0 warps only) one 32-column chunk per staged buffer and store
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32, ++blocks_done) {
+        for (int c = 0; c < BN; c += 32) {
           __syncwarp();
           tmem_ld_32x32(t_addr + c, v);
           tmem_ld_wait_for(v);
@@ -840,49 +787,37 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
           store_staged(buf, col_base + c);
         }
       } else {
-        // half output: this warp's 32 columns are one 64-byte half of the staged
-        // rows; 16-byte pieces are XOR-swizzled with the row index, the pattern
-        // the tensor map uses.  Block k is stored by the warp with half == k mod 2;
-        // before block k + 1 is staged, that warp waits until its store has
-        // read the buffer.
+        // half output: each warp stages its own 32 rows x 32 columns (64-byte
+        // rows; 16-byte pieces XOR-swizzled with bits 1-2 of the row index, the
+        // tensor map's 64-byte swizzle, which also keeps the stores free of bank
+        // conflicts) and hands them to a tensor store of its own, so no barrier
+        // between warps lies on the chain load -> convert -> stage -> store.
+        const uint32_t wbuf = staging_base + uint32_t(warp - 4) * 2048u;
+        const uint32_t wrow = wbuf + uint32_t(lane) * 64u;
+        const uint32_t sw = (uint32_t(lane) >> 1) & 3u;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 64, ++blocks_done) {
-          [[maybe_unused]] const bool fine = stamp && local_tile == 2;
-          [[maybe_unused]] const int fslot = 2048 + (c >> 6) * 8;
-          if (fine) PLB_TRACE_STAMP(2, fslot + 0);
+        for (int c = half * 32; c < BN; c += 64) {
           __syncwarp();
-          tmem_ld_32x32(t_addr + c + half * 32, v);
+          tmem_ld_32x32(t_addr + c, v);
           tmem_ld_wait_for(v);
-          if (fine) PLB_TRACE_STAMP(2, fslot + 1);
           if (c + 64 >= BN) release_accumulator();
-          finish(v, f, c + half * 32);
-          const bool stores_now = (blocks_done & 1u) == uint32_t(half);
-          // the warp that stored the previous block waits until that store has
-          // read the buffer; then both may overwrite it
-          if (!stores_now && lane == 0) tma_store_wait_read<0>();
-          if (fine) PLB_TRACE_STAMP(2, fslot + 2);
-          pair_sync(pair_free_bar(pair));  // buffer free
-          if (fine) PLB_TRACE_STAMP(2, fslot + 3);
+          finish(v, f, c);
+          if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the buffer
+          __syncwarp();
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             __half2 h0 = __floats2half2_rn(f[8 * j], f[8 * j + 1]);
             __half2 h1 = __floats2half2_rn(f[8 * j + 2], f[8 * j + 3]);
             __half2 h2 = __floats2half2_rn(f[8 * j + 4], f[8 * j + 5]);
             __half2 h3 = __floats2half2_rn(f[8 * j + 6], f[8 * j + 7]);
-            st_shared_v4(row_addr + (uint32_t((half * 4 + j) ^ (lane & 7)) << 4),
-                         *reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
-                         *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+            st_shared_v4(wrow + ((uint32_t(j) ^ sw) << 4), *reinterpret_cast<uint32_t *>(&h0),
+                         *reinterpret_cast<uint32_t *>(&h1), *reinterpret_cast<uint32_t *>(&h2),
+                         *reinterpret_cast<uint32_t *>(&h3));
           }
           fence_proxy_async_smem();
-          if (fine) PLB_TRACE_STAMP(2, fslot + 4);
-          pair_sync(pair_staged_bar(pair));  // buffer staged by both warps
-          pair_phase ^= 1u;
-          if (fine) PLB_TRACE_STAMP(2, fslot + 5);
-          if (!pair_ok) break;
-          if (stores_now) store_staged(buf, col_base + c);
-          if (fine) PLB_TRACE_STAMP(2, fslot + 6);
+          __syncwarp();
+          store_staged(wbuf, col_base + c);
         }
-        if (!pair_ok) break;
       }
       if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 2);
       if (stamp) PLB_TRACE_STAMP(2, local_tile * 4 + 3);
@@ -890,10 +825,40 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
     // this thread's stores must have read their staging buffers before the CTA
     // gives up its shared memory (the writes themselves complete with the grid)
     if (tma_store && lane == 0) tma_store_wait_read<0>();
+    if (stamp) PLB_TRACE_STAMP(2, 4016);
   }
 
   if (threadIdx.x == 0) PLB_TRACE_STAMP(2, 4003);
   tc_fence_before_sync();
+  // Every tensor copy must have landed before the CTA gives up its shared
+  // memory.  In a run without errors the MMA issuer has waited for every
+  // stage it consumed, i.e. for all of them; only after an aborted wait can
+  // copies still be in flight, and then they are waited for here (bounded).
+  // Stage s was last filled by pipeline step g = the largest g < total with
+  // g mod kStages == s, in phase (g / kStages) & 1.  With a CTA pair the
+  // barriers live in the MMA-issuing CTA, which waits for both CTAs' copies;
+  // the other CTA cannot leave before the rendezvous below.
+  __syncthreads();
+  if (*abort_flag != 0 && threadIdx.x == 0 && leader) {
+    const int my_tiles =
+        total_tiles > first_unit ? (total_tiles - first_unit + unit_stride - 1) / unit_stride : 0;
+    const long long total_steps = (long long)my_tiles * p_iters;
+    const long long start = clock64();
+    auto drain = [&](uint32_t bar, uint32_t parity) {
+      while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > kWaitCycleLimit) {
+          atomicCAS(args.status, kStatusOk, kStatusDrainTimeout);
+          break;
+        }
+      }
+    };
+    if (kResB && my_tiles > 0) drain(resb_bar, 0);
+    for (int st = 0; st < kStages; ++st) {
+      if (total_steps <= st) continue;
+      const long long g = st + ((total_steps - 1 - st) / kStages) * kStages;
+      drain(full_bar(st), uint32_t((g / kStages) & 1));
+    }
+  }
   // Neither CTA of a pair may go away while the other can still touch its
   // barriers, shared memory or tensor memory: the rendezvous of all threads of
   // the cluster (which is also this CTA's own barrier) orders that.

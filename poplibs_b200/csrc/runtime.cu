@@ -49,7 +49,7 @@ int scratch(plb_context *ctx, int slot, size_t bytes, void **ptr) {
 
 int encodeTensorMap(CUtensorMap *tm, CUtensorMapDataType type, int rank, const void *base,
                     const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box,
-                    const uint32_t *elem_strides) {
+                    const uint32_t *elem_strides, int swizzle_bytes) {
   static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   static std::once_flag once;
   static cudaError_t lookup_err = cudaSuccess;
@@ -80,7 +80,8 @@ int encodeTensorMap(CUtensorMap *tm, CUtensorMapDataType type, int rank, const v
   }
   const CUresult res = encode(tm, type, cuuint32_t(rank), const_cast<void *>(base), gdims,
                               gstrides, gbox, gestr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                  : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS) {
     std::string msg = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string(int(res)) +

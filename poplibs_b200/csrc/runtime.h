@@ -73,7 +73,7 @@ int scratch(plb_context *ctx, int slot, size_t bytes, void **ptr);
 // stride of dims[i + 1].
 int encodeTensorMap(CUtensorMap *tm, CUtensorMapDataType type, int rank, const void *base,
                     const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box,
-                    const uint32_t *elem_strides);
+                    const uint32_t *elem_strides, int swizzle_bytes = 128);
 
 inline size_t dtypeBytes(int dtype) {
   return dtype == PLB_FLOAT ? 4 : dtype == PLB_HALF ? 2 : 1;
