@@ -240,7 +240,9 @@ class Workload:
                 # weak scaling: every rank holds one full per-GPU batch of the layer
                 glob = dict(kw, batch=kw["batch"] * world)
                 self.allreduce = "none (no collective on this pass)"
-                peer = self.pass_ == "wu" and os.environ.get("PLB_BENCH_ALLREDUCE", "p2p") == "p2p"
+                ar = os.environ.get("PLB_BENCH_ALLREDUCE", "p2p")   # p2p | p2p_fused | p2p_oneshot | p2p_rs | nccl
+                peer = self.pass_ == "wu" and ar.startswith("p2p")
+                ar_mode = {"p2p_oneshot": "oneshot", "p2p_rs": "rs", "p2p_fused": "fused"}.get(ar, "auto")
                 # PLB_BENCH_OVERLAP=1: the all-reduce of step i runs on a stream of its own, behind
                 # step i + 1's kernels.  Off by default: the event between the kernels costs the
                 # programmatic launch overlap, and the measured step is not shorter
@@ -248,9 +250,9 @@ class Workload:
                 overlap = peer and os.environ.get("PLB_BENCH_OVERLAP", "0") == "1"
                 try:
                     self.sharded = parallel.ShardedConv(ctx, glob, rank, world, peer_allreduce=peer,
-                                                        overlap_allreduce=overlap)
+                                                        overlap_allreduce=overlap, allreduce_mode=ar_mode)
                     if self.pass_ == "wu":
-                        self.allreduce = (("library kernel over NVLink peer memory"
+                        self.allreduce = ((f"library kernel over NVLink peer memory ({self.sharded.peer.mode})"
                                            + (", overlapped with the next step on a second stream" if overlap else ""))
                                           if peer else "nccl all_reduce + cast")
                 except Exception as e:  # symmetric memory unavailable: the process group's all-reduce

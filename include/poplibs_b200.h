@@ -243,6 +243,36 @@ PLB_API int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_c
 PLB_API int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
                 const void *d_acts, const void *d_out_grads, void *d_weight_grads,
                 float *d_weight_grads_f32);
+/* The weight update of a batch-sharded layer on several GPUs of one box, with the
+ * sum over the ranks fused into the split-K reduction: every rank passes its
+ * batch slice, and d_weight_grads / d_weight_grads_f32 receive the gradient of
+ * the WHOLE batch on every rank (bit-identical on all of them: the ranks' sums
+ * are added in rank order).  The reduction kernel writes this rank's gradient
+ * chunk by chunk into a peer-addressable buffer, flags each chunk to the peers
+ * and adds the peers' chunks with NVLink peer loads as their flags arrive, so the
+ * exchange overlaps the reduction instead of following it as a second kernel.
+ * This replaces plb_conv_wu + plb_allreduce_f32_p2p; the reference has no
+ * counterpart (it spreads one convolution over IPU tiles inside one graph,
+ * lib/poplin/ConvPlan.hpp:28-77).
+ *   d_peer_grads[r]  rank r's gradient buffer: groups * kernel elements * Co * Ci
+ *                    floats, 16-byte aligned, addressable from this GPU; the
+ *                    caller alternates between two such buffers on successive
+ *                    steps (a peer may still be reading the previous step's);
+ *   d_peer_flags[r]  rank r's flag area, plb_conv_wu_allreduce_flag_bytes(p)
+ *                    bytes, zero before the first step, used only by this call;
+ *   epoch            1, 2, 3, ... the same on every rank for the same step.
+ * Every rank must make the call (a rank with an empty slice contributes zeros).
+ * Waits are bounded: a peer that never signals is reported through the context's
+ * status word (plb_synchronize), nothing hangs.  Layers that plb_conv_wu runs
+ * through a preparatory pass (channel counts not a multiple of 8, input dilation
+ * or flip, truncated or flipped kernels, 3-D fields) and gradients larger than
+ * 4 chunks of 2 KiB per SM return PLB_ERR_UNSUPPORTED: use the two-call form. */
+PLB_API int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p,
+                          const plb_conv_options *opt, const void *d_acts, const void *d_out_grads,
+                          int32_t rank, int32_t world, void *const *d_peer_grads,
+                          void *const *d_peer_flags, uint32_t epoch, void *d_weight_grads,
+                          float *d_weight_grads_f32);
+PLB_API uint64_t plb_conv_wu_allreduce_flag_bytes(const plb_conv_params *p);
 /* The same weight gradient for callers that cannot allocate device memory when
  * they need it (code running under an allocator that owns all device memory or
  * inside its hooks, loops that may not take the allocator's lock, processes with
@@ -282,6 +312,25 @@ PLB_API int plb_conv_wu_static_scratch(int device, void *cuda_stream, const plb_
 PLB_API int plb_allreduce_f32_p2p(plb_context *ctx, int32_t rank, int32_t world,
                           const void *const *d_buffers, void *const *d_signal_pads,
                           uint32_t epoch, size_t count, float *d_out_f32, void *d_out_half);
+/* The same sum as a reduce-scatter followed by an all-gather inside one kernel
+ * per rank: rank r adds slice r of every rank's input (peer loads, rank order)
+ * and stores the sums into every rank's result buffer (peer stores); after a
+ * second round of flags every rank reads its own result buffer and writes the
+ * fp32 sum and / or its cast.  Per rank (N - 1) / N of the vector crosses
+ * NVLink in each direction instead of N - 1 times the vector inbound, which
+ * is what pays from about four ranks on; results are bit-identical to
+ * plb_allreduce_f32_p2p's.  No counterpart in the reference (see above).
+ *   d_inputs[r]   rank r's fp32 vector, `count` elements, peer-addressable;
+ *   d_results[r]  rank r's result buffer, `count` elements, peer-addressable,
+ *                 distinct from the inputs;
+ *   d_signal_pads, epoch as above (the same pads may serve both calls).
+ * One input and one result buffer suffice: the second flag round tells a rank
+ * that all peers have read its input, the next call's first round that all
+ * have consumed their results.  Calls on one set of buffers must not overlap. */
+PLB_API int plb_allreduce_f32_p2p_rs(plb_context *ctx, int32_t rank, int32_t world,
+                             const void *const *d_inputs, void *const *d_results,
+                             void *const *d_signal_pads, uint32_t epoch, size_t count,
+                             float *d_out_f32, void *d_out_half);
 PLB_API uint32_t plb_allreduce_p2p_signal_bytes(int32_t world);
 /* weights += scale * weight_grads_f32, cast to the weights' type
  * (popops::scaledAddTo in convolutionWeightUpdate, lib/poplin/Convolution.cpp:3509-3522). */

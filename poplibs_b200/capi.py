@@ -140,7 +140,8 @@ SYMBOLS = (
     "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution",
     "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
     "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_bias_update", "plb_conv_fwd_host",
-    "plb_allreduce_f32_p2p", "plb_allreduce_p2p_signal_bytes", "plb_matmul_host_async",
+    "plb_allreduce_f32_p2p", "plb_allreduce_f32_p2p_rs", "plb_conv_wu_allreduce",
+    "plb_conv_wu_allreduce_flag_bytes", "plb_allreduce_p2p_signal_bytes", "plb_matmul_host_async",
     "plb_conv_fwd_host_async",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
     "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
@@ -195,6 +196,11 @@ def lib():
     L.plb_add_bias.argtypes = [vp, i32, vp, vp, u64, u32]
     L.plb_conv_bias_update.argtypes = [vp, i32, vp, u64, u32, i32, vp, f32]
     L.plb_allreduce_f32_p2p.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u32, sz, vp, vp]
+    L.plb_allreduce_f32_p2p_rs.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), u32, sz,
+                                           vp, vp]
+    L.plb_conv_wu_allreduce.argtypes = [vp, CP, OP, vp, vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u32, vp, vp]
+    L.plb_conv_wu_allreduce_flag_bytes.argtypes = [CP]
+    L.plb_conv_wu_allreduce_flag_bytes.restype = u64
     L.plb_allreduce_p2p_signal_bytes.argtypes = [i32]
     L.plb_allreduce_p2p_signal_bytes.restype = u32
     L.plb_conv_fwd_host.argtypes = [vp, CP, OP, vp, vp, vp, vp]
@@ -322,6 +328,25 @@ class Context:
         pads = (C.c_void_p * world)(*[int(p) for p in signal_pad_ptrs])
         _check(lib().plb_allreduce_f32_p2p(self._h, rank, world, bufs, pads, epoch, count,
                                            _ptr(out_f32), _ptr(out_half)))
+
+    def conv_wu_allreduce(self, p: ConvParams, x, dy, rank, world, grad_ptrs, flag_ptrs, epoch, dw,
+                          dw_f32=None, opt: Optional[ConvOptions] = None):
+        """Weight update of this rank's batch slice with the sum over ranks fused
+        into the reduction kernel; grad_ptrs / flag_ptrs: `world` device addresses."""
+        grads = (C.c_void_p * world)(*[int(v) for v in grad_ptrs])
+        flags = (C.c_void_p * world)(*[int(v) for v in flag_ptrs])
+        _check(lib().plb_conv_wu_allreduce(self._h, C.byref(p), C.byref(opt) if opt else None, _ptr(x),
+                                           _ptr(dy), rank, world, grads, flags, epoch, _ptr(dw),
+                                           _ptr(dw_f32)))
+
+    def allreduce_f32_p2p_rs(self, rank, world, input_ptrs, result_ptrs, signal_pad_ptrs, epoch, count,
+                             out_f32, out_half):
+        """Reduce-scatter + all-gather form; the three tables hold `world` device addresses (ints)."""
+        ins = (C.c_void_p * world)(*[int(p) for p in input_ptrs])
+        res = (C.c_void_p * world)(*[int(p) for p in result_ptrs])
+        pads = (C.c_void_p * world)(*[int(p) for p in signal_pad_ptrs])
+        _check(lib().plb_allreduce_f32_p2p_rs(self._h, rank, world, ins, res, pads, epoch, count,
+                                              _ptr(out_f32), _ptr(out_half)))
 
     def cast_from_f32(self, dtype, dst, src, count):
         _check(lib().plb_cast_from_f32(self._h, dtype, _ptr(dst), _ptr(src), count))

@@ -703,7 +703,9 @@ int plb_matmul_host_async(plb_context *ctx, const plb_matmul_desc *desc, const v
   if (int rc = plb_memcpy_h2d(ctx, da, h_a, a_bytes)) return rc;
   if (int rc = plb_memcpy_h2d(ctx, db, h_b, b_bytes)) return rc;
   if (int rc = plb_matmul(ctx, desc, da, db, dc, dd)) return rc;
-  return plb_memcpy_d2h(ctx, h_d, dd, c_bytes);
+  // enqueued only: the caller synchronises (plb_synchronize) before reading h_d
+  if (c_bytes) PLB_CUDA(cudaMemcpyAsync(h_d, dd, c_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return PLB_OK;
 }
 
 // ---------------------------------------------------------------------------
@@ -1075,7 +1077,10 @@ int plb_conv_fwd_host_async(plb_context *ctx, const plb_conv_params *p,
   if (int rc = plb_memcpy_h2d(ctx, di, h_in, in_bytes)) return rc;
   if (int rc = plb_memcpy_h2d(ctx, dw, h_weights, w_bytes)) return rc;
   if (int rc = plb_conv_fwd(ctx, p, opt, di, dw, static_cast<const float *>(dbias), dout)) return rc;
-  return plb_memcpy_d2h(ctx, h_out, dout, out_bytes);
+  // enqueued only: the caller synchronises (plb_synchronize) before reading h_out
+  if (out_bytes)
+    PLB_CUDA(cudaMemcpyAsync(h_out, dout, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return PLB_OK;
 }
 
 }  // extern "C"

@@ -202,11 +202,74 @@ __global__ void scatterTapsKernel(const T *__restrict__ src, T *__restrict__ dst
   }
 }
 
+// The wu kernel needs more dynamic shared memory than the default limit: raised
+// once per device, for every entry point alike.
+int configureWuKernel(int device) {
+  static std::mutex mutex;
+  static bool configured[64] = {};
+  if (device < 0 || device >= 64) return fail(PLB_ERR_INVALID_PARAMS, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(mutex);
+  if (!configured[device]) {
+    // the caller has made `device` current
+    PLB_CUDA(cudaFuncSetAttribute(wu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured[device] = true;
+  }
+  return PLB_OK;
+}
+
+// Reduction over the K splits of group g (and, with `peer`, over the ranks).
+int launchWuReduce(cudaStream_t stream, const WuArgs &a, size_t w_elems, unsigned g,
+                   void *d_weight_grads, float *d_weight_grads_f32, const WuPeerArgs *peer) {
+  const size_t es = 2;
+  cudaLaunchAttribute pdl[1];
+  pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl[0].val.programmaticStreamSerializationAllowed = 1;
+  float *out32 = d_weight_grads_f32 ? d_weight_grads_f32 + size_t(g) * w_elems : nullptr;
+  uint8_t *out16 =
+      d_weight_grads ? static_cast<uint8_t *>(d_weight_grads) + size_t(g) * w_elems * es : nullptr;
+  if (peer != nullptr) {
+    const size_t count4 = w_elems / 4;
+    const unsigned rgrid = unsigned((count4 + kWuFusedChunk - 1) / kWuFusedChunk);
+    WuPeerArgs pa = *peer;
+    for (int r = 0; r < pa.world; ++r) pa.grads[r] += size_t(g) * count4;
+    pa.chunk_base = g * rgrid;
+    cudaLaunchConfig_t rcfg{};
+    rcfg.gridDim = dim3(rgrid);
+    rcfg.blockDim = dim3(32, kWuReduceLanes);
+    rcfg.stream = stream;
+    rcfg.attrs = pdl;
+    rcfg.numAttrs = 1;
+    PLB_CUDA(cudaLaunchKernelEx(&rcfg, wu_reduce_allreduce_kernel,
+                                reinterpret_cast<const float4 *>(a.partial), a.ksplit, count4, pa,
+                                reinterpret_cast<float4 *>(out32), reinterpret_cast<uint2 *>(out16)));
+  } else if (w_elems % 4 == 0 && (reinterpret_cast<uintptr_t>(out32) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(out16) & 7) == 0) {
+    const size_t count4 = w_elems / 4;
+    const unsigned rgrid = unsigned((count4 + 31) / 32);
+    cudaLaunchConfig_t rcfg{};
+    rcfg.gridDim = dim3(rgrid);
+    rcfg.blockDim = dim3(32, kWuReduceLanes);
+    rcfg.stream = stream;
+    rcfg.attrs = pdl;
+    rcfg.numAttrs = 1;
+    PLB_CUDA(cudaLaunchKernelEx(&rcfg, wu_reduce4_kernel,
+                                reinterpret_cast<const float4 *>(a.partial), a.ksplit, count4,
+                                reinterpret_cast<float4 *>(out32), reinterpret_cast<uint2 *>(out16)));
+  } else {
+    const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
+    wu_reduce_kernel<<<rgrid, 256, 0, stream>>>(a.partial, a.ksplit, w_elems, out32, out16, 0);
+  }
+  PLB_CUDA(cudaGetLastError());
+  return PLB_OK;
+}
+
 // Launches the weight-gradient kernel and the reduction over K splits for every
 // group.  `a.partial` and `a.status` are set by the caller.
+// With `peer` the reduction also adds the gradients of the other ranks
+// (wu_reduce_allreduce_kernel); the caller has checked that the shapes allow it.
 int launchWu(cudaStream_t stream, const plb_conv_params &p, const WuShape &s, const WuArgs &a,
              const void *d_acts, const void *d_out_grads, void *d_weight_grads,
-             float *d_weight_grads_f32, uint64_t *launches) {
+             float *d_weight_grads_f32, uint64_t *launches, const WuPeerArgs *peer = nullptr) {
   const int co = int(p.out_chans_per_group), ci = int(p.in_chans_per_group);
   const int taps = s.KH * s.KW;
   const size_t w_elems = size_t(taps) * co * ci;
@@ -271,27 +334,8 @@ int launchWu(cudaStream_t stream, const plb_conv_params &p, const WuShape &s, co
     cfg.attrs = pdl;
     cfg.numAttrs = 1;
     PLB_CUDA(cudaLaunchKernelEx(&cfg, wu_kernel, tdy, tx, tout, a));
-    float *out32 = d_weight_grads_f32 ? d_weight_grads_f32 + size_t(g) * w_elems : nullptr;
-    uint8_t *out16 =
-        d_weight_grads ? static_cast<uint8_t *>(d_weight_grads) + size_t(g) * w_elems * es : nullptr;
-    if (w_elems % 4 == 0 && (reinterpret_cast<uintptr_t>(out32) & 15) == 0 &&
-        (reinterpret_cast<uintptr_t>(out16) & 7) == 0) {
-      const size_t count4 = w_elems / 4;
-      const unsigned rgrid = unsigned((count4 + 31) / 32);
-      cudaLaunchConfig_t rcfg{};
-      rcfg.gridDim = dim3(rgrid);
-      rcfg.blockDim = dim3(32, kWuReduceLanes);
-      rcfg.stream = stream;
-      rcfg.attrs = pdl;
-      rcfg.numAttrs = 1;
-      PLB_CUDA(cudaLaunchKernelEx(&rcfg, wu_reduce4_kernel,
-                                  reinterpret_cast<const float4 *>(a.partial), a.ksplit, count4,
-                                  reinterpret_cast<float4 *>(out32), reinterpret_cast<uint2 *>(out16)));
-    } else {
-      const int rgrid = int(std::min<size_t>((w_elems + 255) / 256, size_t(148) * 8));
-      wu_reduce_kernel<<<rgrid, 256, 0, stream>>>(a.partial, a.ksplit, w_elems, out32, out16, 0);
-    }
-    PLB_CUDA(cudaGetLastError());
+    if (int rc = launchWuReduce(stream, a, w_elems, g, d_weight_grads, d_weight_grads_f32, peer))
+      return rc;
     if (launches) *launches += 2;
   }
   return PLB_OK;
@@ -497,14 +541,95 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
   if (int rc = scratch(ctx, kSlotOperands, size_t(a.ksplit) * w_elems * sizeof(float), &ws)) return rc;
   a.partial = static_cast<float *>(ws);
 
-  static bool configured[64] = {};
-  if (!configured[ctx->device & 63]) {
-    PLB_CUDA(cudaFuncSetAttribute(wu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    configured[ctx->device & 63] = true;
-  }
+  if (int rc = configureWuKernel(ctx->device)) return rc;
   uint64_t launches = 0;
   if (int rc = launchWu(ctx->stream, *p, s, a, d_acts, d_out_grads, d_weight_grads,
                         d_weight_grads_f32, &launches))
+    return rc;
+  ctx->launches += launches;
+  return PLB_OK;
+}
+
+// Chunks (= blocks of the fused reduction, = flags per sender) of one call.
+static size_t wuPeerChunks(const plb_conv_params &p, const WuShape &s) {
+  const size_t w_elems = size_t(s.KH) * s.KW * p.out_chans_per_group * p.in_chans_per_group;
+  return size_t(p.groups) * ((w_elems / 4 + kWuFusedChunk - 1) / kWuFusedChunk);
+}
+
+uint64_t plb_conv_wu_allreduce_flag_bytes(const plb_conv_params *p) {
+  WuShape s;
+  if (!p || wuShape(*p, &s)) return 0;
+  return uint64_t(wuPeerChunks(*p, s)) * kWuPeerMaxWorld * sizeof(uint32_t);
+}
+
+int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                          const void *d_acts, const void *d_out_grads, int32_t rank, int32_t world,
+                          void *const *d_peer_grads, void *const *d_peer_flags, uint32_t epoch,
+                          void *d_weight_grads, float *d_weight_grads_f32) {
+  if (int rc = activate(ctx)) return rc;
+  if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
+  if (world < 1 || world > kWuPeerMaxWorld || rank < 0 || rank >= world)
+    return fail(PLB_ERR_INVALID_PARAMS, "rank / world size out of range (at most " +
+                                            std::to_string(kWuPeerMaxWorld) + " ranks)");
+  if (!d_peer_grads || !d_peer_flags) return fail(PLB_ERR_INVALID_PARAMS, "null pointer table");
+  if (epoch == 0 || (epoch & 0x80000000u))
+    return fail(PLB_ERR_INVALID_PARAMS, "steps are numbered from 1 to 2^31 - 1 (flags start at zero)");
+  const char *other = "; use plb_conv_wu and plb_allreduce_f32_p2p for this layer";
+  WuShape s;
+  if (int rc = wuShape(*p, &s)) return rc;   // 1-D / 2-D, half, no input dilation / flip, plain kernel
+  const int co = int(p->out_chans_per_group), ci = int(p->in_chans_per_group);
+  const size_t w_elems = size_t(s.KH) * s.KW * co * ci;
+  if (p->groups == 0 || w_elems == 0) return PLB_OK;
+  if (ci % 8 != 0 || co % 8 != 0)
+    return fail(PLB_ERR_UNSUPPORTED,
+                std::string("the fused weight update needs channel counts that are multiples of 8") + other);
+  // all blocks of the reduction wait for their peers' blocks: keep the grid resident
+  if (wuPeerChunks(*p, s) / p->groups > size_t(ctx->sm_count) * 4)
+    return fail(PLB_ERR_UNSUPPORTED,
+                std::string("weight gradient too large for the fused reduction over ranks") + other);
+  WuPeerArgs pa{};
+  for (int r = 0; r < world; ++r) {
+    if (!d_peer_grads[r] || !d_peer_flags[r]) return fail(PLB_ERR_INVALID_PARAMS, "null peer pointer");
+    if ((reinterpret_cast<uintptr_t>(d_peer_grads[r]) & 15) != 0)
+      return fail(PLB_ERR_INVALID_PARAMS, "peer gradient buffers must be 16-byte aligned");
+    pa.grads[r] = static_cast<float4 *>(d_peer_grads[r]);
+    pa.flags[r] = static_cast<uint32_t *>(d_peer_flags[r]);
+  }
+  if ((reinterpret_cast<uintptr_t>(d_weight_grads_f32) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(d_weight_grads) & 7) != 0)
+    return fail(PLB_ERR_INVALID_PARAMS, "outputs must be 16-byte (fp32) / 8-byte (half) aligned");
+  pa.rank = rank;
+  pa.world = world;
+  pa.epoch = epoch;
+  pa.status = ctx->d_status;
+  WuArgs a{};
+  a.status = ctx->d_status;
+  a.trace = ctx->trace;
+  if (int rc = configureWuKernel(ctx->device)) return rc;
+  uint64_t launches = 0;
+  if (p->batch == 0 || s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) {
+    // this rank has no share of the batch: it contributes zeros, through one
+    // split of zero partial sums, so that the peers still get its flags
+    planWu(*p, s, ctx->sm_count, 1, opt ? opt->plan_flags : 0, &a, nullptr);
+    a.ksplit = 1;
+    void *ws = nullptr;
+    if (int rc = scratch(ctx, kSlotOperands, w_elems * sizeof(float), &ws)) return rc;
+    PLB_CUDA(cudaMemsetAsync(ws, 0, w_elems * sizeof(float), ctx->stream));
+    a.partial = static_cast<float *>(ws);
+    for (unsigned g = 0; g < p->groups; ++g) {
+      if (int rc = launchWuReduce(ctx->stream, a, w_elems, g, d_weight_grads, d_weight_grads_f32, &pa))
+        return rc;
+      ++launches;
+    }
+    ctx->launches += launches;
+    return PLB_OK;
+  }
+  planWu(*p, s, ctx->sm_count, opt ? opt->split_k : 0, opt ? opt->plan_flags : 0, &a, nullptr);
+  void *ws = nullptr;
+  if (int rc = scratch(ctx, kSlotOperands, size_t(a.ksplit) * w_elems * sizeof(float), &ws)) return rc;
+  a.partial = static_cast<float *>(ws);
+  if (int rc = launchWu(ctx->stream, *p, s, a, d_acts, d_out_grads, d_weight_grads, d_weight_grads_f32,
+                        &launches, &pa))
     return rc;
   ctx->launches += launches;
   return PLB_OK;
@@ -537,6 +662,7 @@ struct StaticScratch {
   bool ready = false;
   float *partial = nullptr;
   int *status = nullptr;
+  int sm_count = 0;
 };
 StaticScratch g_static_scratch[64];
 std::mutex g_static_scratch_mutex;
@@ -550,7 +676,7 @@ int staticScratchFor(int device, StaticScratch *out) {
     void *scratch_ptr = nullptr, *status_ptr = nullptr;
     PLB_CUDA(cudaGetSymbolAddress(&scratch_ptr, g_wu_static_scratch));
     PLB_CUDA(cudaGetSymbolAddress(&status_ptr, g_wu_static_status));
-    PLB_CUDA(cudaFuncSetAttribute(wu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    PLB_CUDA(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, device));
     s.partial = static_cast<float *>(scratch_ptr);
     s.status = static_cast<int *>(status_ptr);
     s.ready = true;
@@ -587,8 +713,15 @@ extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const p
     const void *result = d_weight_grads ? d_weight_grads : static_cast<const void *>(d_weight_grads_f32);
     if (int rc = checkConvRequest(*p, true, d_acts, n_in, d_out_grads, n_out, result, n_w)) return rc;
   }
+  // This entry point runs none of plb_conv_wu's preparatory passes (they need
+  // scratch memory of their own): say so instead of failing inside the launch.
+  if (ci % 8 != 0 || co % 8 != 0)
+    return fail(PLB_ERR_UNSUPPORTED,
+                "plb_conv_wu_static_scratch needs channel counts per group that are multiples of 8 "
+                "(plb_conv_wu pads other counts in scratch memory); use plb_conv_wu");
   StaticScratch scratch;
   if (int rc = staticScratchFor(device, &scratch)) return rc;
+  if (int rc = configureWuKernel(device)) return rc;
   const size_t es = 2;
   if (p->batch == 0 || s.OHc <= 0 || s.OWc <= 0 || s.He <= 0 || s.We <= 0) {
     const size_t n = size_t(p->groups) * w_elems;
@@ -597,11 +730,8 @@ extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const p
     PLB_CUDA(cudaStreamSynchronize(stream));
     return PLB_OK;
   }
-  cudaDeviceProp prop;
-  PLB_CUDA(cudaGetDeviceProperties(&prop, device));
   WuArgs a{};
-  planWu(*p, s, prop.multiProcessorCount, opt ? opt->split_k : 0, opt ? opt->plan_flags : 0, &a,
-         nullptr);
+  planWu(*p, s, scratch.sm_count, opt ? opt->split_k : 0, opt ? opt->plan_flags : 0, &a, nullptr);
   // as many K splits as the fixed scratch can hold
   const int max_split = int(kStaticScratchBytes / (w_elems * sizeof(float)));
   a.ksplit = std::max(1, std::min(a.ksplit, max_split));

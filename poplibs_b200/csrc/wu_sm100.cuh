@@ -432,4 +432,138 @@ wu_reduce4_kernel(const float4 *__restrict__ partial, int ksplit, size_t count4,
   }
 }
 
+// ---- split-K reduction fused with the sum over ranks -------------------------------
+// Batch-sharded weight update on several GPUs: the split-K reduction above and
+// the all-reduce of the per-rank gradients in ONE kernel.  A block reduces the
+// K splits of a chunk of kWuFusedChunk float4 sums exactly as wu_reduce4_kernel
+// does, writes them into this rank's peer-addressable gradient buffer and at
+// once tells every peer "chunk b of rank r is complete" (a flag per chunk and
+// sender in the receiver's flag area, carrying the step number).  It then
+// waits, with a cycle budget, for the same chunk's flag from every peer, reads
+// the peers' chunk with plain peer loads, adds the ranks' sums in rank order
+// (every rank forms identical bits) and writes the fp32 gradient of the whole
+// batch and / or its cast.  The exchange of a chunk overlaps the reduction of
+// the following ones, so the collective costs little more than one NVLink
+// round trip after the last chunk instead of a kernel launch, a flag round
+// for the whole vector and the transfer.
+//
+// Block b of a rank waits only for block b of the peers, and only after it has
+// sent its own flag; blocks are dispatched in index order, so a block's
+// predecessors on every GPU have all sent theirs.  The host caps the grid at
+// what is resident at once anyway.  No multicast, no TMA on peer memory.
+constexpr int kWuFusedGroups = 4;                     // groups of 32 float4 per block
+constexpr int kWuFusedChunk = 32 * kWuFusedGroups;    // float4 sums per block
+constexpr int kWuPeerMaxWorld = 16;
+constexpr int kStatusWuPeerTimeout = 5;  // a peer's chunk flag did not arrive within the budget
+
+struct WuPeerArgs {
+  float4 *grads[kWuPeerMaxWorld];      // every rank's gradient buffer (this group's part)
+  uint32_t *flags[kWuPeerMaxWorld];    // every rank's flag area: [chunk][sender] words
+  int rank, world;
+  uint32_t epoch;       // step number, 1, 2, 3, ...; flags only grow
+  uint32_t chunk_base;  // first chunk index of this launch (groups follow one another)
+  int *status;
+};
+
+__global__ void __launch_bounds__(32 * kWuReduceLanes)
+wu_reduce_allreduce_kernel(const float4 *__restrict__ partial, int ksplit, size_t count4,
+                           const WuPeerArgs pa, float4 *__restrict__ out_f32,
+                           uint2 *__restrict__ out_half) {
+  __shared__ float4 part[kWuReduceLanes][32];
+  __shared__ int ok;
+  const int tid = threadIdx.y * 32 + threadIdx.x;
+  if (tid == 0) ok = 1;
+  pdl_launch_dependents();
+  pdl_wait();  // the partial sums come from the previous kernel in the stream
+  float4 *mine = pa.grads[pa.rank];
+  for (int j = 0; j < kWuFusedGroups; ++j) {
+    const size_t i = (blockIdx.x * size_t(kWuFusedGroups) + j) * 32 + threadIdx.x;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < count4) {
+#pragma unroll 4
+      for (int k = threadIdx.y; k < ksplit; k += kWuReduceLanes) {
+        const float4 v = partial[size_t(k) * count4 + i];
+        s.x += v.x;
+        s.y += v.y;
+        s.z += v.z;
+        s.w += v.w;
+      }
+    }
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && i < count4) {
+#pragma unroll
+      for (int y = 1; y < kWuReduceLanes; ++y) {
+        const float4 v = part[y][threadIdx.x];
+        s.x += v.x;
+        s.y += v.y;
+        s.z += v.z;
+        s.w += v.w;
+      }
+      mine[i] = s;
+    }
+    __syncthreads();
+  }
+  // this rank's chunk is complete: publish it, then wait for the peers' chunk
+  __threadfence_system();
+  __syncthreads();
+  const uint32_t chunk = pa.chunk_base + blockIdx.x;
+  if (tid < pa.world && tid != pa.rank) {
+    uint32_t *theirs = pa.flags[tid] + size_t(chunk) * kWuPeerMaxWorld + pa.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(pa.epoch) : "memory");
+    const uint32_t *from = pa.flags[pa.rank] + size_t(chunk) * kWuPeerMaxWorld + tid;
+    const long long start = clock64();
+    while (true) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(from) : "memory");
+      if (int32_t(seen - pa.epoch) >= 0) break;
+      if (clock64() - start > kWaitCycleLimit) {
+        atomicCAS(pa.status, kStatusOk, kStatusWuPeerTimeout);
+        ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!ok) return;
+  // sum over ranks, rank order; a thread's peer loads are all in flight together
+  if (tid < kWuFusedChunk) {
+    const size_t i = blockIdx.x * size_t(kWuFusedChunk) + tid;
+    if (i < count4) {
+      float4 v[kWuPeerMaxWorld];
+#pragma unroll
+      for (int r = 0; r < kWuPeerMaxWorld; ++r) {
+        if (r < pa.world) {
+          const float4 *src = pa.grads[r] + i;
+          if (r == pa.rank) {
+            v[r] = *src;
+          } else {
+            // from the peer, never from a stale line of this GPU's caches
+            asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(v[r].x), "=f"(v[r].y), "=f"(v[r].z), "=f"(v[r].w)
+                         : "l"(src)
+                         : "memory");
+          }
+        }
+      }
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < kWuPeerMaxWorld; ++r) {
+        if (r < pa.world) {
+          s.x += v[r].x;
+          s.y += v[r].y;
+          s.z += v[r].z;
+          s.w += v[r].w;
+        }
+      }
+      if (out_f32) out_f32[i] = s;
+      if (out_half) {
+        const __half2 lo = __floats2half2_rn(s.x, s.y), hi = __floats2half2_rn(s.z, s.w);
+        out_half[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                                 *reinterpret_cast<const uint32_t *>(&hi));
+      }
+    }
+  }
+}
+
 }  // namespace plb

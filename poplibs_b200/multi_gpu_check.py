@@ -55,7 +55,9 @@ def main() -> int:
     x, w = pm1(batch, 12, 12, 64).to(device), pm1(3, 3, 72, 64).to(device)
     dy = pm1(batch, 12, 12, 72).to(device)
     full = capi.ConvParams.make(**kw)
-    sh = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True)
+    sh = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, allreduce_mode="oneshot")
+    sh_rs = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, allreduce_mode="rs")
+    sh_fu = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, allreduce_mode="fused")
     b, e = sh.begin, sh.end
     with torch.cuda.stream(stream):
         # unsharded reference (every rank computes it; cheap)
@@ -72,8 +74,12 @@ def main() -> int:
         sh.bwd(dy[b:e].contiguous(), w, dx)
         dw16 = torch.empty(3, 3, 72, 64, dtype=torch.float16, device=device)
         dw32 = torch.empty(3, 3, 72, 64, dtype=torch.float32, device=device)
+        rs16, rs32 = torch.empty_like(dw16), torch.empty_like(dw32)
+        fu16, fu32 = torch.empty_like(dw16), torch.empty_like(dw32)
         for _ in range(3):                 # several steps: both buffer halves, growing epochs
             sh.wu(x[b:e].contiguous(), dy[b:e].contiguous(), dw16, dw32)
+            sh_rs.wu(x[b:e].contiguous(), dy[b:e].contiguous(), rs16, rs32)
+            sh_fu.wu(x[b:e].contiguous(), dy[b:e].contiguous(), fu16, fu32)
         # the same sum by the process group's all-reduce
         local = torch.empty_like(dw32)
         ctx.conv_wu(sh.params, x[b:e].contiguous(), dy[b:e].contiguous(), None, local)
@@ -85,22 +91,28 @@ def main() -> int:
     report("weight gradient over peer memory equals the unsharded gradient", torch.equal(dw32, dw_ref))
     report("weight gradient over peer memory equals the NCCL sum", torch.equal(dw32, local))
     report("half cast of the gradient", torch.equal(dw16, dw_ref.half()))
+    report("reduce-scatter + all-gather form: same bits, fp32 and half",
+           torch.equal(rs32, dw32) and torch.equal(rs16, dw16))
     first = dw32.clone()
     dist.broadcast(first, 0)
     report("all ranks hold identical bits", torch.equal(first, dw32))
 
     # the same with the all-reduce on a stream of its own, several steps in flight
-    sho = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, overlap_allreduce=True)
-    outs = [(torch.empty_like(dw16), torch.empty_like(dw32)) for _ in range(5)]
-    with torch.cuda.stream(stream):
-        for o16, o32 in outs:
-            sho.wu(x[b:e].contiguous(), dy[b:e].contiguous(), o16, o32)
-        sho.peer.wait()
-    ctx.synchronize()
-    sho.peer.synchronize()
-    torch.cuda.synchronize()
-    report("overlapped all-reduce, five steps in flight",
-           all(torch.equal(o32, dw_ref) and torch.equal(o16, dw_ref.half()) for o16, o32 in outs))
+    report("sum over ranks fused into the split-K reduction: same bits, fp32 and half",
+           torch.equal(fu32, dw32) and torch.equal(fu16, dw16))
+    for mode in ("oneshot", "rs"):
+        sho = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, overlap_allreduce=True,
+                                   allreduce_mode=mode)
+        outs = [(torch.empty_like(dw16), torch.empty_like(dw32)) for _ in range(5)]
+        with torch.cuda.stream(stream):
+            for o16, o32 in outs:
+                sho.wu(x[b:e].contiguous(), dy[b:e].contiguous(), o16, o32)
+            sho.peer.wait()
+        ctx.synchronize()
+        sho.peer.synchronize()
+        torch.cuda.synchronize()
+        report(f"all-reduce ({mode}) on a stream of its own, five steps enqueued",
+               all(torch.equal(o32, dw_ref) and torch.equal(o16, dw_ref.half()) for o16, o32 in outs))
 
     m, k, n = 64 * world + 32, 256, 192
     a, bm = pm1(m, k).to(device), pm1(k, n).to(device)

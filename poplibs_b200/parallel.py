@@ -61,8 +61,21 @@ class PeerAllReduce:
     The symmetric buffer comes from torch.distributed's symmetric memory (one
     process per GPU, peers mapped through CUDA IPC / fabric handles)."""
 
-    def __init__(self, ctx: capi.Context, count: int, group=None, overlap: bool = False):
-        """With overlap=True the all-reduce kernel runs on a stream (and library
+    #: inbound bytes per rank ((world - 1) x the vector) from which the
+    #: reduce-scatter + all-gather kernel is used.  Below it every rank simply
+    #: reads all peers' vectors: the second flag round and the fenced peer stores
+    #: cost more than the traffic they save (measured on a 590 KB gradient: 60.2
+    #: against 72.2 us per step on 2 GPUs, 69.0 against 76.1 us on 8)
+    RS_MIN_BYTES = 8 << 20
+
+    def __init__(self, ctx: capi.Context, count: int, group=None, overlap: bool = False,
+                 mode: str = "auto"):
+        """mode: "oneshot" (plb_allreduce_f32_p2p: one flag round, every rank
+        reads all N vectors), "rs" (plb_allreduce_f32_p2p_rs: each rank sums one
+        slice and stores it to all, two flag rounds, 1/N of the traffic) or
+        "auto" (rs from RS_MIN_BYTES of inbound traffic on).
+
+        With overlap=True the all-reduce kernel runs on a stream (and library
         context) of its own: it is ordered after the kernels that fill input()
         by an event, and the next step's kernels on the main stream do not wait
         for it -- the exchange over NVLink then hides behind the next layer's
@@ -76,8 +89,14 @@ class PeerAllReduce:
         group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         device = torch.device("cuda", torch.cuda.current_device())
-        # two halves, used on alternate steps: a peer may still read the last one
-        self.buf = symm_mem.empty((2, count), dtype=torch.float32, device=device)
+        if mode not in ("auto", "oneshot", "rs"):
+            raise ValueError(f"unknown all-reduce mode {mode!r}")
+        big = (self.world - 1) * count * 4 >= self.RS_MIN_BYTES
+        self.mode = ("rs" if big else "oneshot") if mode == "auto" else mode
+        # rows 0, 1: input halves, used on alternate steps (in the one-shot form a
+        # peer may still read the last one); row 2: the result buffer of the
+        # reduce-scatter form, written by the peers
+        self.buf = symm_mem.empty((3, count), dtype=torch.float32, device=device)
         self.handle = symm_mem.rendezvous(self.buf, group)
         need = capi.lib().plb_allreduce_p2p_signal_bytes(self.world)
         if self.handle.signal_pad_size < need:
@@ -89,6 +108,7 @@ class PeerAllReduce:
         # per half: the view to fill and every rank's address of that half
         self.halves = [self.buf[0], self.buf[1]]
         self.half_ptrs = [[p + h * count * 4 for p in self.buffer_ptrs] for h in (0, 1)]
+        self.result_ptrs = [p + 2 * count * 4 for p in self.buffer_ptrs]
         if overlap:
             self.main_stream = torch.cuda.ExternalStream(ctx.stream, device=device)
             self.comm_stream = torch.cuda.Stream(device=device)
@@ -99,9 +119,17 @@ class PeerAllReduce:
     def input(self):
         """The buffer (a torch view, `count` floats) this rank must fill for the next call."""
         half = (self.epoch + 1) & 1
-        if self.overlap and self.done[half] is not None:
-            # the all-reduce of two steps ago read this half: it must have finished
-            self.main_stream.wait_event(self.done[half])
+        if self.overlap:
+            # This rank's all-reduce of step e completing only proves that the
+            # peers have STARTED theirs.  That a peer has finished reading the
+            # half of step e - 1 is known once its flag of step e has arrived,
+            # i.e. when this rank's all-reduce of step e (the latest) is done; in
+            # the reduce-scatter form the second flag round says it directly.
+            # So the main stream waits for the latest all-reduce before it may
+            # overwrite the other half.
+            for ev in self.done:
+                if ev is not None:
+                    self.main_stream.wait_event(ev)
         return self.halves[half]
 
     def run(self, out_f32=None, out_half=None):
@@ -111,14 +139,20 @@ class PeerAllReduce:
         self.epoch += 1
         half = self.epoch & 1
         ptrs = self.half_ptrs[half]
+
+        def launch(c):
+            if self.mode == "rs":
+                c.allreduce_f32_p2p_rs(self.rank, self.world, ptrs, self.result_ptrs, self.signal_ptrs,
+                                       self.epoch, self.count, out_f32, out_half)
+            else:
+                c.allreduce_f32_p2p(self.rank, self.world, ptrs, self.signal_ptrs, self.epoch, self.count,
+                                    out_f32, out_half)
         if not self.overlap:
-            self.ctx.allreduce_f32_p2p(self.rank, self.world, ptrs, self.signal_ptrs, self.epoch, self.count,
-                                       out_f32, out_half)
+            launch(self.ctx)
             return
         self.filled[half].record(self.main_stream)
         self.comm_stream.wait_event(self.filled[half])
-        self.comm_ctx.allreduce_f32_p2p(self.rank, self.world, ptrs, self.signal_ptrs, self.epoch, self.count,
-                                        out_f32, out_half)
+        launch(self.comm_ctx)
         if self.done[half] is None:
             self.done[half] = torch.cuda.Event()
         self.done[half].record(self.comm_stream)
@@ -134,12 +168,57 @@ class PeerAllReduce:
             self.comm_ctx.synchronize()
 
 
+class FusedPeerWeightUpdate:
+    """Buffers of plb_conv_wu_allreduce: the weight-update pass whose split-K
+    reduction kernel also adds the peers' gradients, chunk by chunk, over
+    NVLink peer memory.  Holds two peer-addressable gradient buffers (used on
+    alternate steps: a peer may still be reading the previous step's) and the
+    per-chunk flag area, all in torch.distributed's symmetric memory."""
+
+    def __init__(self, ctx: capi.Context, params: capi.ConvParams, count: int, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.ctx, self.params, self.count = ctx, params, count
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        flag_bytes = int(capi.lib().plb_conv_wu_allreduce_flag_bytes(params))
+        if flag_bytes == 0 or count % 4:
+            raise ValueError("this layer has no fused weight update (see plb_conv_wu_allreduce)")
+        device = torch.device("cuda", torch.cuda.current_device())
+        self.grads = symm_mem.empty((2, count), dtype=torch.float32, device=device)
+        grads_handle = symm_mem.rendezvous(self.grads, group)
+        self.flags = symm_mem.empty((flag_bytes // 4,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        flags_handle = symm_mem.rendezvous(self.flags, group)
+        torch.cuda.synchronize()
+        dist.barrier(group)          # every rank's flags are zero before anyone's first step
+        self._handles = (grads_handle, flags_handle)
+        base = [int(v) for v in grads_handle.buffer_ptrs]
+        self.grad_ptrs = [[v + h * count * 4 for v in base] for h in (0, 1)]
+        self.flag_ptrs = [int(v) for v in flags_handle.buffer_ptrs]
+        self.epoch = 0
+        self.mode, self.overlap = "fused", False
+
+    def wu(self, x_local, dy_local, dw, dw_f32, opt=None):
+        self.epoch += 1
+        self.ctx.conv_wu_allreduce(self.params, x_local, dy_local, self.rank, self.world,
+                                   self.grad_ptrs[self.epoch & 1], self.flag_ptrs, self.epoch, dw, dw_f32,
+                                   opt=opt)
+
+    def wait(self):
+        pass
+
+    def synchronize(self):
+        pass
+
+
 class ShardedConv:
     """One rank's part of a batch-sharded convolution layer."""
 
     def __init__(self, ctx: capi.Context, make_kwargs: dict, rank: int = 0, world: int = 1,
                  group=None, opt: Optional[capi.ConvOptions] = None, peer_allreduce: bool = False,
-                 overlap_allreduce: bool = False):
+                 overlap_allreduce: bool = False, allreduce_mode: str = "auto"):
         self.ctx, self.rank, self.world, self.group, self.opt = ctx, rank, world, group, opt
         self.params, self.begin, self.end = local_conv_params(make_kwargs, rank, world)
         self.global_batch = int(make_kwargs["batch"])
@@ -150,7 +229,20 @@ class ShardedConv:
             count = int(p.groups) * int(p.out_chans_per_group) * int(p.in_chans_per_group)
             for i in range(p.num_field_dims):
                 count *= int(p.kernel[i])
-            self.peer = PeerAllReduce(ctx, count, group, overlap=overlap_allreduce)
+            # "fused" (and "auto" where the layer allows it): the sum over ranks
+            # happens inside the weight update's own reduction kernel
+            self.fused = None
+            if allreduce_mode in ("auto", "fused") and not overlap_allreduce:
+                try:
+                    self.fused = FusedPeerWeightUpdate(ctx, p, count, group)
+                except ValueError:
+                    if allreduce_mode == "fused":
+                        raise
+            if self.fused is not None:
+                self.peer = self.fused
+            else:
+                self.peer = PeerAllReduce(ctx, count, group, overlap=overlap_allreduce,
+                                          mode="auto" if allreduce_mode == "fused" else allreduce_mode)
 
     def fwd(self, x_local, w, y_local, bias=None):
         if self.params.batch:
@@ -164,6 +256,9 @@ class ShardedConv:
         """dw (weights' type) and dw_f32 receive the gradient of the WHOLE batch
         on every rank.  dw_f32 is a torch tensor on the context's device."""
         import torch
+        if self.peer is not None and self.peer.mode == "fused":
+            self.peer.wu(x_local, dy_local, dw, dw_f32, opt=self.opt)
+            return
         if self.peer is not None:
             # local gradient straight into this step's half of the symmetric
             # buffer; one kernel then sums all ranks' halves and casts

@@ -563,6 +563,119 @@ def test_allreduce_over_peer_memory_on_one_gpu(gpu_ctx):
         ctx.allreduce_f32_p2p(0, 1, [bufs[0].data_ptr()], [pads[0].data_ptr()], 0, count, out32, None)
 
 
+def test_allreduce_reduce_scatter_form_on_one_gpu(gpu_ctx):
+    """plb_allreduce_f32_p2p_rs with all "ranks'" buffers on this GPU and the
+    peers' flags of both rounds already set.  Each emulated rank is run in turn:
+    it must add its own slice in rank order and store it into every rank's
+    result buffer; after all have run once, a second round must give every rank
+    the complete sum (fp32 and cast).  Then a step whose peers never signal: the
+    bounded wait runs out and is reported, the context stays usable."""
+    import torch
+    ctx = T.context()
+    world, count = 3, 4 * 10007            # slices of unequal length
+    words = capi.lib().plb_allreduce_p2p_signal_bytes(world) // 4
+    g = torch.Generator().manual_seed(5)
+    ins = [torch.randn(count, generator=g).cuda() for _ in range(world)]
+    res = [torch.zeros(count, device="cuda") for _ in range(world)]
+    pads = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(world)]
+    want = (ins[0] + ins[1]) + ins[2]
+    out32 = [torch.empty(count, device="cuda") for _ in range(world)]
+    out16 = [torch.empty(count, device="cuda", dtype=torch.float16) for _ in range(world)]
+    flag1, flag2 = 32, 48
+
+    def run(rank, epoch, o32, o16):
+        for peer in range(world):
+            if peer != rank:
+                pads[rank][flag1 + peer] = epoch
+                pads[rank][flag2 + peer] = epoch
+        torch.cuda.synchronize()
+        ctx.allreduce_f32_p2p_rs(rank, world, [t.data_ptr() for t in ins], [t.data_ptr() for t in res],
+                                 [p.data_ptr() for p in pads], epoch, count, o32, o16)
+        ctx.synchronize()
+    for rank in range(world):
+        run(rank, 1, out32[rank], out16[rank])
+    # every result buffer now holds every owner's slice
+    for r in range(world):
+        assert torch.equal(res[r], want), f"result buffer of rank {r}"
+    assert torch.equal(out32[world - 1], want)      # the last one already saw all slices
+    for rank in range(world):
+        run(rank, 2, out32[rank], None if rank == 0 else out16[rank])
+        assert torch.equal(out32[rank], want)
+        if rank:
+            assert torch.equal(out16[rank], want.half())
+        for peer in range(world):
+            if peer != rank:
+                assert int(pads[peer][flag1 + rank]) == 2 and int(pads[peer][flag2 + rank]) == 2, "flag not sent"
+    # epoch 3 on rank 1: nobody signals -> reported, not hung
+    ctx.allreduce_f32_p2p_rs(1, world, [t.data_ptr() for t in ins], [t.data_ptr() for t in res],
+                             [p.data_ptr() for p in pads], 3, count, out32[1], None)
+    with pytest.raises(capi.PlbError):
+        ctx.synchronize()
+    # the context still works (a single rank is its own sum)
+    solo_pad = torch.zeros(words, dtype=torch.int32, device="cuda")
+    ctx.allreduce_f32_p2p_rs(0, 1, [ins[0].data_ptr()], [res[0].data_ptr()], [solo_pad.data_ptr()], 1, count,
+                             out32[0], None)
+    ctx.synchronize()
+    assert torch.equal(out32[0], ins[0])
+
+
+def test_weight_update_fused_with_sum_over_ranks_on_one_gpu(gpu_ctx):
+    """plb_conv_wu_allreduce with the "peers'" gradient buffers on this GPU,
+    already filled, and their chunk flags already set: the call must leave this
+    rank's own gradient in its buffer, flag every chunk to every peer and
+    return own + peers in rank order (fp32 and cast), for one and for several
+    groups.  Then a step whose peers never signal: reported, not hung."""
+    import torch
+    ctx = T.context()
+    world, rank = 3, 1
+    r = T.rng(11)
+    for kw in (conv_case(6, [12, 12], [3, 3], 64, 72, padding=1),
+               conv_case(4, [10, 10], [3, 3], 16, 24, padding=1, groups=3)):
+        p = capi.ConvParams.make(**kw)
+        g = p.groups
+        x = torch.from_numpy(T.binary_half(r, (p.batch, *kw["field"], g * p.in_chans_per_group))).cuda()
+        dy = torch.from_numpy(T.binary_half(r, (p.batch, *kw["field"], g * p.out_chans_per_group))).cuda()
+        shape = (g, 3, 3, p.out_chans_per_group, p.in_chans_per_group)
+        count = int(np.prod(shape))
+        local = torch.empty(shape, device="cuda")
+        ctx.conv_wu(p, x, dy, None, local)
+        ctx.synchronize()
+        gen = torch.Generator().manual_seed(4)
+        bufs = [torch.randint(-64, 64, (count,), generator=gen).float().cuda() for _ in range(world)]
+        words = int(capi.lib().plb_conv_wu_allreduce_flag_bytes(p)) // 4
+        assert words > 0
+        flags = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(world)]
+        flags[rank].fill_(1)                      # "all peers' chunks of step 1 have arrived"
+        out32 = torch.empty(shape, device="cuda")
+        out16 = torch.empty(shape, device="cuda", dtype=torch.float16)
+        torch.cuda.synchronize()
+        ctx.conv_wu_allreduce(p, x, dy, rank, world, [b.data_ptr() for b in bufs],
+                              [f.data_ptr() for f in flags], 1, out16, out32)
+        ctx.synchronize()
+        assert torch.equal(bufs[rank].view(shape), local), "own gradient not left in the peer buffer"
+        want = ((bufs[0] + bufs[1]) + bufs[2]).view(shape)
+        assert torch.equal(out32, want)
+        assert torch.equal(out16, want.half())
+        chunks = words // 16
+        for peer in range(world):
+            if peer != rank:
+                sent = flags[peer].view(chunks, 16)[:, rank]
+                assert bool((sent == 1).all()), "a chunk flag was not sent"
+    # step 2: nobody signals -> the bounded wait runs out and is reported
+    ctx.conv_wu_allreduce(p, x, dy, rank, world, [b.data_ptr() for b in bufs], [f.data_ptr() for f in flags],
+                          2, None, out32)
+    with pytest.raises(capi.PlbError):
+        ctx.synchronize()
+    # the context still works, and a single rank is its own sum
+    ctx.conv_wu_allreduce(p, x, dy, 0, 1, [bufs[0].data_ptr()], [flags[0].data_ptr()], 1, None, out32)
+    ctx.synchronize()
+    assert torch.equal(out32, local)
+    # layers that need a preparatory pass are refused with a pointer to the two-call form
+    q = capi.ConvParams.make(**conv_case(2, [8, 8], [3, 3], 12, 20, padding=1))
+    with pytest.raises(capi.PlbError):
+        ctx.conv_wu_allreduce(q, x, dy, 0, 1, [bufs[0].data_ptr()], [flags[0].data_ptr()], 1, None, out32)
+
+
 def test_small_channel_stem_layers(gpu_ctx):
     # 3-channel inputs go through the space-to-depth path
     for kw in (conv_case(2, [18, 22], [7, 7], 3, 64, padding=3, stride=2),
