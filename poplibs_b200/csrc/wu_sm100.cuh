@@ -469,50 +469,80 @@ __global__ void __launch_bounds__(32 * kWuReduceLanes)
 wu_reduce_allreduce_kernel(const float4 *__restrict__ partial, int ksplit, size_t count4,
                            const WuPeerArgs pa, float4 *__restrict__ out_f32,
                            uint2 *__restrict__ out_half) {
-  __shared__ float4 part[kWuReduceLanes][32];
+  __shared__ float4 part[kWuReduceLanes][kWuFusedGroups][32];
   __shared__ int ok;
   const int tid = threadIdx.y * 32 + threadIdx.x;
   if (tid == 0) ok = 1;
   pdl_launch_dependents();
   pdl_wait();  // the partial sums come from the previous kernel in the stream
   float4 *mine = pa.grads[pa.rank];
-  for (int j = 0; j < kWuFusedGroups; ++j) {
-    const size_t i = (blockIdx.x * size_t(kWuFusedGroups) + j) * 32 + threadIdx.x;
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (i < count4) {
-#pragma unroll 4
-      for (int k = threadIdx.y; k < ksplit; k += kWuReduceLanes) {
-        const float4 v = partial[size_t(k) * count4 + i];
-        s.x += v.x;
-        s.y += v.y;
-        s.z += v.z;
-        s.w += v.w;
-      }
-    }
-    part[threadIdx.y][threadIdx.x] = s;
-    __syncthreads();
-    if (threadIdx.y == 0 && i < count4) {
+  // Lane y adds splits y, y + lanes, ... of the block's kWuFusedGroups groups of
+  // 32 sums side by side (one accumulator per group, so that the loads of all
+  // groups are in flight together); then thread (x, j) adds the lanes' sums of
+  // group j in lane order: the same order of additions as wu_reduce4_kernel.
+  const size_t i0 = blockIdx.x * size_t(kWuFusedChunk) + threadIdx.x;
+  float4 s[kWuFusedGroups];
 #pragma unroll
-      for (int y = 1; y < kWuReduceLanes; ++y) {
-        const float4 v = part[y][threadIdx.x];
-        s.x += v.x;
-        s.y += v.y;
-        s.z += v.z;
-        s.w += v.w;
-      }
-      mine[i] = s;
+  for (int j = 0; j < kWuFusedGroups; ++j) s[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+  for (int k = threadIdx.y; k < ksplit; k += kWuReduceLanes) {
+    float4 v[kWuFusedGroups];
+#pragma unroll
+    for (int j = 0; j < kWuFusedGroups; ++j) {
+      const size_t i = i0 + size_t(j) * 32;
+      v[j] = i < count4 ? partial[size_t(k) * count4 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kWuFusedGroups; ++j) {
+      s[j].x += v[j].x;
+      s[j].y += v[j].y;
+      s[j].z += v[j].z;
+      s[j].w += v[j].w;
+    }
   }
-  // this rank's chunk is complete: publish it, then wait for the peers' chunk
-  __threadfence_system();
+#pragma unroll
+  for (int j = 0; j < kWuFusedGroups; ++j) part[threadIdx.y][j][threadIdx.x] = s[j];
   __syncthreads();
+  if (threadIdx.y < kWuFusedGroups) {
+    const int j = threadIdx.y;
+    const size_t i = i0 + size_t(j) * 32;
+    float4 t = part[0][j][threadIdx.x];
+#pragma unroll
+    for (int y = 1; y < kWuReduceLanes; ++y) {
+      const float4 v = part[y][j][threadIdx.x];
+      t.x += v.x;
+      t.y += v.y;
+      t.z += v.z;
+      t.w += v.w;
+    }
+    if (i < count4) mine[i] = t;
+  }
+  __syncthreads();
+  // This rank's chunk is complete; the barrier above orders every thread's
+  // stores before the flag-sending threads.  Publishing: the chunk lies in THIS
+  // GPU's memory and the peers read it through this GPU's L2, the point of
+  // coherence for that memory, so it is enough that the stores have reached L2
+  // before the flag leaves: a device-scope fence (cumulative over the barrier),
+  // then a plain system-scope store of the flag into the peer's memory.  A
+  // system-scope release instead also waits for every access this SM has in
+  // flight over NVLink (other blocks' peer loads and flag stores): measured at
+  // 1.5 to 7.7 us per block against 0.6 us, 63.4 against 56.9 us per step on
+  // two GPUs.  -DPLB_STRICT_SYSTEM_FENCE builds the formally scoped form.
   const uint32_t chunk = pa.chunk_base + blockIdx.x;
   if (tid < pa.world && tid != pa.rank) {
     uint32_t *theirs = pa.flags[tid] + size_t(chunk) * kWuPeerMaxWorld + pa.rank;
+#ifdef PLB_STRICT_SYSTEM_FENCE
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(pa.epoch) : "memory");
+#else
+    __threadfence();
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(pa.epoch) : "memory");
+#endif
     const uint32_t *from = pa.flags[pa.rank] + size_t(chunk) * kWuPeerMaxWorld + tid;
     const long long start = clock64();
+
+    // (acquire loads: a relaxed poll followed by a system-scope fence was
+    // measured slower, the fence also waits for the flag store just sent to be
+    // acknowledged by the peer)
     while (true) {
       uint32_t seen;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(from) : "memory");

@@ -76,7 +76,7 @@ def main() -> int:
         dw32 = torch.empty(3, 3, 72, 64, dtype=torch.float32, device=device)
         rs16, rs32 = torch.empty_like(dw16), torch.empty_like(dw32)
         fu16, fu32 = torch.empty_like(dw16), torch.empty_like(dw32)
-        for _ in range(3):                 # several steps: both buffer halves, growing epochs
+        for _ in range(20):                # many steps: both buffer halves, growing epochs
             sh.wu(x[b:e].contiguous(), dy[b:e].contiguous(), dw16, dw32)
             sh_rs.wu(x[b:e].contiguous(), dy[b:e].contiguous(), rs16, rs32)
             sh_fu.wu(x[b:e].contiguous(), dy[b:e].contiguous(), fu16, fu32)
