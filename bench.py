@@ -6,7 +6,10 @@
 A step is one pass of the hot path (one convolution / matrix product call)
 over one batch of synthetic input.  The default workload is the ResNet 3x3
 forward convolution the metric is quoted on; the other named configurations
-can be selected with --workload.  One JSON line is printed by rank 0.
+can be selected with --workload, and by default each of them is also timed
+in the same process with a bounded step count and reported under
+"workloads" (ms per step, TFLOP/s, roofline, clocks, parity check).  One JSON
+line is printed by rank 0.
 
   value      TFLOP/s with inputs resident in HBM (2 x MACs, products with
              padding not counted, as the reference's getFwdFlops does), timed
@@ -23,10 +26,17 @@ can be selected with --workload.  One JSON line is printed by rank 0.
   cpu_baseline  the reference's own CPU model (oracle/_ref when built, else the
              C restatement) timed on the host cores on a bounded sample.
 
+  parity_check  a sample of what the timed loop computed, compared with the CPU
+             oracle after the timed region (same tolerance as the tests).
+
 With N > 1 (launched under torchrun) every rank runs the same per-GPU
 workload on its own shard of a batch N times larger (weak scaling; the path
-needs no collective in the forward pass; the weight update sums the per-rank
-gradients with the library's all-reduce kernel over NVLink peer memory).
+needs no collective in the forward pass).  The line then also carries "wu":
+the weight update of the 3x3 128-channel layer, whose per-rank gradients are
+summed inside the library's reduction kernel over NVLink peer memory (the one
+collective of the path), checked against the process group's all-reduce, with
+the same rank's update without the collective timed beside it; and
+"strong_scaling": the two largest configurations sharded over the ranks.
 """
 from __future__ import annotations
 
@@ -45,6 +55,11 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 import numpy as np  # noqa: E402
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# Dense fp8 (e4m3) peak, measured on this pool's B200s the way MEASURED_PEAKS.json
+# measures bf16: torch._scaled_mm on 8192^3, best of 10 (burst) and back to back
+# for 4 s (sustained); see profiles/fp8_peak.md.
+FP8_PEAK_TFLOPS = {"burst": 3151.1, "sustained": 2587.6,
+                   "source": "of measured (torch._scaled_mm e4m3 8192^3, burst; profiles/fp8_peak.md)"}
 
 # name -> description of one call.  kind conv: ConvParams kwargs + pass; kind gemm: m, k, n.
 WORKLOADS = {
@@ -209,15 +224,22 @@ class ClockSampler:
 
 class Workload:
     """Device-resident rotating buffer sets (so that consecutive steps do not
-    find their inputs in L2) and pinned host copies for the end-to-end leg."""
+    find their inputs in L2) and, for the workload the headline is quoted on,
+    pinned host copies for the end-to-end leg."""
 
-    def __init__(self, name, spec, ctx, device, rank=0, world=1, sets_bytes_target=300 << 20, force_sets=0):
+    def __init__(self, name, spec, ctx, device, rank=0, world=1, sets_bytes_target=300 << 20, force_sets=0,
+                 host_copies=True, allreduce="auto"):
         import torch
         from poplibs_b200 import capi
         self.name, self.spec, self.ctx, self.capi = name, spec, ctx, capi
-        self.rank, self.world = rank, world
-        g = torch.Generator(device="cpu").manual_seed(1234)
+        self.rank, self.world, self.device = rank, world, device
+        g = torch.Generator(device=device).manual_seed(1234 + rank)
         self.kind = spec["kind"]
+        self.sharded = None
+        self.allreduce = None
+
+        def uniform(shape, scale=1.0):
+            return ((torch.rand(shape, generator=g, device=device) * 2 - 1) * scale).half()
         if self.kind == "conv":
             p = capi.ConvParams.make(**spec["params"])
             self.p = p
@@ -225,45 +247,30 @@ class Workload:
             of = p.output_field()
             ci, co = p.in_chans_per_group, p.out_chans_per_group
             self.flops = 2 * p.macs()
-            x_shape = (p.batch, *kw["field"], ci)
-            y_shape = (p.batch, *of, co)
-            w_shape = (*kw["kernel"], co, ci)
+            self.x_shape = (p.batch, *kw["field"], ci)
+            self.y_shape = (p.batch, *of, co)
+            self.w_shape = (*kw["kernel"], co, ci)
             bound = 1.0 / np.sqrt(ci * int(np.prod(kw["kernel"])))
-            self.host = {
-                "x": (torch.rand(x_shape, generator=g) * 2 - 1).half().pin_memory(),
-                "w": ((torch.rand(w_shape, generator=g) * 2 - 1) * bound).half().pin_memory(),
-                "dy": (torch.rand(y_shape, generator=g) * 2 - 1).half().pin_memory(),
-            }
             self.pass_ = spec["pass_"]
-            if world > 1:
+            proto = {"x": uniform(self.x_shape), "w": uniform(self.w_shape, bound), "dy": uniform(self.y_shape)}
+            if world > 1 and self.pass_ == "wu":
                 from poplibs_b200 import parallel
                 # weak scaling: every rank holds one full per-GPU batch of the layer
                 glob = dict(kw, batch=kw["batch"] * world)
-                self.allreduce = "none (no collective on this pass)"
-                ar = os.environ.get("PLB_BENCH_ALLREDUCE", "p2p")   # p2p | p2p_fused | p2p_oneshot | p2p_rs | nccl
-                peer = self.pass_ == "wu" and ar.startswith("p2p")
-                ar_mode = {"p2p_oneshot": "oneshot", "p2p_rs": "rs", "p2p_fused": "fused"}.get(ar, "auto")
-                # PLB_BENCH_OVERLAP=1: the all-reduce of step i runs on a stream of its own, behind
-                # step i + 1's kernels.  Off by default: the event between the kernels costs the
-                # programmatic launch overlap, and the measured step is not shorter
-                # (2 GPUs 57.1 vs 59.8 us, 8 GPUs 72.4 vs 68.8 us).
-                overlap = peer and os.environ.get("PLB_BENCH_OVERLAP", "0") == "1"
+                peer = allreduce != "nccl"
                 try:
                     self.sharded = parallel.ShardedConv(ctx, glob, rank, world, peer_allreduce=peer,
-                                                        overlap_allreduce=overlap, allreduce_mode=ar_mode)
-                    if self.pass_ == "wu":
-                        self.allreduce = ((f"library kernel over NVLink peer memory ({self.sharded.peer.mode})"
-                                           + (", overlapped with the next step on a second stream" if overlap else ""))
-                                          if peer else "nccl all_reduce + cast")
+                                                        allreduce_mode=allreduce if peer else "auto")
+                    self.allreduce = (f"library kernels over NVLink peer memory ({self.sharded.peer.mode})"
+                                      if peer else "nccl all_reduce + cast")
                 except Exception as e:  # symmetric memory unavailable: the process group's all-reduce
                     self.sharded = parallel.ShardedConv(ctx, glob, rank, world)
                     self.allreduce = f"nccl all_reduce + cast (peer memory unavailable: {type(e).__name__})"
             pass_id = {"bwd": capi.PASS_TRAINING_BWD, "wu": capi.PASS_TRAINING_WU}.get(
                 self.pass_, capi.PASS_TRAINING_FWD)
             self.plan = capi.conv_plan(p, pass_id).as_dict()
-            self.bytes = self.plan["bytes"]
-            per_set = 2 * (int(np.prod(x_shape)) + int(np.prod(y_shape)))
-            out_shape = {"fwd": y_shape, "bwd": x_shape, "wu": w_shape}[self.pass_]
+            per_set = 2 * (int(np.prod(self.x_shape)) + int(np.prod(self.y_shape)))
+            out_shape = {"fwd": self.y_shape, "bwd": self.x_shape, "wu": self.w_shape}[self.pass_]
         else:
             m, k, n = spec["m"], spec["k"], spec["n"]
             self.quarter = spec["quarter"]
@@ -272,37 +279,40 @@ class Workload:
                                              scale_a=-3 if self.quarter else 0, scale_b=-2 if self.quarter else 0)
             self.flops = 2 * m * k * n
             self.plan = capi.matmul_plan(self.desc).as_dict()
-            self.bytes = self.plan["bytes"]
             if self.quarter:
-                a = torch.randn((m, k), generator=g).mul_(8).to(torch.float8_e4m3fn).view(torch.uint8)
-                b = torch.randn((n, k), generator=g).mul_(4).to(torch.float8_e4m3fn).view(torch.uint8)
+                a = torch.randn((m, k), generator=g, device=device).mul_(8).to(torch.float8_e4m3fn).view(torch.uint8)
+                b = torch.randn((n, k), generator=g, device=device).mul_(4).to(torch.float8_e4m3fn).view(torch.uint8)
             else:
-                a = torch.randn((m, k), generator=g).half()
-                b = torch.randn((k, n), generator=g).half()
-            self.host = {"a": a.pin_memory(), "b": b.pin_memory()}
+                a = torch.randn((m, k), generator=g, device=device).half()
+                b = torch.randn((k, n), generator=g, device=device).half()
+            proto = {"a": a, "b": b}
             per_set = a.numel() * a.element_size() + b.numel() * b.element_size() + 2 * m * n
             out_shape = (m, n)
+        self.bytes = self.plan["bytes"]
         self.nsets = int(max(2, min(16, -(-sets_bytes_target // max(per_set, 1)))))
         if force_sets > 0:
             self.nsets = force_sets
         self.dev = []
-        for _ in range(self.nsets):
-            d = {k: v.to(device, non_blocking=False) for k, v in self.host.items()}
+        for i in range(self.nsets):
+            d = proto if i == 0 else {k: v.clone() for k, v in proto.items()}
             d["out"] = torch.empty(out_shape, dtype=torch.float16, device=device)
             if self.kind == "conv" and self.pass_ == "wu":
                 d["out32"] = torch.empty(out_shape, dtype=torch.float32, device=device)
             self.dev.append(d)
-        # end-to-end leg: two contexts (streams) and two pinned output buffers
-        self.host_out = [torch.empty(out_shape, dtype=torch.float16).pin_memory() for _ in range(2)]
+        self.host = self.host_out = None
         self.e2e_ctx = None
-        self.h2d_bytes = sum(v.numel() * v.element_size() for k, v in self.host.items()
-                             if self._is_input(k))
-        self.d2h_bytes = self.host_out[0].numel() * 2
+        if host_copies and self.has_e2e():
+            # end-to-end leg: pinned inputs, two contexts (streams) and two pinned output buffers
+            self.host = {k: v.cpu().pin_memory() for k, v in proto.items() if self._is_input(k)}
+            self.host_out = [torch.empty(out_shape, dtype=torch.float16).pin_memory() for _ in range(2)]
+            self.h2d_bytes = sum(v.numel() * v.element_size() for v in self.host.values())
+            self.d2h_bytes = self.host_out[0].numel() * 2
+        self.launches_per_step = 1
         torch.cuda.synchronize()
 
     def _is_input(self, key):
         if self.kind == "gemm":
-            return True
+            return key in ("a", "b")
         return key in {"fwd": ("x", "w"), "bwd": ("dy", "w"), "wu": ("x", "dy")}[self.pass_]
 
     def step(self, i):
@@ -313,11 +323,16 @@ class Workload:
             self.ctx.conv_fwd(self.p, d["x"], d["w"], d["out"])
         elif self.pass_ == "bwd":
             self.ctx.conv_bwd(self.p, d["dy"], d["w"], d["out"])
-        elif self.world == 1:
+        elif self.sharded is None:
             self.ctx.conv_wu(self.p, d["x"], d["dy"], d["out"], d["out32"])
         else:
-            # per-rank batch reduced locally, then the one collective of the path
+            # per-rank batch reduced locally and summed over the ranks: the one collective of the path
             self.sharded.wu(d["x"], d["dy"], d["out"], d["out32"])
+
+    def step_local(self, i):
+        """The weight update of this rank's batch alone (no sum over ranks)."""
+        d = self.dev[i % self.nsets]
+        self.ctx.conv_wu(self.p, d["x"], d["dy"], d["out"], d["out32"])
 
     def check_allreduce(self):
         """One untimed step of the multi-GPU weight update compared with the
@@ -331,29 +346,11 @@ class Workload:
         dist.all_reduce(local)
         self.sharded.wu(d["x"], d["dy"], d["out"], d["out32"])
         self.ctx.synchronize()
-        self.sync_comm()
         torch.cuda.synchronize()
         diff = float((local - d["out32"]).abs().max().item())
-        scale = float(local.abs().max().item())
-        return {"max_abs_diff_vs_nccl": diff, "max_abs": scale}
-
-    def sync_comm(self):
-        """Waits for the communication stream of an overlapped all-reduce (and checks its status)."""
-        sharded = getattr(self, "sharded", None)
-        if sharded is not None and sharded.peer is not None:
-            sharded.peer.synchronize()
-
-    def join_comm(self):
-        """Orders the main stream after the latest overlapped all-reduce."""
-        sharded = getattr(self, "sharded", None)
-        if sharded is not None and sharded.peer is not None:
-            sharded.peer.wait()
-
-    def comm_launches(self):
-        sharded = getattr(self, "sharded", None)
-        if sharded is not None and sharded.peer is not None and sharded.peer.overlap:
-            return sharded.peer.comm_ctx.launch_count()
-        return 0
+        same16 = bool(torch.equal(local.half(), d["out"]))
+        return {"max_abs_diff_vs_nccl": diff, "max_abs": float(local.abs().max().item()),
+                "half_cast_equal": same16}
 
     def step_e2e(self, i):
         """One end-to-end step: pinned host inputs -> device -> kernel -> pinned
@@ -366,14 +363,69 @@ class Workload:
         out = self.host_out[i & 1]
         if self.kind == "gemm":
             c.matmul_host(self.desc, self.host["a"], self.host["b"], None, out, sync=False)
-        elif self.pass_ == "fwd":
-            c.conv_fwd_host(self.p, self.host["x"], self.host["w"], out, sync=False)
         else:
-            raise RuntimeError("end-to-end leg is defined for the forward pass and matMul")
+            c.conv_fwd_host(self.p, self.host["x"], self.host["w"], out, sync=False)
 
     def has_e2e(self):
         return self.kind == "gemm" or self.pass_ == "fwd"
 
+    # ---- correctness evidence carried by the bench line ------------------------------
+    def parity_check(self):
+        """Compares a sample of what the timed loop left in buffer set 0 with the
+        CPU oracle (the checker; outside every timed region), under the
+        tolerance the tests use: relative 1e-3 (half) / 5e-2 (quarter),
+        absolute max(1e-5, 2.5e-4 * rms(expected))."""
+        import torch
+        import common as T
+        import oracle
+        d = self.dev[0]
+        rel = T.REL_TOL_QUARTER if self.spec.get("quarter") else T.REL_TOL_HALF
+        if self.kind == "gemm":
+            m = self.spec["m"]
+            rows = sorted({0, m // 3, (2 * m) // 3, m - 1})
+            a = d["a"][rows]
+            if self.quarter:
+                av = a.view(torch.float8_e4m3fn).float().cpu().numpy()
+                bv = d["b"].view(torch.float8_e4m3fn).float().cpu().numpy()
+                want = oracle.gemm(av, bv, transpose_b=True) * 2.0 ** -5
+            else:
+                want = oracle.gemm(a.float().cpu().numpy(), d["b"].float().cpu().numpy())
+            got = d["out"][rows].float().cpu().numpy()
+            what = f"{len(rows)} rows of the product"
+        else:
+            p, kw = self.p, self.spec["params"]
+            pick = [0, p.batch - 1] if p.batch > 1 else [0]
+            sub = self.capi.ConvParams.make(**{**kw, "batch": len(pick)})
+            spec = T.spec_from_params(sub)
+            nchw = lambda t: t.permute(0, 3, 1, 2).float().cpu().numpy()       # noqa: E731
+            w = d["w"].permute(2, 3, 0, 1)[None].float().cpu().numpy() if self.pass_ != "wu" else None
+            if self.pass_ == "fwd":
+                want = oracle.conv_fwd(spec, nchw(d["x"][pick]), w)
+                got = nchw(d["out"][pick])
+                what = f"{len(pick)} images of the output"
+            elif self.pass_ == "bwd":
+                want = oracle.conv_bwd(spec, nchw(d["dy"][pick]), w)
+                got = nchw(d["out"][pick])
+                what = f"{len(pick)} images of the input gradient"
+            else:
+                # the gradient sums over the whole batch: the oracle is run on a
+                # two-image batch, through the same entry point
+                x, dy = d["x"][pick].contiguous(), d["dy"][pick].contiguous()
+                g32 = torch.empty(self.w_shape, dtype=torch.float32, device=self.device)
+                self.ctx.conv_wu(sub, x, dy, None, g32)
+                self.ctx.synchronize()
+                want = oracle.conv_wu(spec, nchw(x), nchw(dy))[0]
+                got = g32.permute(2, 3, 0, 1)[None].cpu().numpy()
+                what = f"weight gradient of a {len(pick)}-image batch (same entry point)"
+        got = np.asarray(got, dtype=np.float64)
+        want = np.asarray(want, dtype=np.float64).reshape(got.shape)
+        rms = float(np.sqrt(np.mean(want * want))) if want.size else 0.0
+        abs_tol = max(T.ABS_TOL, 2.5e-4 * rms)
+        bad, _, _ = oracle.check_is_close(got, want, rel, abs_tol)
+        strict_bad, _, _ = oracle.check_is_close(got, want, rel, T.ABS_TOL)
+        return {"sample": what, "elements": int(got.size), "bad": int(bad), "rel_tol": rel, "abs_tol": abs_tol,
+                "passing_only_by_rms_floor": int(strict_bad - bad),
+                "worst_abs_err_over_rms": float(np.abs(got - want).max() / rms) if rms else 0.0}
 
 # --------------------------------------------------------------------------- CPU arm
 
@@ -453,6 +505,71 @@ def cpu_reference_rate(name, spec, budget_s=12.0):
 
 # --------------------------------------------------------------------------- main
 
+# steps of the additional workloads timed in the same process (bounded so that
+# the default run stays within minutes)
+EXTRA_STEPS = {"matmul_fp16_8192": 50, "matmul_fp8_8192": 50, "conv7x7_s2_fwd_n256_224x224_c3_c64": 100}
+EXTRA_STEPS_DEFAULT = 200
+WU_WORKLOAD = "conv3x3_wu_n256_28x28_c128"
+
+
+def roofline_of(name, spec, flops, nbytes, ms_per_step, peaks, peak_src):
+    per_launch_s = ms_per_step * 1e-3
+    if spec["bound"] == "hbm":
+        achieved, peak, unit = nbytes / per_launch_s / 1e9, peaks["hbm_gbs"], "GB/s"
+        src = f"of {peak_src} (copy bandwidth)"
+    elif spec.get("quarter"):
+        achieved, peak, unit = flops / per_launch_s / 1e12, FP8_PEAK_TFLOPS["burst"], "TFLOP/s"
+        src = FP8_PEAK_TFLOPS["source"]
+    else:
+        achieved, peak, unit = flops / per_launch_s / 1e12, peaks["bf16_tflops"], "TFLOP/s"
+        src = f"of {peak_src} (burst)"
+    return {"bound": spec["bound"], "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+            "traffic": NCU_DRAM_TRAFFIC_BYTES.get(name), "peak_source": src,
+            "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": nbytes}
+
+
+def measure_fp8_peak(n=8192, sustained_s=4.0):
+    """Dense e4m3 x e4m3 -> bf16 GEMM of the vendor library on n^3: best of 10
+    launches (burst) and back to back for `sustained_s` seconds (sustained),
+    SM clocks sampled during the sustained loop.  Read-only: no GPU setting is
+    touched.  Prints one JSON line."""
+    import torch
+    dev = torch.device("cuda", 0)
+    a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+    b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()      # column-major right operand
+    one = torch.ones((), device=dev, dtype=torch.float32)
+    run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)  # noqa: E731
+    for _ in range(5):
+        run()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(10):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        run()
+        e.record()
+        e.synchronize()
+        best = min(best, s.elapsed_time(e))
+    sampler = ClockSampler(0)
+    sampler.start()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters, t0 = 0, time.perf_counter()
+    s.record()
+    while time.perf_counter() - t0 < sustained_s:
+        for _ in range(50):
+            run()
+        iters += 50
+        torch.cuda.synchronize()
+    e.record()
+    e.synchronize()
+    clocks = sampler.stop()
+    flops = 2.0 * n ** 3
+    print(json.dumps({"fp8_tflops": flops / (best * 1e-3) / 1e12,
+                      "fp8_tflops_sustained": flops * iters / (s.elapsed_time(e) * 1e-3) / 1e12,
+                      "how": f"torch._scaled_mm e4m3 x e4m3 -> bf16, {n}^3: best of 10 (burst), "
+                             f"back to back for {sustained_s} s (sustained)", "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -461,13 +578,25 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="time only --workload (skip the other configurations, the multi-GPU weight "
+                         "update and the strong-scaling shapes that are added to the line by default)")
     ap.add_argument("--no-graph", action="store_true",
-                    help="time one library call per step instead of replaying a CUDA graph")
+                    help="time one library call per step instead of replaying CUDA graphs")
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "oneshot", "rs", "nccl"],
+                    help="how the multi-GPU weight update sums the per-rank gradients")
     ap.add_argument("--buffer-sets", type=int, default=0,
                     help="number of rotating buffer sets (default: enough to exceed L2; 1 = every step "
                          "re-reads the same, L2-resident, inputs: a diagnostic, not a bench value)")
+    ap.add_argument("--measure-fp8-peak", action="store_true",
+                    help="measure the dense fp8 (e4m3) peak of this GPU with the library GEMM "
+                         "(torch._scaled_mm, 8192^3) and print it: the roofline denominator of the "
+                         "fp8 workloads, not a result of this library")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.measure_fp8_peak:
+        measure_fp8_peak()
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -488,7 +617,8 @@ def main():
             res = cpu_reference_rate(args.workload, spec, budget_s=6.0)
             best = res if best is None or res["value"] > best["value"] else best
         elapsed = time.perf_counter() - t0
-        flops_per_step = None
+        if spec["kind"] == "conv":
+            config["per_gpu_batch"] = spec["params"]["batch"]
         line = {"impl": "reference", "metric": metric, "value": best["value"], "unit": "TFLOP/s",
                 "n_gpus": args.gpus, "steps": steps, "warmup": 0, "ms_per_step": elapsed / steps * 1e3,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
@@ -509,85 +639,87 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     from poplibs_b200 import capi
 
-    # the library enqueues on a torch stream so that NCCL collectives (weight
-    # update at N > 1) are ordered with the kernels without host synchronisation
-    torch_stream = torch.cuda.Stream(device=device)
-    ctx = capi.Context(local_rank, stream=torch_stream.cuda_stream)
-    wl = Workload(args.workload, spec, ctx, device, rank, world, force_sets=args.buffer_sets)
-    config["plan"] = wl.plan
-    config["buffer_sets"] = wl.nsets
-    if args.buffer_sets > 0:
-        config["l2"] = f"DIAGNOSTIC: {wl.nsets} buffer set(s) forced; inputs may stay in L2 between steps"
-    if world > 1 and spec["kind"] == "conv":
-        config["allreduce"] = wl.allreduce
-        if spec["pass_"] == "wu":
-            config["allreduce_check"] = wl.check_allreduce()
-    if spec["kind"] == "conv":
-        config["per_gpu_batch"] = spec["params"]["batch"]
-        config["global_batch"] = spec["params"]["batch"] * world
-    stream = torch_stream
+    # the library enqueues on a torch stream so that NCCL collectives (the
+    # checker of the multi-GPU weight update) are ordered with the kernels
+    stream = torch.cuda.Stream(device=device)
+    ctx = capi.Context(local_rank, stream=stream.cuda_stream)
+    peaks, peak_src = load_peaks()
 
     def barrier():
         torch.cuda.synchronize()
         ctx.synchronize()
-        wl.sync_comm()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(step_fn, steps, warmup, graph_sets=0):
-        """Times `steps` calls of step_fn on the device.  With graph_sets = n the
-        steps are replayed from a CUDA graph of n consecutive steps (one per
-        rotating buffer set), which takes the host's per-launch cost (argument
-        marshalling, tensor-map encoding) out of a loop of microsecond kernels."""
-        with torch.cuda.stream(stream):
-            for i in range(warmup):
-                step_fn(i)
-        barrier()
-        graph = None
-        if graph_sets:
-            try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    for i in range(graph_sets):
-                        step_fn(i)
-                with torch.cuda.stream(stream):
-                    graph.replay()  # untimed: uploads the graph
-                barrier()
-            except Exception as e:  # capture not possible: plain launches
-                print(f"bench: CUDA graph capture failed ({type(e).__name__}: {e}); "
-                      "timing plain launches", file=sys.stderr)
-                graph = None
-                torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches0, comm0 = ctx.launch_count(), wl.comm_launches()
-        with torch.cuda.stream(stream):
-            start.record()
-            if graph is not None:
-                replays, rest = divmod(steps, graph_sets)
-                for _ in range(replays):
-                    graph.replay()
-                for i in range(rest):
-                    step_fn(i)
-            else:
-                for i in range(steps):
-                    step_fn(warmup + i)
-            wl.join_comm()   # the last step's all-reduce belongs to the timed region
-            end.record()
-        end.synchronize()
-        barrier()
-        ms = start.elapsed_time(end)
-        launches = ctx.launch_count() - launches0 + wl.comm_launches() - comm0
-        if graph is not None:
-            # replayed kernels are not counted by the library: add them
-            launches += (steps // graph_sets) * graph_sets * wl.launches_per_step
+    def max_over_ranks(ms):
         if world > 1:
             t = torch.tensor([ms], device=device, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        return ms, launches, graph is not None
+        return ms
 
-    def timed_e2e(steps, warmup):
+    def timed(wl, step_fn, steps, warmup, use_graph):
+        """Device time of exactly `steps` calls of step_fn.  With use_graph the
+        steps are replayed from CUDA graphs, which takes the host's per-launch
+        cost (argument marshalling, tensor-map encoding) out of a loop of
+        microsecond kernels: up to 512 steps are one graph of `steps` nodes
+        (buffer sets in rotation); more are one graph of wl.nsets consecutive
+        steps replayed steps // nsets times plus one of the steps % nsets
+        remaining steps.  Returns (ms, launches, graphed)."""
+        with torch.cuda.stream(stream):
+            for i in range(warmup):
+                step_fn(i)
+        barrier()
+        graphs = None
+        if use_graph:
+            try:
+                graphs = []
+                replays, rest = divmod(steps, wl.nsets)
+                for n, times in (((steps, 1), (0, 0)) if steps <= 512 else ((wl.nsets, replays), (rest, 1))):
+                    if n == 0 or times == 0:
+                        continue
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        for i in range(n):
+                            step_fn(i)
+                    with torch.cuda.stream(stream):
+                        g.replay()  # untimed: uploads the graph
+                    graphs.append((g, times))
+                barrier()
+            except Exception as e:  # capture not possible: plain launches
+                print(f"bench: CUDA graph capture failed ({type(e).__name__}: {e}); "
+                      "timing plain launches", file=sys.stderr)
+                graphs = None
+                torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = ctx.launch_count()
+        with torch.cuda.stream(stream):
+            start.record()
+            if graphs is not None:
+                for g, times in graphs:
+                    for _ in range(times):
+                        g.replay()
+            else:
+                for i in range(steps):
+                    step_fn(warmup + i)
+            end.record()
+        end.synchronize()
+        barrier()
+        ms = max_over_ranks(start.elapsed_time(end))
+        launches = ctx.launch_count() - launches0
+        if graphs is not None:
+            launches += steps * wl.launches_per_step   # replayed kernels are not counted by the library
+        return ms, launches, graphs is not None
+
+    def count_launches(wl, step_fn):
+        n0 = ctx.launch_count()
+        with torch.cuda.stream(stream):
+            step_fn(0)
+        barrier()
+        wl.launches_per_step = ctx.launch_count() - n0
+
+    def timed_e2e(wl, steps, warmup):
         """Device time of `steps` end-to-end steps over the two e2e streams."""
         wl.e2e_ctx = [capi.Context(local_rank), capi.Context(local_rank)]
         for i in range(warmup):
@@ -608,54 +740,118 @@ def main():
         for c in wl.e2e_ctx:
             c.synchronize()
         barrier()
-        ms = start.elapsed_time(end)
-        if world > 1:
-            t = torch.tensor([ms], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return max_over_ranks(start.elapsed_time(end))
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    # kernels per step, counted on one untimed step
-    n0 = ctx.launch_count()
-    with torch.cuda.stream(stream):
-        wl.step(0)
-    barrier()
-    wl.launches_per_step = ctx.launch_count() - n0
-    # The multi-GPU weight update passes a step counter to its all-reduce kernel,
-    # so its steps cannot be replayed from a graph.
-    use_graph = not args.no_graph and not (world > 1 and spec.get("pass_") == "wu")
-    ms, launches, graphed = timed(wl.step, args.steps, args.warmup, wl.nsets if use_graph else 0)
-    config["launch"] = (f"CUDA graph of {wl.nsets} steps (one per buffer set), replayed" if graphed
+    def with_clocks(fn):
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        out = fn()
+        return out, (sampler.stop() if rank == 0 else None)
+
+    # ---- the workload the headline is quoted on ------------------------------------------
+    wl = Workload(args.workload, spec, ctx, device, rank, world, force_sets=args.buffer_sets,
+                  allreduce=args.allreduce)
+    config["plan"] = wl.plan
+    config["buffer_sets"] = wl.nsets
+    if args.buffer_sets > 0:
+        config["l2"] = f"DIAGNOSTIC: {wl.nsets} buffer set(s) forced; inputs may stay in L2 between steps"
+    if spec["kind"] == "conv":
+        config["per_gpu_batch"] = spec["params"]["batch"]
+        config["global_batch"] = spec["params"]["batch"] * world
+    if wl.sharded is not None:
+        config["allreduce"] = wl.allreduce
+        config["allreduce_check"] = wl.check_allreduce()
+    count_launches(wl, wl.step)
+    # The multi-GPU weight update passes a step counter to its kernels, so its
+    # steps cannot be replayed from a graph.
+    use_graph = not args.no_graph and wl.sharded is None
+    (ms, launches, graphed), clocks = with_clocks(lambda: timed(wl, wl.step, args.steps, args.warmup, use_graph))
+    config["launch"] = ((f"one CUDA graph of {args.steps} steps, buffer sets in rotation" if args.steps <= 512
+                         else f"CUDA graphs of {wl.nsets} steps (one per buffer set) and of the remaining "
+                              f"{args.steps % wl.nsets}, replayed: exactly {args.steps} steps") if graphed
                         else "one library call per step")
-    clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
     value = wl.flops * world / (ms_per_step * 1e-3) / 1e12
+    parity = wl.parity_check() if rank == 0 else None
 
     e2e = None
-    if wl.has_e2e():
+    if wl.has_e2e() and wl.host is not None:
         e2e_steps = max(4, min(args.steps, 40))
-        ms_e = timed_e2e(e2e_steps, 3)
+        ms_e = timed_e2e(wl, e2e_steps, 3)
         e2e = {"value": wl.flops * world / (ms_e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
-               "ms_per_step": ms_e / e2e_steps}
+               "ms_per_step": ms_e / e2e_steps,
+               "note": "one layer per call: 25.8 MB over PCIe per 7.2 GFLOP, bound by the host link"
+               if args.workload == DEFAULT_WORKLOAD else None}
+        wl.e2e_ctx = None
+    roofline = roofline_of(args.workload, spec, wl.flops, wl.bytes, ms_per_step, peaks, peak_src)
+    del wl
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations, same process, bounded step counts -----------------------
+    workloads = None
+    if not args.no_extra and world == 1:
+        workloads = {}
+        for name, sp in WORKLOADS.items():
+            if name == args.workload:
+                continue
+            try:
+                w2 = Workload(name, sp, ctx, device, host_copies=False)
+                count_launches(w2, w2.step)
+                steps2 = EXTRA_STEPS.get(name, EXTRA_STEPS_DEFAULT)
+                (ms2, _, g2), clk2 = with_clocks(lambda: timed(w2, w2.step, steps2, 5, not args.no_graph))
+                per = ms2 / steps2
+                workloads[name] = {"ms_per_step": per, "steps": steps2, "tflops": w2.flops / (per * 1e-3) / 1e12,
+                                   "roofline": roofline_of(name, sp, w2.flops, w2.bytes, per, peaks, peak_src),
+                                   "clocks": clk2, "launches_per_step": w2.launches_per_step,
+                                   "graphed": g2, "parity_check": w2.parity_check()}
+                del w2
+            except Exception as e:  # one configuration failing must not lose the line
+                workloads[name] = {"error": f"{type(e).__name__}: {e}"}
+            torch.cuda.empty_cache()
+
+    # ---- multi-GPU: the one collective of the path, and the shapes the path shards ---------
+    wu = strong = None
+    if not args.no_extra and world > 1 and args.workload != WU_WORKLOAD:
+        sp = WORKLOADS[WU_WORKLOAD]
+        w3 = Workload(WU_WORKLOAD, sp, ctx, device, rank, world, host_copies=False, allreduce=args.allreduce)
+        check = w3.check_allreduce()
+        count_launches(w3, w3.step)
+        steps3 = 300
+        (ms_d, _, _), clk3 = with_clocks(lambda: timed(w3, w3.step, steps3, 10, False))
+        ms_l, _, _ = timed(w3, w3.step_local, steps3, 10, False)
+        wu = {"workload": WU_WORKLOAD, "per_gpu_batch": sp["params"]["batch"], "ms_per_step": ms_d / steps3,
+              "tflops": w3.flops * world / (ms_d / steps3 * 1e-3) / 1e12, "allreduce": w3.allreduce,
+              "allreduce_check": check, "local_ms_per_step": ms_l / steps3,
+              "efficiency_vs_local": ms_l / ms_d, "launches_per_step": w3.launches_per_step, "clocks": clk3,
+              "note": "weak scaling; local = the same rank's weight update without the sum over ranks, "
+                      "timed in the same process (max over ranks)"}
+        del w3
+        torch.cuda.empty_cache()
+        # strong scaling: the stated configurations sharded over the ranks (no collective)
+        strong = {}
+        from poplibs_b200 import parallel
+        for name in ("conv3x3_fwd_n256_28x28_c128", "matmul_fp16_8192"):
+            sp = dict(WORKLOADS[name])
+            if sp["kind"] == "conv":
+                b, e = parallel.shard_range(sp["params"]["batch"], rank, world)
+                sp["params"] = dict(sp["params"], batch=e - b)
+                total = 2 * capi.ConvParams.make(**WORKLOADS[name]["params"]).macs()
+            else:
+                b, e = parallel.shard_range(sp["m"], rank, world)
+                sp["m"] = e - b
+                total = 2 * WORKLOADS[name]["m"] * sp["k"] * sp["n"]
+            w4 = Workload(name, sp, ctx, device, rank, 1, host_copies=False)
+            count_launches(w4, w4.step)
+            steps4 = EXTRA_STEPS.get(name, EXTRA_STEPS_DEFAULT)
+            ms4, _, _ = timed(w4, w4.step, steps4, 5, not args.no_graph)
+            strong[name] = {"per_gpu_share": e - b, "ms_per_step": ms4 / steps4,
+                            "tflops_total": total / (ms4 / steps4 * 1e-3) / 1e12}
+            del w4
+            torch.cuda.empty_cache()
 
     if rank == 0:
-        peaks, peak_src = load_peaks()
-        per_launch_s = ms_per_step * 1e-3
-        if spec["bound"] == "hbm":
-            achieved = wl.bytes / per_launch_s / 1e9
-            peak, unit = peaks["hbm_gbs"], "GB/s"
-        else:
-            achieved = wl.flops / per_launch_s / 1e12
-            peak, unit = peaks["bf16_tflops"] * (2.0 if spec.get("quarter") else 1.0), "TFLOP/s"
-        roofline = {"bound": spec["bound"], "achieved": achieved, "peak": peak, "unit": unit,
-                    "frac": achieved / peak, "traffic": NCU_DRAM_TRAFFIC_BYTES.get(args.workload),
-                    "peak_source": f"of {peak_src}" + (" (fp8 taken as 2 x the measured 16-bit burst peak)"
-                                                        if spec.get("quarter") else " (burst)"),
-                    "algorithmic_flops_per_launch": wl.flops, "algorithmic_bytes_per_launch": wl.bytes}
         cpu = None
         if not args.no_cpu_baseline and world == 1:
             cpu = cpu_reference_rate(args.workload, spec)
@@ -663,7 +859,13 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f8e4m3" if spec.get("quarter") else "f16",
                 "data": "synthetic", "config": config, "clocks": clocks, "e2e": e2e,
-                "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu}
+                "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
+                "parity_check": parity}
+        if workloads is not None:
+            line["workloads"] = workloads
+        if wu is not None:
+            line["wu"] = wu
+            line["strong_scaling"] = strong
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
