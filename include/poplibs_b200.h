@@ -95,6 +95,11 @@ PLB_API void *plb_context_stream(plb_context *ctx);
 PLB_API int plb_synchronize(plb_context *ctx);
 /* Number of kernels this context has launched so far. */
 PLB_API uint64_t plb_launch_count(const plb_context *ctx);
+/* PLB_PLAN_* bits (below) that are added to every plan made for a call through
+ * this context, also for calls that take no options (plb_matmul): the role of
+ * the per-graph option flags a poplin user sets once
+ * (lib/poplin/ConvOptions.cpp:40-150).  Used by the tests and for A/B timing. */
+PLB_API void plb_context_set_plan_flags(plb_context *ctx, int32_t plan_flags);
 
 /* Device memory helpers for callers without an allocator of their own. */
 PLB_API int plb_malloc(plb_context *ctx, size_t bytes, void **d_ptr);
@@ -215,6 +220,9 @@ typedef struct plb_conv_options {
 #define PLB_PLAN_NO_HALO 4                /* one activation load per filter tap               */
 #define PLB_PLAN_NO_CTA_PAIR 8            /* every CTA issues its own 128-row MMAs            */
 #define PLB_PLAN_FORCE_CTA_PAIR 16        /* CTA pairs whenever the shape allows them         */
+#define PLB_PLAN_NO_TMA_STORE 32          /* plain vector stores in the epilogue              */
+#define PLB_PLAN_NO_PDL 64                /* launch without programmatic stream serialization */
+#define PLB_PLAN_NO_A_COLLECTOR 128       /* weight update: fetch the outGrad tile per MMA    */
 
 /* out = conv(in, weights) (+ bias), poplin::convolution
  * (include/poplin/Convolution.hpp:345-384, lib/poplin/Convolution.cpp:3128-3215).

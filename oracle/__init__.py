@@ -146,11 +146,12 @@ _REF = None
 _DP = C.POINTER(C.c_double)
 
 
-def build(ref: bool = False) -> None:
-    """Compile liboracle.so (and, when the reference tree is present and
-    ``ref`` is set, _ref/libpoplibs_test_ref.so) with the Makefile here."""
+def build(ref: bool = False, reference_dir: str | None = None) -> None:
+    """Compile liboracle.so (and, when ``ref`` is set, _ref/libpoplibs_test_ref.so
+    from the reference tree at ``reference_dir``) with the Makefile here."""
     targets = ["all"] + (["ref"] if ref else [])
-    subprocess.run(["make", "-s", "-C", _HERE] + targets, check=True)
+    extra = [f"REFERENCE={reference_dir}"] if reference_dir else []
+    subprocess.run(["make", "-s", "-C", _HERE] + extra + targets, check=True)
 
 
 def _lib():

@@ -15,6 +15,7 @@ PASS_NONE, PASS_NONE_MATMUL, PASS_INFERENCE_FWD, PASS_TRAINING_FWD, PASS_TRAININ
     PASS_FC_TRAINING_WU = range(10)
 MAX_DIMS = 3
 PLAN_FORCE_RESIDENT_WEIGHTS, PLAN_NO_RESIDENT_WEIGHTS, PLAN_NO_HALO, PLAN_NO_CTA_PAIR, PLAN_FORCE_CTA_PAIR = 1, 2, 4, 8, 16
+PLAN_NO_TMA_STORE, PLAN_NO_PDL, PLAN_NO_A_COLLECTOR = 32, 64, 128
 _U3 = C.c_uint32 * MAX_DIMS
 
 
@@ -140,7 +141,7 @@ SYMBOLS = (
     "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution",
     "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
     "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_bias_update", "plb_conv_fwd_host",
-    "plb_allreduce_f32_p2p", "plb_allreduce_f32_p2p_rs", "plb_conv_wu_allreduce",
+    "plb_context_set_plan_flags", "plb_allreduce_f32_p2p", "plb_allreduce_f32_p2p_rs", "plb_conv_wu_allreduce",
     "plb_conv_wu_allreduce_flag_bytes", "plb_allreduce_p2p_signal_bytes", "plb_matmul_host_async",
     "plb_conv_fwd_host_async",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
@@ -196,6 +197,8 @@ def lib():
     L.plb_add_bias.argtypes = [vp, i32, vp, vp, u64, u32]
     L.plb_conv_bias_update.argtypes = [vp, i32, vp, u64, u32, i32, vp, f32]
     L.plb_allreduce_f32_p2p.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u32, sz, vp, vp]
+    L.plb_context_set_plan_flags.argtypes = [vp, i32]
+    L.plb_context_set_plan_flags.restype = None
     L.plb_allreduce_f32_p2p_rs.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), u32, sz,
                                            vp, vp]
     L.plb_conv_wu_allreduce.argtypes = [vp, CP, OP, vp, vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u32, vp, vp]
@@ -279,6 +282,10 @@ class Context:
 
     def launch_count(self) -> int:
         return int(lib().plb_launch_count(self._h))
+
+    def set_plan_flags(self, flags: int):
+        """PLAN_* bits added to every plan made for calls through this context."""
+        lib().plb_context_set_plan_flags(self._h, int(flags))
 
     # ---- hot path ---------------------------------------------------------
     def matmul(self, desc: MatmulDesc, a, b, c, d):

@@ -266,6 +266,7 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.bias = bias ? bias + size_t(g) * co : nullptr;
   r.out_f32 = p.output_type == PLB_FLOAT;
   r.force_tile_n = opt ? opt->tile_n : 0;
+  r.force_split_k = opt ? opt->split_k : 0;
   r.plan_flags = opt ? opt->plan_flags : 0;
   if (r.fp8 && opt) r.alpha = std::ldexp(1.0f, opt->scale_in + opt->scale_weights);
   *q = r;
@@ -332,6 +333,7 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   r.out_stride_n = (long long)(ctot * s.W * s.H);
   r.out_f32 = p.output_type == PLB_FLOAT;
   r.force_tile_n = opt ? opt->tile_n : 0;
+  r.force_split_k = opt ? opt->split_k : 0;
   r.plan_flags = opt ? opt->plan_flags : 0;
   if (r.fp8 && opt) r.alpha = std::ldexp(1.0f, opt->scale_in + opt->scale_weights);
   *q = r;
@@ -570,7 +572,8 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
         r.out_stride_n = (long long)(ctot * s.W * s.H);
         r.out_f32 = p.output_type == PLB_FLOAT;
         r.force_tile_n = opt ? opt->tile_n : 0;
-        r.plan_flags = opt ? opt->plan_flags : 0;
+        r.force_split_k = opt ? opt->split_k : 0;
+        r.plan_flags = (opt ? opt->plan_flags : 0) | ctx->plan_flags;
         plb_plan plan{};
         if (int rc = planIgemm(r, ctx->sm_count, &plan)) return rc;
         if (int rc = launchIgemm(ctx, r, plan)) return rc;
@@ -606,6 +609,7 @@ int plb_matmul_plan(const plb_matmul_desc *desc, plb_plan *plan) {
 
 int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a, const void *d_b,
                const void *d_c, void *d_d) {
+  TraceRange trace_range("plb_matmul");
   if (int rc = activate(ctx)) return rc;
   if (!desc) return fail(PLB_ERR_INVALID_PARAMS, "null descriptor");
   const plb_matmul_desc &d = *desc;
@@ -667,6 +671,7 @@ int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a, c
     IgemmProblem p = gemmProblem(d, ag, lda, bg, ldb, b_is_nk,
                                  d_c ? static_cast<const uint8_t *>(d_c) + coff : nullptr,
                                  static_cast<uint8_t *>(d_d) + coff, ld.c);
+    p.plan_flags |= ctx->plan_flags;
     plb_plan plan{};
     if (int rc = planIgemm(p, ctx->sm_count, &plan)) return rc;
     if (int rc = launchIgemm(ctx, p, plan)) return rc;
@@ -777,6 +782,7 @@ int plb_conv_plan(const plb_conv_params *p_in, const plb_conv_options *opt, int3
 int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
                     const void *d_in, const void *d_weights, const float *d_bias, void *d_out,
                     int transpose_and_flip_weights) {
+  TraceRange trace_range("plb_convolution");
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
   {
@@ -913,6 +919,7 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
   for (unsigned g = 0; g < p->groups; ++g) {
     IgemmProblem q;
     if (int rc = convFwdProblem(*p, opt, s, g, d_in, w, d_bias, d_out, &q, swapped)) return rc;
+    q.plan_flags |= ctx->plan_flags;
     plb_plan plan{};
     if (int rc = planIgemm(q, ctx->sm_count, &plan)) return rc;
     if (int rc = launchIgemm(ctx, q, plan)) return rc;
@@ -927,6 +934,7 @@ int plb_conv_fwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
 
 int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
                  const void *d_out_grads, const void *d_weights, void *d_in_grads) {
+  TraceRange trace_range("plb_conv_bwd");
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
   {
@@ -1035,6 +1043,7 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
   for (unsigned g = 0; g < p->groups; ++g) {
     IgemmProblem q;
     if (int rc = convBwdProblem(*p, opt, s, g, d_out_grads, w, d_in_grads, transposed, &q)) return rc;
+    q.plan_flags |= ctx->plan_flags;
     plb_plan plan{};
     if (int rc = planIgemm(q, ctx->sm_count, &plan)) return rc;
     if (int rc = launchIgemm(ctx, q, plan)) return rc;

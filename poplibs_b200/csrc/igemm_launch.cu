@@ -15,44 +15,10 @@ namespace plb {
 
 namespace {
 
-// PLB_DISABLE_TMA_STORE=1 forces the plain vector-store epilogue (for A/B timing).
-const bool g_disable_tma_store = [] {
-  const char *e = std::getenv("PLB_DISABLE_TMA_STORE");
-  return e != nullptr && e[0] == '1';
-}();
-// PLB_DISABLE_HALO=1 loads one activation box per filter tap even where a strip
-// with a halo could serve a whole filter column.
-const bool g_disable_halo = [] {
-  const char *e = std::getenv("PLB_DISABLE_HALO");
-  return e != nullptr && e[0] == '1';
-}();
-// PLB_DISABLE_RESIDENT_WEIGHTS=1 keeps the weights in the streamed pipeline.
-const bool g_disable_resident = [] {
-  const char *e = std::getenv("PLB_DISABLE_RESIDENT_WEIGHTS");
-  return e != nullptr && e[0] == '1';
-}();
-
-// PLB_DISABLE_PDL=1 launches without programmatic stream serialization.
-const bool g_disable_pdl = [] {
-  const char *e = std::getenv("PLB_DISABLE_PDL");
-  return e != nullptr && e[0] == '1';
-}();
-// PLB_DISABLE_CTA_PAIR=1 keeps every CTA on its own 128-row MMAs.
-const bool g_disable_pair = [] {
-  const char *e = std::getenv("PLB_DISABLE_CTA_PAIR");
-  return e != nullptr && e[0] == '1';
-}();
-
-// PLB_FORCE_CTA_PAIR=1 (read at every plan, so a test can toggle it) pairs CTAs
-// whenever the shape allows, also for calls that carry no plan flags.
-bool forcePairFromEnv() {
-  const char *e = std::getenv("PLB_FORCE_CTA_PAIR");
-  return e != nullptr && e[0] == '1';
-}
-
 template <int BN, bool kFp8, bool kBMn, bool kResB, bool kHalo, bool k2Cta>
 int launchInstance(plb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb,
-                   const CUtensorMap &tout, const IgemmArgs &args, int grid, int resident_bytes) {
+                   const CUtensorMap &tout, const IgemmArgs &args, int grid, int resident_bytes,
+                   bool pdl) {
   if constexpr (k2Cta && kBMn && BN < 128) {
     return fail(PLB_ERR_INVALID_OPTION, "a CTA pair needs tile_n >= 128 for a row-major B");
   } else {
@@ -77,7 +43,7 @@ int launchInstance(plb_context *ctx, const CUtensorMap &ta, const CUtensorMap &t
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
     unsigned n_attr = 0;
-    if (!g_disable_pdl) {
+    if (pdl) {
       attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
       attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
       ++n_attr;
@@ -210,9 +176,8 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
   const long k_steps_per_tile =
       long(p.taps_h) * p.taps_w * ((p.k_per_tap + k_elems_stage - 1) / k_elems_stage);
   const int sms_for_pair = sm_count > 0 ? sm_count : 148;
-  const bool pair = !g_disable_pair && (p.plan_flags & PLB_PLAN_NO_CTA_PAIR) == 0 &&
-                    (!p.b_mn || bn >= 128) &&
-                    ((p.plan_flags & PLB_PLAN_FORCE_CTA_PAIR) != 0 || forcePairFromEnv()
+  const bool pair = (p.plan_flags & PLB_PLAN_NO_CTA_PAIR) == 0 && (!p.b_mn || bn >= 128) &&
+                    ((p.plan_flags & PLB_PLAN_FORCE_CTA_PAIR) != 0
                          ? best_tiles >= 2
                          : (k_steps_per_tile >= (bn >= 256 ? 4 : 8) &&
                             best_tiles * n_tiles >= 2L * sms_for_pair));
@@ -230,7 +195,7 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
   const bool want_resident = (p.plan_flags & PLB_PLAN_FORCE_RESIDENT_WEIGHTS) != 0 ||
                              plan->tiles >= 2 * plan->grid;
   plan->resident_weights =
-      (!g_disable_resident && (p.plan_flags & PLB_PLAN_NO_RESIDENT_WEIGHTS) == 0 && n_tiles == 1 &&
+      ((p.plan_flags & PLB_PLAN_NO_RESIDENT_WEIGHTS) == 0 && n_tiles == 1 &&
        resident_bytes <= kMaxResidentBytes && want_resident)
           ? 1
           : 0;
@@ -242,7 +207,7 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
   // instead of box_h rows per tap.  The tile rows are ordered (w, n, h) so that
   // a vertical shift is a whole number of 8-row groups: box_w * box_n % 8 == 0.
   const int halo = (p.taps_h - 1) * p.dil_h;
-  if (!g_disable_halo && (p.plan_flags & PLB_PLAN_NO_HALO) == 0 && p.taps_h > 1 &&
+  if ((p.plan_flags & PLB_PLAN_NO_HALO) == 0 && p.taps_h > 1 &&
       p.stride_h == 1) {
     // Shared-memory fill per pixel tile and channel chunk, the quantity that
     // bounds a layer whose tensor-core work is short: activation rows plus,
@@ -288,8 +253,123 @@ int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan) {
   }
   plan->b_mn_major = p.b_mn ? 1 : 0;
   plan->workspace_bytes = 0;
+  // ---- split-K ---------------------------------------------------------------
+  // A product with few output tiles and a long reduction leaves most SMs idle:
+  // let several CTAs share a tile, each taking a range of its pipeline steps,
+  // and add their fp32 partial sums in a second kernel.  Model (microseconds):
+  // a pipeline step of one CTA takes about 0.17 (the producers' issue rate
+  // bounds short tiles), the extra kernel about 5 plus its traffic at a few
+  // TB/s; the split must save more than it costs.  512 x 1024 x 1024 stays
+  // unsplit (16 steps: 2.7 against 1.4 + 5), 256 x 8192 x 256 splits.
+  {
+    const long units = plan->tiles / (pair ? 2 : 1) + (pair ? plan->tiles % 2 : 0);
+    const long steps = plan->halo_rows > 0 ? long(p.taps_w) * ((p.k_per_tap + k_elems - 1) / k_elems)
+                                           : k_iters;
+    const long sms = sm_count > 0 ? sm_count : 148;
+    int split = 1;
+    if (p.force_split_k > 0) {
+      split = int(std::min<long>(p.force_split_k, steps));
+    } else if (units * 2 <= sms && steps >= 16) {
+      const double out_mb = double(p.out_w) * p.out_h * p.out_n * p.n_total * 4 / 1e6;
+      double best = 0.17 * double(steps);
+      for (long sp = 2; sp <= std::min<long>(steps / 4, sms / units); ++sp) {
+        const double t = 0.17 * double((steps + sp - 1) / sp) + 5.0 + out_mb * double(sp + 1) / 4000.0;
+        if (t < best) {
+          best = t;
+          split = int(sp);
+        }
+      }
+    }
+    if (split > 1 && long(plan->tiles) * split > 0x3fffffffL) split = 1;
+    plan->split_k = split;
+    if (split > 1) {
+      const long units_total = units * split;
+      plan->grid = pair ? int(2 * std::min<long>(units_total, sms / 2)) : int(std::min<long>(units_total, sms));
+      const size_t ld_p = (size_t(p.n_total) + 31) / 32 * 32;
+      plan->workspace_bytes = uint64_t(split) * p.out_w * p.out_h * p.out_n * ld_p * sizeof(float);
+    }
+  }
   return PLB_OK;
 }
+
+namespace {
+
+// Second kernel of a split-K product: adds the splits' partial sums in split
+// order (a fixed order, so the result does not depend on timing) and applies
+// what the implicit-GEMM kernel's own epilogue would have: alpha, bias, the
+// beta-scaled addend, the cast.  One thread per four consecutive channels of
+// one output pixel.
+struct SplitKReduceArgs {
+  const float *partial;
+  int split_k;
+  long long split_stride;  // elements between splits
+  int ld_p;                // elements between pixels in the partial sums
+  int n_total, out_w, out_h, out_n;
+  void *out;
+  long long ldc, out_stride_h, out_stride_n;
+  const void *addend;
+  long long ld_addend;
+  const float *bias;
+  float alpha, beta;
+  int out_is_f32;
+};
+
+__global__ void __launch_bounds__(256) igemm_splitk_reduce_kernel(const SplitKReduceArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();  // the partial sums come from the previous kernel in the stream
+  const int quads = (a.n_total + 3) / 4;
+  const long long pixels = (long long)a.out_w * a.out_h * a.out_n;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < pixels * quads;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long pixel = i / quads;
+    const int c = int(i - pixel * quads) * 4;
+    const float *src = a.partial + pixel * a.ld_p + c;
+    float4 s = *reinterpret_cast<const float4 *>(src);
+    for (int k = 1; k < a.split_k; ++k) {
+      const float4 v = *reinterpret_cast<const float4 *>(src + k * a.split_stride);
+      s.x += v.x;
+      s.y += v.y;
+      s.z += v.z;
+      s.w += v.w;
+    }
+    float f[4] = {s.x, s.y, s.z, s.w};
+    const int valid = min(4, a.n_total - c);
+    if (a.alpha != 1.f)
+      for (int j = 0; j < 4; ++j) f[j] *= a.alpha;
+    if (a.bias != nullptr)
+      for (int j = 0; j < valid; ++j) f[j] += a.bias[c + j];
+    if (a.addend != nullptr) {
+      if (a.out_is_f32) {
+        const float *ad = static_cast<const float *>(a.addend) + pixel * a.ld_addend + c;
+        for (int j = 0; j < valid; ++j) f[j] += a.beta * ad[j];
+      } else {
+        const __half *ad = static_cast<const __half *>(a.addend) + pixel * a.ld_addend + c;
+        for (int j = 0; j < valid; ++j) f[j] += a.beta * __half2float(ad[j]);
+      }
+    }
+    const long long ow = pixel % a.out_w, rest = pixel / a.out_w;
+    const long long oh = rest % a.out_h, on = rest / a.out_h;
+    const long long off = on * a.out_stride_n + oh * a.out_stride_h + ow * a.ldc + c;
+    if (a.out_is_f32) {
+      float *dst = static_cast<float *>(a.out) + off;
+      if (valid == 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0)
+        *reinterpret_cast<float4 *>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+      else
+        for (int j = 0; j < valid; ++j) dst[j] = f[j];
+    } else {
+      __half *dst = static_cast<__half *>(a.out) + off;
+      if (valid == 4 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+        const __half2 lo = __floats2half2_rn(f[0], f[1]), hi = __floats2half2_rn(f[2], f[3]);
+        *reinterpret_cast<uint2 *>(dst) = make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                                                     *reinterpret_cast<const uint32_t *>(&hi));
+      } else {
+        for (int j = 0; j < valid; ++j) dst[j] = __float2half_rn(f[j]);
+      }
+    }
+  }
+}
+
+}  // namespace
 
 int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   const int elem = p.fp8 ? 1 : 2;
@@ -337,6 +417,18 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   }
 
   IgemmArgs a{};
+  a.split_k = std::max(1, int(plan.split_k));
+  a.fd_split = make_fastdiv(uint32_t(a.split_k));
+  const bool split = a.split_k > 1;
+  const size_t ld_p = (size_t(p.n_total) + 31) / 32 * 32;
+  float *partial = nullptr;
+  if (split) {
+    void *ws = nullptr;
+    a.split_stride = (long long)p.out_w * p.out_h * p.out_n * (long long)ld_p;
+    if (int rc = scratch(ctx, kSlotSplitK, size_t(a.split_k) * size_t(a.split_stride) * sizeof(float), &ws))
+      return rc;
+    partial = static_cast<float *>(ws);
+  }
   // Output through TMA when the tensor can be described to it: 16-byte aligned
   // base and pixel stride.  Each epilogue warp stores a (columns, w, h, n) box
   // holding its 32 pixels and 32 columns: 128-byte rows of fp32, 64-byte rows
@@ -353,7 +445,8 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.sub_h = std::min(d2, 32 / a.sub_w);  // extent along the second row dimension
   const int sub_3 = 32 / (a.sub_w * a.sub_h);
   a.use_tma_store = 0;
-  if (!g_disable_tma_store && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
+  if (!split && (p.plan_flags & PLB_PLAN_NO_TMA_STORE) == 0 &&
+      (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
       (size_t(p.ldc) * out_es) % 16 == 0 && (size_t(out_stride_h) * out_es) % 16 == 0 &&
       (size_t(out_stride_n) * out_es) % 16 == 0) {
     uint64_t dims[4] = {uint64_t(p.n_total), 0, 0, 0}, strides[3];
@@ -415,23 +508,34 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.addend = p.beta != 0.f ? p.addend : nullptr;
   a.ld_addend = p.ld_addend;
   a.bias = p.bias;
+  if (split) {
+    // raw fp32 sums, dense in pixels, into this split's slice of the scratch
+    a.out = partial;
+    a.ldc = (long long)ld_p;
+    a.out_stride_h = (long long)p.out_w * a.ldc;
+    a.out_stride_n = (long long)p.out_h * a.out_stride_h;
+    a.addend = nullptr;
+    a.bias = nullptr;
+  }
   a.idesc_formats = p.fp8 ? make_idesc(0, 0, uint32_t(p.fmt_a & 1), uint32_t(p.fmt_b & 1), false, false) & ~(1u << 4)
                           : 0u;
-  a.alpha = p.alpha;
-  a.beta = p.beta;
-  a.out_is_f32 = p.out_f32 ? 1 : 0;
+  a.alpha = split ? 1.f : p.alpha;
+  a.beta = split ? 0.f : p.beta;
+  a.out_is_f32 = split || p.out_f32 ? 1 : 0;
   a.status = ctx->d_status;
   a.trace = ctx->trace;
 
   const int grid = plan.grid;
+  const bool pdl = (p.plan_flags & PLB_PLAN_NO_PDL) == 0;
+  auto dispatch = [&]() -> int {
 #define PLB_DISPATCH3(BN, RES, HALO, PAIR)                                                            \
   if (p.fp8)                                                                                          \
     return launchInstance<BN, true, false, RES, HALO, PAIR>(ctx, ta, tb, tout, a, grid,               \
-                                                            resident_bytes);                          \
+                                                            resident_bytes, pdl);                          \
   if (p.b_mn)                                                                                         \
     return launchInstance<BN, false, true, RES, HALO, PAIR>(ctx, ta, tb, tout, a, grid,               \
-                                                            resident_bytes);                          \
-  return launchInstance<BN, false, false, RES, HALO, PAIR>(ctx, ta, tb, tout, a, grid, resident_bytes);
+                                                            resident_bytes, pdl);                          \
+  return launchInstance<BN, false, false, RES, HALO, PAIR>(ctx, ta, tb, tout, a, grid, resident_bytes, pdl);
 #define PLB_DISPATCH2(BN, RES, HALO)     \
   if (plan.cta_pair) {                   \
     PLB_DISPATCH3(BN, RES, HALO, true)   \
@@ -457,7 +561,44 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
 #undef PLB_DISPATCH
 #undef PLB_DISPATCH2
 #undef PLB_DISPATCH3
-  return fail(PLB_ERR_INVALID_OPTION, "unsupported tile_n in plan");
+    return fail(PLB_ERR_INVALID_OPTION, "unsupported tile_n in plan");
+  };
+  if (int rc = dispatch()) return rc;
+  if (!split) return PLB_OK;
+  SplitKReduceArgs r{};
+  r.partial = partial;
+  r.split_k = a.split_k;
+  r.split_stride = a.split_stride;
+  r.ld_p = int(ld_p);
+  r.n_total = p.n_total;
+  r.out_w = p.out_w;
+  r.out_h = p.out_h;
+  r.out_n = p.out_n;
+  r.out = p.out;
+  r.ldc = p.ldc;
+  r.out_stride_h = out_stride_h;
+  r.out_stride_n = out_stride_n;
+  r.addend = p.beta != 0.f ? p.addend : nullptr;
+  r.ld_addend = p.ld_addend;
+  r.bias = p.bias;
+  r.alpha = p.alpha;
+  r.beta = p.beta;
+  r.out_is_f32 = p.out_f32 ? 1 : 0;
+  const long long work = (long long)p.out_w * p.out_h * p.out_n * ((p.n_total + 3) / 4);
+  cudaLaunchAttribute pdl_attr[1];
+  pdl_attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl_attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(std::max<long long>(1, std::min<long long>((work + 255) / 256,
+                                                                         (long long)ctx->sm_count * 8))));
+  cfg.blockDim = dim3(256);
+  cfg.stream = ctx->stream;
+  cfg.attrs = pdl_attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  PLB_CUDA(cudaLaunchKernelEx(&cfg, igemm_splitk_reduce_kernel, r));
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
 }
 
 }  // namespace plb

@@ -76,6 +76,15 @@ struct IgemmArgs {
   // division by group_m * n_tiles, group_m, tiles_w and (h_outer ? tiles_n : tiles_h)
   FastDiv fd_band, fd_gm, fd_tw, fd_inner;
   int num_stages;  // pipeline depth (<= kIgemmMaxStages)
+  // Split-K: split_k CTAs share one output tile, each taking a contiguous range
+  // of the tile's pipeline steps and leaving raw fp32 sums in its own slice of
+  // a scratch tensor (`out`, split_stride elements apart), which a second
+  // kernel adds in split order before the scale / add / cast.  The role of the
+  // reference's inChanSplit / kernelSplit partitions and the reduction that
+  // follows them (lib/poplin/ConvPlan.hpp:28-77, lib/poplin/ConvReduce.cpp:316-362).
+  int split_k;
+  FastDiv fd_split;
+  long long split_stride;
   uint32_t idesc_formats;  // operand format bits of the instruction descriptor (8-bit operands: 1 = E5M2)
   // ---- epilogue ---------------------------------------------------------------
   void *out;
@@ -250,6 +259,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   const int m_tiles = args.tiles_w * args.tiles_h * args.tiles_n;
   const int m_units = k2Cta ? (m_tiles + 1) / 2 : m_tiles;
   const int total_tiles = m_units * args.n_tiles;
+  // a unit of work is an output tile, or with split-K one of its K ranges
+  // (the splits of a tile are consecutive units, i.e. run on different CTAs)
+  const int total_units = total_tiles * args.split_k;
   const int first_unit = k2Cta ? int(blockIdx.x >> 1) : int(blockIdx.x);
   const int unit_stride = k2Cta ? int(gridDim.x >> 1) : int(gridDim.x);
   // barriers of the CTA that issues the MMAs, as cluster addresses
@@ -264,6 +276,20 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   // put four 64-bit divisions into every thread's prologue)
   const FastDiv fd_band = args.fd_band, fd_gm = args.fd_gm, fd_tw = args.fd_tw, fd_inner = args.fd_inner;
 
+  // unit -> (tile, range [it_begin, it_end) of the tile's pipeline steps)
+  auto unit_coords = [&](int unit, int &tile, int &split, int &it_begin, int &it_end) {
+    if (args.split_k == 1) {
+      tile = unit;
+      split = 0;
+      it_begin = 0;
+      it_end = p_iters;
+    } else {
+      tile = int(fast_div(uint32_t(unit), args.fd_split));
+      split = unit - tile * args.split_k;
+      it_begin = int(fast_div(uint32_t(p_iters * split), args.fd_split));
+      it_end = int(fast_div(uint32_t(p_iters * (split + 1)), args.fd_split));
+    }
+  };
   // tile index -> (m tile, n tile): bands of group_m M tiles, M fastest inside a band
   auto tile_coords = [&](int tile, int &m_idx, int &n_idx) {
     const int band_tiles = args.group_m * args.n_tiles;
@@ -381,13 +407,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       };
       // While the predecessor kernel may still be running: pull the boxes of
       // this producer's first steps towards L2.
-      if (first_unit < total_tiles) {
+      if (first_unit < total_units) {
+        int tile, split, it_begin, it_end;
+        unit_coords(first_unit, tile, split, it_begin, it_end);
         int m_idx, n_idx;
-        tile_coords(first_unit, m_idx, n_idx);
+        tile_coords(tile, m_idx, n_idx);
         int w0, h0, n0;
         tile_origin(m_idx, w0, h0, n0);
-        const int steps = min(p_iters, kStages);
-        for (int it = me; it < steps; it += P) {
+        const int steps = min(it_end, it_begin + kStages);
+        for (int it = it_begin + me; it < steps; it += P) {
           int r, s, kc;
           step_coords(it, r, s, kc);
           issue_step(true, 0u, 0u, r, s, kc, w0 * args.stride_w - args.pad_w,
@@ -396,8 +424,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       }
       pdl_wait();
       if (me == 0) PLB_TRACE_STAMP(2, 4002);
-      for (int tile = first_unit; tile < total_tiles && ok; tile += unit_stride) {
+      for (int unit = first_unit; unit < total_units && ok; unit += unit_stride) {
         if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
+        int tile, split, it_begin, it_end;
+        unit_coords(unit, tile, split, it_begin, it_end);
         int m_idx, n_idx;
         tile_coords(tile, m_idx, n_idx);
         int w0, h0, n0;
@@ -407,7 +437,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         const int h_base = h0 * args.stride_h - args.pad_h;
         const int n_col = n_idx * BN;
         int r = 0, s = 0, kc = 0;
-        for (int it = 0; it < p_iters; ++it) {
+        if (it_begin != 0) step_coords(it_begin, r, s, kc);
+        for (int it = it_begin; it < it_end; ++it) {
           if (turn == me) {
             if (me == 0) { PLB_TRACE_STAMP(0, trace_slot); ++trace_slot; }
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
@@ -472,13 +503,15 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       int local_tile = 0;
       bool ok = true;
       [[maybe_unused]] int trace_slot = 0;
-      if (kResB && first_unit < total_tiles) {
+      if (kResB && first_unit < total_units) {
         if (!mbar_wait(resb_bar, 0, abort_flag)) {
           atomicCAS(args.status, kStatusOk, kStatusMmaTimeout);
           ok = false;
         }
       }
-      for (int tile = first_unit; tile < total_tiles && ok; tile += unit_stride, ++local_tile) {
+      for (int unit = first_unit; unit < total_units && ok; unit += unit_stride, ++local_tile) {
+        int tile, split, it_begin, it_end;
+        unit_coords(unit, tile, split, it_begin, it_end);
         const int acc = local_tile & 1;
         PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
         // wait for the epilogue to have drained this accumulator
@@ -492,7 +525,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
         const uint32_t d_tmem = tmem_base + acc * BN;
         int s_tap = 0, kc = 0;  // halo mode: pipeline step = (s_tap, kc), kc fastest
-        for (int it = 0; it < p_iters; ++it) {
+        if (kHalo && it_begin != 0) {
+          kc = it_begin % args.k_chunks;
+          s_tap = it_begin / args.k_chunks;
+        }
+        for (int it = it_begin; it < it_end; ++it) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
             atomicCAS(args.status, kStatusOk, kStatusMmaTimeout);
             ok = false;
@@ -523,9 +560,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
               const uint64_t b_k =
                   b_desc + uint64_t(kBMn ? k * ((16 * kStageKBytes) >> 4) : k * 2);
               if constexpr (k2Cta)
-                umma_ss_pair<kFp8>(d_tmem, a_k, b_k, idesc, (it | r | k) != 0 ? 1u : 0u);
+                umma_ss_pair<kFp8>(d_tmem, a_k, b_k, idesc, ((it - it_begin) | r | k) != 0 ? 1u : 0u);
               else
-                umma_ss<kFp8>(d_tmem, a_k, b_k, idesc, (it | r | k) != 0 ? 1u : 0u);
+                umma_ss<kFp8>(d_tmem, a_k, b_k, idesc, ((it - it_begin) | r | k) != 0 ? 1u : 0u);
             }
             if constexpr (kHalo) {
               // next filter row: the strip shifted by whole 8-row groups; its
@@ -604,7 +641,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       // copies (a copy costs its issuing thread some hundred cycles, and the
       // first MMA waits for all of them), leaving the producers free to start
       // on the activations at once.
-      if (lane == 0 && first_unit < total_tiles) {
+      if (lane == 0 && first_unit < total_units) {
         for (int it = warp - 4; it < k_iters; it += 16) {
           int r, s, kc;
           step_coords(it, r, s, kc);
@@ -624,8 +661,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       __syncwarp();
     }
     pdl_wait();
-    for (int tile = first_unit + group * unit_stride; tile < total_tiles;
-         tile += 2 * unit_stride, local_tile += 2) {
+    for (int unit = first_unit + group * unit_stride; unit < total_units;
+         unit += 2 * unit_stride, local_tile += 2) {
+      int tile, split, it_begin, it_end;
+      unit_coords(unit, tile, split, it_begin, it_end);
       int m_idx, n_idx;
       tile_coords(tile, m_idx, n_idx);
       int w0, h0, n0;
@@ -696,7 +735,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         const int valid = min(32, args.n_total - col0);
         if (!row_ok || valid <= 0) return;
         if (out_f32) {
-          float *dst = static_cast<float *>(args.out) + out_off + col0;
+          // (with split-K: this split's slice of the partial sums)
+          float *dst = static_cast<float *>(args.out) + split * args.split_stride + out_off + col0;
           if (valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
             // whole 32-byte sectors per lane
 #pragma unroll
@@ -840,9 +880,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   // the other CTA cannot leave before the rendezvous below.
   __syncthreads();
   if (*abort_flag != 0 && threadIdx.x == 0 && leader) {
-    const int my_tiles =
-        total_tiles > first_unit ? (total_tiles - first_unit + unit_stride - 1) / unit_stride : 0;
-    const long long total_steps = (long long)my_tiles * p_iters;
+    int my_tiles = 0;
+    long long total_steps = 0;
+    for (int unit = first_unit; unit < total_units; unit += unit_stride, ++my_tiles) {
+      int tile, split, it_begin, it_end;
+      unit_coords(unit, tile, split, it_begin, it_end);
+      total_steps += it_end - it_begin;
+    }
     const long long start = clock64();
     auto drain = [&](uint32_t bar, uint32_t parity) {
       while (!mbar_try_wait(bar, parity)) {

@@ -633,6 +633,10 @@ void *plb_context_stream(plb_context *ctx) { return ctx ? ctx->stream : nullptr;
 
 uint64_t plb_launch_count(const plb_context *ctx) { return ctx ? ctx->launches : 0; }
 
+void plb_context_set_plan_flags(plb_context *ctx, int32_t plan_flags) {
+  if (ctx) ctx->plan_flags = plan_flags;
+}
+
 int plb_synchronize(plb_context *ctx) {
   if (int rc = activate(ctx)) return rc;
   PLB_CUDA(cudaStreamSynchronize(ctx->stream));

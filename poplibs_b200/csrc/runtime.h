@@ -29,6 +29,7 @@ enum plb_scratch_slot {
   kSlotFoldedWeights,
   kSlotFoldedGrads,
   kSlotDilated,         // zero-stuffed input (input dilation)
+  kSlotSplitK,          // fp32 partial sums of a split-K forward / backward / matrix product
   kSlotCount
 };
 
@@ -43,6 +44,7 @@ struct plb_context {
   int *d_status = nullptr;        // device address
   volatile int *h_status = nullptr;  // host address of the same word
   uint64_t launches = 0;          // kernels launched through this context
+  int plan_flags = 0;             // PLB_PLAN_* bits added to every plan made through this context
   long long *trace = nullptr;     // device timeline buffer for builds with -DPLB_TRACE
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
   // grow-only scratch buffers, one per use (plb_scratch_slot)
@@ -51,7 +53,20 @@ struct plb_context {
   size_t scratch_bytes[kScratchSlots] = {};
 };
 
+#include <nvtx3/nvToolsExt.h>
+
 namespace plb {
+
+// A named range around a public entry point, visible to profilers that hook
+// NVTX (the role of POPLIN_TRACEPOINT at the reference's entry points,
+// include/poplibs_support/Tracepoint.hpp:69-78).  Header-only: without a
+// profiler attached the calls are a null-pointer test each.
+struct TraceRange {
+  explicit TraceRange(const char *name) { nvtxRangePushA(name); }
+  ~TraceRange() { nvtxRangePop(); }
+  TraceRange(const TraceRange &) = delete;
+  TraceRange &operator=(const TraceRange &) = delete;
+};
 
 // Records the message for plb_last_error() and returns `code`.
 int fail(int code, const std::string &message);
@@ -166,6 +181,7 @@ struct IgemmProblem {
   float alpha = 1.f, beta = 0.f;
   bool out_f32 = false;
   int force_tile_n = 0;  // 0 = planner's choice
+  int force_split_k = 0; // 0 = planner's choice; n = n CTAs per output tile (clamped to the K steps)
   int plan_flags = 0;    // PLB_PLAN_* bits
 };
 

@@ -114,11 +114,8 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
   // rows' accumulators in TMEM at once and box_w * box_n a multiple of 8; taken
   // when it costs at most 1/8 more pixel tiles than the best box.
   a->strip_mode = 0;
-  {
-    // measurement switch: fetch the outGrad tile for every instruction
-    const char *e = std::getenv("PLB_DISABLE_COLLECTOR");
-    a->reuse_a = (e && e[0] == '1') ? 0 : 1;
-  }
+  // PLB_PLAN_NO_A_COLLECTOR: fetch the outGrad tile for every instruction (A/B timing)
+  a->reuse_a = (plan_flags & PLB_PLAN_NO_A_COLLECTOR) ? 0 : 1;
   const int halo = (s.KH - 1) * s.dilH;
   if (s.KH > 1 && s.strH == 1 && s.KH * a->ci_blk <= 512 && (plan_flags & PLB_PLAN_NO_HALO) == 0) {
     long sbest = -1;
@@ -384,6 +381,7 @@ int plb_conv_wu_plan(const plb_conv_params *p_in, const plb_conv_options *opt, p
 int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
                 const void *d_acts, const void *d_out_grads, void *d_weight_grads,
                 float *d_weight_grads_f32) {
+  TraceRange trace_range("plb_conv_wu");
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
   {
@@ -534,7 +532,8 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
     return PLB_OK;
   }
   WuArgs a{};
-  planWu(*p, s, ctx->sm_count, opt ? opt->split_k : 0, opt ? opt->plan_flags : 0, &a, nullptr);
+  planWu(*p, s, ctx->sm_count, opt ? opt->split_k : 0, (opt ? opt->plan_flags : 0) | ctx->plan_flags, &a,
+         nullptr);
   a.status = ctx->d_status;
   a.trace = ctx->trace;
   void *ws = nullptr;
@@ -566,6 +565,7 @@ int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p, const plb_
                           const void *d_acts, const void *d_out_grads, int32_t rank, int32_t world,
                           void *const *d_peer_grads, void *const *d_peer_flags, uint32_t epoch,
                           void *d_weight_grads, float *d_weight_grads_f32) {
+  TraceRange trace_range("plb_conv_wu_allreduce");
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
   if (world < 1 || world > kWuPeerMaxWorld || rank < 0 || rank >= world)

@@ -371,11 +371,58 @@ def test_conv_plan_variants_agree_with_oracle(gpu_ctx, name, variant):
     assert_exact(T.gpu_conv_bwd(p, dy, w, opt=opt), oracle.conv_bwd(spec, dy, w), f"bwd {name} {variant}")
 
 
+@pytest.mark.parametrize("split", [2, 3, 5])
+@pytest.mark.parametrize("variant", ["streamed", "resident_halo", "streamed_pair", "resident_halo_pair", "no_pair"])
+@pytest.mark.parametrize("name", ["3x3_pad1", "ragged_chans", "3x3_s2x3", "batch1_big_field"])
+def test_conv_split_k_agrees_with_oracle(gpu_ctx, name, variant, split):
+    """Forward and backward with several CTAs per output tile (the reduction
+    dimension split, fp32 partial sums added by a second kernel in split order)
+    under every way the planner may run the layer: the oracle's result, bit for
+    bit, with a bias and with fp32 output as well."""
+    kw = {**SMALL_CONVS, **STRIDED_CONVS}[name]
+    p = capi.ConvParams.make(**kw)
+    spec = T.spec_from_params(p)
+    opt = capi.ConvOptions.make(plan_flags=PLAN_VARIANTS[variant], split_k=split)
+    plan = capi.conv_plan(p, capi.PASS_TRAINING_FWD, opt)
+    assert 1 <= plan.split_k <= split and (plan.split_k > 1) == (plan.workspace_bytes > 0)
+    r = T.rng(zlib.crc32((name + variant).encode()) % 1000 + split)
+    x, w, dy = conv_data(p, kw, r, exact=True)
+    assert_exact(T.gpu_conv_fwd(p, x, w, opt=opt), oracle.conv_fwd(spec, x, w), f"fwd {name} {variant} /{split}")
+    assert_exact(T.gpu_conv_bwd(p, dy, w, opt=opt), oracle.conv_bwd(spec, dy, w), f"bwd {name} {variant} /{split}")
+    bias = r.integers(-3, 4, size=p.groups * p.out_chans_per_group).astype(np.float32)
+    pf = capi.ConvParams.make(output_type=capi.FLOAT, **kw)
+    assert_exact(T.gpu_conv_fwd(pf, x, w, bias=bias, opt=opt), oracle.conv_fwd(spec, x, w, bias=bias),
+                 f"fwd fp32 + bias {name} {variant} /{split}")
+
+
+def test_matmul_long_k_is_split_by_the_planner(gpu_ctx):
+    """Few output tiles and a long reduction: the planner gives each tile to
+    several CTAs by itself; results stay exact, also with alpha, beta and C."""
+    m, k, n = 256, 8192, 256
+    plan = capi.matmul_plan(capi.MatmulDesc.make(m, k, n))
+    assert plan.split_k > 1 and plan.grid > plan.tiles
+    assert capi.matmul_plan(capi.MatmulDesc.make(512, 1024, 1024)).split_k == 1   # too short to pay
+    r = T.rng(5)
+    a, b = T.binary_half(r, (m, k)), T.binary_half(r, (k, n))
+    assert_exact(T.gpu_matmul(a, b, out_dtype=np.float32), oracle.gemm(a, b), "split matmul")
+    bt = np.ascontiguousarray(b.T)
+    assert_exact(T.gpu_matmul(a, bt, transpose_b=True, out_dtype=np.float32), oracle.gemm(a, b),
+                 "split matmul, transposed B")
+    c = T.small_int_half(r, (m, n)).astype(np.float32)
+    got = T.gpu_matmul(a, b, c, alpha=0.5, beta=2.0, out_dtype=np.float32)
+    assert_exact(got, oracle.gemm(a, b, c, alpha=0.5, beta=2.0), "split matmul with alpha, beta, C")
+    # quarter input (half output): sparse right operand keeps the sums exactly representable
+    av = r.integers(-1, 2, size=(m, k)).astype(np.float64)
+    bv = (r.integers(-2, 3, size=(n, k)) * (r.integers(0, 16, size=(n, k)) == 0)).astype(np.float64)
+    got = T.gpu_matmul(oracle.e4m3_encode(av), oracle.e4m3_encode(bv), transpose_b=True)
+    assert_exact(got, oracle.gemm(av, bv, transpose_b=True), "split quarter matmul")
+
+
 @pytest.fixture
 def force_cta_pair():
-    os.environ["PLB_FORCE_CTA_PAIR"] = "1"
+    T.context().set_plan_flags(capi.PLAN_FORCE_CTA_PAIR)
     yield
-    os.environ.pop("PLB_FORCE_CTA_PAIR", None)
+    T.context().set_plan_flags(0)
 
 
 @pytest.mark.parametrize("m,k,n,tb", [(384, 192, 200, False), (384, 192, 200, True), (1000, 72, 136, False),
