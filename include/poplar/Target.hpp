@@ -25,6 +25,19 @@ public:
   unsigned getTilesPerIPU() const { return 148; }
   unsigned getNumIPUs() const { return 1; }
   std::size_t getTypeSize(const Type &t) const { return t.bytes(); }
+  /// Peak arithmetic per SM and cycle, in the reference's terms: multiply-
+  /// accumulates per cycle = conv units x vector width.  One SM's tensor core
+  /// does 4096 dense fp16 (8192 fp8) MACs per cycle with fp32 accumulation;
+  /// the CUDA cores 128 fp32 FMAs.
+  unsigned getFloatVectorWidth() const { return 128; }
+  unsigned getHalfVectorWidth() const { return 8; }
+  unsigned getQuarterVectorWidth() const { return 16; }
+  unsigned getFp16InFp16OutConvUnitsPerTile() const { return 512; }
+  unsigned getFp16InFp32OutConvUnitsPerTile() const { return 512; }
+  unsigned getFp32InFp32OutConvUnitsPerTile() const { return 0; }
+  unsigned getFp8InFp16OutConvUnitsPerTile() const { return 512; }
+  /// SM clock the cycle estimates refer to (the B200's maximum).
+  double getTileClockFrequency() const { return 1.965e9; }
   std::string getTargetArchString() const { return "sm_100a"; }
   friend bool operator==(const Target &a, const Target &b) { return a.device_ == b.device_; }
   friend bool operator<(const Target &a, const Target &b) { return a.device_ < b.device_; }

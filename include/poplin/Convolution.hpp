@@ -14,6 +14,7 @@
 
 #include <cstdint>
 #include <iosfwd>
+#include <istream>
 #include <limits>
 #include <memory>
 #include <set>
@@ -37,6 +38,12 @@ std::uint64_t getWuFlops(const ConvParams &params);
 /// Time, in seconds, a pass would take at the device's tensor-core peak (the
 /// counterpart of the reference's get*PerfectCycleCount).
 double getFwdPerfectSeconds(const ConvParams &params, double peakFlopsPerSecond);
+/// Cycles of each pass at full use of the target's arithmetic: the
+/// multiply-accumulates (padding excluded) / (MACs per SM and cycle x SMs).
+/// An optimistic number for judging efficiency, as in the reference.
+double getFwdPerfectCycleCount(const poplar::Graph &graph, const ConvParams &params);
+double getBwdPerfectCycleCount(const poplar::Graph &graph, const ConvParams &params);
+double getWuPerfectCycleCount(const poplar::Graph &graph, const ConvParams &params);
 
 poplar::Tensor createWeights(poplar::Graph &graph, const ConvParams &params,
                              const poplar::DebugContext &debugContext = {},
@@ -138,6 +145,67 @@ struct PlanCosts {
 PlanCosts reportPlanEstimatedCosts(const poplar::Graph &graph, const ConvParams &params,
                                    const poplar::OptionFlags &options = {},
                                    PlanningCache *cache = nullptr);
+
+namespace internal {
+/// Itemised estimate of what the plan costs.  The fields keep the reference's
+/// names; on this target a convolution has no exchange, broadcast or dynamic
+/// slicing phases, so those stay zero: `rearrangement` is a preparatory pass
+/// over the operands where the plan needs one (padded channels, space-to-depth,
+/// depth folding), `compute` the contraction kernel at its roofline,
+/// `reduction` the kernel that adds split-K partial sums, `outputCast` is part
+/// of the kernels' epilogues.  parallelSplit = CTAs launched, serialSplit = 1.
+struct DetailedPlanCosts {
+  std::size_t parallelSplit = 1;
+  std::size_t serialSplit = 1;
+  PlanCosts broadcast = {};
+  PlanCosts rearrangement = {};
+  PlanCosts dynamicSlice = {};
+  PlanCosts transform = {};
+  PlanCosts exchange = {};
+  PlanCosts tileLevelTransform = {};
+  PlanCosts inputsCast = {};
+  PlanCosts compute = {};
+  PlanCosts reduction = {};
+  PlanCosts dynamicUpdate = {};
+  PlanCosts addInPlace = {};
+  PlanCosts outputCast = {};
+  PlanCosts total = {};
+
+  template <typename Function>
+  void apply(Function fn, bool includeTotal = true, bool serialSplitOnly = false) const {
+    const_cast<DetailedPlanCosts *>(this)->apply([&fn](const PlanCosts &c) { fn(c); }, includeTotal,
+                                                 serialSplitOnly);
+  }
+  template <typename Function>
+  void apply(Function fn, bool includeTotal = true, bool serialSplitOnly = false) {
+    PlanCosts *always[] = {&dynamicSlice, &transform, &exchange, &tileLevelTransform, &inputsCast,
+                           &compute, &reduction, &dynamicUpdate};
+    if (!serialSplitOnly) {
+      fn(broadcast);
+      fn(rearrangement);
+    }
+    for (PlanCosts *c : always) fn(*c);
+    if (!serialSplitOnly) {
+      fn(addInPlace);
+      fn(outputCast);
+    }
+    if (includeTotal) fn(total);
+  }
+};
+std::ostream &operator<<(std::ostream &os, DetailedPlanCosts const &c);
+std::istream &operator>>(std::istream &is, DetailedPlanCosts &c);
+DetailedPlanCosts reportDetailedPlanEstimatedCosts(const poplar::Graph &graph, const ConvParams &params,
+                                                   const poplar::OptionFlags &options = {},
+                                                   PlanningCache *cache = nullptr);
+}  // namespace internal
+
+/// The weights of a fully connected layer (a 1-D convolution) arranged for the
+/// backward pass described by `params`: [G][Ci][Co][k] from [G][Co][Ci][k].
+poplar::Tensor fullyConnectedWeightTranspose(poplar::Graph &graph, poplar::Tensor weights,
+                                             const ConvParams &params, poplar::program::Sequence &prog,
+                                             const poplar::DebugContext &debugContext = {},
+                                             const poplar::OptionFlags &options = {},
+                                             PlanningCache *cache = nullptr);
 
 /// Throws poplar::invalid_option for an unknown key or a bad value.
 void convolutionValidateOptions(const poplar::OptionFlags &options);

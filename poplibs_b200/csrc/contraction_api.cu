@@ -664,6 +664,44 @@ int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a, c
       b_is_nk = true;
     }
   }
+  // Operands whose rows TMA cannot address (base or row pitch not a multiple of
+  // 16 bytes: a [k][n] right matrix with n % 8 != 0, odd leading dimensions)
+  // are copied once into scratch with the pitch rounded up and the padding
+  // zeroed, the way the convolution path pads channel counts.  The output needs
+  // no such copy: the epilogue falls back to plain stores.
+  {
+    const size_t a_rows = size_t(d.groups) * d.m, b_rows = size_t(d.groups) * (b_is_nk ? d.n : d.k);
+    const size_t a_cols = d.k, b_cols = b_is_nk ? d.k : d.n;
+    auto unaligned = [&](const uint8_t *base, long long pitch) {
+      return (reinterpret_cast<uintptr_t>(base) & 15) != 0 || (size_t(pitch) * es) % 16 != 0;
+    };
+    const bool pad_a = unaligned(a, lda), pad_b = unaligned(b, ldb);
+    if (pad_a || pad_b) {
+      const size_t per16 = 16 / es;
+      const size_t a_pitch = (a_cols + per16 - 1) / per16 * per16, b_pitch = (b_cols + per16 - 1) / per16 * per16;
+      const size_t a_pad_bytes = pad_a ? ((a_rows * a_pitch * es + 255) & ~size_t(255)) : 0;
+      const size_t b_pad_bytes = pad_b ? b_rows * b_pitch * es : 0;
+      void *ws = nullptr;
+      if (int rc = scratch(ctx, kSlotPaddedChans, a_pad_bytes + b_pad_bytes + 256, &ws)) return rc;
+      uint8_t *cursor = static_cast<uint8_t *>(ws);
+      // (all groups' rows are uniformly `pitch` elements apart)
+      auto repitch = [&](const uint8_t *src, long long src_pitch, size_t rows, size_t cols,
+                         size_t dst_pitch, uint8_t *dst) -> int {
+        return copyRowsPitched(ctx, src, size_t(src_pitch) * es, dst, dst_pitch * es, rows, cols * es);
+      };
+      if (pad_a) {
+        if (int rc = repitch(a, lda, a_rows, a_cols, a_pitch, cursor)) return rc;
+        a = cursor;
+        lda = (long long)a_pitch;
+        cursor += a_pad_bytes;
+      }
+      if (pad_b) {
+        if (int rc = repitch(b, ldb, b_rows, b_cols, b_pitch, cursor)) return rc;
+        b = cursor;
+        ldb = (long long)b_pitch;
+      }
+    }
+  }
   for (uint32_t g = 0; g < d.groups; ++g) {
     const uint8_t *ag = a + size_t(g) * d.m * lda * es;
     const uint8_t *bg = b + size_t(g) * (b_is_nk ? d.n : d.k) * ldb * es;

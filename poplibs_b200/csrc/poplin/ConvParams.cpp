@@ -93,7 +93,8 @@ ConvParams::ConvParams(poplar::Type inputType_, poplar::Type outputType_, std::s
       inputChannelsPerConvGroup(inputChannels_), outputChannelsPerConvGroup(outputChannels_),
       numConvGroups(numConvGroups_), inputTransform(std::move(inputTransform_)),
       kernelTransform(std::move(kernelTransform_)), outputTransform(std::move(outputTransform_)) {
-  validate();
+  // not validated here, as in the reference (lib/poplin/ConvParams.cpp:152-170):
+  // validate() is called by whatever consumes the parameters
 }
 
 ConvParams::ConvParams(poplar::Type inputType_, poplar::Type outputType_, std::size_t batchSize_,

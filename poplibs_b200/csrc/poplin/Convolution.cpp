@@ -6,6 +6,7 @@
 #include "poplin/Convolution.hpp"
 
 #include <algorithm>
+#include <fstream>
 #include <cmath>
 #include <iostream>
 #include <map>
@@ -46,6 +47,47 @@ std::string cacheKey(const ConvParams &p, const poplar::OptionFlags &options, in
   return os.str();
 }
 
+// The chosen plan as a planConstraints value that reproduces it when fed back
+// (option planConstraintsOutputFilename; the reference's
+// writePlanConstraintsFile, lib/poplin/ConvPlan.cpp:1574-1664): the K split in
+// the reference's own grammar (level 0, inChanSplit.parallel) and this
+// planner's knobs under "cuda".
+std::string planConstraintsOf(const plb_plan &plan) {
+  std::ostringstream os;
+  const bool igemm = plan.kernel != 1;
+  os << "{\n"
+     << "  \"0\": {\"partition\": {\"inChanSplit\": {\"serial\": 1, \"parallel\": "
+     << std::max(1, int(plan.split_k)) << "}}},\n"
+     << "  \"cuda\": {\"splitK\": " << std::max(1, int(plan.split_k));
+  if (igemm)
+    os << ", \"tileN\": " << plan.tile_n << ", \"residentWeights\": "
+       << (plan.resident_weights ? "true" : "false") << ", \"ctaPair\": "
+       << (plan.cta_pair ? "true" : "false");
+  os << ", \"halo\": " << (plan.halo_rows > 0 ? "true" : "false") << "}\n}\n";
+  return os.str();
+}
+
+// <name>_FWD.json / _BWD.json / _WU.json, as getPlanConstraintsOutputFile
+// (lib/poplin/ConvPlan.cpp:1631-1658).
+void writePlanConstraintsFile(const plb_plan &plan, const internal::ConvOptions &options) {
+  std::string path = options.planConstraintsOutputFilename;
+  switch (options.pass) {
+    case internal::Pass::INFERENCE_FWD:
+    case internal::Pass::TRAINING_FWD:
+    case internal::Pass::FC_INFERENCE_FWD:
+    case internal::Pass::FC_TRAINING_FWD: path += "_FWD"; break;
+    case internal::Pass::TRAINING_BWD:
+    case internal::Pass::FC_TRAINING_BWD: path += "_BWD"; break;
+    case internal::Pass::TRAINING_WU:
+    case internal::Pass::FC_TRAINING_WU: path += "_WU"; break;
+    default: break;
+  }
+  path += ".json";
+  std::ofstream out(path);
+  if (!out) throw poplibs_error("cannot write plan constraints to '" + path + "'");
+  out << planConstraintsOf(plan);
+}
+
 // Plan for one pass of `params` (PLB_PASS_TRAINING_FWD / _BWD / _WU), cached.
 plb_plan planFor(const ConvParams &params, const poplar::OptionFlags &options, int pass,
                  PlanningCache *cache) {
@@ -68,6 +110,7 @@ plb_plan planFor(const ConvParams &params, const poplar::OptionFlags &options, i
   plb_plan plan{};
   poplar::detail::check(plb_conv_plan(&flat, &opt, pass, &plan));
   if (cache) cache->impl->plans[key] = plan;
+  if (!parsed.planConstraintsOutputFilename.empty()) writePlanConstraintsFile(plan, parsed);
   return plan;
 }
 
@@ -199,6 +242,33 @@ std::uint64_t getBwdFlops(const ConvParams &params) { return getFwdFlops(params)
 std::uint64_t getWuFlops(const ConvParams &params) { return getFwdFlops(params); }
 double getFwdPerfectSeconds(const ConvParams &params, double peakFlopsPerSecond) {
   return double(getFwdFlops(params)) / peakFlopsPerSecond;
+}
+
+// MACs / (MACs per SM and cycle x SMs), the reference's getPerfectCycleCount
+// (lib/poplin/Convolution.cpp:3227-3248) with this target's arithmetic widths.
+static double perfectCycleCount(const Graph &graph, const ConvParams &params) {
+  const poplar::Target &target = graph.getTarget();
+  const double macs = double(getFwdFlops(params)) / 2.0;
+  double perTile;
+  if (params.inputType == poplar::FLOAT)
+    perTile = target.getFloatVectorWidth();
+  else if (params.inputType == poplar::QUARTER)
+    perTile = double(target.getFp8InFp16OutConvUnitsPerTile()) * target.getQuarterVectorWidth();
+  else
+    perTile = double(std::max({target.getFp16InFp16OutConvUnitsPerTile(),
+                               target.getFp32InFp32OutConvUnitsPerTile(),
+                               target.getFp16InFp32OutConvUnitsPerTile()})) *
+              target.getHalfVectorWidth();
+  return macs / (perTile * target.getNumTiles());
+}
+double getFwdPerfectCycleCount(const Graph &graph, const ConvParams &params) {
+  return perfectCycleCount(graph, params);
+}
+double getBwdPerfectCycleCount(const Graph &graph, const ConvParams &params) {
+  return perfectCycleCount(graph, params);
+}
+double getWuPerfectCycleCount(const Graph &graph, const ConvParams &params) {
+  return perfectCycleCount(graph, params);
 }
 
 // ---- tensor creation -----------------------------------------------------------------
@@ -562,6 +632,11 @@ void reportWeightUpdatePlanInfo(std::ostream &out, const Graph &, const ConvPara
   const plb_conv_options opt = parsed.toPlb();
   plb_plan plan{};
   poplar::detail::check(plb_conv_wu_plan(&flat, &opt, &plan));
+  if (!parsed.planConstraintsOutputFilename.empty()) {
+    internal::ConvOptions wu = parsed;
+    wu.pass = internal::Pass::TRAINING_WU;
+    writePlanConstraintsFile(plan, wu);
+  }
   out << fwdParams;
   printPlan(out, plan, "weight update");
 }
@@ -577,6 +652,79 @@ PlanCosts reportPlanEstimatedCosts(const Graph &, const ConvParams &params,
   c.cycles = std::size_t(std::max(computeCycles, memoryCycles));
   c.memory = std::size_t(plan.workspace_bytes);
   return c;
+}
+
+namespace internal {
+
+std::ostream &operator<<(std::ostream &os, DetailedPlanCosts const &c) {
+  os << c.parallelSplit << " " << c.serialSplit << "\n";
+  c.apply([&os](const PlanCosts &x) { os << x.cycles << " " << x.memory << "\n"; });
+  return os;
+}
+
+std::istream &operator>>(std::istream &is, DetailedPlanCosts &c) {
+  is >> c.parallelSplit >> c.serialSplit;
+  c.apply([&is](PlanCosts &x) { is >> x.cycles >> x.memory; });
+  return is;
+}
+
+DetailedPlanCosts reportDetailedPlanEstimatedCosts(const Graph &graph, const ConvParams &params,
+                                                   const poplar::OptionFlags &options,
+                                                   PlanningCache *cache) {
+  const ConvOptions parsed(options);
+  const int pass = parsed.pass == Pass::TRAINING_BWD ? PLB_PASS_TRAINING_BWD : PLB_PASS_TRAINING_FWD;
+  const plb_plan plan = planFor(params, options, pass, cache);
+  // bytes per SM cycle the HBM sustains (about 6.5 TB/s at the 1.965 GHz the cycle counts refer to)
+  const double hbmBytesPerCycle = 6.5e12 / graph.getTarget().getTileClockFrequency();
+  auto memoryCycles = [&](double bytes) { return bytes / hbmBytesPerCycle; };
+  DetailedPlanCosts c;
+  c.parallelSplit = std::size_t(std::max(1, plan.grid));
+  c.serialSplit = 1;
+  auto zero = [](PlanCosts &x) { x.cycles = 0; x.memory = 0; };
+  c.apply(zero);
+  // compute: the contraction kernel at the slower of its two rooflines
+  const double macCycles = getFwdPerfectCycleCount(graph, params);
+  c.compute.cycles = std::size_t(std::max(macCycles, memoryCycles(double(plan.bytes))));
+  // reduction: split-K partial sums written once and read once by the second kernel
+  if (plan.split_k > 1) {
+    c.reduction.cycles = std::size_t(memoryCycles(2.0 * double(plan.workspace_bytes)));
+    c.reduction.memory = std::size_t(plan.workspace_bytes);
+  }
+  // rearrangement: the small-channel path rewrites the activations once (space to depth)
+  if (plan.kernel == 2) {
+    double in_bytes = double(params.getBatchSize()) * double(params.getNumInputChans()) *
+                      double(graph.getTarget().getTypeSize(params.inputType));
+    for (std::size_t extent : params.inputFieldShape) in_bytes *= double(extent);
+    c.rearrangement.cycles = std::size_t(memoryCycles(2.0 * in_bytes));
+    c.rearrangement.memory = plan.split_k > 1 ? 0 : std::size_t(plan.workspace_bytes);
+  }
+  c.total.cycles = c.compute.cycles + c.reduction.cycles + c.rearrangement.cycles;
+  c.total.memory = std::size_t(plan.workspace_bytes);
+  return c;
+}
+
+}  // namespace internal
+
+Tensor fullyConnectedWeightTranspose(Graph &graph, Tensor weights, const ConvParams &params,
+                                     Sequence &prog, const poplar::DebugContext &dc,
+                                     const poplar::OptionFlags &options, PlanningCache *) {
+  // (lib/poplin/Convolution.cpp:3846-3921: the weights' channel axes swapped,
+  // in a tensor laid out for the backward-pass convolution `params`)
+  convolutionValidateOptions(options);
+  if (params.getNumFieldDims() != 1)
+    throw poplibs_error("fullyConnectedWeightTranspose() expects a 1-d convolution");
+  const Tensor w = withGroupDim(weights, params);
+  if (w.rank() != 4 || w.dim(0) != params.numConvGroups ||
+      w.dim(1) != params.inputChannelsPerConvGroup || w.dim(2) != params.outputChannelsPerConvGroup)
+    throw poplibs_error("fullyConnectedWeightTranspose: weights must be [G][Co][Ci][k] of the forward "
+                        "pass, i.e. [G][params.Ci][params.Co][k]");
+  Tensor transposed = makeWeights(graph, weights.elementType(), params.numConvGroups,
+                                  params.outputChannelsPerConvGroup, params.inputChannelsPerConvGroup,
+                                  params.kernelShape, dc.getPathName() + "/transposed");
+  if (weights.elementType() == poplar::QUARTER && weights.hasMetadata())
+    graph.setQuarterMetadata(transposed, weights.getMetadata());
+  prog.add(poplar::program::Copy(w.dimShuffle({0, 2, 1, 3}), transposed));
+  return transposed;
 }
 
 // ---- pre-planning -------------------------------------------------------------------------

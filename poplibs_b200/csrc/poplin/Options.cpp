@@ -157,14 +157,14 @@ void checkMethod(const std::string &path, const json::Value &t) {
 }
 
 // The CUDA planner's own constraints, an extension of the reference grammar:
-//   "cuda": {"tileN": 64|128|256, "splitK": n, "residentWeights": bool, "halo": bool}
+//   "cuda": {"tileN": 64|128|256, "splitK": n, "residentWeights": bool, "halo": bool, "ctaPair": bool}
 void checkCuda(const std::string &path, const json::Value &t) {
   requireObject(path, t);
   for (const auto &child : t.items) {
     const std::string sub = path + "." + child.first;
     if (child.first == "tileN" || child.first == "splitK")
       requireUnsigned(sub, child.second);
-    else if (child.first == "residentWeights" || child.first == "halo")
+    else if (child.first == "residentWeights" || child.first == "halo" || child.first == "ctaPair")
       requireBoolean(sub, child.second);
     else
       throw invalid_option("'" + sub + "': " + child.first + " is not a CUDA plan constraint");

@@ -373,6 +373,33 @@ int resizeRows(plb_context *ctx, const void *src, void *dst, size_t rows, size_t
   return PLB_OK;
 }
 
+// The same for source rows `src_pitch` bytes apart: dst row r = the first
+// `row_bytes` bytes of source row r, zero-filled up to `dst_pitch`.
+__global__ void copyRowsPitchedKernel(const uint8_t *__restrict__ src, size_t src_pitch,
+                                      uint8_t *__restrict__ dst, uint32_t dst_pitch, size_t rows,
+                                      uint32_t row_bytes) {
+  const size_t total = rows * dst_pitch;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = i / dst_pitch;
+    const uint32_t b = uint32_t(i - r * dst_pitch);
+    dst[i] = b < row_bytes ? src[r * src_pitch + b] : uint8_t(0);
+  }
+}
+
+int copyRowsPitched(plb_context *ctx, const void *src, size_t src_pitch, void *dst, size_t dst_pitch,
+                    size_t rows, size_t row_bytes) {
+  if (rows == 0 || dst_pitch == 0) return PLB_OK;
+  const size_t total = rows * dst_pitch;
+  const int grid = int(std::min<size_t>((total + 255) / 256, size_t(ctx->sm_count) * 16));
+  copyRowsPitchedKernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint8_t *>(src), src_pitch,
+                                                       static_cast<uint8_t *>(dst), uint32_t(dst_pitch),
+                                                       rows, uint32_t(row_bytes));
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
 // dst[n][h][w][:] = src[n][flip_h ? H-1-h : h][flip_w ? W-1-w : w][:], pixels of
 // `pixel_bytes` bytes: the spatial flip of the reference's input transform.
 __global__ void flipFieldKernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,

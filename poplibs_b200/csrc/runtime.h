@@ -97,6 +97,8 @@ inline size_t dtypeBytes(int dtype) {
 // Row resize (runtime.cu): rows of src_bytes -> rows of dst_bytes, zero fill / drop of the tail.
 int resizeRows(plb_context *ctx, const void *src, void *dst, size_t rows, size_t src_bytes,
                size_t dst_bytes);
+int copyRowsPitched(plb_context *ctx, const void *src, size_t src_pitch, void *dst, size_t dst_pitch,
+                    size_t rows, size_t row_bytes);
 
 // Input flip of the reference's input transform: the convolution of a flipped
 // input equals the convolution of the reversed tensor with the input padding and

@@ -106,6 +106,7 @@ int main(int argc, char **argv) try {
       poplin::ConvParams::OutputTransform(std::vector<unsigned>(nd, 0), std::vector<unsigned>(nd, 0),
                                           stride, std::vector<unsigned>(nd, 0),
                                           std::vector<unsigned>(nd, 0)));
+  params.validate();  // (the constructor does not; sizes below divide by the stride)
   const auto outField = params.getOutputFieldShape();
   const poplin::ConvParams bwdParams = poplin::getGradientParams(params);
 

@@ -4,7 +4,9 @@
 // (tests/poplin/ConvTest.cpp:651-682), option validation (:684-706), the plan
 // constraints grammar (tests/poplin/ConvOptionsTest.cpp:12-107), index ranges
 // (tests/poplin/RangeTest.cpp, ConvUtilTest.cpp:14-51).
+#include <cmath>
 #include <cstdio>
+#include <fstream>
 #include <functional>
 #include <iostream>
 #include <set>
@@ -296,6 +298,76 @@ static void testGraphConstructionWithoutDevice() {
   CHECK(report.str().find("CTA tile (pixels x chans)  128 x 64") != std::string::npos);
   CHECK(report.str().find("weight update (split-K)") != std::string::npos);
   CHECK(reportPlanEstimatedCosts(graph, p, fwdOpts, &cache).cycles != PlanCosts::unknown);
+  // perfect cycle counts: MACs / (4096 fp16 MACs per SM and cycle x 148 SMs)
+  {
+    const double macs = double(getFwdFlops(p)) / 2.0;
+    CHECK(std::abs(getFwdPerfectCycleCount(graph, p) - macs / (4096.0 * 148.0)) < 1e-6 * macs);
+    CHECK(getBwdPerfectCycleCount(graph, p) == getFwdPerfectCycleCount(graph, p));
+    CHECK(getWuPerfectCycleCount(graph, p) == getFwdPerfectCycleCount(graph, p));
+    ConvParams q8 = p;
+    q8.inputType = QUARTER;
+    CHECK(std::abs(getFwdPerfectCycleCount(graph, q8) * 2.0 - getFwdPerfectCycleCount(graph, p)) < 1e-6 * macs);
+  }
+  // itemised costs: written and read back in the reference's text form
+  {
+    const auto d = internal::reportDetailedPlanEstimatedCosts(graph, p, fwdOpts, &cache);
+    CHECK(d.total.cycles == d.compute.cycles + d.reduction.cycles + d.rearrangement.cycles);
+    CHECK(d.compute.cycles >= std::size_t(getFwdPerfectCycleCount(graph, p)) && d.parallelSplit == 148);
+    std::stringstream ss;
+    ss << d;
+    internal::DetailedPlanCosts back;
+    ss >> back;
+    CHECK(back.total.cycles == d.total.cycles && back.compute.cycles == d.compute.cycles &&
+          back.parallelSplit == d.parallelSplit && back.outputCast.memory == d.outputCast.memory);
+    // a long, thin contraction is split over K: the reduction shows up
+    ConvParams thin(HALF, HALF, 1, {256}, {1}, 8192, 256, 1);
+    const auto dt = internal::reportDetailedPlanEstimatedCosts(graph, thin, fwdOpts);
+    CHECK(dt.reduction.cycles > 0 && dt.reduction.memory > 0 && dt.total.memory == dt.reduction.memory);
+  }
+  // the chosen plan written as planConstraints and fed back reproduces the plan
+  {
+    const std::string base = "/tmp/plb_plan_constraints_test";
+    for (const char *cons : {"", R"({"cuda": {"splitK": 3, "tileN": 128, "halo": false, "ctaPair": true}})"}) {
+      poplar::OptionFlags o1 = {{"pass", "TRAINING_FWD"}, {"planConstraintsOutputFilename", base}};
+      if (*cons) o1.set("planConstraints", cons);
+      std::ostringstream first;
+      reportPlanInfo(first, graph, p, o1);
+      std::ifstream in(base + "_FWD.json");
+      CHECK(bool(in));
+      std::stringstream text;
+      text << in.rdbuf();
+      CHECK(text.str().find("\"inChanSplit\"") != std::string::npos);
+      std::ostringstream second;
+      reportPlanInfo(second, graph, p, {{"pass", "TRAINING_FWD"}, {"planConstraints", text.str()}});
+      CHECK(first.str() == second.str());
+      std::remove((base + "_FWD.json").c_str());
+    }
+    std::ostringstream wu1, wu2;
+    reportWeightUpdatePlanInfo(wu1, graph, p, {{"planConstraintsOutputFilename", base}});
+    std::ifstream in(base + "_WU.json");
+    CHECK(bool(in));
+    std::stringstream text;
+    text << in.rdbuf();
+    reportWeightUpdatePlanInfo(wu2, graph, p, {{"planConstraints", text.str()}});
+    CHECK(wu1.str() == wu2.str());
+    std::remove((base + "_WU.json").c_str());
+  }
+  // weights of a fully connected layer rearranged for its backward pass
+  {
+    ConvParams fcBwd(HALF, HALF, 4, {1}, {1}, 96, 40, 2);   // backward pass: 96 = forward Co, 40 = forward Ci
+    auto fcw = graph.addVariable(HALF, {2, 96, 40, 1}, "fcw");   // forward weights [G][Co][Ci][k]
+    poplar::program::Sequence fcProg;
+    auto t = fullyConnectedWeightTranspose(graph, fcw, fcBwd, fcProg, "fct");
+    CHECK((t.shape() == std::vector<std::size_t>{2, 40, 96, 1}) && fcProg.steps().size() == 1);
+    ConvParams twoD(HALF, HALF, 4, {2, 2}, {1, 1}, 96, 40, 2);
+    CHECK((throwsAs<poputil::poplibs_error>([&] { fullyConnectedWeightTranspose(graph, fcw, twoD, fcProg); })));
+  }
+  // the full constructor does not validate; validate() does
+  {
+    CHECK(noThrow([] { ConvParams bad(HALF, HALF, 1, {4, 4}, {3}, 8, 8, 1); (void)bad; }));
+    ConvParams bad(HALF, HALF, 1, {4, 4}, {3}, 8, 8, 1);
+    CHECK((throwsAs<poputil::poplibs_error>([&] { bad.validate(); })));
+  }
   // preplanning fills the cache
   PlanningCache fresh;
   const poplar::Target target = graph.getTarget();
