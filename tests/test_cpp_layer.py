@@ -13,7 +13,8 @@ LIBDIR = os.path.join(ROOT, "poplibs_b200")
 def compile_cpp(source, output):
     from poplibs_b200 import build
     build.build_poplin()
-    cmd = ["g++", "-std=c++17", "-O1", "-I" + os.path.join(ROOT, "include"), source, "-o", output,
+    cmd = ["g++", "-std=c++17", "-O1", "-I" + os.path.join(ROOT, "include"),
+           "-I" + os.path.join(ROOT, "poplibs_b200", "tools"), source, "-o", output,
            "-L" + LIBDIR, "-lpoplin_b200", "-lpoplibs_b200", "-Wl,-rpath," + LIBDIR]
     subprocess.run(cmd, check=True)
 
@@ -235,3 +236,32 @@ def test_single_conv_layer_tool_against_oracle(tmp_path):
                 _, db = oracle.conv_wu(spec, x, flat(t["zDeltas"], 2))
                 expect_b = (t["biases"].ravel() - lr * db).astype(np.float16).astype(np.float64)
                 assert (t["biasesUpdated"].ravel() == expect_b).all(), case["flags"]
+
+
+@pytest.mark.gpu
+def test_multiconv_on_gpu_against_oracle(tmp_path):
+    """poplin::multiconv (two different layers at once: a padded 3x3 and a
+    grouped strided 1x1 with fp32 output) through the Engine: forward outputs,
+    weight gradients and updated weights of both must equal the CPU model bit
+    for bit on small-integer data."""
+    import numpy as np
+    import oracle
+    from oracle import ConvSpec
+    exe = str(tmp_path / "multiconv_gpu")
+    compile_cpp(os.path.join(ROOT, "tests", "cpp", "multiconv_gpu.cpp"), exe)
+    d = tmp_path / "dump"
+    d.mkdir()
+    out = subprocess.run([exe, str(d)], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    t = load_dump(str(d))
+    specs = [ConvSpec.simple(3, [12, 12], [3, 3], 64, 72, padding=1),
+             ConvSpec.simple(2, [9, 10], [1, 1], 32, 48, stride=2, groups=2)]
+    for i, spec in enumerate(specs):
+        x, w, dy = t[f"in{i}"], t[f"w{i}"], t[f"dy{i}"]
+        y = oracle.conv_fwd(spec, x, w).reshape(t[f"out{i}"].shape)
+        assert (t[f"out{i}"] == y).all(), f"multiconv forward {i}"
+        dw = oracle.conv_wu(spec, x, dy)[0].reshape(w.shape)
+        got = t[f"dw{i}"]
+        assert (got == dw.astype(np.float16).astype(np.float64)).all(), f"multiconv weight gradient {i}"
+        upd = (w + -0.5 * dw).astype(np.float16).astype(np.float64)
+        assert (t[f"wUpdated{i}"] == upd).all(), f"multiconv weight update {i}"

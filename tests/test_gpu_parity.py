@@ -753,6 +753,14 @@ def test_config3a_stem_sampled_images(gpu_ctx):
     got = T.gpu_conv_fwd(p, x, w)
     assert (got[128:] == got[:128]).all()
     del got
+    # the same full-size layer on uniform data, the oracle on eight sampled images
+    x, w, _ = conv_data(p, kw, r, exact=False)
+    got = T.gpu_conv_fwd(p, x, w)
+    pick = [0, 1, 37, 100, 127, 128, 200, 255]
+    p8 = capi.ConvParams.make(**{**kw, "batch": len(pick)})
+    assert_close(got[pick], oracle.conv_fwd(T.spec_from_params(p8), x[pick], w), REL_HALF,
+                 "config 3a uniform, sampled images")
+    del got
     torch.cuda.empty_cache()
 
 
@@ -865,6 +873,9 @@ def test_config3b_pointwise_stride2_fwd(gpu_ctx):
     r = T.rng(1234 + 3)
     x, w, _ = conv_data(p, kw, r, exact=True)
     assert_exact(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), "config 3b exact")
+    # the distributions the configuration names: activations U[-1, 1], weights U[-1/16, 1/16]
+    x, w, _ = conv_data(p, kw, r, exact=False)
+    assert_close(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), REL_HALF, "config 3b uniform")
 
 
 def test_config4_fwd_bwd_wu(gpu_ctx):
@@ -879,6 +890,7 @@ def test_config4_fwd_bwd_wu(gpu_ctx):
     assert_exact(dw32, oracle.conv_wu(spec, x, dy)[0], "config 4 wu exact (fp32 sums < 2^24)")
     x, w, dy = conv_data(p, kw, r, exact=False)
     assert_close(T.gpu_conv_fwd(p, x, w), oracle.conv_fwd(spec, x, w), REL_HALF, "config 4 fwd uniform")
+    assert_close(T.gpu_conv_bwd(p, dy, w), oracle.conv_bwd(spec, dy, w), REL_HALF, "config 4 bwd uniform")
     dw16, _ = T.gpu_conv_wu(p, x, dy)
     assert_close(dw16, oracle.conv_wu(spec, x, dy)[0], REL_HALF, "config 4 wu uniform")
 
