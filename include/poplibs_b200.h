@@ -363,6 +363,55 @@ PLB_API int plb_add_bias(plb_context *ctx, int32_t dtype, void *d_acts, const vo
 PLB_API int plb_cast_from_f32(plb_context *ctx, int32_t dtype, void *d_dst, const float *d_src,
                       size_t count);
 
+/* ------------------------------------------------------------------------ */
+/* Batch normalisation of a convolution's output (include/poplin/Norms.hpp:   */
+/* 33-334, lib/poplin/Norms.cpp).  Activations are in the device layout        */
+/* [pixels][chans]; statistics and parameters are per channel; dtype is        */
+/* PLB_HALF or PLB_FLOAT; sums are formed in fp32 in a fixed order.            */
+/* ------------------------------------------------------------------------ */
+/* First and second moments per channel, times `scale` (1 / pixels, or
+ * 1 / (pixels of all replicas) before a caller's own all-reduce):
+ *   d_centre == NULL: d_mean[c] (dtype) = scale * sum x, d_power[c] (fp32) =
+ *                     scale * sum x^2  (popops::reduceMany ADD / SQUARE_ADD,
+ *                     lib/poplin/Norms.cpp:225-242);
+ *   d_centre != NULL: d_power[c] = scale * sum (x - d_centre[c])^2, the
+ *                     "stable" estimator (:205-223); d_mean is not written. */
+PLB_API int plb_norm_moments(plb_context *ctx, int32_t dtype, const void *d_acts, uint64_t pixels,
+                     uint32_t chans, float scale, const void *d_centre, void *d_mean,
+                     float *d_power);
+/* d_inv_std[c] = 1 / sqrt((power - mean^2 + eps) * scale_var), or with `stable`
+ * 1 / sqrt((power + eps) * scale_var): the InverseStdDeviation vertex
+ * (lib/poplin/codelets/InverseStdDeviation.cpp:33-55). */
+PLB_API int plb_norm_inv_std_dev(plb_context *ctx, int32_t dtype, const void *d_mean,
+                         const float *d_power, uint32_t chans, float eps, float scale_var,
+                         int stable, void *d_inv_std);
+/* out = (acts - mean[c]) * inv_std[c]  (poplin::normWhiten, Norms.hpp:212-216). */
+PLB_API int plb_norm_whiten(plb_context *ctx, int32_t dtype, const void *d_acts, const void *d_mean,
+                    const void *d_inv_std, uint64_t pixels, uint32_t chans, void *d_out);
+/* out = acts * scale[c] + shift[c]; d_shift == NULL: out = acts * scale[c]
+ * (poplin::normalise with gamma / beta, Norms.hpp:229-234; poplin::normGradients
+ * with gamma alone, :266-270). */
+PLB_API int plb_norm_scale_shift(plb_context *ctx, int32_t dtype, const void *d_acts,
+                         const void *d_scale, const void *d_shift, uint64_t pixels,
+                         uint32_t chans, void *d_out);
+/* gamma_delta[c] = scale * sum whitened * grads, beta_delta[c] = scale * sum grads
+ * (poplin::normParamGradients, Norms.hpp:249-254), in dtype and / or in fp32;
+ * any of the four outputs may be NULL. */
+PLB_API int plb_norm_param_gradients(plb_context *ctx, int32_t dtype, const void *d_whitened,
+                             const void *d_grads, uint64_t pixels, uint32_t chans, float scale,
+                             void *d_gamma_delta, void *d_beta_delta, float *d_gamma_delta_f32,
+                             float *d_beta_delta_f32);
+/* out = (grads - whitened * mean_c(whitened * grads) - mean_c(grads)) * inv_std[c]
+ * (poplin::normStatisticsGradients, Norms.hpp:289-294).  With d_var_delta and
+ * d_mean_delta (dtype, per channel; both or neither) the two means are taken
+ * from the caller instead, already negated and reduced over the replicas:
+ * out = (grads + whitened * var_delta[c] + mean_delta[c]) * inv_std[c]
+ * (distributedNormStatisticsGradients, Norms.hpp:324-330). */
+PLB_API int plb_norm_statistics_gradients(plb_context *ctx, int32_t dtype, const void *d_whitened,
+                                  const void *d_grads, const void *d_inv_std,
+                                  const void *d_var_delta, const void *d_mean_delta,
+                                  uint64_t pixels, uint32_t chans, void *d_out);
+
 /* Host-buffer variants (device layouts, host memory): upload, run, download,
  * synchronise. */
 PLB_API int plb_conv_fwd_host(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,

@@ -172,6 +172,15 @@ def _lib():
         lib.oracle_check_is_close.argtypes = [_DP, _DP, C.c_size_t, C.c_double, C.c_double,
                                               C.POINTER(C.c_size_t), C.POINTER(C.c_double)]
         lib.oracle_check_is_close.restype = C.c_size_t
+        U = C.c_uint32
+        lib.oracle_norm_statistics.argtypes = [_DP, U, U, U, C.c_double, C.c_int, C.c_int, _DP, _DP]
+        lib.oracle_norm_statistics.restype = None
+        lib.oracle_norm_normalise.argtypes = [_DP] * 5 + [U, U, U, _DP, _DP]
+        lib.oracle_norm_normalise.restype = None
+        lib.oracle_norm_gradients.argtypes = [_DP] * 4 + [U, U, U, _DP]
+        lib.oracle_norm_gradients.restype = None
+        lib.oracle_norm_param_update.argtypes = [_DP, _DP, C.c_double, U, U, U, _DP, _DP]
+        lib.oracle_norm_param_update.restype = None
         lib.oracle_round_to_half.argtypes = [C.c_double]
         lib.oracle_round_to_half.restype = C.c_double
         lib.oracle_e4m3_from_double.argtypes = [C.c_double]
@@ -196,6 +205,11 @@ def _ref():
         lib.ref_conv_wu.argtypes = [PP, _DP, _DP, _DP, _DP]
         lib.ref_gemm.argtypes = [C.c_uint32] * 4 + [_DP] * 4 + [C.c_float, C.c_float, C.c_int, C.c_int]
         lib.ref_last_error.restype = C.c_char_p
+        U = C.c_uint32
+        lib.ref_norm_statistics.argtypes = [_DP, U, U, U, C.c_double, C.c_int, C.c_int, _DP, _DP]
+        lib.ref_norm_normalise.argtypes = [_DP] * 5 + [U, U, U, _DP, _DP]
+        lib.ref_norm_gradients.argtypes = [_DP] * 4 + [U, U, U, _DP]
+        lib.ref_norm_param_update.argtypes = [_DP, _DP, C.c_double, U, U, U, _DP, _DP]
         _REF = lib
     return _REF
 
@@ -301,6 +315,75 @@ def gemm(a, b, c=None, alpha=1.0, beta=0.0, transpose_a=False, transpose_b=False
         if rc:
             raise RuntimeError(f"oracle gemm failed rc={rc}")
     return d[0] if squeeze else d
+
+
+# ---- batch normalisation (poplibs_test::norm, NormType::BatchNorm) -----------------
+# Activations are [batch][chans][field...]; statistics are per channel.
+
+def _bcf(a):
+    a = np.asarray(a, dtype=np.float64)
+    a3 = np.ascontiguousarray(a.reshape(a.shape[0], a.shape[1], -1))
+    return a3, a3.ctypes.data_as(_DP), a3.shape
+
+
+def _check_ref(rc):
+    if rc:
+        raise RuntimeError(_ref().ref_last_error().decode())
+
+
+def norm_statistics(acts, eps, unbiased=False, stable=False, use_ref=False):
+    """(mean[chans], inv_std_dev[chans])."""
+    a, ap, (b, c, f) = _bcf(acts)
+    mean, inv = np.zeros(c), np.zeros(c)
+    args = (ap, b, c, f, float(eps), int(unbiased), int(stable), mean.ctypes.data_as(_DP), inv.ctypes.data_as(_DP))
+    if use_ref:
+        _check_ref(_ref().ref_norm_statistics(*args))
+    else:
+        _lib().oracle_norm_statistics(*args)
+    return mean, inv
+
+
+def norm_normalise(acts, gamma, beta, mean, inv_std, use_ref=False):
+    """(normalised, whitened), both shaped like acts."""
+    a, ap, (b, c, f) = _bcf(acts)
+    out, white = np.zeros_like(a), np.zeros_like(a)
+    vecs = [_d(v) for v in (gamma, beta, mean, inv_std)]
+    args = (ap, *[v[1] for v in vecs], b, c, f, out.ctypes.data_as(_DP), white.ctypes.data_as(_DP))
+    if use_ref:
+        _check_ref(_ref().ref_norm_normalise(*args))
+    else:
+        _lib().oracle_norm_normalise(*args)
+    shape = np.asarray(acts).shape
+    return out.reshape(shape), white.reshape(shape)
+
+
+def norm_gradients(whitened, grads_in, inv_std, gamma, use_ref=False):
+    """Gradient with respect to the normalisation's input."""
+    w, wp, (b, c, f) = _bcf(whitened)
+    g, gp, _ = _bcf(grads_in)
+    i, ip = _d(inv_std)
+    ga, gap = _d(gamma)
+    out = np.zeros_like(w)
+    args = (wp, gp, ip, gap, b, c, f, out.ctypes.data_as(_DP))
+    if use_ref:
+        _check_ref(_ref().ref_norm_gradients(*args))
+    else:
+        _lib().oracle_norm_gradients(*args)
+    return out.reshape(np.asarray(whitened).shape)
+
+
+def norm_param_update(whitened, grads_in, learning_rate, gamma, beta, use_ref=False):
+    """(gamma - lr * sum(whitened * grads), beta - lr * sum(grads)) per channel."""
+    w, wp, (b, c, f) = _bcf(whitened)
+    g, gp, _ = _bcf(grads_in)
+    ga = np.array(gamma, dtype=np.float64)
+    be = np.array(beta, dtype=np.float64)
+    args = (wp, gp, float(learning_rate), b, c, f, ga.ctypes.data_as(_DP), be.ctypes.data_as(_DP))
+    if use_ref:
+        _check_ref(_ref().ref_norm_param_update(*args))
+    else:
+        _lib().oracle_norm_param_update(*args)
+    return ga, be
 
 
 def check_is_close(actual, expected, rel_tol, abs_tol=1e-5):

@@ -630,3 +630,88 @@ uint8_t oracle_e4m3_from_double(double x) {
   const int m = (int)((q / ldexp(1.0, exp2) - 1.0) * 8.0);
   return sign | (uint8_t)(((exp2 + 7) << 3) | m);
 }
+
+
+/* ---- batch normalisation (lib/poplibs_test/Norms.cpp, BatchNorm) ----------- */
+/* Element (b, c, f) of a [batch][chans][field] array. */
+#define NORM_AT(a, b, c, f) ((a)[((size_t)(b) * chans + (c)) * field + (f)])
+
+void oracle_norm_statistics(const double *acts, uint32_t batch, uint32_t chans,
+                            uint32_t field, double eps, int unbiased,
+                            int stable, double *mean, double *inv_std) {
+  const double n = (double)batch * (double)field;
+  for (uint32_t c = 0; c < chans; ++c) {
+    double sum = 0.0, squares = 0.0;
+    for (uint32_t b = 0; b < batch; ++b)
+      for (uint32_t f = 0; f < field; ++f) {
+        const double x = NORM_AT(acts, b, c, f);
+        sum += x;
+        squares += x * x;
+      }
+    const double m = sum / n;
+    if (stable) {
+      squares = 0.0;
+      for (uint32_t b = 0; b < batch; ++b)
+        for (uint32_t f = 0; f < field; ++f) {
+          const double d = NORM_AT(acts, b, c, f) - m;
+          squares += d * d;
+        }
+    }
+    const double biased = squares / n - (stable ? 0.0 : m * m);
+    const double var = n == 1.0 ? 1.0 : (unbiased ? biased * n / (n - 1.0) : biased);
+    mean[c] = m;
+    inv_std[c] = 1.0 / sqrt(var + eps);
+  }
+}
+
+void oracle_norm_normalise(const double *acts, const double *gamma,
+                           const double *beta, const double *mean,
+                           const double *inv_std, uint32_t batch,
+                           uint32_t chans, uint32_t field, double *out,
+                           double *whitened) {
+  for (uint32_t b = 0; b < batch; ++b)
+    for (uint32_t c = 0; c < chans; ++c)
+      for (uint32_t f = 0; f < field; ++f) {
+        const double w = (NORM_AT(acts, b, c, f) - mean[c]) * inv_std[c];
+        if (whitened) NORM_AT(whitened, b, c, f) = w;
+        if (out) NORM_AT(out, b, c, f) = gamma[c] * w + beta[c];
+      }
+}
+
+void oracle_norm_gradients(const double *whitened, const double *grads_in,
+                           const double *inv_std, const double *gamma,
+                           uint32_t batch, uint32_t chans, uint32_t field,
+                           double *grads_out) {
+  const double n = (double)batch * (double)field;
+  for (uint32_t c = 0; c < chans; ++c) {
+    double sum_g = 0.0, sum_wg = 0.0;
+    for (uint32_t b = 0; b < batch; ++b)
+      for (uint32_t f = 0; f < field; ++f) {
+        sum_g += NORM_AT(grads_in, b, c, f);
+        sum_wg += NORM_AT(whitened, b, c, f) * NORM_AT(grads_in, b, c, f);
+      }
+    for (uint32_t b = 0; b < batch; ++b)
+      for (uint32_t f = 0; f < field; ++f) {
+        const double t = NORM_AT(grads_in, b, c, f) -
+                         NORM_AT(whitened, b, c, f) * sum_wg / n - sum_g / n;
+        NORM_AT(grads_out, b, c, f) = t * gamma[c] * inv_std[c];
+      }
+  }
+}
+
+void oracle_norm_param_update(const double *whitened, const double *grads_in,
+                              double learning_rate, uint32_t batch,
+                              uint32_t chans, uint32_t field, double *gamma,
+                              double *beta) {
+  for (uint32_t c = 0; c < chans; ++c) {
+    double d_beta = 0.0, d_gamma = 0.0;
+    for (uint32_t b = 0; b < batch; ++b)
+      for (uint32_t f = 0; f < field; ++f) {
+        d_beta += NORM_AT(grads_in, b, c, f);
+        d_gamma += NORM_AT(whitened, b, c, f) * NORM_AT(grads_in, b, c, f);
+      }
+    beta[c] -= learning_rate * d_beta;
+    gamma[c] -= learning_rate * d_gamma;
+  }
+}
+#undef NORM_AT

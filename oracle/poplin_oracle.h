@@ -112,6 +112,34 @@ double oracle_round_to_half(double x);
 uint8_t oracle_e4m3_from_double(double x); /* RNE, saturating to +-448 */
 double oracle_e4m3_to_double(uint8_t bits);
 
+/* Batch normalisation over activations [batch][chans][field]
+ * (lib/poplibs_test/Norms.cpp, NormType::BatchNorm: statistics per channel
+ * over the batch and the field).
+ * Statistics: mean[c] and inv_std[c] = 1 / sqrt(var[c] + eps), var biased or
+ * (unbiased != 0) scaled by n / (n - 1); with stable != 0 the variance is the
+ * mean of squared deviations, else E[x^2] - mean^2 (:38-85). */
+void oracle_norm_statistics(const double *acts, uint32_t batch, uint32_t chans,
+                            uint32_t field, double eps, int unbiased,
+                            int stable, double *mean, double *inv_std);
+/* whitened = (acts - mean[c]) * inv_std[c]; out = gamma[c] * whitened + beta[c]
+ * (:147-176). */
+void oracle_norm_normalise(const double *acts, const double *gamma,
+                           const double *beta, const double *mean,
+                           const double *inv_std, uint32_t batch,
+                           uint32_t chans, uint32_t field, double *out,
+                           double *whitened);
+/* grads_out = (g - w * mean_c(w * g) - mean_c(g)) * gamma[c] * inv_std[c]
+ * (:226-262). */
+void oracle_norm_gradients(const double *whitened, const double *grads_in,
+                           const double *inv_std, const double *gamma,
+                           uint32_t batch, uint32_t chans, uint32_t field,
+                           double *grads_out);
+/* beta[c] -= lr * sum_c(g); gamma[c] -= lr * sum_c(w * g) (:346-375). */
+void oracle_norm_param_update(const double *whitened, const double *grads_in,
+                              double learning_rate, uint32_t batch,
+                              uint32_t chans, uint32_t field, double *gamma,
+                              double *beta);
+
 int oracle_num_threads(void);
 
 #ifdef __cplusplus

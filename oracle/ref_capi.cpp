@@ -1,6 +1,6 @@
 // C entry points over the REFERENCE's own CPU models, compiled unmodified from
-// the reference tree (lib/poplibs_test/Convolution.cpp and
-// lib/poplibs_test/GeneralMatrixMultiply.cpp) against the stand-in headers in
+// the reference tree (lib/poplibs_test/Convolution.cpp,
+// lib/poplibs_test/GeneralMatrixMultiply.cpp and lib/poplibs_test/Norms.cpp) against the stand-in headers in
 // oracle/shim.  TEST INFRASTRUCTURE ONLY: the resulting library
 // (oracle/_ref/libpoplibs_test_ref.so) validates the C restatement in
 // poplin_oracle.c, generates the golden vectors under tests/golden/, and is
@@ -9,6 +9,7 @@
 
 #include <poplibs_test/Convolution.hpp>
 #include <poplibs_test/GeneralMatrixMultiply.hpp>
+#include <poplibs_test/Norms.hpp>
 
 #include <cstring>
 #include <exception>
@@ -195,6 +196,54 @@ int ref_gemm(uint32_t groups, uint32_t m, uint32_t k, uint32_t n,
     boost::multi_array_ref<double, 3> dRef(d, boost::extents[groups][m][n]);
     poplibs_test::gemm::generalGroupedMatrixMultiply(
         aRef, bRef, cRef, dRef, alpha, beta, transposeA != 0, transposeB != 0);
+  });
+}
+
+// ---- the reference's batch-norm models (lib/poplibs_test/Norms.cpp) ------------
+using Ref3 = boost::multi_array_ref<double, 3>;
+using Ref1 = boost::multi_array_ref<double, 1>;
+static Ref3 r3(const double *p, uint32_t b, uint32_t c, uint32_t f) {
+  return Ref3(const_cast<double *>(p), boost::extents[b][c][f]);
+}
+static Ref1 r1(const double *p, uint32_t c) {
+  return Ref1(const_cast<double *>(p), boost::extents[c]);
+}
+constexpr auto kBatchNorm = poplibs_test::norm::NormType::BatchNorm;
+
+int ref_norm_statistics(const double *acts, uint32_t batch, uint32_t chans, uint32_t field,
+                        double eps, int unbiased, int stable, double *mean, double *inv_std) {
+  return guarded([&] {
+    poplibs_test::norm::normStatistics(r3(acts, batch, chans, field), eps, unbiased != 0, stable != 0,
+                                       r1(mean, chans), r1(inv_std, chans), kBatchNorm, false);
+  });
+}
+
+int ref_norm_normalise(const double *acts, const double *gamma, const double *beta, const double *mean,
+                       const double *inv_std, uint32_t batch, uint32_t chans, uint32_t field,
+                       double *out, double *whitened) {
+  return guarded([&] {
+    poplibs_test::norm::normalise(r3(acts, batch, chans, field), r1(gamma, chans), r1(beta, chans),
+                                  r1(mean, chans), r1(inv_std, chans), r3(out, batch, chans, field),
+                                  r3(whitened, batch, chans, field), kBatchNorm, false);
+  });
+}
+
+int ref_norm_gradients(const double *whitened, const double *grads_in, const double *inv_std,
+                       const double *gamma, uint32_t batch, uint32_t chans, uint32_t field,
+                       double *grads_out) {
+  return guarded([&] {
+    poplibs_test::norm::normGradients(r3(whitened, batch, chans, field), r3(grads_in, batch, chans, field),
+                                      r1(inv_std, chans), r1(gamma, chans),
+                                      r3(grads_out, batch, chans, field), kBatchNorm, false);
+  });
+}
+
+int ref_norm_param_update(const double *whitened, const double *grads_in, double learning_rate,
+                          uint32_t batch, uint32_t chans, uint32_t field, double *gamma, double *beta) {
+  return guarded([&] {
+    poplibs_test::norm::normParamUpdate(r3(whitened, batch, chans, field),
+                                        r3(grads_in, batch, chans, field), learning_rate,
+                                        r1(gamma, chans), r1(beta, chans), kBatchNorm);
   });
 }
 

@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <array>
 #include <cassert>
+#include <cmath>  // (the real header brings it in; the reference's models rely on that)
 #include <cstddef>
 #include <numeric>
 #include <type_traits>

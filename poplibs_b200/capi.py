@@ -141,7 +141,8 @@ SYMBOLS = (
     "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution",
     "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
     "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_bias_update", "plb_conv_fwd_host",
-    "plb_context_set_plan_flags", "plb_allreduce_f32_p2p", "plb_allreduce_f32_p2p_rs", "plb_conv_wu_allreduce",
+    "plb_context_set_plan_flags", "plb_norm_moments", "plb_norm_inv_std_dev", "plb_norm_whiten",
+    "plb_norm_scale_shift", "plb_norm_param_gradients", "plb_norm_statistics_gradients", "plb_allreduce_f32_p2p", "plb_allreduce_f32_p2p_rs", "plb_conv_wu_allreduce",
     "plb_conv_wu_allreduce_flag_bytes", "plb_allreduce_p2p_signal_bytes", "plb_matmul_host_async",
     "plb_conv_fwd_host_async",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
@@ -197,6 +198,12 @@ def lib():
     L.plb_add_bias.argtypes = [vp, i32, vp, vp, u64, u32]
     L.plb_conv_bias_update.argtypes = [vp, i32, vp, u64, u32, i32, vp, f32]
     L.plb_allreduce_f32_p2p.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u32, sz, vp, vp]
+    L.plb_norm_moments.argtypes = [vp, i32, vp, u64, u32, f32, vp, vp, vp]
+    L.plb_norm_inv_std_dev.argtypes = [vp, i32, vp, vp, u32, f32, f32, i32, vp]
+    L.plb_norm_whiten.argtypes = [vp, i32, vp, vp, vp, u64, u32, vp]
+    L.plb_norm_scale_shift.argtypes = [vp, i32, vp, vp, vp, u64, u32, vp]
+    L.plb_norm_param_gradients.argtypes = [vp, i32, vp, vp, u64, u32, f32, vp, vp, vp, vp]
+    L.plb_norm_statistics_gradients.argtypes = [vp, i32, vp, vp, vp, vp, vp, u64, u32, vp]
     L.plb_context_set_plan_flags.argtypes = [vp, i32]
     L.plb_context_set_plan_flags.restype = None
     L.plb_allreduce_f32_p2p_rs.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), u32, sz,
@@ -354,6 +361,35 @@ class Context:
         pads = (C.c_void_p * world)(*[int(p) for p in signal_pad_ptrs])
         _check(lib().plb_allreduce_f32_p2p_rs(self._h, rank, world, ins, res, pads, epoch, count,
                                               _ptr(out_f32), _ptr(out_half)))
+
+    # ---- batch normalisation (device layout [pixels][chans]) -------------------
+    def norm_moments(self, dtype, acts, pixels, chans, scale, centre, mean, power):
+        _check(lib().plb_norm_moments(self._h, dtype, _ptr(acts), pixels, chans, scale, _ptr(centre),
+                                      _ptr(mean), _ptr(power)))
+
+    def norm_inv_std_dev(self, dtype, mean, power, chans, eps, scale_var, stable, inv_std):
+        _check(lib().plb_norm_inv_std_dev(self._h, dtype, _ptr(mean), _ptr(power), chans, eps, scale_var,
+                                          int(stable), _ptr(inv_std)))
+
+    def norm_whiten(self, dtype, acts, mean, inv_std, pixels, chans, out):
+        _check(lib().plb_norm_whiten(self._h, dtype, _ptr(acts), _ptr(mean), _ptr(inv_std), pixels, chans,
+                                     _ptr(out)))
+
+    def norm_scale_shift(self, dtype, acts, scale, shift, pixels, chans, out):
+        _check(lib().plb_norm_scale_shift(self._h, dtype, _ptr(acts), _ptr(scale), _ptr(shift), pixels,
+                                          chans, _ptr(out)))
+
+    def norm_param_gradients(self, dtype, whitened, grads, pixels, chans, scale, gamma_delta, beta_delta,
+                             gamma_delta_f32=None, beta_delta_f32=None):
+        _check(lib().plb_norm_param_gradients(self._h, dtype, _ptr(whitened), _ptr(grads), pixels, chans,
+                                              scale, _ptr(gamma_delta), _ptr(beta_delta),
+                                              _ptr(gamma_delta_f32), _ptr(beta_delta_f32)))
+
+    def norm_statistics_gradients(self, dtype, whitened, grads, inv_std, pixels, chans, out,
+                                  var_delta=None, mean_delta=None):
+        _check(lib().plb_norm_statistics_gradients(self._h, dtype, _ptr(whitened), _ptr(grads),
+                                                   _ptr(inv_std), _ptr(var_delta), _ptr(mean_delta),
+                                                   pixels, chans, _ptr(out)))
 
     def cast_from_f32(self, dtype, dst, src, count):
         _check(lib().plb_cast_from_f32(self._h, dtype, _ptr(dst), _ptr(src), count))

@@ -1,0 +1,402 @@
+// Batch normalisation after a convolution: the kernels behind poplin's Norms
+// API (include/poplin/Norms.hpp:33-334, lib/poplin/Norms.cpp), on device-layout
+// activations [pixels][chans] (NHWC: the channels of a pixel are contiguous),
+// statistics per channel over all pixels.
+//
+// Every operation here moves each activation once or twice and does a handful
+// of flops on it: HBM bound.  The per-channel sums are column reductions of a
+// row-major matrix: a block covers 64 channels x a slab of rows, a thread
+// accumulates two adjacent channels (one 4-byte load per row for half) in fp32
+// down its rows, the block's eight row lanes are added in a fixed order in
+// shared memory, and each block leaves one partial per channel; a second
+// kernel adds the blocks' partials in block order.  The order of additions is
+// fixed, so results do not depend on timing (the reference's reductions are
+// deterministic too).  The element-wise kernels read their per-channel
+// operands from fp32 arrays and round once, in the output type.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <string>
+
+#include "runtime.h"
+#include "sm100_prims.cuh"
+
+namespace plb {
+namespace {
+
+constexpr int kNormChansPerBlock = 64;   // 32 threads x 2 channels
+constexpr int kNormRowLanes = 8;
+
+template <typename T> __device__ __forceinline__ float toFloat(T v);
+template <> __device__ __forceinline__ float toFloat<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float toFloat<float>(float v) { return v; }
+template <typename T> __device__ __forceinline__ T fromFloat(float v);
+template <> __device__ __forceinline__ __half fromFloat<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float fromFloat<float>(float v) { return v; }
+
+// What a column reduction adds up per channel (two sums at once).
+enum NormSums : int {
+  kSumXAndXX = 0,      // sum x, sum x^2
+  kSumCentredXX = 1,   // -, sum (x - centre[c])^2          (centre in the activations' type)
+  kSumXYAndY = 2,      // sum x * y, sum y                  (whitened activations x gradients)
+};
+
+template <typename T, int kMode>
+__global__ void __launch_bounds__(32 * kNormRowLanes)
+normColumnPartialsKernel(const T *__restrict__ x, const T *__restrict__ y,
+                         const T *__restrict__ centre, size_t rows, int chans,
+                         float *__restrict__ partial_a, float *__restrict__ partial_b) {
+  __shared__ float sa[kNormRowLanes][kNormChansPerBlock], sb[kNormRowLanes][kNormChansPerBlock];
+  const int c0 = blockIdx.x * kNormChansPerBlock + 2 * threadIdx.x;
+  const bool ok0 = c0 < chans, ok1 = c0 + 1 < chans;
+  float m0 = 0.f, m1 = 0.f;
+  if (kMode == kSumCentredXX) {
+    if (ok0) m0 = toFloat(centre[c0]);
+    if (ok1) m1 = toFloat(centre[c0 + 1]);
+  }
+  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+  for (size_t r = blockIdx.y * size_t(kNormRowLanes) + threadIdx.y; r < rows;
+       r += size_t(gridDim.y) * kNormRowLanes) {
+    const T *px = x + r * chans + c0;
+    float x0 = ok0 ? toFloat(px[0]) : 0.f, x1 = ok1 ? toFloat(px[1]) : 0.f;
+    if (kMode == kSumXAndXX) {
+      a0 += x0;
+      a1 += x1;
+      b0 += x0 * x0;
+      b1 += x1 * x1;
+    } else if (kMode == kSumCentredXX) {
+      // the deviation is formed in the activations' type, as the reference's
+      // "acts - cast(mean)" map does (lib/poplin/Norms.cpp:216-219)
+      const float d0 = toFloat(fromFloat<T>(x0 - m0)), d1 = toFloat(fromFloat<T>(x1 - m1));
+      b0 += ok0 ? d0 * d0 : 0.f;
+      b1 += ok1 ? d1 * d1 : 0.f;
+    } else {
+      const T *py = y + r * chans + c0;
+      const float y0 = ok0 ? toFloat(py[0]) : 0.f, y1 = ok1 ? toFloat(py[1]) : 0.f;
+      a0 += x0 * y0;
+      a1 += x1 * y1;
+      b0 += y0;
+      b1 += y1;
+    }
+  }
+  sa[threadIdx.y][2 * threadIdx.x] = a0;
+  sa[threadIdx.y][2 * threadIdx.x + 1] = a1;
+  sb[threadIdx.y][2 * threadIdx.x] = b0;
+  sb[threadIdx.y][2 * threadIdx.x + 1] = b1;
+  __syncthreads();
+  const int t = threadIdx.y * 32 + threadIdx.x;
+  if (t < kNormChansPerBlock) {
+    const int c = blockIdx.x * kNormChansPerBlock + t;
+    if (c < chans) {
+      float ta = sa[0][t], tb = sb[0][t];
+#pragma unroll
+      for (int l = 1; l < kNormRowLanes; ++l) {
+        ta += sa[l][t];
+        tb += sb[l][t];
+      }
+      partial_a[size_t(blockIdx.y) * chans + c] = ta;
+      partial_b[size_t(blockIdx.y) * chans + c] = tb;
+    }
+  }
+}
+
+// sums over the row blocks, in block order, times `scale`
+template <typename TA, typename TB>
+__global__ void normColumnFinishKernel(const float *__restrict__ partial_a,
+                                       const float *__restrict__ partial_b, int blocks, int chans,
+                                       float scale, TA *__restrict__ out_a, TB *__restrict__ out_b) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= chans) return;
+  float a = 0.f, b = 0.f;
+  for (int k = 0; k < blocks; ++k) {
+    a += partial_a[size_t(k) * chans + c];
+    b += partial_b[size_t(k) * chans + c];
+  }
+  if (out_a) out_a[c] = fromFloat<TA>(a * scale);
+  if (out_b) out_b[c] = fromFloat<TB>(b * scale);
+}
+
+// iStdDev from mean and power: the reference's InverseStdDeviation vertex
+// (lib/poplin/codelets/InverseStdDeviation.cpp:33-55), in fp32.
+template <typename T>
+__global__ void normInvStdDevKernel(const T *__restrict__ mean, const float *__restrict__ power,
+                                    int chans, float eps, float scale_var, int stable,
+                                    T *__restrict__ inv_std) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= chans) return;
+  float var;
+  if (stable) {
+    var = (power[c] + eps) * scale_var;
+  } else {
+    const float m = toFloat(mean[c]);
+    var = power[c] - m * m;
+    if (var < 0.f) var = 0.f;   // rounding can make the estimate negative
+    var = (var + eps) * scale_var;
+  }
+  inv_std[c] = fromFloat<T>(1.0f / sqrtf(var));
+}
+
+// Element-wise forms, one thread per element, channel = index mod chans.
+enum NormMap : int {
+  kWhiten = 0,          // (x - p[c]) * q[c]
+  kScaleShift = 1,      // x * p[c] + q[c]
+  kScale = 2,           // x * p[c]
+  kStatsGrad = 3,       // (y + x * p[c] + q[c]) * r[c]     x = whitened, y = gradient
+};
+
+template <typename T, int kMode>
+__global__ void normMapKernel(const T *__restrict__ x, const T *__restrict__ y,
+                              const T *__restrict__ p, const T *__restrict__ q,
+                              const T *__restrict__ r, const float *__restrict__ pf,
+                              const float *__restrict__ qf, size_t count, int chans,
+                              T *__restrict__ out) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < count;
+       i += size_t(gridDim.x) * blockDim.x) {
+    const int c = int(i % size_t(chans));
+    const float v = toFloat(x[i]);
+    float o;
+    if (kMode == kWhiten)
+      o = (v - toFloat(p[c])) * toFloat(q[c]);
+    else if (kMode == kScaleShift)
+      o = v * toFloat(p[c]) + toFloat(q[c]);
+    else if (kMode == kScale)
+      o = v * toFloat(p[c]);
+    else
+      o = (toFloat(y[i]) + v * (pf ? pf[c] : toFloat(p[c])) + (qf ? qf[c] : toFloat(q[c]))) * toFloat(r[c]);
+    out[i] = fromFloat<T>(o);
+  }
+}
+
+int rowBlocks(const plb_context *ctx, size_t rows, int chans) {
+  const int chan_blocks = (chans + kNormChansPerBlock - 1) / kNormChansPerBlock;
+  const size_t want = (rows + 4 * kNormRowLanes - 1) / (4 * kNormRowLanes);   // >= 4 rows per thread
+  const size_t cap = std::max<size_t>(1, size_t(ctx->sm_count) * 8 / size_t(chan_blocks));
+  return int(std::max<size_t>(1, std::min(want, cap)));
+}
+
+// Column sums of mode kMode -> out_a, out_b (either may be null), times scale.
+template <typename T, int kMode, typename TA, typename TB>
+int columnSums(plb_context *ctx, const T *x, const T *y, const T *centre, size_t rows, int chans,
+               float scale, TA *out_a, TB *out_b) {
+  const int blocks = rowBlocks(ctx, rows, chans);
+  void *ws = nullptr;
+  if (int rc = scratch(ctx, kSlotBiasUpdate, size_t(2) * blocks * chans * sizeof(float), &ws)) return rc;
+  float *pa = static_cast<float *>(ws), *pb = pa + size_t(blocks) * chans;
+  const dim3 grid(unsigned((chans + kNormChansPerBlock - 1) / kNormChansPerBlock), unsigned(blocks));
+  normColumnPartialsKernel<T, kMode><<<grid, dim3(32, kNormRowLanes), 0, ctx->stream>>>(
+      x, y, centre, rows, chans, pa, pb);
+  PLB_CUDA(cudaGetLastError());
+  normColumnFinishKernel<TA, TB><<<(chans + 127) / 128, 128, 0, ctx->stream>>>(pa, pb, blocks, chans,
+                                                                               scale, out_a, out_b);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches += 2;
+  return PLB_OK;
+}
+
+template <typename T, int kMode>
+int mapLaunch(plb_context *ctx, const T *x, const T *y, const T *p, const T *q, const T *r,
+              const float *pf, const float *qf, size_t count, int chans, T *out) {
+  if (count == 0) return PLB_OK;
+  const int grid = int(std::min<size_t>((count + 255) / 256, size_t(ctx->sm_count) * 16));
+  normMapKernel<T, kMode><<<grid, 256, 0, ctx->stream>>>(x, y, p, q, r, pf, qf, count, chans, out);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int checkNorm(int32_t dtype, uint64_t pixels, uint32_t chans) {
+  if (dtype != PLB_HALF && dtype != PLB_FLOAT)
+    return fail(PLB_ERR_UNSUPPORTED, "normalisation is implemented for half and float activations");
+  if (chans == 0 || chans > (1u << 30) || pixels > (uint64_t(1) << 40))
+    return fail(PLB_ERR_INVALID_PARAMS, "normalisation: channel or pixel count out of range");
+  return PLB_OK;
+}
+
+}  // namespace
+}  // namespace plb
+
+using namespace plb;
+
+#define PLB_NORM_DISPATCH(dtype, CALL_HALF, CALL_FLOAT) \
+  ((dtype) == PLB_HALF ? (CALL_HALF) : (CALL_FLOAT))
+
+extern "C" {
+
+int plb_norm_moments(plb_context *ctx, int32_t dtype, const void *d_acts, uint64_t pixels,
+                     uint32_t chans, float scale, const void *d_centre, void *d_mean,
+                     float *d_power) {
+  TraceRange trace_range("plb_norm_moments");
+  if (int rc = activate(ctx)) return rc;
+  if (int rc = checkNorm(dtype, pixels, chans)) return rc;
+  if (!d_acts && pixels) return fail(PLB_ERR_INVALID_PARAMS, "null activations");
+  if (d_centre) {
+    // mean of squared deviations from a given centre (the "stable" estimator)
+    return PLB_NORM_DISPATCH(
+        dtype,
+        (columnSums<__half, kSumCentredXX, __half, float>(
+            ctx, static_cast<const __half *>(d_acts), nullptr, static_cast<const __half *>(d_centre),
+            pixels, int(chans), scale, nullptr, d_power)),
+        (columnSums<float, kSumCentredXX, float, float>(
+            ctx, static_cast<const float *>(d_acts), nullptr, static_cast<const float *>(d_centre),
+            pixels, int(chans), scale, nullptr, d_power)));
+  }
+  return PLB_NORM_DISPATCH(
+      dtype,
+      (columnSums<__half, kSumXAndXX, __half, float>(ctx, static_cast<const __half *>(d_acts), nullptr,
+                                                     nullptr, pixels, int(chans), scale,
+                                                     static_cast<__half *>(d_mean), d_power)),
+      (columnSums<float, kSumXAndXX, float, float>(ctx, static_cast<const float *>(d_acts), nullptr,
+                                                   nullptr, pixels, int(chans), scale,
+                                                   static_cast<float *>(d_mean), d_power)));
+}
+
+int plb_norm_inv_std_dev(plb_context *ctx, int32_t dtype, const void *d_mean, const float *d_power,
+                         uint32_t chans, float eps, float scale_var, int stable, void *d_inv_std) {
+  if (int rc = activate(ctx)) return rc;
+  if (int rc = checkNorm(dtype, 0, chans)) return rc;
+  if (!d_power || !d_inv_std || (!stable && !d_mean))
+    return fail(PLB_ERR_INVALID_PARAMS, "normalisation: null statistics pointer");
+  const int grid = int((chans + 127) / 128);
+  if (dtype == PLB_HALF)
+    normInvStdDevKernel<__half><<<grid, 128, 0, ctx->stream>>>(
+        static_cast<const __half *>(d_mean), d_power, int(chans), eps, scale_var, stable,
+        static_cast<__half *>(d_inv_std));
+  else
+    normInvStdDevKernel<float><<<grid, 128, 0, ctx->stream>>>(static_cast<const float *>(d_mean),
+                                                             d_power, int(chans), eps, scale_var,
+                                                             stable, static_cast<float *>(d_inv_std));
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
+int plb_norm_whiten(plb_context *ctx, int32_t dtype, const void *d_acts, const void *d_mean,
+                    const void *d_inv_std, uint64_t pixels, uint32_t chans, void *d_out) {
+  TraceRange trace_range("plb_norm_whiten");
+  if (int rc = activate(ctx)) return rc;
+  if (int rc = checkNorm(dtype, pixels, chans)) return rc;
+  const size_t n = size_t(pixels) * chans;
+  return PLB_NORM_DISPATCH(
+      dtype,
+      (mapLaunch<__half, kWhiten>(ctx, static_cast<const __half *>(d_acts), nullptr,
+                                  static_cast<const __half *>(d_mean),
+                                  static_cast<const __half *>(d_inv_std), nullptr, nullptr, nullptr, n,
+                                  int(chans), static_cast<__half *>(d_out))),
+      (mapLaunch<float, kWhiten>(ctx, static_cast<const float *>(d_acts), nullptr,
+                                 static_cast<const float *>(d_mean),
+                                 static_cast<const float *>(d_inv_std), nullptr, nullptr, nullptr, n,
+                                 int(chans), static_cast<float *>(d_out))));
+}
+
+int plb_norm_scale_shift(plb_context *ctx, int32_t dtype, const void *d_acts, const void *d_scale,
+                         const void *d_shift, uint64_t pixels, uint32_t chans, void *d_out) {
+  TraceRange trace_range("plb_norm_scale_shift");
+  if (int rc = activate(ctx)) return rc;
+  if (int rc = checkNorm(dtype, pixels, chans)) return rc;
+  const size_t n = size_t(pixels) * chans;
+  if (d_shift)
+    return PLB_NORM_DISPATCH(
+        dtype,
+        (mapLaunch<__half, kScaleShift>(ctx, static_cast<const __half *>(d_acts), nullptr,
+                                        static_cast<const __half *>(d_scale),
+                                        static_cast<const __half *>(d_shift), nullptr, nullptr, nullptr,
+                                        n, int(chans), static_cast<__half *>(d_out))),
+        (mapLaunch<float, kScaleShift>(ctx, static_cast<const float *>(d_acts), nullptr,
+                                       static_cast<const float *>(d_scale),
+                                       static_cast<const float *>(d_shift), nullptr, nullptr, nullptr, n,
+                                       int(chans), static_cast<float *>(d_out))));
+  return PLB_NORM_DISPATCH(
+      dtype,
+      (mapLaunch<__half, kScale>(ctx, static_cast<const __half *>(d_acts), nullptr,
+                                 static_cast<const __half *>(d_scale), nullptr, nullptr, nullptr, nullptr,
+                                 n, int(chans), static_cast<__half *>(d_out))),
+      (mapLaunch<float, kScale>(ctx, static_cast<const float *>(d_acts), nullptr,
+                                static_cast<const float *>(d_scale), nullptr, nullptr, nullptr, nullptr, n,
+                                int(chans), static_cast<float *>(d_out))));
+}
+
+int plb_norm_param_gradients(plb_context *ctx, int32_t dtype, const void *d_whitened,
+                             const void *d_grads, uint64_t pixels, uint32_t chans, float scale,
+                             void *d_gamma_delta, void *d_beta_delta, float *d_gamma_delta_f32,
+                             float *d_beta_delta_f32) {
+  TraceRange trace_range("plb_norm_param_gradients");
+  if (int rc = activate(ctx)) return rc;
+  if (int rc = checkNorm(dtype, pixels, chans)) return rc;
+  if (d_gamma_delta_f32 || d_beta_delta_f32) {
+    // fp32 sums (what the statistics gradient consumes)
+    if (int rc = PLB_NORM_DISPATCH(
+            dtype,
+            (columnSums<__half, kSumXYAndY, float, float>(
+                ctx, static_cast<const __half *>(d_whitened), static_cast<const __half *>(d_grads),
+                nullptr, pixels, int(chans), scale, d_gamma_delta_f32, d_beta_delta_f32)),
+            (columnSums<float, kSumXYAndY, float, float>(
+                ctx, static_cast<const float *>(d_whitened), static_cast<const float *>(d_grads),
+                nullptr, pixels, int(chans), scale, d_gamma_delta_f32, d_beta_delta_f32))))
+      return rc;
+  }
+  if (d_gamma_delta || d_beta_delta)
+    return PLB_NORM_DISPATCH(
+        dtype,
+        (columnSums<__half, kSumXYAndY, __half, __half>(
+            ctx, static_cast<const __half *>(d_whitened), static_cast<const __half *>(d_grads), nullptr,
+            pixels, int(chans), scale, static_cast<__half *>(d_gamma_delta),
+            static_cast<__half *>(d_beta_delta))),
+        (columnSums<float, kSumXYAndY, float, float>(
+            ctx, static_cast<const float *>(d_whitened), static_cast<const float *>(d_grads), nullptr,
+            pixels, int(chans), scale, static_cast<float *>(d_gamma_delta),
+            static_cast<float *>(d_beta_delta))));
+  return PLB_OK;
+}
+
+int plb_norm_statistics_gradients(plb_context *ctx, int32_t dtype, const void *d_whitened,
+                                  const void *d_grads, const void *d_inv_std, const void *d_var_delta,
+                                  const void *d_mean_delta, uint64_t pixels, uint32_t chans,
+                                  void *d_out) {
+  TraceRange trace_range("plb_norm_statistics_gradients");
+  if (int rc = activate(ctx)) return rc;
+  if (int rc = checkNorm(dtype, pixels, chans)) return rc;
+  if (pixels == 0) return PLB_OK;
+  if ((d_var_delta == nullptr) != (d_mean_delta == nullptr))
+    return fail(PLB_ERR_INVALID_PARAMS, "give both per-channel deltas or neither");
+  if (d_var_delta) {
+    // the two per-channel means come from the caller (already reduced over replicas)
+    const size_t n = size_t(pixels) * chans;
+    return PLB_NORM_DISPATCH(
+        dtype,
+        (mapLaunch<__half, kStatsGrad>(ctx, static_cast<const __half *>(d_whitened),
+                                       static_cast<const __half *>(d_grads),
+                                       static_cast<const __half *>(d_var_delta),
+                                       static_cast<const __half *>(d_mean_delta),
+                                       static_cast<const __half *>(d_inv_std), nullptr, nullptr, n,
+                                       int(chans), static_cast<__half *>(d_out))),
+        (mapLaunch<float, kStatsGrad>(ctx, static_cast<const float *>(d_whitened),
+                                      static_cast<const float *>(d_grads),
+                                      static_cast<const float *>(d_var_delta),
+                                      static_cast<const float *>(d_mean_delta),
+                                      static_cast<const float *>(d_inv_std), nullptr, nullptr, n,
+                                      int(chans), static_cast<float *>(d_out))));
+  }
+  // -mean(whitened * grads) and -mean(grads) per channel, kept in fp32, then
+  // out = (grads + whitened * varDelta + meanDelta) * invStdDev
+  // (lib/poplin/Norms.cpp:447-512, without its split of the scale in two
+  // factors, which only serves half-precision intermediates)
+  void *ws = nullptr;
+  if (int rc = scratch(ctx, kSlotUsedTaps, size_t(2) * chans * sizeof(float) + 256, &ws)) return rc;
+  float *var_delta = static_cast<float *>(ws), *mean_delta = var_delta + chans;
+  if (int rc = plb_norm_param_gradients(ctx, dtype, d_whitened, d_grads, pixels, chans,
+                                        -1.0f / float(pixels), nullptr, nullptr, var_delta, mean_delta))
+    return rc;
+  const size_t n = size_t(pixels) * chans;
+  return PLB_NORM_DISPATCH(
+      dtype,
+      (mapLaunch<__half, kStatsGrad>(ctx, static_cast<const __half *>(d_whitened),
+                                     static_cast<const __half *>(d_grads), nullptr, nullptr,
+                                     static_cast<const __half *>(d_inv_std), var_delta, mean_delta, n,
+                                     int(chans), static_cast<__half *>(d_out))),
+      (mapLaunch<float, kStatsGrad>(ctx, static_cast<const float *>(d_whitened),
+                                    static_cast<const float *>(d_grads), nullptr, nullptr,
+                                    static_cast<const float *>(d_inv_std), var_delta, mean_delta, n,
+                                    int(chans), static_cast<float *>(d_out))));
+}
+
+}  // extern "C"

@@ -233,6 +233,17 @@ Tensor withGroupDim(const Tensor &weights, const ConvParams &p) {
 
 }  // namespace
 
+namespace internal {
+Tensor actsInKernelLayout(Graph &graph, const Tensor &acts, Sequence &prog, bool copyValues) {
+  return arranged(graph, acts, actsOrder(acts.rank()), prog, copyValues);
+}
+Tensor newActsLike(Graph &graph, const Tensor &like, const poplar::Type &type, const std::string &name) {
+  const auto shape = like.shape();
+  return makeActs(graph, type, shape[0], shape[1],
+                  std::vector<std::size_t>(shape.begin() + 2, shape.end()), name);
+}
+}  // namespace internal
+
 // ---- flops ------------------------------------------------------------------------
 std::uint64_t getFwdFlops(const ConvParams &params) {
   const plb_conv_params flat = internal::toPlb(params);

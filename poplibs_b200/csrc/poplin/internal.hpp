@@ -3,7 +3,10 @@
 
 #include <string>
 
+#include "poplar/Graph.hpp"
 #include "poplar/OptionFlags.hpp"
+#include "poplar/Program.hpp"
+#include "poplar/Tensor.hpp"
 #include "poplin/ConvParams.hpp"
 #include "poplibs_b200.h"
 
@@ -57,6 +60,15 @@ std::string validatePlanConstraints(const std::string &jsonText);
 /// matMul option set -> equivalent convolution option set
 /// (lib/poplin/MatMul.cpp:113-195).
 poplar::OptionFlags matMulToConvOptions(const poplar::OptionFlags &matmulOptions);
+
+/// `acts` ([N][C][field...]) in the kernels' memory order (N, field..., C):
+/// itself when it already is, else a scratch copy recorded in `prog`.
+poplar::Tensor actsInKernelLayout(poplar::Graph &graph, const poplar::Tensor &acts,
+                                  poplar::program::Sequence &prog, bool copyValues = true);
+/// A new activations tensor of the logical shape of `like` and element type
+/// `type`, stored in the kernels' memory order.
+poplar::Tensor newActsLike(poplar::Graph &graph, const poplar::Tensor &like, const poplar::Type &type,
+                           const std::string &name);
 
 }  // namespace internal
 }  // namespace poplin

@@ -22,6 +22,7 @@
 #include "poplin/FullyConnected.hpp"
 #include "poplin/MatMul.hpp"
 #include "poplin/MultiConvolution.hpp"
+#include "poplin/Norms.hpp"
 #include "poplin/codelets.hpp"
 #include "poputil/exceptions.hpp"
 
@@ -361,6 +362,44 @@ static void testGraphConstructionWithoutDevice() {
     CHECK((t.shape() == std::vector<std::size_t>{2, 40, 96, 1}) && fcProg.steps().size() == 1);
     ConvParams twoD(HALF, HALF, 4, {2, 2}, {1, 1}, 96, 40, 2);
     CHECK((throwsAs<poputil::poplibs_error>([&] { fullyConnectedWeightTranspose(graph, fcw, twoD, fcProg); })));
+  }
+  // normalisation after a convolution: shapes, types, recorded steps, errors
+  {
+    poplar::program::Sequence np_;
+    auto acts = createConvOutput(graph, p, "bnActs");
+    auto st = normStatistics(graph, acts, 1e-3f, np_, true, false, FLOAT, "bn");
+    CHECK(st.first.shape() == std::vector<std::size_t>{64} && st.second.elementType() == HALF);
+    auto gb = createNormParams(graph, acts, "bn");
+    CHECK(gb.first.numElements() == 64 && gb.second.numElements() == 64);
+    CHECK(createNormGamma(graph, acts, FLOAT).elementType() == FLOAT);
+    auto wht = normWhiten(graph, acts, st.first, st.second, np_, "bn");
+    auto nrm = normalise(graph, wht, gb.first, gb.second, np_, "bn");
+    CHECK(wht.shape() == acts.shape() && nrm.shape() == acts.shape());
+    auto pg = normParamGradients(graph, wht, nrm, np_);
+    CHECK(pg.first.numElements() == 64 && pg.second.elementType() == HALF);
+    CHECK(normGradients(graph, nrm, gb.first, np_).shape() == acts.shape());
+    CHECK(normStatisticsGradients(graph, wht, nrm, st.second, np_).shape() == acts.shape());
+    const std::size_t before = np_.steps().size();
+    // the distributed forms call the reduction callback with (mean, power) / the two deltas
+    unsigned calls = 0, tensors = 0;
+    DistributedNormReduceCallback cb = [&](poplar::Graph &, const std::vector<poplar::Tensor> &in,
+                                           poplar::program::Sequence &, unsigned groupSize,
+                                           const poplar::DebugContext &, const poplar::OptionFlags &) {
+      ++calls;
+      tensors += unsigned(in.size());
+      CHECK(groupSize == 4);
+      return in;
+    };
+    auto dst = distributedNormStatistics(graph, acts, 1e-3f, np_, false, cb, 128);
+    CHECK(calls == 1 && tensors == 2 && dst.first.numElements() == 64);
+    distributedNormStatistics(graph, acts, 1e-3f, np_, false, cb, 128, true);
+    CHECK(calls == 3 && tensors == 4);   // stable: the mean, then the power
+    distributedNormStatisticsGradients(graph, wht, nrm, st.second, np_, cb, 128);
+    CHECK(calls == 4 && tensors == 6 && np_.steps().size() > before);
+    CHECK((throwsAs<poputil::poplibs_error>([&] { distributedNormStatistics(graph, acts, 1e-3f, np_, false, cb, 100); })));
+    CHECK((throwsAs<poputil::poplibs_error>([&] { normWhiten(graph, acts, st.first.slice(0, 8, 0), st.second, np_); })));
+    auto q8 = graph.addVariable(QUARTER, {2, 8, 4, 4}, "q8");
+    CHECK((throwsAs<poputil::poplibs_error>([&] { normStatistics(graph, q8, 1e-3f, np_, false); })));
   }
   // the full constructor does not validate; validate() does
   {

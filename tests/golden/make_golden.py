@@ -69,6 +69,16 @@ GEMM_CASES = {
 }
 
 
+NORM_CASES = {
+    # (batch, chans, field elements, unbiased variance, stable algorithm)
+    "bn_4x8x25": (4, 8, 25, False, False),
+    "bn_unbiased": (3, 5, 7, True, False),
+    "bn_stable": (2, 16, 9, False, True),
+    "bn_stable_unbiased": (5, 3, 4, True, True),
+    "bn_single_element": (1, 4, 1, True, False),
+}
+
+
 def main():
     if not oracle.have_ref():
         raise SystemExit("oracle/_ref/libpoplibs_test_ref.so is missing: run `make -C oracle ref`")
@@ -113,6 +123,23 @@ def main():
         out[f"gemm/{name}/d"] = oracle.gemm(a, b, c, alpha, beta, ta, tb, use_ref=True)
         meta[f"gemm/{name}"] = dict(groups=g, m=m, k=k, n=n, alpha=alpha, beta=beta,
                                     transpose_a=ta, transpose_b=tb)
+    # batch normalisation (lib/poplibs_test/Norms.cpp, BatchNorm): shapes echo the
+    # reference's norm layer tests (tests/popnn/BatchNormTest / NormLayerTests:
+    # small batches of a few channels, fields of one and two dimensions)
+    for idx, (name, (b, c, f, unbiased, stable)) in enumerate(sorted(NORM_CASES.items())):
+        r = np.random.default_rng(3000 + idx)
+        x = r.normal(0.5, 2.0, (b, c, f))
+        g = r.uniform(-1, 1, (b, c, f))
+        gamma, beta = r.uniform(0.5, 2.0, c), r.uniform(-1, 1, c)
+        mean, inv = oracle.norm_statistics(x, 1e-3, unbiased, stable, use_ref=True)
+        y, white = oracle.norm_normalise(x, gamma, beta, mean, inv, use_ref=True)
+        dx = oracle.norm_gradients(white, g, inv, gamma, use_ref=True)
+        gamma2, beta2 = oracle.norm_param_update(white, g, 0.25, gamma, beta, use_ref=True)
+        for key, val in dict(x=x, g=g, gamma=gamma, beta=beta, mean=mean, inv_std=inv, y=y, whitened=white,
+                             dx=dx, gamma_updated=gamma2, beta_updated=beta2).items():
+            out[f"norm/{name}/{key}"] = val
+        meta[f"norm/{name}"] = dict(batch=b, chans=c, field=f, eps=1e-3, unbiased=unbiased, stable=stable,
+                                    learning_rate=0.25)
     np.savez_compressed(os.path.join(HERE, "poplibs_test_models.npz"), **out)
     with open(os.path.join(HERE, "poplibs_test_models.json"), "w") as f:
         json.dump(meta, f, indent=1, sort_keys=True)

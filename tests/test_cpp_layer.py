@@ -265,3 +265,41 @@ def test_multiconv_on_gpu_against_oracle(tmp_path):
         assert (got == dw.astype(np.float16).astype(np.float64)).all(), f"multiconv weight gradient {i}"
         upd = (w + -0.5 * dw).astype(np.float16).astype(np.float64)
         assert (t[f"wUpdated{i}"] == upd).all(), f"multiconv weight update {i}"
+
+
+@pytest.mark.gpu
+def test_convolution_then_batch_norm_on_gpu_against_oracle(tmp_path):
+    """poplin::convolution followed by the Norms chain (statistics, whiten,
+    normalise; then the three gradients) through the Engine, each stage against
+    the CPU models fed with the device's own inputs to that stage."""
+    import numpy as np
+    import oracle
+    from oracle import ConvSpec
+    exe = str(tmp_path / "conv_norm_gpu")
+    compile_cpp(os.path.join(ROOT, "tests", "cpp", "conv_norm_gpu.cpp"), exe)
+    d = tmp_path / "dump"
+    d.mkdir()
+    run = subprocess.run([exe, str(d)], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stdout + run.stderr
+    t = load_dump(str(d))
+
+    def close(got, want, rel, what):
+        want = np.asarray(want, dtype=np.float64).reshape(got.shape)
+        rms = float(np.sqrt(np.mean(want * want)))
+        bad, first, worst = oracle.check_is_close(got, want, rel, max(1e-6, rel * rms))
+        assert bad == 0, (what, bad, got.ravel()[first], want.ravel()[first])
+    spec = ConvSpec.simple(4, [10, 10], [3, 3], 16, 32, padding=1)
+    close(t["y"], oracle.conv_fwd(spec, t["in"], t["w"]), 1e-3, "convolution")
+    mean, inv = oracle.norm_statistics(t["y"], 1e-3, unbiased=True)
+    close(t["mean"], mean, 2e-3, "mean")
+    close(t["iStdDev"], inv, 5e-3, "inverse standard deviation")
+    out, white = oracle.norm_normalise(t["y"], t["gamma"], t["beta"], t["mean"], t["iStdDev"])
+    close(t["white"], white, 2e-3, "whitened")
+    close(t["out"], t["gamma"][None, :, None, None] * t["white"] + t["beta"][None, :, None, None], 2e-3, "normalised")
+    close(t["gradWhite"], t["gradOut"] * t["gamma"][None, :, None, None], 2e-3, "normGradients")
+    zero = np.zeros(32)
+    ga, be = oracle.norm_param_update(t["white"], t["gradOut"], 1.0, zero, zero)
+    close(t["gammaGrad"], -ga, 4e-3, "gamma gradient")
+    close(t["betaGrad"], -be, 4e-3, "beta gradient")
+    close(t["gradY"], oracle.norm_gradients(t["white"], t["gradWhite"], t["iStdDev"], np.ones(32)), 4e-3,
+          "normStatisticsGradients")

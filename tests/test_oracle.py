@@ -197,3 +197,36 @@ def test_number_formats():
     v = r.normal(size=20000) * 8
     assert (oracle._e4m3_encode_np(v) ==
             np.array([oracle._lib().oracle_e4m3_from_double(float(t)) for t in v], dtype=np.uint8)).all()
+
+
+@pytest.mark.parametrize("name", sorted(k[len("norm/"):] for k in META if k.startswith("norm/")))
+def test_norm_against_golden(name):
+    """The C restatement of the batch-norm models against vectors produced by
+    the reference's own lib/poplibs_test/Norms.cpp."""
+    m = META[f"norm/{name}"]
+    g = lambda k: GOLD[f"norm/{name}/{k}"]   # noqa: E731
+    mean, inv = oracle.norm_statistics(g("x"), m["eps"], m["unbiased"], m["stable"])
+    assert np.array_equal(mean, g("mean")) and np.array_equal(inv, g("inv_std"))
+    y, white = oracle.norm_normalise(g("x"), g("gamma"), g("beta"), mean, inv)
+    assert np.array_equal(y, g("y")) and np.array_equal(white, g("whitened"))
+    assert np.array_equal(oracle.norm_gradients(white, g("g"), inv, g("gamma")), g("dx"))
+    ga, be = oracle.norm_param_update(white, g("g"), m["learning_rate"], g("gamma"), g("beta"))
+    assert np.array_equal(ga, g("gamma_updated")) and np.array_equal(be, g("beta_updated"))
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="reference models not built here")
+def test_norm_oracle_equals_reference_on_random_shapes():
+    r = np.random.default_rng(17)
+    for _ in range(20):
+        b, c, f = (int(v) for v in r.integers(1, 7, 3))
+        x, gr = r.normal(0.3, 1.5, (b, c, f)), r.normal(size=(b, c, f))
+        gamma, beta = r.uniform(0.5, 2, c), r.normal(size=c)
+        unb, st = bool(r.integers(0, 2)), bool(r.integers(0, 2))
+        a = oracle.norm_statistics(x, 1e-4, unb, st)
+        b_ = oracle.norm_statistics(x, 1e-4, unb, st, use_ref=True)
+        assert np.array_equal(a[0], b_[0]) and np.array_equal(a[1], b_[1])
+        y1, w1 = oracle.norm_normalise(x, gamma, beta, *a)
+        y2, w2 = oracle.norm_normalise(x, gamma, beta, *a, use_ref=True)
+        assert np.array_equal(y1, y2) and np.array_equal(w1, w2)
+        assert np.array_equal(oracle.norm_gradients(w1, gr, a[1], gamma),
+                              oracle.norm_gradients(w1, gr, a[1], gamma, use_ref=True))
