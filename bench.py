@@ -81,6 +81,8 @@ WORKLOADS = {
     "conv7x7_s2_fwd_n256_224x224_c3_c64": dict(kind="conv", pass_="fwd", bound="hbm",
                                                params=dict(batch=256, field=[224, 224], kernel=[7, 7],
                                                            in_chans=3, out_chans=64, padding=3, stride=2)),
+    # batch normalisation of the 3x3 layer's output, forward: statistics, whiten, scale and shift
+    "batchnorm_fwd_n32_56x56_c64": dict(kind="norm", bound="hbm", batch=32, field=[56, 56], chans=64),
     "matmul_fp16_512x1024x1024": dict(kind="gemm", m=512, k=1024, n=1024, quarter=False, bound="tensor"),
     "matmul_fp16_8192": dict(kind="gemm", m=8192, k=8192, n=8192, quarter=False, bound="tensor"),
     "matmul_fp8_8192": dict(kind="gemm", m=8192, k=8192, n=8192, quarter=True, bound="tensor"),
@@ -240,7 +242,18 @@ class Workload:
 
         def uniform(shape, scale=1.0):
             return ((torch.rand(shape, generator=g, device=device) * 2 - 1) * scale).half()
-        if self.kind == "conv":
+        if self.kind == "norm":
+            shape = (spec["batch"], *spec["field"], spec["chans"])
+            self.pixels, self.chans = int(np.prod(shape[:-1])), spec["chans"]
+            proto = {"x": uniform(shape).add_(0.25), "gamma": uniform((self.chans,)).abs_().add_(0.5),
+                     "beta": uniform((self.chans,))}
+            self.flops = 0
+            # the activations are read twice (moments, whiten), the whitened ones written and read, the output written
+            self.plan = {"kernel": "norm column sums + element-wise maps",
+                         "bytes": 5 * 2 * self.pixels * self.chans}
+            per_set = 3 * 2 * self.pixels * self.chans
+            out_shape = shape
+        elif self.kind == "conv":
             p = capi.ConvParams.make(**spec["params"])
             self.p = p
             kw = spec["params"]
@@ -296,6 +309,11 @@ class Workload:
         for i in range(self.nsets):
             d = proto if i == 0 else {k: v.clone() for k, v in proto.items()}
             d["out"] = torch.empty(out_shape, dtype=torch.float16, device=device)
+            if self.kind == "norm":
+                d["white"] = torch.empty(out_shape, dtype=torch.float16, device=device)
+                d["mean"] = torch.empty(self.chans, dtype=torch.float16, device=device)
+                d["inv"] = torch.empty(self.chans, dtype=torch.float16, device=device)
+                d["power"] = torch.empty(self.chans, dtype=torch.float32, device=device)
             if self.kind == "conv" and self.pass_ == "wu":
                 d["out32"] = torch.empty(out_shape, dtype=torch.float32, device=device)
             self.dev.append(d)
@@ -317,7 +335,13 @@ class Workload:
 
     def step(self, i):
         d = self.dev[i % self.nsets]
-        if self.kind == "gemm":
+        if self.kind == "norm":
+            H, c, n = self.capi.HALF, self.chans, self.pixels
+            self.ctx.norm_moments(H, d["x"], n, c, 1.0 / n, None, d["mean"], d["power"])
+            self.ctx.norm_inv_std_dev(H, d["mean"], d["power"], c, 1e-3, 1.0, False, d["inv"])
+            self.ctx.norm_whiten(H, d["x"], d["mean"], d["inv"], n, c, d["white"])
+            self.ctx.norm_scale_shift(H, d["white"], d["gamma"], d["beta"], n, c, d["out"])
+        elif self.kind == "gemm":
             self.ctx.matmul(self.desc, d["a"], d["b"], None, d["out"])
         elif self.pass_ == "fwd":
             self.ctx.conv_fwd(self.p, d["x"], d["w"], d["out"])
@@ -367,7 +391,7 @@ class Workload:
             c.conv_fwd_host(self.p, self.host["x"], self.host["w"], out, sync=False)
 
     def has_e2e(self):
-        return self.kind == "gemm" or self.pass_ == "fwd"
+        return self.kind == "gemm" or (self.kind == "conv" and self.pass_ == "fwd")
 
     # ---- correctness evidence carried by the bench line ------------------------------
     def parity_check(self):
@@ -380,7 +404,19 @@ class Workload:
         import oracle
         d = self.dev[0]
         rel = T.REL_TOL_QUARTER if self.spec.get("quarter") else T.REL_TOL_HALF
-        if self.kind == "gemm":
+        if self.kind == "norm":
+            # the whole tensor: statistics from the model, the output from the device's own statistics
+            to_bcf = lambda t: t.float().cpu().numpy().reshape(self.spec["batch"], -1, self.chans).transpose(0, 2, 1)  # noqa: E731
+            x = to_bcf(d["x"]).astype(np.float64)
+            mean, inv = oracle.norm_statistics(x, 1e-3)
+            bad_stats = int(oracle.check_is_close(d["inv"].float().cpu().numpy(), inv, 5e-3, 1e-5)[0] +
+                            oracle.check_is_close(d["mean"].float().cpu().numpy(), mean, 2e-3, 1e-4)[0])
+            want, _ = oracle.norm_normalise(x, d["gamma"].float().cpu().numpy(), d["beta"].float().cpu().numpy(),
+                                            d["mean"].float().cpu().numpy(), d["inv"].float().cpu().numpy())
+            got = to_bcf(d["out"])
+            rel = 4e-3   # two roundings to half (whitened, then scaled and shifted)
+            what = f"all {got.size} outputs; statistics outside tolerance: {bad_stats}"
+        elif self.kind == "gemm":
             m = self.spec["m"]
             rows = sorted({0, m // 3, (2 * m) // 3, m - 1})
             a = d["a"][rows]
@@ -420,7 +456,8 @@ class Workload:
         got = np.asarray(got, dtype=np.float64)
         want = np.asarray(want, dtype=np.float64).reshape(got.shape)
         rms = float(np.sqrt(np.mean(want * want))) if want.size else 0.0
-        abs_tol = max(T.ABS_TOL, 2.5e-4 * rms)
+        # (normalisation: outputs near zero carry the rounding of the whitened value, so the floor is rel * rms)
+        abs_tol = max(T.ABS_TOL, (rel if self.kind == "norm" else 2.5e-4) * rms)
         bad, _, _ = oracle.check_is_close(got, want, rel, abs_tol)
         strict_bad, _, _ = oracle.check_is_close(got, want, rel, T.ABS_TOL)
         return {"sample": what, "elements": int(got.size), "bad": int(bad), "rel_tol": rel, "abs_tol": abs_tol,
@@ -802,7 +839,8 @@ def main():
                 steps2 = EXTRA_STEPS.get(name, EXTRA_STEPS_DEFAULT)
                 (ms2, _, g2), clk2 = with_clocks(lambda: timed(w2, w2.step, steps2, 5, not args.no_graph))
                 per = ms2 / steps2
-                workloads[name] = {"ms_per_step": per, "steps": steps2, "tflops": w2.flops / (per * 1e-3) / 1e12,
+                workloads[name] = {"ms_per_step": per, "steps": steps2,
+                                   "tflops": w2.flops / (per * 1e-3) / 1e12 if w2.flops else None,
                                    "roofline": roofline_of(name, sp, w2.flops, w2.bytes, per, peaks, peak_src),
                                    "clocks": clk2, "launches_per_step": w2.launches_per_step,
                                    "graphed": g2, "parity_check": w2.parity_check()}

@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(32 * kNormRowLanes)
 normColumnPartialsKernel(const T *__restrict__ x, const T *__restrict__ y,
                          const T *__restrict__ centre, size_t rows, int chans,
                          float *__restrict__ partial_a, float *__restrict__ partial_b) {
+  pdl_launch_dependents();
+  pdl_wait();  // inputs may come from the previous kernel in the stream
   __shared__ float sa[kNormRowLanes][kNormChansPerBlock], sb[kNormRowLanes][kNormChansPerBlock];
   const int c0 = blockIdx.x * kNormChansPerBlock + 2 * threadIdx.x;
   const bool ok0 = c0 < chans, ok1 = c0 + 1 < chans;
@@ -100,20 +102,137 @@ normColumnPartialsKernel(const T *__restrict__ x, const T *__restrict__ y,
   }
 }
 
-// sums over the row blocks, in block order, times `scale`
+
+// The same sums over 16-byte vectors for channel counts whose vectors per row
+// divide the block size (powers of two from 8 halves / 4 floats up): thread t
+// of the grid walks vectors t, t + T, t + 2T, ... of the whole [rows x chans]
+// array with T a multiple of the vectors per row, so it always meets the same
+// kVec channels and keeps their sums in registers.  Threads of a block that
+// share a channel group are added in thread order in shared memory.
+template <typename T> struct NormVec;
+template <> struct NormVec<__half> {
+  static constexpr int kVec = 8;
+  static __device__ __forceinline__ void load(const __half *p, float (&f)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = __half22float2(h[j]);
+      f[2 * j] = t.x;
+      f[2 * j + 1] = t.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__half *p, const float (&f)[8]) {
+    uint4 v;
+    __half2 *h = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+    *reinterpret_cast<uint4 *>(p) = v;
+  }
+};
+template <> struct NormVec<float> {
+  static constexpr int kVec = 4;
+  static __device__ __forceinline__ void load(const float *p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4 *>(p);
+    f[0] = v.x;
+    f[1] = v.y;
+    f[2] = v.z;
+    f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float *p, const float (&f)[4]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+
+constexpr int kNormVecThreads = 256;
+
+template <typename T, int kMode>
+__global__ void __launch_bounds__(kNormVecThreads)
+normColumnPartialsVecKernel(const T *__restrict__ x, const T *__restrict__ y,
+                            const T *__restrict__ centre, size_t vectors, int chans,
+                            float *__restrict__ partial_a, float *__restrict__ partial_b) {
+  pdl_launch_dependents();
+  pdl_wait();  // inputs may come from the previous kernel in the stream
+  constexpr int kVec = NormVec<T>::kVec;
+  extern __shared__ float red[];   // [2][kNormVecThreads][kVec]
+  const int per_row = chans / kVec;              // divides kNormVecThreads
+  const int group = threadIdx.x % per_row;       // this thread's channels: [group * kVec, +kVec)
+  float m[kVec], a[kVec], b[kVec];
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) a[j] = b[j] = m[j] = 0.f;
+  if (kMode == kSumCentredXX) NormVec<T>::load(centre + group * kVec, m);
+  for (size_t v = blockIdx.x * size_t(kNormVecThreads) + threadIdx.x; v < vectors;
+       v += size_t(gridDim.x) * kNormVecThreads) {
+    float xv[kVec];
+    NormVec<T>::load(x + v * kVec, xv);
+    if (kMode == kSumXAndXX) {
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        a[j] += xv[j];
+        b[j] += xv[j] * xv[j];
+      }
+    } else if (kMode == kSumCentredXX) {
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        const float d = toFloat(fromFloat<T>(xv[j] - m[j]));
+        b[j] += d * d;
+      }
+    } else {
+      float yv[kVec];
+      NormVec<T>::load(y + v * kVec, yv);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) {
+        a[j] += xv[j] * yv[j];
+        b[j] += yv[j];
+      }
+    }
+  }
+  float *ra = red, *rb = red + kNormVecThreads * kVec;
+#pragma unroll
+  for (int j = 0; j < kVec; ++j) {
+    ra[threadIdx.x * kVec + j] = a[j];
+    rb[threadIdx.x * kVec + j] = b[j];
+  }
+  __syncthreads();
+  // thread c < chans adds channel c over the block's threads that share its group, in thread order
+  for (int c = threadIdx.x; c < chans; c += kNormVecThreads) {
+    const int g = c / kVec, j = c - g * kVec;
+    float ta = 0.f, tb = 0.f;
+    for (int t = g; t < kNormVecThreads; t += per_row) {
+      ta += ra[t * kVec + j];
+      tb += rb[t * kVec + j];
+    }
+    partial_a[size_t(blockIdx.x) * chans + c] = ta;
+    partial_b[size_t(blockIdx.x) * chans + c] = tb;
+  }
+}
+
+// Sums over the blocks' partials, times `scale`: a warp per channel, lane l
+// adds blocks l, l + 32, ... in order, then the lanes' sums are added by a
+// fixed tree of shuffles (the order of additions never depends on timing).
 template <typename TA, typename TB>
-__global__ void normColumnFinishKernel(const float *__restrict__ partial_a,
-                                       const float *__restrict__ partial_b, int blocks, int chans,
-                                       float scale, TA *__restrict__ out_a, TB *__restrict__ out_b) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= chans) return;
+__global__ void __launch_bounds__(256)
+normColumnFinishKernel(const float *__restrict__ partial_a, const float *__restrict__ partial_b,
+                       int blocks, int chans, float scale, TA *__restrict__ out_a,
+                       TB *__restrict__ out_b) {
+  pdl_launch_dependents();
+  pdl_wait();  // inputs may come from the previous kernel in the stream
+  const int c = blockIdx.x * 8 + threadIdx.y;
+  if (c >= chans) return;   // (whole warps leave together)
   float a = 0.f, b = 0.f;
-  for (int k = 0; k < blocks; ++k) {
+  for (int k = threadIdx.x; k < blocks; k += 32) {
     a += partial_a[size_t(k) * chans + c];
     b += partial_b[size_t(k) * chans + c];
   }
-  if (out_a) out_a[c] = fromFloat<TA>(a * scale);
-  if (out_b) out_b[c] = fromFloat<TB>(b * scale);
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, d);
+    b += __shfl_xor_sync(0xffffffffu, b, d);
+  }
+  if (threadIdx.x == 0) {
+    if (out_a) out_a[c] = fromFloat<TA>(a * scale);
+    if (out_b) out_b[c] = fromFloat<TB>(b * scale);
+  }
 }
 
 // iStdDev from mean and power: the reference's InverseStdDeviation vertex
@@ -122,6 +241,8 @@ template <typename T>
 __global__ void normInvStdDevKernel(const T *__restrict__ mean, const float *__restrict__ power,
                                     int chans, float eps, float scale_var, int stable,
                                     T *__restrict__ inv_std) {
+  pdl_launch_dependents();
+  pdl_wait();  // inputs may come from the previous kernel in the stream
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= chans) return;
   float var;
@@ -150,6 +271,8 @@ __global__ void normMapKernel(const T *__restrict__ x, const T *__restrict__ y,
                               const T *__restrict__ r, const float *__restrict__ pf,
                               const float *__restrict__ qf, size_t count, int chans,
                               T *__restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();  // inputs may come from the previous kernel in the stream
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < count;
        i += size_t(gridDim.x) * blockDim.x) {
     const int c = int(i % size_t(chans));
@@ -167,6 +290,77 @@ __global__ void normMapKernel(const T *__restrict__ x, const T *__restrict__ y,
   }
 }
 
+// The element-wise forms over 16-byte vectors (channel count a multiple of the
+// vector length, all pointers 16-byte aligned).
+template <typename T, int kMode>
+__global__ void normMapVecKernel(const T *__restrict__ x, const T *__restrict__ y,
+                                 const T *__restrict__ p, const T *__restrict__ q,
+                                 const T *__restrict__ r, const float *__restrict__ pf,
+                                 const float *__restrict__ qf, size_t vectors, int chans,
+                                 T *__restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();  // inputs may come from the previous kernel in the stream
+  constexpr int kVec = NormVec<T>::kVec;
+  const int per_row = chans / kVec;
+  for (size_t v = blockIdx.x * size_t(blockDim.x) + threadIdx.x; v < vectors;
+       v += size_t(gridDim.x) * blockDim.x) {
+    const int c0 = int(v % size_t(per_row)) * kVec;
+    float xv[kVec], yv[kVec], pv[kVec], qv[kVec], rv[kVec], o[kVec];
+    NormVec<T>::load(x + v * kVec, xv);
+    if (kMode == kStatsGrad) {
+      NormVec<T>::load(y + v * kVec, yv);
+      NormVec<T>::load(r + c0, rv);
+      if (pf) {
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+          pv[j] = pf[c0 + j];
+          qv[j] = qf[c0 + j];
+        }
+      } else {
+        NormVec<T>::load(p + c0, pv);
+        NormVec<T>::load(q + c0, qv);
+      }
+    } else {
+      NormVec<T>::load(p + c0, pv);
+      if (kMode != kScale) NormVec<T>::load(q + c0, qv);
+    }
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+      if (kMode == kWhiten)
+        o[j] = (xv[j] - pv[j]) * qv[j];
+      else if (kMode == kScaleShift)
+        o[j] = xv[j] * pv[j] + qv[j];
+      else if (kMode == kScale)
+        o[j] = xv[j] * pv[j];
+      else
+        o[j] = (yv[j] + xv[j] * pv[j] + qv[j]) * rv[j];
+    }
+    NormVec<T>::store(out + v * kVec, o);
+  }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Launch with programmatic stream serialization: the kernel may become
+// resident while its predecessor drains; it waits before touching memory.
+template <typename... KArgs, typename... Args>
+int launchPdl(plb_context *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = (ctx->plan_flags & PLB_PLAN_NO_PDL) ? 0 : 1;
+  PLB_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return PLB_OK;
+}
+
 int rowBlocks(const plb_context *ctx, size_t rows, int chans) {
   const int chan_blocks = (chans + kNormChansPerBlock - 1) / kNormChansPerBlock;
   const size_t want = (rows + 4 * kNormRowLanes - 1) / (4 * kNormRowLanes);   // >= 4 rows per thread
@@ -178,30 +372,52 @@ int rowBlocks(const plb_context *ctx, size_t rows, int chans) {
 template <typename T, int kMode, typename TA, typename TB>
 int columnSums(plb_context *ctx, const T *x, const T *y, const T *centre, size_t rows, int chans,
                float scale, TA *out_a, TB *out_b) {
-  const int blocks = rowBlocks(ctx, rows, chans);
+  constexpr int kVec = NormVec<T>::kVec;
+  const bool vec = chans % kVec == 0 && kNormVecThreads % (chans / kVec) == 0 && aligned16(x) &&
+                   (y == nullptr || aligned16(y)) && (centre == nullptr || aligned16(centre));
+  int blocks;
+  float *pa, *pb;
   void *ws = nullptr;
-  if (int rc = scratch(ctx, kSlotBiasUpdate, size_t(2) * blocks * chans * sizeof(float), &ws)) return rc;
-  float *pa = static_cast<float *>(ws), *pb = pa + size_t(blocks) * chans;
-  const dim3 grid(unsigned((chans + kNormChansPerBlock - 1) / kNormChansPerBlock), unsigned(blocks));
-  normColumnPartialsKernel<T, kMode><<<grid, dim3(32, kNormRowLanes), 0, ctx->stream>>>(
-      x, y, centre, rows, chans, pa, pb);
-  PLB_CUDA(cudaGetLastError());
-  normColumnFinishKernel<TA, TB><<<(chans + 127) / 128, 128, 0, ctx->stream>>>(pa, pb, blocks, chans,
-                                                                               scale, out_a, out_b);
-  PLB_CUDA(cudaGetLastError());
-  ctx->launches += 2;
-  return PLB_OK;
+  if (vec) {
+    const size_t vectors = rows * size_t(chans / kVec);
+    blocks = int(std::max<size_t>(1, std::min<size_t>((vectors + 4 * kNormVecThreads - 1) / (4 * kNormVecThreads),
+                                                      size_t(ctx->sm_count) * 2)));
+    if (int rc = scratch(ctx, kSlotBiasUpdate, size_t(2) * blocks * chans * sizeof(float), &ws)) return rc;
+    pa = static_cast<float *>(ws);
+    pb = pa + size_t(blocks) * chans;
+    if (int rc = launchPdl(ctx, normColumnPartialsVecKernel<T, kMode>, dim3(unsigned(blocks)),
+                           dim3(kNormVecThreads), 2 * kNormVecThreads * kVec * sizeof(float), x, y, centre,
+                           vectors, chans, pa, pb))
+      return rc;
+  } else {
+    blocks = rowBlocks(ctx, rows, chans);
+    if (int rc = scratch(ctx, kSlotBiasUpdate, size_t(2) * blocks * chans * sizeof(float), &ws)) return rc;
+    pa = static_cast<float *>(ws);
+    pb = pa + size_t(blocks) * chans;
+    const dim3 grid(unsigned((chans + kNormChansPerBlock - 1) / kNormChansPerBlock), unsigned(blocks));
+    if (int rc = launchPdl(ctx, normColumnPartialsKernel<T, kMode>, grid, dim3(32, kNormRowLanes), 0, x, y,
+                           centre, rows, chans, pa, pb))
+      return rc;
+  }
+  return launchPdl(ctx, normColumnFinishKernel<TA, TB>, dim3(unsigned((chans + 7) / 8)), dim3(32, 8), 0,
+                   (const float *)pa, (const float *)pb, blocks, chans, scale, out_a, out_b);
 }
 
 template <typename T, int kMode>
 int mapLaunch(plb_context *ctx, const T *x, const T *y, const T *p, const T *q, const T *r,
               const float *pf, const float *qf, size_t count, int chans, T *out) {
   if (count == 0) return PLB_OK;
+  constexpr int kVec = NormVec<T>::kVec;
+  if (chans % kVec == 0 && aligned16(x) && aligned16(out) && (y == nullptr || aligned16(y)) &&
+      (p == nullptr || aligned16(p)) && (q == nullptr || aligned16(q)) && (r == nullptr || aligned16(r))) {
+    const size_t vectors = count / kVec;
+    const int grid = int(std::min<size_t>((vectors + 255) / 256, size_t(ctx->sm_count) * 16));
+    return launchPdl(ctx, normMapVecKernel<T, kMode>, dim3(unsigned(grid)), dim3(256), 0, x, y, p, q, r, pf, qf,
+                     vectors, chans, out);
+  }
   const int grid = int(std::min<size_t>((count + 255) / 256, size_t(ctx->sm_count) * 16));
-  normMapKernel<T, kMode><<<grid, 256, 0, ctx->stream>>>(x, y, p, q, r, pf, qf, count, chans, out);
-  PLB_CUDA(cudaGetLastError());
-  ctx->launches++;
-  return PLB_OK;
+  return launchPdl(ctx, normMapKernel<T, kMode>, dim3(unsigned(grid)), dim3(256), 0, x, y, p, q, r, pf, qf, count,
+                   chans, out);
 }
 
 int checkNorm(int32_t dtype, uint64_t pixels, uint32_t chans) {
@@ -256,18 +472,12 @@ int plb_norm_inv_std_dev(plb_context *ctx, int32_t dtype, const void *d_mean, co
   if (int rc = checkNorm(dtype, 0, chans)) return rc;
   if (!d_power || !d_inv_std || (!stable && !d_mean))
     return fail(PLB_ERR_INVALID_PARAMS, "normalisation: null statistics pointer");
-  const int grid = int((chans + 127) / 128);
+  const dim3 grid(unsigned((chans + 127) / 128));
   if (dtype == PLB_HALF)
-    normInvStdDevKernel<__half><<<grid, 128, 0, ctx->stream>>>(
-        static_cast<const __half *>(d_mean), d_power, int(chans), eps, scale_var, stable,
-        static_cast<__half *>(d_inv_std));
-  else
-    normInvStdDevKernel<float><<<grid, 128, 0, ctx->stream>>>(static_cast<const float *>(d_mean),
-                                                             d_power, int(chans), eps, scale_var,
-                                                             stable, static_cast<float *>(d_inv_std));
-  PLB_CUDA(cudaGetLastError());
-  ctx->launches++;
-  return PLB_OK;
+    return launchPdl(ctx, normInvStdDevKernel<__half>, grid, dim3(128), 0, static_cast<const __half *>(d_mean),
+                     d_power, int(chans), eps, scale_var, stable, static_cast<__half *>(d_inv_std));
+  return launchPdl(ctx, normInvStdDevKernel<float>, grid, dim3(128), 0, static_cast<const float *>(d_mean),
+                   d_power, int(chans), eps, scale_var, stable, static_cast<float *>(d_inv_std));
 }
 
 int plb_norm_whiten(plb_context *ctx, int32_t dtype, const void *d_acts, const void *d_mean,
