@@ -223,6 +223,7 @@ typedef struct plb_conv_options {
 #define PLB_PLAN_NO_TMA_STORE 32          /* plain vector stores in the epilogue              */
 #define PLB_PLAN_NO_PDL 64                /* launch without programmatic stream serialization */
 #define PLB_PLAN_NO_A_COLLECTOR 128       /* weight update: fetch the outGrad tile per MMA    */
+#define PLB_PLAN_NO_DUAL_ISSUE 256        /* one MMA-issuing thread also on short tiles       */
 
 /* out = conv(in, weights) (+ bias), poplin::convolution
  * (include/poplin/Convolution.hpp:345-384, lib/poplin/Convolution.cpp:3128-3215).

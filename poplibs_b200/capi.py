@@ -15,7 +15,7 @@ PASS_NONE, PASS_NONE_MATMUL, PASS_INFERENCE_FWD, PASS_TRAINING_FWD, PASS_TRAININ
     PASS_FC_TRAINING_WU = range(10)
 MAX_DIMS = 3
 PLAN_FORCE_RESIDENT_WEIGHTS, PLAN_NO_RESIDENT_WEIGHTS, PLAN_NO_HALO, PLAN_NO_CTA_PAIR, PLAN_FORCE_CTA_PAIR = 1, 2, 4, 8, 16
-PLAN_NO_TMA_STORE, PLAN_NO_PDL, PLAN_NO_A_COLLECTOR = 32, 64, 128
+PLAN_NO_TMA_STORE, PLAN_NO_PDL, PLAN_NO_A_COLLECTOR, PLAN_NO_DUAL_ISSUE = 32, 64, 128, 256
 _U3 = C.c_uint32 * MAX_DIMS
 
 

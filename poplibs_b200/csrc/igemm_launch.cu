@@ -497,6 +497,16 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   a.b_tiles_per_stage = (halo && !plan.resident_weights) ? p.taps_h : 1;
   a.halo_step_bytes = p.dil_h * plan.box_w * plan.box_n * kStageKBytes;
   a.num_stages = plan.stages;
+  // Short tiles (few tensor-core instructions each) are bound by what one
+  // thread can issue and wait for per tile: let two issuers take alternate tiles.
+  {
+    const int steps_per_tile = halo ? a.taps_w * a.k_chunks : a.taps_h * a.taps_w * a.k_chunks;
+    const int mmas_per_tile = a.taps_h * a.taps_w * a.k_chunks * 4;
+    a.dual_issue = ((p.plan_flags & PLB_PLAN_NO_DUAL_ISSUE) == 0 && steps_per_tile <= 4 && mmas_per_tile <= 48 &&
+                    plan.tiles >= 2 * plan.grid)
+                       ? 1
+                       : 0;
+  }
   const int resident_bytes =
       plan.resident_weights ? a.taps_h * a.taps_w * a.k_chunks *
                                   (plan.tile_n / (plan.cta_pair ? 2 : 1)) * kStageKBytes

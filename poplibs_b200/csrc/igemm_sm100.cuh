@@ -22,6 +22,12 @@
 //                 tensor copy costs a thread a few hundred cycles, so a single
 //                 producer cannot keep the tensor core fed on narrow tiles.
 //   warp 3        issues tcgen05.mma with fp32 accumulators in tensor memory.
+//   warp 20       a second issuer for short tiles: issuing an MMA costs its
+//                 thread about 28 cycles and every tile a few hundred more in
+//                 barrier waits and commits, which on a tile of 16 instructions
+//                 exceeds the 46 cycles the tensor core needs per instruction.
+//                 The two issuers take alternate tiles (and so always the
+//                 same accumulator each).
 //   warps 4..19   epilogue, two groups of eight warps: drain a finished
 //                 accumulator (tcgen05.ld), scale / add / cast, stage 32 rows
 //                 x 128 bytes per pair of warps in shared memory and hand them
@@ -45,9 +51,10 @@ namespace plb {
 
 constexpr int kTileM = 128;        // pixels (rows) per tile = TMEM lanes
 constexpr int kStageKBytes = 128;  // bytes of K per pipeline stage row (one swizzle span)
-constexpr int kIgemmThreads = 640;
+constexpr int kIgemmThreads = 672;
 constexpr int kIgemmProducers = PLB_IGEMM_PRODUCERS;
 constexpr int kIgemmMmaWarp = 3;
+constexpr int kIgemmMmaWarp2 = 20;  // second MMA issuer (short tiles), after the 16 epilogue warps
 constexpr int kEpiStagingBytes = 8 * 4096;  // 8 pairs of epilogue warps x (32 rows x 128 B)
 static_assert(kIgemmProducers >= 1 && kIgemmProducers <= 3, "producer warps are warps 0..2");
 
@@ -85,6 +92,7 @@ struct IgemmArgs {
   int split_k;
   FastDiv fd_split;
   long long split_stride;
+  int dual_issue;  // two MMA-issuing threads take alternate tiles
   uint32_t idesc_formats;  // operand format bits of the instruction descriptor (8-bit operands: 1 = E5M2)
   // ---- epilogue ---------------------------------------------------------------
   void *out;
@@ -200,6 +208,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
   const uint32_t drain_bar = bar_base + 8u * (2 * kMaxStages + 4);
+  const uint32_t drain_bar2 = bar_base + 8u * (2 * kMaxStages + 8);
   const uint32_t resb_bar = bar_base + 8u * (2 * kMaxStages + 5);
   const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxStages + 6);
   uint8_t *bar_gen = smem_raw + (bar_base - smem_u32(smem_raw));
@@ -214,7 +223,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
   // words (one each), a thread of warp 1 asks for the tensor maps, warp 3
   // allocates tensor memory.
   if (warp == 0) {
-    // barrier slots: full[8], empty[8], tmem_full[2], tmem_empty[2], drain, resident-B
+    // barrier slots: full[8], empty[8], tmem_full[2], tmem_empty[2], drain, resident-B;
+    // slot 24: the second issuer's drain
+    if (lane == 22) mbar_init(bar_base + 8u * (2 * kMaxStages + 8), 1u);
     if (lane < 2 * kMaxStages + 6) {
       // tmem_empty counts a group's epilogue threads (of both CTAs of a pair)
       const bool acc_free = lane == 2 * kMaxStages + 2 || lane == 2 * kMaxStages + 3;
@@ -471,10 +482,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       }
       if (me == 0) PLB_TRACE_STAMP(2, 4014);
     }
-  } else if (warp == kIgemmMmaWarp) {
-    // ===================== MMA issuer =====================
+  } else if (warp == kIgemmMmaWarp || warp == kIgemmMmaWarp2) {
+    // ===================== MMA issuer(s) =====================
     // (with a CTA pair only the CTA of rank 0 issues)
-    if (leader && elect_one()) {
+    const int mi = warp == kIgemmMmaWarp ? 0 : 1;
+    const int n_issuers = args.dual_issue ? 2 : 1;
+    if (mi < n_issuers && leader && elect_one()) {
       const uint32_t idesc =
           make_idesc(k2Cta ? 2 * kTileM : kTileM, BN, 0, 0, false, kBMn) | args.idesc_formats;
       // completion of the MMAs issued so far -> barrier (in both CTAs of a pair)
@@ -512,8 +525,17 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
       for (int unit = first_unit; unit < total_units && ok; unit += unit_stride, ++local_tile) {
         int tile, split, it_begin, it_end;
         unit_coords(unit, tile, split, it_begin, it_end);
+        if (n_issuers == 2 && (local_tile & 1) != mi) {
+          // the other issuer's tile: step over its pipeline stages
+          stage += it_end - it_begin;
+          while (stage >= kStages) {
+            stage -= kStages;
+            phase ^= 1u;
+          }
+          continue;
+        }
         const int acc = local_tile & 1;
-        PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
+        if (mi == 0) { PLB_TRACE_STAMP(1, trace_slot); ++trace_slot; }
         // wait for the epilogue to have drained this accumulator
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase[acc] ^ 1u, abort_flag)) {
           atomicCAS(args.status, kStatusOk, kStatusMmaTimeout);
@@ -522,7 +544,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         }
         acc_phase[acc] ^= 1u;
         tc_fence_after_sync();
-        PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
+        if (mi == 0) { PLB_TRACE_STAMP(1, trace_slot); ++trace_slot; }
         const uint32_t d_tmem = tmem_base + acc * BN;
         int s_tap = 0, kc = 0;  // halo mode: pipeline step = (s_tap, kc), kc fastest
         if (kHalo && it_begin != 0) {
@@ -536,7 +558,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             break;
           }
           tc_fence_after_sync();
-          PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
+          if (mi == 0) { PLB_TRACE_STAMP(1, trace_slot); ++trace_slot; }
           // Descriptors are advanced by adding to their start-address field
           // (16-byte units, cannot overflow for shared-memory addresses): the
           // issuing thread's own instruction count bounds the MMA rate on
@@ -572,7 +594,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
             }
           }
           commit(empty_bar(stage));  // frees the stage when these MMAs retire
-          PLB_TRACE_STAMP(1, trace_slot); ++trace_slot;
+          if (mi == 0) { PLB_TRACE_STAMP(1, trace_slot); ++trace_slot; }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -585,20 +607,21 @@ igemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ C
         if (ok) commit(tmem_full_bar(acc));
       }
       // make sure nothing is still executing before TMEM is released
+      const uint32_t my_drain = mi == 0 ? drain_bar : drain_bar2;
       if constexpr (k2Cta)
-        umma_commit_pair(drain_bar, uint16_t(1));
+        umma_commit_pair(my_drain, uint16_t(1));
       else
-        umma_commit(drain_bar);
+        umma_commit(my_drain);
       const long long start = clock64();
-      while (!mbar_try_wait(drain_bar, 0)) {
+      while (!mbar_try_wait(my_drain, 0)) {
         if (clock64() - start > kWaitCycleLimit) {
           atomicCAS(args.status, kStatusOk, kStatusDrainTimeout);
           break;
         }
       }
-      PLB_TRACE_STAMP(2, 4015);
+      if (mi == 0) PLB_TRACE_STAMP(2, 4015);
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 20) {
     // ===================== epilogue (warps 4..19) =====================
     // Accumulator g is drained by the eight warps of group g.  A warp can read
     // the 32 TMEM lanes (tile rows) [32*(warp%4), +32); the two warps that share
