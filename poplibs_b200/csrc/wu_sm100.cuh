@@ -353,7 +353,9 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
           buf ^= 1;
         }
       }
-      if (lane == 0) tma_store_wait_all<0>();
+      // the stores must have read their staging buffers before the CTA gives up
+      // its shared memory; the writes themselves complete with the grid
+      if (lane == 0) tma_store_wait_read<0>();
       __syncwarp();
       if (threadIdx.x == 128) PLB_WU_STAMP(2, 1);
     } else {
