@@ -502,8 +502,10 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
   {
     const int steps_per_tile = halo ? a.taps_w * a.k_chunks : a.taps_h * a.taps_w * a.k_chunks;
     const int mmas_per_tile = a.taps_h * a.taps_w * a.k_chunks * 4;
+    // (only with CTA pairs and 64-column tiles, the case it was built and
+    // verified for: weights resident or streamed, halo strips)
     a.dual_issue = ((p.plan_flags & PLB_PLAN_NO_DUAL_ISSUE) == 0 && steps_per_tile <= 4 && mmas_per_tile <= 48 &&
-                    plan.tiles >= 2 * plan.grid)
+                    plan.tiles >= 2 * plan.grid && plan.cta_pair && plan.tile_n == 64)
                        ? 1
                        : 0;
   }
