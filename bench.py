@@ -94,15 +94,16 @@ DEFAULT_WORKLOAD = "conv3x3_fwd_n32_56x56_c64"
 # Outputs smaller than the 126 MB L2 are still dirty in L2 when the kernel
 # ends, so their write-back does not show in the kernel's own DRAM write count.
 NCU_DRAM_TRAFFIC_BYTES = {
-    "conv3x3_fwd_n32_56x56_c64": 12987392,
-    "conv3x3_fwd_n256_28x28_c128": 51742720 + 10673664,
-    "conv3x3_bwd_n256_28x28_c128": 51746048 + 10921728,
-    "conv3x3_wu_n256_28x28_c128": 105506304 + 5284096,
-    "conv1x1_s2_fwd_n256_56x56_c256_c512": 103098624 + 147304192,
+    "conv3x3_fwd_n32_56x56_c64": 12995328,
+    "conv3x3_fwd_n256_28x28_c128": 51744768 + 13427520,
+    "conv3x3_bwd_n256_28x28_c128": 51750000 + 13090000,
+    "conv3x3_wu_n256_28x28_c128": 105509248 + 4087936,
+    "conv1x1_s2_fwd_n256_56x56_c256_c512": 103111168 + 153707456,
     "conv7x7_s2_fwd_n256_224x224_c3_c64": 114623744 + 352808192,   # the implicit-GEMM kernel of the three
-    "matmul_fp16_512x1024x1024": 3208192,
-    "matmul_fp16_8192": 1096498000 + 126829568,
-    "matmul_fp8_8192": 344297728 + 116545280,
+    "batchnorm_fwd_n32_56x56_c64": 3 * 12850000,                   # moments + the two element-wise kernels (outputs stay in L2)
+    "matmul_fp16_512x1024x1024": 3220000,
+    "matmul_fp16_8192": 1074835000 + 128641408,
+    "matmul_fp8_8192": 344460000 + 119442500,
 }
 
 
