@@ -360,22 +360,33 @@ class Workload:
         self.ctx.conv_wu(self.p, d["x"], d["dy"], d["out"], d["out32"])
 
     def check_allreduce(self):
-        """One untimed step of the multi-GPU weight update compared with the
-        process group's own all-reduce of the per-rank gradients."""
+        """One untimed step of the multi-GPU weight update compared with (a) the
+        per-rank gradients gathered and added in rank order with fp32 adds, which
+        the library's sum must equal bit for bit on every rank, and (b) the process
+        group's own all-reduce, whose order of additions is NCCL's (ring / tree):
+        agreement to the last place or two of fp32."""
         import torch
         import torch.distributed as dist
         d = self.dev[0]
         local = torch.empty_like(d["out32"])
         self.ctx.conv_wu(self.p, d["x"], d["dy"], None, local)
         self.ctx.synchronize()
-        dist.all_reduce(local)
+        gathered = [torch.empty_like(local) for _ in range(self.world)]
+        dist.all_gather(gathered, local)
+        ordered = gathered[0].clone()
+        for g in gathered[1:]:
+            ordered += g
+        nccl = local.clone()
+        dist.all_reduce(nccl)
         self.sharded.wu(d["x"], d["dy"], d["out"], d["out32"])
         self.ctx.synchronize()
         torch.cuda.synchronize()
-        diff = float((local - d["out32"]).abs().max().item())
-        same16 = bool(torch.equal(local.half(), d["out"]))
-        return {"max_abs_diff_vs_nccl": diff, "max_abs": float(local.abs().max().item()),
-                "half_cast_equal": same16}
+        ok = torch.tensor([int(torch.equal(ordered, d["out32"]) and torch.equal(ordered.half(), d["out"]))],
+                          device=local.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        return {"equals_rank_order_sum_on_every_rank": bool(ok.item()),
+                "max_abs_diff_vs_nccl": float((nccl - d["out32"]).abs().max().item()),
+                "max_abs": float(nccl.abs().max().item())}
 
     def step_e2e(self, i):
         """One end-to-end step: pinned host inputs -> device -> kernel -> pinned

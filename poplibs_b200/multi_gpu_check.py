@@ -100,6 +100,28 @@ def main() -> int:
     # the same with the all-reduce on a stream of its own, several steps in flight
     report("sum over ranks fused into the split-K reduction: same bits, fp32 and half",
            torch.equal(fu32, dw32) and torch.equal(fu16, dw16))
+    # different, non-integer data on every rank: the order of additions now matters,
+    # and all three forms must give the per-rank gradients added in rank order
+    gr = torch.Generator().manual_seed(100 + rank)
+    xr = (torch.rand(e - b, 12, 12, 64, generator=gr) * 2 - 1).half().to(device)
+    dyr = (torch.rand(e - b, 12, 12, 72, generator=gr) * 2 - 1).half().to(device)
+    with torch.cuda.stream(stream):
+        mine = torch.empty_like(dw32)
+        ctx.conv_wu(sh.params, xr, dyr, None, mine)
+        outs3 = []
+        for s3 in (sh, sh_rs, sh_fu):
+            o16, o32 = torch.empty_like(dw16), torch.empty_like(dw32)
+            s3.wu(xr, dyr, o16, o32)
+            outs3.append((o16, o32))
+    ctx.synchronize()
+    torch.cuda.synchronize()
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    ordered = parts[0].clone()
+    for part in parts[1:]:
+        ordered += part
+    report("uniform data: one-shot, reduce-scatter and fused sums equal the rank-order sum, fp32 and half",
+           all(torch.equal(o32, ordered) and torch.equal(o16, ordered.half()) for o16, o32 in outs3))
     for mode in ("oneshot", "rs"):
         sho = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, overlap_allreduce=True,
                                    allreduce_mode=mode)
