@@ -57,8 +57,11 @@ typedef enum plb_status {
   PLB_ERR_OUT_OF_MEMORY = 6   /* poplar::graph_memory_allocation_error        */
 } plb_status;
 
-/* poplar::Type values used on this path (HALF, FLOAT, QUARTER). */
-typedef enum plb_dtype { PLB_HALF = 0, PLB_FLOAT = 1, PLB_QUARTER = 2 } plb_dtype;
+/* poplar::Type values used on this path (HALF, FLOAT, QUARTER).  PLB_BFLOAT16
+ * is not a poplar type: it is the operand type a float contraction runs in
+ * (three bfloat16 terms per product, fp32 accumulation) and is accepted as an
+ * input type in its own right; results are PLB_HALF or PLB_FLOAT as for half. */
+typedef enum plb_dtype { PLB_HALF = 0, PLB_FLOAT = 1, PLB_QUARTER = 2, PLB_BFLOAT16 = 3 } plb_dtype;
 
 /* poplin::Pass (lib/poplin/ConvOptions.hpp:13-24). */
 typedef enum plb_pass {
@@ -122,7 +125,10 @@ typedef enum plb_quarter_format { PLB_F143 = 0, PLB_F152 = 1 } plb_quarter_forma
 
 typedef struct plb_matmul_desc {
   uint32_t groups, m, k, n;
-  int32_t input_type;   /* plb_dtype: PLB_HALF or PLB_QUARTER              */
+  int32_t input_type;   /* plb_dtype: PLB_HALF, PLB_QUARTER or PLB_FLOAT (each
+                           product of float operands is formed from three
+                           bfloat16 terms: relative error about 2^-16,
+                           accumulation in fp32)                            */
   int32_t output_type;  /* plb_dtype: PLB_HALF or PLB_FLOAT                */
   int32_t partials_type;/* plb_dtype: option "partialsType"; accumulation is
                            always fp32 on this hardware, PLB_HALF is accepted

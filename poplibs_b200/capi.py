@@ -8,7 +8,7 @@ from typing import Optional, Sequence
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libpoplibs_b200.so")
 
-HALF, FLOAT, QUARTER = 0, 1, 2
+HALF, FLOAT, QUARTER, BFLOAT16 = 0, 1, 2, 3
 F143, F152 = 0, 1   # plb_quarter_format
 PASS_NONE, PASS_NONE_MATMUL, PASS_INFERENCE_FWD, PASS_TRAINING_FWD, PASS_TRAINING_BWD, \
     PASS_TRAINING_WU, PASS_FC_INFERENCE_FWD, PASS_FC_TRAINING_FWD, PASS_FC_TRAINING_BWD, \

@@ -26,7 +26,7 @@ static bool channelsFitTma(const plb_conv_params &p, uint32_t chans) {
 namespace {
 
 int checkMatmulDesc(const plb_matmul_desc &d) {
-  if (d.input_type != PLB_HALF && d.input_type != PLB_QUARTER)
+  if (!is16BitFloat(d.input_type) && d.input_type != PLB_QUARTER && d.input_type != PLB_FLOAT)
     return fail(PLB_ERR_INVALID_PARAMS, "matMul input type must be half or quarter");
   if (d.output_type != PLB_HALF && d.output_type != PLB_FLOAT)
     return fail(PLB_ERR_INVALID_PARAMS, "matMul output type must be half or float");
@@ -61,6 +61,7 @@ IgemmProblem gemmProblem(const plb_matmul_desc &d, const void *a, long long lda,
   IgemmProblem p;
   const size_t es = dtypeBytes(d.input_type);
   p.fp8 = d.input_type == PLB_QUARTER;
+  p.bf16 = d.input_type == PLB_BFLOAT16;
   p.fmt_a = d.format_a;
   p.fmt_b = d.format_b;
   p.b_mn = !b_is_nk;
@@ -128,8 +129,8 @@ int igemmConvShape(const plb_conv_params &p, ConvShape *s) {
   if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
   if (p.num_field_dims > 2)
     return fail(PLB_ERR_UNSUPPORTED, "3-D convolutions are not implemented on this path yet");
-  if (p.input_type != PLB_HALF && p.input_type != PLB_QUARTER)
-    return fail(PLB_ERR_UNSUPPORTED, "convolution input type must be half or quarter");
+  if (!is16BitFloat(p.input_type) && p.input_type != PLB_QUARTER)
+    return fail(PLB_ERR_UNSUPPORTED, "convolution input type must be half, float or quarter");
   if (p.output_type != PLB_HALF && p.output_type != PLB_FLOAT)
     return fail(PLB_ERR_INVALID_PARAMS, "convolution output type must be half or float");
   if (p.input_type == PLB_QUARTER && p.output_type != PLB_HALF)
@@ -208,6 +209,7 @@ int convFwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
   IgemmProblem r;
   r.fp8 = p.input_type == PLB_QUARTER;
+  r.bf16 = p.input_type == PLB_BFLOAT16;
   r.fmt_a = opt ? opt->format_in : 0;
   r.fmt_b = opt ? opt->format_weights : 0;
   // the truncated input is a view: same strides, shifted base, smaller extents
@@ -286,6 +288,7 @@ int convBwdProblem(const plb_conv_params &p, const plb_conv_options *opt, const 
   const uint64_t ci = p.in_chans_per_group, co = p.out_chans_per_group;
   IgemmProblem r;
   r.fp8 = p.input_type == PLB_QUARTER;
+  r.bf16 = p.input_type == PLB_BFLOAT16;
   r.fmt_a = opt ? opt->format_in : 0;
   r.fmt_b = opt ? opt->format_weights : 0;
   // computed part of the output gradients / used part of the input gradients
@@ -522,6 +525,7 @@ int convBwdStrided(plb_context *ctx, const plb_conv_params &p, const plb_conv_op
       for (unsigned g = 0; g < p.groups; ++g) {
         IgemmProblem r;
         r.fp8 = fp8;
+        r.bf16 = p.input_type == PLB_BFLOAT16;
         r.fmt_a = opt ? opt->format_in : 0;
         r.fmt_b = opt ? opt->format_weights : 0;
         r.act = static_cast<const uint8_t *>(dy) +
@@ -592,6 +596,15 @@ extern "C" {
 int plb_matmul_plan(const plb_matmul_desc *desc, plb_plan *plan) {
   if (!desc || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
   if (int rc = checkMatmulDesc(*desc)) return rc;
+  if (desc->input_type == PLB_FLOAT) {
+    // what runs: bfloat16 operands, three terms per product (float_route.cu)
+    const plb_matmul_desc q = floatRouteMatmulDesc(*desc);
+    if (int rc = plb_matmul_plan(&q, plan)) return rc;
+    plan->flops = 2ull * desc->groups * desc->m * desc->k * desc->n;
+    plan->bytes = gemmBytes(*desc);
+    plan->workspace_bytes += size_t(desc->groups) * desc->k * (size_t(desc->m) + desc->n) * 6 + 768;
+    return PLB_OK;
+  }
   *plan = plb_plan{};
   plan->flops = 2ull * desc->groups * desc->m * desc->k * desc->n;
   plan->bytes = gemmBytes(*desc);
@@ -632,6 +645,7 @@ int plb_matmul(plb_context *ctx, const plb_matmul_desc *desc, const void *d_a, c
     }
     return PLB_OK;
   }
+  if (d.input_type == PLB_FLOAT) return floatMatmul(ctx, d, d_a, d_b, d_c, d_d);
   // operand layouts the kernel takes directly: A as [m][k]; B as [n][k], or
   // (half only) [k][n].  Anything else goes through a transpose into scratch.
   const uint8_t *a = static_cast<const uint8_t *>(d_a);
@@ -776,6 +790,18 @@ uint64_t plb_conv_macs(const plb_conv_params *p) { return p ? numberOfMacs(*p) :
 int plb_conv_plan(const plb_conv_params *p_in, const plb_conv_options *opt, int32_t pass,
                   plb_plan *plan) {
   if (!p_in || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  if (p_in->input_type == PLB_FLOAT) {
+    // what runs: bfloat16 operands, three terms per product (float_route.cu)
+    const std::string err = validate(*p_in);
+    if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+    const plb_conv_params q = floatRouteConvParams(*p_in, pass);
+    if (int rc = plb_conv_plan(&q, opt, pass, plan)) return rc;
+    plan->flops = 2 * numberOfMacs(*p_in);
+    size_t n_in, n_w, n_out;
+    convElementCounts(*p_in, &n_in, &n_w, &n_out);
+    plan->workspace_bytes += ((pass == PLB_PASS_TRAINING_BWD ? n_out : n_in) + n_w) * 6 + 768;
+    return PLB_OK;
+  }
   if (p_in->num_field_dims == 3) return conv3dPlan(*p_in, opt, pass, plan);
   // a flipped input runs as the ordinary convolution of the reversed tensor
   plb_conv_params unflipped, undilated;
@@ -829,6 +855,11 @@ int plb_convolution(plb_context *ctx, const plb_conv_params *p, const plb_conv_o
     if (n_in == 0 || n_w == 0) n_in = n_w = 0;  // nothing is read: the output is zero (or the bias)
     if (int rc = checkConvRequest(*p, false, d_in, n_out ? n_in : 0, d_weights, n_out ? n_w : 0, d_out, n_out))
       return rc;
+  }
+  if (p->input_type == PLB_FLOAT) {
+    const std::string err = validate(*p);
+    if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+    return floatConvFwd(ctx, *p, opt, d_in, d_weights, d_bias, d_out, transpose_and_flip_weights);
   }
   if (p->num_field_dims == 3)
     return conv3dFwd(ctx, *p, opt, d_in, d_weights, d_bias, d_out, transpose_and_flip_weights);
@@ -982,6 +1013,11 @@ int plb_conv_bwd(plb_context *ctx, const plb_conv_params *p, const plb_conv_opti
     if (int rc = checkConvRequest(*p, false, d_out_grads, n_in ? n_out : 0, d_weights, n_in ? n_w : 0,
                                   d_in_grads, n_in))
       return rc;
+  }
+  if (p->input_type == PLB_FLOAT) {
+    const std::string err = validate(*p);
+    if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+    return floatConvBwd(ctx, *p, opt, d_out_grads, d_weights, d_in_grads);
   }
   if (p->num_field_dims == 3) return conv3dBwd(ctx, *p, opt, d_out_grads, d_weights, d_in_grads);
   {

@@ -529,7 +529,8 @@ int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan) {
     a.addend = nullptr;
     a.bias = nullptr;
   }
-  a.idesc_formats = p.fp8 ? make_idesc(0, 0, uint32_t(p.fmt_a & 1), uint32_t(p.fmt_b & 1), false, false) & ~(1u << 4)
+  a.idesc_formats = p.bf16 ? make_idesc(0, 0, 1, 1, false, false) & ~(1u << 4)
+                    : p.fp8 ? make_idesc(0, 0, uint32_t(p.fmt_a & 1), uint32_t(p.fmt_b & 1), false, false) & ~(1u << 4)
                           : 0u;
   a.alpha = split ? 1.f : p.alpha;
   a.beta = split ? 0.f : p.beta;

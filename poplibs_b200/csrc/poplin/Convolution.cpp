@@ -219,9 +219,6 @@ void validateTypes(const ConvParams &p) {
       throw poplibs_error("Unsupported convolution type " + t.toString());
   if (p.inputType == poplar::QUARTER && p.outputType != poplar::HALF)
     throw poplibs_error("Output type must be half when input type is quarter");
-  if (p.inputType == poplar::FLOAT)
-    throw poplibs_error("float convolution inputs are not supported on this target "
-                        "(half and quarter are)");
 }
 
 Tensor withGroupDim(const Tensor &weights, const ConvParams &p) {

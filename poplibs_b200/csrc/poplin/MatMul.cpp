@@ -38,9 +38,9 @@ void dimChecks(const std::vector<std::size_t> &a, const std::vector<std::size_t>
 }
 
 void typeChecks(const poplar::Type &in, const poplar::Type &out) {
-  if (in != poplar::HALF && in != poplar::QUARTER)
+  if (in != poplar::HALF && in != poplar::FLOAT && in != poplar::QUARTER)
     throw poplibs_error("matMul input type " + in.toString() +
-                        " is not supported on this target (half and quarter are)");
+                        " is not supported on this target (half, float and quarter are)");
   if (out != poplar::HALF && out != poplar::FLOAT)
     throw poplibs_error("matMul output type must be half or float");
   if (in == poplar::QUARTER && out != poplar::HALF)
@@ -122,9 +122,10 @@ void matMulImpl(Graph &graph, const Tensor &A_, const Tensor &B_, const Tensor &
     A = denseCopy(graph, A_, prog);
     la = layoutOf(A);
   }
-  // a row-major [k][n] right operand needs n % 8 == 0 (half); otherwise (and for
+  // a row-major [k][n] right operand is taken as it is (half, float); otherwise (and for
   // quarter, where it would be transposed at every call anyway) keep a [n][k] copy
-  const bool bRowMajorUsable = lb.ok && !lb.transposed && A.elementType() == poplar::HALF;
+  const bool bRowMajorUsable = lb.ok && !lb.transposed &&
+                               (A.elementType() == poplar::HALF || A.elementType() == poplar::FLOAT);
   if (k > 0 && n > 0 && !(lb.ok && lb.transposed) && !bRowMajorUsable) {
     B = denseCopy(graph, B_.dimShufflePartial({1, 2}, {2, 1}), prog).dimShufflePartial({1, 2}, {2, 1});
     lb = layoutOf(B);

@@ -463,12 +463,12 @@ int checkConvRequest(const plb_conv_params &p, bool wu, const void *first, size_
                      size_t result_elems) {
   const std::string err = validate(p);
   if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
-  if (wu && p.input_type != PLB_HALF)
+  if (wu && !is16BitFloat(p.input_type) && p.input_type != PLB_FLOAT)
     // the reference never runs the weight update in quarter either
     // (tools/single_conv_layer.cpp:725-733)
-    return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half input only");
-  if (p.input_type != PLB_HALF && p.input_type != PLB_QUARTER)
-    return fail(PLB_ERR_UNSUPPORTED, "convolution input type must be half or quarter");
+    return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half and float input only");
+  if (!is16BitFloat(p.input_type) && p.input_type != PLB_QUARTER && p.input_type != PLB_FLOAT)
+    return fail(PLB_ERR_UNSUPPORTED, "convolution input type must be half, float or quarter");
   if (p.output_type != PLB_HALF && p.output_type != PLB_FLOAT)
     return fail(PLB_ERR_INVALID_PARAMS, "convolution output type must be half or float");
   if (p.input_type == PLB_QUARTER && p.output_type != PLB_HALF)

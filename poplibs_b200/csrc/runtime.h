@@ -30,6 +30,7 @@ enum plb_scratch_slot {
   kSlotFoldedGrads,
   kSlotDilated,         // zero-stuffed input (input dilation)
   kSlotSplitK,          // fp32 partial sums of a split-K forward / backward / matrix product
+  kSlotFloatSplit,      // bfloat16 pieces of float operands
   kSlotCount
 };
 
@@ -91,8 +92,10 @@ int encodeTensorMap(CUtensorMap *tm, CUtensorMapDataType type, int rank, const v
                     const uint32_t *elem_strides, int swizzle_bytes = 128);
 
 inline size_t dtypeBytes(int dtype) {
-  return dtype == PLB_FLOAT ? 4 : dtype == PLB_HALF ? 2 : 1;
+  return dtype == PLB_FLOAT ? 4 : (dtype == PLB_HALF || dtype == PLB_BFLOAT16) ? 2 : 1;
 }
+// 16-bit floating-point operands (the kind::f16 instruction takes either)
+inline bool is16BitFloat(int dtype) { return dtype == PLB_HALF || dtype == PLB_BFLOAT16; }
 
 // Row resize (runtime.cu): rows of src_bytes -> rows of dst_bytes, zero fill / drop of the tail.
 int resizeRows(plb_context *ctx, const void *src, void *dst, size_t rows, size_t src_bytes,
@@ -154,7 +157,8 @@ int conv3dPlan(const plb_conv_params &p, const plb_conv_options *opt, int32_t pa
 
 // A fully resolved implicit-GEMM problem: one launch of the igemm kernel.
 struct IgemmProblem {
-  bool fp8 = false;      // 8-bit operands (else fp16)
+  bool fp8 = false;      // 8-bit operands (else 16-bit)
+  bool bf16 = false;     // 16-bit operands are bfloat16 (else half)
   int fmt_a = 0, fmt_b = 0;  // plb_quarter_format of the activations / weights when fp8
   bool b_mn = false;     // right operand stored [tap][K][N], N contiguous
   // activations: 4-D tensor (C, W, H, N) with byte strides of W, H, N
@@ -190,6 +194,23 @@ struct IgemmProblem {
 // Fills the tiling part of `plan` for a problem; returns non-zero if the
 // problem cannot be run by the igemm kernel (message recorded).
 int planIgemm(const IgemmProblem &p, int sm_count, plb_plan *plan);
+
+// ---- float operands (float_route.cu) ------------------------------------------
+// The layer / product that runs for float operands: bfloat16, the reduction
+// dimension of the pass three times as long.
+plb_conv_params floatRouteConvParams(const plb_conv_params &p, int pass);
+plb_matmul_desc floatRouteMatmulDesc(const plb_matmul_desc &d);
+int floatConvFwd(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+                 const void *d_in, const void *d_weights, const float *d_bias, void *d_out,
+                 int transpose_and_flip_weights);
+int floatConvBwd(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+                 const void *d_out_grads, const void *d_weights, void *d_in_grads);
+int floatConvWu(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
+                const void *d_acts, const void *d_out_grads, void *d_weight_grads,
+                float *d_weight_grads_f32);
+int floatMatmul(plb_context *ctx, const plb_matmul_desc &d, const void *d_a, const void *d_b,
+                const void *d_c, void *d_d);
+
 int launchIgemm(plb_context *ctx, const IgemmProblem &p, const plb_plan &plan);
 
 }  // namespace plb

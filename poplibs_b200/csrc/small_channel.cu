@@ -122,88 +122,110 @@ s2dInputRowsKernel(const __half *__restrict__ x, __half *__restrict__ x2, S2dSha
   }
 }
 
+// W2[a][co][(b*s*s + ph*s + pw)*Cp + c] = W[a*s + ph][b*s + pw][co][c], rows padded to 64:
+// element i of the folded weights.
+__device__ __forceinline__ __half foldedWeight(const __half *__restrict__ w, const S2dShape &g,
+                                               unsigned co_total, unsigned i) {
+  const unsigned k = i & 63u;
+  const unsigned r = i >> 6;
+  const unsigned a = r / co_total, co = r - a * co_total;
+  const unsigned b = k / unsigned(g.C2);
+  if (b >= unsigned(g.K2w)) return __float2half(0.f);
+  const unsigned c2 = k - b * g.C2;
+  const unsigned sub = c2 / unsigned(g.Cp), c = c2 - sub * g.Cp;
+  const unsigned ph = sub / unsigned(g.s), pw = sub - ph * g.s;
+  const unsigned kh = a * g.s + ph, kw = b * g.s + pw;
+  if (c < unsigned(g.C) && kh < unsigned(g.KH) && kw < unsigned(g.KW))
+    return w[((size_t(kh) * g.KW + kw) * co_total + co) * g.C + c];
+  return __float2half(0.f);
+}
+
+__global__ void s2dWeightsKernel(const __half *__restrict__ w, __half *__restrict__ w2, S2dShape g,
+                                 int co_total) {
+  const unsigned total = unsigned(g.K2h) * unsigned(co_total) * 64u;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x)
+    w2[i] = foldedWeight(w, g, unsigned(co_total), i);
+}
+
 // The same rearrangement for the common stem shape (3 channels, stride 2, so
 // Cp = 4 and one X2 pixel is two 16-byte vectors, one per vertical phase):
 // a vector is [X(ih, iw) c0..2, 0, X(ih, iw+1) c0..2, 0], i.e. six consecutive
-// halves of one input row.  One thread per vector; consecutive threads take
-// consecutive w2, so a warp reads one contiguous span of the row (four aligned
-// 32-bit loads per thread, overlapping its neighbours' in L1) and writes 512
-// contiguous bytes.  No shared memory, no divisions per element.
-__global__ void __launch_bounds__(256)
-s2dStem3Kernel(const uint32_t *__restrict__ x32, uint4 *__restrict__ x2, S2dShape g) {
-  const long long row_halves = (long long)g.W * 3;  // even: rows start on a 32-bit word
-  const size_t total = size_t(g.N) * g.H2 * 2 * g.W2;
-  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
-       i += size_t(gridDim.x) * blockDim.x) {
-    const int w2 = int(i % g.W2);
-    size_t r = i / g.W2;
-    const int ph = int(r & 1);
-    r >>= 1;
-    const int h2 = int(r % g.H2);
-    const int n = int(r / g.H2);
-    const int ih = 2 * h2 + ph - g.padH, iw = 2 * w2 - g.padW;
-    uint4 out = make_uint4(0u, 0u, 0u, 0u);
-    if (ih >= 0 && ih < g.H && iw + 1 >= 0 && iw < g.W) {
-      const long long row0 = ((long long)n * g.H + ih) * row_halves;  // first half of the row
-      const long long h0 = row0 + (long long)iw * 3;                  // first half wanted
-      const int odd = int(h0 & 1);
-      const long long w0 = (h0 - odd) / 2;  // first 32-bit word (exact division)
-      const long long row_w0 = row0 / 2, row_w1 = (row0 + row_halves) / 2;
-      uint32_t w[4];
+// halves of one input row.  One block per (n, h2) row of X2, one thread per
+// pixel of it (both vectors), so a warp reads one contiguous span of each of
+// the two input rows (four aligned 32-bit loads per thread and row,
+// overlapping its neighbours' in L1) and writes 1024 contiguous bytes.  No
+// shared memory; the only division is one 32-bit one per thread.  The blocks
+// past the last row fold the weights and clear the 128 bytes after X2 (they
+// only ever meet zero weights, but must be finite), so the layer's
+// preparation is one launch.
+__global__ void __launch_bounds__(128)
+s2dStem3Kernel(const uint32_t *__restrict__ x32, uint4 *__restrict__ x2, S2dShape g,
+               const __half *__restrict__ w, __half *__restrict__ w2, int co_total) {
+  // the convolution that follows may set itself up meanwhile; it waits for this
+  // grid to finish before it reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const unsigned rows = unsigned(g.N) * unsigned(g.H2);
+  if (blockIdx.x >= rows) {
+    const unsigned total = unsigned(g.K2h) * unsigned(co_total) * 64u;
+    const unsigned i = (blockIdx.x - rows) * blockDim.x + threadIdx.x;
+    if (i < total) w2[i] = foldedWeight(w, g, unsigned(co_total), i);
+    if (blockIdx.x == rows && threadIdx.x < 8)
+      x2[(size_t(rows) * g.W2 << 1) + threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const int row_words = g.W * 3 / 2;  // W * 3 is even: rows start on a 32-bit word
+  // last rows first: the convolution starts with the first images, which are
+  // then the ones most recently written and still in L2
+  const unsigned row = rows - 1 - blockIdx.x;
+  const unsigned n = row / unsigned(g.H2);
+  const int h2 = int(row - n * unsigned(g.H2));
+  uint4 *dst = x2 + (size_t(row) * g.W2 << 1);
+  for (int w2 = threadIdx.x; w2 < g.W2; w2 += blockDim.x) {
+    const int iw = 2 * w2 - g.padW;
+    const bool cols = iw + 1 >= 0 && iw < g.W;
+    const int h0 = iw * 3;               // first half wanted, relative to the row (may be negative)
+    const int odd = h0 & 1;
+    const int w0 = (h0 - odd) >> 1;      // first 32-bit word (exact; arithmetic shift)
+    const bool left = iw >= 0, right = iw + 1 < g.W;
+    uint4 out[2];
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        w[k] = (w0 + k >= row_w0 && w0 + k < row_w1) ? x32[w0 + k] : 0u;
-      // halves h0 .. h0 + 5 of the 8 loaded
-      uint32_t a, b, c;  // (h0,h1) (h2,h3) (h4,h5)
-      if (odd) {
-        a = __funnelshift_r(w[0], w[1], 16);
-        b = __funnelshift_r(w[1], w[2], 16);
-        c = __funnelshift_r(w[2], w[3], 16);
-      } else {
-        a = w[0];
-        b = w[1];
-        c = w[2];
+    for (int ph = 0; ph < 2; ++ph) {
+      const int ih = 2 * h2 + ph - g.padH;
+      out[ph] = make_uint4(0u, 0u, 0u, 0u);
+      if (cols && ih >= 0 && ih < g.H) {
+        const uint32_t *row = x32 + (size_t(n) * g.H + ih) * row_words;
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) w[k] = (w0 + k >= 0 && w0 + k < row_words) ? row[w0 + k] : 0u;
+        // halves h0 .. h0 + 5 of the 8 loaded
+        uint32_t a, b, c;  // (h0,h1) (h2,h3) (h4,h5)
+        if (odd) {
+          a = __funnelshift_r(w[0], w[1], 16);
+          b = __funnelshift_r(w[1], w[2], 16);
+          c = __funnelshift_r(w[2], w[3], 16);
+        } else {
+          a = w[0];
+          b = w[1];
+          c = w[2];
+        }
+        // pixel iw: h0 h1 h2; pixel iw + 1: h3 h4 h5
+        out[ph].x = left ? a : 0u;
+        out[ph].y = left ? (b & 0xffffu) : 0u;
+        out[ph].z = right ? ((b >> 16) | (c << 16)) : 0u;
+        out[ph].w = right ? (c >> 16) : 0u;
       }
-      const bool left = iw >= 0, right = iw + 1 < g.W;
-      // pixel iw: h0 h1 h2; pixel iw + 1: h3 h4 h5
-      out.x = left ? a : 0u;
-      out.y = left ? (b & 0xffffu) : 0u;
-      out.z = right ? ((b >> 16) | (c << 16)) : 0u;
-      out.w = right ? (c >> 16) : 0u;
     }
-    x2[(((size_t(n) * g.H2 + h2) * g.W2 + w2) << 1) + ph] = out;
+    dst[size_t(w2) << 1] = out[0];
+    dst[(size_t(w2) << 1) + 1] = out[1];
   }
 }
 
-// W2[a][co][(b*s*s + ph*s + pw)*Cp + c] = W[a*s + ph][b*s + pw][co][c], rows padded to 64.
-__global__ void s2dWeightsKernel(const __half *__restrict__ w, __half *__restrict__ w2, S2dShape g,
-                                 int co_total) {
-  const size_t total = size_t(g.K2h) * co_total * 64;
-  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total;
-       i += size_t(gridDim.x) * blockDim.x) {
-    const int k = int(i % 64);
-    size_t r = i / 64;
-    const int co = int(r % co_total);
-    const int a = int(r / co_total);
-    __half val = __float2half(0.f);
-    const int b = k / g.C2;
-    if (b < g.K2w) {
-      const int c2 = k - b * g.C2;
-      const int sub = c2 / g.Cp, c = c2 - sub * g.Cp;
-      const int ph = sub / g.s, pw = sub - ph * g.s;
-      const int kh = a * g.s + ph, kw = b * g.s + pw;
-      if (c < g.C && kh < g.KH && kw < g.KW)
-        val = w[((size_t(kh) * g.KW + kw) * co_total + co) * g.C + c];
-    }
-    w2[i] = val;
-  }
-}
 
 // Returns PLB_ERR_UNSUPPORTED (with a message) when the layer does not fit this path.
 int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_conv_options *opt,
                          const void *d_in, const void *d_weights, const float *d_bias,
                          void *d_out, plb_plan *plan_only) {
-  if (p.num_field_dims != 2 || p.groups != 1 || p.input_type != PLB_HALF)
+  if (p.num_field_dims != 2 || p.groups != 1 || !is16BitFloat(p.input_type))
     return fail(PLB_ERR_UNSUPPORTED,
                 "input channel count must be a multiple of 8 (half) / 16 (quarter) unless the "
                 "layer is a 2-D, ungrouped half convolution");
@@ -292,14 +314,16 @@ int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_c
   __half *x2 = static_cast<__half *>(ws);
   __half *w2 = x2 + ((x2_elems + 127) & ~size_t(127));
   {
+    bool fused_prep = false;
     const int row_elems = g.W * g.C;
     const size_t smem = size_t(g.s) * ((row_elems + 7) & ~7) * 2 + size_t(g.C2) * sizeof(int);
     if (g.C == 3 && g.s == 2 && g.Cp == 4 && row_elems % 2 == 0 &&
-        (reinterpret_cast<uintptr_t>(d_in) & 3) == 0) {
-      const size_t vecs = size_t(g.N) * g.H2 * g.W2 * 2;
-      const int grid = int(std::min<size_t>((vecs + 255) / 256, size_t(ctx->sm_count) * 32));
-      s2dStem3Kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint32_t *>(d_in),
-                                                    reinterpret_cast<uint4 *>(x2), g);
+        (reinterpret_cast<uintptr_t>(d_in) & 3) == 0 && size_t(g.N) * g.H2 < (size_t(1) << 31)) {
+      const unsigned wblocks = unsigned((w2_elems + 127) / 128);
+      s2dStem3Kernel<<<unsigned(g.N) * unsigned(g.H2) + wblocks, 128, 0, ctx->stream>>>(
+          static_cast<const uint32_t *>(d_in), reinterpret_cast<uint4 *>(x2), g,
+          static_cast<const __half *>(d_weights), w2, co);
+      fused_prep = true;
     } else if (smem <= 48 * 1024 && g.C < 256 && g.s < 256) {
       const int rows_aligned =
           (row_elems % 8 == 0 && (reinterpret_cast<uintptr_t>(d_in) & 15) == 0) ? 1 : 0;
@@ -313,13 +337,15 @@ int convFwdSmallChannels(plb_context *ctx, const plb_conv_params &p, const plb_c
     }
     PLB_CUDA(cudaGetLastError());
     ctx->launches++;
-    // the 64 trailing elements only ever meet zero weights, but must be finite
-    PLB_CUDA(cudaMemsetAsync(x2 + size_t(g.N) * g.H2 * g.W2 * g.C2, 0, 128, ctx->stream));
-    const int wgrid = int((w2_elems + 255) / 256);
-    s2dWeightsKernel<<<wgrid, 256, 0, ctx->stream>>>(static_cast<const __half *>(d_weights), w2, g,
-                                                     co);
-    PLB_CUDA(cudaGetLastError());
-    ctx->launches++;
+    if (!fused_prep) {
+      // the 64 trailing elements only ever meet zero weights, but must be finite
+      PLB_CUDA(cudaMemsetAsync(x2 + size_t(g.N) * g.H2 * g.W2 * g.C2, 0, 128, ctx->stream));
+      const int wgrid = int((w2_elems + 255) / 256);
+      s2dWeightsKernel<<<wgrid, 256, 0, ctx->stream>>>(static_cast<const __half *>(d_weights), w2, g,
+                                                       co);
+      PLB_CUDA(cudaGetLastError());
+      ctx->launches++;
+    }
   }
   q.act = x2;
   q.wgt = w2;

@@ -23,10 +23,10 @@ int wuShape(const plb_conv_params &p, WuShape *s) {
   if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
   if (p.num_field_dims > 2)
     return fail(PLB_ERR_UNSUPPORTED, "3-D convolutions are not implemented on this path yet");
-  if (p.input_type != PLB_HALF)
+  if (!is16BitFloat(p.input_type))
     // the reference never runs the weight update in quarter either
     // (tools/single_conv_layer.cpp:725-733)
-    return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half input only");
+    return fail(PLB_ERR_UNSUPPORTED, "weight update is implemented for half and float input only");
   for (unsigned d = 0; d != p.num_field_dims; ++d) {
     // (kernel truncation and flip are resolved by plb_conv_wu before it gets here)
     if (p.in_dilation[d] != 1 || p.in_flip[d] || p.k_trunc_lo[d] || p.k_trunc_hi[d] || p.k_flip[d])
@@ -116,6 +116,7 @@ void planWu(const plb_conv_params &p, const WuShape &s, int sm_count, int force_
   a->strip_mode = 0;
   // PLB_PLAN_NO_A_COLLECTOR: fetch the outGrad tile for every instruction (A/B timing)
   a->reuse_a = (plan_flags & PLB_PLAN_NO_A_COLLECTOR) ? 0 : 1;
+  a->idesc_formats = p.input_type == PLB_BFLOAT16 ? (make_idesc(0, 0, 1, 1, false, false) & ~(1u << 4)) : 0u;
   const int halo = (s.KH - 1) * s.dilH;
   if (s.KH > 1 && s.strH == 1 && s.KH * a->ci_blk <= 512 && (plan_flags & PLB_PLAN_NO_HALO) == 0) {
     long sbest = -1;
@@ -347,6 +348,18 @@ extern "C" {
 
 int plb_conv_wu_plan(const plb_conv_params *p_in, const plb_conv_options *opt, plb_plan *plan) {
   if (!p_in || !plan) return fail(PLB_ERR_INVALID_PARAMS, "null argument");
+  if (p_in->input_type == PLB_FLOAT) {
+    // what runs: bfloat16 operands, three batches side by side (float_route.cu)
+    const std::string err = validate(*p_in);
+    if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+    const plb_conv_params q = floatRouteConvParams(*p_in, PLB_PASS_TRAINING_WU);
+    if (int rc = plb_conv_wu_plan(&q, opt, plan)) return rc;
+    plan->flops = 2 * numberOfMacs(*p_in);
+    size_t n_in, n_w, n_out;
+    convElementCounts(*p_in, &n_in, &n_w, &n_out);
+    plan->workspace_bytes += (n_in + n_out) * 6 + 768;
+    return PLB_OK;
+  }
   if (p_in->num_field_dims == 3) return conv3dPlan(*p_in, opt, PLB_PASS_TRAINING_WU, plan);
   // plan what plb_conv_wu runs: flipped inputs are reversed first, truncated /
   // flipped kernels are computed as ordinary kernels of the truncated extent
@@ -392,6 +405,13 @@ int plb_conv_wu(plb_context *ctx, const plb_conv_params *p, const plb_conv_optio
     if (int rc = checkConvRequest(*p, true, d_acts, n_w ? n_in : 0, d_out_grads, n_w ? n_out : 0, result, n_w))
       return rc;
   }
+  if (p->input_type == PLB_FLOAT) {
+    const std::string err = validate(*p);
+    if (!err.empty()) return fail(PLB_ERR_INVALID_PARAMS, err);
+    return floatConvWu(ctx, *p, opt, d_acts, d_out_grads, d_weight_grads, d_weight_grads_f32);
+  }
+  if (p->input_type == PLB_BFLOAT16 && d_weight_grads)
+    return fail(PLB_ERR_UNSUPPORTED, "a bfloat16 layer's weight gradient is returned as fp32 only");
   if (p->num_field_dims == 3)
     return conv3dWu(ctx, *p, opt, d_acts, d_out_grads, d_weight_grads, d_weight_grads_f32);
   {

@@ -62,6 +62,7 @@ struct WuArgs {
   // The instructions of one 16-pixel step all read the same outGrad tile: keep
   // it in the tensor core's collector buffer between them (0 = fetch it each time).
   int reuse_a;
+  uint32_t idesc_formats;  // operand format bits of the instruction descriptor (bfloat16 operands)
   float *partial;  // [ksplit][taps][co_total][ci_total]
   int *status;
   long long *trace;  // optional timeline of CTA 0 (builds with -DPLB_TRACE only)
@@ -237,9 +238,10 @@ wu_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUt
           !strip && args.ci_blk == args.ci_blk64 * 64 ? max(1, 256 / args.ci_blk) : 1;
       const int tap_bytes = strip ? args.halo_step_bytes : args.ci_blk64 * kWuBlockBytes;
       const uint32_t idesc_full =
-          make_idesc(128, uint32_t(merge * args.ci_blk), 0, 0, true, true);
+          make_idesc(128, uint32_t(merge * args.ci_blk), 0, 0, true, true) | args.idesc_formats;
       const uint32_t idesc_rest =
-          make_idesc(128, uint32_t(max(1, ntaps % merge) * args.ci_blk), 0, 0, true, true);
+          make_idesc(128, uint32_t(max(1, ntaps % merge) * args.ci_blk), 0, 0, true, true) |
+          args.idesc_formats;
       const uint32_t d_step = uint32_t(merge * args.ci_blk);
       const uint64_t b_step16 = uint64_t(merge * tap_bytes) >> 4;
       const uint64_t a_desc0 = make_smem_desc(smem_base, kWuBlockBytes, 1024);

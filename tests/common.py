@@ -102,7 +102,8 @@ def gpu_matmul(a, b, c=None, *, transpose_a=False, transpose_b=False, alpha=1.0,
     n = b.shape[1] if transpose_b else b.shape[2]
     quarter = a.dtype == np.uint8
     desc = capi.MatmulDesc.make(m, k, n, groups=g,
-                                input_type=capi.QUARTER if quarter else capi.HALF,
+                                input_type=capi.QUARTER if quarter else
+                                capi.FLOAT if a.dtype == np.float32 else capi.HALF,
                                 output_type=capi.FLOAT if out_dtype == np.float32 else capi.HALF,
                                 transpose_a=transpose_a, transpose_b=transpose_b,
                                 alpha=alpha, beta=beta, scale_a=scale_a, scale_b=scale_b,
@@ -155,7 +156,8 @@ def gpu_conv_wu(p: capi.ConvParams, x_ncf, dy_ncf, ctx=None, opt=None, want_f32=
     """Returns (dW in the input type, dW fp32), both [G][Co][Ci][k...]."""
     import torch
     ctx = ctx or context()
-    in_dtype = np.uint8 if p.input_type == capi.QUARTER else np.float16
+    in_dtype = (np.uint8 if p.input_type == capi.QUARTER else
+                np.float32 if p.input_type == capi.FLOAT else np.float16)
     kernel = [int(p.kernel[i]) for i in range(p.num_field_dims)]
     shape = [p.groups] + kernel + [p.out_chans_per_group, p.in_chans_per_group]
     dx = to_dev(acts_to_device_layout(x_ncf))
