@@ -96,6 +96,11 @@ PLB_API void *plb_context_stream(plb_context *ctx);
 /* Blocks until all enqueued work is done, then checks the kernel status word:
  * returns PLB_ERR_KERNEL if any kernel gave up on a bounded wait. */
 PLB_API int plb_synchronize(plb_context *ctx);
+/* PCI address of a device ("0000:1b:00.0") into buf (at least 16 bytes): what
+ * a host uses to find the CPUs and memory next to the GPU
+ * (/sys/bus/pci/devices/<address>/local_cpulist) before it allocates the
+ * page-locked buffers of the *_host entry points. */
+PLB_API int plb_device_pci_address(int device, char *buf, size_t len);
 /* Number of kernels this context has launched so far. */
 PLB_API uint64_t plb_launch_count(const plb_context *ctx);
 /* PLB_PLAN_* bits (below) that are added to every plan made for a call through

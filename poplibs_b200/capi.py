@@ -135,7 +135,7 @@ _LIB = None
 # every symbol include/poplibs_b200.h declares
 SYMBOLS = (
     "plb_last_error", "plb_version", "plb_context_create", "plb_context_create_on_stream",
-    "plb_context_destroy", "plb_context_stream", "plb_synchronize", "plb_launch_count",
+    "plb_context_destroy", "plb_context_stream", "plb_synchronize", "plb_launch_count", "plb_device_pci_address",
     "plb_malloc", "plb_free", "plb_memcpy_h2d", "plb_memcpy_d2h", "plb_memset",
     "plb_matmul", "plb_matmul_host", "plb_conv_validate", "plb_conv_output_field",
     "plb_conv_input_index", "plb_conv_macs", "plb_conv_fwd", "plb_convolution",
@@ -168,6 +168,7 @@ def lib():
     L.plb_version.restype = C.c_char_p
     L.plb_context_create.argtypes = [C.c_int, C.POINTER(vp)]
     L.plb_context_create_on_stream.argtypes = [C.c_int, vp, C.POINTER(vp)]
+    L.plb_device_pci_address.argtypes = [C.c_int, C.c_char_p, sz]
     L.plb_context_destroy.argtypes = [vp]
     L.plb_context_destroy.restype = None
     L.plb_context_stream.argtypes = [vp]
@@ -236,6 +237,46 @@ def lib():
 def _check(rc: int):
     if rc != 0:
         raise PlbError(rc, lib().plb_last_error().decode("utf-8", "replace"))
+
+
+def parse_cpulist(text: str):
+    """'0-3,8,10-11' (the kernel's cpulist format) -> {0, 1, 2, 3, 8, 10, 11}."""
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def device_local_cpus(device: int):
+    """CPUs on the NUMA node the GPU hangs off (sysfs), limited to those this
+    process may run on; empty if the platform does not say."""
+    buf = C.create_string_buffer(32)
+    _check(lib().plb_device_pci_address(device, buf, 32))
+    try:
+        with open(f"/sys/bus/pci/devices/{buf.value.decode()}/local_cpulist") as f:
+            local = parse_cpulist(f.read())
+    except (OSError, ValueError):
+        return set()
+    return local & os.sched_getaffinity(0)
+
+
+def bind_host_to_device(device: int):
+    """Runs the calling thread (and the threads it starts) on the CPUs next to
+    the GPU, so that page-locked buffers allocated afterwards land in the
+    memory of that NUMA node and the copies of the *_host entry points do not
+    cross the socket interconnect.  Returns the previous affinity (pass it to
+    os.sched_setaffinity to undo), or None if nothing was changed."""
+    cpus = device_local_cpus(device)
+    if not cpus:
+        return None
+    before = os.sched_getaffinity(0)
+    if cpus == before:
+        return None
+    os.sched_setaffinity(0, cpus)
+    return before
 
 
 def _ptr(x) -> Optional[int]:

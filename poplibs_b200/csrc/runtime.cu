@@ -643,6 +643,14 @@ int plb_context_create(int device, plb_context **out) {
   return plb_context_create_on_stream(device, nullptr, out);
 }
 
+int plb_device_pci_address(int device, char *buf, size_t len) {
+  if (buf == nullptr || len < 16) return fail(PLB_ERR_INVALID_PARAMS, "buffer of at least 16 bytes needed");
+  PLB_CUDA(cudaDeviceGetPCIBusId(buf, int(len), device));
+  for (size_t i = 0; i < len && buf[i]; ++i)
+    if (buf[i] >= 'A' && buf[i] <= 'F') buf[i] = char(buf[i] - 'A' + 'a');  // sysfs spells it in lower case
+  return PLB_OK;
+}
+
 void plb_context_destroy(plb_context *ctx) {
   if (ctx == nullptr) return;
   cudaSetDevice(ctx->device);

@@ -221,3 +221,11 @@ def test_no_silent_fallback_without_a_gpu():
     with pytest.raises(capi.PlbError) as e:
         capi.Context(0)
     assert e.value.code == 4  # PLB_ERR_CUDA: fails loudly, nothing is computed on the host
+
+
+def test_cpulist_parsing():
+    """The kernel's cpulist format, as read from a PCI device's local_cpulist."""
+    from poplibs_b200 import capi
+    assert capi.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert capi.parse_cpulist("") == set()
+    assert capi.parse_cpulist("5") == {5}

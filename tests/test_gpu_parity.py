@@ -955,9 +955,14 @@ def test_scaled_add_and_cast(gpu_ctx):
 
 def test_unsupported_requests_fail_loudly(gpu_ctx):
     # an element type the path does not implement: refused before anything is launched
-    p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, input_type=capi.FLOAT, output_type=capi.FLOAT)
+    p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, input_type=7, output_type=capi.FLOAT)
     with pytest.raises(capi.PlbError) as e:
         gpu_ctx.conv_fwd(p, 0, 0, 0)
+    assert e.value.code == 3
+    # the weight update in quarter (the reference never runs it either)
+    p = capi.ConvParams.make(1, [8, 8], [3, 3], 64, 64, input_type=capi.QUARTER, output_type=capi.HALF)
+    with pytest.raises(capi.PlbError) as e:
+        gpu_ctx.conv_wu(p, 0, 0, 0, 0)
     assert e.value.code == 3
     # null pointers for tensors that have elements: refused, whatever pre-pass the parameters need
     for kw in (dict(), dict(in_dilation=2), dict(in_flip=1)):
