@@ -86,6 +86,9 @@ PLB_API const char *plb_version(void);
 /* Stands in for the poplar::Graph / Engine pair a poplin call is made on    */
 /* (tools/single_conv_layer.cpp:585-587, 1169, 1326-1340).                   */
 /* ------------------------------------------------------------------------ */
+/* Every call that takes a context makes the context's device the calling     */
+/* thread's current CUDA device (cudaSetDevice) and leaves it so; so does     */
+/* plb_conv_wu_static_scratch with its `device` argument.                     */
 typedef struct plb_context plb_context;
 
 PLB_API int plb_context_create(int device, plb_context **out);
