@@ -310,8 +310,9 @@ PLB_API uint64_t plb_conv_wu_allreduce_flag_bytes(const plb_conv_params *p);
  *    would choose when only fewer fit;
  *  - it runs none of the preparatory passes plb_conv_wu has (each needs scratch
  *    memory of its own): channel counts per group must be multiples of 8, and
- *    3-D fields, input dilation or flip, and truncated or flipped kernels are
- *    refused with PLB_ERR_UNSUPPORTED and a message naming plb_conv_wu;
+ *    float operands, 3-D fields, input dilation or flip, and truncated or
+ *    flipped kernels are refused with PLB_ERR_UNSUPPORTED and a message naming
+ *    plb_conv_wu;
  *  - the first call on a device looks up the array's device address (and sets a
  *    kernel attribute): make that first call before any stream capture;
  *  - all calls share the one array: calls that overlap on the GPU (different

@@ -595,6 +595,8 @@ int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p, const plb_
   if (epoch == 0 || (epoch & 0x80000000u))
     return fail(PLB_ERR_INVALID_PARAMS, "steps are numbered from 1 to 2^31 - 1 (flags start at zero)");
   const char *other = "; use plb_conv_wu and plb_allreduce_f32_p2p for this layer";
+  if (p->input_type != PLB_HALF)
+    return fail(PLB_ERR_UNSUPPORTED, std::string("plb_conv_wu_allreduce takes half operands") + other);
   WuShape s;
   if (int rc = wuShape(*p, &s)) return rc;   // 1-D / 2-D, half, no input dilation / flip, plain kernel
   const int co = int(p->out_chans_per_group), ci = int(p->in_chans_per_group);
@@ -713,6 +715,9 @@ extern "C" int plb_conv_wu_static_scratch(int device, void *cuda_stream, const p
                                           float *d_weight_grads_f32) {
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
   if (int rc = checkConvRequest(*p, true, nullptr, 0, nullptr, 0, nullptr, 0)) return rc;
+  if (p->input_type != PLB_HALF)
+    // float operands need scratch for their bfloat16 pieces
+    return fail(PLB_ERR_UNSUPPORTED, "plb_conv_wu_static_scratch takes half operands; use plb_conv_wu for this layer");
   PLB_CUDA(cudaSetDevice(device));
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   WuShape s;
