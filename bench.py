@@ -225,6 +225,24 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- workload state
 
+def workload_plan(spec):
+    """What the library's planner chooses for a workload (host-side arithmetic:
+    no device is touched), as both arms report it in `config.plan`."""
+    from poplibs_b200 import capi
+    if spec["kind"] == "norm":
+        pixels = spec["batch"] * int(np.prod(spec["field"]))
+        return {"kernel": "norm column sums + element-wise maps", "bytes": 5 * 2 * pixels * spec["chans"]}
+    if spec["kind"] == "conv":
+        p = capi.ConvParams.make(**spec["params"])
+        pass_id = {"bwd": capi.PASS_TRAINING_BWD, "wu": capi.PASS_TRAINING_WU}.get(
+            spec["pass_"], capi.PASS_TRAINING_FWD)
+        return capi.conv_plan(p, pass_id).as_dict()
+    q = spec["quarter"]
+    desc = capi.MatmulDesc.make(spec["m"], spec["k"], spec["n"], input_type=capi.QUARTER if q else capi.HALF,
+                                transpose_b=q, scale_a=-3 if q else 0, scale_b=-2 if q else 0)
+    return capi.matmul_plan(desc).as_dict()
+
+
 class Workload:
     """Device-resident rotating buffer sets (so that consecutive steps do not
     find their inputs in L2) and, for the workload the headline is quoted on,
@@ -250,8 +268,7 @@ class Workload:
                      "beta": uniform((self.chans,))}
             self.flops = 0
             # the activations are read twice (moments, whiten), the whitened ones written and read, the output written
-            self.plan = {"kernel": "norm column sums + element-wise maps",
-                         "bytes": 5 * 2 * self.pixels * self.chans}
+            self.plan = workload_plan(spec)
             per_set = 3 * 2 * self.pixels * self.chans
             out_shape = shape
         elif self.kind == "conv":
@@ -280,9 +297,7 @@ class Workload:
                 except Exception as e:  # symmetric memory unavailable: the process group's all-reduce
                     self.sharded = parallel.ShardedConv(ctx, glob, rank, world)
                     self.allreduce = f"nccl all_reduce + cast (peer memory unavailable: {type(e).__name__})"
-            pass_id = {"bwd": capi.PASS_TRAINING_BWD, "wu": capi.PASS_TRAINING_WU}.get(
-                self.pass_, capi.PASS_TRAINING_FWD)
-            self.plan = capi.conv_plan(p, pass_id).as_dict()
+            self.plan = workload_plan(spec)
             per_set = 2 * (int(np.prod(self.x_shape)) + int(np.prod(self.y_shape)))
             out_shape = {"fwd": self.y_shape, "bwd": self.x_shape, "wu": self.w_shape}[self.pass_]
         else:
@@ -292,7 +307,7 @@ class Workload:
                                              transpose_b=self.quarter,
                                              scale_a=-3 if self.quarter else 0, scale_b=-2 if self.quarter else 0)
             self.flops = 2 * m * k * n
-            self.plan = capi.matmul_plan(self.desc).as_dict()
+            self.plan = workload_plan(spec)
             if self.quarter:
                 a = torch.randn((m, k), generator=g, device=device).mul_(8).to(torch.float8_e4m3fn).view(torch.uint8)
                 b = torch.randn((n, k), generator=g, device=device).mul_(4).to(torch.float8_e4m3fn).view(torch.uint8)
@@ -684,6 +699,13 @@ def main():
         elapsed = time.perf_counter() - t0
         if spec["kind"] == "conv":
             config["per_gpu_batch"] = spec["params"]["batch"]
+            config["global_batch"] = spec["params"]["batch"] * world
+        # the same description of the workload as the library's arm gives (the
+        # plan is host-side arithmetic; it needs the library, not a GPU)
+        try:
+            config["plan"] = workload_plan(spec)
+        except (ImportError, OSError):
+            config["plan"] = None
         line = {"impl": "reference", "metric": metric, "value": best["value"], "unit": "TFLOP/s",
                 "n_gpus": args.gpus, "steps": steps, "warmup": 0, "ms_per_step": elapsed / steps * 1e3,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
@@ -818,21 +840,21 @@ def main():
     wl = Workload(args.workload, spec, ctx, device, rank, world, force_sets=args.buffer_sets,
                   allreduce=args.allreduce)
     config["plan"] = wl.plan
-    config["buffer_sets"] = wl.nsets
+    run = {"buffer_sets": wl.nsets}   # how this arm ran the workload (not part of its description)
     if args.buffer_sets > 0:
         config["l2"] = f"DIAGNOSTIC: {wl.nsets} buffer set(s) forced; inputs may stay in L2 between steps"
     if spec["kind"] == "conv":
         config["per_gpu_batch"] = spec["params"]["batch"]
         config["global_batch"] = spec["params"]["batch"] * world
     if wl.sharded is not None:
-        config["allreduce"] = wl.allreduce
-        config["allreduce_check"] = wl.check_allreduce()
+        run["allreduce"] = wl.allreduce
+        run["allreduce_check"] = wl.check_allreduce()
     count_launches(wl, wl.step)
     # The multi-GPU weight update passes a step counter to its kernels, so its
     # steps cannot be replayed from a graph.
     use_graph = not args.no_graph and wl.sharded is None
     (ms, launches, graphed), clocks = with_clocks(lambda: timed(wl, wl.step, args.steps, args.warmup, use_graph))
-    config["launch"] = ((f"one CUDA graph of {args.steps} steps, buffer sets in rotation" if args.steps <= 512
+    run["launch"] = ((f"one CUDA graph of {args.steps} steps, buffer sets in rotation" if args.steps <= 512
                          else f"CUDA graphs of {wl.nsets} steps (one per buffer set) and of the remaining "
                               f"{args.steps % wl.nsets}, replayed: exactly {args.steps} steps") if graphed
                         else "one library call per step")
@@ -924,7 +946,7 @@ def main():
         line = {"metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f8e4m3" if spec.get("quarter") else "f16",
-                "data": "synthetic", "config": config, "clocks": clocks, "e2e": e2e,
+                "data": "synthetic", "config": config, "run": run, "clocks": clocks, "e2e": e2e,
                 "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
                 "parity_check": parity}
         if workloads is not None:
