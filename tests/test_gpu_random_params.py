@@ -63,18 +63,18 @@ def draw(seed, dims=None, dilate_input=False):
     raise RuntimeError("no valid parameters drawn")
 
 
-def data(kw, p, r):
+def data(kw, p, r, dtype=np.float16):
     g = p.groups
-    x = T.binary_half(r, (p.batch, g * p.in_chans_per_group, *kw["field"]))
-    w = T.binary_half(r, (g, p.out_chans_per_group, p.in_chans_per_group, *kw["kernel"]))
-    dy = T.binary_half(r, (p.batch, g * p.out_chans_per_group, *p.output_field()))
+    x = T.binary_half(r, (p.batch, g * p.in_chans_per_group, *kw["field"])).astype(dtype)
+    w = T.binary_half(r, (g, p.out_chans_per_group, p.in_chans_per_group, *kw["kernel"])).astype(dtype)
+    dy = T.binary_half(r, (p.batch, g * p.out_chans_per_group, *p.output_field())).astype(dtype)
     return x, w, dy
 
 
 def check_all_passes(seed, kw, p):
     spec = T.spec_from_params(p)
     r = T.rng(seed)
-    x, w, dy = data(kw, p, r)
+    x, w, dy = data(kw, p, r, np.float32 if p.input_type == capi.FLOAT else np.float16)
     what = f"seed {seed}: {kw}"
     got = T.gpu_conv_fwd(p, x, w)
     assert np.array_equal(got.astype(np.float64), oracle.conv_fwd(spec, x, w).reshape(got.shape)), "fwd " + what
@@ -100,4 +100,13 @@ def test_random_conv_params_3d(gpu_ctx, seed):
 @pytest.mark.parametrize("seed", range(40))
 def test_random_conv_params_dilated_input(gpu_ctx, seed):
     kw, p = draw(seed, dilate_input=True)
+    check_all_passes(seed, kw, p)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_conv_params_float(gpu_ctx, seed):
+    """The same draws with float data (three bfloat16 terms per product): +-1 data
+    are exact in bfloat16, so the oracle's bits are expected here too."""
+    kw, _ = draw(seed, dims=3 if seed % 4 == 3 else None, dilate_input=seed % 4 == 2)
+    p = capi.ConvParams.make(**kw, input_type=capi.FLOAT, output_type=capi.FLOAT)
     check_all_passes(seed, kw, p)
