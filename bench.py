@@ -663,7 +663,7 @@ def main():
                          "update and the strong-scaling shapes that are added to the line by default)")
     ap.add_argument("--no-graph", action="store_true",
                     help="time one library call per step instead of replaying CUDA graphs")
-    ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "oneshot", "rs", "nccl"],
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "fused", "fused_all", "fused_owners", "oneshot", "rs", "nccl"],
                     help="how the multi-GPU weight update sums the per-rank gradients")
     ap.add_argument("--buffer-sets", type=int, default=0,
                     help="number of rotating buffer sets (default: enough to exceed L2; 1 = every step "

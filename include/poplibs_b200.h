@@ -296,6 +296,21 @@ PLB_API int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p,
                           void *const *d_peer_flags, uint32_t epoch, void *d_weight_grads,
                           float *d_weight_grads_f32);
 PLB_API uint64_t plb_conv_wu_allreduce_flag_bytes(const plb_conv_params *p);
+/* The same with the sum shared out: chunk c of the gradient is added (in rank
+ * order) by rank c mod world alone, which leaves it in its result buffer and
+ * flags it; the other ranks fetch the finished chunk from there.  Per rank
+ * 2 * (world - 1) / world of the gradient crosses NVLink instead of world - 1
+ * times, at the price of a second flag per chunk: the form for many ranks.
+ *   d_peer_results[r]  rank r's result buffer, the size of a gradient buffer,
+ *                      16-byte aligned, addressable from this GPU (one buffer:
+ *                      a rank's next step cannot begin before the others have
+ *                      fetched this step's sums from it).
+ * Flags: the same area as plb_conv_wu_allreduce (its size covers both forms). */
+PLB_API int plb_conv_wu_allreduce_owners(plb_context *ctx, const plb_conv_params *p,
+                          const plb_conv_options *opt, const void *d_acts, const void *d_out_grads,
+                          int32_t rank, int32_t world, void *const *d_peer_grads,
+                          void *const *d_peer_results, void *const *d_peer_flags, uint32_t epoch,
+                          void *d_weight_grads, float *d_weight_grads_f32);
 /* The same weight gradient for callers that cannot allocate device memory when
  * they need it (code running under an allocator that owns all device memory or
  * inside its hooks, loops that may not take the allocator's lock, processes with

@@ -142,7 +142,7 @@ SYMBOLS = (
     "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
     "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_bias_update", "plb_conv_fwd_host",
     "plb_context_set_plan_flags", "plb_norm_moments", "plb_norm_inv_std_dev", "plb_norm_whiten",
-    "plb_norm_scale_shift", "plb_norm_param_gradients", "plb_norm_statistics_gradients", "plb_allreduce_f32_p2p", "plb_allreduce_f32_p2p_rs", "plb_conv_wu_allreduce",
+    "plb_norm_scale_shift", "plb_norm_param_gradients", "plb_norm_statistics_gradients", "plb_allreduce_f32_p2p", "plb_allreduce_f32_p2p_rs", "plb_conv_wu_allreduce", "plb_conv_wu_allreduce_owners",
     "plb_conv_wu_allreduce_flag_bytes", "plb_allreduce_p2p_signal_bytes", "plb_matmul_host_async",
     "plb_conv_fwd_host_async",
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
@@ -210,6 +210,8 @@ def lib():
     L.plb_allreduce_f32_p2p_rs.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), u32, sz,
                                            vp, vp]
     L.plb_conv_wu_allreduce.argtypes = [vp, CP, OP, vp, vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u32, vp, vp]
+    L.plb_conv_wu_allreduce_owners.argtypes = [vp, CP, OP, vp, vp, i32, i32, C.POINTER(vp), C.POINTER(vp),
+                                               C.POINTER(vp), u32, vp, vp]
     L.plb_conv_wu_allreduce_flag_bytes.argtypes = [CP]
     L.plb_conv_wu_allreduce_flag_bytes.restype = u64
     L.plb_allreduce_p2p_signal_bytes.argtypes = [i32]
@@ -385,14 +387,22 @@ class Context:
                                            _ptr(out_f32), _ptr(out_half)))
 
     def conv_wu_allreduce(self, p: ConvParams, x, dy, rank, world, grad_ptrs, flag_ptrs, epoch, dw,
-                          dw_f32=None, opt: Optional[ConvOptions] = None):
+                          dw_f32=None, opt: Optional[ConvOptions] = None, result_ptrs=None):
         """Weight update of this rank's batch slice with the sum over ranks fused
-        into the reduction kernel; grad_ptrs / flag_ptrs: `world` device addresses."""
+        into the reduction kernel; grad_ptrs / flag_ptrs: `world` device addresses.
+        With result_ptrs (`world` addresses of result buffers) every chunk is
+        added by one rank and fetched by the others (plb_conv_wu_allreduce_owners)."""
         grads = (C.c_void_p * world)(*[int(v) for v in grad_ptrs])
         flags = (C.c_void_p * world)(*[int(v) for v in flag_ptrs])
-        _check(lib().plb_conv_wu_allreduce(self._h, C.byref(p), C.byref(opt) if opt else None, _ptr(x),
-                                           _ptr(dy), rank, world, grads, flags, epoch, _ptr(dw),
-                                           _ptr(dw_f32)))
+        if result_ptrs is None:
+            _check(lib().plb_conv_wu_allreduce(self._h, C.byref(p), C.byref(opt) if opt else None, _ptr(x),
+                                               _ptr(dy), rank, world, grads, flags, epoch, _ptr(dw),
+                                               _ptr(dw_f32)))
+            return
+        results = (C.c_void_p * world)(*[int(v) for v in result_ptrs])
+        _check(lib().plb_conv_wu_allreduce_owners(self._h, C.byref(p), C.byref(opt) if opt else None,
+                                                  _ptr(x), _ptr(dy), rank, world, grads, results, flags,
+                                                  epoch, _ptr(dw), _ptr(dw_f32)))
 
     def allreduce_f32_p2p_rs(self, rank, world, input_ptrs, result_ptrs, signal_pad_ptrs, epoch, count,
                              out_f32, out_half):

@@ -229,7 +229,10 @@ int launchWuReduce(cudaStream_t stream, const WuArgs &a, size_t w_elems, unsigne
     const size_t count4 = w_elems / 4;
     const unsigned rgrid = unsigned((count4 + kWuFusedChunk - 1) / kWuFusedChunk);
     WuPeerArgs pa = *peer;
-    for (int r = 0; r < pa.world; ++r) pa.grads[r] += size_t(g) * count4;
+    for (int r = 0; r < pa.world; ++r) {
+      pa.grads[r] += size_t(g) * count4;
+      if (pa.results[r] != nullptr) pa.results[r] += size_t(g) * count4;
+    }
     pa.chunk_base = g * rgrid;
     cudaLaunchConfig_t rcfg{};
     rcfg.gridDim = dim3(rgrid);
@@ -578,13 +581,17 @@ static size_t wuPeerChunks(const plb_conv_params &p, const WuShape &s) {
 uint64_t plb_conv_wu_allreduce_flag_bytes(const plb_conv_params *p) {
   WuShape s;
   if (!p || wuShape(*p, &s)) return 0;
-  return uint64_t(wuPeerChunks(*p, s)) * kWuPeerMaxWorld * sizeof(uint32_t);
+  // per chunk a word per sender, then a word per chunk for the owner's "sum complete"
+  return uint64_t(wuPeerChunks(*p, s)) * (kWuPeerMaxWorld + 1) * sizeof(uint32_t);
 }
 
-int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
-                          const void *d_acts, const void *d_out_grads, int32_t rank, int32_t world,
-                          void *const *d_peer_grads, void *const *d_peer_flags, uint32_t epoch,
-                          void *d_weight_grads, float *d_weight_grads_f32) {
+}  // extern "C"
+
+static int wuAllreduce(plb_context *ctx, const plb_conv_params *p, const plb_conv_options *opt,
+                       const void *d_acts, const void *d_out_grads, int32_t rank, int32_t world,
+                       void *const *d_peer_grads, void *const *d_peer_results,
+                       void *const *d_peer_flags, uint32_t epoch, void *d_weight_grads,
+                       float *d_weight_grads_f32) {
   TraceRange trace_range("plb_conv_wu_allreduce");
   if (int rc = activate(ctx)) return rc;
   if (!p) return fail(PLB_ERR_INVALID_PARAMS, "null params");
@@ -616,7 +623,13 @@ int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p, const plb_
       return fail(PLB_ERR_INVALID_PARAMS, "peer gradient buffers must be 16-byte aligned");
     pa.grads[r] = static_cast<float4 *>(d_peer_grads[r]);
     pa.flags[r] = static_cast<uint32_t *>(d_peer_flags[r]);
+    if (d_peer_results) {
+      if (!d_peer_results[r] || (reinterpret_cast<uintptr_t>(d_peer_results[r]) & 15) != 0)
+        return fail(PLB_ERR_INVALID_PARAMS, "peer result buffers must be non-null and 16-byte aligned");
+      pa.results[r] = static_cast<float4 *>(d_peer_results[r]);
+    }
   }
+  pa.result_flags = uint32_t(wuPeerChunks(*p, s) * kWuPeerMaxWorld);
   if ((reinterpret_cast<uintptr_t>(d_weight_grads_f32) & 15) != 0 ||
       (reinterpret_cast<uintptr_t>(d_weight_grads) & 7) != 0)
     return fail(PLB_ERR_INVALID_PARAMS, "outputs must be 16-byte (fp32) / 8-byte (half) aligned");
@@ -657,7 +670,27 @@ int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p, const plb_
   return PLB_OK;
 }
 
-}  // extern "C"
+extern "C" int plb_conv_wu_allreduce(plb_context *ctx, const plb_conv_params *p,
+                                     const plb_conv_options *opt, const void *d_acts,
+                                     const void *d_out_grads, int32_t rank, int32_t world,
+                                     void *const *d_peer_grads, void *const *d_peer_flags,
+                                     uint32_t epoch, void *d_weight_grads,
+                                     float *d_weight_grads_f32) {
+  return wuAllreduce(ctx, p, opt, d_acts, d_out_grads, rank, world, d_peer_grads, nullptr,
+                     d_peer_flags, epoch, d_weight_grads, d_weight_grads_f32);
+}
+
+extern "C" int plb_conv_wu_allreduce_owners(plb_context *ctx, const plb_conv_params *p,
+                                            const plb_conv_options *opt, const void *d_acts,
+                                            const void *d_out_grads, int32_t rank, int32_t world,
+                                            void *const *d_peer_grads,
+                                            void *const *d_peer_results,
+                                            void *const *d_peer_flags, uint32_t epoch,
+                                            void *d_weight_grads, float *d_weight_grads_f32) {
+  if (!d_peer_results) return fail(PLB_ERR_INVALID_PARAMS, "null pointer table");
+  return wuAllreduce(ctx, p, opt, d_acts, d_out_grads, rank, world, d_peer_grads, d_peer_results,
+                     d_peer_flags, epoch, d_weight_grads, d_weight_grads_f32);
+}
 
 // ---------------------------------------------------------------------------
 // Weight update for callers that must not allocate device memory

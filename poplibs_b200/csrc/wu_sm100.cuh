@@ -462,7 +462,11 @@ constexpr int kStatusWuPeerTimeout = 5;  // a peer's chunk flag did not arrive w
 
 struct WuPeerArgs {
   float4 *grads[kWuPeerMaxWorld];      // every rank's gradient buffer (this group's part)
-  uint32_t *flags[kWuPeerMaxWorld];    // every rank's flag area: [chunk][sender] words
+  // Owner mode (results[rank] != nullptr): chunk c is added by rank c mod world
+  // alone, which leaves the sum in its result buffer for the others to fetch.
+  float4 *results[kWuPeerMaxWorld];    // every rank's result buffer (this group's part), or null
+  uint32_t *flags[kWuPeerMaxWorld];    // every rank's flag area: [chunk][sender] words, then [chunk] result flags
+  uint32_t result_flags;               // word offset of the result flags in a flag area
   int rank, world;
   uint32_t epoch;       // step number, 1, 2, 3, ...; flags only grow
   uint32_t chunk_base;  // first chunk index of this launch (groups follow one another)
@@ -533,6 +537,96 @@ wu_reduce_allreduce_kernel(const float4 *__restrict__ partial, int ksplit, size_
   // 1.5 to 7.7 us per block against 0.6 us, 63.4 against 56.9 us per step on
   // two GPUs.  -DPLB_STRICT_SYSTEM_FENCE builds the formally scoped form.
   const uint32_t chunk = pa.chunk_base + blockIdx.x;
+  if (pa.results[pa.rank] != nullptr) {
+    // ---- owner mode: per rank (world - 1) / world of the gradient comes in
+    // twice (the owners' inputs, the others' results) instead of world - 1 times
+    const int owner = int(chunk % uint32_t(pa.world));
+    const size_t i = blockIdx.x * size_t(kWuFusedChunk) + tid;
+    auto publish = [&](uint32_t *flag) {
+#ifdef PLB_STRICT_SYSTEM_FENCE
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(pa.epoch) : "memory");
+#else
+      __threadfence();
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(pa.epoch) : "memory");
+#endif
+    };
+    auto await = [&](const uint32_t *flag) {
+      const long long start = clock64();
+      while (true) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+        if (int32_t(seen - pa.epoch) >= 0) break;
+        if (clock64() - start > kWaitCycleLimit) {
+          atomicCAS(pa.status, kStatusOk, kStatusWuPeerTimeout);
+          ok = 0;
+          break;
+        }
+      }
+    };
+    auto write_out = [&](const float4 &t) {
+      if (out_f32) out_f32[i] = t;
+      if (out_half) {
+        const __half2 lo = __floats2half2_rn(t.x, t.y), hi = __floats2half2_rn(t.z, t.w);
+        out_half[i] = make_uint2(*reinterpret_cast<const uint32_t *>(&lo),
+                                 *reinterpret_cast<const uint32_t *>(&hi));
+      }
+    };
+    if (pa.rank != owner) {
+      if (tid == 0) {
+        // "my chunk is complete" to the owner, then wait for "the sum is complete"
+        publish(pa.flags[owner] + size_t(chunk) * kWuPeerMaxWorld + pa.rank);
+        await(pa.flags[pa.rank] + pa.result_flags + chunk);
+      }
+      __syncthreads();
+      if (!ok) return;
+      if (tid < kWuFusedChunk && i < count4) {
+        float4 t;
+        const float4 *src = pa.results[owner] + i;
+        asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w)
+                     : "l"(src)
+                     : "memory");
+        write_out(t);
+      }
+      return;
+    }
+    if (tid < pa.world && tid != pa.rank)
+      await(pa.flags[pa.rank] + size_t(chunk) * kWuPeerMaxWorld + tid);
+    __syncthreads();
+    if (!ok) return;
+    if (tid < kWuFusedChunk && i < count4) {
+      float4 v[kWuPeerMaxWorld];
+#pragma unroll
+      for (int r = 0; r < kWuPeerMaxWorld; ++r) {
+        if (r < pa.world) {
+          const float4 *src = pa.grads[r] + i;
+          if (r == pa.rank) {
+            v[r] = *src;
+          } else {
+            asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(v[r].x), "=f"(v[r].y), "=f"(v[r].z), "=f"(v[r].w)
+                         : "l"(src)
+                         : "memory");
+          }
+        }
+      }
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < kWuPeerMaxWorld; ++r) {
+        if (r < pa.world) {
+          t.x += v[r].x;
+          t.y += v[r].y;
+          t.z += v[r].z;
+          t.w += v[r].w;
+        }
+      }
+      pa.results[pa.rank][i] = t;
+      write_out(t);
+    }
+    __syncthreads();
+    if (tid < pa.world && tid != pa.rank) publish(pa.flags[tid] + pa.result_flags + chunk);
+    return;
+  }
   if (tid < pa.world && tid != pa.rank) {
     uint32_t *theirs = pa.flags[tid] + size_t(chunk) * kWuPeerMaxWorld + pa.rank;
 #ifdef PLB_STRICT_SYSTEM_FENCE

@@ -57,7 +57,8 @@ def main() -> int:
     full = capi.ConvParams.make(**kw)
     sh = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, allreduce_mode="oneshot")
     sh_rs = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, allreduce_mode="rs")
-    sh_fu = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, allreduce_mode="fused")
+    sh_fu = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, allreduce_mode="fused_all")
+    sh_ow = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, allreduce_mode="fused_owners")
     b, e = sh.begin, sh.end
     with torch.cuda.stream(stream):
         # unsharded reference (every rank computes it; cheap)
@@ -76,10 +77,12 @@ def main() -> int:
         dw32 = torch.empty(3, 3, 72, 64, dtype=torch.float32, device=device)
         rs16, rs32 = torch.empty_like(dw16), torch.empty_like(dw32)
         fu16, fu32 = torch.empty_like(dw16), torch.empty_like(dw32)
+        ow16, ow32 = torch.empty_like(dw16), torch.empty_like(dw32)
         for _ in range(20):                # many steps: both buffer halves, growing epochs
             sh.wu(x[b:e].contiguous(), dy[b:e].contiguous(), dw16, dw32)
             sh_rs.wu(x[b:e].contiguous(), dy[b:e].contiguous(), rs16, rs32)
             sh_fu.wu(x[b:e].contiguous(), dy[b:e].contiguous(), fu16, fu32)
+            sh_ow.wu(x[b:e].contiguous(), dy[b:e].contiguous(), ow16, ow32)
         # the same sum by the process group's all-reduce
         local = torch.empty_like(dw32)
         ctx.conv_wu(sh.params, x[b:e].contiguous(), dy[b:e].contiguous(), None, local)
@@ -100,6 +103,8 @@ def main() -> int:
     # the same with the all-reduce on a stream of its own, several steps in flight
     report("sum over ranks fused into the split-K reduction: same bits, fp32 and half",
            torch.equal(fu32, dw32) and torch.equal(fu16, dw16))
+    report("the same with every chunk added by one owner rank: same bits, fp32 and half",
+           torch.equal(ow32, dw32) and torch.equal(ow16, dw16))
     # different, non-integer data on every rank: the order of additions now matters,
     # and all three forms must give the per-rank gradients added in rank order
     gr = torch.Generator().manual_seed(100 + rank)
@@ -109,7 +114,7 @@ def main() -> int:
         mine = torch.empty_like(dw32)
         ctx.conv_wu(sh.params, xr, dyr, None, mine)
         outs3 = []
-        for s3 in (sh, sh_rs, sh_fu):
+        for s3 in (sh, sh_rs, sh_fu, sh_ow):
             o16, o32 = torch.empty_like(dw16), torch.empty_like(dw32)
             s3.wu(xr, dyr, o16, o32)
             outs3.append((o16, o32))
@@ -120,7 +125,7 @@ def main() -> int:
     ordered = parts[0].clone()
     for part in parts[1:]:
         ordered += part
-    report("uniform data: one-shot, reduce-scatter and fused sums equal the rank-order sum, fp32 and half",
+    report("uniform data: one-shot, reduce-scatter and both fused sums equal the rank-order sum, fp32 and half",
            all(torch.equal(o32, ordered) and torch.equal(o16, ordered.half()) for o16, o32 in outs3))
     for mode in ("oneshot", "rs"):
         sho = parallel.ShardedConv(ctx, kw, rank, world, peer_allreduce=True, overlap_allreduce=True,

@@ -701,10 +701,10 @@ def test_weight_update_fused_with_sum_over_ranks_on_one_gpu(gpu_ctx):
         want = ((bufs[0] + bufs[1]) + bufs[2]).view(shape)
         assert torch.equal(out32, want)
         assert torch.equal(out16, want.half())
-        chunks = words // 16
+        chunks = words // 17          # a word per sender and chunk, then a word per chunk
         for peer in range(world):
             if peer != rank:
-                sent = flags[peer].view(chunks, 16)[:, rank]
+                sent = flags[peer][:chunks * 16].view(chunks, 16)[:, rank]
                 assert bool((sent == 1).all()), "a chunk flag was not sent"
     # step 2: nobody signals -> the bounded wait runs out and is reported
     ctx.conv_wu_allreduce(p, x, dy, rank, world, [b.data_ptr() for b in bufs], [f.data_ptr() for f in flags],
@@ -984,3 +984,77 @@ def test_unsupported_requests_fail_loudly(gpu_ctx):
         gpu_ctx.conv_fwd(p, 0, 0, 0)
     assert e.value.code == 1 and e.value.message == "Stride must be non zero"
     assert gpu_ctx.launch_count() > 0
+
+
+def test_weight_update_fused_with_owner_ranks_on_one_gpu(gpu_ctx):
+    """plb_conv_wu_allreduce_owners with every "rank's" buffers on this GPU and
+    all flags already set.  For the chunks it owns (chunk index mod world) the
+    emulated rank must add the peers' gradients to its own in rank order, leave
+    the sum in its result buffer and flag it to every peer; the other chunks it
+    must fetch from their owner's result buffer after flagging its own chunk to
+    that owner only.  Then a step whose peers never signal: reported, not hung."""
+    import torch
+    ctx = T.context()
+    world = 3
+    r = T.rng(12)
+    for kw in (conv_case(6, [12, 12], [3, 3], 64, 72, padding=1),
+               conv_case(4, [10, 10], [3, 3], 16, 24, padding=1, groups=3)):
+        p = capi.ConvParams.make(**kw)
+        g = p.groups
+        x = torch.from_numpy(T.binary_half(r, (p.batch, *kw["field"], g * p.in_chans_per_group))).cuda()
+        dy = torch.from_numpy(T.binary_half(r, (p.batch, *kw["field"], g * p.out_chans_per_group))).cuda()
+        shape = (g, 3, 3, p.out_chans_per_group, p.in_chans_per_group)
+        count = int(np.prod(shape))
+        per_group = count // g
+        local = torch.empty(shape, device="cuda")
+        ctx.conv_wu(p, x, dy, None, local)
+        ctx.synchronize()
+        words = int(capi.lib().plb_conv_wu_allreduce_flag_bytes(p)) // 4
+        chunks = words // 17
+        per_group_chunks = chunks // g
+        # owner of every element: chunk = group * chunks per group + (offset in the group) // 512 floats
+        idx = torch.arange(count, device="cuda")
+        chunk_of = (idx // per_group) * per_group_chunks + (idx % per_group) // 512
+        owner_of = chunk_of % world
+        gen = torch.Generator().manual_seed(6)
+        for rank in range(world):
+            bufs = [torch.randint(-64, 64, (count,), generator=gen).float().cuda() for _ in range(world)]
+            res = [torch.randint(-999, 999, (count,), generator=gen).float().cuda() for _ in range(world)]
+            fetched = [t.clone() for t in res]
+            flags = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(world)]
+            flags[rank].fill_(1)                      # every flag this rank waits for has "arrived"
+            out32 = torch.empty(shape, device="cuda")
+            out16 = torch.empty(shape, device="cuda", dtype=torch.float16)
+            torch.cuda.synchronize()
+            ctx.conv_wu_allreduce(p, x, dy, rank, world, [b.data_ptr() for b in bufs],
+                                  [f.data_ptr() for f in flags], 1, out16, out32,
+                                  result_ptrs=[t.data_ptr() for t in res])
+            ctx.synchronize()
+            assert torch.equal(bufs[rank].view(shape), local), "own gradient not left in the peer buffer"
+            summed = ((bufs[0] + bufs[1]) + bufs[2])
+            mine = owner_of == rank
+            want = summed.clone()
+            for o in range(world):
+                if o != rank:
+                    want[owner_of == o] = fetched[o][owner_of == o]
+            assert torch.equal(out32.view(-1), want), f"rank {rank}: fp32 result"
+            assert torch.equal(out16.view(-1), want.half()), f"rank {rank}: cast result"
+            assert torch.equal(res[rank][mine], summed[mine]), "owned sums not left in the result buffer"
+            for o in range(world):
+                if o != rank:
+                    assert torch.equal(res[o], fetched[o]), "a peer's result buffer was written"
+            owners = torch.arange(chunks, device="cuda") % world
+            for peer in range(world):
+                if peer == rank:
+                    continue
+                sent = flags[peer][:chunks * 16].view(chunks, 16)[:, rank]
+                assert torch.equal(sent == 1, owners == peer), "chunk flags go to the chunk's owner only"
+                ready = flags[peer][chunks * 16:chunks * 17]
+                assert torch.equal(ready == 1, owners == rank), "result flags of the owned chunks only"
+    # step 2 on the last rank: nobody signals -> the bounded wait runs out and is reported
+    ctx.conv_wu_allreduce(p, x, dy, rank, world, [b.data_ptr() for b in bufs], [f.data_ptr() for f in flags],
+                          2, None, out32, result_ptrs=[t.data_ptr() for t in res])
+    with pytest.raises(capi.PlbError):
+        ctx.synchronize()
+    ctx.conv_wu(p, x, dy, None, local)      # the context still works
+    ctx.synchronize()
