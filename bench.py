@@ -100,7 +100,7 @@ NCU_DRAM_TRAFFIC_BYTES = {
     "conv3x3_wu_n256_28x28_c128": 105509248 + 4087936,
     "conv1x1_s2_fwd_n256_56x56_c256_c512": 103111168 + 153707456,
     "conv7x7_s2_fwd_n256_224x224_c3_c64": 114367232 + 358181632,   # the implicit-GEMM kernel of the two (the fold adds 77.1 + 56.1 MB)
-    "batchnorm_fwd_n32_56x56_c64": 3 * 12850000,                   # moments + the two element-wise kernels (outputs stay in L2)
+    "batchnorm_fwd_n32_56x56_c64": 2 * 12850000,                   # column sums + the normalising pass (outputs stay in L2)
     "matmul_fp16_512x1024x1024": 3220000,
     "matmul_fp16_8192": 1074835000 + 128641408,
     "matmul_fp8_8192": 344460000 + 119442500,
@@ -231,7 +231,7 @@ def workload_plan(spec):
     from poplibs_b200 import capi
     if spec["kind"] == "norm":
         pixels = spec["batch"] * int(np.prod(spec["field"]))
-        return {"kernel": "norm column sums + element-wise maps", "bytes": 5 * 2 * pixels * spec["chans"]}
+        return {"kernel": "norm column sums + element-wise maps", "bytes": 4 * 2 * pixels * spec["chans"]}
     if spec["kind"] == "conv":
         p = capi.ConvParams.make(**spec["params"])
         pass_id = {"bwd": capi.PASS_TRAINING_BWD, "wu": capi.PASS_TRAINING_WU}.get(
@@ -267,7 +267,7 @@ class Workload:
             proto = {"x": uniform(shape).add_(0.25), "gamma": uniform((self.chans,)).abs_().add_(0.5),
                      "beta": uniform((self.chans,))}
             self.flops = 0
-            # the activations are read twice (moments, whiten), the whitened ones written and read, the output written
+            # the activations are read twice (statistics, normalise), the whitened ones and the output written
             self.plan = workload_plan(spec)
             per_set = 3 * 2 * self.pixels * self.chans
             out_shape = shape
@@ -363,10 +363,9 @@ class Workload:
         d = self.dev[i % self.nsets]
         if self.kind == "norm":
             H, c, n = self.capi.HALF, self.chans, self.pixels
-            self.ctx.norm_moments(H, d["x"], n, c, 1.0 / n, None, d["mean"], d["power"])
-            self.ctx.norm_inv_std_dev(H, d["mean"], d["power"], c, 1e-3, 1.0, False, d["inv"])
-            self.ctx.norm_whiten(H, d["x"], d["mean"], d["inv"], n, c, d["white"])
-            self.ctx.norm_scale_shift(H, d["white"], d["gamma"], d["beta"], n, c, d["out"])
+            self.ctx.norm_statistics(H, d["x"], n, c, 1e-3, 1.0, d["mean"], d["inv"], d["power"])
+            self.ctx.norm_normalise(H, d["x"], d["mean"], d["inv"], d["gamma"], d["beta"], n, c, d["white"],
+                                    d["out"])
         elif self.kind == "gemm":
             self.ctx.matmul(self.desc, d["a"], d["b"], None, d["out"])
         elif self.pass_ == "fwd":

@@ -416,6 +416,20 @@ PLB_API int plb_norm_moments(plb_context *ctx, int32_t dtype, const void *d_acts
 PLB_API int plb_norm_inv_std_dev(plb_context *ctx, int32_t dtype, const void *d_mean,
                          const float *d_power, uint32_t chans, float eps, float scale_var,
                          int stable, void *d_inv_std);
+/* Mean and inverse standard deviation in one call (poplin::normStatistics with
+ * the default estimator, Norms.hpp:64-72): plb_norm_moments with scale =
+ * 1 / pixels, and plb_norm_inv_std_dev's arithmetic applied by the kernel that
+ * finishes the sums; the same bits as the two calls.  d_power may be NULL. */
+PLB_API int plb_norm_statistics(plb_context *ctx, int32_t dtype, const void *d_acts, uint64_t pixels,
+                        uint32_t chans, float eps, float scale_var, void *d_mean, void *d_inv_std,
+                        float *d_power);
+/* Whitening followed by scale and shift in one pass over the activations
+ * (poplin::normWhiten then poplin::normalise): out = w * gamma[c] + beta[c] with
+ * w = (acts - mean[c]) * inv_std[c] rounded to the activations' type, as the two
+ * calls would store it; d_whitened (may be NULL) receives w. */
+PLB_API int plb_norm_normalise(plb_context *ctx, int32_t dtype, const void *d_acts, const void *d_mean,
+                       const void *d_inv_std, const void *d_gamma, const void *d_beta,
+                       uint64_t pixels, uint32_t chans, void *d_whitened, void *d_out);
 /* out = (acts - mean[c]) * inv_std[c]  (poplin::normWhiten, Norms.hpp:212-216). */
 PLB_API int plb_norm_whiten(plb_context *ctx, int32_t dtype, const void *d_acts, const void *d_mean,
                     const void *d_inv_std, uint64_t pixels, uint32_t chans, void *d_out);

@@ -142,6 +142,7 @@ SYMBOLS = (
     "plb_conv_wu_static_scratch", "plb_conv_bwd", "plb_conv_wu",
     "plb_scaled_add_to", "plb_cast_from_f32", "plb_add_bias", "plb_conv_bias_update", "plb_conv_fwd_host",
     "plb_context_set_plan_flags", "plb_norm_moments", "plb_norm_inv_std_dev", "plb_norm_whiten",
+    "plb_norm_statistics", "plb_norm_normalise",
     "plb_norm_scale_shift", "plb_norm_param_gradients", "plb_norm_statistics_gradients", "plb_allreduce_f32_p2p", "plb_allreduce_f32_p2p_rs", "plb_conv_wu_allreduce", "plb_conv_wu_allreduce_owners",
     "plb_conv_wu_allreduce_flag_bytes", "plb_allreduce_p2p_signal_bytes", "plb_matmul_host_async",
     "plb_conv_fwd_host_async",
@@ -202,6 +203,8 @@ def lib():
     L.plb_norm_moments.argtypes = [vp, i32, vp, u64, u32, f32, vp, vp, vp]
     L.plb_norm_inv_std_dev.argtypes = [vp, i32, vp, vp, u32, f32, f32, i32, vp]
     L.plb_norm_whiten.argtypes = [vp, i32, vp, vp, vp, u64, u32, vp]
+    L.plb_norm_statistics.argtypes = [vp, i32, vp, u64, u32, f32, f32, vp, vp, vp]
+    L.plb_norm_normalise.argtypes = [vp, i32, vp, vp, vp, vp, vp, u64, u32, vp, vp]
     L.plb_norm_scale_shift.argtypes = [vp, i32, vp, vp, vp, u64, u32, vp]
     L.plb_norm_param_gradients.argtypes = [vp, i32, vp, vp, u64, u32, f32, vp, vp, vp, vp]
     L.plb_norm_statistics_gradients.argtypes = [vp, i32, vp, vp, vp, vp, vp, u64, u32, vp]
@@ -421,6 +424,16 @@ class Context:
     def norm_inv_std_dev(self, dtype, mean, power, chans, eps, scale_var, stable, inv_std):
         _check(lib().plb_norm_inv_std_dev(self._h, dtype, _ptr(mean), _ptr(power), chans, eps, scale_var,
                                           int(stable), _ptr(inv_std)))
+
+    def norm_statistics(self, dtype, acts, pixels, chans, eps, scale_var, mean, inv_std, power=None):
+        """Mean and 1/sigma per channel in one call (the default estimator)."""
+        _check(lib().plb_norm_statistics(self._h, dtype, _ptr(acts), pixels, chans, eps, scale_var, _ptr(mean),
+                                         _ptr(inv_std), _ptr(power)))
+
+    def norm_normalise(self, dtype, acts, mean, inv_std, gamma, beta, pixels, chans, whitened, out):
+        """Whiten, then scale and shift, in one pass; `whitened` may be None."""
+        _check(lib().plb_norm_normalise(self._h, dtype, _ptr(acts), _ptr(mean), _ptr(inv_std), _ptr(gamma),
+                                        _ptr(beta), pixels, chans, _ptr(whitened), _ptr(out)))
 
     def norm_whiten(self, dtype, acts, mean, inv_std, pixels, chans, out):
         _check(lib().plb_norm_whiten(self._h, dtype, _ptr(acts), _ptr(mean), _ptr(inv_std), pixels, chans,

@@ -214,7 +214,7 @@ template <typename TA, typename TB>
 __global__ void __launch_bounds__(256)
 normColumnFinishKernel(const float *__restrict__ partial_a, const float *__restrict__ partial_b,
                        int blocks, int chans, float scale, TA *__restrict__ out_a,
-                       TB *__restrict__ out_b) {
+                       TB *__restrict__ out_b, TA *__restrict__ inv_std, float eps, float scale_var) {
   pdl_launch_dependents();
   pdl_wait();  // inputs may come from the previous kernel in the stream
   const int c = blockIdx.x * 8 + threadIdx.y;
@@ -230,8 +230,18 @@ normColumnFinishKernel(const float *__restrict__ partial_a, const float *__restr
     b += __shfl_xor_sync(0xffffffffu, b, d);
   }
   if (threadIdx.x == 0) {
-    if (out_a) out_a[c] = fromFloat<TA>(a * scale);
-    if (out_b) out_b[c] = fromFloat<TB>(b * scale);
+    const float mean = __fmul_rn(a, scale), power = __fmul_rn(b, scale);
+    if (out_a) out_a[c] = fromFloat<TA>(mean);
+    if (out_b) out_b[c] = fromFloat<TB>(power);
+    if (inv_std) {
+      // normInvStdDevKernel's arithmetic on the values as stored: the mean
+      // rounded to its type, the power in fp32
+      const float m = toFloat(fromFloat<TA>(mean));
+      float var = power - m * m;
+      if (var < 0.f) var = 0.f;
+      var = (var + eps) * scale_var;
+      inv_std[c] = fromFloat<TA>(1.0f / sqrtf(var));
+    }
   }
 }
 
@@ -339,6 +349,38 @@ __global__ void normMapVecKernel(const T *__restrict__ x, const T *__restrict__ 
   }
 }
 
+// Whiten, then scale and shift, in one pass: the whitened value is rounded to
+// the activations' type (and stored, if asked for) before it is scaled, so both
+// outputs are the bits that normMapVecKernel<kWhiten> followed by
+// normMapVecKernel<kScaleShift> leave.
+template <typename T>
+__global__ void normNormaliseVecKernel(const T *__restrict__ x, const T *__restrict__ mean,
+                                       const T *__restrict__ inv_std, const T *__restrict__ gamma,
+                                       const T *__restrict__ beta, size_t vectors, int chans,
+                                       T *__restrict__ whitened, T *__restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();  // inputs may come from the previous kernel in the stream
+  constexpr int kVec = NormVec<T>::kVec;
+  const int per_row = chans / kVec;
+  for (size_t v = blockIdx.x * size_t(blockDim.x) + threadIdx.x; v < vectors;
+       v += size_t(gridDim.x) * blockDim.x) {
+    const int c0 = int(v % size_t(per_row)) * kVec;
+    float xv[kVec], mv[kVec], sv[kVec], gv[kVec], bv[kVec], w[kVec], o[kVec];
+    NormVec<T>::load(x + v * kVec, xv);
+    NormVec<T>::load(mean + c0, mv);
+    NormVec<T>::load(inv_std + c0, sv);
+    NormVec<T>::load(gamma + c0, gv);
+    NormVec<T>::load(beta + c0, bv);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+      w[j] = toFloat(fromFloat<T>((xv[j] - mv[j]) * sv[j]));
+      o[j] = w[j] * gv[j] + bv[j];
+    }
+    if (whitened) NormVec<T>::store(whitened + v * kVec, w);
+    NormVec<T>::store(out + v * kVec, o);
+  }
+}
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // Launch with programmatic stream serialization: the kernel may become
@@ -371,7 +413,8 @@ int rowBlocks(const plb_context *ctx, size_t rows, int chans) {
 // Column sums of mode kMode -> out_a, out_b (either may be null), times scale.
 template <typename T, int kMode, typename TA, typename TB>
 int columnSums(plb_context *ctx, const T *x, const T *y, const T *centre, size_t rows, int chans,
-               float scale, TA *out_a, TB *out_b) {
+               float scale, TA *out_a, TB *out_b, TA *inv_std = nullptr, float eps = 0.f,
+               float scale_var = 1.f) {
   constexpr int kVec = NormVec<T>::kVec;
   const bool vec = chans % kVec == 0 && kNormVecThreads % (chans / kVec) == 0 && aligned16(x) &&
                    (y == nullptr || aligned16(y)) && (centre == nullptr || aligned16(centre));
@@ -400,7 +443,8 @@ int columnSums(plb_context *ctx, const T *x, const T *y, const T *centre, size_t
       return rc;
   }
   return launchPdl(ctx, normColumnFinishKernel<TA, TB>, dim3(unsigned((chans + 7) / 8)), dim3(32, 8), 0,
-                   (const float *)pa, (const float *)pb, blocks, chans, scale, out_a, out_b);
+                   (const float *)pa, (const float *)pb, blocks, chans, scale, out_a, out_b, inv_std, eps,
+                   scale_var);
 }
 
 template <typename T, int kMode>
@@ -418,6 +462,22 @@ int mapLaunch(plb_context *ctx, const T *x, const T *y, const T *p, const T *q, 
   const int grid = int(std::min<size_t>((count + 255) / 256, size_t(ctx->sm_count) * 16));
   return launchPdl(ctx, normMapKernel<T, kMode>, dim3(unsigned(grid)), dim3(256), 0, x, y, p, q, r, pf, qf, count,
                    chans, out);
+}
+
+template <typename T>
+int normaliseFused(plb_context *ctx, const T *x, const T *mean, const T *inv, const T *gamma,
+                          const T *beta, uint64_t pixels, uint32_t chans, T *whitened, T *out) {
+  constexpr int kVec = NormVec<T>::kVec;
+  const size_t n = size_t(pixels) * chans;
+  if (n == 0) return PLB_OK;
+  if (chans % kVec == 0 && aligned16(x) && aligned16(out) && aligned16(mean) && aligned16(inv) &&
+      aligned16(gamma) && aligned16(beta) && (whitened == nullptr || aligned16(whitened))) {
+    const size_t vectors = n / kVec;
+    const int grid = int(std::min<size_t>((vectors + 255) / 256, size_t(ctx->sm_count) * 16));
+    return launchPdl(ctx, normNormaliseVecKernel<T>, dim3(unsigned(grid)), dim3(256), 0, x, mean, inv, gamma,
+                     beta, vectors, int(chans), whitened, out);
+  }
+  return -1;   // not vectorisable: the caller takes the two-pass route
 }
 
 int checkNorm(int32_t dtype, uint64_t pixels, uint32_t chans) {
@@ -464,6 +524,53 @@ int plb_norm_moments(plb_context *ctx, int32_t dtype, const void *d_acts, uint64
       (columnSums<float, kSumXAndXX, float, float>(ctx, static_cast<const float *>(d_acts), nullptr,
                                                    nullptr, pixels, int(chans), scale,
                                                    static_cast<float *>(d_mean), d_power)));
+}
+
+int plb_norm_statistics(plb_context *ctx, int32_t dtype, const void *d_acts, uint64_t pixels,
+                        uint32_t chans, float eps, float scale_var, void *d_mean, void *d_inv_std,
+                        float *d_power) {
+  TraceRange trace_range("plb_norm_statistics");
+  if (int rc = activate(ctx)) return rc;
+  if (int rc = checkNorm(dtype, pixels, chans)) return rc;
+  if ((!d_acts && pixels) || !d_mean || !d_inv_std)
+    return fail(PLB_ERR_INVALID_PARAMS, "normalisation: null pointer");
+  const float scale = pixels > 0 ? 1.0f / float(pixels) : 1.0f;
+  return PLB_NORM_DISPATCH(
+      dtype,
+      (columnSums<__half, kSumXAndXX, __half, float>(ctx, static_cast<const __half *>(d_acts), nullptr,
+                                                     nullptr, pixels, int(chans), scale,
+                                                     static_cast<__half *>(d_mean), d_power,
+                                                     static_cast<__half *>(d_inv_std), eps, scale_var)),
+      (columnSums<float, kSumXAndXX, float, float>(ctx, static_cast<const float *>(d_acts), nullptr,
+                                                   nullptr, pixels, int(chans), scale,
+                                                   static_cast<float *>(d_mean), d_power,
+                                                   static_cast<float *>(d_inv_std), eps, scale_var)));
+}
+
+int plb_norm_normalise(plb_context *ctx, int32_t dtype, const void *d_acts, const void *d_mean,
+                       const void *d_inv_std, const void *d_gamma, const void *d_beta, uint64_t pixels,
+                       uint32_t chans, void *d_whitened, void *d_out) {
+  TraceRange trace_range("plb_norm_normalise");
+  if (int rc = activate(ctx)) return rc;
+  if (int rc = checkNorm(dtype, pixels, chans)) return rc;
+  if (!d_mean || !d_inv_std || !d_gamma || !d_beta || ((!d_acts || !d_out) && pixels))
+    return fail(PLB_ERR_INVALID_PARAMS, "normalisation: null pointer");
+  const int rc = PLB_NORM_DISPATCH(
+      dtype,
+      (normaliseFused<__half>(ctx, static_cast<const __half *>(d_acts), static_cast<const __half *>(d_mean),
+                              static_cast<const __half *>(d_inv_std), static_cast<const __half *>(d_gamma),
+                              static_cast<const __half *>(d_beta), pixels, chans,
+                              static_cast<__half *>(d_whitened), static_cast<__half *>(d_out))),
+      (normaliseFused<float>(ctx, static_cast<const float *>(d_acts), static_cast<const float *>(d_mean),
+                             static_cast<const float *>(d_inv_std), static_cast<const float *>(d_gamma),
+                             static_cast<const float *>(d_beta), pixels, chans,
+                             static_cast<float *>(d_whitened), static_cast<float *>(d_out))));
+  if (rc != -1) return rc;
+  // channel counts or addresses the vector kernel cannot take: whiten (into the
+  // output if the whitened activations are not wanted), then scale and shift
+  void *w = d_whitened ? d_whitened : d_out;
+  if (int rc2 = plb_norm_whiten(ctx, dtype, d_acts, d_mean, d_inv_std, pixels, chans, w)) return rc2;
+  return plb_norm_scale_shift(ctx, dtype, w, d_gamma, d_beta, pixels, chans, d_out);
 }
 
 int plb_norm_inv_std_dev(plb_context *ctx, int32_t dtype, const void *d_mean, const float *d_power,

@@ -89,6 +89,16 @@ std::pair<Tensor, Tensor> statisticsImpl(Graph &graph, const Tensor &acts, float
           static_cast<float *>(powerOut.devicePointer())));
     };
   };
+  if (!stable && !distributed) {
+    // the common case in one call: the kernel that finishes the sums also forms 1 / sigma
+    Tensor iStdDev = perChannel(graph, acts, acts.elementType(), dc.getPathName() + "/iStdDev");
+    prog.add([=](plb_context *ctx) {
+      poplar::detail::check(plb_norm_statistics(ctx, a.dtype, x.devicePointer(), a.pixels, uint32_t(a.chans), eps,
+                                                scaleVar, mean.devicePointer(), iStdDev.devicePointer(),
+                                                static_cast<float *>(power.devicePointer())));
+    });
+    return {mean, iStdDev};
+  }
   if (stable) {
     // mean first (reduced over the replicas), then the squared deviations from it
     Tensor unusedPower = perChannel(graph, acts, poplar::FLOAT, dc.getPathName() + "/rawPower");

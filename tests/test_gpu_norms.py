@@ -124,3 +124,41 @@ def test_norm_rejects_other_types(gpu_ctx):
     x = T.empty_dev([4, 8], np.uint8)
     with pytest.raises(capi.PlbError):
         ctx.norm_whiten(capi.QUARTER, x, x, x, 4, 8, x)
+
+
+@pytest.mark.parametrize("dtype", ["half", "float"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_fused_statistics_and_normalise_give_the_separate_calls_bits(gpu_ctx, shape, dtype):
+    """plb_norm_statistics = plb_norm_moments + plb_norm_inv_std_dev, and
+    plb_norm_normalise = plb_norm_whiten + plb_norm_scale_shift, bit for bit
+    (the separate calls are the ones checked against the oracle above)."""
+    import torch
+    ctx = T.context()
+    b, c, f = shape
+    np_t, plb_t = (np.float16, capi.HALF) if dtype == "half" else (np.float32, capi.FLOAT)
+    r = T.rng(b * 77 + c * 5 + f)
+    x = r.normal(0.4, 1.5, shape).astype(np_t)
+    gamma, beta = r.uniform(0.5, 2.0, c).astype(np_t), r.uniform(-1, 1, c).astype(np_t)
+    pixels = b * f
+    dx, dgamma, dbeta = T.to_dev(dev_layout(x)), T.to_dev(gamma), T.to_dev(beta)
+    mean, inv, power = T.empty_dev([c], np_t), T.empty_dev([c], np_t), T.empty_dev([c], np.float32)
+    mean2, inv2, power2 = T.empty_dev([c], np_t), T.empty_dev([c], np_t), T.empty_dev([c], np.float32)
+    white, out = T.empty_dev([pixels, c], np_t), T.empty_dev([pixels, c], np_t)
+    white2, out2, out3 = (T.empty_dev([pixels, c], np_t) for _ in range(3))
+    for scale_var in (1.0, pixels / max(pixels - 1, 1)):
+        ctx.norm_moments(plb_t, dx, pixels, c, 1.0 / pixels, None, mean, power)
+        ctx.norm_inv_std_dev(plb_t, mean, power, c, 1e-3, scale_var, False, inv)
+        ctx.norm_statistics(plb_t, dx, pixels, c, 1e-3, scale_var, mean2, inv2, power2)
+        ctx.synchronize()
+        assert torch.equal(mean, mean2) and torch.equal(power, power2), "mean / power"
+        assert torch.equal(inv, inv2), f"inverse standard deviation, scale_var {scale_var}"
+    ctx.norm_inv_std_dev(plb_t, mean, power, c, 1e-3, 1.0, False, inv)
+    ctx.norm_statistics(plb_t, dx, pixels, c, 1e-3, 1.0, mean2, inv2, None)   # the power is optional
+    ctx.norm_whiten(plb_t, dx, mean, inv, pixels, c, white)
+    ctx.norm_scale_shift(plb_t, white, dgamma, dbeta, pixels, c, out)
+    ctx.norm_normalise(plb_t, dx, mean, inv, dgamma, dbeta, pixels, c, white2, out2)
+    ctx.norm_normalise(plb_t, dx, mean, inv, dgamma, dbeta, pixels, c, None, out3)
+    ctx.synchronize()
+    assert torch.equal(inv, inv2)
+    assert torch.equal(white, white2), "whitened activations"
+    assert torch.equal(out, out2) and torch.equal(out, out3), "normalised activations"
