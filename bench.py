@@ -607,6 +607,38 @@ def roofline_of(name, spec, flops, nbytes, ms_per_step, peaks, peak_src):
             "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": nbytes}
 
 
+def measure_memory_mix(stream_bytes=1 << 29, reps=20):
+    """TB/s of the library's streaming probe (plb_memory_mix_probe: one grid-stride
+    kernel of 16-byte accesses) for mixes of read and write streams of 512 MB
+    each, timed with CUDA events over `reps` launches after 3 warm-up launches.
+    Prints one JSON line."""
+    import torch
+    from poplibs_b200 import capi
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.Stream(device=dev)
+    ctx = capi.Context(0, stream=stream.cuda_stream)
+    src = torch.empty(stream_bytes, dtype=torch.uint8, device=dev)
+    dst = torch.empty(4 * stream_bytes, dtype=torch.uint8, device=dev)
+    src.random_(0, 255)
+    out = {}
+    for name, reads, writes in (("write_only", 0, 1), ("read_only", 1, 0), ("copy_1r_1w", 1, 1),
+                                ("1r_2w", 1, 2), ("1r_4w", 1, 4)):
+        for _ in range(3):
+            ctx.memory_mix_probe(reads, writes, stream_bytes, src, dst)
+        ctx.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            start.record()
+            for _ in range(reps):
+                ctx.memory_mix_probe(reads, writes, stream_bytes, src, dst)
+            end.record()
+        end.synchronize()
+        out[name] = round((reads + writes) * stream_bytes * reps / (start.elapsed_time(end) * 1e-3) / 1e12, 3)
+    print(json.dumps({"memory_mix_tb_per_s": out, "stream_bytes": stream_bytes, "reps": reps,
+                      "kernel": "plb_memory_mix_probe (grid-stride, 16-byte accesses, 16 blocks of 512 threads per SM)"}))
+
+
 def measure_fp8_peak(n=8192, sustained_s=4.0):
     """Dense e4m3 x e4m3 -> bf16 GEMM of the vendor library on n^3: best of 10
     launches (burst) and back to back for `sustained_s` seconds (sustained),
@@ -671,10 +703,17 @@ def main():
                     help="measure the dense fp8 (e4m3) peak of this GPU with the library GEMM "
                          "(torch._scaled_mm, 8192^3) and print it: the roofline denominator of the "
                          "fp8 workloads, not a result of this library")
+    ap.add_argument("--measure-memory-mix", action="store_true",
+                    help="measure what a streaming kernel of 16-byte accesses gets from the memory system "
+                         "for several mixes of reads and writes (write only ... one read per four writes) "
+                         "and print it: context for the fractions of the HBM-bound workloads")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.measure_fp8_peak:
         measure_fp8_peak()
+        return
+    if args.measure_memory_mix:
+        measure_memory_mix()
         return
 
     rank = int(os.environ.get("RANK", "0"))

@@ -504,6 +504,13 @@ PLB_API int plb_copy_strided(plb_context *ctx, uint32_t elem_bytes, uint32_t ran
                      void *d_dst);
 /* Fills `count` elements of type `dtype` (PLB_HALF / PLB_FLOAT) with `value`. */
 PLB_API int plb_fill(plb_context *ctx, int32_t dtype, void *d_dst, float value, size_t count);
+/* Streaming probe of the memory system, for roofline denominators that match a
+ * kernel's mix of reads and writes: one grid-stride kernel of 16-byte accesses
+ * that reads `reads` (0 or 1) and writes `writes` (0..4) streams of `bytes`
+ * bytes each (d_in: `bytes`; d_out: writes * bytes; both 16-byte aligned).
+ * Timed by the caller (plb_timer_start / plb_timer_stop). */
+PLB_API int plb_memory_mix_probe(plb_context *ctx, int32_t reads, int32_t writes, size_t bytes,
+                         const void *d_in, void *d_out);
 /* Device-side stopwatch on the context's stream (CUDA events). */
 PLB_API int plb_timer_start(plb_context *ctx);
 PLB_API int plb_timer_stop(plb_context *ctx, float *milliseconds);

@@ -149,7 +149,7 @@ SYMBOLS = (
     "plb_rearrange_acts_to_device", "plb_rearrange_acts_from_device",
     "plb_rearrange_weights_to_device", "plb_rearrange_weights_from_device",
     "plb_weights_transpose_chans_flip_xy", "plb_transpose_matrix", "plb_matmul_plan",
-    "plb_conv_plan", "plb_conv_wu_plan", "plb_copy_strided", "plb_fill", "plb_timer_start", "plb_timer_stop",
+    "plb_conv_plan", "plb_conv_wu_plan", "plb_copy_strided", "plb_fill", "plb_timer_start", "plb_timer_stop", "plb_memory_mix_probe",
 )
 
 
@@ -170,6 +170,7 @@ def lib():
     L.plb_context_create.argtypes = [C.c_int, C.POINTER(vp)]
     L.plb_context_create_on_stream.argtypes = [C.c_int, vp, C.POINTER(vp)]
     L.plb_device_pci_address.argtypes = [C.c_int, C.c_char_p, sz]
+    L.plb_memory_mix_probe.argtypes = [vp, i32, i32, sz, vp, vp]
     L.plb_context_destroy.argtypes = [vp]
     L.plb_context_destroy.restype = None
     L.plb_context_stream.argtypes = [vp]
@@ -424,6 +425,10 @@ class Context:
     def norm_inv_std_dev(self, dtype, mean, power, chans, eps, scale_var, stable, inv_std):
         _check(lib().plb_norm_inv_std_dev(self._h, dtype, _ptr(mean), _ptr(power), chans, eps, scale_var,
                                           int(stable), _ptr(inv_std)))
+
+    def memory_mix_probe(self, reads, writes, nbytes, src, dst):
+        """One streaming pass: `reads` (0/1) read and `writes` (0..4) write streams of nbytes each."""
+        _check(lib().plb_memory_mix_probe(self._h, reads, writes, nbytes, _ptr(src), _ptr(dst)))
 
     def norm_statistics(self, dtype, acts, pixels, chans, eps, scale_var, mean, inv_std, power=None):
         """Mean and 1/sigma per channel in one call (the default estimator)."""

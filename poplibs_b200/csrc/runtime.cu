@@ -588,6 +588,24 @@ using namespace plb;
 // ---------------------------------------------------------------------------
 // C ABI: context and memory
 // ---------------------------------------------------------------------------
+namespace plb {
+// Streams of 16-byte accesses: reads one (optional), writes up to four.
+__global__ void __launch_bounds__(512)
+memoryMixKernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, size_t n, int reads, int writes) {
+  uint32_t sink = 0;
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
+    uint4 v = reads ? in[i] : make_uint4(uint32_t(i), uint32_t(i >> 3), uint32_t(i) * 2654435761u, 7u);
+    for (int w = 0; w < writes; ++w) {
+      out[size_t(w) * n + i] = v;
+      v.x ^= 1u;
+    }
+    sink ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+  // a read-only run keeps its loads alive through a store that never happens
+  if (writes == 0 && sink == 0x9e3779b9u && n == 1) out[0] = make_uint4(sink, 0, 0, 0);
+}
+}  // namespace plb
+
 extern "C" {
 
 const char *plb_last_error(void) { return g_last_error.c_str(); }
@@ -932,6 +950,24 @@ int plb_timer_start(plb_context *ctx) {
     PLB_CUDA(cudaEventCreate(&ctx->timer_stop));
   }
   PLB_CUDA(cudaEventRecord(ctx->timer_start, ctx->stream));
+  return PLB_OK;
+}
+
+int plb_memory_mix_probe(plb_context *ctx, int32_t reads, int32_t writes, size_t bytes,
+                         const void *d_in, void *d_out) {
+  if (int rc = activate(ctx)) return rc;
+  if (reads < 0 || reads > 1 || writes < 0 || writes > 4 || reads + writes == 0 || bytes % 16 != 0)
+    return fail(PLB_ERR_INVALID_PARAMS, "memory probe: 0-1 read and 0-4 write streams of a multiple of 16 bytes");
+  if ((reads && !d_in) || (writes && !d_out) || (reinterpret_cast<uintptr_t>(d_in) & 15) ||
+      (reinterpret_cast<uintptr_t>(d_out) & 15))
+    return fail(PLB_ERR_INVALID_PARAMS, "memory probe: null or unaligned buffer");
+  const size_t n = bytes / 16;
+  if (n == 0) return PLB_OK;
+  const int grid = ctx->sm_count * 16;
+  plb::memoryMixKernel<<<grid, 512, 0, ctx->stream>>>(static_cast<const uint4 *>(d_in),
+                                                      static_cast<uint4 *>(d_out), n, reads, writes);
+  PLB_CUDA(cudaGetLastError());
+  ctx->launches++;
   return PLB_OK;
 }
 
